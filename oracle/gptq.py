@@ -1,0 +1,342 @@
+"""Oracle: damped inverse-Hessian factor and the ``fasterquant`` block loop.
+
+Test infrastructure (see ``oracle/__init__.py``).  Restates
+
+* plain GPTQ ``fasterquant``                      gptq_utils/gptq_utils.py:45-174
+* ``_compute_hessian_inverse_with_fallback``      gptq_utils/gptq_plus_utils.py:494-561
+* ``compute_safe_beta_from_reference_loss``       gptq_utils/gptq_plus_utils.py:174-194
+* ``_compute_gradient_terms``                     gptq_utils/gptq_plus_utils.py:563-578
+* GPTQ+ ``fasterquant`` (set-up, inner column loop, lazy trailing update, epilogue) for
+  the modes that need no autograd callback: ``frozen``, ``surrogate_block``,
+  ``surrogate_online``, with or without ``block_atomic_quant``
+                                                  gptq_utils/gptq_plus_utils.py:910-1896
+"""
+from __future__ import annotations
+
+import copy
+
+import torch
+
+LinAlgError = torch._C._LinAlgError
+
+
+# --------------------------------------------------------------------------------------
+# damped Cholesky -> inverse -> upper factor
+# --------------------------------------------------------------------------------------
+def hinv_with_fallback(H_sub: torch.Tensor, percdamp: float = 0.01, step: float = 0.0015):
+    """(Hinv_init, Hinv_upper, damp_percent, identity_fallback).
+
+    Damping ``p * mean(diag)`` is added to the *already damped* working matrix on every
+    retry and the mean is re-taken from it; a failed or non-finite factorisation bumps
+    ``p`` by ``step``; at ``p >= 1`` both results are the identity
+    (gptq_plus_utils.py:494-561).
+    """
+    p = float(percdamp)
+    if p <= 0:
+        raise ValueError("damp_percent must be positive")
+    work = H_sub.clone()
+    idx = torch.arange(work.shape[0])
+    while 0 < p < 1:
+        try:
+            work[idx, idx] += p * torch.mean(torch.diag(work))
+            low = torch.linalg.cholesky(work)
+            inv = torch.cholesky_inverse(low)
+            up = torch.linalg.cholesky(inv, upper=True)
+            if not torch.isfinite(inv).all() or not torch.isfinite(up).all():
+                raise LinAlgError("non-finite inverse")
+            return inv, up, p, False
+        except LinAlgError:
+            p += step
+    eye = torch.eye(H_sub.shape[0], dtype=H_sub.dtype)
+    return eye, eye.clone(), p, True
+
+
+def plain_hinv(H: torch.Tensor, percdamp: float = 0.01, step: float = 0.0015) -> torch.Tensor:
+    """Upper factor of the damped inverse as plain GPTQ builds it; ``H`` is damped in
+    place like the reference; running out of range raises (gptq_utils.py:88-106)."""
+    p = percdamp
+    n = H.shape[0]
+    idx = torch.arange(n)
+    while 0 < p < 1:
+        try:
+            H[idx, idx] += p * torch.mean(torch.diag(H))
+            low = torch.linalg.cholesky(H)
+            inv = torch.cholesky_inverse(low)
+            return torch.linalg.cholesky(inv, upper=True)
+        except LinAlgError:
+            p += step
+    raise ValueError(f"Quantization: `damp_percent` must between 0 and 1. current is {p}")
+
+
+# --------------------------------------------------------------------------------------
+# GPTQ+ first-order terms
+# --------------------------------------------------------------------------------------
+def safe_beta(grad_sub, hinv_init, reference_loss: float, alpha: float):
+    """Per-row beta in [0, 1] and ``G . H^-1`` (gptq_plus_utils.py:174-194)."""
+    ghinv_init = grad_sub.matmul(hinv_init)
+    if reference_loss <= 0:
+        return torch.zeros(grad_sub.shape[0], dtype=grad_sub.dtype), ghinv_init
+    c = (grad_sub * ghinv_init).sum(dim=1) - ((ghinv_init ** 2) / torch.diagonal(hinv_init).unsqueeze(0)).mean(1)
+    target = 2 * alpha * reference_loss
+    c = torch.clamp(c, min=target)
+    ratio = torch.where(c > 0, target / c, torch.zeros_like(c))
+    ratio = torch.clamp(ratio, min=0.0, max=1.0)
+    beta = 1 - torch.sqrt(torch.clamp(1 - ratio, min=0.0))
+    return torch.nan_to_num(beta, nan=0.0, posinf=1.0, neginf=0.0), ghinv_init
+
+
+def gradient_terms(grad_sub, hinv_init, hinv, alpha: float, reference_loss: float,
+                   rows: int, columns: int, enable: bool = True):
+    """(beta, beta_view, Z, GHinv) with ``alpha_eff = alpha / (rows*columns)``; a
+    non-positive alpha or a disabled update gives a single zero beta, hence Z = GHinv = 0
+    (gptq_plus_utils.py:563-578)."""
+    if enable and alpha > 0:
+        beta, _ = safe_beta(grad_sub, hinv_init, reference_loss, alpha / (rows * columns))
+    else:
+        beta = torch.zeros([1], dtype=grad_sub.dtype)
+    bview = beta.unsqueeze(1)
+    Z = grad_sub.matmul(hinv.T) * bview
+    return beta, bview, Z, Z.matmul(hinv)
+
+
+# --------------------------------------------------------------------------------------
+# plain GPTQ
+# --------------------------------------------------------------------------------------
+def plain_fasterquant(weight: torch.Tensor, H: torch.Tensor, quantizer, blocksize=128, percdamp=0.01,
+                      groupsize=-1, actorder=False, static_groups=False):
+    """Returns dict(Q, W_int, Scale, perm) for a plain-GPTQ linear (gptq_utils.py:45-174).
+
+    ``Q`` is un-permuted like the layer weight the reference writes; ``W_int`` and
+    ``Scale`` stay in the permuted column order, exactly as the reference registers
+    them under ``export_to_et`` (:147-166).
+    """
+    W = weight.clone().float()
+    Scale = weight.clone().float()
+    W_int = weight.clone().float()
+    columns = W.shape[1]
+    if not quantizer.ready():
+        quantizer.find_params(W)
+    H = H.clone()
+    if (H == 0).all():
+        H = torch.eye(columns)
+    dead = torch.diag(H) == 0
+    H[dead, dead] = 1
+    W[:, dead] = 0
+
+    groups = None
+    if static_groups:
+        groups = []
+        for i in range(0, columns, groupsize):
+            q = copy.deepcopy(quantizer)
+            q.find_params(W[:, i:i + groupsize])
+            groups.append(q)
+
+    perm = None
+    if actorder:
+        perm = torch.argsort(torch.diag(H), descending=True)
+        W = W[:, perm]
+        H = H[perm][:, perm]
+        invperm = torch.argsort(perm)
+
+    Q = torch.zeros_like(W)
+    Hinv = plain_hinv(H, percdamp)
+
+    for i1 in range(0, columns, blocksize):
+        i2 = min(i1 + blocksize, columns)
+        W1 = W[:, i1:i2].clone()
+        Q1 = torch.zeros_like(W1)
+        Wi1 = torch.zeros_like(W1)
+        S1 = torch.zeros_like(W1)
+        Err1 = torch.zeros_like(W1)
+        Hinv1 = Hinv[i1:i2, i1:i2]
+        for i in range(i2 - i1):
+            w = W1[:, i]
+            d = Hinv1[i, i]
+            if groupsize != -1:
+                if not static_groups:
+                    if (i1 + i) % groupsize == 0:
+                        quantizer.find_params(W[:, (i1 + i):(i1 + i + groupsize)])
+                else:
+                    idx = i1 + i
+                    if actorder:
+                        idx = perm[idx]
+                    quantizer = groups[idx // groupsize]
+            q, codes, scale = quantizer.fake_quantize(w.unsqueeze(1))
+            q = q.flatten()
+            Q1[:, i] = q
+            Wi1[:, i] = codes.flatten()
+            S1[:, i] = scale.flatten()
+            err = (w - q) / d
+            W1[:, i:] -= err.unsqueeze(1).matmul(Hinv1[i, i:].unsqueeze(0))
+            Err1[:, i] = err
+        Q[:, i1:i2] = Q1
+        W_int[:, i1:i2] = Wi1
+        Scale[:, i1:i2] = S1
+        W[:, i2:] -= Err1.matmul(Hinv[i1:i2, i2:])
+
+    if actorder:
+        Q = Q[:, invperm]
+    return {"Q": Q, "W_int": W_int, "Scale": Scale, "perm": perm, "Hinv": Hinv}
+
+
+# --------------------------------------------------------------------------------------
+# GPTQ+
+# --------------------------------------------------------------------------------------
+def _effective_ghinv(base, cur_w, ref_w, bview, mode):
+    """gptq_plus_utils.py:580-584."""
+    if mode == "frozen":
+        return base
+    return base + bview * (cur_w - ref_w)
+
+
+def plus_fasterquant(weight, H, act_square, gradients, quantizer, num_groups, alpha, reference_loss,
+                     blocksize=128, percdamp=0.01, groupsize=-1, actorder=False, static_groups=False,
+                     enable_gradient_update=True, g_update_mode="frozen", block_atomic_quant=False):
+    """GPTQ+ quantization of one linear (gptq_plus_utils.py:910-1896) for the callback-free
+    modes.  ``H`` is the finalised ``[G, C, C]`` Hessian.  Returns dict(Q, W_int, Scale,
+    perm, states) with all three matrices in the layer's natural column order (:1850-1866).
+    """
+    assert g_update_mode in ("frozen", "surrogate_block", "surrogate_online")
+    W = weight.clone().float()
+    rows, columns = W.shape
+    Q_final = torch.zeros_like(W)
+    Wint_final = torch.zeros_like(W)
+    Scale_final = torch.zeros_like(W)
+    if not quantizer.ready():
+        quantizer.find_params(W)
+
+    dynamic_groups = groupsize != -1 and not static_groups
+    if dynamic_groups and groupsize != blocksize:
+        raise ValueError("`groupsize` must equal `blocksize` when using dynamic groups in GPTQ+.")
+
+    shared_groups = None
+    if groupsize != -1 and static_groups:                       # all rows, before dead-zeroing (:995-1002)
+        shared_groups = []
+        for c0 in range(0, columns, groupsize):
+            q = copy.deepcopy(quantizer)
+            q.find_params(W[:, c0:min(c0 + groupsize, columns)])
+            shared_groups.append(q)
+
+    fast = groupsize == -1 and quantizer.bits < 16 and quantizer.ready()
+    maxq = int(quantizer.maxq)
+    rps = rows // num_groups
+    states = []
+    for g in range(num_groups):
+        r0, r1 = g * rps, (g + 1) * rps
+        W_sub = W[r0:r1].clone()
+        H_sub = H[g].clone()
+        G_sub = gradients[r0:r1].float().clone()
+        dead = torch.diag(H_sub) == 0
+        H_sub[dead, dead] = 1
+        W_sub[:, dead] = 0
+        perm = invperm = None
+        if actorder:
+            perm = torch.argsort(act_square, descending=True)
+            W_sub = W_sub[:, perm]
+            H_sub = H_sub[perm][:, perm]
+            G_sub = G_sub[:, perm]
+            invperm = torch.argsort(perm)
+        hinv_init, hinv, damp, ident = hinv_with_fallback(H_sub, percdamp)
+        beta, bview, Z, GHinv = gradient_terms(G_sub, hinv_init, hinv, alpha, max(reference_loss, 0),
+                                               rows, columns, enable_gradient_update)
+        states.append(dict(r0=r0, r1=r1, W_sub=W_sub, Hinv=hinv, Hinv_init=hinv_init, beta=beta, bview=bview,
+                           Z=Z, GHinv=GHinv, anchor=W_sub.clone(), Q=torch.zeros_like(W_sub),
+                           Wint=torch.zeros_like(W_sub), Scale=torch.zeros_like(W_sub), perm=perm,
+                           invperm=invperm, damp=damp, identity=ident,
+                           fast_scale=quantizer.scale[r0:r1] if fast else None))
+
+    inner_mode = g_update_mode
+    outer_mode = "frozen" if g_update_mode == "frozen" else "surrogate_block"
+    for i1 in range(0, columns, blocksize):
+        i2 = min(i1 + blocksize, columns)
+        count = i2 - i1
+        atomic = block_atomic_quant and not (i2 >= columns)
+        D = torch.arange(count - 1, -1, -1).to(W)
+        per_block = []
+        for st in states:
+            W1 = st["W_sub"][:, i1:i2].clone()
+            Wref1 = st["anchor"][:, i1:i2]
+            Wstart = W1.clone()
+            Q1 = torch.zeros_like(W1)
+            Wi1 = torch.zeros_like(W1)
+            S1 = torch.zeros_like(W1)
+            Err1 = torch.zeros_like(W1)
+            Hinv1 = st["Hinv"][i1:i2, i1:i2]
+            GH1 = st["GHinv"][:, i1:i2].clone()
+            Z1 = st["Z"][:, i1:i2]
+            online = inner_mode == "surrogate_online"
+            GH1_eff = _effective_ghinv(GH1, W1 if online else Wstart, Wref1, st["bview"], inner_mode)
+            dyn_q = None
+            if dynamic_groups:
+                dyn_q = copy.deepcopy(quantizer)
+                dyn_q.find_params(Wstart)
+            if st["fast_scale"] is not None:
+                S1.copy_(st["fast_scale"].expand_as(S1))
+
+            def column_quantizer(i):
+                if dyn_q is not None:
+                    return dyn_q, None, None
+                if groupsize != -1:
+                    idx = i1 + i
+                    if actorder:
+                        idx = st["perm"][idx]
+                    return shared_groups[idx // groupsize], st["r0"], st["r1"]
+                return quantizer, st["r0"], st["r1"]
+
+            if atomic:
+                if groupsize == -1:
+                    q, codes, scale = quantizer.fake_quantize(Wstart, st_idx=st["r0"], end_idx=st["r1"])
+                    Q1.copy_(q)
+                    Wi1.copy_(codes)
+                    S1.copy_(scale.expand_as(Wstart))
+                else:
+                    for i in range(count):
+                        qz, a, b = column_quantizer(i)
+                        q, codes, scale = qz.fake_quantize(Wstart[:, i].unsqueeze(1), st_idx=a, end_idx=b)
+                        Q1[:, i] = q.flatten()
+                        Wi1[:, i] = codes.flatten()
+                        S1[:, i] = scale.flatten()
+                Err1.copy_(torch.linalg.solve_triangular(Hinv1.T, (Wstart - Q1 - GH1_eff).T, upper=False).T)
+            else:
+                for i in range(count):
+                    w = W1[:, i]
+                    d = Hinv1[i, i]
+                    wc = w.unsqueeze(1)
+                    if st["fast_scale"] is not None:
+                        codes = torch.clamp(torch.round(wc / st["fast_scale"]), -(maxq + 1), maxq)
+                        qf = (st["fast_scale"] * codes).to(wc.dtype)
+                    else:
+                        qz, a, b = column_quantizer(i)
+                        qf, codes, scale = qz.fake_quantize(wc, st_idx=a, end_idx=b)
+                        S1[:, i] = scale.flatten()
+                    q = qf.flatten()
+                    Q1[:, i] = q
+                    Wi1[:, i] = codes.flatten()
+                    err = (w - q - GH1_eff[:, i]) / d
+                    W1[:, i:] -= err.unsqueeze(1).matmul(Hinv1[i, i:].unsqueeze(0)) + GH1_eff[:, i:]
+                    Err1[:, i] = err
+                    GH1[:, i:].sub_(Z1[:, i].unsqueeze(1).matmul(Hinv1[i, i:].unsqueeze(0)))
+                    if inner_mode != "frozen":
+                        GH1_eff = _effective_ghinv(GH1, W1 if online else Wstart, Wref1, st["bview"], inner_mode)
+            st["Q"][:, i1:i2] = Q1
+            st["Wint"][:, i1:i2] = Wi1
+            st["Scale"][:, i1:i2] = S1
+            per_block.append((st, Err1, Z1))
+
+        for st, Err1, Z1 in per_block:                                    # lazy update (:1500-1570)
+            rest = _effective_ghinv(st["GHinv"][:, i2:], st["W_sub"][:, i2:], st["anchor"][:, i2:],
+                                    st["bview"], outer_mode)
+            g_update = count * rest - torch.einsum("ij,j,jk->ik", Z1, D, st["Hinv"][i1:i2, i2:])
+            second = Err1.matmul(st["Hinv"][i1:i2, i2:])
+            st["W_sub"][:, i2:] -= second + g_update
+            st["GHinv"][:, i2:] -= st["Z"][:, i1:i2].matmul(st["Hinv"][i1:i2, i2:])
+
+    for st in states:
+        Qs, Wi, Sc = st["Q"], st["Wint"], st["Scale"]
+        if actorder:
+            Qs, Wi, Sc = Qs[:, st["invperm"]], Wi[:, st["invperm"]], Sc[:, st["invperm"]]
+        Q_final[st["r0"]:st["r1"]] = Qs
+        Wint_final[st["r0"]:st["r1"]] = Wi
+        Scale_final[st["r0"]:st["r1"]] = Sc
+    return {"Q": Q_final, "W_int": Wint_final, "Scale": Scale_final,
+            "perm": states[0]["perm"], "states": states}

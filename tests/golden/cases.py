@@ -1,0 +1,109 @@
+"""Seeded input generators shared by the golden-fixture script and the tests.
+
+The value distributions mirror the benchmark configurations at small sizes:
+weights ~ N(0, 0.02^2) with a few input columns scaled x10, activations ~ N(0, 1)
+times per-channel log-normal(0, 1) scales, per-token per-group saliency ~
+log-normal(0, 3) clipped at its 99th percentile (the reference clips the same way,
+gptq_utils/gptq_plus_utils.py:2834-2839), weight gradient ~ N(0, 1e-4^2).
+"""
+from __future__ import annotations
+
+import hashlib
+
+import numpy as np
+import torch
+
+
+def _gen(seed: int) -> torch.Generator:
+    g = torch.Generator(device="cpu")
+    g.manual_seed(seed)
+    return g
+
+
+def make_weight(rows: int, cols: int, seed: int, outlier_frac: float = 0.02) -> torch.Tensor:
+    g = _gen(seed)
+    W = torch.randn(rows, cols, generator=g) * 0.02
+    n_out = max(1, int(round(cols * outlier_frac)))
+    idx = torch.randperm(cols, generator=g)[:n_out]
+    W[:, idx] *= 10.0
+    return W
+
+
+def make_acts(nseq: int, seqlen: int, cols: int, seed: int, dtype=torch.float32) -> torch.Tensor:
+    g = _gen(seed + 1000)
+    ch = torch.exp(torch.randn(cols, generator=g))
+    X = torch.randn(nseq, seqlen, cols, generator=g) * ch
+    return X.to(dtype)
+
+
+def make_saliency(nseq: int, seqlen: int, groups: int, seed: int) -> torch.Tensor:
+    g = _gen(seed + 2000)
+    s = torch.exp(3.0 * torch.randn(nseq, seqlen, groups, generator=g))
+    cap = torch.quantile(s.flatten().double(), 0.99).float()
+    return torch.clamp(s, max=cap)
+
+
+def make_grad(rows: int, cols: int, seed: int, std: float = 1e-4) -> torch.Tensor:
+    g = _gen(seed + 3000)
+    return torch.randn(rows, cols, generator=g) * std
+
+
+def digest(*tensors) -> str:
+    """Short content hash of the generated inputs; stored in each fixture so that a
+    drift of the generators (other torch build, edited code) is reported as such
+    rather than as a parity failure."""
+    h = hashlib.sha256()
+    for t in tensors:
+        h.update(np.ascontiguousarray(t.detach().float().numpy()).tobytes())
+    return h.hexdigest()[:16]
+
+
+# ---------------------------------------------------------------------------------------
+# case tables (small enough for the pure-CPU reference to finish in seconds)
+# ---------------------------------------------------------------------------------------
+QUANTIZER_CASES = [
+    # name, rows, cols, bits, perchannel, sym, mse
+    ("w4_sym_pc", 48, 256, 4, True, True, False),
+    ("w4_asym_pc", 48, 256, 4, True, False, False),
+    ("w3_sym_pc", 40, 200, 3, True, True, False),
+    ("w4_sym_pt", 24, 96, 4, False, True, False),
+    ("w4_sym_pc_mse", 32, 128, 4, True, True, True),
+    ("w4_asym_pc_mse", 32, 128, 4, True, False, True),
+    ("w8_asym_pt", 16, 64, 8, False, False, False),
+]
+
+HADAMARD_CASES = [
+    # name, rows, n, dtype
+    ("n128_f32", 37, 128, "float32"),
+    ("n1024_f32", 9, 1024, "float32"),
+    ("n4096_f32", 3, 4096, "float32"),
+    ("n96_f32_k12", 21, 96, "float32"),
+    ("n1536_f32_k12", 5, 1536, "float32"),
+    ("n640_f32_k20", 6, 640, "float32"),
+    ("n896_f32_k28", 6, 896, "float32"),
+    ("n1024_bf16", 9, 1024, "bfloat16"),
+    ("n1536_bf16_k12", 5, 1536, "bfloat16"),
+    ("n512_f16", 4, 512, "float16"),
+]
+
+PLAIN_CASES = [
+    # name, rows, cols, nseq, seqlen, bits, sym, groupsize, actorder, static_groups, blocksize
+    ("plain_pc_act", 48, 256, 4, 96, 4, False, -1, True, True, 128),
+    ("plain_pc_noact", 48, 256, 4, 96, 4, True, -1, False, False, 128),
+    ("plain_g64_static_act", 32, 256, 4, 96, 4, True, 64, True, True, 128),
+    ("plain_g128_dynamic", 32, 256, 3, 96, 4, True, 128, False, False, 128),
+    ("plain_ragged_block", 24, 200, 3, 80, 3, True, -1, True, True, 128),
+]
+
+PLUS_CASES = [
+    # name, rows, cols, nseq, seqlen, G, bits, groupsize, actorder, static, alpha, ref_loss, mode, atomic
+    ("plus_frozen_pc", 64, 256, 4, 96, 4, 4, -1, True, True, 0.25, 0.7, "frozen", False),
+    ("plus_frozen_alpha0", 64, 256, 4, 96, 4, 4, -1, True, True, 0.0, 0.7, "frozen", False),
+    ("plus_frozen_g128_static", 32, 256, 4, 96, 2, 4, 128, True, True, 0.25, 0.7, "frozen", False),
+    ("plus_frozen_g128_dynamic", 32, 256, 4, 96, 2, 4, 128, False, False, 0.25, 0.7, "frozen", False),
+    ("plus_frozen_w3_noact", 32, 384, 3, 64, 4, 3, -1, False, False, 0.5, 0.3, "frozen", False),
+    ("plus_surrogate_block", 32, 256, 4, 96, 2, 4, -1, True, True, 0.25, 0.7, "surrogate_block", False),
+    ("plus_surrogate_online", 32, 256, 4, 96, 2, 4, -1, True, True, 0.25, 0.7, "surrogate_online", False),
+    ("plus_atomic", 32, 256, 4, 96, 2, 4, -1, True, True, 0.25, 0.7, "frozen", True),
+    ("plus_ragged", 32, 200, 3, 80, 4, 4, -1, True, True, 0.25, 0.7, "frozen", False),
+]

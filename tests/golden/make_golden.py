@@ -1,0 +1,204 @@
+"""Generate the golden fixtures of this directory from the UNMODIFIED reference.
+
+Run where the reference checkout is mounted (it cannot travel to the GPU box):
+
+    python tests/golden/make_golden.py [--ref /path/to/gptq_plus_mp_quant]
+
+The script imports the reference's own classes (``GPTQ``, ``GPTQPlus``,
+``WeightQuantizer``, ``hadamard_utils``) on CPU, feeds them the seeded inputs of
+``cases.py`` and stores their outputs in ``*.npz`` files next to this script.  The
+only accommodations, none of which edits the reference: ``transformers`` is imported
+first, the absent ``accelerate`` package is stubbed, and the CUDA-only calls
+``torch.cuda.synchronize`` / ``memory_utils.cleanup_memory`` are turned into no-ops.
+"""
+from __future__ import annotations
+
+import argparse
+import os
+import sys
+import types
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, HERE)
+import cases  # noqa: E402
+
+
+def import_reference(ref_root: str):
+    import transformers  # noqa: F401  (must precede the reference's own imports)
+    for name, attrs in (("accelerate", ("dispatch_model", "infer_auto_device_map")),
+                        ("accelerate.utils", ("get_balanced_memory",)),
+                        ("accelerate.hooks", ("remove_hook_from_module",))):
+        if name not in sys.modules:
+            mod = types.ModuleType(name)
+            for a in attrs:
+                setattr(mod, a, lambda *args, **kw: None)
+            sys.modules[name] = mod
+    sys.path.insert(0, ref_root)
+    from utils import quant_utils, hadamard_utils, memory_utils
+    from gptq_utils import gptq_utils, gptq_plus_utils
+    torch.cuda.synchronize = lambda *a, **k: None
+    memory_utils.cleanup_memory = lambda *a, **k: None
+    return quant_utils, hadamard_utils, gptq_utils, gptq_plus_utils
+
+
+# cases whose full Hessian / inverse factor is stored (the rest keep only the small outputs)
+HEAVY = {"plain_pc_act", "plain_ragged_block", "plus_frozen_pc", "plus_ragged"}
+
+
+def np32(t):
+    return t.detach().float().cpu().clone().numpy()       # clone: later in-place edits must not leak in
+
+
+def gen_quantizer(qu, out):
+    for name, rows, cols, bits, pc, sym, mse in cases.QUANTIZER_CASES:
+        W = cases.make_weight(rows, cols, seed=11)
+        q = qu.WeightQuantizer()
+        q.configure(bits, perchannel=pc, sym=sym, mse=mse)
+        q.find_params(W)
+        deq, codes, scale = q.fake_quantize(W)
+        ste = q.quantize(W)
+        out[f"{name}.digest"] = np.array(cases.digest(W))
+        out[f"{name}.scale"] = np32(q.scale)
+        out[f"{name}.zero"] = np32(q.zero)
+        out[f"{name}.maxq"] = np.array(int(q.maxq))
+        out[f"{name}.fake_deq"] = np32(deq)
+        out[f"{name}.fake_codes"] = np32(codes)
+        out[f"{name}.ste"] = np32(ste)
+
+
+def gen_hadamard(hu, out):
+    had_tab = torch.load(os.path.join(os.path.dirname(hu.__file__), "had_mat.pt"))
+    for k in (12, 20, 28):
+        out[f"had{k}"] = np32(had_tab[k]).astype(np.int8)
+    out["table_keys"] = np.array(sorted(had_tab.keys()))
+    for name, rows, n, dtype in cases.HADAMARD_CASES:
+        dt = getattr(torch, dtype)
+        x = cases.make_acts(1, rows, n, seed=5).reshape(rows, n).to(dt)
+        hadK, K = hu.get_hadK(n)
+        y_cuda_form = hu.matmul_hadU_cuda(x.clone(), hadK, K)      # FWHT chunks + hadK mix
+        y_strided = hu.matmul_hadU(x.clone())                      # strided radix-2 form
+        out[f"{name}.digest"] = np.array(cases.digest(x))
+        out[f"{name}.K"] = np.array(K)
+        out[f"{name}.y"] = np32(y_cuda_form)
+        out[f"{name}.y_strided"] = np32(y_strided)
+
+
+class _Lin(torch.nn.Module):
+    def __init__(self, W):
+        super().__init__()
+        self.weight = torch.nn.Parameter(W.clone(), requires_grad=False)
+
+
+def gen_plain(qu, gu, out):
+    for (name, rows, cols, nseq, seqlen, bits, sym, gs, act, static, bs) in cases.PLAIN_CASES:
+        W = cases.make_weight(rows, cols, seed=21)
+        X = cases.make_acts(nseq, seqlen, cols, seed=21)
+        if "ragged" in name:
+            X[..., 7] = 0.0                                         # a dead input channel
+        layer = _Lin(W)
+        g = gu.GPTQ(layer)
+        g.quantizer = qu.WeightQuantizer()
+        g.quantizer.configure(bits, perchannel=True, sym=sym, mse=False)
+        for s in range(nseq):
+            g.add_batch(X[s:s + 1], None)
+        out[f"{name}.digest"] = np.array(cases.digest(W, X))
+        if name in HEAVY:
+            out[f"{name}.H"] = np32(g.H)
+        g.fasterquant(blocksize=bs, percdamp=0.01, groupsize=gs, actorder=act, static_groups=static,
+                      export_to_et=True)
+        out[f"{name}.Q"] = np32(layer.weight.data)
+        out[f"{name}.W_int"] = np32(layer.int_weight).astype(np.int8)
+        out[f"{name}.Scale"] = np32(layer.scale)
+
+
+def gen_plus(qu, gpu, out):
+    for (name, rows, cols, nseq, seqlen, G, bits, gs, act, static, alpha, ref_loss, mode, atomic) in cases.PLUS_CASES:
+        W = cases.make_weight(rows, cols, seed=31)
+        X = cases.make_acts(nseq, seqlen, cols, seed=31)
+        if "ragged" in name:
+            X[..., 5] = 0.0
+        S = cases.make_saliency(nseq, seqlen, G, seed=31)
+        Gr = cases.make_grad(rows, cols, seed=31)
+        layer = _Lin(W)
+        g = gpu.GPTQPlus(layer, S, Gr, G, alpha, ref_loss)
+        g.quantizer = qu.WeightQuantizer()
+        g.quantizer.configure(bits, perchannel=True, sym=True, mse=False)
+        g.add_batch(X[:1], None)
+        g.add_batch(X[1:], None)
+        act_sum = g.act_square.clone()
+        g.finalize_hessian()
+        out[f"{name}.digest"] = np.array(cases.digest(W, X, S, Gr))
+        out[f"{name}.act_sum"] = np32(act_sum)
+        if name in HEAVY:
+            out[f"{name}.H"] = np32(g.H)
+        out[f"{name}.act_square"] = np32(g.act_square)
+        # inverse factor and first-order terms of sub-group 0, as fasterquant derives them
+        H0 = g.H[0].clone()
+        dead = torch.diag(H0) == 0
+        H0[dead, dead] = 1
+        G0 = Gr[: rows // G].clone()
+        if act:
+            perm = torch.argsort(g.act_square, descending=True)
+            H0 = H0[perm][:, perm]
+            G0 = G0[:, perm]
+            out[f"{name}.perm"] = perm.numpy()
+        hinv_init, hinv, damp, ident = g._compute_hessian_inverse_with_fallback(H0, percdamp=0.01)
+        beta, bview, Z, GH = g._compute_gradient_terms(G0, hinv_init, hinv, True)
+        if name in HEAVY:
+            out[f"{name}.Hinv0"] = np32(hinv)
+        out[f"{name}.Hinv_init0_diag"] = np32(torch.diagonal(hinv_init))
+        out[f"{name}.beta0"] = np32(beta)
+        out[f"{name}.Z0"] = np32(Z)
+        out[f"{name}.GHinv0"] = np32(GH)
+        g.fasterquant(blocksize=128, percdamp=0.01, groupsize=gs, actorder=act, static_groups=static,
+                      enable_gradient_update=True, g_update_mode=mode, export_to_et=True,
+                      block_atomic_quant=atomic)
+        out[f"{name}.Q"] = np32(layer.weight.data)
+        out[f"{name}.W_int"] = np32(layer.int_weight).astype(np.int8)
+        out[f"{name}.Scale"] = np32(layer.scale)
+
+
+def gen_faults(qu, gpu, out):
+    """Numeric guards: a non-SPD Hessian that needs damping retries, and non-finite entries."""
+    torch.manual_seed(7)
+    C = 64
+    A = torch.randn(C, 8)
+    H = A @ A.t()                                   # rank 8: Cholesky needs damping to succeed
+    H[3, 5] += 5.0
+    H[5, 3] += 5.0                                  # and an indefinite perturbation
+    layer = _Lin(torch.zeros(4, C))
+    g = gpu.GPTQPlus(layer, torch.ones(1, 1, 1), torch.zeros(4, C), 1, 0.0, 0.0)
+    import logging
+    logging.disable(logging.WARNING)
+    hinv_init, hinv, damp, ident = g._compute_hessian_inverse_with_fallback(H, percdamp=0.01)
+    logging.disable(logging.NOTSET)
+    out["nonspd.H"] = np32(H)
+    out["nonspd.Hinv"] = np32(hinv)
+    out["nonspd.damp"] = np.array(damp)
+    out["nonspd.identity"] = np.array(ident)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--ref", default="/root/reference")
+    args = ap.parse_args()
+    torch.set_num_threads(1)                        # fixed reduction order on any host
+    qu, hu, gu, gpu = import_reference(args.ref)
+    for fname, fn, mods in (("quantizer.npz", gen_quantizer, (qu,)),
+                            ("hadamard.npz", gen_hadamard, (hu,)),
+                            ("plain_gptq.npz", gen_plain, (qu, gu)),
+                            ("gptq_plus.npz", gen_plus, (qu, gpu)),
+                            ("faults.npz", gen_faults, (qu, gpu))):
+        out = {}
+        with torch.no_grad():
+            fn(*mods, out)
+        path = os.path.join(HERE, fname)
+        np.savez_compressed(path, **out)
+        print(f"{fname}: {len(out)} arrays, {os.path.getsize(path) / 1024:.0f} KiB")
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,182 @@
+"""The CPU oracle against outputs of the unmodified reference (tests/golden/*.npz,
+made by tests/golden/make_golden.py).  The oracle uses the same ATen CPU operations in
+the same order as the reference, so integer codes must be identical and floating-point
+results equal to within a few ulps (tolerances stated per check)."""
+import numpy as np
+import pytest
+import torch
+
+import cases
+from oracle import gptq as ogptq
+from oracle import hadamard as ohad
+from oracle import hessian as ohess
+from oracle import quantizer as oq
+
+torch.set_num_threads(1)
+
+
+def t(a):
+    return torch.from_numpy(np.asarray(a))
+
+
+@pytest.mark.parametrize("case", cases.QUANTIZER_CASES, ids=lambda c: c[0])
+def test_quantizer(golden, case):
+    name, rows, cols, bits, pc, sym, mse = case
+    g = golden("quantizer.npz")
+    W = cases.make_weight(rows, cols, seed=11)
+    assert cases.digest(W) == str(g[f"{name}.digest"]), "input generator drifted"
+    q = oq.OracleWeightQuantizer()
+    q.configure(bits, perchannel=pc, sym=sym, mse=mse)
+    q.find_params(W)
+    assert int(q.maxq) == int(g[f"{name}.maxq"])
+    assert torch.equal(q.scale, t(g[f"{name}.scale"]))          # bit-exact: same ops, same order
+    assert torch.equal(q.zero, t(g[f"{name}.zero"]))
+    deq, codes, _ = q.fake_quantize(W)
+    assert torch.equal(codes, t(g[f"{name}.fake_codes"]))
+    assert torch.equal(deq, t(g[f"{name}.fake_deq"]))
+    assert torch.equal(q.quantize(W), t(g[f"{name}.ste"]))
+
+
+@pytest.mark.parametrize("case", cases.HADAMARD_CASES, ids=lambda c: c[0])
+def test_hadamard(golden, case):
+    name, rows, n, dtype = case
+    g = golden("hadamard.npz")
+    dt = getattr(torch, dtype)
+    x = cases.make_acts(1, rows, n, seed=5).reshape(rows, n).to(dt)
+    assert cases.digest(x) == str(g[f"{name}.digest"])
+    K = ohad.pick_K(n, [int(k) for k in g["table_keys"]])
+    assert K == int(g[f"{name}.K"])
+    hadK = t(g[f"had{K}"]).float() if K > 1 else None
+    y = ohad.rotate(x, hadK, K)
+    assert torch.equal(y.float(), t(g[f"{name}.y"]))            # bit-exact restatement
+    ys = ohad.rotate_strided(x, hadK, K)
+    assert torch.equal(ys.float(), t(g[f"{name}.y_strided"]))
+    # the fp64 evaluation is the exact operator: both reference forms sit within their dtype's rounding of it
+    exact = ohad.rotate_exact(x, hadK, K)
+    tol = {"float32": 2e-6, "bfloat16": 3e-2, "float16": 4e-3}[dtype]
+    scale = exact.abs().max()
+    assert (y.double() - exact).abs().max() <= tol * scale
+
+
+def _plain_setup(case):
+    (name, rows, cols, nseq, seqlen, bits, sym, gs, act, static, bs) = case
+    W = cases.make_weight(rows, cols, seed=21)
+    X = cases.make_acts(nseq, seqlen, cols, seed=21)
+    if "ragged" in name:
+        X[..., 7] = 0.0
+    return W, X
+
+
+@pytest.mark.parametrize("case", cases.PLAIN_CASES, ids=lambda c: c[0])
+def test_plain_gptq(golden, case):
+    (name, rows, cols, nseq, seqlen, bits, sym, gs, act, static, bs) = case
+    g = golden("plain_gptq.npz")
+    W, X = _plain_setup(case)
+    assert cases.digest(W, X) == str(g[f"{name}.digest"])
+    acc = ohess.PlainHessian(cols)
+    for s in range(nseq):
+        acc.add_batch(X[s:s + 1])
+    if f"{name}.H" in g:
+        assert torch.equal(acc.H, t(g[f"{name}.H"]))
+    q = oq.OracleWeightQuantizer()
+    q.configure(bits, perchannel=True, sym=sym, mse=False)
+    out = ogptq.plain_fasterquant(W, acc.H, q, blocksize=bs, percdamp=0.01, groupsize=gs, actorder=act,
+                                  static_groups=static)
+    assert torch.equal(out["W_int"], t(g[f"{name}.W_int"]).float())
+    assert torch.equal(out["Scale"], t(g[f"{name}.Scale"]))
+    assert torch.equal(out["Q"], t(g[f"{name}.Q"]))
+
+
+def _plus_setup(case):
+    (name, rows, cols, nseq, seqlen, G, bits, gs, act, static, alpha, ref_loss, mode, atomic) = case
+    W = cases.make_weight(rows, cols, seed=31)
+    X = cases.make_acts(nseq, seqlen, cols, seed=31)
+    if "ragged" in name:
+        X[..., 5] = 0.0
+    S = cases.make_saliency(nseq, seqlen, G, seed=31)
+    Gr = cases.make_grad(rows, cols, seed=31)
+    return W, X, S, Gr
+
+
+@pytest.mark.parametrize("case", cases.PLUS_CASES, ids=lambda c: c[0])
+def test_gptq_plus(golden, case):
+    (name, rows, cols, nseq, seqlen, G, bits, gs, act, static, alpha, ref_loss, mode, atomic) = case
+    g = golden("gptq_plus.npz")
+    W, X, S, Gr = _plus_setup(case)
+    assert cases.digest(W, X, S, Gr) == str(g[f"{name}.digest"])
+    acc = ohess.GroupedHessian(cols, S)
+    acc.add_batch(X[:1])
+    acc.add_batch(X[1:])
+    assert torch.equal(acc.act_square, t(g[f"{name}.act_sum"]))
+    acc.finalize()
+    if f"{name}.H" in g:
+        assert torch.equal(acc.H, t(g[f"{name}.H"]))
+    assert torch.equal(acc.act_square, t(g[f"{name}.act_square"]))
+    q = oq.OracleWeightQuantizer()
+    q.configure(bits, perchannel=True, sym=True, mse=False)
+    out = ogptq.plus_fasterquant(W, acc.H, acc.act_square, Gr, q, G, alpha, ref_loss, blocksize=128,
+                                 percdamp=0.01, groupsize=gs, actorder=act, static_groups=static,
+                                 g_update_mode=mode, block_atomic_quant=atomic)
+    st0 = out["states"][0]
+    if act:
+        assert torch.equal(out["perm"], t(g[f"{name}.perm"]))
+    if f"{name}.Hinv0" in g:
+        assert torch.equal(st0["Hinv"], t(g[f"{name}.Hinv0"]))
+    assert torch.equal(torch.diagonal(st0["Hinv_init"]), t(g[f"{name}.Hinv_init0_diag"]))
+    assert torch.equal(st0["beta"], t(g[f"{name}.beta0"]))
+    assert torch.equal(st0["Z"], t(g[f"{name}.Z0"]))
+    assert torch.equal(out["W_int"], t(g[f"{name}.W_int"]).float())
+    assert torch.equal(out["Scale"], t(g[f"{name}.Scale"]))
+    assert torch.equal(out["Q"], t(g[f"{name}.Q"]))
+
+
+def test_sharded_accumulation_matches_single(golden):
+    """Token-sharded accumulation followed by a sum of the partial state (what the all-reduce
+    in finalize_hessian does) equals the single-process result to fp32 summation noise."""
+    case = cases.PLUS_CASES[0]
+    (name, rows, cols, nseq, seqlen, G, *_rest) = case
+    W, X, S, Gr = _plus_setup(case)
+    one = ohess.GroupedHessian(cols, S)
+    one.add_batch(X)
+    one.finalize()
+    parts = []
+    for r in range(2):
+        sl = slice(r * nseq // 2, (r + 1) * nseq // 2)
+        p = ohess.GroupedHessian(cols, S[sl])
+        p.add_batch(X[sl])
+        parts.append(p)
+    merged = ohess.GroupedHessian.merge(parts)
+    merged.finalize()
+    rel = (merged.H - one.H).norm() / one.H.norm()
+    assert rel < 1e-6                                            # relative Frobenius
+    assert torch.allclose(merged.act_square, one.act_square, rtol=1e-5)
+
+
+def test_nonspd_damping_retry(golden):
+    g = golden("faults.npz")
+    H = t(g["nonspd.H"])
+    import logging
+    logging.disable(logging.WARNING)
+    inv, up, damp, ident = ogptq.hinv_with_fallback(H, 0.01)
+    logging.disable(logging.NOTSET)
+    assert ident == bool(g["nonspd.identity"])
+    assert abs(damp - float(g["nonspd.damp"])) < 1e-12
+    assert torch.equal(up, t(g["nonspd.Hinv"]))
+
+
+def test_nonfinite_hessian_is_zeroed():
+    S = torch.ones(1, 4, 1)
+    acc = ohess.GroupedHessian(3, S)
+    X = torch.tensor([[[1.0, 2.0, float("inf")], [0.5, 1.0, 1.0], [1.0, 0.0, 1.0], [2.0, 1.0, 1.0]]])
+    acc.add_batch(X)
+    n_nan, n_inf = acc.finalize()
+    assert n_nan + n_inf > 0
+    assert torch.isfinite(acc.H).all()
+    with pytest.raises(RuntimeError):
+        acc.add_batch(X)
+
+
+def test_finalize_before_accumulate_raises():
+    acc = ohess.GroupedHessian(3, torch.ones(1, 4, 1))
+    with pytest.raises(RuntimeError):
+        acc.finalize()
