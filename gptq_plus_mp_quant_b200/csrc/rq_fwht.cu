@@ -1,0 +1,196 @@
+// Walsh-Hadamard rotation  y = x . H_n * scale  for n = K * 2^m  (HBM-bound).
+//
+// A work item is one row (or, for short rows, a batch of rows) held in shared memory as fp32.
+// The power-of-two part runs as radix-16 register butterflies over shared memory (at most
+// ceil(m/4) passes); the optional K x K mix (K = 12, 20, 28, ...: the non-power-of-two factor)
+// is a small +-1 matrix product per position.  Input is read once and output written once with
+// 16-byte accesses where alignment allows; all arithmetic is fp32 whatever the I/O type.
+#include "rq_common.cuh"
+
+namespace rq {
+namespace fwht {
+
+constexpr int kThreads = 256;
+constexpr int kMaxK = 64;       // register-resident mix; larger K takes the generic path
+
+// one padding word per 16 keeps the strided radix-16 accesses of every pass on distinct banks
+__device__ __forceinline__ int pad(int i) { return i + (i >> 4); }
+
+template <int R>
+__device__ __forceinline__ void butterflies(float (&v)[1 << R]) {
+#pragma unroll
+    for (int h = 1; h < (1 << R); h <<= 1) {
+#pragma unroll
+        for (int b = 0; b < (1 << R); ++b) {
+            if ((b & h) == 0) {
+                const float a = v[b], c = v[b | h];
+                v[b] = a + c;
+                v[b | h] = a - c;
+            }
+        }
+    }
+}
+
+// One pass over index bits [lo, lo+R) of `total` shared-memory elements.
+template <int R>
+__device__ __forceinline__ void smem_pass(float* buf, int total, int lo) {
+    const int groups = total >> R;
+    const int lomask = (1 << lo) - 1;
+    for (int gi = threadIdx.x; gi < groups; gi += kThreads) {
+        const int base = ((gi >> lo) << (lo + R)) | (gi & lomask);
+        float v[1 << R];
+#pragma unroll
+        for (int b = 0; b < (1 << R); ++b) v[b] = buf[pad(base + (b << lo))];
+        butterflies<R>(v);
+#pragma unroll
+        for (int b = 0; b < (1 << R); ++b) buf[pad(base + (b << lo))] = v[b];
+    }
+}
+
+// chunk k' = sum_k hadK[k'][k] * chunk k at one position; hadK entries are +-1 so the products are exact.
+template <int KK>
+__device__ __forceinline__ void mix(float* buf, const float* hk, int base, int P) {
+    float v[KK];
+#pragma unroll
+    for (int k = 0; k < KK; ++k) v[k] = buf[pad(base + k * P)];
+#pragma unroll 4
+    for (int ko = 0; ko < KK; ++ko) {
+        float acc = 0.f;
+#pragma unroll
+        for (int k = 0; k < KK; ++k) acc = fmaf(hk[ko * KK + k], v[k], acc);
+        buf[pad(base + ko * P)] = acc;
+    }
+}
+
+__device__ __noinline__ void mix_any(float* buf, const float* hk, int base, int P, int K) {
+    float v[kMaxK];
+    for (int k = 0; k < K; ++k) v[k] = buf[pad(base + k * P)];
+    for (int ko = 0; ko < K; ++ko) {
+        float acc = 0.f;
+        for (int k = 0; k < K; ++k) acc = fmaf(hk[ko * K + k], v[k], acc);
+        buf[pad(base + ko * P)] = acc;
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads) fwht_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t rows,
+                                                        int n, int K, int m, int rows_per_item,
+                                                        const float* __restrict__ hadK, float scale) {
+    extern __shared__ float buf[];                       // pad(rows_per_item * n) floats, then K*K mix matrix
+    const int item_elems = rows_per_item * n;
+    float* hk = buf + pad(item_elems) + 1;
+    if (K > 1)
+        for (int e = threadIdx.x; e < K * K; e += kThreads) hk[e] = hadK[e];
+    const int64_t items = (rows + rows_per_item - 1) / rows_per_item;
+    const int P = n / K;
+
+    for (int64_t item = blockIdx.x; item < items; item += gridDim.x) {
+        const int64_t row0 = item * rows_per_item;
+        const int64_t valid = (rows - row0 < rows_per_item ? rows - row0 : rows_per_item) * (int64_t)n;
+        const T* src = x + row0 * n;
+        T* dst = y + row0 * n;
+        __syncthreads();                                  // previous item fully written out
+        // ---- load (16-byte vectors when the item start is aligned)
+        constexpr int V = 16 / sizeof(T);
+        const bool aligned = ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15) == 0 &&
+                             (valid % V) == 0;
+        if (aligned) {
+            for (int64_t e = (int64_t)threadIdx.x * V; e < valid; e += (int64_t)kThreads * V) {
+                const uint4 raw = *reinterpret_cast<const uint4*>(src + e);
+                const T* t = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+                for (int k = 0; k < V; ++k) buf[pad((int)e + k)] = load_as_float<T>(t, k);
+            }
+        } else {
+            for (int e = threadIdx.x; e < valid; e += kThreads) buf[pad(e)] = load_as_float<T>(src, e);
+        }
+        for (int e = (int)valid + threadIdx.x; e < item_elems; e += kThreads) buf[pad(e)] = 0.f;   // ragged last item
+        __syncthreads();
+        // ---- butterflies over bits [0, m)
+        int lo = 0;
+        while (lo < m) {
+            const int r = (m - lo) >= 4 ? 4 : (m - lo);
+            if (r == 4) smem_pass<4>(buf, item_elems, lo);
+            else if (r == 3) smem_pass<3>(buf, item_elems, lo);
+            else if (r == 2) smem_pass<2>(buf, item_elems, lo);
+            else smem_pass<1>(buf, item_elems, lo);
+            lo += r;
+            __syncthreads();
+        }
+        // ---- K x K mix across the K chunks of each row (in place: a thread owns one position of one row)
+        if (K > 1) {
+            const int positions = rows_per_item * P;
+            for (int pi = threadIdx.x; pi < positions; pi += kThreads) {
+                const int r = pi / P, p = pi - r * P;
+                const int base = r * n + p;
+                if (K == 12) mix<12>(buf, hk, base, P);
+                else if (K == 20) mix<20>(buf, hk, base, P);
+                else if (K == 28) mix<28>(buf, hk, base, P);
+                else mix_any(buf, hk, base, P, K);
+            }
+            __syncthreads();
+        }
+        // ---- store
+        if (aligned) {
+            for (int64_t e = (int64_t)threadIdx.x * V; e < valid; e += (int64_t)kThreads * V) {
+                uint4 raw;
+                T* t = reinterpret_cast<T*>(&raw);
+#pragma unroll
+                for (int k = 0; k < V; ++k) store_from_float<T>(t, k, buf[pad((int)e + k)] * scale);
+                *reinterpret_cast<uint4*>(dst + e) = raw;
+            }
+        } else {
+            for (int e = threadIdx.x; e < valid; e += kThreads) store_from_float<T>(dst, e, buf[pad(e)] * scale);
+        }
+    }
+}
+
+}  // namespace fwht
+}  // namespace rq
+
+using namespace rq;
+
+extern "C" int rq_fwht(const void* x, void* y, int dtype, int64_t rows, int n, int K, const float* hadK, float scale,
+                       void* stream) {
+    using namespace rq::fwht;
+    if (!x || !y || rows < 0 || n <= 0 || K <= 0 || n % K != 0) return RQ_ERR_INVALID;
+    if (K > 1 && !hadK) return RQ_ERR_INVALID;
+    if (K > kMaxK) return RQ_ERR_UNSUPPORTED;
+    const int P = n / K;
+    if ((P & (P - 1)) != 0) return RQ_ERR_INVALID;
+    if (rows == 0) return RQ_OK;
+    int m = 0;
+    while ((1 << m) < P) ++m;
+    // short rows are batched so that an item has about 4096 elements; whole chunks only
+    int rows_per_item = 1;
+    if (n < 4096) {
+        rows_per_item = 4096 / n;
+        if (rows_per_item > rows) rows_per_item = (int)rows;
+        if (rows_per_item < 1) rows_per_item = 1;
+    }
+    const int64_t item_elems = (int64_t)rows_per_item * n;
+    const size_t smem = ((size_t)(item_elems + (item_elems >> 4)) + 2 + (size_t)K * K) * sizeof(float);
+    if (smem > 220 * 1024) return RQ_ERR_UNSUPPORTED;
+    const int64_t items = (rows + rows_per_item - 1) / rows_per_item;
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    int per_sm = (int)((200 * 1024) / (smem + 1024));
+    if (per_sm < 1) per_sm = 1;
+    if (per_sm > 8) per_sm = 8;
+    int64_t grid = (int64_t)sms * per_sm;
+    if (grid > items) grid = items;
+    cudaStream_t st = as_stream(stream);
+    cudaError_t e = cudaSuccess;
+#define RQ_FWHT_LAUNCH(T)                                                                                       \
+    e = cudaFuncSetAttribute(fwht_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);           \
+    if (e != cudaSuccess) return RQ_ERR_CUDA;                                                                   \
+    fwht_kernel<T><<<(unsigned)grid, kThreads, smem, st>>>(reinterpret_cast<const T*>(x), reinterpret_cast<T*>(y), \
+                                                           rows, n, K, m, rows_per_item, hadK, scale)
+    if (dtype == RQ_F32) { RQ_FWHT_LAUNCH(float); }
+    else if (dtype == RQ_BF16) { RQ_FWHT_LAUNCH(__nv_bfloat16); }
+    else if (dtype == RQ_F16) { RQ_FWHT_LAUNCH(__half); }
+    else return RQ_ERR_INVALID;
+#undef RQ_FWHT_LAUNCH
+    return check_launch();
+}

@@ -1,0 +1,526 @@
+// Saliency-weighted Hessian accumulation  H[g] = beta*H[g] + alpha * X^T diag(s_g) X  on the
+// 5th-generation tensor cores (tcgen05 + tensor memory), fed by TMA.
+//
+// Two kernels per chunk of tokens:
+//   1. pack:  reads X (fp32 / bf16 / fp16) and the saliency once, and writes token-contiguous
+//             ("K-major") bf16 planes  X_hi, X_lo, Y_hi[g], Y_lo[g]  with  Y_g = s_g * X,
+//             v_hi = bf16(v), v_lo = bf16(v - v_hi); also the per-channel sum of squares.
+//   2. umma:  persistent, warp-specialised GEMM over the upper-triangular 128x256 tiles of
+//             every H[g]:  D = X_hi.Y_lo^T + X_lo.Y_hi^T + X_hi.Y_hi^T  accumulated in fp32 in
+//             tensor memory, then read-modify-written into H.
+// The three-product split keeps the result within ~1e-6 relative Frobenius of an fp32 GEMM.
+#include <cuda.h>
+
+#include "rq_common.cuh"
+#include "rq_sm100.cuh"
+
+namespace rq {
+namespace hess {
+
+using namespace rq::sm100;
+
+constexpr int BM = 128;          // tile rows   (channels i)   = UMMA M
+constexpr int BN = 256;          // tile cols   (channels j)   = UMMA N
+constexpr int UK = 16;           // bf16 UMMA K
+constexpr int kThreads = 192;    // warp 0: TMA producer, warp 1: MMA issuer, warps 2-5: epilogue
+constexpr int kTmemCols = 512;   // two 128x256 fp32 accumulators
+constexpr int kPackTile = 64;    // pack kernel tile edge (tokens and channels)
+
+template <int BK, int NPROD>
+struct Cfg {
+    static constexpr int kLayout = BK == 64 ? 2 : 4;              // UMMA swizzle mode: 128 B / 64 B
+    static constexpr int kSBO = 8 * BK * 2;                        // bytes between 8-row groups
+    static constexpr int kATile = BM * BK * 2;
+    static constexpr int kBTile = BN * BK * 2;
+    static constexpr int kAPlanes = NPROD == 3 ? 2 : 1;
+    static constexpr int kStageBytes = kAPlanes * kATile + 2 * kBTile;
+    static constexpr int kStages = (200 * 1024) / kStageBytes;
+    static constexpr int kBarBytes = 256;
+    static constexpr int kSmemBytes = kStages * kStageBytes + kBarBytes + 1024;   // +1024: alignment slack
+};
+
+// ------------------------------------------------------------------------------------------
+// pack
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ void split_bf16(float v, __nv_bfloat16& hi, __nv_bfloat16& lo) {
+    hi = __float2bfloat16_rn(v);
+    lo = __float2bfloat16_rn(v - __bfloat162float(hi));
+}
+
+// grid (ceil(C/64), Kc/64), 256 threads.  planes: [P][C][Kc] bf16, P = 2 (no saliency) or 2+2G.
+// partial: [Kc/64][C] per-tile sums of x^2 (may be NULL).
+template <typename T>
+__global__ void __launch_bounds__(256) pack_kernel(const T* __restrict__ x, int64_t ldx,
+                                                   const float* __restrict__ sal, int nvalid, int C, int G, int Kc,
+                                                   __nv_bfloat16* __restrict__ planes, float* __restrict__ partial,
+                                                   int write_xlo) {
+    __shared__ float xs[kPackTile][kPackTile + 1];
+    __shared__ float ss[kPackTile][8];
+    const int c0 = blockIdx.x * kPackTile;
+    const int t0 = blockIdx.y * kPackTile;
+    const int tid = threadIdx.x;
+
+    {   // load: 64 consecutive channels of one token per pass of 64 threads
+        const int cc = tid & 63;
+        const int tr = tid >> 6;
+#pragma unroll 4
+        for (int p = 0; p < 16; ++p) {
+            const int t = p * 4 + tr;
+            float v = 0.f;
+            if (t0 + t < nvalid && c0 + cc < C) v = load_as_float<T>(x, (int64_t)(t0 + t) * ldx + c0 + cc);
+            xs[t][cc] = v;
+        }
+        if (sal != nullptr) {
+            for (int e = tid; e < kPackTile * G; e += 256) {
+                const int t = e / G, g = e - t * G;
+                ss[t][g] = (t0 + t < nvalid) ? sal[(int64_t)(t0 + t) * G + g] : 0.f;
+            }
+        }
+    }
+    __syncthreads();
+
+    const int warp = tid >> 5, lane = tid & 31;
+    const int64_t plane_stride = (int64_t)C * Kc;
+    const int ta = 2 * lane, tb = 2 * lane + 1;
+    for (int cc = warp; cc < kPackTile; cc += 8) {
+        const int c = c0 + cc;
+        if (c >= C) break;                                     // warp-uniform
+        const float xa = xs[ta][cc], xb = xs[tb][cc];
+        const int64_t off = (int64_t)c * Kc + t0 + ta;          // even -> 4-byte aligned pair
+        __nv_bfloat16 ha, la, hb, lb;
+        split_bf16(xa, ha, la);
+        split_bf16(xb, hb, lb);
+        *reinterpret_cast<__nv_bfloat162*>(planes + off) = __halves2bfloat162(ha, hb);
+        if (write_xlo) *reinterpret_cast<__nv_bfloat162*>(planes + plane_stride + off) = __halves2bfloat162(la, lb);
+        if (sal != nullptr) {
+            for (int g = 0; g < G; ++g) {
+                const float ya = __fmul_rn(xa, ss[ta][g]);
+                const float yb = __fmul_rn(xb, ss[tb][g]);
+                split_bf16(ya, ha, la);
+                split_bf16(yb, hb, lb);
+                *reinterpret_cast<__nv_bfloat162*>(planes + (2 + 2 * g) * plane_stride + off) = __halves2bfloat162(ha, hb);
+                *reinterpret_cast<__nv_bfloat162*>(planes + (3 + 2 * g) * plane_stride + off) = __halves2bfloat162(la, lb);
+            }
+        }
+        if (partial != nullptr) {
+            float sq = xa * xa + xb * xb;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+            if (lane == 0) partial[(int64_t)blockIdx.y * C + c] = sq;
+        }
+    }
+}
+
+// act_sq[c] += sum over token tiles, in tile order (deterministic).
+__global__ void act_reduce_kernel(const float* __restrict__ partial, int ntiles, int C, float* __restrict__ act_sq) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    float s = 0.f;
+    for (int t = 0; t < ntiles; ++t) s += partial[(int64_t)t * C + c];
+    act_sq[c] += s;
+}
+
+// ------------------------------------------------------------------------------------------
+// tile schedule: upper-triangular 128x256 tiles.  Column block j (256 wide) needs row blocks
+// i = 0 .. min(MT-1, 2j+1).  Linear index u -> (i, j) with cum(j) = j*(j+1).
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ void decode_tile(int u, int& i, int& j) {
+    int jj = static_cast<int>((sqrtf(4.f * static_cast<float>(u) + 1.f) - 1.f) * 0.5f);
+    while ((jj + 1) * (jj + 2) <= u) ++jj;
+    while (jj * (jj + 1) > u) --jj;
+    j = jj;
+    i = u - jj * (jj + 1);
+}
+
+struct Bars {
+    uint64_t full[8];
+    uint64_t empty[8];
+    uint64_t tfull[2];
+    uint64_t tempty[2];
+    uint32_t tmem_slot;
+    int abort_flag;
+};
+static_assert(sizeof(Bars) <= 256, "barrier block");
+
+template <int BK, int NPROD>
+__global__ void __launch_bounds__(kThreads, 1)
+umma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
+            float* __restrict__ H, int C, int G, int MT, int NT, int kblocks, int a_plane, int b_plane0,
+            float alpha, float beta, int* __restrict__ status) {
+    using K = Cfg<BK, NPROD>;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t tiles = (raw + 1023u) & ~1023u;                       // shared-space address of stage 0
+    Bars* bars = reinterpret_cast<Bars*>(smem_raw + (tiles - raw) + K::kStages * K::kStageBytes);
+    volatile int* abort_flag = &bars->abort_flag;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int tiles_per_group = (NT - 1) * NT + MT;
+    const int total_tiles = tiles_per_group * G;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < K::kStages; ++s) {
+            mbar_init(smem_u32(&bars->full[s]), 1);
+            mbar_init(smem_u32(&bars->empty[s]), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(smem_u32(&bars->tfull[a]), 1);
+            mbar_init(smem_u32(&bars->tempty[a]), 4);
+        }
+        bars->abort_flag = 0;
+        mbar_fence_init();
+        tma_prefetch_desc(&mapA);
+        tma_prefetch_desc(&mapB);
+    }
+    if (warp == 0) {
+        tmem_alloc(smem_u32(&bars->tmem_slot), kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = bars->tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+                const int g = t % G;
+                int i, j;
+                decode_tile(t / G, i, j);
+                for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                    const uint32_t s = it % K::kStages;
+                    const uint32_t ph = (it / K::kStages) & 1u;
+                    if (!mbar_wait(smem_u32(&bars->empty[s]), ph ^ 1u, abort_flag)) { ok = false; break; }
+                    const uint32_t fb = smem_u32(&bars->full[s]);
+                    uint32_t dst = tiles + s * K::kStageBytes;
+                    mbar_expect_tx(fb, K::kStageBytes);
+                    tma_load_3d(dst, &mapA, fb, kb * BK, i * BM, a_plane);
+                    dst += K::kATile;
+                    if (NPROD == 3) {
+                        tma_load_3d(dst, &mapA, fb, kb * BK, i * BM, a_plane + 1);
+                        dst += K::kATile;
+                    }
+                    tma_load_3d(dst, &mapB, fb, kb * BK, j * BN, b_plane0 + 2 * g);
+                    dst += K::kBTile;
+                    tma_load_3d(dst, &mapB, fb, kb * BK, j * BN, b_plane0 + 2 * g + 1);
+                }
+            }
+            if (!ok) {
+                // Another role gave up: let the copies already issued land before the CTA exits.
+                const uint32_t inflight = it < (uint32_t)K::kStages ? it : (uint32_t)K::kStages;
+                for (uint32_t b = 0; b < inflight; ++b) {
+                    const uint32_t q = it - 1 - b;
+                    const uint32_t fb = smem_u32(&bars->full[q % K::kStages]);
+                    const long long t0 = clock64();
+                    while (!mbar_try_wait(fb, (q / K::kStages) & 1u) && clock64() - t0 < kWaitCycles) {}
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc_bf16_f32(BM, BN);
+            uint32_t it = 0, tile_iter = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_iter) {
+                const uint32_t acc = tile_iter & 1u;
+                const uint32_t acc_ph = (tile_iter >> 1) & 1u;
+                if (!mbar_wait(smem_u32(&bars->tempty[acc]), acc_ph ^ 1u, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                    const uint32_t s = it % K::kStages;
+                    const uint32_t ph = (it / K::kStages) & 1u;
+                    if (!mbar_wait(smem_u32(&bars->full[s]), ph, abort_flag)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t a_hi = tiles + s * K::kStageBytes;
+                    const uint32_t a_lo = a_hi + K::kATile;
+                    const uint32_t b_hi = a_hi + K::kAPlanes * K::kATile;
+                    const uint32_t b_lo = b_hi + K::kBTile;
+#pragma unroll
+                    for (int k = 0; k < BK / UK; ++k) {
+                        const uint32_t koff = k * UK * 2;               // bytes along K inside the swizzle row
+                        const uint64_t dah = umma_smem_desc(a_hi + koff, K::kSBO, K::kLayout);
+                        const uint64_t dbh = umma_smem_desc(b_hi + koff, K::kSBO, K::kLayout);
+                        const uint64_t dbl = umma_smem_desc(b_lo + koff, K::kSBO, K::kLayout);
+                        umma_bf16(d_tmem, dah, dbl, idesc, (kb | k) != 0 ? 1u : 0u);   // small terms first
+                        if (NPROD == 3) {
+                            const uint64_t dal = umma_smem_desc(a_lo + koff, K::kSBO, K::kLayout);
+                            umma_bf16(d_tmem, dal, dbh, idesc, 1u);
+                        }
+                        umma_bf16(d_tmem, dah, dbh, idesc, 1u);
+                    }
+                    umma_commit(smem_u32(&bars->empty[s]));            // frees the stage when these MMAs retire
+                }
+                if (ok) umma_commit(smem_u32(&bars->tfull[acc]));      // accumulator complete
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue (4 warps = 128 lanes)
+        const int q = warp & 3;                                        // tensor-memory lane quadrant of this warp
+        uint32_t tile_iter = 0;
+        const bool vec_ok = (C & 3) == 0;
+        for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++tile_iter) {
+            const int g = t % G;
+            int i, j;
+            decode_tile(t / G, i, j);
+            const uint32_t acc = tile_iter & 1u;
+            const uint32_t acc_ph = (tile_iter >> 1) & 1u;
+            int ok = 1;
+            if (lane == 0) ok = mbar_wait(smem_u32(&bars->tfull[acc]), acc_ph, abort_flag) ? 1 : 0;
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) break;
+            tc_fence_after();
+            const int row0 = i * BM + q * 32;
+            const int row = row0 + lane;
+            float* hrow = H + ((int64_t)g * C + row) * (int64_t)C;
+#pragma unroll 1
+            for (int cb = 0; cb < BN / 32; ++cb) {
+                const int col0 = j * BN + cb * 32;
+                if (col0 >= C || col0 + 31 < row0 || row0 >= C) continue;    // warp-uniform: outside / below diagonal
+                float v[32];
+                tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + cb * 32, v);
+                if (row < C) {
+                    if (vec_ok && col0 + 32 <= C) {
+                        float4* p4 = reinterpret_cast<float4*>(hrow + col0);
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) {
+                            float4 o = (beta != 0.f) ? p4[e] : make_float4(0.f, 0.f, 0.f, 0.f);
+                            if (beta != 1.f) { o.x *= beta; o.y *= beta; o.z *= beta; o.w *= beta; }
+                            o.x += alpha * v[4 * e + 0];
+                            o.y += alpha * v[4 * e + 1];
+                            o.z += alpha * v[4 * e + 2];
+                            o.w += alpha * v[4 * e + 3];
+                            p4[e] = o;
+                        }
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) {
+                            if (col0 + e < C) {
+                                float o = (beta != 0.f) ? hrow[col0 + e] : 0.f;
+                                if (beta != 1.f) o *= beta;
+                                hrow[col0 + e] = o + alpha * v[e];
+                            }
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bars->tempty[acc]));
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem_base, kTmemCols);
+    if (threadIdx.x == 0 && *abort_flag && status != nullptr) atomicExch(status, RQ_ERR_TIMEOUT);
+}
+
+// ------------------------------------------------------------------------------------------
+// finalize / mirror: one block per 32x32 tile pair (bi <= bj) of one group
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) finalize_kernel(float* __restrict__ H, float* __restrict__ act_sq, int C,
+                                                       float div_tokens, float div_scale, float div_seq,
+                                                       int sanitize, unsigned long long* __restrict__ counts) {
+    __shared__ float tile[32][33];
+    const int g = blockIdx.y;
+    int bi, bj;
+    {   // pairs ordered by bj: cum(bj) = bj*(bj+1)/2, bi in [0, bj]
+        const int u = blockIdx.x;
+        int jj = static_cast<int>((sqrtf(8.f * static_cast<float>(u) + 1.f) - 1.f) * 0.5f);
+        while ((jj + 1) * (jj + 2) / 2 <= u) ++jj;
+        while (jj * (jj + 1) / 2 > u) --jj;
+        bj = jj;
+        bi = u - jj * (jj + 1) / 2;
+    }
+    float* Hg = H + (int64_t)g * C * C;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    unsigned int n_nan = 0, n_inf = 0;
+    const unsigned int weight = (bi == bj) ? 1u : 2u;
+#pragma unroll
+    for (int r = ty; r < 32; r += 8) {
+        const int row = bi * 32 + r, col = bj * 32 + tx;
+        float v = 0.f;
+        if (row < C && col < C) {
+            v = Hg[(int64_t)row * C + col];
+            if (div_tokens != 1.f) v = __fdiv_rn(v, div_tokens);
+            if (div_scale != 1.f) v = __fdiv_rn(v, div_scale);
+            if (sanitize && (bi != bj || row <= col)) {
+                if (isnan(v)) { n_nan += (bi == bj && row != col) ? 2u : weight; v = 0.f; }
+                else if (isinf(v)) { n_inf += (bi == bj && row != col) ? 2u : weight; v = 0.f; }
+            }
+        }
+        tile[r][tx] = v;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int r = ty; r < 32; r += 8) {
+        if (bi == bj) {
+            const int row = bi * 32 + r, col = bi * 32 + tx;
+            if (row < C && col < C) Hg[(int64_t)row * C + col] = (r <= tx) ? tile[r][tx] : tile[tx][r];
+        } else {
+            int row = bi * 32 + r, col = bj * 32 + tx;
+            if (row < C && col < C) Hg[(int64_t)row * C + col] = tile[r][tx];
+            row = bj * 32 + r;
+            col = bi * 32 + tx;
+            if (row < C && col < C) Hg[(int64_t)row * C + col] = tile[tx][r];
+        }
+    }
+    if (sanitize && counts != nullptr) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            n_nan += __shfl_xor_sync(0xffffffffu, n_nan, o);
+            n_inf += __shfl_xor_sync(0xffffffffu, n_inf, o);
+        }
+        if (tx == 0) {
+            if (n_nan) atomicAdd(&counts[0], (unsigned long long)n_nan);
+            if (n_inf) atomicAdd(&counts[1], (unsigned long long)n_inf);
+        }
+    }
+    if (act_sq != nullptr && div_seq != 1.f && g == 0) {
+        for (int c = blockIdx.x * 256 + threadIdx.x; c < C; c += gridDim.x * 256) act_sq[c] = __fdiv_rn(act_sq[c], div_seq);
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// host side
+// ------------------------------------------------------------------------------------------
+static int encode_map(CUtensorMap* map, void* base, int64_t Kc, int C, int planes, int box_k, int box_rows, int bk) {
+    EncodeTiledFn enc = get_encode_tiled();
+    if (!enc) return RQ_ERR_CUDA;
+    cuuint64_t dims[3] = {(cuuint64_t)Kc, (cuuint64_t)C, (cuuint64_t)planes};
+    cuuint64_t strides[2] = {(cuuint64_t)Kc * 2, (cuuint64_t)Kc * 2 * (cuuint64_t)C};
+    cuuint32_t box[3] = {(cuuint32_t)box_k, (cuuint32_t)box_rows, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, base, dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, bk == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? RQ_OK : RQ_ERR_CUDA;
+}
+
+static int num_sms() {
+    static int n = 0;
+    if (n == 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    }
+    return n;
+}
+
+template <int BK, int NPROD>
+static int launch_umma(void* planes, int64_t Kc, int C, int G, int nplanes, int b_plane0, float* H, float alpha,
+                       float beta, int* status, cudaStream_t st) {
+    using K = Cfg<BK, NPROD>;
+    CUtensorMap mapA, mapB;
+    int rc = encode_map(&mapA, planes, Kc, C, nplanes, BK, BM, BK);
+    if (rc != RQ_OK) return rc;
+    rc = encode_map(&mapB, planes, Kc, C, nplanes, BK, BN, BK);
+    if (rc != RQ_OK) return rc;
+    if (cudaFuncSetAttribute(umma_kernel<BK, NPROD>, cudaFuncAttributeMaxDynamicSharedMemorySize, K::kSmemBytes) !=
+        cudaSuccess)
+        return RQ_ERR_CUDA;
+    const int MT = (C + BM - 1) / BM, NT = (C + BN - 1) / BN;
+    const int total = ((NT - 1) * NT + MT) * G;
+    const int grid = total < num_sms() ? total : num_sms();
+    prof::Scope timed(RQ_PROF_HESSIAN_UMMA, st);
+    umma_kernel<BK, NPROD><<<grid, kThreads, K::kSmemBytes, st>>>(mapA, mapB, H, C, G, MT, NT, (int)(Kc / BK), 0,
+                                                                  b_plane0, alpha, beta, status);
+    return check_launch();
+}
+
+}  // namespace hess
+}  // namespace rq
+
+using namespace rq;
+
+extern "C" size_t rq_hessian_workspace_bytes(int64_t chunk_tokens, int C, int G, int has_saliency) {
+    if (chunk_tokens <= 0 || C <= 0 || G <= 0) return 0;
+    const int64_t Kc = (chunk_tokens + 63) / 64 * 64;
+    const int64_t planes = has_saliency ? 2 + 2 * (int64_t)G : 2;
+    size_t bytes = (size_t)planes * (size_t)C * (size_t)Kc * 2;
+    bytes = (bytes + 1023) / 1024 * 1024;
+    bytes += (size_t)(Kc / 64) * (size_t)C * 4;            // per-tile sums of squares
+    return bytes + 1024;
+}
+
+extern "C" int rq_hessian_accum(const void* x, int x_dtype, int64_t ldx, const float* sal, float* H, float* act_sq,
+                                int64_t N, int C, int G, float alpha, float beta, void* workspace,
+                                size_t workspace_bytes, int* status, int variant, void* stream) {
+    using namespace rq::hess;
+    if (!x || !H || !workspace || C <= 0 || G <= 0 || G > 8 || N < 0 || ldx < C) return RQ_ERR_INVALID;
+    if (!sal && G != 1) return RQ_ERR_INVALID;
+    if (x_dtype != RQ_F32 && x_dtype != RQ_BF16 && x_dtype != RQ_F16) return RQ_ERR_INVALID;
+    if (variant != 0 && variant != 1) return RQ_ERR_UNSUPPORTED;
+    if (reinterpret_cast<uintptr_t>(workspace) % 1024 != 0) return RQ_ERR_INVALID;
+    if (N == 0) return RQ_OK;
+    cudaStream_t st = as_stream(stream);
+
+    // largest chunk (multiple of 64 tokens) the workspace can hold
+    const int has_sal = sal != nullptr;
+    int64_t chunk = (N + 63) / 64 * 64;
+    while (chunk > 64 && rq_hessian_workspace_bytes(chunk, C, G, has_sal) > workspace_bytes) chunk -= 64;
+    if (rq_hessian_workspace_bytes(chunk, C, G, has_sal) > workspace_bytes) return RQ_ERR_WORKSPACE;
+
+    const int nplanes = has_sal ? 2 + 2 * G : 2;
+    const int b_plane0 = has_sal ? 2 : 0;
+    const int nprod = (x_dtype == RQ_BF16) ? 2 : 3;
+    __nv_bfloat16* planes = reinterpret_cast<__nv_bfloat16*>(workspace);
+    const size_t esz = x_dtype == RQ_F32 ? 4 : 2;
+
+    for (int64_t n0 = 0; n0 < N; n0 += chunk) {
+        const int nvalid = (int)((N - n0) < chunk ? (N - n0) : chunk);
+        const int64_t Kc = ((int64_t)nvalid + 63) / 64 * 64;
+        size_t plane_bytes = (size_t)nplanes * (size_t)C * (size_t)Kc * 2;
+        plane_bytes = (plane_bytes + 1023) / 1024 * 1024;
+        float* partial = act_sq ? reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) + plane_bytes) : nullptr;
+        const uint8_t* xp = reinterpret_cast<const uint8_t*>(x) + (size_t)n0 * (size_t)ldx * esz;
+        const float* sp = has_sal ? sal + n0 * G : nullptr;
+        dim3 pgrid((C + kPackTile - 1) / kPackTile, (unsigned)(Kc / kPackTile));
+        const int write_xlo = (nprod == 3 || !has_sal) ? 1 : 0;     // without saliency X_lo doubles as Y_lo
+        {
+        prof::Scope timed(RQ_PROF_HESSIAN_PACK, st);
+        if (x_dtype == RQ_F32)
+            pack_kernel<float><<<pgrid, 256, 0, st>>>(reinterpret_cast<const float*>(xp), ldx, sp, nvalid, C, G, (int)Kc,
+                                                       planes, partial, write_xlo);
+        else if (x_dtype == RQ_BF16)
+            pack_kernel<__nv_bfloat16><<<pgrid, 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(xp), ldx, sp, nvalid,
+                                                               C, G, (int)Kc, planes, partial, write_xlo);
+        else
+            pack_kernel<__half><<<pgrid, 256, 0, st>>>(reinterpret_cast<const __half*>(xp), ldx, sp, nvalid, C, G,
+                                                        (int)Kc, planes, partial, write_xlo);
+        }
+        int rc = check_launch();
+        if (rc != RQ_OK) return rc;
+        if (act_sq) {
+            act_reduce_kernel<<<(C + 255) / 256, 256, 0, st>>>(partial, (int)(Kc / kPackTile), C, act_sq);
+            rc = check_launch();
+            if (rc != RQ_OK) return rc;
+        }
+        const float b = (n0 == 0) ? beta : 1.f;
+        if (variant == 0)
+            rc = nprod == 3 ? launch_umma<64, 3>(planes, Kc, C, G, nplanes, b_plane0, H, alpha, b, status, st)
+                            : launch_umma<64, 2>(planes, Kc, C, G, nplanes, b_plane0, H, alpha, b, status, st);
+        else
+            rc = nprod == 3 ? launch_umma<32, 3>(planes, Kc, C, G, nplanes, b_plane0, H, alpha, b, status, st)
+                            : launch_umma<32, 2>(planes, Kc, C, G, nplanes, b_plane0, H, alpha, b, status, st);
+        if (rc != RQ_OK) return rc;
+    }
+    return RQ_OK;
+}
+
+extern "C" int rq_hessian_finalize(float* H, float* act_sq, int C, int G, float div_tokens, float div_scale,
+                                   float div_seq, int sanitize, unsigned long long* counts, void* stream) {
+    if (!H || C <= 0 || G <= 0) return RQ_ERR_INVALID;
+    if (div_tokens == 0.f || div_scale == 0.f || div_seq == 0.f) return RQ_ERR_INVALID;
+    const int T = (C + 31) / 32;
+    dim3 grid((unsigned)(T * (T + 1) / 2), (unsigned)G);
+    rq::hess::finalize_kernel<<<grid, 256, 0, as_stream(stream)>>>(H, act_sq, C, div_tokens, div_scale, div_seq,
+                                                                  sanitize, counts);
+    return check_launch();
+}

@@ -1,0 +1,219 @@
+// Weight-quantizer kernels: per-row / per-group range search (optionally with the shrink-grid
+// error search) and round/clamp quantize-dequantize.  All HBM-bound except the grid search.
+#include "rq_common.cuh"
+
+namespace rq {
+namespace quant {
+
+constexpr int kThreads = 256;
+
+__device__ __forceinline__ float warp_min(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fminf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// scale / zero from a range that already contains 0.
+__device__ __forceinline__ void range_to_params(float lo, float hi, int maxq, int sym, float& scale, float& zero) {
+    if (sym) {
+        scale = __fdiv_rn(fmaxf(fmaxf(fabsf(lo), hi), 1e-5f), (float)maxq);
+        zero = 0.f;
+    } else {
+        if (lo == 0.f && hi == 0.f) { lo = -1.f; hi = 1.f; }
+        scale = __fdiv_rn(fmaxf(hi - lo, 1e-5f), (float)maxq);
+        zero = rintf(__fdiv_rn(-lo, scale));
+    }
+}
+
+// block-wide min/max of (lo, hi); result valid in every thread
+__device__ __forceinline__ void block_minmax(float& lo, float& hi, float* red) {
+    lo = warp_min(lo);
+    hi = warp_max(hi);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    __syncthreads();
+    if (lane == 0) { red[warp] = lo; red[8 + warp] = hi; }
+    __syncthreads();
+    lo = red[0];
+    hi = red[8];
+#pragma unroll
+    for (int w = 1; w < kThreads / 32; ++w) { lo = fminf(lo, red[w]); hi = fmaxf(hi, red[8 + w]); }
+}
+
+__device__ __forceinline__ double block_sum(double v, double* red) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    double s = 0.0;
+#pragma unroll
+    for (int w = 0; w < kThreads / 32; ++w) s += red[w];
+    return s;
+}
+
+// One block per (row, group).  groups == 1 covers the per-channel case.  With mse the block
+// re-reads its span once per lattice point (it stays in L1/L2).
+__global__ void __launch_bounds__(kThreads) find_params_kernel(const float* __restrict__ W, int64_t R, int64_t C,
+                                                               int64_t ldw, int groupsize, int maxq, int sym, int mse,
+                                                               float norm, int grid, float maxshrink,
+                                                               float* __restrict__ scale, float* __restrict__ zero) {
+    __shared__ float red[16];
+    __shared__ double dred[8];
+    const int64_t r = blockIdx.x;
+    const int g = blockIdx.y;
+    const int64_t c0 = groupsize > 0 ? (int64_t)g * groupsize : 0;
+    const int64_t c1 = groupsize > 0 ? (c0 + groupsize < C ? c0 + groupsize : C) : C;
+    const float* row = W + r * ldw;
+    float lo = 0.f, hi = 0.f;                                // the range always contains 0
+    for (int64_t c = c0 + threadIdx.x; c < c1; c += kThreads) {
+        const float v = row[c];
+        lo = fminf(lo, v);
+        hi = fmaxf(hi, v);
+    }
+    block_minmax(lo, hi, red);
+    float s, z;
+    range_to_params(lo, hi, maxq, sym, s, z);
+    if (!sym && lo == 0.f && hi == 0.f) { lo = -1.f; hi = 1.f; }
+    if (mse) {
+        float best = __int_as_float(0x7f800000);
+        const int steps = (int)(maxshrink * (float)grid);
+        const float fmaxq = (float)maxq;
+        for (int i = 0; i < steps; ++i) {
+            for (int j = 0; j < steps; ++j) {
+                // (1 - i/grid) is evaluated in double like the reference's Python scalar, then rounded to fp32
+                const float lo1 = (float)(1.0 - (double)i / (double)grid) * lo;
+                const float hi1 = (float)(1.0 - (double)j / (double)grid) * hi;
+                float s1, z1;
+                if (sym) {
+                    s1 = __fdiv_rn(fmaxf(fmaxf(fabsf(lo1), hi1), 1e-5f), fmaxq);
+                    z1 = 0.f;
+                } else {
+                    s1 = __fdiv_rn(hi1 - lo1, fmaxq);
+                    z1 = rintf(__fdiv_rn(-lo1, s1));
+                }
+                double acc = 0.0;
+                for (int64_t c = c0 + threadIdx.x; c < c1; c += kThreads) {
+                    const float v = row[c];
+                    float q;
+                    if (sym) {
+                        q = rintf(__fdiv_rn(v, s1));
+                        q = q < -(fmaxq + 1.f) ? -(fmaxq + 1.f) : (q > fmaxq ? fmaxq : q);
+                        q = s1 * q;
+                    } else {
+                        q = rintf(__fdiv_rn(v, s1)) + z1;
+                        q = q < 0.f ? 0.f : (q > fmaxq ? fmaxq : q);
+                        q = s1 * (q - z1);
+                    }
+                    acc += (double)powf(fabsf(q - v), norm);
+                }
+                const float err = (float)block_sum(acc, dred);
+                if (err < best) { best = err; s = s1; z = z1; }
+            }
+        }
+    }
+    if (threadIdx.x == 0) {
+        scale[(int64_t)g * R + r] = s;
+        zero[(int64_t)g * R + r] = z;
+    }
+}
+
+// whole-tensor range (perchannel == 0): single block, result replicated to all R entries
+__global__ void __launch_bounds__(kThreads) find_params_tensor_kernel(const float* __restrict__ W, int64_t R, int64_t C,
+                                                                      int64_t ldw, int maxq, int sym,
+                                                                      float* __restrict__ scale,
+                                                                      float* __restrict__ zero) {
+    __shared__ float red[16];
+    float lo = 0.f, hi = 0.f;
+    for (int64_t e = threadIdx.x; e < R * C; e += kThreads) {
+        const float v = W[(e / C) * ldw + (e % C)];
+        lo = fminf(lo, v);
+        hi = fmaxf(hi, v);
+    }
+    block_minmax(lo, hi, red);
+    float s, z;
+    range_to_params(lo, hi, maxq, sym, s, z);
+    for (int64_t r = threadIdx.x; r < R; r += kThreads) { scale[r] = s; zero[r] = z; }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads) quantize_kernel(const T* __restrict__ x, T* __restrict__ deq,
+                                                            float* __restrict__ codes, int64_t R, int64_t C,
+                                                            const float* __restrict__ scale,
+                                                            const float* __restrict__ zero, int pertensor, int maxq,
+                                                            int honour_zero) {
+    const int64_t total = R * C;
+    const float fmaxq = (float)maxq;
+    for (int64_t e = (int64_t)blockIdx.x * kThreads + threadIdx.x; e < total; e += (int64_t)gridDim.x * kThreads) {
+        const int64_t r = pertensor ? 0 : e / C;
+        const float s = scale[r];
+        const float v = load_as_float<T>(x, e);
+        float q = rintf(__fdiv_rn(v, s));
+        float d;
+        if (honour_zero) {
+            const float z = zero[r];
+            q = q + z;
+            q = q < 0.f ? 0.f : (q > fmaxq ? fmaxq : q);
+            d = s * (q - z);
+        } else {
+            q = q < -(fmaxq + 1.f) ? -(fmaxq + 1.f) : (q > fmaxq ? fmaxq : q);
+            d = s * q;
+        }
+        if (deq) store_from_float<T>(deq, e, d);
+        if (codes) codes[e] = q;
+    }
+}
+
+}  // namespace quant
+}  // namespace rq
+
+using namespace rq;
+
+extern "C" int rq_find_params(const float* W, int64_t R, int64_t C, int64_t ldw, int groupsize, int perchannel,
+                              int maxq, int sym, int mse, float norm, int grid, float maxshrink, float* scale,
+                              float* zero, void* stream) {
+    using namespace rq::quant;
+    if (!W || !scale || !zero || R <= 0 || C <= 0 || ldw < C || maxq <= 0) return RQ_ERR_INVALID;
+    cudaStream_t st = as_stream(stream);
+    if (!perchannel) {
+        if (groupsize > 0 || mse) return RQ_ERR_UNSUPPORTED;
+        find_params_tensor_kernel<<<1, kThreads, 0, st>>>(W, R, C, ldw, maxq, sym, scale, zero);
+        return check_launch();
+    }
+    const int64_t groups = groupsize > 0 ? (C + groupsize - 1) / groupsize : 1;
+    if (R > 2147483647LL || groups > 65535) return RQ_ERR_INVALID;
+    dim3 gridDim3((unsigned)R, (unsigned)groups);
+    find_params_kernel<<<gridDim3, kThreads, 0, st>>>(W, R, C, ldw, groupsize, maxq, sym, mse, norm, grid, maxshrink,
+                                                      scale, zero);
+    return check_launch();
+}
+
+extern "C" int rq_quantize(const void* x, void* deq, float* codes, int dtype, int64_t R, int64_t C, const float* scale,
+                           const float* zero, int pertensor, int maxq, int honour_zero, void* stream) {
+    using namespace rq::quant;
+    if (!x || !scale || (!deq && !codes) || R < 0 || C < 0 || (honour_zero && !zero)) return RQ_ERR_INVALID;
+    if (R * C == 0) return RQ_OK;
+    int64_t blocks = (R * C + kThreads - 1) / kThreads;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    cudaStream_t st = as_stream(stream);
+    if (dtype == RQ_F32)
+        quantize_kernel<float><<<(unsigned)blocks, kThreads, 0, st>>>(reinterpret_cast<const float*>(x),
+                                                                      reinterpret_cast<float*>(deq), codes, R, C, scale,
+                                                                      zero, pertensor, maxq, honour_zero);
+    else if (dtype == RQ_BF16)
+        quantize_kernel<__nv_bfloat16><<<(unsigned)blocks, kThreads, 0, st>>>(
+            reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<__nv_bfloat16*>(deq), codes, R, C, scale, zero,
+            pertensor, maxq, honour_zero);
+    else if (dtype == RQ_F16)
+        quantize_kernel<__half><<<(unsigned)blocks, kThreads, 0, st>>>(reinterpret_cast<const __half*>(x),
+                                                                       reinterpret_cast<__half*>(deq), codes, R, C,
+                                                                       scale, zero, pertensor, maxq, honour_zero);
+    else
+        return RQ_ERR_INVALID;
+    return check_launch();
+}

@@ -1,0 +1,134 @@
+"""GPTQ+ on B200: the ``GPTQPlus`` object of the reference's ``gptq_utils/gptq_plus_utils.py``
+(:430-2361) with the same constructor, methods, keyword arguments and attributes.  The
+saliency-grouped Hessian accumulation, its finalisation, the damped inverse factor, the
+first-order terms and the block loop run in the sm_100a kernels of this package; the
+cross-rank sum stays a ``torch.distributed`` all-reduce."""
+from __future__ import annotations
+
+import logging
+from contextlib import nullcontext
+
+import torch
+
+from .. import ops
+from ..utils import dist_utils
+from . import fasterquant_impl
+
+_NULL_CONTEXT = nullcontext()
+
+
+class GPTQPlus:
+    def __init__(self, layer, saliency: torch.Tensor, gradient: torch.Tensor, num_groups: int, alpha: float,
+                 reference_loss: float, hessian_saliency_scale: float = 1.0):
+        self.layer = layer
+        self.dev = self.layer.weight.device
+        self.rows = layer.weight.shape[0]
+        self.columns = layer.weight.shape[1]
+        self.num_groups = num_groups
+        assert self.num_groups == saliency.shape[2], "Number of groups for GuidedQuant must match saliency shape!"
+        self.alpha = alpha
+        self.reference_loss = max(reference_loss, 0)
+        self.hessian_saliency_scale = float(hessian_saliency_scale)
+        self.saliencies = saliency.float()
+        self.gradients = gradient.float()
+        # [G, C, C]; an un-normalised SUM until finalize_hessian.  The accumulation kernel
+        # maintains the tiles on or above the diagonal; reads through ``H`` see the full matrix.
+        self._H = torch.zeros((self.num_groups, self.columns, self.columns), device=self.dev)
+        self._H_upper_only = False
+        self.act_square = torch.zeros((self.columns), device=self.dev)
+        self.nsamples = saliency.shape[0]
+        self.index = 0
+        self.token_count = 0
+        self._finalized = False
+        self.profile_recorder = None
+        assert self.rows % self.num_groups == 0, (
+            f"Number of rows ({self.rows}) must be divisible by num_groups ({self.num_groups})")
+
+    @property
+    def H(self):
+        if self._H is not None and self._H_upper_only:
+            ops.hessian_finalize(self._H, None)
+            self._H_upper_only = False
+        return self._H
+
+    @H.setter
+    def H(self, value):
+        self._H = value
+        self._H_upper_only = False
+
+    @torch.no_grad()
+    def add_batch(self, inp: torch.Tensor, out):
+        """``H[g] += X^T diag(s_g) X``; ``act_square += sum x^2`` (gptq_plus_utils.py:798-857)."""
+        if self._finalized:
+            raise RuntimeError("add_batch called after finalize_hessian. Re-init GPTQPlus to reuse.")
+        rec = self.profile_recorder
+        with rec.section("add_batch.total") if rec else _NULL_CONTEXT:
+            if inp.dim() == 2:
+                inp = inp.unsqueeze(0)
+            else:
+                assert inp.dim() == 3, "Input must be 2D or 3D. Got %dD." % inp.dim()
+            with rec.section("add_batch.slice_saliency") if rec else _NULL_CONTEXT:
+                bsz = inp.shape[0]
+                sal_batch = self.saliencies[self.index: self.index + bsz].to(self.dev, non_blocking=True)
+                self.index += bsz
+            if sal_batch.dim() == 3 and inp.shape[1] > sal_batch.shape[1]:
+                inp = inp[:, inp.shape[1] - sal_batch.shape[1]:]          # leading sink tokens carry no saliency
+            with rec.section("add_batch.prepare_inputs") if rec else _NULL_CONTEXT:
+                inp = inp.reshape(-1, inp.shape[-1])
+                sal_batch = sal_batch.reshape(-1, sal_batch.shape[-1])
+                n_tokens = inp.shape[0]
+            with rec.section("add_batch.hessian_block") if rec else _NULL_CONTEXT:
+                ops.hessian_accum(inp, sal_batch, self._H, self.act_square, alpha=1.0, beta=1.0)
+                self._H_upper_only = True
+            self.token_count += n_tokens
+
+    @torch.no_grad()
+    def finalize_hessian(self):
+        """All-reduce the sums over ranks, normalise, symmetrise, zero non-finite entries
+        (gptq_plus_utils.py:859-908)."""
+        if self._finalized:
+            return
+        dist_utils.allreduce_sum_(self._H)
+        dist_utils.allreduce_sum_(self.act_square)
+        total_samples = dist_utils.allreduce_sum_scalar(self.index)
+        total_tokens = dist_utils.allreduce_sum_scalar(self.token_count)
+        if total_samples <= 0 or total_tokens <= 0:
+            raise RuntimeError("finalize_hessian called before any add_batch ran.")
+        seq_len = total_tokens / total_samples
+        counts = ops.hessian_finalize(self._H, self.act_square, div_tokens=total_samples * seq_len,
+                                      div_scale=self.hessian_saliency_scale, div_seq=seq_len, sanitize=True)
+        self._H_upper_only = False
+        ops.check_status(self.dev)
+        n_nan, n_inf = (int(v) for v in counts.tolist())
+        if n_nan or n_inf:
+            logging.warning(
+                "finalize_hessian: non-finite in H (nan=%d, inf=%d, total=%d, module=%s); "
+                "sanitising to 0 — fasterquant's dead-channel check will take over.",
+                n_nan, n_inf, self._H.numel(), self.layer.__class__.__name__)
+        self._finalized = True
+
+    def fasterquant(self, blocksize=128, percdamp=0.01, groupsize=-1, actorder=False, static_groups=False,
+                    enable_gradient_update=True, g_update_mode="frozen", export_to_et=False, profile_recorder=None,
+                    gradient_refresh_fn=None, grad_lr=1e-3, grad_optimizer="sgd", curvature_damping=0.1,
+                    grad_reg_strategy="none", grad_reg_lambda=0.0, grad_gate_floor=0.1, grad_gate_sharpness=1.0,
+                    grad_gate_sine_amp=0.0, second_order_scale=1.0, block_atomic_quant=False, block_observer=None,
+                    grad_clip=1.0, diagnostic_recorder=None, slide_refresh_start=0, slide_refresh_block_total=None,
+                    refresh_full_metrics=False):
+        """gptq_plus_utils.py:910-1896."""
+        profile_recorder = profile_recorder or self.profile_recorder
+        with profile_recorder.section("fasterquant.total") if profile_recorder else _NULL_CONTEXT:
+            fasterquant_impl.plus_fasterquant(
+                self, blocksize=blocksize, percdamp=percdamp, groupsize=groupsize, actorder=actorder,
+                static_groups=static_groups, enable_gradient_update=enable_gradient_update,
+                g_update_mode=g_update_mode, export_to_et=export_to_et, profile_recorder=profile_recorder,
+                gradient_refresh_fn=gradient_refresh_fn, grad_reg_strategy=grad_reg_strategy,
+                second_order_scale=second_order_scale, block_atomic_quant=block_atomic_quant,
+                block_observer=block_observer, diagnostic_recorder=diagnostic_recorder)
+        if torch.any(torch.isnan(self.layer.weight.data)):
+            logging.warning("NaN in weights")
+            raise ValueError("NaN in weights")
+
+    def free(self):
+        self.H = None
+        self.Losses = None
+        torch.cuda.empty_cache()

@@ -1,0 +1,93 @@
+"""Thin torch-facing wrappers of the Hessian entry points of the C ABI: argument checks,
+scratch memory taken from torch's caching allocator, current-stream plumbing."""
+from __future__ import annotations
+
+import os
+
+import torch
+
+from . import _lib
+
+# tokens packed and contracted per launch pair; the scratch grows with it (about
+# (2 + 2G) * C * chunk * 2 bytes)
+HESSIAN_CHUNK_TOKENS = int(os.environ.get("REALQ_HESSIAN_CHUNK", "8192"))
+
+_scratch = {}
+_status = {}
+
+
+def _workspace(device, nbytes: int) -> torch.Tensor:
+    buf = _scratch.get(device)
+    if buf is None or buf.numel() < nbytes:
+        _scratch[device] = None
+        buf = torch.empty(nbytes + 1024, dtype=torch.uint8, device=device)
+        _scratch[device] = buf
+    return buf
+
+
+def release_workspace() -> None:
+    _scratch.clear()
+
+
+def status_word(device) -> torch.Tensor:
+    """Device int32 that kernels set when one of their bounded waits ran out."""
+    t = _status.get(device)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=device)
+        _status[device] = t
+    return t
+
+
+def check_status(device) -> None:
+    """Read the status word (synchronises) and raise if a kernel reported a time-out."""
+    code = int(status_word(device).item())
+    if code != _lib.RQ_OK:
+        status_word(device).zero_()
+        raise _lib.RealQError("device status", code)
+
+
+def hessian_accum(x: torch.Tensor, sal, H: torch.Tensor, act_sq, alpha: float = 1.0, beta: float = 1.0,
+                  variant: int = 0, chunk_tokens: int | None = None) -> None:
+    """``H[g] = beta*H[g] + alpha * X^T diag(sal[:, g]) X`` (upper-triangular tiles only) and
+    ``act_sq += sum x^2``.  x: [N, C] fp32/bf16/fp16 (row stride free), sal: [N, G] fp32 or None,
+    H: [G, C, C] fp32 contiguous (or [C, C] when sal is None)."""
+    _lib.require_cuda(x, H, sal, act_sq)
+    assert x.dim() == 2, "x must be [tokens, channels]"
+    N, Cc = x.shape
+    if x.stride(1) != 1:
+        x = x.contiguous()
+    G = 1 if sal is None else sal.shape[1]
+    assert H.is_contiguous() and H.dtype == torch.float32 and H.numel() == G * Cc * Cc
+    if sal is not None:
+        assert sal.shape[0] == N
+        sal = sal.to(dtype=torch.float32).contiguous()
+    if act_sq is not None:
+        assert act_sq.dtype == torch.float32 and act_sq.is_contiguous() and act_sq.numel() == Cc
+    chunk = int(chunk_tokens or HESSIAN_CHUNK_TOKENS)
+    chunk = max(64, min(chunk, (N + 63) // 64 * 64))
+    with torch.cuda.device(x.device):
+        need = _lib.lib.rq_hessian_workspace_bytes(chunk, Cc, G, 0 if sal is None else 1)
+        ws = _workspace(x.device, need)
+        base = ws.data_ptr()
+        aligned = (base + 1023) // 1024 * 1024
+        rc = _lib.lib.rq_hessian_accum(_lib.ptr(x), _lib.dtype_code(x), x.stride(0), _lib.ptr(sal), _lib.ptr(H),
+                                       _lib.ptr(act_sq), N, Cc, G, float(alpha), float(beta), aligned,
+                                       ws.numel() - (aligned - base), _lib.ptr(status_word(x.device)), int(variant),
+                                       _lib.stream_of(x))
+    _lib.check("rq_hessian_accum", rc)
+
+
+def hessian_finalize(H: torch.Tensor, act_sq, div_tokens: float = 1.0, div_scale: float = 1.0,
+                     div_seq: float = 1.0, sanitize: bool = False):
+    """Scale, mirror the upper triangle into the lower one, optionally zero non-finite entries.
+    Returns the device uint64[2] (NaN count, Inf count) when ``sanitize`` else None."""
+    _lib.require_cuda(H, act_sq)
+    assert H.is_contiguous() and H.dtype == torch.float32
+    Cc = H.shape[-1]
+    G = H.numel() // (Cc * Cc)
+    counts = torch.zeros(2, dtype=torch.int64, device=H.device) if sanitize else None
+    with torch.cuda.device(H.device):
+        rc = _lib.lib.rq_hessian_finalize(_lib.ptr(H), _lib.ptr(act_sq), Cc, G, float(div_tokens), float(div_scale),
+                                          float(div_seq), 1 if sanitize else 0, _lib.ptr(counts), _lib.stream_of(H))
+    _lib.check("rq_hessian_finalize", rc)
+    return counts

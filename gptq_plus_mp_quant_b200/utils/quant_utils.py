@@ -1,0 +1,207 @@
+"""Weight quantizer on B200: the ``WeightQuantizer`` / STE interface of the reference's
+``utils/quant_utils.py`` (:21-84, :300-486) over the ``rq_find_params`` / ``rq_quantize``
+kernels.  Names, arguments, buffer shapes and error behaviour follow the reference; the
+per-token grouped variant (``weight_groupsize > 0``, :333-388), which the GPTQ path never
+reaches, is not provided and raises.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+
+from .. import _lib
+
+
+def get_minq_maxq(bits, sym):
+    """quant_utils.py:21-29."""
+    if sym:
+        maxq = torch.tensor(2 ** (bits - 1) - 1)
+        minq = -maxq - 1
+    else:
+        maxq = torch.tensor(2 ** bits - 1)
+        minq = 0
+    return minq, maxq
+
+
+def _row_params(x: torch.Tensor, scale: torch.Tensor, zero):
+    """Flatten scale/zero to one fp32 entry per row of ``x`` viewed ``[R, C]`` (or a single entry)."""
+    R = x.shape[0] if x.dim() > 1 else 1
+    s = scale.to(device=x.device, dtype=torch.float32).reshape(-1)
+    z = None if zero is None else zero.to(device=x.device, dtype=torch.float32).reshape(-1)
+    if s.numel() == 1:
+        return s.contiguous(), (None if z is None else z.contiguous()), 1
+    if s.numel() != R:
+        raise ValueError(f"scale has {s.numel()} entries for {R} rows")
+    return s.contiguous(), (None if z is None else z.contiguous()), 0
+
+
+def quantize_dequantize(x: torch.Tensor, scale, zero, maxq, honour_zero: bool, want_codes: bool = False):
+    """One kernel pass: ``(dequantized in x.dtype, integer codes fp32 or None)``."""
+    _lib.require_cuda(x)
+    xc = x.contiguous()
+    R = xc.shape[0] if xc.dim() > 1 else 1
+    Ccols = xc.numel() // R if R else 0
+    s, z, pertensor = _row_params(xc, scale, zero if honour_zero else None)
+    deq = torch.empty_like(xc)
+    codes = torch.empty(xc.shape, dtype=torch.float32, device=xc.device) if want_codes else None
+    with torch.cuda.device(xc.device):
+        rc = _lib.lib.rq_quantize(_lib.ptr(xc), _lib.ptr(deq), _lib.ptr(codes), _lib.dtype_code(xc), R, Ccols,
+                                  _lib.ptr(s), _lib.ptr(z), pertensor, int(maxq), 1 if honour_zero else 0,
+                                  _lib.stream_of(xc))
+    _lib.check("rq_quantize", rc)
+    return deq, codes
+
+
+def sym_quant(x, scale, maxq):
+    """quant_utils.py:47-50."""
+    _, q = quantize_dequantize(x, scale, None, maxq, False, want_codes=True)
+    return q.to(x.dtype), scale.to(x.device)
+
+
+def sym_dequant(q, scale):
+    return scale * q
+
+
+def sym_quant_dequant(x, scale, maxq):
+    """quant_utils.py:57-58."""
+    return quantize_dequantize(x, scale, None, maxq, False)[0]
+
+
+def asym_quant(x, scale, zero, maxq):
+    """quant_utils.py:32-36."""
+    _, q = quantize_dequantize(x, scale, zero, maxq, True, want_codes=True)
+    return q.to(x.dtype), scale.to(x.device), zero.to(x.device)
+
+
+def asym_dequant(q, scale, zero):
+    return scale * (q - zero)
+
+
+def asym_quant_dequant(x, scale, zero, maxq):
+    """quant_utils.py:43-44."""
+    return quantize_dequantize(x, scale, zero, maxq, True)[0]
+
+
+class STEQuantize(torch.autograd.Function):
+    """Symmetric quantize-dequantize with a straight-through gradient (quant_utils.py:60-71)."""
+
+    @staticmethod
+    def forward(ctx, x, scale, maxq):
+        return quantize_dequantize(x, scale, None, maxq, False)[0]
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        return grad_output, None, None
+
+
+class AsymSTEQuantize(torch.autograd.Function):
+    """Asymmetric variant (quant_utils.py:74-84)."""
+
+    @staticmethod
+    def forward(ctx, x, scale, zero, maxq):
+        return quantize_dequantize(x, scale, zero, maxq, True)[0]
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        return grad_output, None, None, None
+
+
+def find_params_groups(W: torch.Tensor, groupsize: int, maxq: int, sym: bool, mse: bool = False,
+                       norm: float = 2.4, grid: int = 50, maxshrink: float = 0.5):
+    """Per-row ranges of every ``groupsize``-wide column group in one launch:
+    ``(scale, zero)`` each ``[ngroups, R]``.  Equals ``deepcopy(quantizer).find_params(W[:, g*gs:(g+1)*gs])``
+    for every g (gptq_utils/gptq_plus_utils.py:995-1002)."""
+    _lib.require_cuda(W)
+    assert W.dim() == 2 and W.dtype == torch.float32
+    R, Ccols = W.shape
+    ng = (Ccols + groupsize - 1) // groupsize if groupsize > 0 else 1
+    scale = torch.empty(ng, R, dtype=torch.float32, device=W.device)
+    zero = torch.empty(ng, R, dtype=torch.float32, device=W.device)
+    Wc = W if W.stride(1) == 1 else W.contiguous()
+    with torch.cuda.device(W.device):
+        rc = _lib.lib.rq_find_params(_lib.ptr(Wc), R, Ccols, Wc.stride(0), int(groupsize), 1, int(maxq),
+                                     1 if sym else 0, 1 if mse else 0, float(norm), int(grid), float(maxshrink),
+                                     _lib.ptr(scale), _lib.ptr(zero), _lib.stream_of(W))
+    _lib.check("rq_find_params", rc)
+    return scale, zero
+
+
+class WeightQuantizer(torch.nn.Module):
+    """Drop-in for the reference ``WeightQuantizer`` (quant_utils.py:300-486)."""
+
+    def __init__(self, shape: int = 1) -> None:
+        super().__init__()
+        self.register_buffer("maxq", torch.tensor(0))
+        self.register_buffer("scale", torch.zeros(shape))
+        self.register_buffer("zero", torch.zeros(shape))
+
+    def configure(self, bits, perchannel: bool = False, sym: bool = True, mse: bool = False, norm: float = 2.4,
+                  grid: int = 50, maxshrink: float = 0.5, weight_groupsize: int = -1) -> None:
+        self.bits = bits
+        self.perchannel = perchannel
+        self.sym = sym
+        self.mse = mse
+        self.norm = norm
+        self.grid = grid
+        self.maxshrink = maxshrink
+        self.weight_groupsize = weight_groupsize
+        if sym:
+            self.maxq = torch.tensor(2 ** (bits - 1) - 1)
+        else:
+            self.maxq = torch.tensor(2 ** bits - 1)
+
+    def find_params(self, x) -> None:
+        if self.bits == 16:
+            return
+        if self.weight_groupsize > 0:
+            raise NotImplementedError("grouped per-token weight ranges (weight_groupsize > 0) are outside the GPTQ path")
+        _lib.require_cuda(x)
+        dev = x.device
+        self.maxq = self.maxq.to(dev)
+        shape = x.shape
+        x2 = x.flatten(1) if self.perchannel else x.flatten().unsqueeze(0)
+        x2 = x2.float()
+        if x2.stride(1) != 1:
+            x2 = x2.contiguous()
+        R, Ccols = x2.shape
+        if not self.perchannel and self.mse:
+            raise NotImplementedError("the shrink-grid search is provided for per-channel ranges only")
+        scale = torch.empty(R, dtype=torch.float32, device=dev)
+        zero = torch.empty(R, dtype=torch.float32, device=dev)
+        with torch.cuda.device(dev):
+            rc = _lib.lib.rq_find_params(_lib.ptr(x2), R, Ccols, x2.stride(0), -1, 1, int(self.maxq),
+                                         1 if self.sym else 0, 1 if self.mse else 0, float(self.norm),
+                                         int(self.grid), float(self.maxshrink), _lib.ptr(scale), _lib.ptr(zero),
+                                         _lib.stream_of(x2))
+        _lib.check("rq_find_params", rc)
+        if not self.perchannel:
+            scale = scale.repeat(shape[0])
+            zero = zero.repeat(shape[0])
+        out_shape = [-1] + [1] * (len(shape) - 1)
+        self.scale = scale.reshape(out_shape)
+        self.zero = zero.reshape(out_shape)
+
+    def quantize(self, x):
+        x_dtype = x.dtype
+        if self.ready() and self.bits < 16:
+            if self.sym:
+                return STEQuantize.apply(x, self.scale, self.maxq).to(x_dtype)
+            return AsymSTEQuantize.apply(x, self.scale, self.zero, self.maxq).to(x_dtype)
+        return x
+
+    def fake_quantize(self, x, st_idx=None, end_idx=None):
+        """(dequantized, integer codes, scale): always the symmetric clamp, the zero-point is
+        ignored, exactly like the reference (quant_utils.py:471-480)."""
+        if self.ready() and self.bits < 16:
+            scale = self.scale.to(x.device)
+            if st_idx is not None and end_idx is not None:
+                scale = scale[st_idx:end_idx]
+            deq, codes = quantize_dequantize(x, scale, None, self.maxq, False, want_codes=True)
+            return deq, codes.to(x.dtype), scale
+        return None, None, None
+
+    def enabled(self):
+        return self.maxq > 0
+
+    def ready(self):
+        return torch.all(self.scale != 0)

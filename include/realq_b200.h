@@ -1,0 +1,117 @@
+/*
+ * realq_b200 — C ABI of the B200 (sm_100a) kernels behind the per-layer GPTQ / GPTQ+
+ * quantization path of REAL-Q (Mrluxianseng/gptq_plus_mp_quant).
+ *
+ * The reference is pure PyTorch and has no FFI layer of its own; each entry point below names
+ * the reference statements (file:line inside the reference project) that it replaces.  All
+ * pointers are DEVICE pointers unless stated otherwise, all matrices are row-major, `stream`
+ * is a cudaStream_t passed as void*, and every function returns an RQ_* status code.  Nothing
+ * here allocates device memory: scratch is passed in by the caller.  No function synchronises
+ * the stream.
+ */
+#ifndef REALQ_B200_H_
+#define REALQ_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* status codes */
+#define RQ_OK 0
+#define RQ_ERR_INVALID 1     /* bad argument (null pointer, unsupported size, misaligned) */
+#define RQ_ERR_CUDA 2        /* a CUDA runtime / driver call failed                       */
+#define RQ_ERR_TIMEOUT 3     /* a bounded device-side wait ran out (written to `status`)   */
+#define RQ_ERR_WORKSPACE 4   /* caller-provided scratch too small                          */
+#define RQ_ERR_UNSUPPORTED 5 /* configuration not implemented by this build                */
+
+/* element types of activations / weights crossing the boundary */
+#define RQ_F32 0
+#define RQ_BF16 1
+#define RQ_F16 2
+
+int rq_version(void);
+const char* rq_error_string(int code);
+
+/* Per-kernel device timing for benchmarks (no counterpart in the reference, which wraps its
+ * stages in CUDA-event pairs from Python, gptq_utils/gptq_plus_utils.py:228-289).  While enabled,
+ * every launch of a tagged kernel is bracketed by two CUDA events on its stream;
+ * rq_profile_read waits for them and returns the summed duration and launch count of one tag.
+ * rq_profile_enable (either value) drops the spans recorded so far. */
+#define RQ_PROF_HESSIAN_UMMA 1
+#define RQ_PROF_HESSIAN_PACK 2
+#define RQ_PROF_FWHT 3
+#define RQ_PROF_CHOL 4
+#define RQ_PROF_BLOCK 5
+#define RQ_PROF_LAZY 6
+int rq_profile_enable(int on);
+int rq_profile_read(int tag, double* total_ms, long long* launches);
+
+/* ------------------------------------------------------------------------------------------
+ * Hessian accumulation.
+ * Replaces GPTQPlus.add_batch (gptq_utils/gptq_plus_utils.py:839-856:
+ *   weighted = inp[None] * sal^T[:, :, None]; H += bmm(inp^T, weighted); act_square += (inp**2).sum(0))
+ * and GPTQ.add_batch (gptq_utils/gptq_utils.py:39-43: H *= n/(n+b); H += (2/n) X^T X).
+ *
+ *   H[g] = beta * H[g] + alpha * X^T diag(sal[:, g]) X        g < G   (sal == NULL: weights 1, G must be 1)
+ *   act_sq += sum_tokens x^2                                   (skipped when act_sq == NULL)
+ *
+ * x: [N, C] with row stride ldx elements, dtype x_dtype; sal: [N, G] fp32; H: [G, C, C] fp32.
+ * Only tiles on or above the diagonal of every H[g] are written; rq_hessian_finalize (or its
+ * mirror-only mode) fills the lower triangle.  The contraction runs on the tensor cores as a
+ * split-bf16 product with fp32 accumulation: three products when x is fp32/fp16, two when x is
+ * bf16 (its low part is exactly zero).
+ * workspace: rq_hessian_workspace_bytes(chunk_tokens, C, G, sal != NULL) bytes for the chunk
+ * size the caller wants (a multiple of 64; tokens are processed chunk by chunk), 1024-byte aligned.
+ * status: optional device int; set to RQ_ERR_TIMEOUT if a device-side wait ran out.
+ * variant: 0 = 64-token pipeline stages (128-byte swizzle), 1 = 32-token stages (64-byte swizzle).
+ */
+size_t rq_hessian_workspace_bytes(int64_t chunk_tokens, int C, int G, int has_saliency);
+int rq_hessian_accum(const void* x, int x_dtype, int64_t ldx, const float* sal, float* H, float* act_sq,
+                     int64_t N, int C, int G, float alpha, float beta, void* workspace, size_t workspace_bytes,
+                     int* status, int variant, void* stream);
+
+/* Replaces GPTQPlus.finalize_hessian after its all-reduce (gptq_utils/gptq_plus_utils.py:881-907):
+ *   H /= div_tokens; H /= div_scale (skipped when 1); act_sq /= div_seq;
+ *   H = (H + H^T)/2  — realised by mirroring the computed upper triangle —; non-finite -> 0.
+ * counts: optional device uint64[2] receiving the number of NaN and Inf entries found (in the
+ * full symmetric matrix), which the host turns into the reference's warning.
+ * With div_tokens = div_scale = div_seq = 1, act_sq = NULL and sanitize = 0 this is a pure mirror. */
+int rq_hessian_finalize(float* H, float* act_sq, int C, int G, float div_tokens, float div_scale, float div_seq,
+                        int sanitize, unsigned long long* counts, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Walsh-Hadamard rotation y = x . H_n * scale, n = K * 2^m.
+ * Replaces hadamard_utils.matmul_hadU_cuda / HadamardTransform (utils/hadamard_utils.py:89-98,121-130)
+ * and the third-party fast_hadamard_transform call (utils/hadamard_utils.py:31-34).
+ * x, y: [rows, n] contiguous, same dtype (in place allowed); hadK: device fp32 [K, K] (+-1), NULL when K == 1.
+ * The FWHT runs over each contiguous n/K chunk, then chunk k' = sum_k hadK[k'][k] * chunk k. */
+int rq_fwht(const void* x, void* y, int dtype, int64_t rows, int n, int K, const float* hadK, float scale,
+            void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Weight quantizer.
+ * rq_find_params replaces WeightQuantizer.find_params (utils/quant_utils.py:390-457), and, with
+ * groupsize > 0, the static-group loop `deepcopy(quantizer).find_params(W[:, g*gs:(g+1)*gs])`
+ * (gptq_utils/gptq_plus_utils.py:995-1002, gptq_utils/gptq_utils.py:72-77).
+ * W: [R, C] fp32 row stride ldw.  groupsize <= 0: one range per row (or one for the whole tensor
+ * when perchannel == 0) -> scale/zero [R].  groupsize > 0: ngroups = ceil(C/groupsize) ranges
+ * per row -> scale/zero [ngroups, R].  mse != 0 runs the shrink-grid search (norm, grid, maxshrink). */
+int rq_find_params(const float* W, int64_t R, int64_t C, int64_t ldw, int groupsize, int perchannel, int maxq,
+                   int sym, int mse, float norm, int grid, float maxshrink, float* scale, float* zero,
+                   void* stream);
+
+/* rq_quantize replaces STEQuantize / AsymSTEQuantize forward and WeightQuantizer.fake_quantize
+ * (utils/quant_utils.py:60-84, 471-480).  x, deq: [R, C] of dtype; scale/zero: [R] fp32 (row r uses
+ * entry r; pertensor != 0: entry 0).  honour_zero != 0: clamp(round(x/s)+z, 0, maxq), deq = s*(q-z);
+ * otherwise the symmetric clamp [-(maxq+1), maxq] and deq = s*q.  codes (optional, fp32 [R, C])
+ * receives the integer codes. */
+int rq_quantize(const void* x, void* deq, float* codes, int dtype, int64_t R, int64_t C, const float* scale,
+                const float* zero, int pertensor, int maxq, int honour_zero, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* REALQ_B200_H_ */

@@ -74,6 +74,10 @@ def gen_hadamard(hu, out):
     for k in (12, 20, 28):
         out[f"had{k}"] = np32(had_tab[k]).astype(np.int8)
     out["table_keys"] = np.array(sorted(had_tab.keys()))
+    import hashlib
+    for k in sorted(had_tab.keys()):
+        raw = np.ascontiguousarray(np32(had_tab[k]).astype(np.int8)).tobytes()
+        out[f"had_sha.{k}"] = np.array(hashlib.sha256(raw).hexdigest()[:16])
     for name, rows, n, dtype in cases.HADAMARD_CASES:
         dt = getattr(torch, dtype)
         x = cases.make_acts(1, rows, n, seed=5).reshape(rows, n).to(dt)
