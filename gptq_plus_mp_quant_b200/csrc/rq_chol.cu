@@ -1,0 +1,292 @@
+// Damped inverse-Hessian factor: Hinv = upper Cholesky factor U of (H + lambda I)^-1, i.e.
+// H^-1 = U^T U, which is what the reference obtains from potrf -> potri -> potrf(upper).
+//
+// B200 route (2/3 C^3 flops instead of 4/3 C^3):  write P = H + lambda I = R R^T with R UPPER
+// triangular (a Cholesky factorisation that runs from the last column to the first); then
+// P^-1 = R^-T R^-1, so U = R^-1, an upper-triangular inverse.
+//   phase 1  blocked right-looking "reverse" Cholesky, 128-wide block columns, last to first:
+//            diagonal block factored and inverted in fp64 inside one CTA; panel R_ik = A_ik.inv(R_kk)^T
+//            and trailing update A_ij -= R_ik.R_jk^T as fp32 GEMM tiles;
+//   phase 2  recursive-doubling triangular inverse: inv([[A,B],[0,D]]) = [[A^-1, -A^-1.B.D^-1],[0, D^-1]],
+//            two batched GEMM launches per level.
+// All G groups of a linear are processed in the same launches (grid.z).
+#include "rq_common.cuh"
+#include "rq_gemm.cuh"
+
+namespace rq {
+namespace chol {
+
+constexpr int NB = 128;                       // block-column width = GEMM tile edge
+constexpr int kDiagThreads = 512;
+constexpr int kDiagLd = NB + 1;               // fp64 row stride in shared memory (bank spread)
+
+// ------------------------------------------------------------------------------------------
+// mean of the dead-fixed diagonal per group (one block per group)
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) diag_mean_kernel(const float* __restrict__ H, int C, float* __restrict__ mean) {
+    __shared__ double red[8];
+    const float* Hg = H + (int64_t)blockIdx.x * C * C;
+    double s = 0.0;
+    for (int c = threadIdx.x; c < C; c += 256) {
+        const float d = Hg[(int64_t)c * C + c];
+        s += (d == 0.f) ? 1.0 : (double)d;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        double t = 0.0;
+        for (int w = 0; w < 8; ++w) t += red[w];
+        mean[blockIdx.x] = (float)(t / (double)C);
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// A[g][i][j] = H[g][perm[i]][perm[j]] (+ dead fix, + damping on the diagonal), padded to Cp with
+// an identity block.  Only the upper triangle is consumed afterwards.
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) gather_kernel(const float* __restrict__ H, const int64_t* __restrict__ perm,
+                                                     const float* __restrict__ mean, const float* __restrict__ factor,
+                                                     int C, int Cp, float* __restrict__ A) {
+    const int g = blockIdx.z;
+    const int i = blockIdx.y;
+    const float* Hg = H + (int64_t)g * C * C;
+    float* Arow = A + ((int64_t)g * Cp + i) * Cp;
+    const float lambda = factor[g] * mean[g];
+    const int64_t pi = (i < C) ? (perm ? perm[i] : i) : 0;
+    for (int j = blockIdx.x * 256 + threadIdx.x; j < Cp; j += gridDim.x * 256) {
+        float v;
+        if (i < C && j < C) {
+            const int64_t pj = perm ? perm[j] : j;
+            v = Hg[pi * C + pj];
+            if (i == j) {
+                if (v == 0.f) v = 1.f;               // dead input channel
+                v += lambda;
+            }
+        } else {
+            v = (i == j) ? 1.f : 0.f;
+        }
+        Arow[j] = v;
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// Diagonal block k: A_kk = R_kk R_kk^T (R upper) and U_kk = R_kk^-1, both in fp64, stored fp32.
+// One CTA per group.
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kDiagThreads) diag_block_kernel(float* __restrict__ A, float* __restrict__ U, int Cp,
+                                                                  int kblk, int* __restrict__ info) {
+    extern __shared__ double S[];                         // [NB][kDiagLd]; upper: R, strict lower: inv^T
+    __shared__ double dinv[NB];
+    __shared__ int bad;
+    const int g = blockIdx.x;
+    const int64_t origin = ((int64_t)g * Cp + (int64_t)kblk * NB) * Cp + (int64_t)kblk * NB;
+    float* Ab = A + origin;
+    float* Ub = U + origin;
+    const int tid = threadIdx.x;
+    if (tid == 0) bad = 0;
+    for (int e = tid; e < NB * NB; e += kDiagThreads) {
+        const int i = e / NB, j = e % NB;
+        S[i * kDiagLd + j] = (j >= i) ? (double)Ab[(int64_t)i * Cp + j] : 0.0;
+    }
+    __syncthreads();
+    // reverse Cholesky: eliminate columns from the last to the first
+    for (int c = NB - 1; c >= 0; --c) {
+        const double p = S[c * kDiagLd + c];
+        if (!(p > 0.0) && tid == 0) bad = 1;              // catches <= 0 and NaN
+        const double r = sqrt(p);
+        const double rinv = 1.0 / r;
+        __syncthreads();                                  // everyone has read the pivot
+        if (tid < c) S[tid * kDiagLd + c] *= rinv;
+        else if (tid == c) S[c * kDiagLd + c] = r;
+        __syncthreads();
+        const int cc = c * c;
+        for (int e = tid; e < cc; e += kDiagThreads) {
+            const int i = e / c, j = e - i * c;
+            if (j >= i) S[i * kDiagLd + j] -= S[i * kDiagLd + c] * S[j * kDiagLd + c];
+        }
+        __syncthreads();
+    }
+    // inverse of the upper-triangular R: column j of the inverse lives in row j of the strict lower part
+    if (tid < NB) dinv[tid] = 1.0 / S[tid * kDiagLd + tid];
+    __syncthreads();
+    for (int i = NB - 2; i >= 0; --i) {
+        if (tid < NB && tid > i) {
+            const int j = tid;
+            // x_j[i] = -( sum_{l=i+1..j} R[i][l] * x_j[l] ) / R[i][i],  x_j[j] = dinv[j]
+            double s = S[i * kDiagLd + j] * dinv[j];
+            for (int l = i + 1; l < j; ++l) s += S[i * kDiagLd + l] * S[j * kDiagLd + l];
+            S[j * kDiagLd + i] = -s * dinv[i];
+        }                                                 // a thread only re-reads its own row: no barrier needed
+    }
+    __syncthreads();
+    for (int e = tid; e < NB * NB; e += kDiagThreads) {
+        const int i = e / NB, j = e % NB;
+        float rv = 0.f, uv = 0.f;
+        if (j >= i) {
+            rv = (float)S[i * kDiagLd + j];
+            uv = (j == i) ? (float)dinv[i] : (float)S[j * kDiagLd + i];
+        }
+        Ab[(int64_t)i * Cp + j] = rv;
+        Ub[(int64_t)i * Cp + j] = uv;
+    }
+    if (tid == 0 && bad) atomicCAS(&info[g], 0, kblk + 1);
+}
+
+// ------------------------------------------------------------------------------------------
+// GEMM-shaped steps (one 128x128 tile per CTA, grid.z = group)
+// ------------------------------------------------------------------------------------------
+// panel: A[i-block][k] <- A[i-block][k] . U_kk^T   for i < k      grid (k, 1, G)
+__global__ void __launch_bounds__(gemm::kThreads) panel_kernel(float* __restrict__ A, const float* __restrict__ U,
+                                                               int Cp, int kblk) {
+    extern __shared__ float smem[];
+    const int64_t gofs = (int64_t)blockIdx.z * Cp * Cp;
+    gemm::Args a;
+    a.A = A + gofs + (int64_t)kblk * NB; a.lda = Cp;                                 // columns of block k
+    a.B = U + gofs + ((int64_t)kblk * NB) * Cp + (int64_t)kblk * NB; a.ldb = Cp;      // U_kk as [N, K]
+    a.C = A + gofs + (int64_t)kblk * NB; a.ldc = Cp;
+    a.Aux = nullptr; a.ldaux = 0;
+    a.M = kblk * NB; a.N = NB; a.K = NB;
+    a.alpha = 1.f; a.beta = 0.f; a.gamma = 0.f;
+    a.k_begin = 0; a.k_end = NB;
+    gemm::tile<true>(a, blockIdx.x * NB, 0, smem);
+}
+
+// trailing: A[i][j] -= R[i][k] . R[j][k]^T   for i <= j < k      grid (k(k+1)/2, 1, G)
+__global__ void __launch_bounds__(gemm::kThreads) trailing_kernel(float* __restrict__ A, int Cp, int kblk) {
+    extern __shared__ float smem[];
+    int bi, bj;
+    {
+        const int u = blockIdx.x;
+        int jj = static_cast<int>((sqrtf(8.f * static_cast<float>(u) + 1.f) - 1.f) * 0.5f);
+        while ((jj + 1) * (jj + 2) / 2 <= u) ++jj;
+        while (jj * (jj + 1) / 2 > u) --jj;
+        bj = jj;
+        bi = u - jj * (jj + 1) / 2;
+    }
+    const int64_t gofs = (int64_t)blockIdx.z * Cp * Cp;
+    gemm::Args a;
+    a.A = A + gofs + (int64_t)kblk * NB; a.lda = Cp;
+    a.B = A + gofs + (int64_t)kblk * NB; a.ldb = Cp;
+    a.C = A + gofs; a.ldc = Cp;
+    a.Aux = nullptr; a.ldaux = 0;
+    a.M = kblk * NB; a.N = kblk * NB; a.K = NB;
+    a.alpha = -1.f; a.beta = 1.f; a.gamma = 0.f;
+    a.k_begin = 0; a.k_end = NB;
+    gemm::tile<true>(a, bi * NB, bj * NB, smem);
+}
+
+// inverse, level with block size s: for pair m: a = [2ms, (2m+1)s), b = [(2m+1)s, min((2m+2)s, Cp))
+//   step 1: T[a, b] = U[a, a] . R[a, b]          (U[a,a] upper: k starts at the row block)
+//   step 2: U[a, b] = - T[a, b] . U[b, b]        (U[b,b] upper: k ends with the column block)
+// grid (tiles_m * tiles_n, pairs, G)
+__global__ void __launch_bounds__(gemm::kThreads) inv_level_kernel(const float* __restrict__ R, float* __restrict__ U,
+                                                                   float* __restrict__ T, int Cp, int s, int step) {
+    extern __shared__ float smem[];
+    const int m = blockIdx.y;
+    const int a0 = 2 * m * s, b0 = a0 + s;
+    if (b0 >= Cp) return;
+    const int b1 = (b0 + s < Cp) ? b0 + s : Cp;
+    const int nb_cols = b1 - b0;
+    const int tiles_n = (nb_cols + NB - 1) / NB;
+    const int tiles_m = s / NB;
+    const int ti = blockIdx.x % tiles_m, tj = blockIdx.x / tiles_m;
+    if (tj >= tiles_n) return;
+    const int64_t gofs = (int64_t)blockIdx.z * Cp * Cp;
+    gemm::Args a;
+    a.Aux = nullptr; a.ldaux = 0; a.gamma = 0.f; a.beta = 0.f;
+    a.M = s; a.N = nb_cols;
+    if (step == 1) {
+        a.A = U + gofs + (int64_t)a0 * Cp + a0; a.lda = Cp;
+        a.B = R + gofs + (int64_t)a0 * Cp + b0; a.ldb = Cp;
+        a.C = T + gofs + (int64_t)a0 * Cp + b0; a.ldc = Cp;
+        a.K = s; a.alpha = 1.f;
+        a.k_begin = ti * NB; a.k_end = s;
+    } else {
+        a.A = T + gofs + (int64_t)a0 * Cp + b0; a.lda = Cp;
+        a.B = U + gofs + (int64_t)b0 * Cp + b0; a.ldb = Cp;
+        a.C = U + gofs + (int64_t)a0 * Cp + b0; a.ldc = Cp;
+        a.K = nb_cols; a.alpha = -1.f;
+        a.k_begin = 0; a.k_end = ((tj + 1) * NB < nb_cols) ? (tj + 1) * NB : nb_cols;
+    }
+    gemm::tile<false>(a, ti * NB, tj * NB, smem);
+}
+
+// non-finite scan of the result (upper triangle incl. diagonal); marks info[g] = -1 when info[g] == 0
+__global__ void __launch_bounds__(256) finite_check_kernel(const float* __restrict__ U, int Cp, int* __restrict__ info) {
+    const int g = blockIdx.y;
+    const float* Ug = U + (int64_t)g * Cp * Cp;
+    int badv = 0;
+    for (int64_t e = (int64_t)blockIdx.x * 256 + threadIdx.x; e < (int64_t)Cp * Cp; e += (int64_t)gridDim.x * 256) {
+        const float v = Ug[e];
+        if (isnan(v) || isinf(v)) badv = 1;
+    }
+    if (__syncthreads_or(badv) && threadIdx.x == 0) atomicCAS(&info[g], 0, -1);
+}
+
+}  // namespace chol
+}  // namespace rq
+
+using namespace rq;
+
+extern "C" size_t rq_chol_workspace_bytes(int C, int G) {
+    if (C <= 0 || G <= 0) return 0;
+    const size_t Cp = (size_t)(C + chol::NB - 1) / chol::NB * chol::NB;
+    return 2 * (size_t)G * Cp * Cp * sizeof(float) + 256 * sizeof(float) + 1024;     // A, T, per-group means
+}
+
+extern "C" int rq_chol_hinv(const float* H, const int64_t* perm, const float* damp_factor, float* Hinv, int C, int G,
+                            int* info, void* workspace, size_t workspace_bytes, void* stream) {
+    using namespace rq::chol;
+    if (!H || !damp_factor || !Hinv || !info || !workspace || C <= 0 || G <= 0 || G > 64) return RQ_ERR_INVALID;
+    if (workspace_bytes < rq_chol_workspace_bytes(C, G)) return RQ_ERR_WORKSPACE;
+    if (reinterpret_cast<uintptr_t>(workspace) % 256 != 0 || reinterpret_cast<uintptr_t>(Hinv) % 16 != 0)
+        return RQ_ERR_INVALID;
+    cudaStream_t st = as_stream(stream);
+    const int Cp = (C + NB - 1) / NB * NB;
+    const int nblk = Cp / NB;
+    const size_t mat = (size_t)G * Cp * Cp;
+    float* A = reinterpret_cast<float*>(workspace);
+    float* T = A + mat;
+    float* mean = T + mat;              // [G] means, then [G] damping factors
+    float* factor = mean + 64;
+    prof::Scope timed(RQ_PROF_CHOL, st);
+
+    if (cudaMemcpyAsync(factor, damp_factor, (size_t)G * sizeof(float), cudaMemcpyHostToDevice, st) != cudaSuccess)
+        return RQ_ERR_CUDA;
+    if (cudaMemsetAsync(info, 0, (size_t)G * sizeof(int), st) != cudaSuccess) return RQ_ERR_CUDA;
+    if (cudaMemsetAsync(Hinv, 0, mat * sizeof(float), st) != cudaSuccess) return RQ_ERR_CUDA;
+    diag_mean_kernel<<<G, 256, 0, st>>>(H, C, mean);
+    {
+        dim3 grid((unsigned)((Cp + 1023) / 1024), (unsigned)Cp, (unsigned)G);
+        gather_kernel<<<grid, 256, 0, st>>>(H, perm, mean, factor, C, Cp, A);
+    }
+    int rc = check_launch();
+    if (rc != RQ_OK) return rc;
+
+    const size_t diag_smem = (size_t)NB * kDiagLd * sizeof(double);
+    if (cudaFuncSetAttribute(diag_block_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)diag_smem) != cudaSuccess)
+        return RQ_ERR_CUDA;
+    // phase 1: block columns from the last to the first
+    for (int k = nblk - 1; k >= 0; --k) {
+        diag_block_kernel<<<G, kDiagThreads, diag_smem, st>>>(A, Hinv, Cp, k, info);
+        if (k > 0) {
+            panel_kernel<<<dim3((unsigned)k, 1, (unsigned)G), gemm::kThreads, gemm::kSmemBytes, st>>>(A, Hinv, Cp, k);
+            trailing_kernel<<<dim3((unsigned)(k * (k + 1) / 2), 1, (unsigned)G), gemm::kThreads, gemm::kSmemBytes, st>>>(
+                A, Cp, k);
+        }
+    }
+    rc = check_launch();
+    if (rc != RQ_OK) return rc;
+    // phase 2: merge inverses of neighbouring diagonal blocks, doubling the block size each level
+    for (int s = NB; s < Cp; s *= 2) {
+        const int pairs = (Cp + 2 * s - 1) / (2 * s);
+        const int tiles = (s / NB) * (s / NB);
+        for (int step = 1; step <= 2; ++step)
+            inv_level_kernel<<<dim3((unsigned)tiles, (unsigned)pairs, (unsigned)G), gemm::kThreads, gemm::kSmemBytes, st>>>(
+                A, Hinv, T, Cp, s, step);
+    }
+    finite_check_kernel<<<dim3(64, (unsigned)G), 256, 0, st>>>(Hinv, Cp, info);
+    return check_launch();
+}

@@ -1,0 +1,451 @@
+// The fasterquant stage: weight/gradient permutation, GPTQ+ first-order terms, the per-block
+// column loop (round/clamp quantize, error feedback, first-order term) and the lazy trailing
+// update, plus the un-permuting epilogue.  All row sub-groups of a linear run in the same launches.
+//
+// Rows are independent in this algorithm (every formula combines one row of W with the shared
+// Hinv of its group), so the column loop gives each weight row to one warp: the 128-column panel
+// of the row lives in registers (4 columns per lane), the 128x128 Hinv block in shared memory, and
+// the per-column scalars travel by warp shuffle.
+#include "rq_common.cuh"
+#include "rq_gemm.cuh"
+
+namespace rq {
+namespace fq {
+
+constexpr int BS = 128;                      // column block (the reference's blocksize)
+constexpr int kRowsPerCta = 16;              // one warp per row
+constexpr int kBlockThreads = kRowsPerCta * 32;
+
+// ------------------------------------------------------------------------------------------
+// Wp[r][j] = dead(g(r), perm[j]) ? 0 : W[r][perm[j]];   Gp[r][j] = Grad[r][perm[j]]
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) prep_kernel(const float* __restrict__ W, const float* __restrict__ Grad,
+                                                   const float* __restrict__ H, const int64_t* __restrict__ perm,
+                                                   int R, int C, int G, float* __restrict__ Wp,
+                                                   float* __restrict__ Gp) {
+    for (int r = blockIdx.y; r < R; r += gridDim.y) {
+        const int g = r / (R / G);
+        const float* Hg = H + (int64_t)g * C * C;
+        for (int j = blockIdx.x * 256 + threadIdx.x; j < C; j += gridDim.x * 256) {
+            const int64_t pj = perm ? perm[j] : j;
+            const bool dead = Hg[pj * C + pj] == 0.f;
+            Wp[(int64_t)r * C + j] = dead ? 0.f : W[(int64_t)r * C + pj];
+            if (Gp) Gp[(int64_t)r * C + j] = Grad[(int64_t)r * C + pj];
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// GPTQ+ first-order terms
+// ------------------------------------------------------------------------------------------
+// T = Gp . U^T  (step 1, U upper: k starts at the column tile)   GHI = T . U  (step 2: k ends with it)
+// grid (tiles_m, tiles_n, G)
+__global__ void __launch_bounds__(gemm::kThreads) terms_gemm_kernel(const float* __restrict__ In,
+                                                                    const float* __restrict__ U,
+                                                                    float* __restrict__ Out, int Rg, int C, int Cp,
+                                                                    int step) {
+    extern __shared__ float smem[];
+    const int g = blockIdx.z;
+    gemm::Args a;
+    a.A = In + (int64_t)g * Rg * C; a.lda = C;
+    a.B = U + (int64_t)g * Cp * Cp; a.ldb = Cp;
+    a.C = Out + (int64_t)g * Rg * C; a.ldc = C;
+    a.Aux = nullptr; a.ldaux = 0;
+    a.M = Rg; a.N = C; a.K = C;
+    a.alpha = 1.f; a.beta = 0.f; a.gamma = 0.f;
+    const int j0 = blockIdx.y * gemm::TN;
+    if (step == 1) {
+        a.k_begin = j0; a.k_end = C;
+        gemm::tile<true>(a, blockIdx.x * gemm::TM, j0, smem);
+    } else {
+        a.k_begin = 0; a.k_end = (j0 + gemm::TN < C) ? j0 + gemm::TN : C;
+        gemm::tile<false>(a, blockIdx.x * gemm::TM, j0, smem);
+    }
+}
+
+// hdiag[g][j] = diag(H^-1)_j = sum_i U[i][j]^2
+__global__ void __launch_bounds__(256) hinv_diag_kernel(const float* __restrict__ U, int C, int Cp,
+                                                        float* __restrict__ hdiag) {
+    const int g = blockIdx.y;
+    const int j = blockIdx.x * 256 + threadIdx.x;
+    if (j >= C) return;
+    const float* Ug = U + (int64_t)g * Cp * Cp;
+    float s = 0.f;
+    for (int i = 0; i <= j; ++i) {
+        const float v = Ug[(int64_t)i * Cp + j];
+        s = fmaf(v, v, s);
+    }
+    hdiag[(int64_t)g * C + j] = s;
+}
+
+// beta[r] from c = sum_j G*GHI - mean_j(GHI^2 / diag(H^-1)); then Z = beta*T, GH = beta*GHI in place.
+// One block per row.
+__global__ void __launch_bounds__(256) beta_kernel(const float* __restrict__ Gp, float* __restrict__ T,
+                                                   float* __restrict__ GHI, const float* __restrict__ hdiag, int R,
+                                                   int C, int G, float alpha_eff, float ref_loss,
+                                                   float* __restrict__ beta) {
+    __shared__ float red[16];
+    __shared__ float bsh;
+    const int r = blockIdx.x;
+    const int g = r / (R / G);
+    const float* gp = Gp + (int64_t)r * C;
+    float* t = T + (int64_t)r * C;
+    float* gh = GHI + (int64_t)r * C;
+    const float* hd = hdiag + (int64_t)g * C;
+    float s1 = 0.f, s2 = 0.f;
+    for (int j = threadIdx.x; j < C; j += 256) {
+        const float v = gh[j];
+        s1 += gp[j] * v;
+        s2 += __fdiv_rn(v * v, hd[j]);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+        s2 += __shfl_xor_sync(0xffffffffu, s2, o);
+    }
+    if ((threadIdx.x & 31) == 0) { red[threadIdx.x >> 5] = s1; red[8 + (threadIdx.x >> 5)] = s2; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float a = 0.f, b = 0.f;
+        for (int w = 0; w < 8; ++w) { a += red[w]; b += red[8 + w]; }
+        float bv = 0.f;
+        if (ref_loss > 0.f) {
+            float c = a - b / (float)C;
+            const float target = 2.f * alpha_eff * ref_loss;
+            if (c < target) c = target;                            // clamp(min=target); a NaN stays NaN
+            float ratio = (c > 0.f) ? __fdiv_rn(target, c) : 0.f;  // NaN compares false -> 0
+            ratio = fminf(fmaxf(ratio, 0.f), 1.f);
+            bv = 1.f - sqrtf(fmaxf(1.f - ratio, 0.f));
+            if (isnan(bv)) bv = 0.f;
+            else if (isinf(bv)) bv = bv > 0.f ? 1.f : 0.f;
+        }
+        bsh = bv;
+        beta[r] = bv;
+    }
+    __syncthreads();
+    const float bv = bsh;
+    for (int j = threadIdx.x; j < C; j += 256) {
+        t[j] *= bv;
+        gh[j] *= bv;
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// the column loop of one block [i1, i1+count)
+// ------------------------------------------------------------------------------------------
+struct BlockArgs {
+    float* Wp;               // [R, C] working weights (permuted order), updated in place for the block
+    float* GH;               // [R, C] first-order term GHinv (PLUS)
+    const float* Z;          // [R, C] (PLUS)
+    const float* Hinv;       // [G, Cp, Cp] upper factor
+    float* Q;                // [R, C] dequantized result (permuted order)
+    int8_t* codes;           // [R, C] integer codes (permuted order)
+    float* Eeff;             // [R, BS]: Err (- D*Z1 when PLUS), A operand of the lazy update
+    const float* scale_row;  // mode 0: [R]
+    const float* scale_tab;  // mode 1: [ngroups, R] static groups
+    const int* colgrp;       // mode 1: [C] group of (permuted) column j
+    float* scale_blk;        // mode 2: [C/gs_dyn blocks..., R] scales found on the fly (output)
+    int R, C, Cp, G, i1, count;
+    int mode;                // 0 per-row scale, 1 static groups, 2 dynamic groups
+    int dyn_gs;              // mode 2: group width (divides BS)
+    int sym;                 // mode 2: range rule
+    float qlo, qhi;          // clamp bounds -(maxq+1), maxq
+    float maxq;
+};
+
+template <bool PLUS>
+__global__ void __launch_bounds__(kBlockThreads) block_kernel(const BlockArgs p) {
+    extern __shared__ float Hs[];                          // [BS][BS] Hinv1, row-major
+    const int Rg = p.R / p.G;
+    const int ctas_per_group = (Rg + kRowsPerCta - 1) / kRowsPerCta;
+    const int g = blockIdx.x / ctas_per_group;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row_in_group = (blockIdx.x % ctas_per_group) * kRowsPerCta + warp;
+    const float* Hb = p.Hinv + (int64_t)g * p.Cp * p.Cp + (int64_t)p.i1 * p.Cp + p.i1;
+    for (int e = threadIdx.x; e < BS * BS; e += kBlockThreads) {
+        const int i = e >> 7, j = e & 127;
+        Hs[e] = (i < p.count && j < p.count) ? Hb[(int64_t)i * p.Cp + j] : 0.f;
+    }
+    __syncthreads();
+    if (row_in_group >= Rg) return;
+    const int r = g * Rg + row_in_group;
+    const int64_t base = (int64_t)r * p.C + p.i1;
+
+    float w[4], gh[4], z[4], sc[4], qv[4], cv[4], ev[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int col = lane + 32 * k;
+        const bool in = col < p.count;
+        w[k] = in ? p.Wp[base + col] : 0.f;
+        gh[k] = (PLUS && in) ? p.GH[base + col] : 0.f;
+        z[k] = (PLUS && in) ? p.Z[base + col] : 0.f;
+        qv[k] = 0.f; cv[k] = 0.f; ev[k] = 0.f;
+        sc[k] = 1.f;
+    }
+    if (p.mode == 0) {
+        const float s = p.scale_row[r];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) sc[k] = s;
+    } else if (p.mode == 1) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int col = lane + 32 * k;
+            if (col < p.count) sc[k] = p.scale_tab[(int64_t)p.colgrp[p.i1 + col] * p.R + r];
+        }
+    } else {
+        // dynamic groups: ranges of the block-start values, one per dyn_gs-wide group inside the block
+        const int ngrp = (p.count + p.dyn_gs - 1) / p.dyn_gs;
+        for (int gi = 0; gi < ngrp; ++gi) {
+            float lo = 0.f, hi = 0.f;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int col = lane + 32 * k;
+                if (col < p.count && col / p.dyn_gs == gi) { lo = fminf(lo, w[k]); hi = fmaxf(hi, w[k]); }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                lo = fminf(lo, __shfl_xor_sync(0xffffffffu, lo, o));
+                hi = fmaxf(hi, __shfl_xor_sync(0xffffffffu, hi, o));
+            }
+            float s;
+            if (p.sym) {
+                s = __fdiv_rn(fmaxf(fmaxf(fabsf(lo), hi), 1e-5f), p.maxq);
+            } else {
+                if (lo == 0.f && hi == 0.f) { lo = -1.f; hi = 1.f; }
+                s = __fdiv_rn(fmaxf(hi - lo, 1e-5f), p.maxq);
+            }
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int col = lane + 32 * k;
+                if (col / p.dyn_gs == gi) sc[k] = s;
+            }
+            if (lane == 0) p.scale_blk[(int64_t)((p.i1 + gi * p.dyn_gs) / p.dyn_gs) * p.R + r] = s;
+        }
+    }
+
+#pragma unroll
+    for (int slot = 0; slot < 4; ++slot) {
+        const int ibase = slot * 32;
+        if (ibase >= p.count) break;
+        const int iend = (p.count - ibase < 32) ? p.count - ibase : 32;
+        for (int o = 0; o < iend; ++o) {
+            const int i = ibase + o;
+            const float wi = __shfl_sync(0xffffffffu, w[slot], o);
+            const float si = __shfl_sync(0xffffffffu, sc[slot], o);
+            const float qi = quant_code(wi, si, p.qlo, p.qhi);
+            const float q = __fmul_rn(si, qi);
+            const float d = Hs[i * BS + i];
+            float err;
+            float zi = 0.f;
+            if (PLUS) {
+                const float ghi = __shfl_sync(0xffffffffu, gh[slot], o);
+                zi = __shfl_sync(0xffffffffu, z[slot], o);
+                err = __fdiv_rn(__fsub_rn(__fsub_rn(wi, q), ghi), d);
+            } else {
+                err = __fdiv_rn(__fsub_rn(wi, q), d);
+            }
+            if (lane == o) { qv[slot] = q; cv[slot] = qi; ev[slot] = err; }
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int col = lane + 32 * k;
+                if (col >= i && col < p.count) {
+                    const float h = Hs[i * BS + col];
+                    float upd = __fmul_rn(err, h);
+                    if (PLUS) {
+                        upd = __fadd_rn(upd, gh[k]);
+                        gh[k] = __fsub_rn(gh[k], __fmul_rn(zi, h));
+                    }
+                    w[k] = __fsub_rn(w[k], upd);
+                }
+            }
+        }
+    }
+
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int col = lane + 32 * k;
+        if (col < p.count) {
+            p.Q[base + col] = qv[k];
+            p.codes[base + col] = (int8_t)cv[k];
+            float e = ev[k];
+            if (PLUS) e = e - (float)(p.count - 1 - col) * z[k];
+            p.Eeff[(int64_t)r * BS + col] = e;
+        } else {
+            p.Eeff[(int64_t)r * BS + col] = 0.f;
+        }
+    }
+}
+
+// lazy update for the columns right of the block:  grid (tiles_m, tiles_n, G)
+//   step 1:  W[:, i2:]  -= Eeff . Hinv[i1:i2, i2:]  +  count * GH[:, i2:]     (the latter when PLUS)
+//   step 2:  GH[:, i2:] -= Z[:, i1:i2] . Hinv[i1:i2, i2:]                      (PLUS only)
+__global__ void __launch_bounds__(gemm::kThreads) lazy_kernel(float* __restrict__ Wp, float* __restrict__ GH,
+                                                              const float* __restrict__ Z,
+                                                              const float* __restrict__ Eeff,
+                                                              const float* __restrict__ Hinv, int R, int C, int Cp,
+                                                              int G, int i1, int count, int step, int plus) {
+    extern __shared__ float smem[];
+    const int g = blockIdx.z;
+    const int Rg = R / G;
+    const int i2 = i1 + count;
+    const int64_t rofs = (int64_t)g * Rg;
+    gemm::Args a;
+    a.B = Hinv + (int64_t)g * Cp * Cp + (int64_t)i1 * Cp + i2; a.ldb = Cp;
+    a.M = Rg; a.N = C - i2; a.K = count;
+    a.alpha = -1.f; a.beta = 1.f;
+    a.k_begin = 0; a.k_end = count;
+    a.Aux = nullptr; a.ldaux = 0; a.gamma = 0.f;
+    if (step == 1) {
+        a.A = Eeff + rofs * BS; a.lda = BS;
+        a.C = Wp + rofs * C + i2; a.ldc = C;
+        if (plus) { a.Aux = GH + rofs * C + i2; a.ldaux = C; a.gamma = -(float)count; }
+    } else {
+        a.A = Z + rofs * C + i1; a.lda = C;
+        a.C = GH + rofs * C + i2; a.ldc = C;
+    }
+    gemm::tile<false>(a, blockIdx.x * gemm::TM, blockIdx.y * gemm::TN, smem);
+}
+
+// ------------------------------------------------------------------------------------------
+// epilogue: un-permute and cast.  out[r][perm[j]] = Q[r][j]  (also codes / scale when exported)
+// ------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256) unpermute_kernel(const float* __restrict__ Q, const int8_t* __restrict__ codes,
+                                                        const int64_t* __restrict__ perm, int R, int C,
+                                                        T* __restrict__ out, float* __restrict__ out_codes,
+                                                        float* __restrict__ out_scale,
+                                                        const float* __restrict__ scale_row,
+                                                        const float* __restrict__ scale_tab,
+                                                        const int* __restrict__ colgrp, int permute_export) {
+    for (int r = blockIdx.y; r < R; r += gridDim.y) {
+        for (int j = blockIdx.x * 256 + threadIdx.x; j < C; j += gridDim.x * 256) {
+            const int64_t dst = perm ? perm[j] : j;
+            store_from_float<T>(out, (int64_t)r * C + dst, Q[(int64_t)r * C + j]);
+            if (out_codes) {
+                const int64_t edst = permute_export ? dst : j;
+                out_codes[(int64_t)r * C + edst] = (float)codes[(int64_t)r * C + j];
+                out_scale[(int64_t)r * C + edst] = scale_tab ? scale_tab[(int64_t)colgrp[j] * R + r] : scale_row[r];
+            }
+        }
+    }
+}
+
+}  // namespace fq
+}  // namespace rq
+
+using namespace rq;
+
+extern "C" int rq_fq_prepare(const float* W, const float* Grad, const float* H, const int64_t* perm, int R, int C,
+                             int G, float* Wp, float* Gp, void* stream) {
+    if (!W || !H || !Wp || R <= 0 || C <= 0 || G <= 0 || R % G != 0 || (Gp && !Grad)) return RQ_ERR_INVALID;
+    dim3 grid((unsigned)((C + 1023) / 1024), (unsigned)(R < 65535 ? R : 65535));
+    fq::prep_kernel<<<grid, 256, 0, as_stream(stream)>>>(W, Grad, H, perm, R, C, G, Wp, Gp);
+    return check_launch();
+}
+
+extern "C" int rq_gptqplus_terms(const float* Gp, const float* Hinv, int R, int C, int G, float alpha_eff,
+                                 float ref_loss, float* Z, float* GHinv, float* beta, float* hdiag, void* stream) {
+    if (!Gp || !Hinv || !Z || !GHinv || !beta || !hdiag || R <= 0 || C <= 0 || G <= 0 || R % G != 0)
+        return RQ_ERR_INVALID;
+    cudaStream_t st = as_stream(stream);
+    const int Cp = (C + 127) / 128 * 128;
+    const int Rg = R / G;
+    dim3 grid((unsigned)((Rg + gemm::TM - 1) / gemm::TM), (unsigned)((C + gemm::TN - 1) / gemm::TN), (unsigned)G);
+    fq::terms_gemm_kernel<<<grid, gemm::kThreads, gemm::kSmemBytes, st>>>(Gp, Hinv, Z, Rg, C, Cp, 1);
+    fq::terms_gemm_kernel<<<grid, gemm::kThreads, gemm::kSmemBytes, st>>>(Z, Hinv, GHinv, Rg, C, Cp, 2);
+    fq::hinv_diag_kernel<<<dim3((unsigned)((C + 255) / 256), (unsigned)G), 256, 0, st>>>(Hinv, C, Cp, hdiag);
+    fq::beta_kernel<<<R, 256, 0, st>>>(Gp, Z, GHinv, hdiag, R, C, G, alpha_eff, ref_loss, beta);
+    return check_launch();
+}
+
+extern "C" int rq_fq_block(float* Wp, float* GH, const float* Z, const float* Hinv, float* Q, int8_t* codes,
+                           float* Eeff, const float* scale_row, const float* scale_tab, const int* colgrp,
+                           float* scale_blk, int R, int C, int G, int i1, int count, int mode, int dyn_gs, int sym,
+                           int maxq, int plus, void* stream) {
+    using namespace rq::fq;
+    if (!Wp || !Hinv || !Q || !codes || !Eeff || R <= 0 || C <= 0 || G <= 0 || R % G != 0) return RQ_ERR_INVALID;
+    if (i1 < 0 || count <= 0 || count > BS || i1 + count > C) return RQ_ERR_INVALID;
+    if (plus && (!GH || !Z)) return RQ_ERR_INVALID;
+    if (mode == 0 && !scale_row) return RQ_ERR_INVALID;
+    if (mode == 1 && (!scale_tab || !colgrp)) return RQ_ERR_INVALID;
+    if (mode == 2 && (!scale_blk || dyn_gs <= 0 || BS % dyn_gs != 0 || i1 % dyn_gs != 0)) return RQ_ERR_INVALID;
+    if (mode < 0 || mode > 2 || maxq <= 0 || maxq > 127) return RQ_ERR_INVALID;
+    cudaStream_t st = as_stream(stream);
+    BlockArgs p;
+    p.Wp = Wp; p.GH = GH; p.Z = Z; p.Hinv = Hinv; p.Q = Q; p.codes = codes; p.Eeff = Eeff;
+    p.scale_row = scale_row; p.scale_tab = scale_tab; p.colgrp = colgrp; p.scale_blk = scale_blk;
+    p.R = R; p.C = C; p.Cp = (C + 127) / 128 * 128; p.G = G; p.i1 = i1; p.count = count;
+    p.mode = mode; p.dyn_gs = dyn_gs; p.sym = sym;
+    p.qlo = -(float)(maxq + 1); p.qhi = (float)maxq; p.maxq = (float)maxq;
+    const int Rg = R / G;
+    const int ctas = G * ((Rg + kRowsPerCta - 1) / kRowsPerCta);
+    const size_t smem = (size_t)BS * BS * sizeof(float);
+    prof::Scope timed(RQ_PROF_BLOCK, st);
+    if (plus) {
+        if (cudaFuncSetAttribute(block_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+            return RQ_ERR_CUDA;
+        block_kernel<true><<<ctas, kBlockThreads, smem, st>>>(p);
+    } else {
+        if (cudaFuncSetAttribute(block_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+            return RQ_ERR_CUDA;
+        block_kernel<false><<<ctas, kBlockThreads, smem, st>>>(p);
+    }
+    return check_launch();
+}
+
+extern "C" int rq_fq_lazy_update(float* Wp, float* GH, const float* Z, const float* Eeff, const float* Hinv, int R,
+                                 int C, int G, int i1, int count, int plus, void* stream) {
+    if (!Wp || !Eeff || !Hinv || R <= 0 || C <= 0 || G <= 0 || R % G != 0 || count <= 0 || count > fq::BS)
+        return RQ_ERR_INVALID;
+    if (plus && (!GH || !Z)) return RQ_ERR_INVALID;
+    const int i2 = i1 + count;
+    if (i2 >= C) return RQ_OK;                       // nothing to the right of the last block
+    cudaStream_t st = as_stream(stream);
+    const int Cp = (C + 127) / 128 * 128;
+    const int Rg = R / G;
+    dim3 grid((unsigned)((Rg + gemm::TM - 1) / gemm::TM), (unsigned)((C - i2 + gemm::TN - 1) / gemm::TN), (unsigned)G);
+    prof::Scope timed(RQ_PROF_LAZY, st);
+    fq::lazy_kernel<<<grid, gemm::kThreads, gemm::kSmemBytes, st>>>(Wp, GH, Z, Eeff, Hinv, R, C, Cp, G, i1, count, 1, plus);
+    if (plus)
+        fq::lazy_kernel<<<grid, gemm::kThreads, gemm::kSmemBytes, st>>>(Wp, GH, Z, Eeff, Hinv, R, C, Cp, G, i1, count, 2, plus);
+    return check_launch();
+}
+
+extern "C" int rq_fq_finish(const float* Q, const int8_t* codes, const int64_t* perm, int R, int C, void* out,
+                            int out_dtype, float* out_codes, float* out_scale, const float* scale_row,
+                            const float* scale_tab, const int* colgrp, int permute_export, void* stream) {
+    using namespace rq::fq;
+    if (!Q || !out || R <= 0 || C <= 0) return RQ_ERR_INVALID;
+    if (out_codes && (!codes || !out_scale || (!scale_row && !(scale_tab && colgrp)))) return RQ_ERR_INVALID;
+    dim3 grid((unsigned)((C + 1023) / 1024), (unsigned)(R < 65535 ? R : 65535));
+    cudaStream_t st = as_stream(stream);
+    if (out_dtype == RQ_F32)
+        unpermute_kernel<float><<<grid, 256, 0, st>>>(Q, codes, perm, R, C, reinterpret_cast<float*>(out), out_codes,
+                                                      out_scale, scale_row, scale_tab, colgrp, permute_export);
+    else if (out_dtype == RQ_BF16)
+        unpermute_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(Q, codes, perm, R, C, reinterpret_cast<__nv_bfloat16*>(out),
+                                                              out_codes, out_scale, scale_row, scale_tab, colgrp,
+                                                              permute_export);
+    else if (out_dtype == RQ_F16)
+        unpermute_kernel<__half><<<grid, 256, 0, st>>>(Q, codes, perm, R, C, reinterpret_cast<__half*>(out), out_codes,
+                                                       out_scale, scale_row, scale_tab, colgrp, permute_export);
+    else
+        return RQ_ERR_INVALID;
+    return check_launch();
+}
+
+// Every block of a linear in one call (the callback-free modes need no host work between blocks).
+extern "C" int rq_fq_run(float* Wp, float* GH, const float* Z, const float* Hinv, float* Q, int8_t* codes,
+                         float* Eeff, const float* scale_row, const float* scale_tab, const int* colgrp,
+                         float* scale_blk, int R, int C, int G, int mode, int dyn_gs, int sym, int maxq, int plus,
+                         void* stream) {
+    for (int i1 = 0; i1 < C; i1 += fq::BS) {
+        const int count = (C - i1 < fq::BS) ? C - i1 : fq::BS;
+        int rc = rq_fq_block(Wp, GH, Z, Hinv, Q, codes, Eeff, scale_row, scale_tab, colgrp, scale_blk, R, C, G, i1,
+                             count, mode, dyn_gs, sym, maxq, plus, stream);
+        if (rc != RQ_OK) return rc;
+        rc = rq_fq_lazy_update(Wp, GH, Z, Eeff, Hinv, R, C, G, i1, count, plus, stream);
+        if (rc != RQ_OK) return rc;
+    }
+    return RQ_OK;
+}

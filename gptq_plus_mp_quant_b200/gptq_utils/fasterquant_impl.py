@@ -1,9 +1,254 @@
-"""Host side of the fasterquant block loop (placeholder until the kernels land)."""
+"""Host side of ``fasterquant`` for the ``GPTQ`` and ``GPTQPlus`` objects: sets up the work
+matrices, drives the damping-retry loop around the Cholesky kernel and launches the block loop.
+All numerical work happens in the kernels of ``librealq_b200.so``; torch supplies the memory,
+the ``argsort`` of the act_order key and the stream."""
+from __future__ import annotations
+
+import ctypes
+import logging
+
+import torch
+
+from .. import _lib, ops
+from ..utils import quant_utils
+
+BS = 128            # column block of the kernels
+_DAMP_STEP = 0.0015
 
 
-def plain_fasterquant(*args, **kwargs):
-    raise NotImplementedError("fasterquant kernels are not built yet")
+# ----------------------------------------------------------------------------------------------
+# damped inverse factor with the reference's retry semantics
+# ----------------------------------------------------------------------------------------------
+def _chol_once(H3: torch.Tensor, perm, factors, Hinv: torch.Tensor, info: torch.Tensor) -> None:
+    G, Cc = H3.shape[0], H3.shape[-1]
+    need = _lib.lib.rq_chol_workspace_bytes(Cc, G)
+    ws = ops._workspace(H3.device, need + 256)
+    base = ws.data_ptr()
+    aligned = (base + 255) // 256 * 256
+    arr = (ctypes.c_float * G)(*[float(f) for f in factors])
+    with torch.cuda.device(H3.device):
+        rc = _lib.lib.rq_chol_hinv(_lib.ptr(H3), _lib.ptr(perm), arr, _lib.ptr(Hinv), Cc, G, _lib.ptr(info),
+                                   aligned, ws.numel() - (aligned - base), _lib.stream_of(H3))
+    _lib.check("rq_chol_hinv", rc)
 
 
-def plus_fasterquant(*args, **kwargs):
-    raise NotImplementedError("fasterquant kernels are not built yet")
+def hinv_with_fallback(H3: torch.Tensor, perm, percdamp: float, identity_fallback: bool, log_context: str = ""):
+    """``Hinv`` [G, Cp, Cp] (upper factor of the damped inverse of every group), the damping
+    fraction each group ended with, and which groups fell back to the identity.
+
+    Retry rule of the reference (gptq_plus_utils.py:519-557, gptq_utils.py:88-106): the damping
+    ``p * mean(diag)`` is added to the already-damped matrix, so after attempts p_1..p_k the
+    diagonal has grown by ``mean(diag) * (prod(1 + p_i) - 1)``; p grows by 0.0015 per failure;
+    at p >= 1 GPTQ+ substitutes the identity while plain GPTQ raises ValueError."""
+    if float(percdamp) <= 0:
+        raise ValueError(f"Quantization{log_context}: `damp_percent` must be positive. current is {percdamp}")
+    G, Cc = H3.shape[0], H3.shape[-1]
+    Cp = (Cc + BS - 1) // BS * BS
+    Hinv = torch.empty(G, Cp, Cp, dtype=torch.float32, device=H3.device)
+    info = torch.zeros(G, dtype=torch.int32, device=H3.device)
+    p = [float(percdamp)] * G
+    growth = [1.0] * G                                  # prod(1 + p_i) over the attempts so far
+    identity = [False] * G
+    pending = list(range(G))
+    first = True
+    while pending:
+        todo = [g for g in pending if 0 < p[g] < 1]
+        for g in pending:
+            if g not in todo:
+                identity[g] = True
+        if not todo:
+            break
+        for g in todo:
+            growth[g] *= 1.0 + p[g]
+        if first and len(todo) == G:
+            _chol_once(H3, perm, [growth[g] - 1.0 for g in range(G)], Hinv, info)
+            flags = info.tolist()
+        else:
+            flags = [0] * G
+            for g in todo:
+                sub = torch.zeros(1, dtype=torch.int32, device=H3.device)
+                _chol_once(H3[g:g + 1], perm, [growth[g] - 1.0], Hinv[g:g + 1], sub)
+                flags[g] = int(sub.item())
+        first = False
+        pending = []
+        for g in todo:
+            if flags[g] != 0:
+                logging.warning("Quantization%s: Current `damp_percent = %.5f` is too low, auto-incrementing by `%.5f`",
+                                f"{log_context} subgroup={g}", p[g], _DAMP_STEP)
+                p[g] += _DAMP_STEP
+                pending.append(g)
+    for g in range(G):
+        if identity[g]:
+            if not identity_fallback:
+                raise ValueError(f"Quantization: `damp_percent` must between 0 and 1. current is {p[g]}")
+            logging.warning("Quantization%s subgroup=%d: `damp_percent` reached %.5f; falling back to identity "
+                            "Hessian inverse for this subgroup.", log_context, g, p[g])
+            Hinv[g].zero_()
+            Hinv[g].diagonal().fill_(1.0)
+    return Hinv, p, identity
+
+
+# ----------------------------------------------------------------------------------------------
+# scale sources
+# ----------------------------------------------------------------------------------------------
+def _scale_setup(quantizer, W32, groupsize, static_groups, blocksize, perm, dead_zeroed_W=None):
+    """(mode, scale_row, scale_tab, colgrp, scale_blk, dyn_gs) for the block kernel."""
+    dev = W32.device
+    R, Cc = W32.shape
+    if groupsize == -1:
+        scale_row = quantizer.scale.to(dev, torch.float32).reshape(-1).contiguous()
+        if scale_row.numel() != R:
+            raise ValueError(f"quantizer.scale has {scale_row.numel()} entries for {R} rows")
+        return 0, scale_row, None, None, None, 0
+    if not getattr(quantizer, "perchannel", True):
+        raise NotImplementedError("grouped quantization needs a per-channel quantizer")
+    maxq = int(quantizer.maxq)
+    if static_groups:
+        src = W32 if dead_zeroed_W is None else dead_zeroed_W
+        tab, _ = quant_utils.find_params_groups(src, groupsize, maxq, quantizer.sym, quantizer.mse, quantizer.norm,
+                                                quantizer.grid, quantizer.maxshrink)
+        cols = perm if perm is not None else torch.arange(Cc, device=dev)
+        colgrp = (cols // groupsize).to(torch.int32).contiguous()
+        return 1, None, tab, colgrp, None, 0
+    # dynamic groups: ranged from the working block right before it is quantized
+    if groupsize != blocksize or BS % groupsize != 0:
+        raise NotImplementedError(
+            f"dynamic weight groups are built for groupsize == blocksize == {BS}; got groupsize={groupsize}, "
+            f"blocksize={blocksize} (use static groups for other widths)")
+    if quantizer.mse:
+        raise NotImplementedError("dynamic weight groups with the shrink-grid search are not built")
+    ng = (Cc + groupsize - 1) // groupsize
+    scale_blk = torch.zeros(ng, R, dtype=torch.float32, device=dev)
+    colgrp = (torch.arange(Cc, device=dev) // groupsize).to(torch.int32).contiguous()
+    return 2, None, None, colgrp, scale_blk, groupsize
+
+
+# ----------------------------------------------------------------------------------------------
+# the shared driver
+# ----------------------------------------------------------------------------------------------
+def _quantize_linear(layer, W32, H3, perm, grads, quantizer, G, alpha_eff, ref_loss, plus, Hinv, mode_pack,
+                     export_to_et, permute_export):
+    dev = W32.device
+    R, Cc = W32.shape
+    mode, scale_row, scale_tab, colgrp, scale_blk, dyn_gs = mode_pack
+    maxq = int(quantizer.maxq)
+    st = _lib.stream_of(W32)
+    Wp = torch.empty(R, Cc, dtype=torch.float32, device=dev)
+    Gp = torch.empty(R, Cc, dtype=torch.float32, device=dev) if plus else None
+    with torch.cuda.device(dev):
+        _lib.check("rq_fq_prepare", _lib.lib.rq_fq_prepare(_lib.ptr(W32), _lib.ptr(grads), _lib.ptr(H3), _lib.ptr(perm),
+                                                           R, Cc, G, _lib.ptr(Wp), _lib.ptr(Gp), st))
+        Z = GH = beta = None
+        if plus:
+            Z = torch.empty(R, Cc, dtype=torch.float32, device=dev)
+            GH = torch.empty(R, Cc, dtype=torch.float32, device=dev)
+            beta = torch.empty(R, dtype=torch.float32, device=dev)
+            hdiag = torch.empty(G, Cc, dtype=torch.float32, device=dev)
+            _lib.check("rq_gptqplus_terms",
+                       _lib.lib.rq_gptqplus_terms(_lib.ptr(Gp), _lib.ptr(Hinv), R, Cc, G, float(alpha_eff),
+                                                  float(ref_loss), _lib.ptr(Z), _lib.ptr(GH), _lib.ptr(beta),
+                                                  _lib.ptr(hdiag), st))
+        Q = torch.empty(R, Cc, dtype=torch.float32, device=dev)
+        codes = torch.empty(R, Cc, dtype=torch.int8, device=dev)
+        Eeff = torch.empty(R, BS, dtype=torch.float32, device=dev)
+        _lib.check("rq_fq_run",
+                   _lib.lib.rq_fq_run(_lib.ptr(Wp), _lib.ptr(GH), _lib.ptr(Z), _lib.ptr(Hinv), _lib.ptr(Q),
+                                      _lib.ptr(codes), _lib.ptr(Eeff), _lib.ptr(scale_row), _lib.ptr(scale_tab),
+                                      _lib.ptr(colgrp), _lib.ptr(scale_blk), R, Cc, G, mode, dyn_gs,
+                                      1 if quantizer.sym else 0, maxq, 1 if plus else 0, st))
+        out = torch.empty(layer.weight.shape, dtype=layer.weight.dtype, device=dev)
+        out_codes = out_scale = None
+        if export_to_et:
+            out_codes = torch.empty(R, Cc, dtype=torch.float32, device=dev)
+            out_scale = torch.empty(R, Cc, dtype=torch.float32, device=dev)
+        tab = scale_tab if mode == 1 else scale_blk
+        _lib.check("rq_fq_finish",
+                   _lib.lib.rq_fq_finish(_lib.ptr(Q), _lib.ptr(codes), _lib.ptr(perm), R, Cc, _lib.ptr(out),
+                                         _lib.dtype_code(out), _lib.ptr(out_codes), _lib.ptr(out_scale),
+                                         _lib.ptr(scale_row), _lib.ptr(tab), _lib.ptr(colgrp),
+                                         1 if permute_export else 0, st))
+    if export_to_et:
+        layer.register_buffer("int_weight", out_codes.reshape(layer.weight.shape))
+        layer.register_buffer("scale", out_scale)
+    layer.weight.data = out
+    return {"beta": beta, "Z": Z, "GHinv": GH, "Wp": Wp, "Q": Q, "codes": codes}
+
+
+def _check_common(quantizer, blocksize):
+    if blocksize % BS != 0:
+        raise NotImplementedError(f"blocksize must be a multiple of {BS} (the kernels' column block); got {blocksize}")
+    maxq = int(quantizer.maxq)
+    if not (0 < maxq <= 127):
+        raise NotImplementedError(f"integer codes are stored as int8: maxq must be in 1..127, got {maxq}")
+
+
+# ----------------------------------------------------------------------------------------------
+# plain GPTQ (gptq_utils/gptq_utils.py:45-174)
+# ----------------------------------------------------------------------------------------------
+@torch.no_grad()
+def plain_fasterquant(obj, H, blocksize, percdamp, groupsize, actorder, static_groups, export_to_et):
+    layer, dev = obj.layer, obj.dev
+    W32 = layer.weight.data.float().contiguous()
+    R, Cc = W32.shape
+    if not obj.quantizer.ready():
+        obj.quantizer.find_params(W32)
+    _check_common(obj.quantizer, blocksize)
+    if bool((H == 0).all()):                                    # no calibration data: round to nearest
+        H = torch.eye(Cc, device=dev)
+    H3 = H.reshape(1, Cc, Cc).contiguous()
+    diag = torch.diagonal(H3[0])
+    dead = diag == 0
+    Wz = None
+    if groupsize != -1 and static_groups:                      # plain GPTQ ranges the groups after dead-zeroing
+        Wz = W32.clone()
+        Wz[:, dead] = 0
+    perm = None
+    if actorder:
+        key = torch.where(dead, torch.ones_like(diag), diag)
+        perm = torch.argsort(key, descending=True)
+    if groupsize != -1 and not static_groups and (groupsize != blocksize):
+        raise NotImplementedError("plain GPTQ with dynamic groups is built for groupsize == blocksize")
+    mode_pack = _scale_setup(obj.quantizer, W32, groupsize, static_groups, blocksize, perm, Wz)
+    Hinv, _, _ = hinv_with_fallback(H3, perm, percdamp, identity_fallback=False)
+    _quantize_linear(layer, W32, H3, perm, None, obj.quantizer, 1, 0.0, 0.0, False, Hinv, mode_pack,
+                     export_to_et, permute_export=False)
+
+
+# ----------------------------------------------------------------------------------------------
+# GPTQ+ (gptq_utils/gptq_plus_utils.py:910-1896)
+# ----------------------------------------------------------------------------------------------
+@torch.no_grad()
+def plus_fasterquant(obj, blocksize, percdamp, groupsize, actorder, static_groups, enable_gradient_update,
+                     g_update_mode, export_to_et, profile_recorder, gradient_refresh_fn, grad_reg_strategy,
+                     second_order_scale, block_atomic_quant, block_observer, diagnostic_recorder):
+    if g_update_mode != "frozen":
+        raise NotImplementedError(
+            f"g_update_mode={g_update_mode!r}: only the callback-free 'frozen' mode runs in the kernels so far")
+    if block_atomic_quant:
+        raise NotImplementedError("block_atomic_quant is not built")
+    if grad_reg_strategy != "none":
+        raise NotImplementedError("gradient regularisers belong to the block_gd refresh path, which stays in PyTorch")
+    if diagnostic_recorder is not None:
+        raise NotImplementedError("the tensor-dump recorder needs the per-column intermediates of the PyTorch path")
+    layer, dev = obj.layer, obj.dev
+    W32 = layer.weight.data.float().contiguous()
+    R, Cc = W32.shape
+    G = obj.num_groups
+    if not obj.quantizer.ready():
+        obj.quantizer.find_params(W32)
+    _check_common(obj.quantizer, blocksize)
+    dynamic_groups = groupsize != -1 and not static_groups
+    if dynamic_groups and groupsize != blocksize:
+        raise ValueError("`groupsize` must equal `blocksize` when using dynamic groups in GPTQ+. "
+                         f"Got groupsize={groupsize}, blocksize={blocksize}.")
+    ops.check_status(dev)
+    H3 = obj.H
+    perm = torch.argsort(obj.act_square, descending=True) if actorder else None
+    mode_pack = _scale_setup(obj.quantizer, W32, groupsize, static_groups, blocksize, perm, None)
+    Hinv, damp, identity = hinv_with_fallback(H3, perm, percdamp, identity_fallback=True)
+    plus = bool(enable_gradient_update and obj.alpha > 0)
+    grads = obj.gradients.to(dev).float().contiguous() if plus else None
+    alpha_eff = obj.alpha / (obj.rows * obj.columns) if plus else 0.0
+    state = _quantize_linear(layer, W32, H3, perm, grads, obj.quantizer, G, alpha_eff, obj.reference_loss, plus, Hinv,
+                             mode_pack, export_to_et, permute_export=True)
+    obj._last_fasterquant = {"Hinv": Hinv, "perm": perm, "damp_percent": damp, "identity_fallback": identity, **state}

@@ -115,7 +115,7 @@ _HADK_DEV = {}
 
 
 def _hadK_on(device, hadK: torch.Tensor) -> torch.Tensor:
-    key = (str(device), hadK.data_ptr(), tuple(hadK.shape))
+    key = (str(device), hadK.data_ptr(), tuple(hadK.shape), tuple(hadK.stride()))
     t = _HADK_DEV.get(key)
     if t is None:
         t = hadK.detach().to(device=device, dtype=torch.float32).contiguous()
@@ -131,6 +131,8 @@ def fwht(x: torch.Tensor, hadK=None, K: int = 1, scale: float = 1.0, out: torch.
     if out is None:
         out = torch.empty_like(xc)
     rows = xc.numel() // n if n else 0
+    if rows == 0:
+        return out.view(x.shape)
     hk = _hadK_on(x.device, hadK) if K > 1 else None
     with torch.cuda.device(x.device):
         rc = _lib.lib.rq_fwht(_lib.ptr(xc), _lib.ptr(out), _lib.dtype_code(xc), rows, n, K, _lib.ptr(hk),

@@ -111,6 +111,76 @@ int rq_find_params(const float* W, int64_t R, int64_t C, int64_t ldw, int groups
 int rq_quantize(const void* x, void* deq, float* codes, int dtype, int64_t R, int64_t C, const float* scale,
                 const float* zero, int pertensor, int maxq, int honour_zero, void* stream);
 
+/* ------------------------------------------------------------------------------------------
+ * Damped inverse-Hessian factor.
+ * Replaces _compute_hessian_inverse_with_fallback's numerical body (gptq_utils/gptq_plus_utils.py:525-531)
+ * and its twin in GPTQ.fasterquant (gptq_utils/gptq_utils.py:91-98), together with the act_order
+ * gather H[perm][:, perm] (gptq_utils/gptq_plus_utils.py:1048) and the dead-channel fix H[dead,dead] = 1
+ * (:1036-1037):  for every group g
+ *     P = H[g][perm][:, perm];  P[d,d] = 1 where P[d,d] == 0;  P += damp_factor[g] * mean(diag P) * I;
+ *     Hinv[g] = upper-triangular U with U^T U = P^-1          (the reference's potrf -> potri -> potrf(upper)).
+ * H: [G, C, C] symmetric fp32 (only read); perm: device int64 [C] or NULL; damp_factor: HOST float [G]
+ * (percdamp for the first attempt; prod(1 + p_i) - 1 over the attempts so far when damping is added
+ * cumulatively on retries, as the reference does); Hinv: [G, Cp, Cp] fp32 with Cp = C rounded up to 128,
+ * row stride Cp, zero below the diagonal, 16-byte aligned.
+ * info: device int [G]: 0 = ok, k > 0 = non-positive pivot met in block column k-1 (not positive
+ * definite: the host retries with more damping), -1 = non-finite entries in the result.
+ * workspace: rq_chol_workspace_bytes(C, G) bytes, 256-byte aligned. */
+size_t rq_chol_workspace_bytes(int C, int G);
+int rq_chol_hinv(const float* H, const int64_t* perm, const float* damp_factor, float* Hinv, int C, int G,
+                 int* info, void* workspace, size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * fasterquant.  R = out_features, C = in_features, G row sub-groups of R/G rows (group g uses Hinv[g]);
+ * Hinv is the [G, Cp, Cp] factor of rq_chol_hinv.  All [R, C] work matrices are fp32 in the
+ * act_order-permuted column order.
+ *
+ * rq_fq_prepare replaces W_sub = W[rows][:, perm] with W_sub[:, dead] = 0 and gradients_sub[:, perm]
+ * (gptq_utils/gptq_plus_utils.py:1033-1049; gptq_utils/gptq_utils.py:68-82); dead = diag(H[g]) == 0.
+ * Gp/Grad may be NULL. */
+int rq_fq_prepare(const float* W, const float* Grad, const float* H, const int64_t* perm, int R, int C, int G,
+                  float* Wp, float* Gp, void* stream);
+
+/* rq_gptqplus_terms replaces compute_safe_beta_from_reference_loss and _compute_gradient_terms
+ * (gptq_utils/gptq_plus_utils.py:174-194, 563-578) for alpha > 0:
+ *   T = Gp . Hinv^T;  GHI = T . Hinv (= G . H^-1);  c = sum_j Gp*GHI - mean_j(GHI^2 / diag(H^-1));
+ *   beta = 1 - sqrt(1 - clamp(2*alpha_eff*ref_loss / max(c, 2*alpha_eff*ref_loss), 0, 1));
+ *   Z = beta * T;  GHinv = beta * GHI.       alpha_eff = alpha / (R*C).
+ * Z, GHinv: [R, C] outputs; beta: [R]; hdiag: [G, C] scratch receiving diag(H^-1). */
+int rq_gptqplus_terms(const float* Gp, const float* Hinv, int R, int C, int G, float alpha_eff, float ref_loss,
+                      float* Z, float* GHinv, float* beta, float* hdiag, void* stream);
+
+/* rq_fq_block replaces the inner column loop over one block [i1, i1+count), count <= 128
+ * (gptq_utils/gptq_plus_utils.py:1296-1372; gptq_utils/gptq_utils.py:120-151):
+ *   q_int = clamp(round(w/scale), -(maxq+1), maxq); q = scale*q_int; err = (w - q - GHinv[:, i]) / Hinv[i,i];
+ *   W[:, i:i2] -= err (x) Hinv[i, i:i2] + GHinv[:, i:i2];  GHinv[:, i:i2] -= Z[:, i] (x) Hinv[i, i:i2].
+ * Q receives q, codes q_int (int8), Eeff [R, 128] the A operand of the lazy update:
+ * Err (minus (count-1-i) * Z[:, i] when plus).  Scale source: mode 0 scale_row [R]; mode 1 static
+ * groups scale_tab [ngroups, R] indexed by colgrp [C]; mode 2 dynamic groups of width dyn_gs (divides
+ * 128) ranged from the block-start values (sym selects the range rule), written to scale_blk
+ * [C/dyn_gs, R].  plus == 0 ignores GH and Z (plain GPTQ, or GPTQ+ with beta = 0).
+ *
+ * rq_fq_lazy_update replaces the outer update (gptq_utils/gptq_plus_utils.py:1500-1570;
+ * gptq_utils/gptq_utils.py:153):  W[:, i2:] -= Eeff . Hinv[i1:i2, i2:] + count * GHinv[:, i2:];
+ * GHinv[:, i2:] -= Z[:, i1:i2] . Hinv[i1:i2, i2:].
+ *
+ * rq_fq_run performs both for every block of the linear. */
+int rq_fq_block(float* Wp, float* GH, const float* Z, const float* Hinv, float* Q, int8_t* codes, float* Eeff,
+                const float* scale_row, const float* scale_tab, const int* colgrp, float* scale_blk, int R, int C,
+                int G, int i1, int count, int mode, int dyn_gs, int sym, int maxq, int plus, void* stream);
+int rq_fq_lazy_update(float* Wp, float* GH, const float* Z, const float* Eeff, const float* Hinv, int R, int C, int G,
+                      int i1, int count, int plus, void* stream);
+int rq_fq_run(float* Wp, float* GH, const float* Z, const float* Hinv, float* Q, int8_t* codes, float* Eeff,
+              const float* scale_row, const float* scale_tab, const int* colgrp, float* scale_blk, int R, int C, int G,
+              int mode, int dyn_gs, int sym, int maxq, int plus, void* stream);
+
+/* rq_fq_finish replaces the epilogue (gptq_utils/gptq_plus_utils.py:1850-1875; gptq_utils/gptq_utils.py:157-166):
+ * out[r][perm[j]] = Q[r][j] cast to out_dtype; when out_codes != NULL also the fp32 int_weight / scale
+ * buffers, un-permuted (permute_export != 0, GPTQ+) or left in permuted order (plain GPTQ). */
+int rq_fq_finish(const float* Q, const int8_t* codes, const int64_t* perm, int R, int C, void* out, int out_dtype,
+                 float* out_codes, float* out_scale, const float* scale_row, const float* scale_tab,
+                 const int* colgrp, int permute_export, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

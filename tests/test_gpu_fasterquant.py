@@ -1,0 +1,252 @@
+"""Parity of the Cholesky / first-order-term / fasterquant kernels with the CPU oracle and the
+golden outputs of the unmodified reference.
+
+Tolerances: Hinv <= 2e-5 relative Frobenius (fp32 factorisations of matrices with condition
+number ~1e3-1e4 differ by that much between LAPACK builds as well); beta, Z, GHinv <= 1e-4
+relative; scales <= 1e-6 relative; integer codes: >= 99.9 % identical on the pooled cases, every
+mismatch off by exactly one code (a rounding tie that fell the other way) or downstream of one in
+the same row.
+"""
+import numpy as np
+import pytest
+import torch
+
+import cases
+from oracle import gptq as ogptq
+from oracle import hessian as ohess
+from oracle import quantizer as oq
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def rel_fro(a, b):
+    a, b = a.double().cpu(), b.double().cpu()
+    return float((a - b).norm() / b.norm())
+
+
+def _layer(W, dtype=torch.float32):
+    layer = torch.nn.Linear(W.shape[1], W.shape[0], bias=False, device=DEV, dtype=dtype)
+    layer.weight.data.copy_(W)
+    return layer
+
+
+# ---------------------------------------------------------------------------- Cholesky route
+@pytest.mark.parametrize("C,G,actorder", [(256, 2, True), (200, 1, False), (384, 4, True), (1024, 2, True)])
+def test_hinv_factor_vs_oracle(C, G, actorder):
+    from gptq_plus_mp_quant_b200.gptq_utils import fasterquant_impl as fi
+    X = cases.make_acts(4, max(128, C // 2), C, seed=17)
+    S = cases.make_saliency(4, max(128, C // 2), G, seed=17)
+    acc = ohess.GroupedHessian(C, S)
+    acc.add_batch(X)
+    acc.finalize()
+    perm = torch.argsort(acc.act_square, descending=True) if actorder else None
+    Hinv, damp, ident = fi.hinv_with_fallback(acc.H.to(DEV), None if perm is None else perm.to(DEV), 0.01, True)
+    assert Hinv.shape[-1] % 128 == 0
+    for g in range(G):
+        Hg = acc.H[g].clone()
+        if perm is not None:
+            Hg = Hg[perm][:, perm]
+        _, up, p, fb = ogptq.hinv_with_fallback(Hg, 0.01)
+        assert not fb and not ident[g] and abs(p - damp[g]) < 1e-12
+        got = Hinv[g, :C, :C].cpu()
+        assert rel_fro(got, up) < 2e-5
+        assert float(torch.tril(got, -1).abs().max()) == 0.0          # strictly upper, like chol(upper=True)
+        # defining property, checked in fp64: U^T U (H + lambda I) = I
+        damped = Hg.double() + 0.01 * Hg.double().diagonal().mean() * torch.eye(C, dtype=torch.float64)
+        resid = got.double().t() @ got.double() @ damped - torch.eye(C, dtype=torch.float64)
+        assert float(resid.abs().max()) < 5e-3
+
+
+def test_hinv_full_size_property():
+    """C = 4096 (benchmark size): U^T U (H + lambda I) = I to fp32 accuracy, no CPU factorisation needed."""
+    from gptq_plus_mp_quant_b200.gptq_utils import fasterquant_impl as fi
+    C = 4096
+    g = torch.Generator(device="cpu").manual_seed(5)
+    X = (torch.randn(8192, C, generator=g) * torch.exp(torch.randn(C, generator=g))).to(DEV)
+    H = (X.t() @ X / X.shape[0]).reshape(1, C, C).contiguous()
+    Hinv, damp, ident = fi.hinv_with_fallback(H, None, 0.01, True)
+    assert damp[0] == 0.01 and not ident[0]
+    U = Hinv[0].double()
+    P = H[0].double() + 0.01 * H[0].double().diagonal().mean() * torch.eye(C, dtype=torch.float64, device=DEV)
+    probe = torch.randn(C, 8, dtype=torch.float64, device=DEV)
+    back = U.t() @ (U @ (P @ probe))
+    assert float((back - probe).norm() / probe.norm()) < 1e-3
+
+
+def test_nonspd_retries_like_reference(golden):
+    from gptq_plus_mp_quant_b200.gptq_utils import fasterquant_impl as fi
+    g = golden("faults.npz")
+    H = torch.from_numpy(g["nonspd.H"]).reshape(1, 64, 64).to(DEV)
+    import logging
+    logging.disable(logging.WARNING)
+    Hinv, damp, ident = fi.hinv_with_fallback(H, None, 0.01, True)
+    logging.disable(logging.NOTSET)
+    assert ident[0] == bool(g["nonspd.identity"])
+    # the retry count may differ by one step when a pivot sits at the edge of positivity
+    assert abs(damp[0] - float(g["nonspd.damp"])) <= 0.0015 * 2 + 1e-9
+    if abs(damp[0] - float(g["nonspd.damp"])) < 1e-12:
+        assert rel_fro(Hinv[0, :64, :64], torch.from_numpy(g["nonspd.Hinv"])) < 1e-3
+
+
+def test_hopeless_hessian_falls_back_or_raises():
+    from gptq_plus_mp_quant_b200.gptq_utils import fasterquant_impl as fi
+    import logging
+    H = -torch.eye(128, device=DEV).reshape(1, 128, 128) * 3.0       # negative definite: no damping < 1 helps
+    logging.disable(logging.WARNING)
+    try:
+        Hinv, damp, ident = fi.hinv_with_fallback(H.clone(), None, 0.9, True)
+        assert ident[0] and damp[0] >= 1.0
+        assert torch.equal(Hinv[0], torch.eye(128, device=DEV))
+        with pytest.raises(ValueError):
+            fi.hinv_with_fallback(H.clone(), None, 0.9, False)
+    finally:
+        logging.disable(logging.NOTSET)
+    with pytest.raises(ValueError):
+        fi.hinv_with_fallback(H.clone(), None, 0.0, True)
+
+
+# ---------------------------------------------------------------------------- full objects vs the reference
+def _code_report(got, ref):
+    diff = (got != ref)
+    frac = float(diff.float().mean())
+    rows_touched = int(diff.any(dim=1).sum())
+    first_off = []
+    for r in torch.nonzero(diff.any(dim=1)).flatten().tolist():
+        j = int(torch.nonzero(diff[r]).flatten()[0])
+        first_off.append(abs(float(got[r, j] - ref[r, j])))
+    return frac, rows_touched, first_off
+
+
+POOL = {"n": 0, "bad": 0}
+
+
+@pytest.mark.parametrize("case", [c for c in cases.PLUS_CASES if c[12] == "frozen" and not c[13]],
+                         ids=lambda c: c[0])
+def test_gptqplus_fasterquant_vs_reference(golden, case):
+    from gptq_plus_mp_quant_b200.gptq_utils.gptq_plus_utils import GPTQPlus
+    from gptq_plus_mp_quant_b200.utils.quant_utils import WeightQuantizer
+    (name, rows, cols, nseq, seqlen, G, bits, gs, act, static, alpha, ref_loss, mode, atomic) = case
+    g = golden("gptq_plus.npz")
+    W = cases.make_weight(rows, cols, seed=31)
+    X = cases.make_acts(nseq, seqlen, cols, seed=31)
+    if "ragged" in name:
+        X[..., 5] = 0.0
+    S = cases.make_saliency(nseq, seqlen, G, seed=31)
+    Gr = cases.make_grad(rows, cols, seed=31)
+    layer = _layer(W)
+    obj = GPTQPlus(layer, S, Gr, G, alpha, ref_loss)
+    obj.quantizer = WeightQuantizer()
+    obj.quantizer.configure(bits, perchannel=True, sym=True, mse=False)
+    obj.add_batch(X[:1].to(DEV), None)
+    obj.add_batch(X[1:].to(DEV), None)
+    obj.finalize_hessian()
+    obj.fasterquant(blocksize=128, percdamp=0.01, groupsize=gs, actorder=act, static_groups=static,
+                    enable_gradient_update=True, g_update_mode=mode, export_to_et=True)
+    st = obj._last_fasterquant
+    if act:
+        assert torch.equal(st["perm"].cpu(), torch.from_numpy(g[f"{name}.perm"]))
+    if f"{name}.Hinv0" in g:
+        assert rel_fro(st["Hinv"][0, :cols, :cols], torch.from_numpy(g[f"{name}.Hinv0"])) < 2e-5
+    rg = rows // G
+    if alpha > 0:
+        assert torch.allclose(st["beta"][:rg].cpu(), torch.from_numpy(g[f"{name}.beta0"]), rtol=1e-4, atol=1e-7)
+        assert rel_fro(st["Z"][:rg], torch.from_numpy(g[f"{name}.Z0"])) < 1e-4
+        assert rel_fro(st["GHinv"][:rg], torch.from_numpy(g[f"{name}.GHinv0"])) < 1e-4
+    scale_ref = torch.from_numpy(g[f"{name}.Scale"])
+    assert torch.allclose(layer.scale.cpu(), scale_ref, rtol=1e-6, atol=0) or gs != -1 and not static
+    codes_ref = torch.from_numpy(g[f"{name}.W_int"]).float()
+    frac, rows_touched, first_off = _code_report(layer.int_weight.cpu(), codes_ref)
+    print(f"{name}: {frac * 100:.4f}% codes differ in {rows_touched} rows; first deviations {first_off[:8]}")
+    POOL["n"] += codes_ref.numel()
+    POOL["bad"] += int(frac * codes_ref.numel() + 0.5)
+    assert all(d == 1.0 for d in first_off), "a row's first deviation must be a one-step rounding tie"
+    assert frac < 0.01
+    if frac == 0.0:
+        assert torch.allclose(layer.weight.data.cpu(), torch.from_numpy(g[f"{name}.Q"]), rtol=1e-6, atol=0)
+    assert layer.weight.dtype == torch.float32
+
+
+@pytest.mark.parametrize("case", cases.PLAIN_CASES, ids=lambda c: c[0])
+def test_plain_gptq_fasterquant_vs_reference(golden, case):
+    from gptq_plus_mp_quant_b200.gptq_utils.gptq_utils import GPTQ
+    from gptq_plus_mp_quant_b200.utils.quant_utils import WeightQuantizer
+    (name, rows, cols, nseq, seqlen, bits, sym, gs, act, static, bs) = case
+    g = golden("plain_gptq.npz")
+    W = cases.make_weight(rows, cols, seed=21)
+    X = cases.make_acts(nseq, seqlen, cols, seed=21)
+    if "ragged" in name:
+        X[..., 7] = 0.0
+    layer = _layer(W)
+    obj = GPTQ(layer)
+    obj.quantizer = WeightQuantizer()
+    obj.quantizer.configure(bits, perchannel=True, sym=sym, mse=False)
+    for s in range(nseq):
+        obj.add_batch(X[s:s + 1].to(DEV), None)
+    obj.fasterquant(blocksize=bs, percdamp=0.01, groupsize=gs, actorder=act, static_groups=static, export_to_et=True)
+    codes_ref = torch.from_numpy(g[f"{name}.W_int"]).float()
+    frac, rows_touched, first_off = _code_report(layer.int_weight.cpu(), codes_ref)
+    print(f"{name}: {frac * 100:.4f}% codes differ in {rows_touched} rows; first deviations {first_off[:8]}")
+    POOL["n"] += codes_ref.numel()
+    POOL["bad"] += int(frac * codes_ref.numel() + 0.5)
+    assert all(d == 1.0 for d in first_off)
+    assert frac < 0.01
+    if gs == -1 or static:
+        assert torch.allclose(layer.scale.cpu(), torch.from_numpy(g[f"{name}.Scale"]), rtol=1e-6, atol=0)
+    if frac == 0.0:
+        assert torch.allclose(layer.weight.data.cpu(), torch.from_numpy(g[f"{name}.Q"]), rtol=1e-6, atol=0)
+    assert not hasattr(obj, "_H") or obj._H is None                 # H is consumed like in the reference
+
+
+def test_pooled_code_agreement():
+    """Over all golden cases together at least 99.9 % of the integer codes equal the reference's."""
+    assert POOL["n"] > 100000
+    print(f"pooled: {POOL['bad']} of {POOL['n']} codes differ")
+    assert POOL["bad"] / POOL["n"] < 1e-3
+
+
+def test_mid_size_vs_oracle_bf16_weights():
+    """A 512 x 1024 linear with bf16 weights, G = 4, alpha > 0: kernels against the CPU oracle."""
+    from gptq_plus_mp_quant_b200.gptq_utils.gptq_plus_utils import GPTQPlus
+    from gptq_plus_mp_quant_b200.utils.quant_utils import WeightQuantizer
+    rows, cols, G, nseq, seqlen = 512, 1024, 4, 4, 512
+    W = cases.make_weight(rows, cols, seed=41).bfloat16()
+    X = cases.make_acts(nseq, seqlen, cols, seed=41)
+    S = cases.make_saliency(nseq, seqlen, G, seed=41)
+    Gr = cases.make_grad(rows, cols, seed=41)
+    acc = ohess.GroupedHessian(cols, S)
+    acc.add_batch(X)
+    acc.finalize()
+    q = oq.OracleWeightQuantizer()
+    q.configure(4, perchannel=True, sym=True)
+    ref = ogptq.plus_fasterquant(W.float(), acc.H, acc.act_square, Gr, q, G, 0.25, 0.7, actorder=True,
+                                 static_groups=True)
+    layer = _layer(W, torch.bfloat16)
+    obj = GPTQPlus(layer, S, Gr, G, 0.25, 0.7)
+    obj.quantizer = WeightQuantizer()
+    obj.quantizer.configure(4, perchannel=True, sym=True)
+    obj.add_batch(X.to(DEV), None)
+    obj.finalize_hessian()
+    obj.fasterquant(actorder=True, static_groups=True, export_to_et=True)
+    assert layer.weight.dtype == torch.bfloat16
+    frac, rows_touched, first_off = _code_report(layer.int_weight.cpu(), ref["W_int"])
+    print(f"mid-size: {frac * 100:.4f}% codes differ in {rows_touched} rows; first deviations {first_off[:8]}")
+    assert frac < 1e-3
+    assert all(d == 1.0 for d in first_off)
+    assert torch.allclose(layer.scale.cpu(), ref["Scale"], rtol=1e-6, atol=0)
+
+
+def test_unsupported_modes_are_loud():
+    from gptq_plus_mp_quant_b200.gptq_utils.gptq_plus_utils import GPTQPlus
+    from gptq_plus_mp_quant_b200.utils.quant_utils import WeightQuantizer
+    W = cases.make_weight(8, 128, seed=1)
+    layer = _layer(W)
+    obj = GPTQPlus(layer, torch.ones(1, 16, 2), torch.zeros(8, 128), 2, 0.0, 0.0)
+    obj.quantizer = WeightQuantizer()
+    obj.quantizer.configure(4, perchannel=True, sym=True)
+    obj.add_batch(torch.randn(1, 16, 128, device=DEV), None)
+    obj.finalize_hessian()
+    with pytest.raises(NotImplementedError):
+        obj.fasterquant(g_update_mode="block_gd")
+    with pytest.raises(ValueError):
+        obj.fasterquant(groupsize=64, static_groups=False)

@@ -1,6 +1,8 @@
 """Parity of the sm_100a kernels (through the C ABI) with the CPU oracle and with the golden
 outputs of the reference: Hessian accumulation/finalisation, Hadamard rotation, weight
-quantizer.  Tolerances: H <= 2e-6 relative Frobenius (bar: 1e-5), scale/zero <= 1e-6 relative
+quantizer.  Tolerances: H <= 5e-6 relative Frobenius for sums over a few hundred tokens and
+<= 2e-6 from a few thousand tokens on (the split-bf16 rounding terms average out with the
+token count; bar: 1e-5), scale/zero <= 1e-6 relative
 (bar: 1e-5), integer codes identical, rotation within one rounding of the I/O dtype."""
 import numpy as np
 import pytest
@@ -51,9 +53,30 @@ def test_grouped_hessian_sum(C, G, nseq, seqlen, dtype, variant):
     ops.check_status(torch.device(DEV))
     ref_sym = 0.5 * (ref.H + ref.H.transpose(-1, -2))
     for g in range(G):
-        assert rel_fro(H[g], ref_sym[g]) < 2e-6, f"group {g}"
+        assert rel_fro(H[g], ref_sym[g]) < 5e-6, f"group {g}"
     assert torch.allclose(act.cpu(), ref.act_square, rtol=2e-6, atol=0)
     assert torch.equal(H, H.transpose(-1, -2))                       # exactly symmetric
+
+
+@pytest.mark.parametrize("dtype,bound", [(torch.float32, 2e-6), (torch.bfloat16, 1e-6)])
+def test_grouped_hessian_many_tokens_is_fp32_faithful(dtype, bound):
+    """From a few thousand tokens on the result sits at fp32-GEMM quality."""
+    from gptq_plus_mp_quant_b200 import ops
+    C, G, nseq, seqlen = 512, 4, 4, 2048
+    X = cases.make_acts(nseq, seqlen, C, seed=13, dtype=dtype)
+    S = cases.make_saliency(nseq, seqlen, G, seed=13)
+    Xd = X.double().reshape(-1, C)
+    Sd = S.double().reshape(-1, G)
+    exact = torch.stack([Xd.t() @ (Xd * Sd[:, g:g + 1]) for g in range(G)])
+    H = torch.zeros(G, C, C, device=DEV)
+    ops.hessian_accum(X.reshape(-1, C).to(DEV), S.reshape(-1, G).to(DEV), H, None)
+    ops.hessian_finalize(H, None)
+    err = rel_fro(H, exact)
+    ref = _oracle_grouped(X.float(), S)                                # the fp32 CPU path, for scale
+    err_ref = rel_fro(ref.H, exact)
+    print(f"rel. Frobenius vs fp64: kernel {err:.3e}, fp32 CPU path {err_ref:.3e}")
+    assert err < bound
+    assert err_ref < 1e-6
 
 
 def test_hessian_chunking_and_accumulation_across_calls():
@@ -69,7 +92,7 @@ def test_hessian_chunking_and_accumulation_across_calls():
         ops.hessian_accum(X[s].to(DEV), S[s].to(DEV), H, act, chunk_tokens=64)
     ops.hessian_finalize(H, None)
     ref_sym = 0.5 * (ref.H + ref.H.transpose(-1, -2))
-    assert rel_fro(H, ref_sym) < 2e-6
+    assert rel_fro(H, ref_sym) < 5e-6
     assert torch.allclose(act.cpu(), ref.act_square, rtol=2e-6)
 
 
@@ -94,7 +117,7 @@ def test_gptqplus_add_batch_finalize_vs_reference(golden, case):
     obj.add_batch(X[1:].to(DEV), None)
     obj.finalize_hessian()
     Href = torch.from_numpy(g[f"{name}.H"])
-    assert rel_fro(obj.H, Href) < 2e-6
+    assert rel_fro(obj.H, Href) < 5e-6
     assert torch.allclose(obj.act_square.cpu(), torch.from_numpy(g[f"{name}.act_square"]), rtol=2e-6)
     if "ragged" in name:
         assert float(obj.H[:, 5, :].abs().max()) == 0.0             # the dead channel stays exactly zero
@@ -116,7 +139,7 @@ def test_plain_gptq_running_mean_vs_reference(golden):
     for s in range(nseq):
         obj.add_batch(X[s:s + 1].to(DEV), None)
     assert obj.nsamples == nseq
-    assert rel_fro(obj.H, torch.from_numpy(g[f"{name}.H"])) < 2e-6
+    assert rel_fro(obj.H, torch.from_numpy(g[f"{name}.H"])) < 5e-6
 
 
 def test_finalize_sanitises_nonfinite_and_counts():
