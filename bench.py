@@ -1,19 +1,24 @@
 #!/usr/bin/env python
 """Benchmark of the per-layer GPTQ+ quantization path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload NAME]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload layer|hessian_c1]
 
-Prints ONE JSON line.  A step is one pass of the hot path over one batch of seeded synthetic
-input shaped like the reference's calibration activations (no dataset or checkpoint is used).
-With N > 1 (launched by torchrun, one rank per GPU) the calibration sequences are sharded over
-the ranks exactly like the reference shards them, each rank accumulates its partial Hessian sum
-and one NCCL all-reduce combines them; the value is whole-job throughput, timed on the device and
-taken as the max over ranks.
+Prints ONE JSON line.  The default workload is one Qwen3-8B-shape decoder layer (hidden 4096,
+intermediate 12288, 32 query / 8 KV heads of 128): a step rotates the calibration activations
+online (Hadamard on [N, 4096] and [N, 12288]), accumulates the saliency-weighted Hessians of the
+seven linears over 128 x 2048 tokens, finalises them and runs fasterquant (W4, groupsize 128,
+act_order, GPTQ+ first-order term) on all seven.  Inputs are seeded synthetic tensors with the
+shapes and value distributions of the reference's calibration run; no dataset or checkpoint is
+used.  With N > 1 (torchrun, one rank per GPU) the calibration sequences are sharded over the ranks
+as the reference shards them, each partial Hessian sum is reduced over NCCL to the rank that owns
+the linear, the seven linears' fasterquant stages are spread over the ranks, and the quantized
+weights are broadcast back; timing is on the device, max over ranks.
 """
 from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
 import subprocess
 import sys
@@ -25,6 +30,8 @@ import torch
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 sys.path.insert(0, os.path.join(ROOT, "tests", "golden"))
+
+METRIC = "seconds per decoder layer quantized (Qwen3-8B shape)"
 
 
 # ----------------------------------------------------------------------------------------------
@@ -81,15 +88,12 @@ class ClockSampler:
             for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
                 if val.lower().startswith("active"):
                     reasons.add(name)
-        # the highest-clock half of the samples is the load phase (idle samples sit at low clocks too,
-        # so the median is taken over samples at or above the overall median)
         sm.sort()
-        load = sm[len(sm) // 2:] if sm else []
-        med = load[len(load) // 2] if load else None
+        med = sm[len(sm) // 2] if sm else None
         return {"sm_mhz": med, "sm_max_mhz": smax, "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def dist_setup(n_gpus: int):
+def dist_setup():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -102,92 +106,210 @@ def dist_setup(n_gpus: int):
     return rank, world, local
 
 
-# ----------------------------------------------------------------------------------------------
-# workload: saliency-weighted multi-group Hessian of the up_proj shape (configs[1])
-# ----------------------------------------------------------------------------------------------
-class HessianC1:
-    """W [12288 x 4096] (up_proj), 128 x 2048 tokens x 4096 fp32 activations, G = 4 saliency groups.
-    One step = GPTQPlus.add_batch over every local sequence (8 sequences per call) followed by
-    finalize_hessian (all-reduce when N > 1, normalise, symmetrise, sanitise)."""
-    name = "c1: Hessian accumulation, up_proj shape 12288x4096, 128x2048 tokens fp32, G=4"
-    C, R, G, NSEQ, T, BSZ = 4096, 12288, 4, 128, 2048, 8
+def assign_owners(costs, world):
+    """Longest-processing-time-first assignment of the linears' fasterquant stages to ranks."""
+    load = [0.0] * world
+    owner = {}
+    for name, c in sorted(costs.items(), key=lambda kv: -kv[1]):
+        r = min(range(world), key=lambda i: load[i])
+        owner[name] = r
+        load[r] += c
+    return owner
 
-    def __init__(self, rank, world, scale_down=1):
-        import cases
+
+# ----------------------------------------------------------------------------------------------
+# workload: one Qwen3-8B-shape decoder layer (configs[2])
+# ----------------------------------------------------------------------------------------------
+class LayerWorkload:
+    name = ("c2: one Qwen3-8B-shape decoder layer, 7 linears W4 g128 act_order GPTQ+ (G=4), "
+            "128x2048 calibration tokens bf16, online Hadamard on [N,4096] and [N,12288]")
+    HID, INTER, KV = 4096, 12288, 1024
+    NSEQ, T, G, BSZ = 128, 2048, 4, 8
+    LINEARS = [  # name, out_features, in_features, input stream
+        ("q_proj", 4096, 4096, "hid"), ("k_proj", 1024, 4096, "hid"), ("v_proj", 1024, 4096, "hid"),
+        ("o_proj", 4096, 4096, "attn"), ("gate_proj", 12288, 4096, "hid"), ("up_proj", 12288, 4096, "hid"),
+        ("down_proj", 4096, 12288, "mlp"),
+    ]
+
+    def __init__(self, rank, world, nseq=None):
+        from gptq_plus_mp_quant_b200.utils import hadamard_utils as hu
         self.rank, self.world = rank, world
-        self.nseq_local = self.NSEQ // world if world > 1 else self.NSEQ
-        self.nseq_local = max(self.BSZ, self.nseq_local // scale_down)
-        g = torch.Generator(device="cpu")
-        g.manual_seed(1234 + rank)
-        ch = torch.exp(torch.randn(self.C, generator=g))
-        # host (pinned) copy for the end-to-end leg; device copy for the kernel-throughput leg
-        # 8 distinct seeded sequences, tiled to the full count (the values do not affect the timing)
-        self.x_host = torch.empty(self.nseq_local, self.T, self.C, dtype=torch.float32).pin_memory()
-        base = torch.randn(8, self.T, self.C, generator=g) * ch
-        for s in range(0, self.nseq_local, 8):
-            self.x_host[s:s + 8] = base[: min(8, self.nseq_local - s)]
-        sal = torch.exp(3.0 * torch.randn(self.nseq_local, self.T, self.G, generator=g))
-        cap = torch.quantile(sal.flatten()[:1_000_000].double(), 0.99).float()
-        self.sal = torch.clamp(sal, max=cap)
-        self.x_dev = self.x_host.cuda()
-        self.grad = torch.zeros(self.R, self.C)
-        self.layer = torch.nn.Linear(self.C, self.R, bias=False, device="cuda")
+        total = nseq or self.NSEQ
+        self.nseq_total = total
+        self.nseq_local = total // world
+        dev = torch.device("cuda", torch.cuda.current_device())
+        self.dev = dev
+        g = torch.Generator(device=dev)
+        g.manual_seed(4321 + rank)
+        n, T = self.nseq_local, self.T
 
-    @property
-    def tokens_global(self):
-        return self.nseq_local * self.T * (self.world if self.world > 1 else 1)
+        def acts(width):
+            ch = torch.exp(torch.randn(width, generator=g, device=dev))
+            out = torch.empty(n, T, width, dtype=torch.bfloat16, device=dev)
+            for s in range(0, n, 8):
+                out[s:s + 8] = (torch.randn(min(8, n - s), T, width, generator=g, device=dev) * ch).bfloat16()
+            return out
 
-    def flops_per_step(self):
-        return 2.0 * self.tokens_global * self.C * self.C * self.G
+        self.dev_in = {"hid": acts(self.HID), "attn": acts(self.HID), "mlp": acts(self.INTER)}
+        self.host_in = {k: v.cpu().pin_memory() for k, v in self.dev_in.items()}
+        self.had12, _ = hu.get_hadK(self.INTER)
+        gw = torch.Generator(device=dev)
+        gw.manual_seed(99)                                       # weights identical on every rank
+        self.layers, self.master, self.sal, self.grad = {}, {}, {}, {}
+        for name, R, C, _ in self.LINEARS:
+            w = (torch.randn(R, C, generator=gw, device=dev) * 0.02).bfloat16()
+            lin = torch.nn.Linear(C, R, bias=False, device=dev, dtype=torch.bfloat16)
+            lin.weight.requires_grad_(False)
+            self.layers[name], self.master[name] = lin, w
+            s = torch.exp(3.0 * torch.randn(n, T, self.G, generator=g, device=dev))
+            cap = torch.quantile(s.flatten()[:1_000_000], 0.99)
+            self.sal[name] = torch.clamp(s, max=cap)
+            self.grad[name] = torch.randn(R, C, generator=gw, device=dev) * 1e-4
+        costs = {name: (2.0 / 3.0) * C ** 3 * self.G + 5.0 * R * C * C for name, R, C, _ in self.LINEARS}
+        self.owner = assign_owners(costs, world)
 
-    def _obj(self):
+    # ---- algorithmic work figures
+    def hessian_flops(self, local=False):
+        n = (self.nseq_local if local else self.nseq_total) * self.T
+        return sum(2.0 * n * C * C * self.G for _, _, C, _ in self.LINEARS)
+
+    def fwht_bytes_local(self):
+        n = self.nseq_local * self.T
+        return 2 * n * (self.HID + self.INTER) * 2
+
+    def _quantize(self, inputs, from_host):
         from gptq_plus_mp_quant_b200.gptq_utils.gptq_plus_utils import GPTQPlus
-        o = GPTQPlus(self.layer, self.sal, self.grad, self.G, 0.0, 0.0)
-        o.saliencies = o.saliencies.cuda()
-        return o
+        from gptq_plus_mp_quant_b200.utils import hadamard_utils as hu
+        from gptq_plus_mp_quant_b200.utils.quant_utils import WeightQuantizer
+        import torch.distributed as dist
+        objs = {}
+        for name, R, C, _ in self.LINEARS:
+            self.layers[name].weight.data.copy_(self.master[name])
+            o = GPTQPlus(self.layers[name], self.sal[name], self.grad[name], self.G, 0.25, 0.7)
+            o.quantizer = WeightQuantizer()
+            o.quantizer.configure(4, perchannel=True, sym=True, mse=False)
+            objs[name] = o
+        for s in range(0, self.nseq_local, self.BSZ):
+            batch = {}
+            for key in ("hid", "attn", "mlp"):
+                x = inputs[key][s:s + self.BSZ]
+                batch[key] = x.cuda(non_blocking=True) if from_host else x
+            rot = {"hid": hu.matmul_hadU_cuda(batch["hid"], None, 1), "attn": batch["attn"],
+                   "mlp": hu.matmul_hadU_cuda(batch["mlp"], self.had12, 12)}
+            for name, _, _, key in self.LINEARS:
+                objs[name].add_batch(rot[key], None)
+        checksum = torch.zeros((), device=self.dev)
+        for name, R, C, _ in self.LINEARS:
+            o = objs[name]
+            o.hessian_owner = self.owner[name] if self.world > 1 else None
+            o.finalize_hessian()
+            if self.world == 1 or self.owner[name] == self.rank:
+                o.fasterquant(blocksize=128, percdamp=0.01, groupsize=128, actorder=True, static_groups=True)
+            if self.world > 1:
+                dist.broadcast(self.layers[name].weight.data, src=self.owner[name])
+            checksum += self.layers[name].weight.data.float().abs().mean()
+            o.free()
+        return checksum
 
     def step_device(self):
-        o = self._obj()
-        for s in range(0, self.nseq_local, self.BSZ):
-            o.add_batch(self.x_dev[s:s + self.BSZ], None)
-        o.finalize_hessian()
-        return o
+        return self._quantize(self.dev_in, False)
 
     def step_e2e(self):
-        """Same work through the public API with HOST activations: every batch is copied from pinned
-        host memory inside the timed region and act_square is read back at the end."""
-        o = self._obj()
-        for s in range(0, self.nseq_local, self.BSZ):
-            xb = self.x_host[s:s + self.BSZ].cuda(non_blocking=True)
-            o.add_batch(xb, None)
-        o.finalize_hessian()
-        return o.act_square.cpu()
+        """Public API with HOST activations: each batch is copied from pinned host memory inside the timed
+        region and a checksum of the quantized weights is read back."""
+        return float(self._quantize(self.host_in, True).item())
 
     def h2d_bytes(self):
-        return self.nseq_local * self.T * self.C * 4
+        return sum(v.numel() * 2 for v in self.host_in.values())
 
-    def d2h_bytes(self):
-        return self.C * 4
+    def launches_per_step(self):
+        """Kernel launches of this library in one step, counted from the host loops."""
+        batches = self.nseq_local // self.BSZ
+        chunks = max(1, (self.BSZ * self.T) // 8192)
+        n = batches * 2                                               # two rotations per batch
+        n += batches * len(self.LINEARS) * chunks * 3                 # pack + sum-of-squares reduce + tensor-core GEMM
+        for name, R, C, _ in self.LINEARS:
+            n += 1                                                    # finalize
+            if self.world == 1 or self.owner[name] == self.rank:
+                blocks = C // 128
+                n += 1 + 2 + 3 * blocks + 2 * math.ceil(math.log2(blocks)) + 1   # ranges, Cholesky route
+                n += 1 + 4 + blocks * 3 + 1                           # prepare, first-order terms, block loop, epilogue
+        return n
 
-    def cpu_reference(self, nseq_sample: int):
-        """The CPU port of the reference's add_batch + finalize_hessian on a bounded sample."""
-        from oracle import hessian as ohess
-        acc = ohess.GroupedHessian(self.C, self.sal[:nseq_sample])
-        t0 = time.perf_counter()
-        for s in range(0, nseq_sample, self.BSZ):
-            acc.add_batch(self.x_host[s:s + self.BSZ])
-        acc.finalize()
-        dt = time.perf_counter() - t0
-        return 2.0 * nseq_sample * self.T * self.C * self.C * self.G / dt / 1e12, dt
+
+# ----------------------------------------------------------------------------------------------
+# CPU arm: the port of the reference's own code on the host cores
+# ----------------------------------------------------------------------------------------------
+def cpu_layer_seconds(hess_seqs: int, fq_rows: int):
+    """Times the CPU port on a bounded sample and extrapolates to the whole layer:
+    Hessian stage by its flop count, fasterquant by rows (the sample quantizes `fq_rows` rows of a
+    4096-input linear with G = 4; Cholesky cost is per linear, the block loop per row)."""
+    import cases
+    from oracle import gptq as ogptq
+    from oracle import hessian as ohess
+    from oracle import quantizer as oq
+    W = LayerWorkload
+    C, G, T = W.HID, W.G, W.T
+    X = cases.make_acts(hess_seqs, T, C, seed=77)
+    S = cases.make_saliency(hess_seqs, T, G, seed=77)
+    acc = ohess.GroupedHessian(C, S)
+    t0 = time.perf_counter()
+    acc.add_batch(X)
+    t_h = time.perf_counter() - t0
+    acc.finalize()
+    hess_tflops = 2.0 * hess_seqs * T * C * C * G / t_h / 1e12
+    Wt = cases.make_weight(fq_rows, C, seed=78)
+    Gr = cases.make_grad(fq_rows, C, seed=78)
+    q = oq.OracleWeightQuantizer()
+    q.configure(4, perchannel=True, sym=True)
+    t0 = time.perf_counter()
+    hinv_t0 = time.perf_counter()
+    ogptq.hinv_with_fallback(acc.H[0], 0.01)
+    t_chol = (time.perf_counter() - hinv_t0) * G                       # per 4096-input linear
+    ogptq.plus_fasterquant(Wt, acc.H, acc.act_square, Gr, q, G, 0.25, 0.7, groupsize=128, actorder=True,
+                           static_groups=True)
+    t_fq = time.perf_counter() - t0 - t_chol / G
+    per_row = max(t_fq - t_chol, 0.0) / fq_rows                        # block loop + lazy update per row at C = 4096
+    total_h = sum(2.0 * W.NSEQ * T * c * c * G for _, _, c, _ in W.LINEARS) / (hess_tflops * 1e12)
+    total_fq = 0.0
+    for _, R, Cc, _ in W.LINEARS:
+        scale_c = (Cc / C)
+        total_fq += t_chol * scale_c ** 3 + per_row * R * scale_c ** 2
+    return total_h + total_fq, hess_tflops, t_h + t_fq
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    torch.set_num_threads(os.cpu_count() or 1)
+    vals, busy = [], []
+    for i in range(max(args.warmup, 0) + args.steps):
+        v, tf, b = cpu_layer_seconds(hess_seqs=2, fq_rows=64)
+        if i >= args.warmup:
+            vals.append(v)
+            busy.append(b)
+    v = sum(vals) / len(vals)
+    sample = ("per step: reference add_batch on 2 of 128 sequences at C=4096 G=4 plus fasterquant of 64 rows x 4096 "
+              "(G=4, g128, act_order, alpha=0.25), extrapolated to the layer by flops (Hessian), C^3 (Cholesky) "
+              "and rows*C^2 (block loop)")
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": round(v, 2), "unit": "s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(1e3 * sum(busy) / len(busy), 1),
+        "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": LayerWorkload.name, "sample": sample},
+        "cpu_baseline": {"value": round(v, 2), "unit": "s", "cores": torch.get_num_threads(), "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": round(v, 2), "unit": "s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
 
 
 # ----------------------------------------------------------------------------------------------
 def run_ours(args):
     from gptq_plus_mp_quant_b200 import _lib
-    rank, world, local = dist_setup(args.gpus)
+    rank, world, local = dist_setup()
     peaks = load_peaks()
-    wl = HessianC1(rank, world)
-    dev = torch.device("cuda", torch.cuda.current_device())
+    wl = LayerWorkload(rank, world)
+    dev = wl.dev
 
     def barrier():
         if world > 1:
@@ -207,108 +329,71 @@ def run_ours(args):
             torch.distributed.all_reduce(ms, op=torch.distributed.ReduceOp.MAX)
         return float(ms.item())
 
-    for _ in range(max(args.warmup, 3)):
+    warm = max(args.warmup, 3)
+    for _ in range(warm):
         wl.step_device()
     sampler = ClockSampler(local)
     sampler.start()
     _lib.profile_enable(True)
     total_ms = timed(wl.step_device, args.steps)
-    umma_ms, umma_n = _lib.profile_read(_lib.PROF_HESSIAN_UMMA)
-    pack_ms, pack_n = _lib.profile_read(_lib.PROF_HESSIAN_PACK)
+    prof = {name: _lib.profile_read(tag) for name, tag in
+            (("umma", _lib.PROF_HESSIAN_UMMA), ("pack", _lib.PROF_HESSIAN_PACK), ("fwht", _lib.PROF_FWHT),
+             ("chol", _lib.PROF_CHOL), ("block", _lib.PROF_BLOCK), ("lazy", _lib.PROF_LAZY))}
     _lib.profile_enable(False)
     clocks = sampler.stop()
-    for _ in range(2):
-        wl.step_e2e()
+    wl.step_e2e()
     e2e_ms = timed(wl.step_e2e, args.steps)
 
-    ms_per_step = total_ms / args.steps
-    value = wl.flops_per_step() / (ms_per_step * 1e-3) / 1e12
-    e2e_value = wl.flops_per_step() / (e2e_ms / args.steps * 1e-3) / 1e12
-    # roofline of the dominant kernel: algorithmic flops of one launch / its mean duration
-    launches_per_step = umma_n / args.steps
-    local_flops = 2.0 * wl.nseq_local * wl.T * wl.C * wl.C * wl.G
-    flops_per_launch = local_flops / launches_per_step
-    achieved = flops_per_launch / (umma_ms / umma_n * 1e-3) / 1e12
+    sec_per_layer = total_ms / args.steps / 1e3
+    umma_ms, umma_n = prof["umma"]
+    # roofline of the dominant kernel: algorithmic flops 2*N*C^2*G of the launches / their summed duration
+    achieved = wl.hessian_flops(local=True) * args.steps / (umma_ms * 1e-3) / 1e12 if umma_ms else 0.0
     peak = peaks["bf16_tflops_sustained"]
-    # three bf16 products on the 272 of 512 tiles that touch the upper triangle (C = 4096)
-    nt, mt = wl.C // 256, wl.C // 128
-    issued_factor = 3.0 * ((nt - 1) * nt + mt) / (nt * mt)
+    fwht_ms, fwht_n = prof["fwht"]
     out = {
-        "metric": "Hessian-accum TFLOP/s", "value": round(value, 2), "unit": "TFLOP/s", "n_gpus": world,
-        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms_per_step, 3),
-        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16x3 split, f32 accumulate",
+        "metric": METRIC, "value": round(sec_per_layer, 4), "unit": "s", "n_gpus": world, "steps": args.steps,
+        "warmup": warm, "ms_per_step": round(total_ms / args.steps, 2), "higher_is_better": False,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16 split products, f32 accumulate; f32 elsewhere",
         "data": "synthetic",
-        "config": {"workload": wl.name, "tokens": wl.tokens_global, "hessian_accum_bsz": wl.BSZ,
-                   "l2": "activations (4.3 GB) and packed operands (0.67 GB per chunk) exceed the 126 MB L2",
-                   "parallelism": f"dp{world} over calibration sequences + NCCL all-reduce of H"},
-        "roofline": {"bound": "tensor", "achieved": round(achieved, 2), "peak": peak, "unit": "TFLOP/s",
+        "config": {"workload": wl.name, "tokens": wl.nseq_total * wl.T, "hessian_accum_bsz": wl.BSZ,
+                   "l2": "per-step inputs (10.7 GB of activations, 4 GB of Hessians) exceed the 126 MB L2",
+                   "parallelism": (f"dp{world}: calibration sequences sharded, NCCL reduce of each H to the owner "
+                                   f"of its linear, fasterquant of the 7 linears spread over ranks"),
+                   "fasterquant_owner": wl.owner if world > 1 else None},
+        "hessian_accum_tflops": round(wl.hessian_flops() * args.steps / (umma_ms * 1e-3 + prof["pack"][0] * 1e-3)
+                                      / 1e12, 1) if umma_ms else None,
+        "roofline": {"bound": "tensor", "achieved": round(achieved, 1), "peak": peak, "unit": "TFLOP/s",
                      "frac": round(achieved / peak, 4), "traffic": None, "peak_source": peaks["source"] + " sustained",
-                     "kernel": "rq::hess::umma_kernel<64,3>", "launch_ms": round(umma_ms / umma_n, 4),
-                     "issued_tflops": round(achieved * issued_factor, 2),
-                     "issued_frac": round(achieved * issued_factor / peak, 4)},
-        "kernel_share": {"umma_ms_per_step": round(umma_ms / args.steps, 3),
-                         "pack_ms_per_step": round(pack_ms / args.steps, 3)},
-        "e2e": {"value": round(e2e_value, 2), "unit": "TFLOP/s", "h2d_bytes_per_step": wl.h2d_bytes(),
-                "d2h_bytes_per_step": wl.d2h_bytes()},
-        "gpu_launches": int(umma_n + 2 * pack_n + args.steps),   # tensor-core GEMM, pack + its reduction, finalize
+                     "kernel": "rq::hess::umma_kernel<64,2> (+<64,3> for fp32 inputs)", "launches": umma_n,
+                     "note": "algorithmic 2*N*C^2*G; the kernel issues 2 bf16 products on the ~53% of tiles that "
+                             "touch the upper triangle"},
+        "stage_ms_per_step": {k: round(v[0] / args.steps, 2) for k, v in prof.items()},
+        "fwht_gbs": round(wl.fwht_bytes_local() * args.steps / (fwht_ms * 1e-3) / 1e9, 1) if fwht_ms else None,
+        "e2e": {"value": round(e2e_ms / args.steps / 1e3, 4), "unit": "s", "h2d_bytes_per_step": wl.h2d_bytes(),
+                "d2h_bytes_per_step": 4},
+        "gpu_launches": wl.launches_per_step() * args.steps,
         "clocks": clocks,
     }
-    if rank == 0 and world == 1:
+    if rank == 0 and world == 1 and not args.no_cpu:
         torch.set_num_threads(os.cpu_count() or 1)
-        v, dt = wl.cpu_reference(nseq_sample=8)
-        out["cpu_baseline"] = {"value": round(v, 4), "unit": "TFLOP/s", "cores": torch.get_num_threads(),
-                               "kind": "port", "sample": f"8 of {wl.NSEQ} sequences (16384 tokens), {dt:.1f} s"}
+        v, tf, busy = cpu_layer_seconds(hess_seqs=2, fq_rows=64)
+        out["cpu_baseline"] = {"value": round(v, 1), "unit": "s", "cores": torch.get_num_threads(), "kind": "port",
+                               "sample": f"add_batch on 2 of 128 sequences (C=4096, G=4: {tf:.2f} TFLOP/s) and "
+                                         f"fasterquant of 64 rows x 4096, {busy:.1f} s of CPU work, extrapolated to "
+                                         "the layer by flops / C^3 / rows*C^2"}
     if rank == 0:
         print(json.dumps(out))
     if world > 1:
         torch.distributed.destroy_process_group()
 
 
-def run_reference(args):
-    """The reference's own CPU implementation (the oracle port: the reference is Python and does
-    not travel to the GPU box) on the box's host cores, all threads."""
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
-        return
-    torch.set_num_threads(os.cpu_count() or 1)
-    g = torch.Generator(device="cpu")
-    g.manual_seed(1234)
-    C, G, T, BSZ, nseq = HessianC1.C, HessianC1.G, HessianC1.T, 4, 4
-    from oracle import hessian as ohess
-    ch = torch.exp(torch.randn(C, generator=g))
-    X = torch.randn(nseq, T, C, generator=g) * ch
-    S = torch.exp(3.0 * torch.randn(nseq, T, G, generator=g)).clamp(max=1000.0)
-
-    def step():
-        acc = ohess.GroupedHessian(C, S)
-        for s in range(0, nseq, BSZ):
-            acc.add_batch(X[s:s + BSZ])
-        acc.finalize()
-
-    for _ in range(min(args.warmup, 1)):
-        step()
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        step()
-    dt = (time.perf_counter() - t0) / args.steps
-    v = 2.0 * nseq * T * C * C * G / dt / 1e12
-    sample = f"{nseq} of {HessianC1.NSEQ} sequences ({nseq * T} tokens) per step"
-    print(json.dumps({
-        "impl": "reference", "metric": "Hessian-accum TFLOP/s", "value": round(v, 4), "unit": "TFLOP/s",
-        "n_gpus": args.gpus, "steps": args.steps, "warmup": min(args.warmup, 1), "ms_per_step": round(dt * 1e3, 1),
-        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": HessianC1.name, "sample": sample},
-        "cpu_baseline": {"value": round(v, 4), "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
-                         "sample": sample},
-        "e2e": {"value": round(v, 4), "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
-
-
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu", dest="no_cpu", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -182,6 +182,7 @@ extern "C" int rq_fwht(const void* x, void* y, int dtype, int64_t rows, int n, i
     if (grid > items) grid = items;
     cudaStream_t st = as_stream(stream);
     cudaError_t e = cudaSuccess;
+    prof::Scope timed(RQ_PROF_FWHT, st);
 #define RQ_FWHT_LAUNCH(T)                                                                                       \
     e = cudaFuncSetAttribute(fwht_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);           \
     if (e != cudaSuccess) return RQ_ERR_CUDA;                                                                   \

@@ -7,7 +7,10 @@
 //             v_hi = bf16(v), v_lo = bf16(v - v_hi); also the per-channel sum of squares.
 //   2. umma:  persistent, warp-specialised GEMM over the upper-triangular 128x256 tiles of
 //             every H[g]:  D = X_hi.Y_lo^T + X_lo.Y_hi^T + X_hi.Y_hi^T  accumulated in fp32 in
-//             tensor memory, then read-modify-written into H.
+//             tensor memory over windows of 128 tokens; the epilogue warps sum the windows in
+//             registers with round-to-nearest adds (the tensor core's own accumulation truncates
+//             toward zero and would drift by ~4e-8 per MMA; measured: 5e-5 over 8192 tokens, and the
+//             same with the operand sign flipped) and read-modify-write the tile into H at the end.
 // The three-product split keeps the result within ~1e-6 relative Frobenius of an fp32 GEMM.
 #include <cuda.h>
 
@@ -22,8 +25,10 @@ using namespace rq::sm100;
 constexpr int BM = 128;          // tile rows   (channels i)   = UMMA M
 constexpr int BN = 256;          // tile cols   (channels j)   = UMMA N
 constexpr int UK = 16;           // bf16 UMMA K
-constexpr int kThreads = 192;    // warp 0: TMA producer, warp 1: MMA issuer, warps 2-5: epilogue
+constexpr int kEpilogueWarps = 8;
+constexpr int kThreads = 64 + 32 * kEpilogueWarps;   // warp 0: TMA producer, warp 1: MMA issuer, warps 2-9: epilogue
 constexpr int kTmemCols = 512;   // two 128x256 fp32 accumulators
+constexpr int kWindowTokens = 128;   // tokens accumulated on the tensor core before a round-to-nearest add
 constexpr int kPackTile = 64;    // pack kernel tile edge (tokens and channels)
 
 template <int BK, int NPROD>
@@ -148,6 +153,7 @@ umma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CU
             float* __restrict__ H, int C, int G, int MT, int NT, int kblocks, int a_plane, int b_plane0,
             float alpha, float beta, int* __restrict__ status) {
     using K = Cfg<BK, NPROD>;
+    constexpr int WIN = kWindowTokens / BK;                              // k-blocks per accumulation window
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t tiles = (raw + 1023u) & ~1023u;                       // shared-space address of stage 0
@@ -158,6 +164,7 @@ umma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CU
     const int lane = threadIdx.x & 31;
     const int tiles_per_group = (NT - 1) * NT + MT;
     const int total_tiles = tiles_per_group * G;
+    const int nwin = (kblocks + WIN - 1) / WIN;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < K::kStages; ++s) {
@@ -166,7 +173,7 @@ umma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CU
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(smem_u32(&bars->tfull[a]), 1);
-            mbar_init(smem_u32(&bars->tempty[a]), 4);
+            mbar_init(smem_u32(&bars->tempty[a]), kEpilogueWarps);
         }
         bars->abort_flag = 0;
         mbar_fence_init();
@@ -224,77 +231,111 @@ umma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CU
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0) {
             constexpr uint32_t idesc = umma_idesc_bf16_f32(BM, BN);
-            uint32_t it = 0, tile_iter = 0;
+            uint32_t it = 0, win_iter = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_iter) {
-                const uint32_t acc = tile_iter & 1u;
-                const uint32_t acc_ph = (tile_iter >> 1) & 1u;
-                if (!mbar_wait(smem_u32(&bars->tempty[acc]), acc_ph ^ 1u, abort_flag)) { ok = false; break; }
-                tc_fence_after();
-                const uint32_t d_tmem = tmem_base + acc * BN;
-                for (int kb = 0; kb < kblocks; ++kb, ++it) {
-                    const uint32_t s = it % K::kStages;
-                    const uint32_t ph = (it / K::kStages) & 1u;
-                    if (!mbar_wait(smem_u32(&bars->full[s]), ph, abort_flag)) { ok = false; break; }
+            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+                for (int w = 0; w < nwin && ok; ++w, ++win_iter) {
+                    const uint32_t acc = win_iter & 1u;
+                    const uint32_t acc_ph = (win_iter >> 1) & 1u;
+                    if (!mbar_wait(smem_u32(&bars->tempty[acc]), acc_ph ^ 1u, abort_flag)) { ok = false; break; }
                     tc_fence_after();
-                    const uint32_t a_hi = tiles + s * K::kStageBytes;
-                    const uint32_t a_lo = a_hi + K::kATile;
-                    const uint32_t b_hi = a_hi + K::kAPlanes * K::kATile;
-                    const uint32_t b_lo = b_hi + K::kBTile;
+                    const uint32_t d_tmem = tmem_base + acc * BN;
+                    const int kb_end = ((w + 1) * WIN < kblocks) ? (w + 1) * WIN : kblocks;
+                    for (int kb = w * WIN; kb < kb_end; ++kb, ++it) {
+                        const uint32_t s = it % K::kStages;
+                        const uint32_t ph = (it / K::kStages) & 1u;
+                        if (!mbar_wait(smem_u32(&bars->full[s]), ph, abort_flag)) { ok = false; break; }
+                        tc_fence_after();
+                        const uint32_t a_hi = tiles + s * K::kStageBytes;
+                        const uint32_t a_lo = a_hi + K::kATile;
+                        const uint32_t b_hi = a_hi + K::kAPlanes * K::kATile;
+                        const uint32_t b_lo = b_hi + K::kBTile;
 #pragma unroll
-                    for (int k = 0; k < BK / UK; ++k) {
-                        const uint32_t koff = k * UK * 2;               // bytes along K inside the swizzle row
-                        const uint64_t dah = umma_smem_desc(a_hi + koff, K::kSBO, K::kLayout);
-                        const uint64_t dbh = umma_smem_desc(b_hi + koff, K::kSBO, K::kLayout);
-                        const uint64_t dbl = umma_smem_desc(b_lo + koff, K::kSBO, K::kLayout);
-                        umma_bf16(d_tmem, dah, dbl, idesc, (kb | k) != 0 ? 1u : 0u);   // small terms first
-                        if (NPROD == 3) {
-                            const uint64_t dal = umma_smem_desc(a_lo + koff, K::kSBO, K::kLayout);
-                            umma_bf16(d_tmem, dal, dbh, idesc, 1u);
+                        for (int k = 0; k < BK / UK; ++k) {
+                            const uint32_t koff = k * UK * 2;           // bytes along K inside the swizzle row
+                            const uint64_t dah = umma_smem_desc(a_hi + koff, K::kSBO, K::kLayout);
+                            const uint64_t dbh = umma_smem_desc(b_hi + koff, K::kSBO, K::kLayout);
+                            const uint64_t dbl = umma_smem_desc(b_lo + koff, K::kSBO, K::kLayout);
+                            // the first MMA of a window overwrites the accumulator; small terms go first
+                            umma_bf16(d_tmem, dah, dbl, idesc, (kb != w * WIN || k != 0) ? 1u : 0u);
+                            if (NPROD == 3) {
+                                const uint64_t dal = umma_smem_desc(a_lo + koff, K::kSBO, K::kLayout);
+                                umma_bf16(d_tmem, dal, dbh, idesc, 1u);
+                            }
+                            umma_bf16(d_tmem, dah, dbh, idesc, 1u);
                         }
-                        umma_bf16(d_tmem, dah, dbh, idesc, 1u);
+                        umma_commit(smem_u32(&bars->empty[s]));        // frees the stage when these MMAs retire
                     }
-                    umma_commit(smem_u32(&bars->empty[s]));            // frees the stage when these MMAs retire
+                    if (ok) umma_commit(smem_u32(&bars->tfull[acc]));  // window complete
                 }
-                if (ok) umma_commit(smem_u32(&bars->tfull[acc]));      // accumulator complete
             }
         }
     } else {
-        // ------------------------------------------------------------ epilogue (4 warps = 128 lanes)
-        const int q = warp & 3;                                        // tensor-memory lane quadrant of this warp
-        uint32_t tile_iter = 0;
+        // ------------------------------------------------------------ epilogue: 8 warps.  Warp (2+e) reads
+        // tensor-memory lanes 32*(warp%4).. and the column half e/4 of the tile.  The tensor core's fp32
+        // accumulation truncates, which drifts over thousands of MMAs; so an accumulator only ever
+        // collects one window (kWindowTokens tokens) and the windows are summed here, in registers,
+        // with round-to-nearest adds.
+        const int q = warp & 3;
+        const int half = (warp - 2) >> 2;
+        uint32_t win_iter = 0;
         const bool vec_ok = (C & 3) == 0;
-        for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++tile_iter) {
+        bool alive = true;
+        for (int t = blockIdx.x; t < total_tiles && alive; t += gridDim.x) {
             const int g = t % G;
             int i, j;
             decode_tile(t / G, i, j);
-            const uint32_t acc = tile_iter & 1u;
-            const uint32_t acc_ph = (tile_iter >> 1) & 1u;
-            int ok = 1;
-            if (lane == 0) ok = mbar_wait(smem_u32(&bars->tfull[acc]), acc_ph, abort_flag) ? 1 : 0;
-            ok = __shfl_sync(0xffffffffu, ok, 0);
-            if (!ok) break;
-            tc_fence_after();
             const int row0 = i * BM + q * 32;
             const int row = row0 + lane;
-            float* hrow = H + ((int64_t)g * C + row) * (int64_t)C;
-#pragma unroll 1
-            for (int cb = 0; cb < BN / 32; ++cb) {
-                const int col0 = j * BN + cb * 32;
-                if (col0 >= C || col0 + 31 < row0 || row0 >= C) continue;    // warp-uniform: outside / below diagonal
-                float v[32];
-                tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + cb * 32, v);
-                if (row < C) {
+            const int colbase = j * BN + half * 128;
+            // warp-uniform activity of the four 32-column chunks: inside the matrix and not wholly below the diagonal
+            bool use[4];
+#pragma unroll
+            for (int cb = 0; cb < 4; ++cb) {
+                const int col0 = colbase + cb * 32;
+                use[cb] = !(col0 >= C || col0 + 31 < row0 || row0 >= C);
+            }
+            float run[128];
+#pragma unroll
+            for (int e = 0; e < 128; ++e) run[e] = 0.f;
+            for (int w = 0; w < nwin; ++w, ++win_iter) {
+                const uint32_t acc = win_iter & 1u;
+                const uint32_t acc_ph = (win_iter >> 1) & 1u;
+                int ok = 1;
+                if (lane == 0) ok = mbar_wait(smem_u32(&bars->tfull[acc]), acc_ph, abort_flag) ? 1 : 0;
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) { alive = false; break; }
+                tc_fence_after();
+#pragma unroll
+                for (int cb = 0; cb < 4; ++cb) {
+                    if (use[cb]) {
+                        float v[32];
+                        tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + half * 128 + cb * 32, v);
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) run[cb * 32 + e] += v[e];
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&bars->tempty[acc]));
+            }
+            if (!alive) break;
+            if (row < C) {
+                float* hrow = H + ((int64_t)g * C + row) * (int64_t)C;
+#pragma unroll
+                for (int cb = 0; cb < 4; ++cb) {
+                    const int col0 = colbase + cb * 32;
+                    if (!use[cb]) continue;
                     if (vec_ok && col0 + 32 <= C) {
                         float4* p4 = reinterpret_cast<float4*>(hrow + col0);
 #pragma unroll
                         for (int e = 0; e < 8; ++e) {
                             float4 o = (beta != 0.f) ? p4[e] : make_float4(0.f, 0.f, 0.f, 0.f);
                             if (beta != 1.f) { o.x *= beta; o.y *= beta; o.z *= beta; o.w *= beta; }
-                            o.x += alpha * v[4 * e + 0];
-                            o.y += alpha * v[4 * e + 1];
-                            o.z += alpha * v[4 * e + 2];
-                            o.w += alpha * v[4 * e + 3];
+                            o.x += alpha * run[cb * 32 + 4 * e + 0];
+                            o.y += alpha * run[cb * 32 + 4 * e + 1];
+                            o.z += alpha * run[cb * 32 + 4 * e + 2];
+                            o.w += alpha * run[cb * 32 + 4 * e + 3];
                             p4[e] = o;
                         }
                     } else {
@@ -303,15 +344,12 @@ umma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CU
                             if (col0 + e < C) {
                                 float o = (beta != 0.f) ? hrow[col0 + e] : 0.f;
                                 if (beta != 1.f) o *= beta;
-                                hrow[col0 + e] = o + alpha * v[e];
+                                hrow[col0 + e] = o + alpha * run[cb * 32 + e];
                             }
                         }
                     }
                 }
             }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&bars->tempty[acc]));
         }
     }
 

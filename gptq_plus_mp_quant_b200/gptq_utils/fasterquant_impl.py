@@ -14,6 +14,8 @@ from ..utils import quant_utils
 
 BS = 128            # column block of the kernels
 _DAMP_STEP = 0.0015
+# tests set this to keep a copy of the first-order term as it is before the block loop updates it in place
+KEEP_INTERMEDIATES = False
 
 
 # ----------------------------------------------------------------------------------------------
@@ -148,6 +150,7 @@ def _quantize_linear(layer, W32, H3, perm, grads, quantizer, G, alpha_eff, ref_l
                        _lib.lib.rq_gptqplus_terms(_lib.ptr(Gp), _lib.ptr(Hinv), R, Cc, G, float(alpha_eff),
                                                   float(ref_loss), _lib.ptr(Z), _lib.ptr(GH), _lib.ptr(beta),
                                                   _lib.ptr(hdiag), st))
+        GH_initial = GH.clone() if (plus and KEEP_INTERMEDIATES) else None
         Q = torch.empty(R, Cc, dtype=torch.float32, device=dev)
         codes = torch.empty(R, Cc, dtype=torch.int8, device=dev)
         Eeff = torch.empty(R, BS, dtype=torch.float32, device=dev)
@@ -171,7 +174,7 @@ def _quantize_linear(layer, W32, H3, perm, grads, quantizer, G, alpha_eff, ref_l
         layer.register_buffer("int_weight", out_codes.reshape(layer.weight.shape))
         layer.register_buffer("scale", out_scale)
     layer.weight.data = out
-    return {"beta": beta, "Z": Z, "GHinv": GH, "Wp": Wp, "Q": Q, "codes": codes}
+    return {"beta": beta, "Z": Z, "GHinv_initial": GH_initial}
 
 
 def _check_common(quantizer, blocksize):
@@ -251,4 +254,5 @@ def plus_fasterquant(obj, blocksize, percdamp, groupsize, actorder, static_group
     alpha_eff = obj.alpha / (obj.rows * obj.columns) if plus else 0.0
     state = _quantize_linear(layer, W32, H3, perm, grads, obj.quantizer, G, alpha_eff, obj.reference_loss, plus, Hinv,
                              mode_pack, export_to_et, permute_export=True)
-    obj._last_fasterquant = {"Hinv": Hinv, "perm": perm, "damp_percent": damp, "identity_fallback": identity, **state}
+    obj._last_fasterquant = {"Hinv": Hinv if KEEP_INTERMEDIATES else None, "perm": perm, "damp_percent": damp,
+                             "identity_fallback": identity, **state}

@@ -41,6 +41,9 @@ class GPTQPlus:
         self.token_count = 0
         self._finalized = False
         self.profile_recorder = None
+        # Rank that runs fasterquant for this linear when the linears of a layer are spread over the
+        # ranks; None keeps the reference behaviour (every rank receives the summed Hessian).
+        self.hessian_owner = None
         assert self.rows % self.num_groups == 0, (
             f"Number of rows ({self.rows}) must be divisible by num_groups ({self.num_groups})")
 
@@ -88,7 +91,10 @@ class GPTQPlus:
         (gptq_plus_utils.py:859-908)."""
         if self._finalized:
             return
-        dist_utils.allreduce_sum_(self._H)
+        if self.hessian_owner is None:
+            dist_utils.allreduce_sum_(self._H)
+        else:
+            dist_utils.reduce_sum_(self._H, self.hessian_owner)
         dist_utils.allreduce_sum_(self.act_square)
         total_samples = dist_utils.allreduce_sum_scalar(self.index)
         total_tokens = dist_utils.allreduce_sum_scalar(self.token_count)

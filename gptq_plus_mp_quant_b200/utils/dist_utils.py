@@ -46,6 +46,13 @@ def allreduce_sum_(tensor: torch.Tensor) -> torch.Tensor:
     return tensor
 
 
+def reduce_sum_(tensor: torch.Tensor, dst: int) -> torch.Tensor:
+    """In-place SUM reduce to rank ``dst`` only (the other ranks' buffers are left unspecified)."""
+    if get_world_size() > 1:
+        dist.reduce(tensor, dst=dst, op=dist.ReduceOp.SUM)
+    return tensor
+
+
 def allreduce_sum_scalar(scalar) -> float:
     """Sum of a Python scalar over ranks in fp64 (dist_utils.py:142-149)."""
     if get_world_size() <= 1:
