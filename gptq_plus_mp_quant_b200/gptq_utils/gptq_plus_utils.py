@@ -135,6 +135,7 @@ class GPTQPlus:
             raise ValueError("NaN in weights")
 
     def free(self):
+        # Drops the Hessian; unlike the reference this does not return cached blocks to the driver
+        # (torch.cuda.empty_cache / cleanup_memory): the next linear re-uses them without a cudaMalloc.
         self.H = None
         self.Losses = None
-        torch.cuda.empty_cache()

@@ -1,0 +1,84 @@
+"""Host-side data-parallel logic on CPU with the gloo backend, world size 2: contiguous sharding of
+the calibration sequences, summation of the un-normalised partial Hessian state over ranks (the
+exchange step of finalize_hessian), reduce-to-owner, the cross-rank bit-exactness assertion and the
+assignment of linears to ranks."""
+import os
+import sys
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _worker(rank, world, port, results):
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests", "golden"))
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        import cases
+        from oracle import hessian as ohess
+        from gptq_plus_mp_quant_b200.utils import dist_utils as du
+        torch.set_num_threads(1)
+        nseq, seqlen, C, G = 4, 64, 96, 2
+        X = cases.make_acts(nseq, seqlen, C, seed=7)
+        S = cases.make_saliency(nseq, seqlen, G, seed=7)
+        sl = du.shard_slice(nseq)
+        assert (sl.start, sl.stop) == (rank * 2, rank * 2 + 2)
+        assert du.shard_size(nseq) == 2
+        with pytest.raises(ValueError):
+            du.shard_slice(5)
+        part = ohess.GroupedHessian(C, S[sl])
+        part.add_batch(X[sl])
+        # exchange step exactly as finalize_hessian performs it
+        du.allreduce_sum_(part.H)
+        du.allreduce_sum_(part.act_square)
+        part.index = int(du.allreduce_sum_scalar(part.index))
+        part.token_count = int(du.allreduce_sum_scalar(part.token_count))
+        part.finalize()
+        whole = ohess.GroupedHessian(C, S)
+        whole.add_batch(X)
+        whole.finalize()
+        rel = float((part.H - whole.H).norm() / whole.H.norm())
+        assert rel < 1e-6, rel
+        assert torch.allclose(part.act_square, whole.act_square, rtol=1e-5)
+        du.assert_bit_exact(part.H, "H after all-reduce")            # every rank holds the same bits
+        bad = part.H.clone()
+        if rank == 1:
+            bad[0, 0, 0] += 1.0
+            with pytest.raises(RuntimeError):
+                du.assert_bit_exact(bad, "perturbed")
+        else:
+            du.assert_bit_exact(bad, "perturbed")                    # rank 0 is the reference copy
+        # reduce-to-owner: only the owner needs the sum
+        t = torch.full((8,), float(rank + 1))
+        du.reduce_sum_(t, 1)
+        if rank == 1:
+            assert torch.equal(t, torch.full((8,), 3.0))
+        results[rank] = "ok"
+    finally:
+        dist.destroy_process_group()
+
+
+def test_world2_sharded_hessian_and_helpers():
+    world = 2
+    port = 29500 + (os.getpid() % 2000)
+    mgr = mp.Manager()
+    results = mgr.dict()
+    mp.spawn(_worker, args=(world, port, results), nprocs=world, join=True)
+    assert dict(results) == {0: "ok", 1: "ok"}
+
+
+def test_owner_assignment_balances_cost():
+    sys.path.insert(0, ROOT)
+    import bench
+    costs = {"a": 10.0, "b": 9.0, "c": 2.0, "d": 1.0, "e": 1.0}
+    own = bench.assign_owners(costs, 2)
+    load = [sum(c for n, c in costs.items() if own[n] == r) for r in range(2)]
+    assert set(own.values()) == {0, 1}
+    assert abs(load[0] - load[1]) <= 2.0
+    assert bench.assign_owners(costs, 1) == {k: 0 for k in costs}
