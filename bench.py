@@ -93,6 +93,37 @@ class ClockSampler:
         return {"sm_mhz": med, "sm_max_mhz": smax, "reasons": sorted(reasons), "samples": len(sm)}
 
 
+class EventRecorder:
+    """Stand-in for the reference's QuantProfileRecorder: `section(name)` brackets a stage with CUDA events
+    on the current stream; `summary()` returns milliseconds per section name."""
+
+    def __init__(self):
+        self.spans = []
+
+    class _Span:
+        def __init__(self, owner, name):
+            self.owner, self.name = owner, name
+
+        def __enter__(self):
+            self.a = torch.cuda.Event(enable_timing=True)
+            self.b = torch.cuda.Event(enable_timing=True)
+            self.a.record()
+
+        def __exit__(self, *exc):
+            self.b.record()
+            self.owner.spans.append((self.name, self.a, self.b))
+
+    def section(self, name):
+        return EventRecorder._Span(self, name)
+
+    def summary(self):
+        torch.cuda.synchronize()
+        out = {}
+        for name, a, b in self.spans:
+            out[name] = out.get(name, 0.0) + a.elapsed_time(b)
+        return out
+
+
 def dist_setup():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -167,6 +198,7 @@ class LayerWorkload:
             self.grad[name] = torch.randn(R, C, generator=gw, device=dev) * 1e-4
         costs = {name: (2.0 / 3.0) * C ** 3 * self.G + 5.0 * R * C * C for name, R, C, _ in self.LINEARS}
         self.owner = assign_owners(costs, world)
+        self.recorder = None
 
     # ---- algorithmic work figures
     def hessian_flops(self, local=False):
@@ -188,6 +220,7 @@ class LayerWorkload:
             o = GPTQPlus(self.layers[name], self.sal[name], self.grad[name], self.G, 0.25, 0.7)
             o.quantizer = WeightQuantizer()
             o.quantizer.configure(4, perchannel=True, sym=True, mse=False)
+            o.profile_recorder = self.recorder
             objs[name] = o
         for s in range(0, self.nseq_local, self.BSZ):
             batch = {}
@@ -341,6 +374,10 @@ def run_ours(args):
              ("chol", _lib.PROF_CHOL), ("block", _lib.PROF_BLOCK), ("lazy", _lib.PROF_LAZY))}
     _lib.profile_enable(False)
     clocks = sampler.stop()
+    wl.recorder = EventRecorder()                      # one extra, untimed step for the host-level stage breakdown
+    wl.step_device()
+    sections = {k: round(v, 2) for k, v in sorted(wl.recorder.summary().items(), key=lambda kv: -kv[1])}
+    wl.recorder = None
     wl.step_e2e()
     e2e_ms = timed(wl.step_e2e, args.steps)
 
@@ -368,6 +405,7 @@ def run_ours(args):
                      "note": "algorithmic 2*N*C^2*G; the kernel issues 2 bf16 products on the ~53% of tiles that "
                              "touch the upper triangle"},
         "stage_ms_per_step": {k: round(v[0] / args.steps, 2) for k, v in prof.items()},
+        "section_ms": sections,
         "fwht_gbs": round(wl.fwht_bytes_local() * args.steps / (fwht_ms * 1e-3) / 1e9, 1) if fwht_ms else None,
         "e2e": {"value": round(e2e_ms / args.steps / 1e3, 4), "unit": "s", "h2d_bytes_per_step": wl.h2d_bytes(),
                 "d2h_bytes_per_step": 4},

@@ -6,11 +6,20 @@ from __future__ import annotations
 
 import ctypes
 import logging
+from contextlib import nullcontext
 
 import torch
 
 from .. import _lib, ops
 from ..utils import quant_utils
+
+_NULL = nullcontext()
+
+
+def _sec(rec, name):
+    """Section of the caller's profile recorder (the reference's QuantProfileRecorder.section names)."""
+    return rec.section(name) if rec is not None else _NULL
+
 
 BS = 128            # column block of the kernels
 _DAMP_STEP = 0.0015
@@ -129,7 +138,7 @@ def _scale_setup(quantizer, W32, groupsize, static_groups, blocksize, perm, dead
 # the shared driver
 # ----------------------------------------------------------------------------------------------
 def _quantize_linear(layer, W32, H3, perm, grads, quantizer, G, alpha_eff, ref_loss, plus, Hinv, mode_pack,
-                     export_to_et, permute_export):
+                     export_to_et, permute_export, rec=None):
     dev = W32.device
     R, Cc = W32.shape
     mode, scale_row, scale_tab, colgrp, scale_blk, dyn_gs = mode_pack
@@ -138,38 +147,42 @@ def _quantize_linear(layer, W32, H3, perm, grads, quantizer, G, alpha_eff, ref_l
     Wp = torch.empty(R, Cc, dtype=torch.float32, device=dev)
     Gp = torch.empty(R, Cc, dtype=torch.float32, device=dev) if plus else None
     with torch.cuda.device(dev):
-        _lib.check("rq_fq_prepare", _lib.lib.rq_fq_prepare(_lib.ptr(W32), _lib.ptr(grads), _lib.ptr(H3), _lib.ptr(perm),
-                                                           R, Cc, G, _lib.ptr(Wp), _lib.ptr(Gp), st))
+        with _sec(rec, "fasterquant.subgroup.slice_inputs"):
+            _lib.check("rq_fq_prepare", _lib.lib.rq_fq_prepare(_lib.ptr(W32), _lib.ptr(grads), _lib.ptr(H3),
+                                                               _lib.ptr(perm), R, Cc, G, _lib.ptr(Wp), _lib.ptr(Gp), st))
         Z = GH = beta = None
         if plus:
             Z = torch.empty(R, Cc, dtype=torch.float32, device=dev)
             GH = torch.empty(R, Cc, dtype=torch.float32, device=dev)
             beta = torch.empty(R, dtype=torch.float32, device=dev)
             hdiag = torch.empty(G, Cc, dtype=torch.float32, device=dev)
-            _lib.check("rq_gptqplus_terms",
-                       _lib.lib.rq_gptqplus_terms(_lib.ptr(Gp), _lib.ptr(Hinv), R, Cc, G, float(alpha_eff),
-                                                  float(ref_loss), _lib.ptr(Z), _lib.ptr(GH), _lib.ptr(beta),
-                                                  _lib.ptr(hdiag), st))
+            with _sec(rec, "fasterquant.subgroup.init_ghinv"):
+                _lib.check("rq_gptqplus_terms",
+                           _lib.lib.rq_gptqplus_terms(_lib.ptr(Gp), _lib.ptr(Hinv), R, Cc, G, float(alpha_eff),
+                                                      float(ref_loss), _lib.ptr(Z), _lib.ptr(GH), _lib.ptr(beta),
+                                                      _lib.ptr(hdiag), st))
         GH_initial = GH.clone() if (plus and KEEP_INTERMEDIATES) else None
         Q = torch.empty(R, Cc, dtype=torch.float32, device=dev)
         codes = torch.empty(R, Cc, dtype=torch.int8, device=dev)
         Eeff = torch.empty(R, BS, dtype=torch.float32, device=dev)
-        _lib.check("rq_fq_run",
-                   _lib.lib.rq_fq_run(_lib.ptr(Wp), _lib.ptr(GH), _lib.ptr(Z), _lib.ptr(Hinv), _lib.ptr(Q),
-                                      _lib.ptr(codes), _lib.ptr(Eeff), _lib.ptr(scale_row), _lib.ptr(scale_tab),
-                                      _lib.ptr(colgrp), _lib.ptr(scale_blk), R, Cc, G, mode, dyn_gs,
-                                      1 if quantizer.sym else 0, maxq, 1 if plus else 0, st))
+        with _sec(rec, "fasterquant.block.total"):
+            _lib.check("rq_fq_run",
+                       _lib.lib.rq_fq_run(_lib.ptr(Wp), _lib.ptr(GH), _lib.ptr(Z), _lib.ptr(Hinv), _lib.ptr(Q),
+                                          _lib.ptr(codes), _lib.ptr(Eeff), _lib.ptr(scale_row), _lib.ptr(scale_tab),
+                                          _lib.ptr(colgrp), _lib.ptr(scale_blk), R, Cc, G, mode, dyn_gs,
+                                          1 if quantizer.sym else 0, maxq, 1 if plus else 0, st))
         out = torch.empty(layer.weight.shape, dtype=layer.weight.dtype, device=dev)
         out_codes = out_scale = None
         if export_to_et:
             out_codes = torch.empty(R, Cc, dtype=torch.float32, device=dev)
             out_scale = torch.empty(R, Cc, dtype=torch.float32, device=dev)
         tab = scale_tab if mode == 1 else scale_blk
-        _lib.check("rq_fq_finish",
-                   _lib.lib.rq_fq_finish(_lib.ptr(Q), _lib.ptr(codes), _lib.ptr(perm), R, Cc, _lib.ptr(out),
-                                         _lib.dtype_code(out), _lib.ptr(out_codes), _lib.ptr(out_scale),
-                                         _lib.ptr(scale_row), _lib.ptr(tab), _lib.ptr(colgrp),
-                                         1 if permute_export else 0, st))
+        with _sec(rec, "fasterquant.write_layer_weight"):
+            _lib.check("rq_fq_finish",
+                       _lib.lib.rq_fq_finish(_lib.ptr(Q), _lib.ptr(codes), _lib.ptr(perm), R, Cc, _lib.ptr(out),
+                                             _lib.dtype_code(out), _lib.ptr(out_codes), _lib.ptr(out_scale),
+                                             _lib.ptr(scale_row), _lib.ptr(tab), _lib.ptr(colgrp),
+                                             1 if permute_export else 0, st))
     if export_to_et:
         layer.register_buffer("int_weight", out_codes.reshape(layer.weight.shape))
         layer.register_buffer("scale", out_scale)
@@ -234,11 +247,14 @@ def plus_fasterquant(obj, blocksize, percdamp, groupsize, actorder, static_group
     if diagnostic_recorder is not None:
         raise NotImplementedError("the tensor-dump recorder needs the per-column intermediates of the PyTorch path")
     layer, dev = obj.layer, obj.dev
-    W32 = layer.weight.data.float().contiguous()
+    rec = profile_recorder
+    with _sec(rec, "fasterquant.allocate_outputs"):
+        W32 = layer.weight.data.float().contiguous()
     R, Cc = W32.shape
     G = obj.num_groups
-    if not obj.quantizer.ready():
-        obj.quantizer.find_params(W32)
+    with _sec(rec, "fasterquant.quantizer_find_params_initial"):
+        if not obj.quantizer.ready():
+            obj.quantizer.find_params(W32)
     _check_common(obj.quantizer, blocksize)
     dynamic_groups = groupsize != -1 and not static_groups
     if dynamic_groups and groupsize != blocksize:
@@ -246,13 +262,16 @@ def plus_fasterquant(obj, blocksize, percdamp, groupsize, actorder, static_group
                          f"Got groupsize={groupsize}, blocksize={blocksize}.")
     ops.check_status(dev)
     H3 = obj.H
-    perm = torch.argsort(obj.act_square, descending=True) if actorder else None
-    mode_pack = _scale_setup(obj.quantizer, W32, groupsize, static_groups, blocksize, perm, None)
-    Hinv, damp, identity = hinv_with_fallback(H3, perm, percdamp, identity_fallback=True)
+    with _sec(rec, "fasterquant.subgroup.actorder_permute"):
+        perm = torch.argsort(obj.act_square, descending=True) if actorder else None
+    with _sec(rec, "fasterquant.quantizer_build_groups"):
+        mode_pack = _scale_setup(obj.quantizer, W32, groupsize, static_groups, blocksize, perm, None)
+    with _sec(rec, "fasterquant.subgroup.compute_hinv"):
+        Hinv, damp, identity = hinv_with_fallback(H3, perm, percdamp, identity_fallback=True)
     plus = bool(enable_gradient_update and obj.alpha > 0)
     grads = obj.gradients.to(dev).float().contiguous() if plus else None
     alpha_eff = obj.alpha / (obj.rows * obj.columns) if plus else 0.0
     state = _quantize_linear(layer, W32, H3, perm, grads, obj.quantizer, G, alpha_eff, obj.reference_loss, plus, Hinv,
-                             mode_pack, export_to_et, permute_export=True)
+                             mode_pack, export_to_et, permute_export=True, rec=rec)
     obj._last_fasterquant = {"Hinv": Hinv if KEEP_INTERMEDIATES else None, "perm": perm, "damp_percent": damp,
                              "identity_fallback": identity, **state}
