@@ -14,7 +14,7 @@ import torch
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "csrc", "librealq_b200.so")
 
-RQ_OK, RQ_ERR_INVALID, RQ_ERR_CUDA, RQ_ERR_TIMEOUT, RQ_ERR_WORKSPACE, RQ_ERR_UNSUPPORTED = range(6)
+RQ_OK, RQ_ERR_INVALID, RQ_ERR_CUDA, RQ_ERR_TIMEOUT, RQ_ERR_WORKSPACE, RQ_ERR_UNSUPPORTED, RQ_ERR_TOO_LARGE = range(7)
 RQ_F32, RQ_BF16, RQ_F16 = 0, 1, 2
 _DTYPES = {torch.float32: RQ_F32, torch.bfloat16: RQ_BF16, torch.float16: RQ_F16}
 
@@ -28,6 +28,8 @@ SIGNATURES = {
     "rq_profile_read": (_i, [_i, C.POINTER(C.c_double), C.POINTER(C.c_longlong)]),
     "rq_hessian_workspace_bytes": (_sz, [_i64, _i, _i, _i]),
     "rq_hessian_accum": (_i, [_vp, _i, _i64, _vp, _vp, _vp, _i64, _i, _i, _f, _f, _vp, _sz, _vp, _i, _vp]),
+    "rq_hessian_noalloc_scratch_bytes": (_sz, []),
+    "rq_hessian_accum_noalloc": (_i, [_vp, _i, _i64, _vp, _vp, _vp, _i64, _i, _i, _f, _f, _vp, _vp]),
     "rq_hessian_finalize": (_i, [_vp, _vp, _i, _i, _f, _f, _f, _i, _vp, _vp]),
     "rq_fwht": (_i, [_vp, _vp, _i, _i64, _i, _i, _vp, _f, _vp]),
     "rq_find_params": (_i, [_vp, _i64, _i64, _i64, _i, _i, _i, _i, _i, _f, _i, _f, _vp, _vp, _vp]),

@@ -11,6 +11,7 @@ extern "C" const char* rq_error_string(int code) {
         case RQ_ERR_TIMEOUT: return "a bounded device-side wait ran out";
         case RQ_ERR_WORKSPACE: return "workspace too small";
         case RQ_ERR_UNSUPPORTED: return "configuration not supported by this build";
+        case RQ_ERR_TOO_LARGE: return "problem exceeds the fixed 64 MiB scratch of the allocation-free entry point";
         default: return "unknown status";
     }
 }

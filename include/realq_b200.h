@@ -26,6 +26,7 @@ extern "C" {
 #define RQ_ERR_TIMEOUT 3     /* a bounded device-side wait ran out (written to `status`)   */
 #define RQ_ERR_WORKSPACE 4   /* caller-provided scratch too small                          */
 #define RQ_ERR_UNSUPPORTED 5 /* configuration not implemented by this build                */
+#define RQ_ERR_TOO_LARGE 6   /* problem exceeds the fixed scratch of an allocation-free entry point */
 
 /* element types of activations / weights crossing the boundary */
 #define RQ_F32 0
@@ -72,6 +73,23 @@ size_t rq_hessian_workspace_bytes(int64_t chunk_tokens, int C, int G, int has_sa
 int rq_hessian_accum(const void* x, int x_dtype, int64_t ldx, const float* sal, float* H, float* act_sq,
                      int64_t N, int C, int G, float alpha, float beta, void* workspace, size_t workspace_bytes,
                      int* status, int variant, void* stream);
+
+/* Allocation-free variant of rq_hessian_accum.  It has no counterpart in the reference; it exists
+ * for hosts that must not allocate device memory where they feed calibration batches (a hook that
+ * runs while the framework's memory pool is frozen, a process whose device-memory budget belongs to
+ * another component, a caller with no allocator to borrow scratch from).  Same arguments and result
+ * as rq_hessian_accum minus workspace and variant: the bf16 operand planes are packed into a fixed
+ * rq_hessian_noalloc_scratch_bytes() = 64 MiB array inside the library's device image (every GPU that
+ * loads the library holds it until the process exits), tokens being processed in as many chunks as
+ * that takes.  Limit: one 64-token chunk must fit, i.e. roughly C * (2 + 2G) <= 520 000 (C = 28672
+ * with G = 4 fits); wider problems return RQ_ERR_TOO_LARGE.  The function calls no cudaMalloc /
+ * cudaFree or other allocating routine.  Its first call on a device looks up the array's address
+ * on that device (with that device current); make that first call outside any stream capture.
+ * All calls share the one array: calls that overlap on the same GPU (two streams, two threads)
+ * race and must be serialised by the caller.  Nothing needs clearing between calls. */
+size_t rq_hessian_noalloc_scratch_bytes(void);
+int rq_hessian_accum_noalloc(const void* x, int x_dtype, int64_t ldx, const float* sal, float* H, float* act_sq,
+                             int64_t N, int C, int G, float alpha, float beta, int* status, void* stream);
 
 /* Replaces GPTQPlus.finalize_hessian after its all-reduce (gptq_utils/gptq_plus_utils.py:881-907):
  *   H /= div_tokens; H /= div_scale (skipped when 1); act_sq /= div_seq;
