@@ -18,7 +18,6 @@ namespace chol {
 
 constexpr int NB = 128;                       // block-column width = GEMM tile edge
 constexpr int kDiagThreads = 512;
-constexpr int kDiagLd = NB + 1;               // fp64 row stride in shared memory (bank spread)
 
 // ------------------------------------------------------------------------------------------
 // mean of the dead-fixed diagonal per group (one block per group)
@@ -73,64 +72,141 @@ __global__ void __launch_bounds__(256) gather_kernel(const float* __restrict__ H
 
 // ------------------------------------------------------------------------------------------
 // Diagonal block k: A_kk = R_kk R_kk^T (R upper) and U_kk = R_kk^-1, both in fp64, stored fp32.
-// One CTA per group.
+// One CTA of 512 threads per group.  The 128x128 block is spread over the registers of the CTA:
+// thread (ty, tx) = (tid / 32, tid % 32) owns rows ty + 16a (a < 8) and columns tx + 32b (b < 4).
+// Every elimination step publishes one column (factorisation) or one row (inverse) through shared
+// memory; all updates are register FMAs.
 // ------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(kDiagThreads) diag_block_kernel(float* __restrict__ A, float* __restrict__ U, int Cp,
                                                                   int kblk, int* __restrict__ info) {
-    extern __shared__ double S[];                         // [NB][kDiagLd]; upper: R, strict lower: inv^T
-    __shared__ double dinv[NB];
+    __shared__ double vec[2][NB];          // published column / row, double-buffered by step parity
+    __shared__ double pivot[2];
+    __shared__ double dinv[NB];            // 1 / R[c][c]
+    __shared__ double part[16][NB];        // inverse: partial sums per ty
     __shared__ int bad;
     const int g = blockIdx.x;
     const int64_t origin = ((int64_t)g * Cp + (int64_t)kblk * NB) * Cp + (int64_t)kblk * NB;
     float* Ab = A + origin;
     float* Ub = U + origin;
     const int tid = threadIdx.x;
+    const int ty = tid >> 5, tx = tid & 31;
     if (tid == 0) bad = 0;
-    for (int e = tid; e < NB * NB; e += kDiagThreads) {
-        const int i = e / NB, j = e % NB;
-        S[i * kDiagLd + j] = (j >= i) ? (double)Ab[(int64_t)i * Cp + j] : 0.0;
-    }
+
+    double v[8][4];
+#pragma unroll
+    for (int a = 0; a < 8; ++a)
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+            const int i = ty + 16 * a, j = tx + 32 * b;
+            v[a][b] = (j >= i) ? (double)Ab[(int64_t)i * Cp + j] : 0.0;
+        }
     __syncthreads();
-    // reverse Cholesky: eliminate columns from the last to the first
+
+    // ---- reverse Cholesky: eliminate columns from the last to the first
     for (int c = NB - 1; c >= 0; --c) {
-        const double p = S[c * kDiagLd + c];
-        if (!(p > 0.0) && tid == 0) bad = 1;              // catches <= 0 and NaN
+        const int par = c & 1;
+#pragma unroll
+        for (int a = 0; a < 8; ++a)
+#pragma unroll
+            for (int b = 0; b < 4; ++b)
+                if (ty + 16 * a == c && tx + 32 * b == c) pivot[par] = v[a][b];
+        __syncthreads();
+        const double p = pivot[par];
+        if (!(p > 0.0) && tid == 0) bad = 1;               // catches <= 0 and NaN
         const double r = sqrt(p);
         const double rinv = 1.0 / r;
-        __syncthreads();                                  // everyone has read the pivot
-        if (tid < c) S[tid * kDiagLd + c] *= rinv;
-        else if (tid == c) S[c * kDiagLd + c] = r;
-        __syncthreads();
-        const int cc = c * c;
-        for (int e = tid; e < cc; e += kDiagThreads) {
-            const int i = e / c, j = e - i * c;
-            if (j >= i) S[i * kDiagLd + j] -= S[i * kDiagLd + c] * S[j * kDiagLd + c];
+        if (tid == 0) dinv[c] = rinv;
+        if (tx == (c & 31)) {                                // owners of column c
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+                if (tx + 32 * b == c) {
+#pragma unroll
+                    for (int a = 0; a < 8; ++a) {
+                        const int i = ty + 16 * a;
+                        if (i < c) {
+                            v[a][b] *= rinv;
+                            vec[par][i] = v[a][b];
+                        } else if (i == c) {
+                            v[a][b] = r;
+                        }
+                    }
+                }
+            }
         }
         __syncthreads();
-    }
-    // inverse of the upper-triangular R: column j of the inverse lives in row j of the strict lower part
-    if (tid < NB) dinv[tid] = 1.0 / S[tid * kDiagLd + tid];
-    __syncthreads();
-    for (int i = NB - 2; i >= 0; --i) {
-        if (tid < NB && tid > i) {
-            const int j = tid;
-            // x_j[i] = -( sum_{l=i+1..j} R[i][l] * x_j[l] ) / R[i][i],  x_j[j] = dinv[j]
-            double s = S[i * kDiagLd + j] * dinv[j];
-            for (int l = i + 1; l < j; ++l) s += S[i * kDiagLd + l] * S[j * kDiagLd + l];
-            S[j * kDiagLd + i] = -s * dinv[i];
-        }                                                 // a thread only re-reads its own row: no barrier needed
-    }
-    __syncthreads();
-    for (int e = tid; e < NB * NB; e += kDiagThreads) {
-        const int i = e / NB, j = e % NB;
-        float rv = 0.f, uv = 0.f;
-        if (j >= i) {
-            rv = (float)S[i * kDiagLd + j];
-            uv = (j == i) ? (float)dinv[i] : (float)S[j * kDiagLd + i];
+#pragma unroll
+        for (int a = 0; a < 8; ++a) {
+            const int i = ty + 16 * a;
+            if (i < c) {
+                const double ci = vec[par][i];
+#pragma unroll
+                for (int b = 0; b < 4; ++b) {
+                    const int j = tx + 32 * b;
+                    if (j >= i && j < c) v[a][b] -= ci * vec[par][j];
+                }
+            }
         }
-        Ab[(int64_t)i * Cp + j] = rv;
-        Ub[(int64_t)i * Cp + j] = uv;
     }
+    __syncthreads();
+
+    // ---- U = R^-1, rows from the last to the first:
+    //      U[c][c] = 1/R[c][c];  U[c][j] = -(1/R[c][c]) * sum_{l=c+1..j} R[c][l] * U[l][j]
+    double u[8][4];
+#pragma unroll
+    for (int a = 0; a < 8; ++a)
+#pragma unroll
+        for (int b = 0; b < 4; ++b) u[a][b] = 0.0;
+    for (int c = NB - 1; c >= 0; --c) {
+        const int par = c & 1;
+        if (ty == (c & 15)) {                                // owners of row c publish R[c][:]
+#pragma unroll
+            for (int a = 0; a < 8; ++a)
+                if (ty + 16 * a == c) {
+#pragma unroll
+                    for (int b = 0; b < 4; ++b) vec[par][tx + 32 * b] = v[a][b];
+                }
+        }
+        __syncthreads();
+        double ps[4] = {0.0, 0.0, 0.0, 0.0};
+#pragma unroll
+        for (int a = 0; a < 8; ++a) {
+            const int l = ty + 16 * a;
+            if (l > c) {
+                const double rl = vec[par][l];
+#pragma unroll
+                for (int b = 0; b < 4; ++b) ps[b] += rl * u[a][b];     // u[l][j] is zero for l > j
+            }
+        }
+#pragma unroll
+        for (int b = 0; b < 4; ++b) part[ty][tx + 32 * b] = ps[b];
+        __syncthreads();
+        if (ty == (c & 15)) {
+            const double dc = dinv[c];
+#pragma unroll
+            for (int a = 0; a < 8; ++a)
+                if (ty + 16 * a == c) {
+#pragma unroll
+                    for (int b = 0; b < 4; ++b) {
+                        const int j = tx + 32 * b;
+                        double sum = 0.0;
+#pragma unroll
+                        for (int t = 0; t < 16; ++t) sum += part[t][j];
+                        u[a][b] = (j > c) ? -dc * sum : (j == c ? dc : 0.0);
+                    }
+                }
+        }
+        // the next step publishes into the other buffer and rewrites `part` only after its own barrier
+    }
+    __syncthreads();
+
+#pragma unroll
+    for (int a = 0; a < 8; ++a)
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+            const int i = ty + 16 * a, j = tx + 32 * b;
+            Ab[(int64_t)i * Cp + j] = (j >= i) ? (float)v[a][b] : 0.f;
+            Ub[(int64_t)i * Cp + j] = (j >= i) ? (float)u[a][b] : 0.f;
+        }
     if (tid == 0 && bad) atomicCAS(&info[g], 0, kblk + 1);
 }
 
@@ -138,7 +214,7 @@ __global__ void __launch_bounds__(kDiagThreads) diag_block_kernel(float* __restr
 // GEMM-shaped steps (one 128x128 tile per CTA, grid.z = group)
 // ------------------------------------------------------------------------------------------
 // panel: A[i-block][k] <- A[i-block][k] . U_kk^T   for i < k      grid (k, 1, G)
-__global__ void __launch_bounds__(gemm::kThreads) panel_kernel(float* __restrict__ A, const float* __restrict__ U,
+__global__ void __launch_bounds__(gemm::kThreads, 2) panel_kernel(float* __restrict__ A, const float* __restrict__ U,
                                                                int Cp, int kblk) {
     extern __shared__ float smem[];
     const int64_t gofs = (int64_t)blockIdx.z * Cp * Cp;
@@ -154,7 +230,7 @@ __global__ void __launch_bounds__(gemm::kThreads) panel_kernel(float* __restrict
 }
 
 // trailing: A[i][j] -= R[i][k] . R[j][k]^T   for i <= j < k      grid (k(k+1)/2, 1, G)
-__global__ void __launch_bounds__(gemm::kThreads) trailing_kernel(float* __restrict__ A, int Cp, int kblk) {
+__global__ void __launch_bounds__(gemm::kThreads, 2) trailing_kernel(float* __restrict__ A, int Cp, int kblk) {
     extern __shared__ float smem[];
     int bi, bj;
     {
@@ -181,7 +257,7 @@ __global__ void __launch_bounds__(gemm::kThreads) trailing_kernel(float* __restr
 //   step 1: T[a, b] = U[a, a] . R[a, b]          (U[a,a] upper: k starts at the row block)
 //   step 2: U[a, b] = - T[a, b] . U[b, b]        (U[b,b] upper: k ends with the column block)
 // grid (tiles_m * tiles_n, pairs, G)
-__global__ void __launch_bounds__(gemm::kThreads) inv_level_kernel(const float* __restrict__ R, float* __restrict__ U,
+__global__ void __launch_bounds__(gemm::kThreads, 2) inv_level_kernel(const float* __restrict__ R, float* __restrict__ U,
                                                                    float* __restrict__ T, int Cp, int s, int step) {
     extern __shared__ float smem[];
     const int m = blockIdx.y;
@@ -265,12 +341,9 @@ extern "C" int rq_chol_hinv(const float* H, const int64_t* perm, const float* da
     int rc = check_launch();
     if (rc != RQ_OK) return rc;
 
-    const size_t diag_smem = (size_t)NB * kDiagLd * sizeof(double);
-    if (cudaFuncSetAttribute(diag_block_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)diag_smem) != cudaSuccess)
-        return RQ_ERR_CUDA;
     // phase 1: block columns from the last to the first
     for (int k = nblk - 1; k >= 0; --k) {
-        diag_block_kernel<<<G, kDiagThreads, diag_smem, st>>>(A, Hinv, Cp, k, info);
+        diag_block_kernel<<<G, kDiagThreads, 0, st>>>(A, Hinv, Cp, k, info);
         if (k > 0) {
             panel_kernel<<<dim3((unsigned)k, 1, (unsigned)G), gemm::kThreads, gemm::kSmemBytes, st>>>(A, Hinv, Cp, k);
             trailing_kernel<<<dim3((unsigned)(k * (k + 1) / 2), 1, (unsigned)G), gemm::kThreads, gemm::kSmemBytes, st>>>(

@@ -40,7 +40,7 @@ __global__ void __launch_bounds__(256) prep_kernel(const float* __restrict__ W, 
 // ------------------------------------------------------------------------------------------
 // T = Gp . U^T  (step 1, U upper: k starts at the column tile)   GHI = T . U  (step 2: k ends with it)
 // grid (tiles_m, tiles_n, G)
-__global__ void __launch_bounds__(gemm::kThreads) terms_gemm_kernel(const float* __restrict__ In,
+__global__ void __launch_bounds__(gemm::kThreads, 2) terms_gemm_kernel(const float* __restrict__ In,
                                                                     const float* __restrict__ U,
                                                                     float* __restrict__ Out, int Rg, int C, int Cp,
                                                                     int step) {
@@ -279,7 +279,7 @@ __global__ void __launch_bounds__(kBlockThreads) block_kernel(const BlockArgs p)
 // lazy update for the columns right of the block:  grid (tiles_m, tiles_n, G)
 //   step 1:  W[:, i2:]  -= Eeff . Hinv[i1:i2, i2:]  +  count * GH[:, i2:]     (the latter when PLUS)
 //   step 2:  GH[:, i2:] -= Z[:, i1:i2] . Hinv[i1:i2, i2:]                      (PLUS only)
-__global__ void __launch_bounds__(gemm::kThreads) lazy_kernel(float* __restrict__ Wp, float* __restrict__ GH,
+__global__ void __launch_bounds__(gemm::kThreads, 2) lazy_kernel(float* __restrict__ Wp, float* __restrict__ GH,
                                                               const float* __restrict__ Z,
                                                               const float* __restrict__ Eeff,
                                                               const float* __restrict__ Hinv, int R, int C, int Cp,
