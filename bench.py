@@ -371,7 +371,9 @@ def run_ours(args):
     total_ms = timed(wl.step_device, args.steps)
     prof = {name: _lib.profile_read(tag) for name, tag in
             (("umma", _lib.PROF_HESSIAN_UMMA), ("pack", _lib.PROF_HESSIAN_PACK), ("fwht", _lib.PROF_FWHT),
-             ("chol", _lib.PROF_CHOL), ("block", _lib.PROF_BLOCK), ("lazy", _lib.PROF_LAZY))}
+             ("chol", _lib.PROF_CHOL), ("chol_diag", _lib.PROF_CHOL_DIAG), ("chol_panel", _lib.PROF_CHOL_PANEL),
+             ("chol_trailing", _lib.PROF_CHOL_TRAILING), ("chol_inverse", _lib.PROF_CHOL_INVERSE),
+             ("terms", _lib.PROF_TERMS), ("block", _lib.PROF_BLOCK), ("lazy", _lib.PROF_LAZY))}
     _lib.profile_enable(False)
     clocks = sampler.stop()
     wl.recorder = EventRecorder()                      # one extra, untimed step for the host-level stage breakdown

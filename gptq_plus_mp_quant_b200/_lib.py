@@ -41,6 +41,10 @@ SIGNATURES = {
     "rq_fq_block": (_i, [_vp] * 11 + [_i] * 10 + [_vp]),
     "rq_fq_lazy_update": (_i, [_vp] * 5 + [_i] * 6 + [_vp]),
     "rq_fq_run": (_i, [_vp] * 11 + [_i] * 8 + [_vp]),
+    "rq_fq_tc_workspace_bytes": (_sz, [_i, _i, _i, _i]),
+    "rq_fq_tc_prepare": (_i, [_vp, _i, _i, _i, _i, _vp, _sz, _vp]),
+    "rq_gptqplus_terms_tc": (_i, [_vp, _vp, _i, _i, _i, _f, _f, _vp, _vp, _vp, _vp, _vp, _sz, _vp, _vp]),
+    "rq_fq_run_tc": (_i, [_vp] * 11 + [_i] * 8 + [_vp, _sz, _vp, _vp]),
     "rq_fq_finish": (_i, [_vp, _vp, _vp, _i, _i, _vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _vp]),
 }
 
@@ -79,6 +83,7 @@ def check(fn: str, code: int) -> None:
 
 
 PROF_HESSIAN_UMMA, PROF_HESSIAN_PACK, PROF_FWHT, PROF_CHOL, PROF_BLOCK, PROF_LAZY = 1, 2, 3, 4, 5, 6
+PROF_CHOL_DIAG, PROF_CHOL_PANEL, PROF_CHOL_TRAILING, PROF_CHOL_INVERSE, PROF_TERMS = 7, 8, 9, 10, 11
 
 
 def profile_enable(on: bool) -> None:

@@ -12,6 +12,7 @@
 // All G groups of a linear are processed in the same launches (grid.z).
 #include "rq_common.cuh"
 #include "rq_gemm.cuh"
+#include "rq_umma_gemm.cuh"
 
 namespace rq {
 namespace chol {
@@ -301,15 +302,27 @@ __global__ void __launch_bounds__(256) finite_check_kernel(const float* __restri
     if (__syncthreads_or(badv) && threadIdx.x == 0) atomicCAS(&info[g], 0, -1);
 }
 
+// a device-side wait of a tensor-core launch ran out: report it through every group's info word
+__global__ void merge_status_kernel(const int* __restrict__ status, int* __restrict__ info, int G) {
+    if (*status != 0)
+        for (int g = threadIdx.x; g < G; g += blockDim.x) info[g] = -2;
+}
+
+// use the tensor-core trailing update from this many block columns on (below that the launch is all prologue)
+constexpr int kTensorTrailingMinBlocks = 4;
+
 }  // namespace chol
 }  // namespace rq
 
 using namespace rq;
 
+static size_t chol_panel_plane_bytes(size_t Cp, int G) { return (size_t)G * 2 * Cp * chol::NB * 2; }
+
 extern "C" size_t rq_chol_workspace_bytes(int C, int G) {
     if (C <= 0 || G <= 0) return 0;
     const size_t Cp = (size_t)(C + chol::NB - 1) / chol::NB * chol::NB;
-    return 2 * (size_t)G * Cp * Cp * sizeof(float) + 256 * sizeof(float) + 1024;     // A, T, per-group means
+    // A, T, per-group means / factors / status, bf16 planes of one block column
+    return 2 * (size_t)G * Cp * Cp * sizeof(float) + 256 * sizeof(float) + chol_panel_plane_bytes(Cp, G) + 2048;
 }
 
 extern "C" int rq_chol_hinv(const float* H, const int64_t* perm, const float* damp_factor, float* Hinv, int C, int G,
@@ -325,9 +338,13 @@ extern "C" int rq_chol_hinv(const float* H, const int64_t* perm, const float* da
     const size_t mat = (size_t)G * Cp * Cp;
     float* A = reinterpret_cast<float*>(workspace);
     float* T = A + mat;
-    float* mean = T + mat;              // [G] means, then [G] damping factors
+    float* mean = T + mat;              // [G] means, then [G] damping factors, then the tensor-core status word
     float* factor = mean + 64;
+    int* tc_status = reinterpret_cast<int*>(mean + 128);
+    __nv_bfloat16* panel_planes = reinterpret_cast<__nv_bfloat16*>(
+        (reinterpret_cast<uintptr_t>(mean + 256) + 1023) / 1024 * 1024);
     prof::Scope timed(RQ_PROF_CHOL, st);
+    if (cudaMemsetAsync(tc_status, 0, sizeof(int), st) != cudaSuccess) return RQ_ERR_CUDA;
 
     if (cudaMemcpyAsync(factor, damp_factor, (size_t)G * sizeof(float), cudaMemcpyHostToDevice, st) != cudaSuccess)
         return RQ_ERR_CUDA;
@@ -343,16 +360,45 @@ extern "C" int rq_chol_hinv(const float* H, const int64_t* perm, const float* da
 
     // phase 1: block columns from the last to the first
     for (int k = nblk - 1; k >= 0; --k) {
-        diag_block_kernel<<<G, kDiagThreads, 0, st>>>(A, Hinv, Cp, k, info);
+        {
+            prof::Scope t1(RQ_PROF_CHOL_DIAG, st);
+            diag_block_kernel<<<G, kDiagThreads, 0, st>>>(A, Hinv, Cp, k, info);
+        }
         if (k > 0) {
-            panel_kernel<<<dim3((unsigned)k, 1, (unsigned)G), gemm::kThreads, gemm::kSmemBytes, st>>>(A, Hinv, Cp, k);
-            trailing_kernel<<<dim3((unsigned)(k * (k + 1) / 2), 1, (unsigned)G), gemm::kThreads, gemm::kSmemBytes, st>>>(
-                A, Cp, k);
+            {
+                prof::Scope t2(RQ_PROF_CHOL_PANEL, st);
+                panel_kernel<<<dim3((unsigned)k, 1, (unsigned)G), gemm::kThreads, gemm::kSmemBytes, st>>>(A, Hinv, Cp, k);
+            }
+            prof::Scope t3(RQ_PROF_CHOL_TRAILING, st);
+            if (k >= kTensorTrailingMinBlocks) {
+                // split the panel R[0:k*128, block k] into bf16 planes and run A_ij -= R_ik . R_jk^T on the tensor cores
+                tcgemm::SplitArgs sa;
+                sa.src = A + (size_t)k * NB; sa.ld = Cp; sa.src_z = (long long)Cp * Cp;
+                sa.rows = k * NB; sa.cols = NB;
+                sa.dst = panel_planes; sa.Kp = NB; sa.plane_stride = (long long)Cp * NB;
+                sa.plane = 0; sa.plane_z = 2; sa.dst_row0 = 0; sa.dst_row_z = 0; sa.dst_k0 = 0; sa.pad_k_to = 0;
+                rc = tcgemm::split_rows(sa, G, st);
+                if (rc != RQ_OK) return rc;
+                tcgemm::PlaneTensor pt{panel_planes, NB, Cp, 2LL * G};
+                tcgemm::Params gp;
+                gp.a_row0 = gp.b_row0 = 0; gp.a_k0 = gp.b_k0 = 0; gp.a_plane = gp.b_plane = 0;
+                gp.a_plane_z = gp.b_plane_z = 2; gp.a_row_z = gp.b_row_z = 0;
+                gp.M = gp.N = k * NB; gp.k_len = NB; gp.tri = 1; gp.kmode = 0; gp.batch = G;
+                gp.C = A; gp.ldc = Cp; gp.c_z = (long long)Cp * Cp;
+                gp.Aux = nullptr; gp.ldaux = 0; gp.aux_z = 0;
+                gp.alpha = -1.f; gp.beta = 1.f; gp.gamma = 0.f;
+                rc = tcgemm::launch(pt, pt, gp, tc_status, st);
+                if (rc != RQ_OK) return rc;
+            } else {
+                trailing_kernel<<<dim3((unsigned)(k * (k + 1) / 2), 1, (unsigned)G), gemm::kThreads, gemm::kSmemBytes, st>>>(
+                    A, Cp, k);
+            }
         }
     }
     rc = check_launch();
     if (rc != RQ_OK) return rc;
     // phase 2: merge inverses of neighbouring diagonal blocks, doubling the block size each level
+    prof::Scope t4(RQ_PROF_CHOL_INVERSE, st);
     for (int s = NB; s < Cp; s *= 2) {
         const int pairs = (Cp + 2 * s - 1) / (2 * s);
         const int tiles = (s / NB) * (s / NB);
@@ -361,5 +407,6 @@ extern "C" int rq_chol_hinv(const float* H, const int64_t* perm, const float* da
                 A, Hinv, T, Cp, s, step);
     }
     finite_check_kernel<<<dim3(64, (unsigned)G), 256, 0, st>>>(Hinv, Cp, info);
+    merge_status_kernel<<<1, 64, 0, st>>>(tc_status, info, G);
     return check_launch();
 }

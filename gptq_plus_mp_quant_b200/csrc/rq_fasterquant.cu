@@ -8,6 +8,7 @@
 // the per-column scalars travel by warp shuffle.
 #include "rq_common.cuh"
 #include "rq_gemm.cuh"
+#include "rq_umma_gemm.cuh"
 
 namespace rq {
 namespace fq {
@@ -141,6 +142,8 @@ struct BlockArgs {
     float* Q;                // [R, C] dequantized result (permuted order)
     int8_t* codes;           // [R, C] integer codes (permuted order)
     float* Eeff;             // [R, BS]: Err (- D*Z1 when PLUS), A operand of the lazy update
+    __nv_bfloat16* Ehi;      // optional: the same operand split into bf16 planes [R][BS] for the tensor-core update
+    __nv_bfloat16* Elo;
     const float* scale_row;  // mode 0: [R]
     const float* scale_tab;  // mode 1: [ngroups, R] static groups
     const int* colgrp;       // mode 1: [C] group of (permuted) column j
@@ -270,8 +273,17 @@ __global__ void __launch_bounds__(kBlockThreads) block_kernel(const BlockArgs p)
             float e = ev[k];
             if (PLUS) e = e - (float)(p.count - 1 - col) * z[k];
             p.Eeff[(int64_t)r * BS + col] = e;
+            if (p.Ehi) {
+                const __nv_bfloat16 h = __float2bfloat16_rn(e);
+                p.Ehi[(int64_t)r * BS + col] = h;
+                p.Elo[(int64_t)r * BS + col] = __float2bfloat16_rn(e - __bfloat162float(h));
+            }
         } else {
             p.Eeff[(int64_t)r * BS + col] = 0.f;
+            if (p.Ehi) {
+                p.Ehi[(int64_t)r * BS + col] = __float2bfloat16_rn(0.f);
+                p.Elo[(int64_t)r * BS + col] = __float2bfloat16_rn(0.f);
+            }
         }
     }
 }
@@ -358,10 +370,10 @@ extern "C" int rq_gptqplus_terms(const float* Gp, const float* Hinv, int R, int 
     return check_launch();
 }
 
-extern "C" int rq_fq_block(float* Wp, float* GH, const float* Z, const float* Hinv, float* Q, int8_t* codes,
-                           float* Eeff, const float* scale_row, const float* scale_tab, const int* colgrp,
-                           float* scale_blk, int R, int C, int G, int i1, int count, int mode, int dyn_gs, int sym,
-                           int maxq, int plus, void* stream) {
+static int fq_block_launch(float* Wp, float* GH, const float* Z, const float* Hinv, float* Q, int8_t* codes,
+                           float* Eeff, __nv_bfloat16* Ehi, __nv_bfloat16* Elo, const float* scale_row,
+                           const float* scale_tab, const int* colgrp, float* scale_blk, int R, int C, int G, int i1,
+                           int count, int mode, int dyn_gs, int sym, int maxq, int plus, void* stream) {
     using namespace rq::fq;
     if (!Wp || !Hinv || !Q || !codes || !Eeff || R <= 0 || C <= 0 || G <= 0 || R % G != 0) return RQ_ERR_INVALID;
     if (i1 < 0 || count <= 0 || count > BS || i1 + count > C) return RQ_ERR_INVALID;
@@ -373,6 +385,7 @@ extern "C" int rq_fq_block(float* Wp, float* GH, const float* Z, const float* Hi
     cudaStream_t st = as_stream(stream);
     BlockArgs p;
     p.Wp = Wp; p.GH = GH; p.Z = Z; p.Hinv = Hinv; p.Q = Q; p.codes = codes; p.Eeff = Eeff;
+    p.Ehi = Ehi; p.Elo = Elo;
     p.scale_row = scale_row; p.scale_tab = scale_tab; p.colgrp = colgrp; p.scale_blk = scale_blk;
     p.R = R; p.C = C; p.Cp = (C + 127) / 128 * 128; p.G = G; p.i1 = i1; p.count = count;
     p.mode = mode; p.dyn_gs = dyn_gs; p.sym = sym;
@@ -391,6 +404,14 @@ extern "C" int rq_fq_block(float* Wp, float* GH, const float* Z, const float* Hi
         block_kernel<false><<<ctas, kBlockThreads, smem, st>>>(p);
     }
     return check_launch();
+}
+
+extern "C" int rq_fq_block(float* Wp, float* GH, const float* Z, const float* Hinv, float* Q, int8_t* codes,
+                           float* Eeff, const float* scale_row, const float* scale_tab, const int* colgrp,
+                           float* scale_blk, int R, int C, int G, int i1, int count, int mode, int dyn_gs, int sym,
+                           int maxq, int plus, void* stream) {
+    return fq_block_launch(Wp, GH, Z, Hinv, Q, codes, Eeff, nullptr, nullptr, scale_row, scale_tab, colgrp, scale_blk, R,
+                           C, G, i1, count, mode, dyn_gs, sym, maxq, plus, stream);
 }
 
 extern "C" int rq_fq_lazy_update(float* Wp, float* GH, const float* Z, const float* Eeff, const float* Hinv, int R,
@@ -446,6 +467,149 @@ extern "C" int rq_fq_run(float* Wp, float* GH, const float* Z, const float* Hinv
         if (rc != RQ_OK) return rc;
         rc = rq_fq_lazy_update(Wp, GH, Z, Eeff, Hinv, R, C, G, i1, count, plus, stream);
         if (rc != RQ_OK) return rc;
+    }
+    return RQ_OK;
+}
+
+// ------------------------------------------------------------------------------------------
+// tensor-core variants: the GEMM-shaped parts run on tcgen05 from bf16-split operand planes
+// ------------------------------------------------------------------------------------------
+namespace {
+struct TcLayout {
+    size_t put, pu, pa, pe, status, total;
+    int Cp;
+};
+
+TcLayout tc_layout(int R, int C, int G, int plus) {
+    TcLayout L;
+    L.Cp = (C + 127) / 128 * 128;
+    auto up = [](size_t v) { return (v + 1023) / 1024 * 1024; };
+    size_t off = 0;
+    L.put = off; off = up(off + (size_t)G * 2 * L.Cp * L.Cp * 2);
+    L.pu = off;  if (plus) off = up(off + (size_t)G * 2 * L.Cp * L.Cp * 2);
+    L.pa = off;  if (plus) off = up(off + (size_t)2 * R * L.Cp * 2);
+    L.pe = off;  off = up(off + (size_t)2 * R * rq::fq::BS * 2);
+    L.status = off; off += 1024;
+    L.total = off;
+    return L;
+}
+
+int split_full_rows(const float* src, int R, int C, int Cp, __nv_bfloat16* dst, cudaStream_t st) {
+    rq::tcgemm::SplitArgs a;
+    a.src = src; a.ld = C; a.src_z = 0; a.rows = R; a.cols = C;
+    a.dst = dst; a.Kp = Cp; a.plane_stride = (long long)R * Cp;
+    a.plane = 0; a.plane_z = 0; a.dst_row0 = 0; a.dst_row_z = 0; a.dst_k0 = 0; a.pad_k_to = Cp;
+    return rq::tcgemm::split_rows(a, 1, st);
+}
+}  // namespace
+
+extern "C" size_t rq_fq_tc_workspace_bytes(int R, int C, int G, int plus) {
+    if (R <= 0 || C <= 0 || G <= 0) return 0;
+    return tc_layout(R, C, G, plus).total + 1024;
+}
+
+// Split Hinv into the operand planes used below: U^T (rows = columns of U) always, U itself when plus.
+extern "C" int rq_fq_tc_prepare(const float* Hinv, int R, int C, int G, int plus, void* workspace, size_t workspace_bytes,
+                                void* stream) {
+    if (!Hinv || !workspace || R <= 0 || C <= 0 || G <= 0) return RQ_ERR_INVALID;
+    if (reinterpret_cast<uintptr_t>(workspace) % 1024 != 0) return RQ_ERR_INVALID;
+    const TcLayout L = tc_layout(R, C, G, plus);
+    if (workspace_bytes < L.total) return RQ_ERR_WORKSPACE;
+    cudaStream_t st = as_stream(stream);
+    uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
+    if (cudaMemsetAsync(ws + L.status, 0, sizeof(int), st) != cudaSuccess) return RQ_ERR_CUDA;
+    rq::tcgemm::SplitArgs a;
+    a.src = Hinv; a.ld = L.Cp; a.src_z = (long long)L.Cp * L.Cp; a.rows = L.Cp; a.cols = L.Cp;
+    a.Kp = L.Cp; a.plane_stride = (long long)L.Cp * L.Cp; a.plane = 0; a.plane_z = 2;
+    a.dst_row0 = 0; a.dst_row_z = 0; a.dst_k0 = 0; a.pad_k_to = 0;
+    a.dst = reinterpret_cast<__nv_bfloat16*>(ws + L.put);
+    int rc = rq::tcgemm::split_transpose(a, G, st);
+    if (rc != RQ_OK) return rc;
+    if (plus) {
+        a.dst = reinterpret_cast<__nv_bfloat16*>(ws + L.pu);
+        rc = rq::tcgemm::split_rows(a, G, st);
+    }
+    return rc;
+}
+
+extern "C" int rq_gptqplus_terms_tc(const float* Gp, const float* Hinv, int R, int C, int G, float alpha_eff,
+                                    float ref_loss, float* Z, float* GHinv, float* beta, float* hdiag, void* workspace,
+                                    size_t workspace_bytes, int* status, void* stream) {
+    using namespace rq::tcgemm;
+    if (!Gp || !Hinv || !Z || !GHinv || !beta || !hdiag || !workspace || R <= 0 || C <= 0 || G <= 0 || R % G != 0)
+        return RQ_ERR_INVALID;
+    const TcLayout L = tc_layout(R, C, G, 1);
+    if (workspace_bytes < L.total) return RQ_ERR_WORKSPACE;
+    cudaStream_t st = as_stream(stream);
+    uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
+    __nv_bfloat16* PA = reinterpret_cast<__nv_bfloat16*>(ws + L.pa);
+    int* tc_status = status ? status : reinterpret_cast<int*>(ws + L.status);
+    const int Rg = R / G, Cp = L.Cp;
+    prof::Scope timed(RQ_PROF_TERMS, st);
+    PlaneTensor tA{PA, Cp, R, 2};
+    PlaneTensor tU{ws + L.pu, Cp, Cp, 2LL * G};
+    PlaneTensor tUt{ws + L.put, Cp, Cp, 2LL * G};
+    Params p;
+    p.a_row0 = 0; p.b_row0 = 0; p.a_k0 = 0; p.b_k0 = 0; p.a_plane = 0; p.b_plane = 0;
+    p.a_plane_z = 0; p.b_plane_z = 2; p.a_row_z = Rg; p.b_row_z = 0;
+    p.M = Rg; p.N = C; p.k_len = Cp; p.tri = 0; p.batch = G;
+    p.ldc = C; p.c_z = (long long)Rg * C; p.Aux = nullptr; p.ldaux = 0; p.aux_z = 0;
+    p.alpha = 1.f; p.beta = 0.f; p.gamma = 0.f;
+    int rc = split_full_rows(Gp, R, C, Cp, PA, st);                 // T = Gp . U^T
+    if (rc != RQ_OK) return rc;
+    p.kmode = 3; p.C = Z;
+    rc = launch(tA, tU, p, tc_status, st);
+    if (rc != RQ_OK) return rc;
+    rc = split_full_rows(Z, R, C, Cp, PA, st);                      // G.H^-1 = T . U
+    if (rc != RQ_OK) return rc;
+    p.kmode = 2; p.C = GHinv;
+    rc = launch(tA, tUt, p, tc_status, st);
+    if (rc != RQ_OK) return rc;
+    fq::hinv_diag_kernel<<<dim3((unsigned)((C + 255) / 256), (unsigned)G), 256, 0, st>>>(Hinv, C, Cp, hdiag);
+    fq::beta_kernel<<<R, 256, 0, st>>>(Gp, Z, GHinv, hdiag, R, C, G, alpha_eff, ref_loss, beta);
+    rc = check_launch();
+    if (rc != RQ_OK) return rc;
+    return split_full_rows(Z, R, C, Cp, PA, st);                     // planes of Z = beta * T for the lazy updates
+}
+
+extern "C" int rq_fq_run_tc(float* Wp, float* GH, const float* Z, const float* Hinv, float* Q, int8_t* codes,
+                            float* Eeff, const float* scale_row, const float* scale_tab, const int* colgrp,
+                            float* scale_blk, int R, int C, int G, int mode, int dyn_gs, int sym, int maxq, int plus,
+                            void* workspace, size_t workspace_bytes, int* status, void* stream) {
+    using namespace rq::tcgemm;
+    if (!workspace || R <= 0 || C <= 0 || G <= 0 || R % G != 0) return RQ_ERR_INVALID;
+    const TcLayout L = tc_layout(R, C, G, plus);
+    if (workspace_bytes < L.total) return RQ_ERR_WORKSPACE;
+    cudaStream_t st = as_stream(stream);
+    uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
+    __nv_bfloat16* PE = reinterpret_cast<__nv_bfloat16*>(ws + L.pe);
+    int* tc_status = status ? status : reinterpret_cast<int*>(ws + L.status);
+    const int Rg = R / G, Cp = L.Cp;
+    PlaneTensor tE{PE, fq::BS, R, 2};
+    PlaneTensor tZ{ws + L.pa, Cp, R, 2};
+    PlaneTensor tUt{ws + L.put, Cp, Cp, 2LL * G};
+    for (int i1 = 0; i1 < C; i1 += fq::BS) {
+        const int count = (C - i1 < fq::BS) ? C - i1 : fq::BS;
+        int rc = fq_block_launch(Wp, GH, Z, Hinv, Q, codes, Eeff, PE, PE + (size_t)R * fq::BS, scale_row, scale_tab,
+                                 colgrp, scale_blk, R, C, G, i1, count, mode, dyn_gs, sym, maxq, plus, stream);
+        if (rc != RQ_OK) return rc;
+        const int i2 = i1 + count;
+        if (i2 >= C) break;
+        prof::Scope timed(RQ_PROF_LAZY, st);
+        Params p;
+        p.a_row0 = 0; p.a_k0 = 0; p.a_plane = 0; p.a_plane_z = 0; p.a_row_z = Rg;
+        p.b_row0 = i2; p.b_k0 = i1; p.b_plane = 0; p.b_plane_z = 2; p.b_row_z = 0;
+        p.M = Rg; p.N = C - i2; p.k_len = fq::BS; p.tri = 0; p.kmode = 0; p.batch = G;
+        p.C = Wp + i2; p.ldc = C; p.c_z = (long long)Rg * C;
+        p.Aux = plus ? GH + i2 : nullptr; p.ldaux = C; p.aux_z = (long long)Rg * C;
+        p.alpha = -1.f; p.beta = 1.f; p.gamma = plus ? -(float)count : 0.f;
+        rc = launch(tE, tUt, p, tc_status, st);                      // W[:, i2:] -= Eeff . Hinv[i1:i2, i2:] + count * GH
+        if (rc != RQ_OK) return rc;
+        if (plus) {
+            p.a_k0 = i1; p.C = GH + i2; p.Aux = nullptr; p.gamma = 0.f;
+            rc = launch(tZ, tUt, p, tc_status, st);                  // GH[:, i2:] -= Z[:, i1:i2] . Hinv[i1:i2, i2:]
+            if (rc != RQ_OK) return rc;
+        }
     }
     return RQ_OK;
 }

@@ -6,6 +6,7 @@ from __future__ import annotations
 
 import ctypes
 import logging
+import os
 from contextlib import nullcontext
 
 import torch
@@ -23,6 +24,9 @@ def _sec(rec, name):
 
 BS = 128            # column block of the kernels
 _DAMP_STEP = 0.0015
+# GEMM-shaped parts (first-order terms, lazy update) on the tensor cores (split-bf16, four products) or,
+# when False, as fp32 FMA tiles on the CUDA cores
+USE_TENSOR_CORES = os.environ.get("REALQ_FQ_TENSOR", "1") != "0"
 # tests set this to keep a copy of the first-order term as it is before the block loop updates it in place
 KEEP_INTERMEDIATES = False
 
@@ -82,6 +86,8 @@ def hinv_with_fallback(H3: torch.Tensor, perm, percdamp: float, identity_fallbac
                 flags[g] = int(sub.item())
         first = False
         pending = []
+        if any(flags[g] == -2 for g in todo):
+            raise _lib.RealQError("rq_chol_hinv (device wait)", _lib.RQ_ERR_TIMEOUT)
         for g in todo:
             if flags[g] != 0:
                 logging.warning("Quantization%s: Current `damp_percent = %.5f` is too low, auto-incrementing by `%.5f`",
@@ -151,26 +157,51 @@ def _quantize_linear(layer, W32, H3, perm, grads, quantizer, G, alpha_eff, ref_l
             _lib.check("rq_fq_prepare", _lib.lib.rq_fq_prepare(_lib.ptr(W32), _lib.ptr(grads), _lib.ptr(H3),
                                                                _lib.ptr(perm), R, Cc, G, _lib.ptr(Wp), _lib.ptr(Gp), st))
         Z = GH = beta = None
+        tc = USE_TENSOR_CORES
+        ws_ptr = ws_bytes = 0
+        status = _lib.ptr(ops.status_word(dev))
+        if tc:
+            need = _lib.lib.rq_fq_tc_workspace_bytes(R, Cc, G, 1 if plus else 0)
+            ws = ops._workspace(dev, need + 1024, key="fasterquant")
+            ws_ptr = (ws.data_ptr() + 1023) // 1024 * 1024
+            ws_bytes = ws.numel() - (ws_ptr - ws.data_ptr())
+            with _sec(rec, "fasterquant.subgroup.split_hinv"):
+                _lib.check("rq_fq_tc_prepare", _lib.lib.rq_fq_tc_prepare(_lib.ptr(Hinv), R, Cc, G, 1 if plus else 0,
+                                                                         ws_ptr, ws_bytes, st))
         if plus:
             Z = torch.empty(R, Cc, dtype=torch.float32, device=dev)
             GH = torch.empty(R, Cc, dtype=torch.float32, device=dev)
             beta = torch.empty(R, dtype=torch.float32, device=dev)
             hdiag = torch.empty(G, Cc, dtype=torch.float32, device=dev)
             with _sec(rec, "fasterquant.subgroup.init_ghinv"):
-                _lib.check("rq_gptqplus_terms",
-                           _lib.lib.rq_gptqplus_terms(_lib.ptr(Gp), _lib.ptr(Hinv), R, Cc, G, float(alpha_eff),
-                                                      float(ref_loss), _lib.ptr(Z), _lib.ptr(GH), _lib.ptr(beta),
-                                                      _lib.ptr(hdiag), st))
+                if tc:
+                    _lib.check("rq_gptqplus_terms_tc",
+                               _lib.lib.rq_gptqplus_terms_tc(_lib.ptr(Gp), _lib.ptr(Hinv), R, Cc, G, float(alpha_eff),
+                                                             float(ref_loss), _lib.ptr(Z), _lib.ptr(GH), _lib.ptr(beta),
+                                                             _lib.ptr(hdiag), ws_ptr, ws_bytes, status, st))
+                else:
+                    _lib.check("rq_gptqplus_terms",
+                               _lib.lib.rq_gptqplus_terms(_lib.ptr(Gp), _lib.ptr(Hinv), R, Cc, G, float(alpha_eff),
+                                                          float(ref_loss), _lib.ptr(Z), _lib.ptr(GH), _lib.ptr(beta),
+                                                          _lib.ptr(hdiag), st))
         GH_initial = GH.clone() if (plus and KEEP_INTERMEDIATES) else None
         Q = torch.empty(R, Cc, dtype=torch.float32, device=dev)
         codes = torch.empty(R, Cc, dtype=torch.int8, device=dev)
         Eeff = torch.empty(R, BS, dtype=torch.float32, device=dev)
         with _sec(rec, "fasterquant.block.total"):
-            _lib.check("rq_fq_run",
-                       _lib.lib.rq_fq_run(_lib.ptr(Wp), _lib.ptr(GH), _lib.ptr(Z), _lib.ptr(Hinv), _lib.ptr(Q),
-                                          _lib.ptr(codes), _lib.ptr(Eeff), _lib.ptr(scale_row), _lib.ptr(scale_tab),
-                                          _lib.ptr(colgrp), _lib.ptr(scale_blk), R, Cc, G, mode, dyn_gs,
-                                          1 if quantizer.sym else 0, maxq, 1 if plus else 0, st))
+            if tc:
+                _lib.check("rq_fq_run_tc",
+                           _lib.lib.rq_fq_run_tc(_lib.ptr(Wp), _lib.ptr(GH), _lib.ptr(Z), _lib.ptr(Hinv), _lib.ptr(Q),
+                                                 _lib.ptr(codes), _lib.ptr(Eeff), _lib.ptr(scale_row),
+                                                 _lib.ptr(scale_tab), _lib.ptr(colgrp), _lib.ptr(scale_blk), R, Cc, G,
+                                                 mode, dyn_gs, 1 if quantizer.sym else 0, maxq, 1 if plus else 0,
+                                                 ws_ptr, ws_bytes, status, st))
+            else:
+                _lib.check("rq_fq_run",
+                           _lib.lib.rq_fq_run(_lib.ptr(Wp), _lib.ptr(GH), _lib.ptr(Z), _lib.ptr(Hinv), _lib.ptr(Q),
+                                              _lib.ptr(codes), _lib.ptr(Eeff), _lib.ptr(scale_row), _lib.ptr(scale_tab),
+                                              _lib.ptr(colgrp), _lib.ptr(scale_blk), R, Cc, G, mode, dyn_gs,
+                                              1 if quantizer.sym else 0, maxq, 1 if plus else 0, st))
         out = torch.empty(layer.weight.shape, dtype=layer.weight.dtype, device=dev)
         out_codes = out_scale = None
         if export_to_et:

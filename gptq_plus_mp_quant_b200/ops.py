@@ -16,12 +16,14 @@ _scratch = {}
 _status = {}
 
 
-def _workspace(device, nbytes: int) -> torch.Tensor:
-    buf = _scratch.get(device)
+def _workspace(device, nbytes: int, key: str = "main") -> torch.Tensor:
+    """Cached scratch buffer per (device, key); grown on demand, never shrunk."""
+    k = (device, key)
+    buf = _scratch.get(k)
     if buf is None or buf.numel() < nbytes:
-        _scratch[device] = None
+        _scratch[k] = None
         buf = torch.empty(nbytes + 1024, dtype=torch.uint8, device=device)
-        _scratch[device] = buf
+        _scratch[k] = buf
     return buf
 
 

@@ -64,8 +64,15 @@ def main():
     elif a.case == "chol":
         x = torch.randn(4 * a.C, a.C, generator=g, device=dev) * torch.exp(torch.randn(a.C, generator=g, device=dev))
         H = (x.t() @ x / x.shape[0]).unsqueeze(0).repeat(a.G, 1, 1).contiguous()
+        from . import _lib
+        fi.hinv_with_fallback(H, None, 0.01, True)
+        _lib.profile_enable(True)
         ms = _time(lambda: fi.hinv_with_fallback(H, None, 0.01, True), a.reps)
-        print(f"chol C={a.C} G={a.G}: {ms:.3f} ms per call, {(2.0 / 3.0) * a.C ** 3 * a.G / ms / 1e9:.2f} TFLOP/s (2/3 C^3 per group)")
+        parts = {name: _lib.profile_read(tag)[0] / (a.reps + 1) for name, tag in
+                 (("diag", 7), ("panel", 8), ("trailing", 9), ("inverse", 10))}
+        _lib.profile_enable(False)
+        print(f"chol C={a.C} G={a.G}: {ms:.3f} ms per call, {(2.0 / 3.0) * a.C ** 3 * a.G / ms / 1e9:.2f} TFLOP/s (2/3 C^3 per group); "
+              + ", ".join(f"{k} {v:.2f} ms" for k, v in parts.items()))
     else:
         from .gptq_utils.gptq_plus_utils import GPTQPlus
         from .utils.quant_utils import WeightQuantizer

@@ -47,6 +47,11 @@ const char* rq_error_string(int code);
 #define RQ_PROF_CHOL 4
 #define RQ_PROF_BLOCK 5
 #define RQ_PROF_LAZY 6
+#define RQ_PROF_CHOL_DIAG 7
+#define RQ_PROF_CHOL_PANEL 8
+#define RQ_PROF_CHOL_TRAILING 9
+#define RQ_PROF_CHOL_INVERSE 10
+#define RQ_PROF_TERMS 11
 int rq_profile_enable(int on);
 int rq_profile_read(int tag, double* total_ms, long long* launches);
 
@@ -142,7 +147,8 @@ int rq_quantize(const void* x, void* deq, float* codes, int dtype, int64_t R, in
  * cumulatively on retries, as the reference does); Hinv: [G, Cp, Cp] fp32 with Cp = C rounded up to 128,
  * row stride Cp, zero below the diagonal, 16-byte aligned.
  * info: device int [G]: 0 = ok, k > 0 = non-positive pivot met in block column k-1 (not positive
- * definite: the host retries with more damping), -1 = non-finite entries in the result.
+ * definite: the host retries with more damping), -1 = non-finite entries in the result,
+ * -2 = a bounded device-side wait of a tensor-core launch ran out (treat as RQ_ERR_TIMEOUT).
  * workspace: rq_chol_workspace_bytes(C, G) bytes, 256-byte aligned. */
 size_t rq_chol_workspace_bytes(int C, int G);
 int rq_chol_hinv(const float* H, const int64_t* perm, const float* damp_factor, float* Hinv, int C, int G,
@@ -191,6 +197,23 @@ int rq_fq_lazy_update(float* Wp, float* GH, const float* Z, const float* Eeff, c
 int rq_fq_run(float* Wp, float* GH, const float* Z, const float* Hinv, float* Q, int8_t* codes, float* Eeff,
               const float* scale_row, const float* scale_tab, const int* colgrp, float* scale_blk, int R, int C, int G,
               int mode, int dyn_gs, int sym, int maxq, int plus, void* stream);
+
+/* Tensor-core variants of the GEMM-shaped parts of fasterquant (same reference lines as above): operands
+ * are split into bf16 hi/lo planes and multiplied with four tcgen05 products per k-step, which keeps
+ * fp32-level accuracy.  rq_fq_tc_prepare splits Hinv once per linear (U^T always, U too when plus) into
+ * `workspace` (rq_fq_tc_workspace_bytes bytes, 1024-byte aligned); rq_gptqplus_terms_tc and rq_fq_run_tc then
+ * take the same workspace (terms first: it leaves the planes of Z there for the lazy updates).
+ * status: optional device int receiving RQ_ERR_TIMEOUT if a bounded device wait ran out. */
+size_t rq_fq_tc_workspace_bytes(int R, int C, int G, int plus);
+int rq_fq_tc_prepare(const float* Hinv, int R, int C, int G, int plus, void* workspace, size_t workspace_bytes,
+                     void* stream);
+int rq_gptqplus_terms_tc(const float* Gp, const float* Hinv, int R, int C, int G, float alpha_eff, float ref_loss,
+                         float* Z, float* GHinv, float* beta, float* hdiag, void* workspace, size_t workspace_bytes,
+                         int* status, void* stream);
+int rq_fq_run_tc(float* Wp, float* GH, const float* Z, const float* Hinv, float* Q, int8_t* codes, float* Eeff,
+                 const float* scale_row, const float* scale_tab, const int* colgrp, float* scale_blk, int R, int C,
+                 int G, int mode, int dyn_gs, int sym, int maxq, int plus, void* workspace, size_t workspace_bytes,
+                 int* status, void* stream);
 
 /* rq_fq_finish replaces the epilogue (gptq_utils/gptq_plus_utils.py:1850-1875; gptq_utils/gptq_utils.py:157-166):
  * out[r][perm[j]] = Q[r][j] cast to out_dtype; when out_codes != NULL also the fp32 int_weight / scale
