@@ -310,6 +310,8 @@ __global__ void merge_status_kernel(const int* __restrict__ status, int* __restr
 
 // use the tensor-core trailing update from this many block columns on (below that the launch is all prologue)
 constexpr int kTensorTrailingMinBlocks = 4;
+// levels of the triangular inverse with blocks at least this wide run on the tensor cores
+constexpr int kTensorInverseMinBlock = 512;
 
 }  // namespace chol
 }  // namespace rq
@@ -317,12 +319,16 @@ constexpr int kTensorTrailingMinBlocks = 4;
 using namespace rq;
 
 static size_t chol_panel_plane_bytes(size_t Cp, int G) { return (size_t)G * 2 * Cp * chol::NB * 2; }
+static size_t chol_full_plane_bytes(size_t Cp, int G) {       // hi + lo planes of one Cp x Cp matrix per group
+    return Cp >= (size_t)chol::kTensorInverseMinBlock * 2 ? (size_t)G * 2 * Cp * Cp * 2 + 1024 : 0;
+}
 
 extern "C" size_t rq_chol_workspace_bytes(int C, int G) {
     if (C <= 0 || G <= 0) return 0;
     const size_t Cp = (size_t)(C + chol::NB - 1) / chol::NB * chol::NB;
     // A, T, per-group means / factors / status, bf16 planes of one block column
-    return 2 * (size_t)G * Cp * Cp * sizeof(float) + 256 * sizeof(float) + chol_panel_plane_bytes(Cp, G) + 2048;
+    return 2 * (size_t)G * Cp * Cp * sizeof(float) + 256 * sizeof(float) + chol_panel_plane_bytes(Cp, G) + 4096 +
+           4 * chol_full_plane_bytes(Cp, G);                  // R^T, U, U^T, T planes for the inverse
 }
 
 extern "C" int rq_chol_hinv(const float* H, const int64_t* perm, const float* damp_factor, float* Hinv, int C, int G,
@@ -399,12 +405,61 @@ extern "C" int rq_chol_hinv(const float* H, const int64_t* perm, const float* da
     if (rc != RQ_OK) return rc;
     // phase 2: merge inverses of neighbouring diagonal blocks, doubling the block size each level
     prof::Scope t4(RQ_PROF_CHOL_INVERSE, st);
+    const size_t fpb = chol_full_plane_bytes(Cp, G);
+    uint8_t* plane_base = reinterpret_cast<uint8_t*>(
+        (reinterpret_cast<uintptr_t>(panel_planes) + chol_panel_plane_bytes(Cp, G) + 1023) / 1024 * 1024);
+    __nv_bfloat16* PRt = reinterpret_cast<__nv_bfloat16*>(plane_base);
+    __nv_bfloat16* PU = reinterpret_cast<__nv_bfloat16*>(plane_base + fpb);
+    __nv_bfloat16* PUt = reinterpret_cast<__nv_bfloat16*>(plane_base + 2 * fpb);
+    __nv_bfloat16* PT = reinterpret_cast<__nv_bfloat16*>(plane_base + 3 * fpb);
+    auto split_full = [&](const float* src, __nv_bfloat16* dst, bool transpose) {
+        tcgemm::SplitArgs sa;
+        sa.src = src; sa.ld = Cp; sa.src_z = (long long)Cp * Cp; sa.rows = Cp; sa.cols = Cp;
+        sa.dst = dst; sa.Kp = Cp; sa.plane_stride = (long long)Cp * Cp; sa.plane = 0; sa.plane_z = 2;
+        sa.dst_row0 = 0; sa.dst_row_z = 0; sa.dst_k0 = 0; sa.pad_k_to = 0;
+        return transpose ? tcgemm::split_transpose(sa, G, st) : tcgemm::split_rows(sa, G, st);
+    };
+    bool rt_ready = false;
     for (int s = NB; s < Cp; s *= 2) {
         const int pairs = (Cp + 2 * s - 1) / (2 * s);
-        const int tiles = (s / NB) * (s / NB);
-        for (int step = 1; step <= 2; ++step)
-            inv_level_kernel<<<dim3((unsigned)tiles, (unsigned)pairs, (unsigned)G), gemm::kThreads, gemm::kSmemBytes, st>>>(
-                A, Hinv, T, Cp, s, step);
+        if (s < kTensorInverseMinBlock || fpb == 0) {
+            const int tiles = (s / NB) * (s / NB);
+            for (int step = 1; step <= 2; ++step)
+                inv_level_kernel<<<dim3((unsigned)tiles, (unsigned)pairs, (unsigned)G), gemm::kThreads, gemm::kSmemBytes, st>>>(
+                    A, Hinv, T, Cp, s, step);
+            continue;
+        }
+        // tensor-core level: pair m merges a = [2ms, 2ms+s) and b = [2ms+s, min(2ms+2s, Cp))
+        if (!rt_ready) {
+            rc = split_full(A, PRt, true);                       // planes of R^T: [n][k] = R[k][n]
+            if (rc != RQ_OK) return rc;
+            rt_ready = true;
+        }
+        rc = split_full(Hinv, PU, false);
+        if (rc != RQ_OK) return rc;
+        rc = split_full(Hinv, PUt, true);
+        if (rc != RQ_OK) return rc;
+        tcgemm::PlaneTensor tRt{PRt, Cp, Cp, 2LL * G}, tU{PU, Cp, Cp, 2LL * G}, tUt{PUt, Cp, Cp, 2LL * G},
+            tT{PT, Cp, Cp, 2LL * G};
+        tcgemm::Params gp;
+        gp.a_plane = gp.b_plane = 0; gp.a_plane_z = gp.b_plane_z = 2; gp.a_row_z = gp.b_row_z = 0;
+        gp.M = s; gp.N = s; gp.k_len = s; gp.tri = 0; gp.batch = pairs * G; gp.nz1 = pairs;
+        gp.ldc = Cp; gp.c_z = (long long)Cp * Cp; gp.c_z1 = (long long)2 * s * Cp + 2 * s;
+        gp.Aux = nullptr; gp.ldaux = 0; gp.aux_z = 0; gp.gamma = 0.f; gp.beta = 0.f;
+        gp.n_limit = Cp - s; gp.n_limit_z1 = 2 * s;
+        gp.a_row_z1 = 2 * s; gp.b_row_z1 = 2 * s; gp.a_k_z1 = 2 * s; gp.b_k_z1 = 2 * s;
+        // step 1: T[a, b] = U[a, a] . R[a, b]
+        gp.a_row0 = 0; gp.a_k0 = 0; gp.b_row0 = s; gp.b_k0 = 0; gp.kmode = 1;
+        gp.C = T + s; gp.alpha = 1.f;
+        rc = tcgemm::launch(tU, tRt, gp, tc_status, st);
+        if (rc != RQ_OK) return rc;
+        rc = split_full(T, PT, false);
+        if (rc != RQ_OK) return rc;
+        // step 2: U[a, b] = -T[a, b] . U[b, b]
+        gp.a_row0 = 0; gp.a_k0 = s; gp.b_row0 = s; gp.b_k0 = s; gp.kmode = 2;
+        gp.C = Hinv + s; gp.alpha = -1.f;
+        rc = tcgemm::launch(tT, tUt, gp, tc_status, st);
+        if (rc != RQ_OK) return rc;
     }
     finite_check_kernel<<<dim3(64, (unsigned)G), 256, 0, st>>>(Hinv, Cp, info);
     merge_status_kernel<<<1, 64, 0, st>>>(tc_status, info, G);

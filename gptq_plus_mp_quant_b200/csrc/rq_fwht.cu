@@ -6,6 +6,7 @@
 // is a small +-1 matrix product per position.  Input is read once and output written once with
 // 16-byte accesses where alignment allows; all arithmetic is fp32 whatever the I/O type.
 #include "rq_common.cuh"
+#include "rq_fwht_warp.cuh"
 
 namespace rq {
 namespace fwht {
@@ -161,6 +162,95 @@ extern "C" int rq_fwht(const void* x, void* y, int dtype, int64_t rows, int n, i
     if (rows == 0) return RQ_OK;
     int m = 0;
     while ((1 << m) < P) ++m;
+    int dev0 = 0, sms0 = 148;
+    cudaGetDevice(&dev0);
+    cudaDeviceGetAttribute(&sms0, cudaDevAttrMultiProcessorCount, dev0);
+    const bool aligned16 = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15) == 0;
+    // ---- fast path: register-resident warp transform
+    if (aligned16 && K == 1 && (P == 2048 || P == 4096 || P == 8192)) {
+        // one chunk per CTA of P/1024 warps
+        cudaStream_t st = as_stream(stream);
+        prof::Scope timed(RQ_PROF_FWHT, st);
+        const int W = P / 1024;
+        const int64_t nchunks = rows;
+        const size_t smem = (size_t)W * warp_slice_floats(1024) * sizeof(float);
+        int per_sm = (int)((200 * 1024) / (smem + 1024));
+        if (per_sm > 16 / W * 2) per_sm = 16 / W * 2;
+        if (per_sm < 1) per_sm = 1;
+        int64_t grid = nchunks < (int64_t)sms0 * per_sm ? nchunks : (int64_t)sms0 * per_sm;
+        cudaError_t e = cudaSuccess;
+#define RQ_SPLIT_LAUNCH(T, WW)                                                                                    \
+    e = cudaFuncSetAttribute(fwht_split_kernel<T, WW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);    \
+    if (e != cudaSuccess) return RQ_ERR_CUDA;                                                                      \
+    fwht_split_kernel<T, WW><<<(unsigned)grid, 32 * WW, smem, st>>>(reinterpret_cast<const T*>(x),                 \
+                                                                    reinterpret_cast<T*>(y), nchunks, scale)
+#define RQ_SPLIT_DISPATCH(T)                                \
+    if (W == 2) { RQ_SPLIT_LAUNCH(T, 2); }                  \
+    else if (W == 4) { RQ_SPLIT_LAUNCH(T, 4); }             \
+    else { RQ_SPLIT_LAUNCH(T, 8); }
+        if (dtype == RQ_F32) { RQ_SPLIT_DISPATCH(float) }
+        else if (dtype == RQ_BF16) { RQ_SPLIT_DISPATCH(__nv_bfloat16) }
+        else if (dtype == RQ_F16) { RQ_SPLIT_DISPATCH(__half) }
+        else return RQ_ERR_INVALID;
+#undef RQ_SPLIT_DISPATCH
+#undef RQ_SPLIT_LAUNCH
+        return check_launch();
+    }
+    if (aligned16 && P <= 4096 && (K == 1 || (P >= 1024 && K <= 28))) {
+        cudaStream_t st = as_stream(stream);
+        prof::Scope timed(RQ_PROF_FWHT, st);
+        const int logs = m < 10 ? 10 : m;
+        const int S = 1 << logs;
+        cudaError_t e = cudaSuccess;
+        if (K == 1) {
+            const int64_t total = rows * (int64_t)n;
+            const int64_t nsc = (total + S - 1) / S;
+            const size_t smem = (size_t)kWarpsPerCta * warp_slice_floats(S) * sizeof(float);
+            int per_sm = (int)((200 * 1024) / (smem + 1024));
+            if (per_sm > 8) per_sm = 8;
+            int64_t grid = (nsc + kWarpsPerCta - 1) / kWarpsPerCta;
+            if (grid > (int64_t)sms0 * per_sm) grid = (int64_t)sms0 * per_sm;
+#define RQ_WARP_LAUNCH(T, L)                                                                                      \
+    e = cudaFuncSetAttribute(fwht_warp_kernel<T, L>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);      \
+    if (e != cudaSuccess) return RQ_ERR_CUDA;                                                                      \
+    fwht_warp_kernel<T, L><<<(unsigned)grid, 32 * kWarpsPerCta, smem, st>>>(reinterpret_cast<const T*>(x),         \
+                                                                            reinterpret_cast<T*>(y), total, m, scale)
+#define RQ_WARP_DISPATCH(T)                                  \
+    if (logs == 10) { RQ_WARP_LAUNCH(T, 10); }               \
+    else if (logs == 11) { RQ_WARP_LAUNCH(T, 11); }          \
+    else { RQ_WARP_LAUNCH(T, 12); }
+            if (dtype == RQ_F32) { RQ_WARP_DISPATCH(float) }
+            else if (dtype == RQ_BF16) { RQ_WARP_DISPATCH(__nv_bfloat16) }
+            else if (dtype == RQ_F16) { RQ_WARP_DISPATCH(__half) }
+            else return RQ_ERR_INVALID;
+#undef RQ_WARP_DISPATCH
+#undef RQ_WARP_LAUNCH
+            return check_launch();
+        }
+        const size_t smem = ((size_t)K * warp_slice_floats(S) + (size_t)K * K) * sizeof(float);
+        if (smem <= 220 * 1024) {
+            int per_sm = (int)((220 * 1024) / (smem + 1024));
+            if (per_sm < 1) per_sm = 1;
+            int64_t grid = rows < (int64_t)sms0 * per_sm ? rows : (int64_t)sms0 * per_sm;
+#define RQ_MIX_LAUNCH(T, L)                                                                                       \
+    e = cudaFuncSetAttribute(fwht_mix_kernel<T, L>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);       \
+    if (e != cudaSuccess) return RQ_ERR_CUDA;                                                                      \
+    fwht_mix_kernel<T, L><<<(unsigned)grid, 32 * kMixWarps, smem, st>>>(reinterpret_cast<const T*>(x),          \
+                                                                           reinterpret_cast<T*>(y), rows, K, hadK, scale)
+#define RQ_MIX_DISPATCH(T)                                  \
+    if (logs == 10) { RQ_MIX_LAUNCH(T, 10); }               \
+    else if (logs == 11) { RQ_MIX_LAUNCH(T, 11); }          \
+    else { RQ_MIX_LAUNCH(T, 12); }
+            if (dtype == RQ_F32) { RQ_MIX_DISPATCH(float) }
+            else if (dtype == RQ_BF16) { RQ_MIX_DISPATCH(__nv_bfloat16) }
+            else if (dtype == RQ_F16) { RQ_MIX_DISPATCH(__half) }
+            else return RQ_ERR_INVALID;
+#undef RQ_MIX_DISPATCH
+#undef RQ_MIX_LAUNCH
+            return check_launch();
+        }
+    }
+    // ---- general path: shared-memory radix passes (any K up to 64, chunks longer than 4096, unaligned buffers)
     // short rows are batched so that an item has about 4096 elements; whole chunks only
     int rows_per_item = 1;
     if (n < 4096) {
@@ -182,7 +272,7 @@ extern "C" int rq_fwht(const void* x, void* y, int dtype, int64_t rows, int n, i
     if (grid > items) grid = items;
     cudaStream_t st = as_stream(stream);
     cudaError_t e = cudaSuccess;
-    prof::Scope timed(RQ_PROF_FWHT, st);
+    prof::Scope timed2(RQ_PROF_FWHT, st);
 #define RQ_FWHT_LAUNCH(T)                                                                                       \
     e = cudaFuncSetAttribute(fwht_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);           \
     if (e != cudaSuccess) return RQ_ERR_CUDA;                                                                   \

@@ -1,0 +1,325 @@
+// Warp-level Walsh-Hadamard transform: the fast path of rq_fwht for power-of-two chunks up to 4096.
+//
+// One warp owns a "super-chunk" of S = 1024 / 2048 / 4096 consecutive elements (one chunk, or several
+// short ones) and keeps it in registers, E = S/32 per lane:
+//   load   lane l reads 8 consecutive elements (16 B for bf16/fp16) at j*256 + l*8, j < E/8;
+//   phase A  butterflies over the index bits that are thread-local in this mapping (0-2 and 8+);
+//   transposition through the warp's private shared-memory slice (128-bit accesses, 8 padding words
+//            per 256 keep every access conflict free) so that index bits 3-7 become thread-local;
+//   phase B  butterflies over bits 3-7; the result goes back to the same shared-memory slots.
+// About 16 instructions per element instead of the ~50 of a shared-memory radix pass design, which is
+// what an HBM-bound kernel can afford at 6.5 TB/s.  The K x K mix (n = K * 2^m) runs per row from shared memory.
+#pragma once
+
+#include "rq_common.cuh"
+
+namespace rq {
+namespace fwht {
+
+constexpr int kWarpsPerCta = 4;
+constexpr int kMixWarps = 8;          // warps of a CTA that transforms and mixes one row (n = K * 2^m, K > 1)
+
+__device__ __forceinline__ int wphys(int idx) { return idx + ((idx >> 8) << 3); }
+__host__ __device__ constexpr int warp_slice_floats(int S) { return S + (S >> 8) * 8; }
+
+template <typename T>
+__device__ __forceinline__ void load8(const T* p, float (&v)[8]);
+template <>
+__device__ __forceinline__ void load8<float>(const float* p, float (&v)[8]) {
+    const float4 a = *reinterpret_cast<const float4*>(p);
+    const float4 b = *reinterpret_cast<const float4*>(p + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+template <>
+__device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[8]) {
+    const uint4 r = *reinterpret_cast<const uint4*>(p);
+    const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        v[2 * i] = __uint_as_float(w[i] << 16);
+        v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+}
+template <>
+__device__ __forceinline__ void load8<__half>(const __half* p, float (&v)[8]) {
+    const uint4 r = *reinterpret_cast<const uint4*>(p);
+    const __half2* h = reinterpret_cast<const __half2*>(&r);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 f = __half22float2(h[i]);
+        v[2 * i] = f.x;
+        v[2 * i + 1] = f.y;
+    }
+}
+
+template <typename T>
+__device__ __forceinline__ void store8(T* p, const float (&v)[8]);
+template <>
+__device__ __forceinline__ void store8<float>(float* p, const float (&v)[8]) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+}
+template <>
+__device__ __forceinline__ void store8<__nv_bfloat16>(__nv_bfloat16* p, const float (&v)[8]) {
+    uint4 r;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&r);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+    *reinterpret_cast<uint4*>(p) = r;
+}
+template <>
+__device__ __forceinline__ void store8<__half>(__half* p, const float (&v)[8]) {
+    uint4 r;
+    __half2* h = reinterpret_cast<__half2*>(&r);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+    *reinterpret_cast<uint4*>(p) = r;
+}
+
+// butterfly over register-index bit RB of a[E]
+template <int E, int RB>
+__device__ __forceinline__ void reg_butterfly(float (&a)[E]) {
+#pragma unroll
+    for (int r = 0; r < E; ++r) {
+        if ((r & (1 << RB)) == 0) {
+            const float u = a[r], w = a[r | (1 << RB)];
+            a[r] = u + w;
+            a[r | (1 << RB)] = u - w;
+        }
+    }
+}
+
+template <int E, int RB, int LOG2E>
+struct PhaseA {   // register bit rb <-> index bit rb (rb < 3) or rb + 5 (rb >= 3)
+    static __device__ __forceinline__ void run(float (&a)[E], int m) {
+        if ((RB < 3 ? RB : RB + 5) < m) reg_butterfly<E, RB>(a);
+        PhaseA<E, RB + 1, LOG2E>::run(a, m);
+    }
+};
+template <int E, int LOG2E>
+struct PhaseA<E, LOG2E, LOG2E> {
+    static __device__ __forceinline__ void run(float (&)[E], int) {}
+};
+
+template <int E, int CB, int LOG2V>
+struct PhaseB {   // register bit LOG2V + cb <-> index bit 3 + cb, cb < 5
+    static __device__ __forceinline__ void run(float (&a)[E], int m) {
+        if (3 + CB < m) reg_butterfly<E, LOG2V + CB>(a);
+        PhaseB<E, CB + 1, LOG2V>::run(a, m);
+    }
+};
+template <int E, int LOG2V>
+struct PhaseB<E, 5, LOG2V> {
+    static __device__ __forceinline__ void run(float (&)[E], int) {}
+};
+
+// Transform the super-chunk that starts at element `base` of src (elements at or beyond `total` read as 0);
+// the result is left in `wbuf` (this warp's slice) at wphys(natural index).
+template <typename T, int LOGS>
+__device__ __forceinline__ void warp_transform(const T* __restrict__ src, int64_t base, int64_t total, int m,
+                                               float* wbuf, int lane) {
+    constexpr int S = 1 << LOGS, E = S / 32, LOG2E = LOGS - 5, J = E / 8, V = E / 32, LOG2V = LOG2E - 5;
+    float a[E];
+#pragma unroll
+    for (int j = 0; j < J; ++j) {
+        const int idx = j * 256 + lane * 8;
+        float v[8];
+        if (base + idx + 8 <= total) {
+            load8<T>(src + base + idx, v);
+        } else {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[e] = (base + idx + e < total) ? load_as_float<T>(src, base + idx + e) : 0.f;
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) a[j * 8 + e] = v[e];
+    }
+    PhaseA<E, 0, LOG2E>::run(a, m);
+#pragma unroll
+    for (int j = 0; j < J; ++j) {
+        float* p = wbuf + wphys(j * 256 + lane * 8);
+        *reinterpret_cast<float4*>(p) = make_float4(a[j * 8], a[j * 8 + 1], a[j * 8 + 2], a[j * 8 + 3]);
+        *reinterpret_cast<float4*>(p + 4) = make_float4(a[j * 8 + 4], a[j * 8 + 5], a[j * 8 + 6], a[j * 8 + 7]);
+    }
+    __syncwarp();
+    // second mapping: thread-local = bits 3-7 (c) and the lowest LOG2V bits (u); lane = remaining low bits + bits 8+
+    constexpr int LOWN = 8 / V;                               // lanes that share a 256-element block differ in the low part
+    const int lowpart = lane % LOWN, highpart = lane / LOWN;
+    const int off = highpart * 256 + lowpart * V;
+    float b[E];
+#pragma unroll
+    for (int c = 0; c < 32; ++c) {
+        const float* p = wbuf + wphys(off + c * 8);
+        if (V == 4) {
+            const float4 t = *reinterpret_cast<const float4*>(p);
+            b[c * 4] = t.x; b[c * 4 + 1] = t.y; b[c * 4 + 2] = t.z; b[c * 4 + 3] = t.w;
+        } else if (V == 2) {
+            const float2 t = *reinterpret_cast<const float2*>(p);
+            b[c * 2] = t.x; b[c * 2 + 1] = t.y;
+        } else {
+            b[c] = *p;
+        }
+    }
+    PhaseB<E, 0, LOG2V>::run(b, m);
+#pragma unroll
+    for (int c = 0; c < 32; ++c) {
+        float* p = wbuf + wphys(off + c * 8);
+        if (V == 4) *reinterpret_cast<float4*>(p) = make_float4(b[c * 4], b[c * 4 + 1], b[c * 4 + 2], b[c * 4 + 3]);
+        else if (V == 2) *reinterpret_cast<float2*>(p) = make_float2(b[c * 2], b[c * 2 + 1]);
+        else *p = b[c];
+    }
+    __syncwarp();
+}
+
+// K == 1: every warp transforms super-chunks independently and writes them back with 16-byte stores.
+template <typename T, int LOGS>
+__global__ void __launch_bounds__(32 * kWarpsPerCta) fwht_warp_kernel(const T* __restrict__ x, T* __restrict__ y,
+                                                                      int64_t total, int m, float scale) {
+    constexpr int S = 1 << LOGS, E = S / 32, J = E / 8;
+    extern __shared__ float wsm[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    float* wbuf = wsm + warp * warp_slice_floats(S);
+    const int64_t nsc = (total + S - 1) / S;
+    for (int64_t sc = (int64_t)blockIdx.x * kWarpsPerCta + warp; sc < nsc; sc += (int64_t)gridDim.x * kWarpsPerCta) {
+        const int64_t base = sc * S;
+        warp_transform<T, LOGS>(x, base, total, m, wbuf, lane);
+#pragma unroll
+        for (int j = 0; j < J; ++j) {
+            const int idx = j * 256 + lane * 8;
+            const float* p = wbuf + wphys(idx);
+            const float4 t0 = *reinterpret_cast<const float4*>(p);
+            const float4 t1 = *reinterpret_cast<const float4*>(p + 4);
+            const float v[8] = {t0.x * scale, t0.y * scale, t0.z * scale, t0.w * scale,
+                                t1.x * scale, t1.y * scale, t1.z * scale, t1.w * scale};
+            if (base + idx + 8 <= total) {
+                store8<T>(y + base + idx, v);
+            } else {
+#pragma unroll
+                for (int e = 0; e < 8; ++e)
+                    if (base + idx + e < total) store_from_float<T>(y, base + idx + e, v[e]);
+            }
+        }
+        __syncwarp();
+    }
+}
+
+// K == 1, chunk length P = W * 1024 with W = 2, 4 or 8: a CTA of W warps owns one chunk.  Every warp transforms
+// its 1024-element quarter over index bits 0-9 (32 registers per lane, so many warps stay resident and hide
+// the load latency); after a CTA barrier a last radix-W pass over bits 10+ combines the W slices position by
+// position and writes the result with 16-byte stores.
+template <typename T, int W>
+__global__ void __launch_bounds__(32 * W) fwht_split_kernel(const T* __restrict__ x, T* __restrict__ y,
+                                                            int64_t nchunks, float scale) {
+    constexpr int S = 1024;
+    constexpr int slice = warp_slice_floats(S);
+    extern __shared__ float wsm[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t total = nchunks * (int64_t)(W * S);
+    for (int64_t ch = blockIdx.x; ch < nchunks; ch += gridDim.x) {
+        const int64_t base = ch * (int64_t)(W * S);
+        __syncthreads();                                        // previous chunk fully written out
+        warp_transform<T, 10>(x, base + (int64_t)warp * S, total, 10, wsm + warp * slice, lane);
+        __syncthreads();
+        // thread t handles positions 8t .. 8t+7 of every slice (W * 32 threads cover 1024 positions when W = 4;
+        // other W loop)
+        for (int p = 8 * threadIdx.x; p < S; p += 8 * 32 * W) {
+            float v[W][8];
+#pragma unroll
+            for (int w = 0; w < W; ++w) {
+                const float* q = wsm + w * slice + wphys(p);
+                const float4 t0 = *reinterpret_cast<const float4*>(q);
+                const float4 t1 = *reinterpret_cast<const float4*>(q + 4);
+                v[w][0] = t0.x; v[w][1] = t0.y; v[w][2] = t0.z; v[w][3] = t0.w;
+                v[w][4] = t1.x; v[w][5] = t1.y; v[w][6] = t1.z; v[w][7] = t1.w;
+            }
+#pragma unroll
+            for (int h = 1; h < W; h <<= 1)
+#pragma unroll
+                for (int w = 0; w < W; ++w)
+                    if ((w & h) == 0) {
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) {
+                            const float a = v[w][e], b = v[w | h][e];
+                            v[w][e] = a + b;
+                            v[w | h][e] = a - b;
+                        }
+                    }
+#pragma unroll
+            for (int w = 0; w < W; ++w) {
+                float o[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) o[e] = v[w][e] * scale;
+                store8<T>(y + base + (int64_t)w * S + p, o);
+            }
+        }
+    }
+}
+
+template <typename T>
+__device__ __forceinline__ void store2(T* p, float a, float b);
+template <>
+__device__ __forceinline__ void store2<float>(float* p, float a, float b) { *reinterpret_cast<float2*>(p) = make_float2(a, b); }
+template <>
+__device__ __forceinline__ void store2<__nv_bfloat16>(__nv_bfloat16* p, float a, float b) {
+    *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b);
+}
+template <>
+__device__ __forceinline__ void store2<__half>(__half* p, float a, float b) {
+    *reinterpret_cast<__half2*>(p) = __floats2half2_rn(a, b);
+}
+
+// two neighbouring positions of every chunk -> K outputs each; hadK entries are +-1, so the products are exact
+template <typename T, int KK>
+__device__ __forceinline__ void mix_pair(const float* buf, int slice, const float* hk, int p, int P, T* yrow,
+                                         float scale, int K) {
+    float v0[KK], v1[KK];
+#pragma unroll
+    for (int k = 0; k < KK; ++k) {
+        if (k < K) {
+            const float2 t = *reinterpret_cast<const float2*>(buf + k * slice + wphys(p));
+            v0[k] = t.x;
+            v1[k] = t.y;
+        }
+    }
+    for (int ko = 0; ko < K; ++ko) {
+        float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+        for (int k = 0; k < KK; ++k) {
+            if (k < K) {
+                const float h = hk[ko * K + k];
+                s0 = fmaf(h, v0[k], s0);
+                s1 = fmaf(h, v1[k], s1);
+            }
+        }
+        store2<T>(yrow + (int64_t)ko * P + p, s0 * scale, s1 * scale);
+    }
+}
+
+// K > 1 with chunk length P = S: one CTA per row; warps transform the K chunks into shared memory, then
+// all threads mix the chunks position by position.
+template <typename T, int LOGS>
+__global__ void __launch_bounds__(32 * kMixWarps) fwht_mix_kernel(const T* __restrict__ x, T* __restrict__ y,
+                                                                     int64_t rows, int K,
+                                                                     const float* __restrict__ hadK, float scale) {
+    constexpr int S = 1 << LOGS;
+    constexpr int slice = warp_slice_floats(S);
+    extern __shared__ float wsm[];
+    float* hk = wsm + (size_t)K * slice;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int e = threadIdx.x; e < K * K; e += blockDim.x) hk[e] = hadK[e];
+    const int64_t n = (int64_t)K * S;
+    for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+        __syncthreads();                                        // previous row's mix has finished reading
+        for (int c = warp; c < K; c += kMixWarps)
+            warp_transform<T, LOGS>(x, row * n + (int64_t)c * S, (rows * n), LOGS, wsm + (size_t)c * slice, lane);
+        __syncthreads();
+        T* yrow = y + row * n;
+        for (int p = 2 * threadIdx.x; p < S; p += 2 * blockDim.x) {
+            if (K <= 12) mix_pair<T, 12>(wsm, slice, hk, p, S, yrow, scale, K);
+            else if (K <= 20) mix_pair<T, 20>(wsm, slice, hk, p, S, yrow, scale, K);
+            else mix_pair<T, 28>(wsm, slice, hk, p, S, yrow, scale, K);
+        }
+    }
+}
+
+}  // namespace fwht
+}  // namespace rq

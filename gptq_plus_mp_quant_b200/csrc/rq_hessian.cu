@@ -31,14 +31,21 @@ constexpr int kTmemCols = 512;   // two 128x256 fp32 accumulators
 constexpr int kWindowTokens = 128;   // tokens accumulated on the tensor core before a round-to-nearest add
 constexpr int kPackTile = 64;    // pack kernel tile edge (tokens and channels)
 
-template <int BK, int NPROD>
+template <int BK, int NPROD, bool WIDE_Y = false>
 struct Cfg {
     static constexpr int kLayout = BK == 64 ? 2 : 4;              // UMMA swizzle mode: 128 B / 64 B
     static constexpr int kSBO = 8 * BK * 2;                        // bytes between 8-row groups
     static constexpr int kATile = BM * BK * 2;
     static constexpr int kBTile = BN * BK * 2;
-    static constexpr int kAPlanes = NPROD == 3 ? 2 : 1;
-    static constexpr int kStageBytes = kAPlanes * kATile + 2 * kBTile;
+    // NPROD == 3 (fp32 / fp16 X):  A side (128 rows) = X_hi, X_lo;  B side (256 rows) = Y_hi, Y_lo.
+    // NPROD == 2 (bf16 X, X_lo = 0): the two-plane operand Y goes on the narrow A side and the single
+    // plane X_hi on the wide B side, 64 KB per stage instead of 80 KB: less L2->SM traffic per MMA
+    // and room for a third stage.
+    // WIDE_Y keeps Y on the wide side also for NPROD == 2 (80 KB per stage), for comparison.
+    static constexpr bool kSwap = NPROD == 2 && !WIDE_Y;
+    static constexpr int kAPlanes = (NPROD == 3 || kSwap) ? 2 : 1;
+    static constexpr int kBPlanes = (NPROD == 3 || !kSwap) ? 2 : 1;
+    static constexpr int kStageBytes = kAPlanes * kATile + kBPlanes * kBTile;
     static constexpr int kStages = (200 * 1024) / kStageBytes;
     static constexpr int kBarBytes = 256;
     static constexpr int kSmemBytes = kStages * kStageBytes + kBarBytes + 1024;   // +1024: alignment slack
@@ -147,12 +154,12 @@ struct Bars {
 };
 static_assert(sizeof(Bars) <= 256, "barrier block");
 
-template <int BK, int NPROD>
+template <int BK, int NPROD, bool WIDE_Y>
 __global__ void __launch_bounds__(kThreads, 1)
 umma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
             float* __restrict__ H, int C, int G, int MT, int NT, int kblocks, int a_plane, int b_plane0,
             float alpha, float beta, int* __restrict__ status) {
-    using K = Cfg<BK, NPROD>;
+    using K = Cfg<BK, NPROD, WIDE_Y>;
     constexpr int WIN = kWindowTokens / BK;                              // k-blocks per accumulation window
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
@@ -205,15 +212,21 @@ umma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CU
                     const uint32_t fb = smem_u32(&bars->full[s]);
                     uint32_t dst = tiles + s * K::kStageBytes;
                     mbar_expect_tx(fb, K::kStageBytes);
-                    tma_load_3d(dst, &mapA, fb, kb * BK, i * BM, a_plane);
-                    dst += K::kATile;
                     if (NPROD == 3) {
-                        tma_load_3d(dst, &mapA, fb, kb * BK, i * BM, a_plane + 1);
-                        dst += K::kATile;
+                        tma_load_3d(dst, &mapA, fb, kb * BK, i * BM, a_plane);
+                        tma_load_3d(dst + K::kATile, &mapA, fb, kb * BK, i * BM, a_plane + 1);
+                        dst += 2 * K::kATile;
+                        tma_load_3d(dst, &mapB, fb, kb * BK, j * BN, b_plane0 + 2 * g);
+                        tma_load_3d(dst + K::kBTile, &mapB, fb, kb * BK, j * BN, b_plane0 + 2 * g + 1);
+                    } else if (K::kSwap) {
+                        tma_load_3d(dst, &mapA, fb, kb * BK, i * BM, b_plane0 + 2 * g);
+                        tma_load_3d(dst + K::kATile, &mapA, fb, kb * BK, i * BM, b_plane0 + 2 * g + 1);
+                        tma_load_3d(dst + 2 * K::kATile, &mapB, fb, kb * BK, j * BN, a_plane);
+                    } else {
+                        tma_load_3d(dst, &mapA, fb, kb * BK, i * BM, a_plane);
+                        tma_load_3d(dst + K::kATile, &mapB, fb, kb * BK, j * BN, b_plane0 + 2 * g);
+                        tma_load_3d(dst + K::kATile + K::kBTile, &mapB, fb, kb * BK, j * BN, b_plane0 + 2 * g + 1);
                     }
-                    tma_load_3d(dst, &mapB, fb, kb * BK, j * BN, b_plane0 + 2 * g);
-                    dst += K::kBTile;
-                    tma_load_3d(dst, &mapB, fb, kb * BK, j * BN, b_plane0 + 2 * g + 1);
                 }
             }
             if (!ok) {
@@ -254,13 +267,19 @@ umma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CU
                         for (int k = 0; k < BK / UK; ++k) {
                             const uint32_t koff = k * UK * 2;           // bytes along K inside the swizzle row
                             const uint64_t dah = umma_smem_desc(a_hi + koff, K::kSBO, K::kLayout);
+                            const uint64_t dal = umma_smem_desc(a_lo + koff, K::kSBO, K::kLayout);
                             const uint64_t dbh = umma_smem_desc(b_hi + koff, K::kSBO, K::kLayout);
-                            const uint64_t dbl = umma_smem_desc(b_lo + koff, K::kSBO, K::kLayout);
                             // the first MMA of a window overwrites the accumulator; small terms go first
-                            umma_bf16(d_tmem, dah, dbl, idesc, (kb != w * WIN || k != 0) ? 1u : 0u);
+                            const uint32_t keep = (kb != w * WIN || k != 0) ? 1u : 0u;
                             if (NPROD == 3) {
-                                const uint64_t dal = umma_smem_desc(a_lo + koff, K::kSBO, K::kLayout);
+                                const uint64_t dbl = umma_smem_desc(b_lo + koff, K::kSBO, K::kLayout);
+                                umma_bf16(d_tmem, dah, dbl, idesc, keep);
                                 umma_bf16(d_tmem, dal, dbh, idesc, 1u);
+                            } else if (K::kSwap) {
+                                umma_bf16(d_tmem, dal, dbh, idesc, keep);
+                            } else {
+                                const uint64_t dbl = umma_smem_desc(b_lo + koff, K::kSBO, K::kLayout);
+                                umma_bf16(d_tmem, dah, dbl, idesc, keep);
                             }
                             umma_bf16(d_tmem, dah, dbh, idesc, 1u);
                         }
@@ -451,23 +470,23 @@ static int num_sms() {
     return n;
 }
 
-template <int BK, int NPROD>
+template <int BK, int NPROD, bool WIDE_Y = false>
 static int launch_umma(void* planes, int64_t Kc, int C, int G, int nplanes, int b_plane0, float* H, float alpha,
                        float beta, int* status, cudaStream_t st) {
-    using K = Cfg<BK, NPROD>;
+    using K = Cfg<BK, NPROD, WIDE_Y>;
     CUtensorMap mapA, mapB;
     int rc = encode_map(&mapA, planes, Kc, C, nplanes, BK, BM, BK);
     if (rc != RQ_OK) return rc;
     rc = encode_map(&mapB, planes, Kc, C, nplanes, BK, BN, BK);
     if (rc != RQ_OK) return rc;
-    if (cudaFuncSetAttribute(umma_kernel<BK, NPROD>, cudaFuncAttributeMaxDynamicSharedMemorySize, K::kSmemBytes) !=
+    if (cudaFuncSetAttribute(umma_kernel<BK, NPROD, WIDE_Y>, cudaFuncAttributeMaxDynamicSharedMemorySize, K::kSmemBytes) !=
         cudaSuccess)
         return RQ_ERR_CUDA;
     const int MT = (C + BM - 1) / BM, NT = (C + BN - 1) / BN;
     const int total = ((NT - 1) * NT + MT) * G;
     const int grid = total < num_sms() ? total : num_sms();
     prof::Scope timed(RQ_PROF_HESSIAN_UMMA, st);
-    umma_kernel<BK, NPROD><<<grid, kThreads, K::kSmemBytes, st>>>(mapA, mapB, H, C, G, MT, NT, (int)(Kc / BK), 0,
+    umma_kernel<BK, NPROD, WIDE_Y><<<grid, kThreads, K::kSmemBytes, st>>>(mapA, mapB, H, C, G, MT, NT, (int)(Kc / BK), 0,
                                                                   b_plane0, alpha, beta, status);
     return check_launch();
 }
@@ -494,7 +513,7 @@ extern "C" int rq_hessian_accum(const void* x, int x_dtype, int64_t ldx, const f
     if (!x || !H || !workspace || C <= 0 || G <= 0 || G > 8 || N < 0 || ldx < C) return RQ_ERR_INVALID;
     if (!sal && G != 1) return RQ_ERR_INVALID;
     if (x_dtype != RQ_F32 && x_dtype != RQ_BF16 && x_dtype != RQ_F16) return RQ_ERR_INVALID;
-    if (variant != 0 && variant != 1) return RQ_ERR_UNSUPPORTED;
+    if (variant < 0 || variant > 2) return RQ_ERR_UNSUPPORTED;
     if (reinterpret_cast<uintptr_t>(workspace) % 1024 != 0) return RQ_ERR_INVALID;
     if (N == 0) return RQ_OK;
     cudaStream_t st = as_stream(stream);
@@ -541,7 +560,10 @@ extern "C" int rq_hessian_accum(const void* x, int x_dtype, int64_t ldx, const f
             if (rc != RQ_OK) return rc;
         }
         const float b = (n0 == 0) ? beta : 1.f;
-        if (variant == 0)
+        if (variant == 2)
+            rc = nprod == 3 ? launch_umma<64, 3>(planes, Kc, C, G, nplanes, b_plane0, H, alpha, b, status, st)
+                            : launch_umma<64, 2, true>(planes, Kc, C, G, nplanes, b_plane0, H, alpha, b, status, st);
+        else if (variant == 0)
             rc = nprod == 3 ? launch_umma<64, 3>(planes, Kc, C, G, nplanes, b_plane0, H, alpha, b, status, st)
                             : launch_umma<64, 2>(planes, Kc, C, G, nplanes, b_plane0, H, alpha, b, status, st);
         else

@@ -44,11 +44,38 @@ struct Params {
     int tri;                       // 1: skip tiles that lie wholly below the diagonal (i0 >= j0 + BN)
     int kmode;                     // 0: all k;  1: k >= i0 (A[m,k] = 0 for k < m);  2: k < j0 + BN (B[n,k] = 0 for k > n);
                                    // 3: k >= j0 (B[n,k] = 0 for k < n)
-    int batch;
+    int batch;                     // total batch count = nz1 * (number of outer batches)
     float* C; long long ldc, c_z;
     const float* Aux; long long ldaux, aux_z;
     float alpha, beta, gamma;
+    // optional inner batch (z = z1 + nz1 * z2; the *_z fields above step with z2): used for the block pairs
+    // of one level of the triangular inverse.  n_limit > 0 clips N per inner batch to n_limit - z1 * n_limit_z1.
+    int nz1 = 1;
+    int a_row_z1 = 0, b_row_z1 = 0, a_k_z1 = 0, b_k_z1 = 0;
+    long long c_z1 = 0;
+    int n_limit = 0, n_limit_z1 = 0;
 };
+
+struct TileCtx {
+    int i, j, z1, z2, n_eff;
+    bool skip;
+};
+
+__device__ __forceinline__ TileCtx decode(const Params& p, int t, int MT, int NT) {
+    TileCtx c;
+    c.i = t % MT;
+    c.j = (t / MT) % NT;
+    const int z = t / (MT * NT);
+    c.z1 = z % p.nz1;
+    c.z2 = z / p.nz1;
+    c.n_eff = p.N;
+    if (p.n_limit > 0) {
+        const int lim = p.n_limit - c.z1 * p.n_limit_z1;
+        if (lim < c.n_eff) c.n_eff = lim;
+    }
+    c.skip = (p.tri && c.i * BM >= (c.j + 1) * BN) || c.j * BN >= c.n_eff;
+    return c;
+}
 
 struct Bars {
     uint64_t full[kStages];
@@ -117,22 +144,25 @@ split_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
             uint32_t it = 0;
             bool ok = true;
             for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-                const int i = t % MT, j = (t / MT) % NT, z = t / (MT * NT);
-                if (p.tri && i * BM >= (j + 1) * BN) continue;
+                const TileCtx c = decode(p, t, MT, NT);
+                if (c.skip) continue;
+                const int i = c.i, j = c.j;
                 int kb0, kb1;
                 tile_k_range(p, i * BM, j * BN, kb0, kb1);
-                const int arow = p.a_row0 + z * p.a_row_z + i * BM, brow = p.b_row0 + z * p.b_row_z + j * BN;
-                const int apl = p.a_plane + z * p.a_plane_z, bpl = p.b_plane + z * p.b_plane_z;
+                const int arow = p.a_row0 + c.z2 * p.a_row_z + c.z1 * p.a_row_z1 + i * BM;
+                const int brow = p.b_row0 + c.z2 * p.b_row_z + c.z1 * p.b_row_z1 + j * BN;
+                const int apl = p.a_plane + c.z2 * p.a_plane_z, bpl = p.b_plane + c.z2 * p.b_plane_z;
+                const int ak0 = p.a_k0 + c.z1 * p.a_k_z1, bk0 = p.b_k0 + c.z1 * p.b_k_z1;
                 for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
                     if (!mbar_wait(smem_u32(&bars->empty[s]), ph ^ 1u, abort_flag)) { ok = false; break; }
                     const uint32_t fb = smem_u32(&bars->full[s]);
                     const uint32_t dst = tiles + s * kStageBytes;
                     mbar_expect_tx(fb, kStageBytes);
-                    tma_load_3d(dst, &mapA, fb, p.a_k0 + kb * BK, arow, apl);
-                    tma_load_3d(dst + kATile, &mapA, fb, p.a_k0 + kb * BK, arow, apl + 1);
-                    tma_load_3d(dst + 2 * kATile, &mapB, fb, p.b_k0 + kb * BK, brow, bpl);
-                    tma_load_3d(dst + 2 * kATile + kBTile, &mapB, fb, p.b_k0 + kb * BK, brow, bpl + 1);
+                    tma_load_3d(dst, &mapA, fb, ak0 + kb * BK, arow, apl);
+                    tma_load_3d(dst + kATile, &mapA, fb, ak0 + kb * BK, arow, apl + 1);
+                    tma_load_3d(dst + 2 * kATile, &mapB, fb, bk0 + kb * BK, brow, bpl);
+                    tma_load_3d(dst + 2 * kATile + kBTile, &mapB, fb, bk0 + kb * BK, brow, bpl + 1);
                 }
             }
             if (!ok) {
@@ -152,10 +182,10 @@ split_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
             uint32_t it = 0, win_iter = 0;
             bool ok = true;
             for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-                const int i = t % MT, j = (t / MT) % NT;
-                if (p.tri && i * BM >= (j + 1) * BN) continue;
+                const TileCtx c = decode(p, t, MT, NT);
+                if (c.skip) continue;
                 int kb0, kb1;
-                tile_k_range(p, i * BM, j * BN, kb0, kb1);
+                tile_k_range(p, c.i * BM, c.j * BN, kb0, kb1);
                 for (int w0 = kb0; w0 < kb1 && ok; w0 += kWindowBlocks, ++win_iter) {
                     const uint32_t acc = win_iter & 1u, acc_ph = (win_iter >> 1) & 1u;
                     if (!mbar_wait(smem_u32(&bars->tempty[acc]), acc_ph ^ 1u, abort_flag)) { ok = false; break; }
@@ -193,8 +223,9 @@ split_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
         uint32_t win_iter = 0;
         bool alive = true;
         for (int t = blockIdx.x; t < total_tiles && alive; t += gridDim.x) {
-            const int i = t % MT, j = (t / MT) % NT, z = t / (MT * NT);
-            if (p.tri && i * BM >= (j + 1) * BN) continue;
+            const TileCtx c = decode(p, t, MT, NT);
+            if (c.skip) continue;
+            const int i = c.i, j = c.j, n_eff = c.n_eff;
             int kb0, kb1;
             tile_k_range(p, i * BM, j * BN, kb0, kb1);
             const int row0 = i * BM + q * 32, row = row0 + lane;
@@ -203,7 +234,7 @@ split_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
 #pragma unroll
             for (int cb = 0; cb < 4; ++cb) {
                 const int col0 = colbase + cb * 32;
-                use[cb] = !(col0 >= p.N || row0 >= p.M || (p.tri && col0 + 31 < row0));
+                use[cb] = !(col0 >= n_eff || row0 >= p.M || (p.tri && col0 + 31 < row0));
             }
             float run[128];
 #pragma unroll
@@ -230,14 +261,14 @@ split_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
             }
             if (!alive) break;
             if (row < p.M) {
-                float* crow = p.C + (long long)z * p.c_z + (long long)row * p.ldc;
-                const float* xrow = p.Aux ? p.Aux + (long long)z * p.aux_z + (long long)row * p.ldaux : nullptr;
+                float* crow = p.C + (long long)c.z2 * p.c_z + (long long)c.z1 * p.c_z1 + (long long)row * p.ldc;
+                const float* xrow = p.Aux ? p.Aux + (long long)c.z2 * p.aux_z + (long long)row * p.ldaux : nullptr;
                 const bool vec_ok = ((reinterpret_cast<uintptr_t>(crow) | (xrow ? reinterpret_cast<uintptr_t>(xrow) : 0)) & 15) == 0;
 #pragma unroll
                 for (int cb = 0; cb < 4; ++cb) {
                     const int col0 = colbase + cb * 32;
                     if (!use[cb]) continue;
-                    if (vec_ok && col0 + 32 <= p.N && p.beta == 1.f) {
+                    if (vec_ok && col0 + 32 <= n_eff && p.beta == 1.f) {
                         const float4* x4 = xrow ? reinterpret_cast<const float4*>(xrow + col0) : nullptr;
 #pragma unroll
                         for (int e = 0; e < 8; ++e) {
@@ -249,7 +280,7 @@ split_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
                             }
                             red_add_v4(crow + col0 + 4 * e, o.x, o.y, o.z, o.w);
                         }
-                    } else if (vec_ok && col0 + 32 <= p.N) {
+                    } else if (vec_ok && col0 + 32 <= n_eff) {
                         float4* c4 = reinterpret_cast<float4*>(crow + col0);
                         const float4* x4 = xrow ? reinterpret_cast<const float4*>(xrow + col0) : nullptr;
 #pragma unroll
@@ -269,7 +300,7 @@ split_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
                     } else {
 #pragma unroll
                         for (int e = 0; e < 32; ++e) {
-                            if (col0 + e < p.N) {
+                            if (col0 + e < n_eff) {
                                 float o = (p.beta != 0.f) ? p.beta * crow[col0 + e] : 0.f;
                                 o += p.alpha * run[cb * 32 + e];
                                 if (xrow) o += p.gamma * xrow[col0 + e];

@@ -39,6 +39,7 @@ def main():
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "f32", "f16"])
     ap.add_argument("--reps", type=int, default=3)
+    ap.add_argument("--variant", type=int, default=0)
     a = ap.parse_args()
     from . import ops
     from .gptq_utils import fasterquant_impl as fi
@@ -52,7 +53,7 @@ def main():
         s = torch.exp(3 * torch.randn(a.tokens, a.G, generator=g, device=dev)).clamp(max=1000.0)
         H = torch.zeros(a.G, a.C, a.C, device=dev)
         act = torch.zeros(a.C, device=dev)
-        ms = _time(lambda: ops.hessian_accum(x, s, H, act), a.reps)
+        ms = _time(lambda: ops.hessian_accum(x, s, H, act, variant=a.variant), a.reps)
         fl = 2.0 * a.tokens * a.C * a.C * a.G
         print(f"hessian C={a.C} G={a.G} tokens={a.tokens} {a.dtype}: {ms:.3f} ms per call, {fl / ms / 1e9:.1f} algorithmic TFLOP/s")
     elif a.case == "fwht":

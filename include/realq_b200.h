@@ -72,7 +72,8 @@ int rq_profile_read(int tag, double* total_ms, long long* launches);
  * workspace: rq_hessian_workspace_bytes(chunk_tokens, C, G, sal != NULL) bytes for the chunk
  * size the caller wants (a multiple of 64; tokens are processed chunk by chunk), 1024-byte aligned.
  * status: optional device int; set to RQ_ERR_TIMEOUT if a device-side wait ran out.
- * variant: 0 = 64-token pipeline stages (128-byte swizzle), 1 = 32-token stages (64-byte swizzle).
+ * variant: 0 = 64-token pipeline stages (128-byte swizzle), 1 = 32-token stages (64-byte swizzle),
+ *          2 = as 0 but with the two-plane operand on the 256-row side also for bf16 input.
  */
 size_t rq_hessian_workspace_bytes(int64_t chunk_tokens, int C, int G, int has_saliency);
 int rq_hessian_accum(const void* x, int x_dtype, int64_t ldx, const float* sal, float* H, float* act_sq,
