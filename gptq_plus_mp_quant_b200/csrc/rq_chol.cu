@@ -5,7 +5,7 @@
 // triangular (a Cholesky factorisation that runs from the last column to the first); then
 // P^-1 = R^-T R^-1, so U = R^-1, an upper-triangular inverse.
 //   phase 1  blocked right-looking "reverse" Cholesky, 128-wide block columns, last to first:
-//            diagonal block factored and inverted in fp64 inside one CTA; panel R_ik = A_ik.inv(R_kk)^T
+//            diagonal block factored and inverted inside one CTA (fp32, register-distributed); panel R_ik = A_ik.inv(R_kk)^T
 //            and trailing update A_ij -= R_ik.R_jk^T as fp32 GEMM tiles;
 //   phase 2  recursive-doubling triangular inverse: inv([[A,B],[0,D]]) = [[A^-1, -A^-1.B.D^-1],[0, D^-1]],
 //            two batched GEMM launches per level.
@@ -72,142 +72,98 @@ __global__ void __launch_bounds__(256) gather_kernel(const float* __restrict__ H
 }
 
 // ------------------------------------------------------------------------------------------
-// Diagonal block k: A_kk = R_kk R_kk^T (R upper) and U_kk = R_kk^-1, both in fp64, stored fp32.
-// One CTA of 512 threads per group.  The 128x128 block is spread over the registers of the CTA:
-// thread (ty, tx) = (tid / 32, tid % 32) owns rows ty + 16a (a < 8) and columns tx + 32b (b < 4).
-// Every elimination step publishes one column (factorisation) or one row (inverse) through shared
-// memory; all updates are register FMAs.
+// Diagonal block k: A_kk = R_kk R_kk^T (R upper) and U_kk = R_kk^-1.  One CTA of 512 threads per group, the
+// block and its inverse in shared memory, fp32 throughout with correctly rounded division and square root: the
+// accuracy class of an fp32 LAPACK potrf / trtri on the block, which is what the reference runs.  (fp64
+// arithmetic runs at 1/64 of the fp32 rate on this part; formulations with fp64 or compensated dot products,
+// with the block spread over registers, and with shared-memory rank-1 updates were all measured slower.)
+// Four lanes share a row (factorisation, left-looking: column c needs t_i = A[i][c] - sum_{l>c} R[i][l] R[c][l])
+// or a column (inverse: U[c][j] = -(sum_{c<l<=j} R[c][l] U[l][j]) / R[c][c]).
 // ------------------------------------------------------------------------------------------
+constexpr int kDiagLd = NB + 4;               // fp32 row stride: rows 4 banks apart
+
 __global__ void __launch_bounds__(kDiagThreads) diag_block_kernel(float* __restrict__ A, float* __restrict__ U, int Cp,
                                                                   int kblk, int* __restrict__ info) {
-    __shared__ double vec[2][NB];          // published column / row, double-buffered by step parity
-    __shared__ double pivot[2];
-    __shared__ double dinv[NB];            // 1 / R[c][c]
-    __shared__ double part[16][NB];        // inverse: partial sums per ty
+    extern __shared__ float dsm[];
+    float* S = dsm;                               // [NB][kDiagLd]  R (upper)
+    float* V = dsm + NB * kDiagLd;                // [NB][kDiagLd]  R^-1 (upper)
+    __shared__ float piv;
     __shared__ int bad;
     const int g = blockIdx.x;
     const int64_t origin = ((int64_t)g * Cp + (int64_t)kblk * NB) * Cp + (int64_t)kblk * NB;
     float* Ab = A + origin;
     float* Ub = U + origin;
     const int tid = threadIdx.x;
-    const int ty = tid >> 5, tx = tid & 31;
+    const int own = tid >> 2, q = tid & 3;        // row (phase 1) / column (phase 2) and quarter of the dot product
     if (tid == 0) bad = 0;
-
-    double v[8][4];
-#pragma unroll
-    for (int a = 0; a < 8; ++a)
-#pragma unroll
-        for (int b = 0; b < 4; ++b) {
-            const int i = ty + 16 * a, j = tx + 32 * b;
-            v[a][b] = (j >= i) ? (double)Ab[(int64_t)i * Cp + j] : 0.0;
-        }
-    __syncthreads();
-
-    // ---- reverse Cholesky: eliminate columns from the last to the first
-    for (int c = NB - 1; c >= 0; --c) {
-        const int par = c & 1;
-#pragma unroll
-        for (int a = 0; a < 8; ++a)
-#pragma unroll
-            for (int b = 0; b < 4; ++b)
-                if (ty + 16 * a == c && tx + 32 * b == c) pivot[par] = v[a][b];
-        __syncthreads();
-        const double p = pivot[par];
-        if (!(p > 0.0) && tid == 0) bad = 1;               // catches <= 0 and NaN
-        const double r = sqrt(p);
-        const double rinv = 1.0 / r;
-        if (tid == 0) dinv[c] = rinv;
-        if (tx == (c & 31)) {                                // owners of column c
-#pragma unroll
-            for (int b = 0; b < 4; ++b) {
-                if (tx + 32 * b == c) {
-#pragma unroll
-                    for (int a = 0; a < 8; ++a) {
-                        const int i = ty + 16 * a;
-                        if (i < c) {
-                            v[a][b] *= rinv;
-                            vec[par][i] = v[a][b];
-                        } else if (i == c) {
-                            v[a][b] = r;
-                        }
-                    }
-                }
-            }
-        }
-        __syncthreads();
-#pragma unroll
-        for (int a = 0; a < 8; ++a) {
-            const int i = ty + 16 * a;
-            if (i < c) {
-                const double ci = vec[par][i];
-#pragma unroll
-                for (int b = 0; b < 4; ++b) {
-                    const int j = tx + 32 * b;
-                    if (j >= i && j < c) v[a][b] -= ci * vec[par][j];
-                }
-            }
-        }
+    for (int e = tid; e < NB * NB; e += kDiagThreads) {
+        const int i = e >> 7, j = e & (NB - 1);
+        S[i * kDiagLd + j] = (j >= i) ? Ab[(int64_t)i * Cp + j] : 0.f;
+        V[i * kDiagLd + j] = 0.f;
     }
     __syncthreads();
 
-    // ---- U = R^-1, rows from the last to the first:
-    //      U[c][c] = 1/R[c][c];  U[c][j] = -(1/R[c][c]) * sum_{l=c+1..j} R[c][l] * U[l][j]
-    double u[8][4];
-#pragma unroll
-    for (int a = 0; a < 8; ++a)
-#pragma unroll
-        for (int b = 0; b < 4; ++b) u[a][b] = 0.0;
+    // ---- phase 1: columns from the last to the first
     for (int c = NB - 1; c >= 0; --c) {
-        const int par = c & 1;
-        if (ty == (c & 15)) {                                // owners of row c publish R[c][:]
-#pragma unroll
-            for (int a = 0; a < 8; ++a)
-                if (ty + 16 * a == c) {
-#pragma unroll
-                    for (int b = 0; b < 4; ++b) vec[par][tx + 32 * b] = v[a][b];
-                }
+        const float* ri = S + own * kDiagLd;
+        const float* rc = S + c * kDiagLd;
+        if ((tid & ~31) >> 2 > c) {                   // none of this warp's 8 rows takes part any more
+            __syncthreads();
+            __syncthreads();
+            continue;
         }
-        __syncthreads();
-        double ps[4] = {0.0, 0.0, 0.0, 0.0};
-#pragma unroll
-        for (int a = 0; a < 8; ++a) {
-            const int l = ty + 16 * a;
-            if (l > c) {
-                const double rl = vec[par][l];
-#pragma unroll
-                for (int b = 0; b < 4; ++b) ps[b] += rl * u[a][b];     // u[l][j] is zero for l > j
+        float acc = 0.f;
+        if (own <= c) {
+            float p0 = 0.f, p1 = 0.f;                 // two chains
+#pragma unroll 4
+            for (int l = c + 1 + q; l < NB; l += 8) {
+                p0 = fmaf(ri[l], rc[l], p0);
+                if (l + 4 < NB) p1 = fmaf(ri[l + 4], rc[l + 4], p1);
             }
+            acc = p0 + p1;
         }
-#pragma unroll
-        for (int b = 0; b < 4; ++b) part[ty][tx + 32 * b] = ps[b];
+        acc += __shfl_xor_sync(0xffffffffu, acc, 1);  // executed by every lane of the warp
+        acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+        const float t = __fsub_rn(ri[c], acc);
+        if (own == c && q == 0) {
+            if (!(t > 0.f)) bad = 1;                  // catches <= 0 and NaN
+            piv = __fsqrt_rn(t);
+        }
         __syncthreads();
-        if (ty == (c & 15)) {
-            const double dc = dinv[c];
-#pragma unroll
-            for (int a = 0; a < 8; ++a)
-                if (ty + 16 * a == c) {
-#pragma unroll
-                    for (int b = 0; b < 4; ++b) {
-                        const int j = tx + 32 * b;
-                        double sum = 0.0;
-#pragma unroll
-                        for (int t = 0; t < 16; ++t) sum += part[t][j];
-                        u[a][b] = (j > c) ? -dc * sum : (j == c ? dc : 0.0);
-                    }
+        if (own <= c && q == 0) S[own * kDiagLd + c] = (own == c) ? piv : __fdiv_rn(t, piv);
+        __syncthreads();
+    }
+
+    // ---- phase 2: inverse, one column per lane quad, no CTA-wide dependency
+    {
+        const int j = own;
+        if (q == 0) V[j * kDiagLd + j] = __fdiv_rn(1.f, S[j * kDiagLd + j]);
+        __syncwarp();
+        const int jmax = (tid | 31) >> 2;             // last column handled by this warp: uniform trip count
+        for (int c = jmax - 1; c >= 0; --c) {
+            const float* rc = S + c * kDiagLd;
+            float acc = 0.f;
+            if (c < j) {
+                float p0 = 0.f, p1 = 0.f;
+#pragma unroll 4
+                for (int l = c + 1 + q; l <= j; l += 8) {
+                    p0 = fmaf(rc[l], V[l * kDiagLd + j], p0);
+                    if (l + 4 <= j) p1 = fmaf(rc[l + 4], V[(l + 4) * kDiagLd + j], p1);
                 }
+                acc = p0 + p1;
+            }
+            acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+            acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+            if (q == 0 && c < j) V[c * kDiagLd + j] = __fdiv_rn(-acc, rc[c]);
+            __syncwarp();
         }
-        // the next step publishes into the other buffer and rewrites `part` only after its own barrier
     }
     __syncthreads();
-
-#pragma unroll
-    for (int a = 0; a < 8; ++a)
-#pragma unroll
-        for (int b = 0; b < 4; ++b) {
-            const int i = ty + 16 * a, j = tx + 32 * b;
-            Ab[(int64_t)i * Cp + j] = (j >= i) ? (float)v[a][b] : 0.f;
-            Ub[(int64_t)i * Cp + j] = (j >= i) ? (float)u[a][b] : 0.f;
-        }
+    for (int e = tid; e < NB * NB; e += kDiagThreads) {
+        const int i = e >> 7, j = e & (NB - 1);
+        Ab[(int64_t)i * Cp + j] = (j >= i) ? S[i * kDiagLd + j] : 0.f;
+        Ub[(int64_t)i * Cp + j] = (j >= i) ? V[i * kDiagLd + j] : 0.f;
+    }
     if (tid == 0 && bad) atomicCAS(&info[g], 0, kblk + 1);
 }
 
@@ -364,11 +320,14 @@ extern "C" int rq_chol_hinv(const float* H, const int64_t* perm, const float* da
     int rc = check_launch();
     if (rc != RQ_OK) return rc;
 
+    const size_t diag_smem = (size_t)2 * NB * kDiagLd * sizeof(float);
+    if (cudaFuncSetAttribute(diag_block_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)diag_smem) != cudaSuccess)
+        return RQ_ERR_CUDA;
     // phase 1: block columns from the last to the first
     for (int k = nblk - 1; k >= 0; --k) {
         {
             prof::Scope t1(RQ_PROF_CHOL_DIAG, st);
-            diag_block_kernel<<<G, kDiagThreads, 0, st>>>(A, Hinv, Cp, k, info);
+            diag_block_kernel<<<G, kDiagThreads, diag_smem, st>>>(A, Hinv, Cp, k, info);
         }
         if (k > 0) {
             {

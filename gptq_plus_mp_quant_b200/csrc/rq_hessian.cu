@@ -59,7 +59,8 @@ __device__ __forceinline__ void split_bf16(float v, __nv_bfloat16& hi, __nv_bflo
     lo = __float2bfloat16_rn(v - __bfloat162float(hi));
 }
 
-// grid (ceil(C/64), Kc/64), 256 threads.  planes: [P][C][Kc] bf16, P = 2 (no saliency) or 2+2G.
+// grid (Kc/64, ceil(C/64)), 256 threads: token tiles vary fastest, so that concurrently running blocks
+// extend the same plane rows (contiguous DRAM pages on the write side).  planes: [P][C][Kc] bf16, P = 2 (no saliency) or 2+2G.
 // partial: [Kc/64][C] per-tile sums of x^2 (may be NULL).
 template <typename T>
 __global__ void __launch_bounds__(256) pack_kernel(const T* __restrict__ x, int64_t ldx,
@@ -68,8 +69,8 @@ __global__ void __launch_bounds__(256) pack_kernel(const T* __restrict__ x, int6
                                                    int write_xlo) {
     __shared__ float xs[kPackTile][kPackTile + 1];
     __shared__ float ss[kPackTile][8];
-    const int c0 = blockIdx.x * kPackTile;
-    const int t0 = blockIdx.y * kPackTile;
+    const int t0 = blockIdx.x * kPackTile;
+    const int c0 = blockIdx.y * kPackTile;
     const int tid = threadIdx.x;
 
     {   // load: 64 consecutive channels of one token per pass of 64 threads
@@ -118,7 +119,7 @@ __global__ void __launch_bounds__(256) pack_kernel(const T* __restrict__ x, int6
             float sq = xa * xa + xb * xb;
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
-            if (lane == 0) partial[(int64_t)blockIdx.y * C + c] = sq;
+            if (lane == 0) partial[(int64_t)blockIdx.x * C + c] = sq;
         }
     }
 }
@@ -538,7 +539,7 @@ extern "C" int rq_hessian_accum(const void* x, int x_dtype, int64_t ldx, const f
         float* partial = act_sq ? reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) + plane_bytes) : nullptr;
         const uint8_t* xp = reinterpret_cast<const uint8_t*>(x) + (size_t)n0 * (size_t)ldx * esz;
         const float* sp = has_sal ? sal + n0 * G : nullptr;
-        dim3 pgrid((C + kPackTile - 1) / kPackTile, (unsigned)(Kc / kPackTile));
+        dim3 pgrid((unsigned)(Kc / kPackTile), (unsigned)((C + kPackTile - 1) / kPackTile));
         const int write_xlo = (nprod == 3 || !has_sal) ? 1 : 0;     // without saliency X_lo doubles as Y_lo
         {
         prof::Scope timed(RQ_PROF_HESSIAN_PACK, st);
