@@ -149,6 +149,10 @@ struct BlockArgs {
     const int* colgrp;       // mode 1: [C] group of (permuted) column j
     float* scale_blk;        // mode 2: [C/gs_dyn blocks..., R] scales found on the fly (output)
     int R, C, Cp, G, i1, count;
+    const float* anchor;     // [R, C] weights as they were before the first block (surrogate modes)
+    const float* beta;       // [R] (surrogate modes)
+    int inner_mode;          // 0 frozen, 1 surrogate_block, 2 surrogate_online: GHinv_eff = GHinv + beta*(W - anchor)
+    int atomic;              // quantize the whole block from its start values, then solve for the errors
     int mode;                // 0 per-row scale, 1 static groups, 2 dynamic groups
     int dyn_gs;              // mode 2: group width (divides BS)
     int sym;                 // mode 2: range rule
@@ -174,7 +178,9 @@ __global__ void __launch_bounds__(kBlockThreads) block_kernel(const BlockArgs p)
     const int r = g * Rg + row_in_group;
     const int64_t base = (int64_t)r * p.C + p.i1;
 
-    float w[4], gh[4], z[4], sc[4], qv[4], cv[4], ev[4];
+    float w[4], gh[4], z[4], sc[4], qv[4], cv[4], ev[4], dref[4];
+    const bool surrogate = PLUS && p.inner_mode != 0;
+    const float bt = surrogate ? p.beta[r] : 0.f;
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
         const int col = lane + 32 * k;
@@ -184,6 +190,9 @@ __global__ void __launch_bounds__(kBlockThreads) block_kernel(const BlockArgs p)
         z[k] = (PLUS && in) ? p.Z[base + col] : 0.f;
         qv[k] = 0.f; cv[k] = 0.f; ev[k] = 0.f;
         sc[k] = 1.f;
+        // surrogate_block keeps (W_block_start - W_anchor); surrogate_online needs the anchor itself
+        dref[k] = (surrogate && in) ? p.anchor[base + col] : 0.f;
+        if (surrogate && p.inner_mode == 1) dref[k] = __fsub_rn(w[k], dref[k]);
     }
     if (p.mode == 0) {
         const float s = p.scale_row[r];
@@ -226,6 +235,40 @@ __global__ void __launch_bounds__(kBlockThreads) block_kernel(const BlockArgs p)
         }
     }
 
+    // effective first-order term of column k right now (the reference's _current_ghinv)
+    auto effective = [&](int k) -> float {
+        if (!surrogate) return gh[k];
+        const float diff = (p.inner_mode == 1) ? dref[k] : __fsub_rn(w[k], dref[k]);
+        return __fadd_rn(gh[k], __fmul_rn(bt, diff));
+    };
+    if (p.atomic) {
+        // whole block quantized from its start values; Err solves  Err . Hinv1 = W_start - Q - GHinv_eff
+        float res[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float qi = quant_code(w[k], sc[k], p.qlo, p.qhi);
+            cv[k] = qi;
+            qv[k] = __fmul_rn(sc[k], qi);
+            res[k] = __fsub_rn(w[k], qv[k]);
+            if (PLUS) res[k] = __fsub_rn(res[k], effective(k));
+        }
+#pragma unroll
+        for (int slot = 0; slot < 4; ++slot) {
+            const int ibase = slot * 32;
+            if (ibase >= p.count) break;
+            const int iend = (p.count - ibase < 32) ? p.count - ibase : 32;
+            for (int o = 0; o < iend; ++o) {
+                const int i = ibase + o;
+                const float x = __fdiv_rn(__shfl_sync(0xffffffffu, res[slot], o), Hs[i * BS + i]);
+                if (lane == o) ev[slot] = x;
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const int col = lane + 32 * k;
+                    if (col > i && col < p.count) res[k] = __fsub_rn(res[k], __fmul_rn(x, Hs[i * BS + col]));
+                }
+            }
+        }
+    } else {
 #pragma unroll
     for (int slot = 0; slot < 4; ++slot) {
         const int ibase = slot * 32;
@@ -240,8 +283,11 @@ __global__ void __launch_bounds__(kBlockThreads) block_kernel(const BlockArgs p)
             const float d = Hs[i * BS + i];
             float err;
             float zi = 0.f;
+            float eff[4] = {0.f, 0.f, 0.f, 0.f};
             if (PLUS) {
-                const float ghi = __shfl_sync(0xffffffffu, gh[slot], o);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) eff[k] = effective(k);
+                const float ghi = __shfl_sync(0xffffffffu, eff[slot], o);
                 zi = __shfl_sync(0xffffffffu, z[slot], o);
                 err = __fdiv_rn(__fsub_rn(__fsub_rn(wi, q), ghi), d);
             } else {
@@ -255,13 +301,14 @@ __global__ void __launch_bounds__(kBlockThreads) block_kernel(const BlockArgs p)
                     const float h = Hs[i * BS + col];
                     float upd = __fmul_rn(err, h);
                     if (PLUS) {
-                        upd = __fadd_rn(upd, gh[k]);
+                        upd = __fadd_rn(upd, eff[k]);
                         gh[k] = __fsub_rn(gh[k], __fmul_rn(zi, h));
                     }
                     w[k] = __fsub_rn(w[k], upd);
                 }
             }
         }
+    }
     }
 
 #pragma unroll
@@ -284,6 +331,20 @@ __global__ void __launch_bounds__(kBlockThreads) block_kernel(const BlockArgs p)
                 p.Ehi[(int64_t)r * BS + col] = __float2bfloat16_rn(0.f);
                 p.Elo[(int64_t)r * BS + col] = __float2bfloat16_rn(0.f);
             }
+        }
+    }
+}
+
+// outer surrogate term: the lazy update subtracts count * beta * (W - anchor) as well, taken at the weights
+// before the update (gptq_plus_utils.py:1502-1513 with outer mode surrogate_block); applied as a pre-pass.
+__global__ void __launch_bounds__(256) surrogate_outer_kernel(float* __restrict__ Wp, const float* __restrict__ anchor,
+                                                              const float* __restrict__ beta, int R, int C, int i2,
+                                                              float count) {
+    for (int r = blockIdx.y; r < R; r += gridDim.y) {
+        const float cb = count * beta[r];
+        for (int j = i2 + blockIdx.x * 256 + threadIdx.x; j < C; j += gridDim.x * 256) {
+            const int64_t e = (int64_t)r * C + j;
+            Wp[e] = __fsub_rn(Wp[e], __fmul_rn(cb, __fsub_rn(Wp[e], anchor[e])));
         }
     }
 }
@@ -373,7 +434,8 @@ extern "C" int rq_gptqplus_terms(const float* Gp, const float* Hinv, int R, int 
 static int fq_block_launch(float* Wp, float* GH, const float* Z, const float* Hinv, float* Q, int8_t* codes,
                            float* Eeff, __nv_bfloat16* Ehi, __nv_bfloat16* Elo, const float* scale_row,
                            const float* scale_tab, const int* colgrp, float* scale_blk, int R, int C, int G, int i1,
-                           int count, int mode, int dyn_gs, int sym, int maxq, int plus, void* stream) {
+                           int count, int mode, int dyn_gs, int sym, int maxq, int plus, const float* anchor,
+                           const float* beta, int inner_mode, int atomic, void* stream) {
     using namespace rq::fq;
     if (!Wp || !Hinv || !Q || !codes || !Eeff || R <= 0 || C <= 0 || G <= 0 || R % G != 0) return RQ_ERR_INVALID;
     if (i1 < 0 || count <= 0 || count > BS || i1 + count > C) return RQ_ERR_INVALID;
@@ -382,8 +444,10 @@ static int fq_block_launch(float* Wp, float* GH, const float* Z, const float* Hi
     if (mode == 1 && (!scale_tab || !colgrp)) return RQ_ERR_INVALID;
     if (mode == 2 && (!scale_blk || dyn_gs <= 0 || BS % dyn_gs != 0 || i1 % dyn_gs != 0)) return RQ_ERR_INVALID;
     if (mode < 0 || mode > 2 || maxq <= 0 || maxq > 127) return RQ_ERR_INVALID;
+    if (inner_mode < 0 || inner_mode > 2 || (inner_mode != 0 && (!plus || !anchor || !beta))) return RQ_ERR_INVALID;
     cudaStream_t st = as_stream(stream);
     BlockArgs p;
+    p.anchor = anchor; p.beta = beta; p.inner_mode = inner_mode; p.atomic = atomic ? 1 : 0;
     p.Wp = Wp; p.GH = GH; p.Z = Z; p.Hinv = Hinv; p.Q = Q; p.codes = codes; p.Eeff = Eeff;
     p.Ehi = Ehi; p.Elo = Elo;
     p.scale_row = scale_row; p.scale_tab = scale_tab; p.colgrp = colgrp; p.scale_blk = scale_blk;
@@ -409,13 +473,22 @@ static int fq_block_launch(float* Wp, float* GH, const float* Z, const float* Hi
 extern "C" int rq_fq_block(float* Wp, float* GH, const float* Z, const float* Hinv, float* Q, int8_t* codes,
                            float* Eeff, const float* scale_row, const float* scale_tab, const int* colgrp,
                            float* scale_blk, int R, int C, int G, int i1, int count, int mode, int dyn_gs, int sym,
-                           int maxq, int plus, void* stream) {
+                           int maxq, int plus, const float* anchor, const float* beta, int inner_mode, int atomic,
+                           void* stream) {
     return fq_block_launch(Wp, GH, Z, Hinv, Q, codes, Eeff, nullptr, nullptr, scale_row, scale_tab, colgrp, scale_blk, R,
-                           C, G, i1, count, mode, dyn_gs, sym, maxq, plus, stream);
+                           C, G, i1, count, mode, dyn_gs, sym, maxq, plus, anchor, beta, inner_mode, atomic, stream);
+}
+
+static int surrogate_outer(float* Wp, const float* anchor, const float* beta, int R, int C, int i2, int count,
+                           cudaStream_t st) {
+    dim3 grid((unsigned)((C - i2 + 1023) / 1024), (unsigned)(R < 65535 ? R : 65535));
+    fq::surrogate_outer_kernel<<<grid, 256, 0, st>>>(Wp, anchor, beta, R, C, i2, (float)count);
+    return check_launch();
 }
 
 extern "C" int rq_fq_lazy_update(float* Wp, float* GH, const float* Z, const float* Eeff, const float* Hinv, int R,
-                                 int C, int G, int i1, int count, int plus, void* stream) {
+                                 int C, int G, int i1, int count, int plus, const float* anchor, const float* beta,
+                                 int outer_surrogate, void* stream) {
     if (!Wp || !Eeff || !Hinv || R <= 0 || C <= 0 || G <= 0 || R % G != 0 || count <= 0 || count > fq::BS)
         return RQ_ERR_INVALID;
     if (plus && (!GH || !Z)) return RQ_ERR_INVALID;
@@ -426,6 +499,11 @@ extern "C" int rq_fq_lazy_update(float* Wp, float* GH, const float* Z, const flo
     const int Rg = R / G;
     dim3 grid((unsigned)((Rg + gemm::TM - 1) / gemm::TM), (unsigned)((C - i2 + gemm::TN - 1) / gemm::TN), (unsigned)G);
     prof::Scope timed(RQ_PROF_LAZY, st);
+    if (outer_surrogate) {
+        if (!plus || !anchor || !beta) return RQ_ERR_INVALID;
+        const int rc0 = surrogate_outer(Wp, anchor, beta, R, C, i2, count, st);
+        if (rc0 != RQ_OK) return rc0;
+    }
     fq::lazy_kernel<<<grid, gemm::kThreads, gemm::kSmemBytes, st>>>(Wp, GH, Z, Eeff, Hinv, R, C, Cp, G, i1, count, 1, plus);
     if (plus)
         fq::lazy_kernel<<<grid, gemm::kThreads, gemm::kSmemBytes, st>>>(Wp, GH, Z, Eeff, Hinv, R, C, Cp, G, i1, count, 2, plus);
@@ -459,13 +537,15 @@ extern "C" int rq_fq_finish(const float* Q, const int8_t* codes, const int64_t* 
 extern "C" int rq_fq_run(float* Wp, float* GH, const float* Z, const float* Hinv, float* Q, int8_t* codes,
                          float* Eeff, const float* scale_row, const float* scale_tab, const int* colgrp,
                          float* scale_blk, int R, int C, int G, int mode, int dyn_gs, int sym, int maxq, int plus,
-                         void* stream) {
+                         const float* anchor, const float* beta, int inner_mode, int atomic, void* stream) {
     for (int i1 = 0; i1 < C; i1 += fq::BS) {
         const int count = (C - i1 < fq::BS) ? C - i1 : fq::BS;
+        const int last = i1 + count >= C;
         int rc = rq_fq_block(Wp, GH, Z, Hinv, Q, codes, Eeff, scale_row, scale_tab, colgrp, scale_blk, R, C, G, i1,
-                             count, mode, dyn_gs, sym, maxq, plus, stream);
+                             count, mode, dyn_gs, sym, maxq, plus, anchor, beta, inner_mode, (atomic && !last) ? 1 : 0,
+                             stream);
         if (rc != RQ_OK) return rc;
-        rc = rq_fq_lazy_update(Wp, GH, Z, Eeff, Hinv, R, C, G, i1, count, plus, stream);
+        rc = rq_fq_lazy_update(Wp, GH, Z, Eeff, Hinv, R, C, G, i1, count, plus, anchor, beta, inner_mode != 0, stream);
         if (rc != RQ_OK) return rc;
     }
     return RQ_OK;
@@ -575,7 +655,8 @@ extern "C" int rq_gptqplus_terms_tc(const float* Gp, const float* Hinv, int R, i
 extern "C" int rq_fq_run_tc(float* Wp, float* GH, const float* Z, const float* Hinv, float* Q, int8_t* codes,
                             float* Eeff, const float* scale_row, const float* scale_tab, const int* colgrp,
                             float* scale_blk, int R, int C, int G, int mode, int dyn_gs, int sym, int maxq, int plus,
-                            void* workspace, size_t workspace_bytes, int* status, void* stream) {
+                            const float* anchor, const float* beta, int inner_mode, int atomic, void* workspace,
+                            size_t workspace_bytes, int* status, void* stream) {
     using namespace rq::tcgemm;
     if (!workspace || R <= 0 || C <= 0 || G <= 0 || R % G != 0) return RQ_ERR_INVALID;
     const TcLayout L = tc_layout(R, C, G, plus);
@@ -590,12 +671,17 @@ extern "C" int rq_fq_run_tc(float* Wp, float* GH, const float* Z, const float* H
     PlaneTensor tUt{ws + L.put, Cp, Cp, 2LL * G};
     for (int i1 = 0; i1 < C; i1 += fq::BS) {
         const int count = (C - i1 < fq::BS) ? C - i1 : fq::BS;
-        int rc = fq_block_launch(Wp, GH, Z, Hinv, Q, codes, Eeff, PE, PE + (size_t)R * fq::BS, scale_row, scale_tab,
-                                 colgrp, scale_blk, R, C, G, i1, count, mode, dyn_gs, sym, maxq, plus, stream);
-        if (rc != RQ_OK) return rc;
         const int i2 = i1 + count;
+        int rc = fq_block_launch(Wp, GH, Z, Hinv, Q, codes, Eeff, PE, PE + (size_t)R * fq::BS, scale_row, scale_tab,
+                                 colgrp, scale_blk, R, C, G, i1, count, mode, dyn_gs, sym, maxq, plus, anchor, beta,
+                                 inner_mode, (atomic && i2 < C) ? 1 : 0, stream);
+        if (rc != RQ_OK) return rc;
         if (i2 >= C) break;
         prof::Scope timed(RQ_PROF_LAZY, st);
+        if (inner_mode != 0) {
+            rc = surrogate_outer(Wp, anchor, beta, R, C, i2, count, st);
+            if (rc != RQ_OK) return rc;
+        }
         Params p;
         p.a_row0 = 0; p.a_k0 = 0; p.a_plane = 0; p.a_plane_z = 0; p.a_row_z = Rg;
         p.b_row0 = i2; p.b_k0 = i1; p.b_plane = 0; p.b_plane_z = 2; p.b_row_z = 0;

@@ -143,8 +143,11 @@ def _scale_setup(quantizer, W32, groupsize, static_groups, blocksize, perm, dead
 # ----------------------------------------------------------------------------------------------
 # the shared driver
 # ----------------------------------------------------------------------------------------------
+_INNER_MODES = {"frozen": 0, "surrogate_block": 1, "surrogate_online": 2}
+
+
 def _quantize_linear(layer, W32, H3, perm, grads, quantizer, G, alpha_eff, ref_loss, plus, Hinv, mode_pack,
-                     export_to_et, permute_export, rec=None):
+                     export_to_et, permute_export, rec=None, inner_mode=0, atomic=False):
     dev = W32.device
     R, Cc = W32.shape
     mode, scale_row, scale_tab, colgrp, scale_blk, dyn_gs = mode_pack
@@ -185,6 +188,10 @@ def _quantize_linear(layer, W32, H3, perm, grads, quantizer, G, alpha_eff, ref_l
                                                           float(ref_loss), _lib.ptr(Z), _lib.ptr(GH), _lib.ptr(beta),
                                                           _lib.ptr(hdiag), st))
         GH_initial = GH.clone() if (plus and KEEP_INTERMEDIATES) else None
+        if not plus:
+            inner_mode = 0                      # beta = 0: the surrogate term vanishes
+        # surrogate modes measure the drift of the weights from their values before the first block
+        anchor = Wp.clone() if inner_mode else None
         Q = torch.empty(R, Cc, dtype=torch.float32, device=dev)
         codes = torch.empty(R, Cc, dtype=torch.int8, device=dev)
         Eeff = torch.empty(R, BS, dtype=torch.float32, device=dev)
@@ -195,13 +202,16 @@ def _quantize_linear(layer, W32, H3, perm, grads, quantizer, G, alpha_eff, ref_l
                                                  _lib.ptr(codes), _lib.ptr(Eeff), _lib.ptr(scale_row),
                                                  _lib.ptr(scale_tab), _lib.ptr(colgrp), _lib.ptr(scale_blk), R, Cc, G,
                                                  mode, dyn_gs, 1 if quantizer.sym else 0, maxq, 1 if plus else 0,
-                                                 ws_ptr, ws_bytes, status, st))
+                                                 _lib.ptr(anchor), _lib.ptr(beta) if inner_mode else 0,
+                                                 int(inner_mode), 1 if atomic else 0, ws_ptr, ws_bytes, status, st))
             else:
                 _lib.check("rq_fq_run",
                            _lib.lib.rq_fq_run(_lib.ptr(Wp), _lib.ptr(GH), _lib.ptr(Z), _lib.ptr(Hinv), _lib.ptr(Q),
                                               _lib.ptr(codes), _lib.ptr(Eeff), _lib.ptr(scale_row), _lib.ptr(scale_tab),
                                               _lib.ptr(colgrp), _lib.ptr(scale_blk), R, Cc, G, mode, dyn_gs,
-                                              1 if quantizer.sym else 0, maxq, 1 if plus else 0, st))
+                                              1 if quantizer.sym else 0, maxq, 1 if plus else 0,
+                                              _lib.ptr(anchor), _lib.ptr(beta) if inner_mode else 0,
+                                              int(inner_mode), 1 if atomic else 0, st))
         out = torch.empty(layer.weight.shape, dtype=layer.weight.dtype, device=dev)
         out_codes = out_scale = None
         if export_to_et:
@@ -268,11 +278,16 @@ def plain_fasterquant(obj, H, blocksize, percdamp, groupsize, actorder, static_g
 def plus_fasterquant(obj, blocksize, percdamp, groupsize, actorder, static_groups, enable_gradient_update,
                      g_update_mode, export_to_et, profile_recorder, gradient_refresh_fn, grad_reg_strategy,
                      second_order_scale, block_atomic_quant, block_observer, diagnostic_recorder):
-    if g_update_mode != "frozen":
+    if g_update_mode not in _INNER_MODES:
+        if g_update_mode in ("block_backward", "block_gd"):
+            raise NotImplementedError(
+                f"g_update_mode={g_update_mode!r} re-runs the model between blocks (gradient_refresh_fn); only the "
+                "callback-free modes 'frozen', 'surrogate_block' and 'surrogate_online' run in the kernels")
+        raise ValueError(f"Unknown g_update_mode '{g_update_mode}'")
+    if (g_update_mode != "frozen" or block_atomic_quant) and blocksize != BS:
         raise NotImplementedError(
-            f"g_update_mode={g_update_mode!r}: only the callback-free 'frozen' mode runs in the kernels so far")
-    if block_atomic_quant:
-        raise NotImplementedError("block_atomic_quant is not built")
+            f"surrogate modes and block_atomic_quant depend on the block boundaries: blocksize must be {BS}, "
+            f"got {blocksize}")
     if grad_reg_strategy != "none":
         raise NotImplementedError("gradient regularisers belong to the block_gd refresh path, which stays in PyTorch")
     if diagnostic_recorder is not None:
@@ -303,6 +318,7 @@ def plus_fasterquant(obj, blocksize, percdamp, groupsize, actorder, static_group
     grads = obj.gradients.to(dev).float().contiguous() if plus else None
     alpha_eff = obj.alpha / (obj.rows * obj.columns) if plus else 0.0
     state = _quantize_linear(layer, W32, H3, perm, grads, obj.quantizer, G, alpha_eff, obj.reference_loss, plus, Hinv,
-                             mode_pack, export_to_et, permute_export=True, rec=rec)
+                             mode_pack, export_to_et, permute_export=True, rec=rec,
+                             inner_mode=_INNER_MODES[g_update_mode], atomic=bool(block_atomic_quant))
     obj._last_fasterquant = {"Hinv": Hinv if KEEP_INTERMEDIATES else None, "perm": perm, "damp_percent": damp,
                              "identity_fallback": identity, **state}

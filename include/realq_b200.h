@@ -189,15 +189,24 @@ int rq_gptqplus_terms(const float* Gp, const float* Hinv, int R, int C, int G, f
  * gptq_utils/gptq_utils.py:153):  W[:, i2:] -= Eeff . Hinv[i1:i2, i2:] + count * GHinv[:, i2:];
  * GHinv[:, i2:] -= Z[:, i1:i2] . Hinv[i1:i2, i2:].
  *
- * rq_fq_run performs both for every block of the linear. */
+ * rq_fq_run performs both for every block of the linear.
+ *
+ * Modes without a host callback: inner_mode 0 = frozen, 1 = surrogate_block, 2 = surrogate_online add
+ * beta * (W - anchor) to the first-order term (gptq_utils/gptq_plus_utils.py:580-584, 1190-1200, 1360-1367, 1500-1509;
+ * anchor = Wp as it was before the first block, beta [R] from rq_gptqplus_terms); atomic != 0 quantizes the whole
+ * block from its start values and obtains Err from the triangular solve Err . Hinv[i1:i2, i1:i2] = W - Q - GHinv
+ * (:1238-1288; rq_fq_run never applies it to the last block, :1174). */
 int rq_fq_block(float* Wp, float* GH, const float* Z, const float* Hinv, float* Q, int8_t* codes, float* Eeff,
                 const float* scale_row, const float* scale_tab, const int* colgrp, float* scale_blk, int R, int C,
-                int G, int i1, int count, int mode, int dyn_gs, int sym, int maxq, int plus, void* stream);
+                int G, int i1, int count, int mode, int dyn_gs, int sym, int maxq, int plus, const float* anchor,
+                const float* beta, int inner_mode, int atomic, void* stream);
 int rq_fq_lazy_update(float* Wp, float* GH, const float* Z, const float* Eeff, const float* Hinv, int R, int C, int G,
-                      int i1, int count, int plus, void* stream);
+                      int i1, int count, int plus, const float* anchor, const float* beta, int outer_surrogate,
+                      void* stream);
 int rq_fq_run(float* Wp, float* GH, const float* Z, const float* Hinv, float* Q, int8_t* codes, float* Eeff,
               const float* scale_row, const float* scale_tab, const int* colgrp, float* scale_blk, int R, int C, int G,
-              int mode, int dyn_gs, int sym, int maxq, int plus, void* stream);
+              int mode, int dyn_gs, int sym, int maxq, int plus, const float* anchor, const float* beta,
+              int inner_mode, int atomic, void* stream);
 
 /* Tensor-core variants of the GEMM-shaped parts of fasterquant (same reference lines as above): operands
  * are split into bf16 hi/lo planes and multiplied with four tcgen05 products per k-step, which keeps
@@ -213,8 +222,8 @@ int rq_gptqplus_terms_tc(const float* Gp, const float* Hinv, int R, int C, int G
                          int* status, void* stream);
 int rq_fq_run_tc(float* Wp, float* GH, const float* Z, const float* Hinv, float* Q, int8_t* codes, float* Eeff,
                  const float* scale_row, const float* scale_tab, const int* colgrp, float* scale_blk, int R, int C,
-                 int G, int mode, int dyn_gs, int sym, int maxq, int plus, void* workspace, size_t workspace_bytes,
-                 int* status, void* stream);
+                 int G, int mode, int dyn_gs, int sym, int maxq, int plus, const float* anchor, const float* beta,
+                 int inner_mode, int atomic, void* workspace, size_t workspace_bytes, int* status, void* stream);
 
 /* rq_fq_finish replaces the epilogue (gptq_utils/gptq_plus_utils.py:1850-1875; gptq_utils/gptq_utils.py:157-166):
  * out[r][perm[j]] = Q[r][j] cast to out_dtype; when out_codes != NULL also the fp32 int_weight / scale
