@@ -147,7 +147,7 @@ _INNER_MODES = {"frozen": 0, "surrogate_block": 1, "surrogate_online": 2}
 
 
 def _quantize_linear(layer, W32, H3, perm, grads, quantizer, G, alpha_eff, ref_loss, plus, Hinv, mode_pack,
-                     export_to_et, permute_export, rec=None, inner_mode=0, atomic=False):
+                     export_to_et, permute_export, rec=None, inner_mode=0, atomic=False, refresh=None):
     dev = W32.device
     R, Cc = W32.shape
     mode, scale_row, scale_tab, colgrp, scale_blk, dyn_gs = mode_pack
@@ -196,7 +196,11 @@ def _quantize_linear(layer, W32, H3, perm, grads, quantizer, G, alpha_eff, ref_l
         codes = torch.empty(R, Cc, dtype=torch.int8, device=dev)
         Eeff = torch.empty(R, BS, dtype=torch.float32, device=dev)
         with _sec(rec, "fasterquant.block.total"):
-            if tc:
+            if refresh is not None:
+                beta, Z, GH = _block_backward_loop(
+                    refresh, W32, Wp, GH, Z, beta, Hinv, Q, codes, Eeff, mode_pack, perm, G, alpha_eff, ref_loss,
+                    plus, 1 if quantizer.sym else 0, maxq, atomic, st, rec)
+            elif tc:
                 _lib.check("rq_fq_run_tc",
                            _lib.lib.rq_fq_run_tc(_lib.ptr(Wp), _lib.ptr(GH), _lib.ptr(Z), _lib.ptr(Hinv), _lib.ptr(Q),
                                                  _lib.ptr(codes), _lib.ptr(Eeff), _lib.ptr(scale_row),
@@ -229,6 +233,79 @@ def _quantize_linear(layer, W32, H3, perm, grads, quantizer, G, alpha_eff, ref_l
         layer.register_buffer("scale", out_scale)
     layer.weight.data = out
     return {"beta": beta, "Z": Z, "GHinv_initial": GH_initial}
+
+
+_OBSERVER_NONE_KEYS = (
+    "second_order_update_abs_mean", "second_order_update_mean_row_l2", "second_order_update_abs_max",
+    "second_order_update_abs_q99", "first_order_raw_abs_mean", "first_order_raw_mean_row_l2",
+    "first_order_update_abs_mean", "first_order_update_mean_row_l2", "first_order_update_abs_max",
+    "first_order_update_abs_q99", "regularizer_update_abs_mean", "regularizer_update_mean_row_l2",
+    "sine_regularizer_update_abs_mean", "sine_regularizer_update_mean_row_l2")
+_OBSERVER_META_KEYS = ("mean_refresh_loss", "train_mean_refresh_loss", "val_mean_refresh_loss",
+                       "refresh_subset_mean_refresh_loss")
+
+
+def _block_backward_loop(refresh, W32, Wp, GH, Z, beta, Hinv, Q, codes, Eeff, mode_pack, perm, G, alpha_eff,
+                         ref_loss, plus, sym, maxq, atomic, st, rec):
+    """``g_update_mode="block_backward"`` (gptq_plus_utils.py:1190, 1392-1498): every block runs in the kernel
+    with the online surrogate term; between the block and its lazy update the host hands the caller's
+    ``gradient_refresh_fn`` the current weights (quantized columns up to the block's end, working values to
+    the right, natural column order), and the first-order terms are rebuilt from the gradient it returns."""
+    refresh_fn, observer, enabled, clip, full_metrics = refresh
+    dev = Wp.device
+    R, Cc = Wp.shape
+    mode, scale_row, scale_tab, colgrp, scale_blk, dyn_gs = mode_pack
+    inv = torch.argsort(perm) if perm is not None else None
+    anchor = Wp.clone() if plus else None
+    hdiag = torch.empty(G, Cc, dtype=torch.float32, device=dev) if plus else None
+    for i1 in range(0, Cc, BS):
+        count = min(BS, Cc - i1)
+        i2 = i1 + count
+        with _sec(rec, "fasterquant.block.inner_loop"):
+            _lib.check("rq_fq_block",
+                       _lib.lib.rq_fq_block(_lib.ptr(Wp), _lib.ptr(GH), _lib.ptr(Z), _lib.ptr(Hinv), _lib.ptr(Q),
+                                            _lib.ptr(codes), _lib.ptr(Eeff), _lib.ptr(scale_row), _lib.ptr(scale_tab),
+                                            _lib.ptr(colgrp), _lib.ptr(scale_blk), R, Cc, G, i1, count, mode, dyn_gs,
+                                            sym, maxq, 1 if plus else 0, _lib.ptr(anchor), _lib.ptr(beta),
+                                            2 if plus else 0, 1 if (atomic and i2 < Cc) else 0, st))
+        if enabled:
+            if refresh_fn is None:
+                raise ValueError("`gradient_refresh_fn` must be provided for g_update_mode='block_backward'.")
+            with _sec(rec, "fasterquant.block.true_gradient_refresh"):
+                current = Wp.clone()
+                current[:, :i2] = Q[:, :i2]
+                refreshed, meta = refresh_fn(current[:, inv] if inv is not None else current)
+                refreshed = refreshed.to(dev).float()
+                Gp = (refreshed[:, perm] if perm is not None else refreshed).contiguous()
+                if plus:
+                    # the kernel left Err - D*Z_old as the lazy update's operand; swap in the refreshed Z
+                    Dk = torch.arange(count - 1, -1, -1, device=dev, dtype=torch.float32)
+                    err = Eeff[:, :count] + Dk * Z[:, i1:i2]
+                    _lib.check("rq_gptqplus_terms",
+                               _lib.lib.rq_gptqplus_terms(_lib.ptr(Gp), _lib.ptr(Hinv), R, Cc, G, float(alpha_eff),
+                                                          float(ref_loss), _lib.ptr(Z), _lib.ptr(GH), _lib.ptr(beta),
+                                                          _lib.ptr(hdiag), st))
+                    Eeff[:, :count] = err - Dk * Z[:, i1:i2]
+                    anchor = current
+                if observer is not None:
+                    trailing = Gp[:, i2:] if (full_metrics and i2 < Cc) else None
+                    report = {"block_idx": i1 // BS, "col_start": i1, "col_end": i2, "remaining_columns": Cc - i2,
+                              "remaining_grad_abs_mean": None, "remaining_grad_clipped_abs_mean": None,
+                              "remaining_grad_mean_row_l2": None}
+                    if trailing is not None:
+                        report["remaining_grad_abs_mean"] = trailing.abs().mean().item()
+                        report["remaining_grad_mean_row_l2"] = torch.linalg.norm(trailing, dim=1).mean().item()
+                        report["remaining_grad_clipped_abs_mean"] = (
+                            trailing.clamp(min=-clip, max=clip).abs().mean().item()
+                            if clip is not None and clip > 0 else report["remaining_grad_abs_mean"])
+                    report.update({k: None for k in _OBSERVER_NONE_KEYS})
+                    report.update({k: None if meta is None else meta.get(k) for k in _OBSERVER_META_KEYS})
+                    observer(report)
+        with _sec(rec, "fasterquant.block.outer_update_delta_w"):
+            _lib.check("rq_fq_lazy_update",
+                       _lib.lib.rq_fq_lazy_update(_lib.ptr(Wp), _lib.ptr(GH), _lib.ptr(Z), _lib.ptr(Eeff),
+                                                  _lib.ptr(Hinv), R, Cc, G, i1, count, 1 if plus else 0, 0, 0, 0, st))
+    return beta, Z, GH
 
 
 def _check_common(quantizer, blocksize):
@@ -277,12 +354,14 @@ def plain_fasterquant(obj, H, blocksize, percdamp, groupsize, actorder, static_g
 @torch.no_grad()
 def plus_fasterquant(obj, blocksize, percdamp, groupsize, actorder, static_groups, enable_gradient_update,
                      g_update_mode, export_to_et, profile_recorder, gradient_refresh_fn, grad_reg_strategy,
-                     second_order_scale, block_atomic_quant, block_observer, diagnostic_recorder):
-    if g_update_mode not in _INNER_MODES:
-        if g_update_mode in ("block_backward", "block_gd"):
-            raise NotImplementedError(
-                f"g_update_mode={g_update_mode!r} re-runs the model between blocks (gradient_refresh_fn); only the "
-                "callback-free modes 'frozen', 'surrogate_block' and 'surrogate_online' run in the kernels")
+                     second_order_scale, block_atomic_quant, block_observer, diagnostic_recorder, grad_clip=1.0,
+                     refresh_full_metrics=False):
+    if g_update_mode == "block_gd":
+        raise NotImplementedError(
+            "g_update_mode='block_gd' (an optimizer step on the trailing weights between blocks, "
+            "gptq_plus_utils.py:1572-1848) is not built; 'frozen', 'surrogate_block', 'surrogate_online' and "
+            "'block_backward' are")
+    if g_update_mode not in _INNER_MODES and g_update_mode != "block_backward":
         raise ValueError(f"Unknown g_update_mode '{g_update_mode}'")
     if (g_update_mode != "frozen" or block_atomic_quant) and blocksize != BS:
         raise NotImplementedError(
@@ -319,6 +398,8 @@ def plus_fasterquant(obj, blocksize, percdamp, groupsize, actorder, static_group
     alpha_eff = obj.alpha / (obj.rows * obj.columns) if plus else 0.0
     state = _quantize_linear(layer, W32, H3, perm, grads, obj.quantizer, G, alpha_eff, obj.reference_loss, plus, Hinv,
                              mode_pack, export_to_et, permute_export=True, rec=rec,
-                             inner_mode=_INNER_MODES[g_update_mode], atomic=bool(block_atomic_quant))
+                             inner_mode=_INNER_MODES.get(g_update_mode, 0), atomic=bool(block_atomic_quant),
+                             refresh=((gradient_refresh_fn, block_observer, bool(enable_gradient_update), grad_clip,
+                                       bool(refresh_full_metrics)) if g_update_mode == "block_backward" else None))
     obj._last_fasterquant = {"Hinv": Hinv if KEEP_INTERMEDIATES else None, "perm": perm, "damp_percent": damp,
                              "identity_fallback": identity, **state}

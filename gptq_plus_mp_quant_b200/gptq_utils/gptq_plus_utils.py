@@ -129,7 +129,8 @@ class GPTQPlus:
                 g_update_mode=g_update_mode, export_to_et=export_to_et, profile_recorder=profile_recorder,
                 gradient_refresh_fn=gradient_refresh_fn, grad_reg_strategy=grad_reg_strategy,
                 second_order_scale=second_order_scale, block_atomic_quant=block_atomic_quant,
-                block_observer=block_observer, diagnostic_recorder=diagnostic_recorder)
+                block_observer=block_observer, diagnostic_recorder=diagnostic_recorder, grad_clip=grad_clip,
+                refresh_full_metrics=refresh_full_metrics)
         if torch.any(torch.isnan(self.layer.weight.data)):
             logging.warning("NaN in weights")
             raise ValueError("NaN in weights")

@@ -191,12 +191,14 @@ def _effective_ghinv(base, cur_w, ref_w, bview, mode):
 
 def plus_fasterquant(weight, H, act_square, gradients, quantizer, num_groups, alpha, reference_loss,
                      blocksize=128, percdamp=0.01, groupsize=-1, actorder=False, static_groups=False,
-                     enable_gradient_update=True, g_update_mode="frozen", block_atomic_quant=False):
+                     enable_gradient_update=True, g_update_mode="frozen", block_atomic_quant=False,
+                     gradient_refresh_fn=None):
     """GPTQ+ quantization of one linear (gptq_plus_utils.py:910-1896) for the callback-free
     modes.  ``H`` is the finalised ``[G, C, C]`` Hessian.  Returns dict(Q, W_int, Scale,
     perm, states) with all three matrices in the layer's natural column order (:1850-1866).
     """
-    assert g_update_mode in ("frozen", "surrogate_block", "surrogate_online")
+    assert g_update_mode in ("frozen", "surrogate_block", "surrogate_online", "block_backward")
+    backward = g_update_mode == "block_backward"
     W = weight.clone().float()
     rows, columns = W.shape
     Q_final = torch.zeros_like(W)
@@ -245,8 +247,8 @@ def plus_fasterquant(weight, H, act_square, gradients, quantizer, num_groups, al
                            invperm=invperm, damp=damp, identity=ident,
                            fast_scale=quantizer.scale[r0:r1] if fast else None))
 
-    inner_mode = g_update_mode
-    outer_mode = "frozen" if g_update_mode == "frozen" else "surrogate_block"
+    inner_mode = "surrogate_online" if backward else g_update_mode                        # :1190
+    outer_mode = "frozen" if g_update_mode in ("frozen", "block_backward") else "surrogate_block"   # :1500
     for i1 in range(0, columns, blocksize):
         i2 = min(i1 + blocksize, columns)
         count = i2 - i1
@@ -321,9 +323,30 @@ def plus_fasterquant(weight, H, act_square, gradients, quantizer, num_groups, al
             st["Q"][:, i1:i2] = Q1
             st["Wint"][:, i1:i2] = Wi1
             st["Scale"][:, i1:i2] = S1
-            per_block.append((st, Err1, Z1))
+            cur = None
+            if backward:                                                  # :1392-1396
+                cur = st["W_sub"].clone()
+                cur[:, :i1] = st["Q"][:, :i1]
+                cur[:, i1:i2] = Q1
+            per_block.append([st, Err1, Z1, cur])
 
-        for st, Err1, Z1 in per_block:                                    # lazy update (:1500-1570)
+        if backward and enable_gradient_update:                           # true-gradient refresh (:1408-1460)
+            snapshot = weight.clone().float()
+            for st, _, _, cur in per_block:
+                snapshot[st["r0"]:st["r1"]] = cur[:, st["invperm"]] if actorder else cur
+            refreshed, _meta = gradient_refresh_fn(snapshot)
+            refreshed = refreshed.float()
+            for item in per_block:
+                st, cur = item[0], item[3]
+                g_sub = refreshed[st["r0"]:st["r1"]]
+                if actorder:
+                    g_sub = g_sub[:, st["perm"]]
+                beta, bview, Z, GHinv = gradient_terms(g_sub, st["Hinv_init"], st["Hinv"], alpha,
+                                                       max(reference_loss, 0), rows, columns, enable_gradient_update)
+                st.update(beta=beta, bview=bview, Z=Z, GHinv=GHinv, anchor=cur.clone())
+                item[2] = Z[:, i1:i2]
+
+        for st, Err1, Z1, _ in per_block:                                 # lazy update (:1500-1570)
             rest = _effective_ghinv(st["GHinv"][:, i2:], st["W_sub"][:, i2:], st["anchor"][:, i2:],
                                     st["bview"], outer_mode)
             g_update = count * rest - torch.einsum("ij,j,jk->ik", Z1, D, st["Hinv"][i1:i2, i2:])

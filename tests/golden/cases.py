@@ -106,4 +106,23 @@ PLUS_CASES = [
     ("plus_surrogate_online", 32, 256, 4, 96, 2, 4, -1, True, True, 0.25, 0.7, "surrogate_online", False),
     ("plus_atomic", 32, 256, 4, 96, 2, 4, -1, True, True, 0.25, 0.7, "frozen", True),
     ("plus_ragged", 32, 200, 3, 80, 4, 4, -1, True, True, 0.25, 0.7, "frozen", False),
+    ("plus_block_backward", 32, 384, 4, 96, 2, 4, -1, True, True, 0.25, 0.7, "block_backward", False),
 ]
+
+
+def make_refresh_fn(W0, G0, calls=None):
+    """Deterministic stand-in for the model backward that ``block_backward`` calls between blocks: the
+    gradient of a diagonal quadratic around the original weights, elementwise in fp32 on the CPU so that
+    every implementation sees bit-identical refreshed gradients for identical snapshots."""
+    W0 = W0.detach().float().cpu().clone()
+    G0 = G0.detach().float().cpu().clone()
+    curv = torch.linspace(0.5, 2.0, W0.shape[1]).unsqueeze(0) * 1e-3
+
+    def refresh(weight_snapshot):
+        snap = weight_snapshot.detach().float().cpu()
+        grad = G0 + (snap - W0) * curv
+        if calls is not None:
+            calls.append(snap.clone())
+        return grad.to(weight_snapshot.device), {"mean_refresh_loss": float(((snap - W0) ** 2).mean())}
+
+    return refresh

@@ -159,7 +159,8 @@ def gen_plus(qu, gpu, out):
         out[f"{name}.GHinv0"] = np32(GH)
         g.fasterquant(blocksize=128, percdamp=0.01, groupsize=gs, actorder=act, static_groups=static,
                       enable_gradient_update=True, g_update_mode=mode, export_to_et=True,
-                      block_atomic_quant=atomic)
+                      block_atomic_quant=atomic,
+                      gradient_refresh_fn=cases.make_refresh_fn(W, Gr) if mode == "block_backward" else None)
         out[f"{name}.Q"] = np32(layer.weight.data)
         out[f"{name}.W_int"] = np32(layer.int_weight).astype(np.int8)
         out[f"{name}.Scale"] = np32(layer.scale)

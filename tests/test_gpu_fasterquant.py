@@ -162,10 +162,12 @@ def test_gptqplus_fasterquant_vs_reference(golden, case):
     H_dev, act_sq_dev = obj.H.clone().cpu(), obj.act_square.clone().cpu()
     from gptq_plus_mp_quant_b200.gptq_utils import fasterquant_impl as fi
     fi.KEEP_INTERMEDIATES = True
+    seen = []
     try:
         obj.fasterquant(blocksize=128, percdamp=0.01, groupsize=gs, actorder=act, static_groups=static,
                         enable_gradient_update=True, g_update_mode=mode, export_to_et=True,
-                        block_atomic_quant=atomic)
+                        block_atomic_quant=atomic, block_observer=seen.append,
+                        gradient_refresh_fn=cases.make_refresh_fn(W, Gr) if mode == "block_backward" else None)
     finally:
         fi.KEEP_INTERMEDIATES = False
     st = obj._last_fasterquant
@@ -174,7 +176,10 @@ def test_gptqplus_fasterquant_vs_reference(golden, case):
     if f"{name}.Hinv0" in g:
         assert rel_fro(st["Hinv"][0, :cols, :cols], torch.from_numpy(g[f"{name}.Hinv0"])) < 5e-4
     rg = rows // G
-    if alpha > 0:
+    if mode == "block_backward":
+        assert [b["col_end"] for b in seen] == list(range(128, cols + 1, 128))
+        assert all(b["mean_refresh_loss"] is not None for b in seen)
+    elif alpha > 0:
         assert torch.allclose(st["beta"][:rg].cpu(), torch.from_numpy(g[f"{name}.beta0"]), rtol=1e-3, atol=1e-6)
         assert rel_fro(st["Z"][:rg], torch.from_numpy(g[f"{name}.Z0"])) < 1e-3
         assert rel_fro(st["GHinv_initial"][:rg], torch.from_numpy(g[f"{name}.GHinv0"])) < 1e-3
@@ -199,7 +204,8 @@ def test_gptqplus_fasterquant_vs_reference(golden, case):
     q = oq.OracleWeightQuantizer()
     q.configure(bits, perchannel=True, sym=True)
     o = og.plus_fasterquant(W, H_dev, act_sq_dev, Gr, q, G, alpha, ref_loss, groupsize=gs, actorder=act,
-                            static_groups=static, g_update_mode=mode, block_atomic_quant=atomic)
+                            static_groups=static, g_update_mode=mode, block_atomic_quant=atomic,
+                            gradient_refresh_fn=cases.make_refresh_fn(W, Gr) if mode == "block_backward" else None)
     frac2, _, first2 = _code_report(layer.int_weight.cpu(), o["W_int"].float(), order)
     print(f"{name}: against the oracle on the device's Hessian {frac2 * 100:.4f}% differ")
     assert frac2 < 0.002 and all(d == 1.0 for d in first2)
