@@ -138,7 +138,7 @@ def dist_setup():
 
 
 def assign_owners(costs, world):
-    """Longest-processing-time-first assignment of the linears' fasterquant stages to ranks."""
+    """Longest-processing-time-first assignment of fasterquant work units to ranks."""
     load = [0.0] * world
     owner = {}
     for name, c in sorted(costs.items(), key=lambda kv: -kv[1]):
@@ -196,8 +196,12 @@ class LayerWorkload:
             cap = torch.quantile(s.flatten()[:1_000_000], 0.99)
             self.sal[name] = torch.clamp(s, max=cap)
             self.grad[name] = torch.randn(R, C, generator=gw, device=dev) * 1e-4
-        costs = {name: (2.0 / 3.0) * C ** 3 * self.G + 5.0 * R * C * C for name, R, C, _ in self.LINEARS}
-        self.owner = assign_owners(costs, world)
+        # a unit of fasterquant work = one saliency group of one linear (own Hessian, own rows): factorisation
+        # ~ C^3, first-order terms and lazy updates ~ rows * C^2, plus a per-unit launch overhead
+        costs = {(name, g): (2.0 / 3.0) * C ** 3 + 5.0 * (R // self.G) * C * C + 3e10
+                 for name, R, C, _ in self.LINEARS for g in range(self.G)}
+        unit_owner = assign_owners(costs, world)
+        self.owner = {name: [unit_owner[(name, g)] for g in range(self.G)] for name, _, _, _ in self.LINEARS}
         self.recorder = None
 
     # ---- algorithmic work figures
@@ -234,12 +238,14 @@ class LayerWorkload:
         checksum = torch.zeros((), device=self.dev)
         for name, R, C, _ in self.LINEARS:
             o = objs[name]
-            o.hessian_owner = self.owner[name] if self.world > 1 else None
+            o.group_owners = self.owner[name] if self.world > 1 else None
             o.finalize_hessian()
-            if self.world == 1 or self.owner[name] == self.rank:
+            if self.world == 1 or self.rank in self.owner[name]:
                 o.fasterquant(blocksize=128, percdamp=0.01, groupsize=128, actorder=True, static_groups=True)
             if self.world > 1:
-                dist.broadcast(self.layers[name].weight.data, src=self.owner[name])
+                w, rps = self.layers[name].weight.data, R // self.G
+                for g, src in enumerate(self.owner[name]):
+                    dist.broadcast(w[g * rps:(g + 1) * rps], src=src)
             checksum += self.layers[name].weight.data.float().abs().mean()
             o.free()
         return checksum
@@ -255,6 +261,11 @@ class LayerWorkload:
     def h2d_bytes(self):
         return sum(v.numel() * 2 for v in self.host_in.values())
 
+    def _owned_runs(self, name):
+        """Runs of consecutive groups of this linear that this rank owns (one fasterquant pass each)."""
+        mine = [g for g, r in enumerate(self.owner[name]) if r == self.rank]
+        return sum(1 for i, g in enumerate(mine) if i == 0 or mine[i - 1] != g - 1)
+
     def launches_per_step(self):
         """Kernel launches of this library in one step, counted from the host loops."""
         batches = self.nseq_local // self.BSZ
@@ -263,10 +274,10 @@ class LayerWorkload:
         n += batches * len(self.LINEARS) * chunks * 3                 # pack + sum-of-squares reduce + tensor-core GEMM
         for name, R, C, _ in self.LINEARS:
             n += 1                                                    # finalize
-            if self.world == 1 or self.owner[name] == self.rank:
-                blocks = C // 128
-                n += 1 + 2 + 3 * blocks + 2 * math.ceil(math.log2(blocks)) + 1   # ranges, Cholesky route
-                n += 1 + 4 + blocks * 3 + 1                           # prepare, first-order terms, block loop, epilogue
+            runs = 1 if self.world == 1 else self._owned_runs(name)
+            blocks = C // 128
+            n += runs * (1 + 2 + 3 * blocks + 2 * math.ceil(math.log2(blocks)) + 1)   # ranges, Cholesky route
+            n += runs * (1 + 4 + blocks * 3 + 1)                      # prepare, first-order terms, block loop, epilogue
         return n
 
 
@@ -396,8 +407,9 @@ def run_ours(args):
         "data": "synthetic",
         "config": {"workload": wl.name, "tokens": wl.nseq_total * wl.T, "hessian_accum_bsz": wl.BSZ,
                    "l2": "per-step inputs (10.7 GB of activations, 4 GB of Hessians) exceed the 126 MB L2",
-                   "parallelism": (f"dp{world}: calibration sequences sharded, NCCL reduce of each H to the owner "
-                                   f"of its linear, fasterquant of the 7 linears spread over ranks"),
+                   "parallelism": (f"dp{world}: calibration sequences sharded, NCCL reduce of each group's H to the "
+                                   "owner of that (linear, group), fasterquant of the 28 (linear, group) units "
+                                   "spread over ranks, quantized rows broadcast from their owners"),
                    "fasterquant_owner": wl.owner if world > 1 else None},
         "hessian_accum_tflops": round(wl.hessian_flops() * args.steps / (umma_ms * 1e-3 + prof["pack"][0] * 1e-3)
                                       / 1e12, 1) if umma_ms else None,

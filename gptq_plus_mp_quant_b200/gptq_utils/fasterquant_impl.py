@@ -108,15 +108,21 @@ def hinv_with_fallback(H3: torch.Tensor, perm, percdamp: float, identity_fallbac
 # ----------------------------------------------------------------------------------------------
 # scale sources
 # ----------------------------------------------------------------------------------------------
-def _scale_setup(quantizer, W32, groupsize, static_groups, blocksize, perm, dead_zeroed_W=None):
-    """(mode, scale_row, scale_tab, colgrp, scale_blk, dyn_gs) for the block kernel."""
+def _scale_setup(quantizer, W32, groupsize, static_groups, blocksize, perm, dead_zeroed_W=None, rows=None):
+    """(mode, scale_row, scale_tab, colgrp, scale_blk, dyn_gs) for the block kernel; ``rows`` restricts
+    it to a row slice of the layer (every scale is per row, so a slice is a problem of its own)."""
     dev = W32.device
-    R, Cc = W32.shape
     if groupsize == -1:
         scale_row = quantizer.scale.to(dev, torch.float32).reshape(-1).contiguous()
-        if scale_row.numel() != R:
-            raise ValueError(f"quantizer.scale has {scale_row.numel()} entries for {R} rows")
+        if scale_row.numel() != W32.shape[0]:
+            raise ValueError(f"quantizer.scale has {scale_row.numel()} entries for {W32.shape[0]} rows")
+        if rows is not None:
+            scale_row = scale_row[rows].contiguous()
         return 0, scale_row, None, None, None, 0
+    if rows is not None:
+        W32 = W32[rows]
+        dead_zeroed_W = None if dead_zeroed_W is None else dead_zeroed_W[rows]
+    R, Cc = W32.shape
     if not getattr(quantizer, "perchannel", True):
         raise NotImplementedError("grouped quantization needs a per-channel quantizer")
     maxq = int(quantizer.maxq)
@@ -316,6 +322,65 @@ def _check_common(quantizer, blocksize):
         raise NotImplementedError(f"integer codes are stored as int8: maxq must be in 1..127, got {maxq}")
 
 
+class _RowSlice:
+    """Stand-in for ``layer`` that lets the shared driver write the result of a row slice."""
+
+    class _Weight:
+        def __init__(self, data):
+            self.data, self.shape, self.dtype = data, data.shape, data.dtype
+
+    def __init__(self, weight_rows):
+        self.weight = self._Weight(weight_rows)
+        self.buffers = {}
+
+    def register_buffer(self, name, tensor):
+        self.buffers[name] = tensor
+
+
+def _quantize_owned_groups(obj, W32, H3, perm, grads, alpha_eff, plus, percdamp, groupsize, static_groups, blocksize,
+                           export_to_et, rec, inner_mode, atomic):
+    """The groups whose owner is this rank, as runs of consecutive groups; rows of other groups stay as they are
+    (export buffers: zero there)."""
+    from ..utils import dist_utils
+    layer = obj.layer
+    rank = dist_utils.get_rank()
+    G = obj.num_groups
+    rps = obj.rows // G
+    owned = [g for g in range(G) if obj.group_owners[g] == rank]
+    runs = []
+    for g in owned:
+        if runs and runs[-1][1] == g:
+            runs[-1][1] = g + 1
+        else:
+            runs.append([g, g + 1])
+    out = layer.weight.data.clone()
+    codes = torch.zeros_like(W32) if export_to_et else None
+    scales = torch.zeros_like(W32) if export_to_et else None
+    last = {"Hinv": None, "perm": perm, "damp_percent": [None] * G, "identity_fallback": [None] * G}
+    for g0, g1 in runs:
+        rows = slice(g0 * rps, g1 * rps)
+        with _sec(rec, "fasterquant.quantizer_build_groups"):
+            mode_pack = _scale_setup(obj.quantizer, W32, groupsize, static_groups, blocksize, perm, None, rows=rows)
+        with _sec(rec, "fasterquant.subgroup.compute_hinv"):
+            Hinv, damp, identity = hinv_with_fallback(H3[g0:g1], perm, percdamp, identity_fallback=True,
+                                                      log_context=f" groups {g0}..{g1 - 1}")
+        part = _RowSlice(layer.weight.data[rows])
+        _quantize_linear(part, W32[rows], H3[g0:g1], perm, grads[rows] if plus else None, obj.quantizer, g1 - g0,
+                         alpha_eff, obj.reference_loss, plus, Hinv, mode_pack, export_to_et, permute_export=True,
+                         rec=rec, inner_mode=inner_mode, atomic=atomic)
+        out[rows] = part.weight.data
+        if export_to_et:
+            codes[rows] = part.buffers["int_weight"]
+            scales[rows] = part.buffers["scale"]
+        last["damp_percent"][g0:g1] = damp
+        last["identity_fallback"][g0:g1] = identity
+    layer.weight.data = out
+    if export_to_et:
+        layer.register_buffer("int_weight", codes.reshape(layer.weight.shape))
+        layer.register_buffer("scale", scales)
+    obj._last_fasterquant = last
+
+
 # ----------------------------------------------------------------------------------------------
 # plain GPTQ (gptq_utils/gptq_utils.py:45-174)
 # ----------------------------------------------------------------------------------------------
@@ -389,17 +454,26 @@ def plus_fasterquant(obj, blocksize, percdamp, groupsize, actorder, static_group
     H3 = obj.H
     with _sec(rec, "fasterquant.subgroup.actorder_permute"):
         perm = torch.argsort(obj.act_square, descending=True) if actorder else None
+    plus = bool(enable_gradient_update and obj.alpha > 0)
+    grads = obj.gradients.to(dev).float().contiguous() if plus else None
+    alpha_eff = obj.alpha / (obj.rows * obj.columns) if plus else 0.0
+    refresh = ((gradient_refresh_fn, block_observer, bool(enable_gradient_update), grad_clip,
+                bool(refresh_full_metrics)) if g_update_mode == "block_backward" else None)
+    if getattr(obj, "group_owners", None) is not None:
+        if refresh is not None:
+            raise NotImplementedError("block_backward needs every row group on one rank (the callback sees the "
+                                      "whole weight); use hessian_owner instead of group_owners")
+        _quantize_owned_groups(obj, W32, H3, perm, grads, alpha_eff, plus, percdamp, groupsize, static_groups,
+                               blocksize, export_to_et, rec, _INNER_MODES.get(g_update_mode, 0),
+                               bool(block_atomic_quant))
+        return
     with _sec(rec, "fasterquant.quantizer_build_groups"):
         mode_pack = _scale_setup(obj.quantizer, W32, groupsize, static_groups, blocksize, perm, None)
     with _sec(rec, "fasterquant.subgroup.compute_hinv"):
         Hinv, damp, identity = hinv_with_fallback(H3, perm, percdamp, identity_fallback=True)
-    plus = bool(enable_gradient_update and obj.alpha > 0)
-    grads = obj.gradients.to(dev).float().contiguous() if plus else None
-    alpha_eff = obj.alpha / (obj.rows * obj.columns) if plus else 0.0
     state = _quantize_linear(layer, W32, H3, perm, grads, obj.quantizer, G, alpha_eff, obj.reference_loss, plus, Hinv,
                              mode_pack, export_to_et, permute_export=True, rec=rec,
                              inner_mode=_INNER_MODES.get(g_update_mode, 0), atomic=bool(block_atomic_quant),
-                             refresh=((gradient_refresh_fn, block_observer, bool(enable_gradient_update), grad_clip,
-                                       bool(refresh_full_metrics)) if g_update_mode == "block_backward" else None))
+                             refresh=refresh)
     obj._last_fasterquant = {"Hinv": Hinv if KEEP_INTERMEDIATES else None, "perm": perm, "damp_percent": damp,
                              "identity_fallback": identity, **state}

@@ -44,6 +44,11 @@ class GPTQPlus:
         # Rank that runs fasterquant for this linear when the linears of a layer are spread over the
         # ranks; None keeps the reference behaviour (every rank receives the summed Hessian).
         self.hessian_owner = None
+        # Finer spreading: one owning rank per saliency group (list of num_groups ranks).  The groups of a
+        # linear are independent problems (own Hessian, own rows), so finalize_hessian sums group g on
+        # group_owners[g] only and fasterquant quantizes just the rows of the groups this rank owns; the
+        # other rows of layer.weight keep their values until the caller gathers them from their owners.
+        self.group_owners = None
         assert self.rows % self.num_groups == 0, (
             f"Number of rows ({self.rows}) must be divisible by num_groups ({self.num_groups})")
 
@@ -91,7 +96,11 @@ class GPTQPlus:
         (gptq_plus_utils.py:859-908)."""
         if self._finalized:
             return
-        if self.hessian_owner is None:
+        if self.group_owners is not None:
+            assert len(self.group_owners) == self.num_groups
+            for g, owner in enumerate(self.group_owners):
+                dist_utils.reduce_sum_(self._H[g], owner)
+        elif self.hessian_owner is None:
             dist_utils.allreduce_sum_(self._H)
         else:
             dist_utils.reduce_sum_(self._H, self.hessian_owner)

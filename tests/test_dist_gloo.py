@@ -59,6 +59,40 @@ def _worker(rank, world, port, results):
         du.reduce_sum_(t, 1)
         if rank == 1:
             assert torch.equal(t, torch.full((8,), 3.0))
+        # per-group ownership: group g of the Hessian is summed on its owner only, the owner quantizes that
+        # group's rows, the rows travel back by broadcast; equals quantizing everything in one process
+        from oracle import gptq as og, quantizer as oq
+        rows = 8
+        W = cases.make_weight(rows, C, seed=7)
+        Gr = cases.make_grad(rows, C, seed=7)
+        owners = [1, 0]
+        part2 = ohess.GroupedHessian(C, S[sl])
+        part2.add_batch(X[sl])
+        for g, owner in enumerate(owners):
+            du.reduce_sum_(part2.H[g], owner)
+        du.allreduce_sum_(part2.act_square)
+        part2.index = int(du.allreduce_sum_scalar(part2.index))
+        part2.token_count = int(du.allreduce_sum_scalar(part2.token_count))
+        part2.finalize()
+        rps = rows // G
+        Wq = W.clone()
+        for g, owner in enumerate(owners):
+            if owner == rank:
+                q = oq.OracleWeightQuantizer()
+                q.configure(4, perchannel=True, sym=True)
+                r = slice(g * rps, (g + 1) * rps)
+                # alpha_eff of the whole layer: alpha / (rows * C) = (alpha / G) / (rps * C)
+                o = og.plus_fasterquant(W[r], part2.H[g:g + 1], part2.act_square, Gr[r], q, 1, 0.25 / G, 0.7,
+                                        actorder=True, static_groups=True)
+                Wq[r] = o["Q"]
+        for g, owner in enumerate(owners):
+            dist.broadcast(Wq[g * rps:(g + 1) * rps], src=owner)
+        q = oq.OracleWeightQuantizer()
+        q.configure(4, perchannel=True, sym=True)
+        full = og.plus_fasterquant(W, whole.H, whole.act_square, Gr, q, G, 0.25, 0.7, actorder=True,
+                                   static_groups=True)["Q"]
+        assert float((Wq != full).float().mean()) < 0.02             # summation order differs in the last bit
+        du.assert_bit_exact(Wq, "gathered weights")
         results[rank] = "ok"
     finally:
         dist.destroy_process_group()

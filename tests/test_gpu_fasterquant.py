@@ -298,3 +298,34 @@ def test_unsupported_modes_are_loud():
         obj.fasterquant(g_update_mode="block_gd")
     with pytest.raises(ValueError):
         obj.fasterquant(groupsize=64, static_groups=False)
+
+
+def test_group_owners_quantize_only_owned_rows():
+    """With per-group owners a rank quantizes just the rows of its groups, and those rows come out exactly
+    as in the run over the whole linear (the groups are independent problems)."""
+    from gptq_plus_mp_quant_b200.gptq_utils.gptq_plus_utils import GPTQPlus
+    from gptq_plus_mp_quant_b200.utils.quant_utils import WeightQuantizer
+    rows, cols, nseq, seqlen, G = 64, 256, 4, 96, 4
+    W = cases.make_weight(rows, cols, seed=31)
+    X = cases.make_acts(nseq, seqlen, cols, seed=31)
+    S = cases.make_saliency(nseq, seqlen, G, seed=31)
+    Gr = cases.make_grad(rows, cols, seed=31)
+    outs = []
+    for owners in (None, [0, 1, 0, 0]):
+        layer = _layer(W)
+        obj = GPTQPlus(layer, S, Gr, G, 0.25, 0.7)
+        obj.quantizer = WeightQuantizer()
+        obj.quantizer.configure(4, perchannel=True, sym=True, mse=False)
+        obj.add_batch(X.to(DEV), None)
+        obj.group_owners = owners
+        obj.finalize_hessian()
+        obj.fasterquant(blocksize=128, percdamp=0.01, groupsize=128, actorder=True, static_groups=True,
+                        export_to_et=True)
+        outs.append((layer.weight.data.cpu(), layer.int_weight.cpu(), layer.scale.cpu()))
+    rps = rows // G
+    (qa, ca, sa), (qb, cb, sb) = outs
+    for g in (0, 2, 3):
+        r = slice(g * rps, (g + 1) * rps)
+        assert torch.equal(qa[r], qb[r]) and torch.equal(ca[r], cb[r]) and torch.equal(sa[r], sb[r])
+    r = slice(rps, 2 * rps)
+    assert torch.equal(qb[r], W[r]) and not torch.equal(qa[r], W[r])
