@@ -75,94 +75,255 @@ __global__ void __launch_bounds__(256) gather_kernel(const float* __restrict__ H
 // Diagonal block k: A_kk = R_kk R_kk^T (R upper) and U_kk = R_kk^-1.  One CTA of 512 threads per group, the
 // block and its inverse in shared memory, fp32 throughout with correctly rounded division and square root: the
 // accuracy class of an fp32 LAPACK potrf / trtri on the block, which is what the reference runs.  (fp64
-// arithmetic runs at 1/64 of the fp32 rate on this part; formulations with fp64 or compensated dot products,
-// with the block spread over registers, and with shared-memory rank-1 updates were all measured slower.)
-// Four lanes share a row (factorisation, left-looking: column c needs t_i = A[i][c] - sum_{l>c} R[i][l] R[c][l])
-// or a column (inverse: U[c][j] = -(sum_{c<l<=j} R[c][l] U[l][j]) / R[c][c]).
+// arithmetic runs at 1/64 of the fp32 rate on this part; an unblocked column-by-column formulation with CTA-wide
+// barriers per column was latency-bound at ~1300 cycles per column.)
+// The 128-wide block is itself blocked 4 x 32, last sub-block first:
+//   sub-block factor + inverse  one warp, row i (factor) / column j (inverse) in the registers of lane i / j,
+//                               the pivot column travels through a 32-float shared buffer, no CTA barrier;
+//   panel                       R_ib = A_ib . W_bb^T           (W_bb = R_bb^-1), 32x32x32 jobs of 64 threads;
+//   trailing                    A_ij -= R_ib . R_jb^T          for i <= j < b;
+// then the inverse of the block-triangular R by recursive doubling (sub-block pairs, then the 64-wide pair):
+//   U_ab = -(U_aa . R_ab) . U_bb, the inner product parked in the unused lower blocks of the inverse.
 // ------------------------------------------------------------------------------------------
-constexpr int kDiagLd = NB + 4;               // fp32 row stride: rows 4 banks apart
+constexpr int kDiagLd = NB + 4;               // fp32 row stride: rows 4 banks apart, rows 16-byte aligned
+constexpr int SB = 32;                        // sub-block width
+
+// acc[x][y] += sum_k A[4*tr+x][k] * B[tc+8*y][k], k < 32 (both operands k-contiguous).  Output columns are
+// interleaved over the 8 threads of a row group so that their B rows are consecutive: conflict-free 16-byte loads.
+__device__ __forceinline__ void diag_job_nt(float (&acc)[4][4], const float* __restrict__ Ab, const float* __restrict__ Bb,
+                                            int tr, int tc) {
+#pragma unroll
+    for (int k = 0; k < SB; k += 4) {
+        float4 a[4], b[4];
+#pragma unroll
+        for (int x = 0; x < 4; ++x) a[x] = *reinterpret_cast<const float4*>(Ab + (4 * tr + x) * kDiagLd + k);
+#pragma unroll
+        for (int y = 0; y < 4; ++y) b[y] = *reinterpret_cast<const float4*>(Bb + (tc + 8 * y) * kDiagLd + k);
+#pragma unroll
+        for (int x = 0; x < 4; ++x)
+#pragma unroll
+            for (int y = 0; y < 4; ++y) {
+                acc[x][y] = fmaf(a[x].x, b[y].x, acc[x][y]);
+                acc[x][y] = fmaf(a[x].y, b[y].y, acc[x][y]);
+                acc[x][y] = fmaf(a[x].z, b[y].z, acc[x][y]);
+                acc[x][y] = fmaf(a[x].w, b[y].w, acc[x][y]);
+            }
+    }
+}
+
+// acc[x][y] += sum_k A[4*tr+x][k] * B[k][4*tc+y], k < 32 (A k-contiguous, B column-contiguous)
+__device__ __forceinline__ void diag_job_nn(float (&acc)[4][4], const float* __restrict__ Ab, const float* __restrict__ Bb,
+                                            int tr, int tc) {
+#pragma unroll
+    for (int k = 0; k < SB; k += 4) {
+        float4 a[4], b[4];
+#pragma unroll
+        for (int x = 0; x < 4; ++x) a[x] = *reinterpret_cast<const float4*>(Ab + (4 * tr + x) * kDiagLd + k);
+#pragma unroll
+        for (int l = 0; l < 4; ++l) b[l] = *reinterpret_cast<const float4*>(Bb + (k + l) * kDiagLd + 4 * tc);
+#pragma unroll
+        for (int x = 0; x < 4; ++x) {
+            const float av[4] = {a[x].x, a[x].y, a[x].z, a[x].w};
+#pragma unroll
+            for (int l = 0; l < 4; ++l) {
+                acc[x][0] = fmaf(av[l], b[l].x, acc[x][0]);
+                acc[x][1] = fmaf(av[l], b[l].y, acc[x][1]);
+                acc[x][2] = fmaf(av[l], b[l].z, acc[x][2]);
+                acc[x][3] = fmaf(av[l], b[l].w, acc[x][3]);
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void diag_store(float* __restrict__ Cb, const float (&acc)[4][4], int tr, int tc, float sign) {
+#pragma unroll
+    for (int x = 0; x < 4; ++x)
+        *reinterpret_cast<float4*>(Cb + (4 * tr + x) * kDiagLd + 4 * tc) =
+            make_float4(sign * acc[x][0], sign * acc[x][1], sign * acc[x][2], sign * acc[x][3]);
+}
+
+// One warp: the 32x32 block at Sb (upper part valid) becomes R (upper, zero below), Vb receives R^-1 (upper;
+// the part below the diagonal is left as it is, i.e. zero).  Returns non-zero when a pivot was not positive.
+// 1/sqrt(pivot) comes from the hardware approximation plus one Newton step (about one ulp); the column is scaled by
+// it instead of being divided by the square root, which takes two long-latency operations out of the chain between
+// consecutive pivots.  That chain is: scale -> update of the next pivot row's entry -> broadcast by shuffle; the
+// rest of the rank-1 update travels through shared memory off the critical path.
+__device__ __forceinline__ int diag_factor_sub(float* __restrict__ Sb, float* __restrict__ Vb, float* __restrict__ colbuf,
+                                               float* __restrict__ rdiag, int lane) {
+    float m[SB];
+#pragma unroll
+    for (int j = 0; j < SB; ++j) m[j] = Sb[lane * kDiagLd + j];        // entries left of the diagonal are never used
+    int bad = 0;
+    float d = __shfl_sync(0xffffffffu, m[SB - 1], SB - 1);
+    float4 pend[SB / 4] = {};                                          // column c+1 as read back from shared memory
+    float rprev = 0.f;
+#pragma unroll
+    for (int c = SB - 1; c >= 0; --c) {
+        if (!(d > 0.f)) bad = 1;                                       // catches <= 0 and NaN
+        float rinv = rsqrtf(d);
+        rinv = fmaf(0.5f * rinv, fmaf(-d * rinv, rinv, 1.f), rinv);
+        const float r = (lane == c) ? d * rinv : ((lane < c) ? m[c] * rinv : 0.f);
+        // the two entries the next two pivots depend on go by shuffle ...
+        if (c > 0) {
+            const float dn = fmaf(-r, r, m[c - 1]);                    // meaningful in lane c-1: the next pivot
+            const float rho = __shfl_sync(0xffffffffu, r, c - 1);
+            d = __shfl_sync(0xffffffffu, dn, c - 1);
+            m[c - 1] = fmaf(-r, rho, m[c - 1]);
+        }
+        if (c > 1) m[c - 2] = fmaf(-r, __shfl_sync(0xffffffffu, r, c - 2), m[c - 2]);
+        Sb[lane * kDiagLd + c] = r;
+        if (lane == c) rdiag[c] = rinv;
+        float* cb = colbuf + (c & 1) * SB;                             // two buffers: one warp barrier per column
+        cb[lane] = r;
+        // ... the rest of the rank-1 update m[i][j] -= R[i][c] R[j][c] (j < c-2) through shared memory, applied one
+        // column late so that its round trip stays off the pivot chain: here column c+1, j < c-1
+        if (c < SB - 1) {
+#pragma unroll
+            for (int j4 = SB / 4 - 1; j4 >= 0; --j4) {
+                if (4 * j4 + 3 < c - 1) m[4 * j4 + 3] = fmaf(-rprev, pend[j4].w, m[4 * j4 + 3]);
+                if (4 * j4 + 2 < c - 1) m[4 * j4 + 2] = fmaf(-rprev, pend[j4].z, m[4 * j4 + 2]);
+                if (4 * j4 + 1 < c - 1) m[4 * j4 + 1] = fmaf(-rprev, pend[j4].y, m[4 * j4 + 1]);
+                if (4 * j4 + 0 < c - 1) m[4 * j4 + 0] = fmaf(-rprev, pend[j4].x, m[4 * j4 + 0]);
+            }
+        }
+        __syncwarp();
+#pragma unroll
+        for (int j4 = 0; j4 < SB / 4; ++j4)
+            if (4 * j4 < c - 2) pend[j4] = *reinterpret_cast<const float4*>(cb + 4 * j4);
+        rprev = r;
+    }
+    __syncwarp();
+    // inverse: lane j owns column j; W[c][j] = -(sum_{c<l<=j} R[c][l] W[l][j]) / R[c][c], W[j][j] = 1 / R[j][j];
+    // terms are added from the far end so that the newest entry closes the chain
+    float w[SB];
+#pragma unroll
+    for (int c = 0; c < SB; ++c) w[c] = 0.f;
+#pragma unroll
+    for (int c = SB - 1; c >= 0; --c) {
+        float p[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int l4 = SB / 4 - 1; l4 >= (c >> 2); --l4) {
+            const float4 v = *reinterpret_cast<const float4*>(Sb + c * kDiagLd + 4 * l4);   // same address in every lane
+            if (4 * l4 + 3 > c) p[3] = fmaf(v.w, w[4 * l4 + 3], p[3]);  // w[l] is zero for l > lane
+            if (4 * l4 + 2 > c) p[2] = fmaf(v.z, w[4 * l4 + 2], p[2]);
+            if (4 * l4 + 1 > c) p[1] = fmaf(v.y, w[4 * l4 + 1], p[1]);
+            if (4 * l4 + 0 > c) p[0] = fmaf(v.x, w[4 * l4 + 0], p[0]);
+        }
+        const float num = (c == lane) ? 1.f : -((p[0] + p[1]) + (p[2] + p[3]));
+        w[c] = (c <= lane) ? num * rdiag[c] : 0.f;
+        if (c <= lane) Vb[c * kDiagLd + lane] = w[c];
+    }
+    return bad;
+}
 
 __global__ void __launch_bounds__(kDiagThreads) diag_block_kernel(float* __restrict__ A, float* __restrict__ U, int Cp,
                                                                   int kblk, int* __restrict__ info) {
-    extern __shared__ float dsm[];
-    float* S = dsm;                               // [NB][kDiagLd]  R (upper)
-    float* V = dsm + NB * kDiagLd;                // [NB][kDiagLd]  R^-1 (upper)
-    __shared__ float piv;
+    extern __shared__ __align__(16) float dsm[];
+    float* S = dsm;                               // [NB][kDiagLd]  A, then R (upper)
+    float* V = dsm + NB * kDiagLd;                // [NB][kDiagLd]  R^-1 (upper); lower blocks are scratch
+    __shared__ __align__(16) float colbuf[2 * SB];
+    __shared__ float rdiag[SB];
     __shared__ int bad;
     const int g = blockIdx.x;
     const int64_t origin = ((int64_t)g * Cp + (int64_t)kblk * NB) * Cp + (int64_t)kblk * NB;
     float* Ab = A + origin;
     float* Ub = U + origin;
     const int tid = threadIdx.x;
-    const int own = tid >> 2, q = tid & 3;        // row (phase 1) / column (phase 2) and quarter of the dot product
+    const int job = tid >> 6, t = tid & 63, tr = t >> 3, tc = t & 7;     // 8 job slots of 64 threads, 4x4 outputs each
     if (tid == 0) bad = 0;
-    for (int e = tid; e < NB * NB; e += kDiagThreads) {
-        const int i = e >> 7, j = e & (NB - 1);
-        S[i * kDiagLd + j] = (j >= i) ? Ab[(int64_t)i * Cp + j] : 0.f;
-        V[i * kDiagLd + j] = 0.f;
-    }
-    __syncthreads();
-
-    // ---- phase 1: columns from the last to the first
-    for (int c = NB - 1; c >= 0; --c) {
-        const float* ri = S + own * kDiagLd;
-        const float* rc = S + c * kDiagLd;
-        if ((tid & ~31) >> 2 > c) {                   // none of this warp's 8 rows takes part any more
-            __syncthreads();
-            __syncthreads();
-            continue;
+    {   // 16-byte loads, all of a thread's requests in flight at once; entries below the diagonal are never read
+        float4 in[NB * NB / 4 / kDiagThreads];
+#pragma unroll
+        for (int it = 0; it < NB * NB / 4 / kDiagThreads; ++it) {
+            const int e = tid + it * kDiagThreads, i = e >> 5, j = (e & 31) * 4;
+            in[it] = (j + 3 >= i) ? *reinterpret_cast<const float4*>(Ab + (int64_t)i * Cp + j) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
-        float acc = 0.f;
-        if (own <= c) {
-            float p0 = 0.f, p1 = 0.f;                 // two chains
-#pragma unroll 4
-            for (int l = c + 1 + q; l < NB; l += 8) {
-                p0 = fmaf(ri[l], rc[l], p0);
-                if (l + 4 < NB) p1 = fmaf(ri[l + 4], rc[l + 4], p1);
-            }
-            acc = p0 + p1;
-        }
-        acc += __shfl_xor_sync(0xffffffffu, acc, 1);  // executed by every lane of the warp
-        acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-        const float t = __fsub_rn(ri[c], acc);
-        if (own == c && q == 0) {
-            if (!(t > 0.f)) bad = 1;                  // catches <= 0 and NaN
-            piv = __fsqrt_rn(t);
-        }
-        __syncthreads();
-        if (own <= c && q == 0) S[own * kDiagLd + c] = (own == c) ? piv : __fdiv_rn(t, piv);
-        __syncthreads();
-    }
-
-    // ---- phase 2: inverse, one column per lane quad, no CTA-wide dependency
-    {
-        const int j = own;
-        if (q == 0) V[j * kDiagLd + j] = __fdiv_rn(1.f, S[j * kDiagLd + j]);
-        __syncwarp();
-        const int jmax = (tid | 31) >> 2;             // last column handled by this warp: uniform trip count
-        for (int c = jmax - 1; c >= 0; --c) {
-            const float* rc = S + c * kDiagLd;
-            float acc = 0.f;
-            if (c < j) {
-                float p0 = 0.f, p1 = 0.f;
-#pragma unroll 4
-                for (int l = c + 1 + q; l <= j; l += 8) {
-                    p0 = fmaf(rc[l], V[l * kDiagLd + j], p0);
-                    if (l + 4 <= j) p1 = fmaf(rc[l + 4], V[(l + 4) * kDiagLd + j], p1);
-                }
-                acc = p0 + p1;
-            }
-            acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-            acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-            if (q == 0 && c < j) V[c * kDiagLd + j] = __fdiv_rn(-acc, rc[c]);
-            __syncwarp();
+#pragma unroll
+        for (int it = 0; it < NB * NB / 4 / kDiagThreads; ++it) {
+            const int e = tid + it * kDiagThreads, i = e >> 5, j = (e & 31) * 4;
+            *reinterpret_cast<float4*>(S + i * kDiagLd + j) = in[it];
+            *reinterpret_cast<float4*>(V + i * kDiagLd + j) = make_float4(0.f, 0.f, 0.f, 0.f);
         }
     }
     __syncthreads();
-    for (int e = tid; e < NB * NB; e += kDiagThreads) {
-        const int i = e >> 7, j = e & (NB - 1);
-        Ab[(int64_t)i * Cp + j] = (j >= i) ? S[i * kDiagLd + j] : 0.f;
-        Ub[(int64_t)i * Cp + j] = (j >= i) ? V[i * kDiagLd + j] : 0.f;
+    auto blk = [&](float* M, int bi, int bj) -> float* { return M + (bi * SB) * kDiagLd + bj * SB; };
+
+    // ---- factorisation, sub-block columns from the last to the first
+    for (int b = NB / SB - 1; b >= 0; --b) {
+        if (tid < 32) {
+            if (diag_factor_sub(blk(S, b, b), blk(V, b, b), colbuf, rdiag, tid) && tid == 0) bad = 1;
+        }
+        __syncthreads();
+        if (b == 0) break;
+        float acc[4][4] = {};
+        if (job < b) diag_job_nt(acc, blk(S, job, b), blk(V, b, b), tr, tc);          // R_ib = A_ib . W_bb^T
+        __syncthreads();
+        if (job < b) {
+            float* Cb = blk(S, job, b);
+#pragma unroll
+            for (int x = 0; x < 4; ++x)
+#pragma unroll
+                for (int y = 0; y < 4; ++y) Cb[(4 * tr + x) * kDiagLd + tc + 8 * y] = acc[x][y];
+        }
+        __syncthreads();
+        if (job < b * (b + 1) / 2) {                                                  // A_ij -= R_ib . R_jb^T
+            int i = 0, rest = job;
+            while (rest >= b - i) { rest -= b - i; ++i; }
+            const int jj = i + rest;
+            float a2[4][4] = {};
+            diag_job_nt(a2, blk(S, i, b), blk(S, jj, b), tr, tc);
+            float* Cb = blk(S, i, jj);
+#pragma unroll
+            for (int x = 0; x < 4; ++x)
+#pragma unroll
+                for (int y = 0; y < 4; ++y) Cb[(4 * tr + x) * kDiagLd + tc + 8 * y] -= a2[x][y];
+        }
+        __syncthreads();
+    }
+
+    // ---- inverse of the block-triangular factor
+    {   // sub-block pairs (0,1) and (2,3):  T = W_aa . R_ab (parked at V(b,a)),  U_ab = -T . W_bb
+        const int a = 2 * job, b = 2 * job + 1;
+        float acc[4][4] = {};
+        if (job < 2) {
+            diag_job_nn(acc, blk(V, a, a), blk(S, a, b), tr, tc);
+            diag_store(blk(V, b, a), acc, tr, tc, 1.f);
+        }
+        __syncthreads();
+        float ac2[4][4] = {};
+        if (job < 2) {
+            diag_job_nn(ac2, blk(V, b, a), blk(V, b, b), tr, tc);
+            diag_store(blk(V, a, b), ac2, tr, tc, -1.f);
+        }
+        __syncthreads();
+    }
+    {   // the 64-wide pair: p in {0,1}, q in {2,3}:  T_pq = sum_{l=p..1} U_pl . R_lq (parked at V(q,p)),
+        //                                            U_pq = -sum_{l=2..q} T_pl . U_lq
+        const int p = job >> 1, q = 2 + (job & 1);
+        float acc[4][4] = {};
+        if (job < 4) {
+            for (int l = p; l < 2; ++l) diag_job_nn(acc, blk(V, p, l), blk(S, l, q), tr, tc);
+            diag_store(blk(V, q, p), acc, tr, tc, 1.f);
+        }
+        __syncthreads();
+        float ac2[4][4] = {};
+        if (job < 4) {
+            for (int l = 2; l <= q; ++l) diag_job_nn(ac2, blk(V, l, p), blk(V, l, q), tr, tc);
+            diag_store(blk(V, p, q), ac2, tr, tc, -1.f);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int it = 0; it < NB * NB / 4 / kDiagThreads; ++it) {
+        const int e = tid + it * kDiagThreads, i = e >> 5, j = (e & 31) * 4;
+        float4 r = *reinterpret_cast<const float4*>(S + i * kDiagLd + j);
+        float4 u = *reinterpret_cast<const float4*>(V + i * kDiagLd + j);
+        if (j + 0 < i) { r.x = 0.f; u.x = 0.f; }
+        if (j + 1 < i) { r.y = 0.f; u.y = 0.f; }
+        if (j + 2 < i) { r.z = 0.f; u.z = 0.f; }
+        if (j + 3 < i) { r.w = 0.f; u.w = 0.f; }
+        *reinterpret_cast<float4*>(Ab + (int64_t)i * Cp + j) = r;
+        *reinterpret_cast<float4*>(Ub + (int64_t)i * Cp + j) = u;
     }
     if (tid == 0 && bad) atomicCAS(&info[g], 0, kblk + 1);
 }
