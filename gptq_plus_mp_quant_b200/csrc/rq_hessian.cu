@@ -145,6 +145,32 @@ __device__ __forceinline__ void decode_tile(int u, int& i, int& j) {
     i = u - jj * (jj + 1);
 }
 
+// Tile order of one launch.  Concurrently running CTAs take consecutive indices, so the order decides what
+// they share in L2.  The operand that depends on the group (Y_g) is the expensive one: no two groups share it.
+//   Y on the 256-wide side: group fastest, then row block i inside column block j (CTAs share X_hi[i] across
+//     groups and Y_g[j] across the i of a column block);
+//   Y on the 128-row side (bf16 X): row-major, all column blocks j of one (i, g) consecutively, so the CTAs of
+//     a wave share a handful of Y_g[i] row blocks and stream the X_hi plane once.
+template <bool ROW_MAJOR>
+__device__ __forceinline__ void decode_work(int t, int G, int NT, int& g, int& i, int& j) {
+    if (ROW_MAJOR) {
+        int rem = t;
+        i = 0;
+        for (;;) {
+            const int cnt = G * (NT - (i >> 1));
+            if (rem < cnt) break;
+            rem -= cnt;
+            ++i;
+        }
+        const int per = NT - (i >> 1);
+        g = rem / per;
+        j = (i >> 1) + (rem - g * per);
+    } else {
+        g = t % G;
+        decode_tile(t / G, i, j);
+    }
+}
+
 struct Bars {
     uint64_t full[8];
     uint64_t empty[8];
@@ -203,9 +229,8 @@ umma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CU
             uint32_t it = 0;
             bool ok = true;
             for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-                const int g = t % G;
-                int i, j;
-                decode_tile(t / G, i, j);
+                int g, i, j;
+                decode_work<K::kSwap>(t, G, NT, g, i, j);
                 for (int kb = 0; kb < kblocks; ++kb, ++it) {
                     const uint32_t s = it % K::kStages;
                     const uint32_t ph = (it / K::kStages) & 1u;
@@ -302,9 +327,8 @@ umma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CU
         const bool vec_ok = (C & 3) == 0;
         bool alive = true;
         for (int t = blockIdx.x; t < total_tiles && alive; t += gridDim.x) {
-            const int g = t % G;
-            int i, j;
-            decode_tile(t / G, i, j);
+            int g, i, j;
+            decode_work<K::kSwap>(t, G, NT, g, i, j);
             const int row0 = i * BM + q * 32;
             const int row = row0 + lane;
             const int colbase = j * BN + half * 128;
