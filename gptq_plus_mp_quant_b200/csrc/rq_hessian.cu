@@ -185,7 +185,7 @@ template <int BK, int NPROD, bool WIDE_Y>
 __global__ void __launch_bounds__(kThreads, 1)
 umma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
             float* __restrict__ H, int C, int G, int MT, int NT, int kblocks, int a_plane, int b_plane0,
-            float alpha, float beta, int* __restrict__ status) {
+            float alpha, float beta, int ksplit, int* __restrict__ status) {
     using K = Cfg<BK, NPROD, WIDE_Y>;
     constexpr int WIN = kWindowTokens / BK;                              // k-blocks per accumulation window
     extern __shared__ uint8_t smem_raw[];
@@ -198,7 +198,12 @@ umma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CU
     const int lane = threadIdx.x & 31;
     const int tiles_per_group = (NT - 1) * NT + MT;
     const int total_tiles = tiles_per_group * G;
-    const int nwin = (kblocks + WIN - 1) / WIN;
+    // A work unit is (tile, part of the chunk's tokens): with ksplit > 1 every tile is visited ksplit times, each
+    // visit adding the sum over its share of the k-blocks into H (only with the reduction epilogue, beta == 1),
+    // which evens out the last round when the tile count is a poor multiple of the grid.  Units are ordered
+    // part-major so that concurrently running CTAs stream the same token range.
+    const int total_units = total_tiles * ksplit;
+    const int kb_per_part = ((kblocks + ksplit - 1) / ksplit + WIN - 1) / WIN * WIN;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < K::kStages; ++s) {
@@ -228,10 +233,13 @@ umma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CU
         if (lane == 0) {
             uint32_t it = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+            for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
+                const int part = u / total_tiles, t = u - part * total_tiles;
+                const int kb0 = part * kb_per_part;
+                const int kb1 = (kb0 + kb_per_part < kblocks) ? kb0 + kb_per_part : kblocks;
                 int g, i, j;
                 decode_work<K::kSwap>(t, G, NT, g, i, j);
-                for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     const uint32_t s = it % K::kStages;
                     const uint32_t ph = (it / K::kStages) & 1u;
                     if (!mbar_wait(smem_u32(&bars->empty[s]), ph ^ 1u, abort_flag)) { ok = false; break; }
@@ -272,15 +280,20 @@ umma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CU
             constexpr uint32_t idesc = umma_idesc_bf16_f32(BM, BN);
             uint32_t it = 0, win_iter = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+            for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
+                const int part = u / total_tiles;
+                const int kb0 = part * kb_per_part;
+                const int kb1 = (kb0 + kb_per_part < kblocks) ? kb0 + kb_per_part : kblocks;
+                const int nwin = (kb1 - kb0 + WIN - 1) / WIN;
                 for (int w = 0; w < nwin && ok; ++w, ++win_iter) {
                     const uint32_t acc = win_iter & 1u;
                     const uint32_t acc_ph = (win_iter >> 1) & 1u;
                     if (!mbar_wait(smem_u32(&bars->tempty[acc]), acc_ph ^ 1u, abort_flag)) { ok = false; break; }
                     tc_fence_after();
                     const uint32_t d_tmem = tmem_base + acc * BN;
-                    const int kb_end = ((w + 1) * WIN < kblocks) ? (w + 1) * WIN : kblocks;
-                    for (int kb = w * WIN; kb < kb_end; ++kb, ++it) {
+                    const int kb_begin = kb0 + w * WIN;
+                    const int kb_end = (kb_begin + WIN < kb1) ? kb_begin + WIN : kb1;
+                    for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
                         const uint32_t s = it % K::kStages;
                         const uint32_t ph = (it / K::kStages) & 1u;
                         if (!mbar_wait(smem_u32(&bars->full[s]), ph, abort_flag)) { ok = false; break; }
@@ -296,7 +309,7 @@ umma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CU
                             const uint64_t dal = umma_smem_desc(a_lo + koff, K::kSBO, K::kLayout);
                             const uint64_t dbh = umma_smem_desc(b_hi + koff, K::kSBO, K::kLayout);
                             // the first MMA of a window overwrites the accumulator; small terms go first
-                            const uint32_t keep = (kb != w * WIN || k != 0) ? 1u : 0u;
+                            const uint32_t keep = (kb != kb_begin || k != 0) ? 1u : 0u;
                             if (NPROD == 3) {
                                 const uint64_t dbl = umma_smem_desc(b_lo + koff, K::kSBO, K::kLayout);
                                 umma_bf16(d_tmem, dah, dbl, idesc, keep);
@@ -326,7 +339,12 @@ umma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CU
         uint32_t win_iter = 0;
         const bool vec_ok = (C & 3) == 0;
         bool alive = true;
-        for (int t = blockIdx.x; t < total_tiles && alive; t += gridDim.x) {
+        for (int u = blockIdx.x; u < total_units && alive; u += gridDim.x) {
+            const int part = u / total_tiles, t = u - part * total_tiles;
+            const int kb0 = part * kb_per_part;
+            const int kb1 = (kb0 + kb_per_part < kblocks) ? kb0 + kb_per_part : kblocks;
+            const int nwin = (kb1 - kb0 + WIN - 1) / WIN;
+            if (nwin <= 0) continue;
             int g, i, j;
             decode_work<K::kSwap>(t, G, NT, g, i, j);
             const int row0 = i * BM + q * 32;
@@ -370,7 +388,18 @@ umma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CU
                 for (int cb = 0; cb < 4; ++cb) {
                     const int col0 = colbase + cb * 32;
                     if (!use[cb]) continue;
-                    if (vec_ok && col0 + 32 <= C) {
+                    if (vec_ok && col0 + 32 <= C && beta == 1.f) {
+                        // accumulate in place with fire-and-forget vector reductions: this launch updates every
+                        // element of H from exactly one thread, so the result is the same add as a
+                        // load-add-store, without the read round trip that would keep this warp away from
+                        // the next tile's accumulation windows
+#pragma unroll
+                        for (int e = 0; e < 8; ++e)
+                            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(hrow + col0 + 4 * e),
+                                         "f"(alpha * run[cb * 32 + 4 * e + 0]), "f"(alpha * run[cb * 32 + 4 * e + 1]),
+                                         "f"(alpha * run[cb * 32 + 4 * e + 2]), "f"(alpha * run[cb * 32 + 4 * e + 3])
+                                         : "memory");
+                    } else if (vec_ok && col0 + 32 <= C) {
                         float4* p4 = reinterpret_cast<float4*>(hrow + col0);
 #pragma unroll
                         for (int e = 0; e < 8; ++e) {
@@ -509,10 +538,26 @@ static int launch_umma(void* planes, int64_t Kc, int C, int G, int nplanes, int 
         return RQ_ERR_CUDA;
     const int MT = (C + BM - 1) / BM, NT = (C + BN - 1) / BN;
     const int total = ((NT - 1) * NT + MT) * G;
-    const int grid = total < num_sms() ? total : num_sms();
+    const int kblocks = (int)(Kc / BK);
+    // token split: pick the number of parts that minimises rounds x (k-blocks per part + a per-visit overhead);
+    // needs the reduction epilogue (beta == 1, whole 32-column chunks), since two visits of a tile may overlap
+    int ksplit = 1;
+    if (beta == 1.f && (C & 31) == 0) {
+        constexpr int WIN = kWindowTokens / BK;
+        long long best = -1;
+        for (int sp = 1; sp <= 8; ++sp) {
+            const int per = ((kblocks + sp - 1) / sp + WIN - 1) / WIN * WIN;
+            if (sp > 1 && per < 8 * WIN) break;
+            const long long rounds = ((long long)total * sp + num_sms() - 1) / num_sms();
+            const long long cost = rounds * (per + 3);
+            if (best < 0 || cost < best) { best = cost; ksplit = sp; }
+        }
+    }
+    const long long units = (long long)total * ksplit;
+    const int grid = units < num_sms() ? (int)units : num_sms();
     prof::Scope timed(RQ_PROF_HESSIAN_UMMA, st);
-    umma_kernel<BK, NPROD, WIDE_Y><<<grid, kThreads, K::kSmemBytes, st>>>(mapA, mapB, H, C, G, MT, NT, (int)(Kc / BK), 0,
-                                                                  b_plane0, alpha, beta, status);
+    umma_kernel<BK, NPROD, WIDE_Y><<<grid, kThreads, K::kSmemBytes, st>>>(mapA, mapB, H, C, G, MT, NT, kblocks, 0,
+                                                                  b_plane0, alpha, beta, ksplit, status);
     return check_launch();
 }
 
