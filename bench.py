@@ -137,6 +137,11 @@ def dist_setup():
     return rank, world, local
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the Hessian kernel at C = 4096, G = 4, 8192 tokens
+# (ncu, summarised in profiles/hessian_umma_C4096_G4_tok8192_bf16.md)
+UMMA_TRAFFIC_BYTES = 1.203e9
+
+
 def assign_owners(costs, world):
     """Longest-processing-time-first assignment of fasterquant work units to ranks."""
     load = [0.0] * world
@@ -414,7 +419,10 @@ def run_ours(args):
         "hessian_accum_tflops": round(wl.hessian_flops() * args.steps / (umma_ms * 1e-3 + prof["pack"][0] * 1e-3)
                                       / 1e12, 1) if umma_ms else None,
         "roofline": {"bound": "tensor", "achieved": round(achieved, 1), "peak": peak, "unit": "TFLOP/s",
-                     "frac": round(achieved / peak, 4), "traffic": None, "peak_source": peaks["source"] + " sustained",
+                     "frac": round(achieved / peak, 4), "traffic": UMMA_TRAFFIC_BYTES,
+                     "traffic_note": "dram__bytes_read+write of one C=4096 G=4 8192-token launch (6 of the 7 launches "
+                                     "per chunk), ncu; algorithmic 0.89e9; the C=12288 launch was not captured",
+                     "peak_source": peaks["source"] + " sustained",
                      "kernel": "rq::hess::umma_kernel<64,2> (+<64,3> for fp32 inputs)", "launches": umma_n,
                      "note": "algorithmic 2*N*C^2*G; the kernel issues 2 bf16 products on the ~53% of tiles that "
                              "touch the upper triangle"},
