@@ -67,7 +67,9 @@ __global__ void __launch_bounds__(256) pack_kernel(const T* __restrict__ x, int6
                                                    const float* __restrict__ sal, int nvalid, int C, int G, int Kc,
                                                    __nv_bfloat16* __restrict__ planes, float* __restrict__ partial,
                                                    int write_xlo) {
-    __shared__ float xs[kPackTile][kPackTile + 1];
+    // channel-major tile: the write side (64 consecutive channels of one token per 64 threads) strides by the
+    // row length, the read side takes two adjacent tokens of one channel as one 8-byte word
+    __shared__ __align__(8) float xs[kPackTile][kPackTile + 2];
     __shared__ float ss[kPackTile][8];
     const int t0 = blockIdx.x * kPackTile;
     const int c0 = blockIdx.y * kPackTile;
@@ -81,7 +83,7 @@ __global__ void __launch_bounds__(256) pack_kernel(const T* __restrict__ x, int6
             const int t = p * 4 + tr;
             float v = 0.f;
             if (t0 + t < nvalid && c0 + cc < C) v = load_as_float<T>(x, (int64_t)(t0 + t) * ldx + c0 + cc);
-            xs[t][cc] = v;
+            xs[cc][t] = v;
         }
         if (sal != nullptr) {
             for (int e = tid; e < kPackTile * G; e += 256) {
@@ -95,10 +97,17 @@ __global__ void __launch_bounds__(256) pack_kernel(const T* __restrict__ x, int6
     const int warp = tid >> 5, lane = tid & 31;
     const int64_t plane_stride = (int64_t)C * Kc;
     const int ta = 2 * lane, tb = 2 * lane + 1;
+    float sa[8], sb[8];                                        // this lane's two tokens' saliencies, read once
+#pragma unroll
+    for (int g = 0; g < 8; ++g) {
+        sa[g] = (sal != nullptr && g < G) ? ss[ta][g] : 0.f;
+        sb[g] = (sal != nullptr && g < G) ? ss[tb][g] : 0.f;
+    }
     for (int cc = warp; cc < kPackTile; cc += 8) {
         const int c = c0 + cc;
         if (c >= C) break;                                     // warp-uniform
-        const float xa = xs[ta][cc], xb = xs[tb][cc];
+        const float2 xab = *reinterpret_cast<const float2*>(&xs[cc][ta]);
+        const float xa = xab.x, xb = xab.y;
         const int64_t off = (int64_t)c * Kc + t0 + ta;          // even -> 4-byte aligned pair
         __nv_bfloat16 ha, la, hb, lb;
         split_bf16(xa, ha, la);
@@ -106,9 +115,11 @@ __global__ void __launch_bounds__(256) pack_kernel(const T* __restrict__ x, int6
         *reinterpret_cast<__nv_bfloat162*>(planes + off) = __halves2bfloat162(ha, hb);
         if (write_xlo) *reinterpret_cast<__nv_bfloat162*>(planes + plane_stride + off) = __halves2bfloat162(la, lb);
         if (sal != nullptr) {
-            for (int g = 0; g < G; ++g) {
-                const float ya = __fmul_rn(xa, ss[ta][g]);
-                const float yb = __fmul_rn(xb, ss[tb][g]);
+#pragma unroll
+            for (int g = 0; g < 8; ++g) {
+                if (g >= G) break;
+                const float ya = __fmul_rn(xa, sa[g]);
+                const float yb = __fmul_rn(xb, sb[g]);
                 split_bf16(ya, ha, la);
                 split_bf16(yb, hb, lb);
                 *reinterpret_cast<__nv_bfloat162*>(planes + (2 + 2 * g) * plane_stride + off) = __halves2bfloat162(ha, hb);
