@@ -532,14 +532,28 @@ extern "C" int rq_chol_hinv(const float* H, const int64_t* perm, const float* da
     __nv_bfloat16* PU = reinterpret_cast<__nv_bfloat16*>(plane_base + fpb);
     __nv_bfloat16* PUt = reinterpret_cast<__nv_bfloat16*>(plane_base + 2 * fpb);
     __nv_bfloat16* PT = reinterpret_cast<__nv_bfloat16*>(plane_base + 3 * fpb);
-    auto split_full = [&](const float* src, __nv_bfloat16* dst, bool transpose) {
+    // Operand planes are filled only where a level reads them.  Entries of U are final once written, so its
+    // planes (U and U^T) start as the band of diagonal blocks the CUDA-core levels produced and then receive,
+    // level by level, just the off-diagonal blocks that level created; T is split block by block as well;
+    // R^T once, above the diagonal.
+    auto plane_args = [&](const float* src, __nv_bfloat16* dst) {
         tcgemm::SplitArgs sa;
         sa.src = src; sa.ld = Cp; sa.src_z = (long long)Cp * Cp; sa.rows = Cp; sa.cols = Cp;
         sa.dst = dst; sa.Kp = Cp; sa.plane_stride = (long long)Cp * Cp; sa.plane = 0; sa.plane_z = 2;
         sa.dst_row0 = 0; sa.dst_row_z = 0; sa.dst_k0 = 0; sa.pad_k_to = 0;
+        return sa;
+    };
+    // blocks (a, b) of level s: rows [2ms, 2ms+s), columns [2ms+s, min(2ms+2s, Cp)), m = 0 .. pairs-1
+    auto split_pair_blocks = [&](const float* src, __nv_bfloat16* dst, int s, int pairs, bool transpose) {
+        tcgemm::SplitArgs sa = plane_args(src + s, dst);
+        sa.rows = s; sa.cols = s; sa.nz1 = pairs; sa.src_z1 = (long long)2 * s * Cp + 2 * s;
+        sa.src_col0 = s; sa.src_col_z1 = 2 * s; sa.src_cols_total = Cp;
+        sa.src_row0 = 0; sa.src_row_z1 = 2 * s; sa.src_rows_total = Cp;
+        if (transpose) { sa.dst_row0 = s; sa.dst_k0 = 0; } else { sa.dst_row0 = 0; sa.dst_k0 = s; }
+        sa.dst_row_z1 = 2 * s; sa.dst_k_z1 = 2 * s;
         return transpose ? tcgemm::split_transpose(sa, G, st) : tcgemm::split_rows(sa, G, st);
     };
-    bool rt_ready = false;
+    bool planes_ready = false;
     for (int s = NB; s < Cp; s *= 2) {
         const int pairs = (Cp + 2 * s - 1) / (2 * s);
         if (s < kTensorInverseMinBlock || fpb == 0) {
@@ -550,15 +564,22 @@ extern "C" int rq_chol_hinv(const float* H, const int64_t* perm, const float* da
             continue;
         }
         // tensor-core level: pair m merges a = [2ms, 2ms+s) and b = [2ms+s, min(2ms+2s, Cp))
-        if (!rt_ready) {
-            rc = split_full(A, PRt, true);                       // planes of R^T: [n][k] = R[k][n]
+        if (!planes_ready) {
+            tcgemm::SplitArgs sa = plane_args(A, PRt);             // planes of R^T: [n][k] = R[k][n], k <= n
+            sa.upper_only = 1;
+            rc = tcgemm::split_transpose(sa, G, st);
             if (rc != RQ_OK) return rc;
-            rt_ready = true;
+            for (int tr = 0; tr < 2; ++tr) {                       // diagonal blocks of width s of U and U^T
+                tcgemm::SplitArgs sd = plane_args(Hinv, tr ? PUt : PU);
+                sd.rows = s; sd.cols = s; sd.nz1 = (Cp + s - 1) / s; sd.src_z1 = (long long)s * Cp + s;
+                sd.src_col0 = 0; sd.src_col_z1 = s; sd.src_cols_total = Cp;
+                sd.src_row0 = 0; sd.src_row_z1 = s; sd.src_rows_total = Cp;
+                sd.dst_row_z1 = s; sd.dst_k_z1 = s;
+                rc = tr ? tcgemm::split_transpose(sd, G, st) : tcgemm::split_rows(sd, G, st);
+                if (rc != RQ_OK) return rc;
+            }
+            planes_ready = true;
         }
-        rc = split_full(Hinv, PU, false);
-        if (rc != RQ_OK) return rc;
-        rc = split_full(Hinv, PUt, true);
-        if (rc != RQ_OK) return rc;
         tcgemm::PlaneTensor tRt{PRt, Cp, Cp, 2LL * G}, tU{PU, Cp, Cp, 2LL * G}, tUt{PUt, Cp, Cp, 2LL * G},
             tT{PT, Cp, Cp, 2LL * G};
         tcgemm::Params gp;
@@ -573,13 +594,19 @@ extern "C" int rq_chol_hinv(const float* H, const int64_t* perm, const float* da
         gp.C = T + s; gp.alpha = 1.f;
         rc = tcgemm::launch(tU, tRt, gp, tc_status, st);
         if (rc != RQ_OK) return rc;
-        rc = split_full(T, PT, false);
+        rc = split_pair_blocks(T, PT, s, pairs, false);
         if (rc != RQ_OK) return rc;
         // step 2: U[a, b] = -T[a, b] . U[b, b]
         gp.a_row0 = 0; gp.a_k0 = s; gp.b_row0 = s; gp.b_k0 = s; gp.kmode = 2;
         gp.C = Hinv + s; gp.alpha = -1.f;
         rc = tcgemm::launch(tT, tUt, gp, tc_status, st);
         if (rc != RQ_OK) return rc;
+        if (2 * s < Cp) {                                          // the next level reads the blocks just created
+            rc = split_pair_blocks(Hinv, PU, s, pairs, false);
+            if (rc != RQ_OK) return rc;
+            rc = split_pair_blocks(Hinv, PUt, s, pairs, true);
+            if (rc != RQ_OK) return rc;
+        }
     }
     finite_check_kernel<<<dim3(64, (unsigned)G), 256, 0, st>>>(Hinv, Cp, info);
     merge_status_kernel<<<1, 64, 0, st>>>(tc_status, info, G);

@@ -329,6 +329,16 @@ struct SplitArgs {
     int plane, plane_z;                         // hi plane index and its per-batch increment
     int dst_row0, dst_row_z, dst_k0;            // where the block lands inside the plane
     int pad_k_to;                               // zero-fill k in [cols_k, pad_k_to) (relative to dst_k0); 0 = no fill
+    // second batch dimension (blockIdx.z = z * nz1 + z1): a series of equally shaped blocks of one matrix
+    int nz1 = 1;
+    long long src_z1 = 0;                       // source offset per z1 (elements)
+    int dst_row_z1 = 0, dst_k_z1 = 0;           // destination offsets per z1
+    // when src_cols_total > 0 the block's columns are clipped to src_cols_total - (src_col0 + z1 * src_col_z1)
+    int src_col0 = 0, src_col_z1 = 0, src_cols_total = 0;
+    // likewise for rows: src_rows_total - (src_row0 + z1 * src_row_z1)
+    int src_row0 = 0, src_row_z1 = 0, src_rows_total = 0;
+    int upper_only = 0;                         // transpose: skip source tiles that lie strictly below the diagonal
+    int vec4 = 0;                               // set by the launcher when every offset is a multiple of 4 elements
 };
 
 __device__ __forceinline__ void split2(float v, __nv_bfloat16& hi, __nv_bfloat16& lo) {
@@ -336,50 +346,109 @@ __device__ __forceinline__ void split2(float v, __nv_bfloat16& hi, __nv_bfloat16
     lo = __float2bfloat16_rn(v - __bfloat162float(hi));
 }
 
-// rows stay rows: dst[row0 + r][k0 + c] = src[r][c].  grid (ceil(kspan/256), rows (capped), batch)
+__device__ __forceinline__ int split_clipped_rows(const SplitArgs& a, int z1) {
+    int rows = a.rows;
+    if (a.src_rows_total > 0) {
+        const int lim = a.src_rows_total - (a.src_row0 + z1 * a.src_row_z1);
+        if (lim < rows) rows = lim;
+    }
+    return rows;
+}
+
+__device__ __forceinline__ int split_clipped_cols(const SplitArgs& a, int z1) {
+    int cols = a.cols;
+    if (a.src_cols_total > 0) {
+        const int lim = a.src_cols_total - (a.src_col0 + z1 * a.src_col_z1);
+        if (lim < cols) cols = lim;
+    }
+    return cols;
+}
+
+// rows stay rows: dst[row0 + r][k0 + c] = src[r][c].  grid (ceil(kspan/1024), rows (capped), batch)
 static __global__ void __launch_bounds__(256) split_rows_kernel(const SplitArgs a) {
-    const int z = blockIdx.z;
-    const float* src = a.src + (long long)z * a.src_z;
+    const int z = blockIdx.z / a.nz1, z1 = blockIdx.z - z * a.nz1;
+    const float* src = a.src + (long long)z * a.src_z + (long long)z1 * a.src_z1;
     __nv_bfloat16* hi = a.dst + (long long)(a.plane + z * a.plane_z) * a.plane_stride;
     __nv_bfloat16* lo = hi + a.plane_stride;
-    const int kspan = a.pad_k_to > a.cols ? a.pad_k_to : a.cols;
-    for (int r = blockIdx.y; r < a.rows; r += gridDim.y) {
-        const long long drow = (long long)(a.dst_row0 + z * a.dst_row_z + r) * a.Kp + a.dst_k0;
-        for (int c = blockIdx.x * 256 + threadIdx.x; c < kspan; c += gridDim.x * 256) {
-            const float v = c < a.cols ? src[(long long)r * a.ld + c] : 0.f;
-            __nv_bfloat16 h, l;
-            split2(v, h, l);
-            hi[drow + c] = h;
-            lo[drow + c] = l;
+    const int cols = split_clipped_cols(a, z1);
+    if (cols <= 0 && a.pad_k_to <= 0) return;
+    const int kspan = a.pad_k_to > cols ? a.pad_k_to : cols;
+    const int rows = split_clipped_rows(a, z1);
+    for (int r = blockIdx.y; r < rows; r += gridDim.y) {
+        const long long drow =
+            (long long)(a.dst_row0 + z * a.dst_row_z + z1 * a.dst_row_z1 + r) * a.Kp + a.dst_k0 + z1 * a.dst_k_z1;
+        const float* srow = src + (long long)r * a.ld;
+        if (a.vec4) {
+            for (int c = (blockIdx.x * 256 + threadIdx.x) * 4; c < kspan; c += gridDim.x * 1024) {
+                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (c + 3 < cols) {
+                    v = *reinterpret_cast<const float4*>(srow + c);
+                } else {
+                    if (c + 0 < cols) v.x = srow[c + 0];
+                    if (c + 1 < cols) v.y = srow[c + 1];
+                    if (c + 2 < cols) v.z = srow[c + 2];
+                }
+                __nv_bfloat16 h0, h1, h2, h3, l0, l1, l2, l3;
+                split2(v.x, h0, l0); split2(v.y, h1, l1); split2(v.z, h2, l2); split2(v.w, h3, l3);
+                if (c + 3 < kspan) {
+                    __nv_bfloat162 hp[2] = {__halves2bfloat162(h0, h1), __halves2bfloat162(h2, h3)};
+                    __nv_bfloat162 lp[2] = {__halves2bfloat162(l0, l1), __halves2bfloat162(l2, l3)};
+                    *reinterpret_cast<uint2*>(hi + drow + c) = *reinterpret_cast<const uint2*>(hp);
+                    *reinterpret_cast<uint2*>(lo + drow + c) = *reinterpret_cast<const uint2*>(lp);
+                } else {
+                    const __nv_bfloat16 hs[4] = {h0, h1, h2, h3}, ls[4] = {l0, l1, l2, l3};
+                    for (int e = 0; e < 4 && c + e < kspan; ++e) { hi[drow + c + e] = hs[e]; lo[drow + c + e] = ls[e]; }
+                }
+            }
+        } else {
+            for (int c = blockIdx.x * 256 + threadIdx.x; c < kspan; c += gridDim.x * 256) {
+                const float v = c < cols ? srow[c] : 0.f;
+                __nv_bfloat16 h, l;
+                split2(v, h, l);
+                hi[drow + c] = h;
+                lo[drow + c] = l;
+            }
         }
     }
 }
 
-// transpose: dst[row0 + c][k0 + r] = src[r][c]   (source rows become k).  grid (ceil(cols/32), ceil(rows/32), batch)
+// transpose: dst[row0 + c][k0 + r] = src[r][c]   (source rows become k).  One CTA moves 64 source rows x 32 columns;
+// a thread stores two consecutive k.  grid (ceil(cols/32), ceil(kspan/64), batch)
 static __global__ void __launch_bounds__(256) split_transpose_kernel(const SplitArgs a) {
-    __shared__ float tile[32][33];
-    const int z = blockIdx.z;
-    const float* src = a.src + (long long)z * a.src_z;
+    __shared__ float tile[64][33];
+    const int z = blockIdx.z / a.nz1, z1 = blockIdx.z - z * a.nz1;
+    const float* src = a.src + (long long)z * a.src_z + (long long)z1 * a.src_z1;
     __nv_bfloat16* hi = a.dst + (long long)(a.plane + z * a.plane_z) * a.plane_stride;
     __nv_bfloat16* lo = hi + a.plane_stride;
+    const int cols = split_clipped_cols(a, z1);
+    const int rows = split_clipped_rows(a, z1);
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
-    const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+    const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 64;
+    if (c0 >= cols || (r0 >= rows && a.pad_k_to <= rows)) return;
+    if (a.upper_only && r0 > c0 + 31) return;            // every element of the tile has row > column
 #pragma unroll
-    for (int rr = ty; rr < 32; rr += 8) {
+    for (int rr = ty; rr < 64; rr += 8) {
         const int r = r0 + rr, c = c0 + tx;
-        tile[rr][tx] = (r < a.rows && c < a.cols) ? src[(long long)r * a.ld + c] : 0.f;
+        tile[rr][tx] = (r < rows && c < cols) ? src[(long long)r * a.ld + c] : 0.f;
     }
     __syncthreads();
-    const int kspan = a.pad_k_to > a.rows ? a.pad_k_to : a.rows;
+    const int kspan = a.pad_k_to > rows ? a.pad_k_to : rows;
+    const bool pair_ok = ((a.Kp | a.dst_k0 | a.dst_k_z1 | a.plane_stride) & 1) == 0;
 #pragma unroll
     for (int cc = ty; cc < 32; cc += 8) {
-        const int c = c0 + cc, r = r0 + tx;              // r runs along k of the destination
-        if (c < a.cols && r < kspan) {
-            const long long d = (long long)(a.dst_row0 + z * a.dst_row_z + c) * a.Kp + a.dst_k0 + r;
-            __nv_bfloat16 h, l;
-            split2(tile[tx][cc], h, l);
-            hi[d] = h;
-            lo[d] = l;
+        const int c = c0 + cc, r = r0 + 2 * tx;           // r runs along k of the destination
+        if (c >= cols || r >= kspan) continue;
+        const long long d =
+            (long long)(a.dst_row0 + z * a.dst_row_z + z1 * a.dst_row_z1 + c) * a.Kp + a.dst_k0 + z1 * a.dst_k_z1 + r;
+        __nv_bfloat16 h0, l0, h1, l1;
+        split2(tile[2 * tx][cc], h0, l0);
+        split2(tile[2 * tx + 1][cc], h1, l1);
+        if (pair_ok && r + 1 < kspan) {
+            *reinterpret_cast<__nv_bfloat162*>(hi + d) = __halves2bfloat162(h0, h1);
+            *reinterpret_cast<__nv_bfloat162*>(lo + d) = __halves2bfloat162(l0, l1);
+        } else {
+            hi[d] = h0; lo[d] = l0;
+            if (r + 1 < kspan) { hi[d + 1] = h1; lo[d + 1] = l1; }
         }
     }
 }
@@ -431,19 +500,23 @@ inline int launch(const PlaneTensor& A, const PlaneTensor& B, const Params& p, i
     return check_launch();
 }
 
-inline int split_rows(const SplitArgs& a, int batch, cudaStream_t st) {
-    if (a.rows <= 0 || batch <= 0) return RQ_OK;
+inline int split_rows(const SplitArgs& a_in, int batch, cudaStream_t st) {
+    SplitArgs a = a_in;
+    if (a.rows <= 0 || batch <= 0 || a.nz1 <= 0) return RQ_OK;
     const int kspan = a.pad_k_to > a.cols ? a.pad_k_to : a.cols;
     if (kspan <= 0) return RQ_OK;
-    dim3 grid((unsigned)((kspan + 1023) / 1024), (unsigned)(a.rows < 32768 ? a.rows : 32768), (unsigned)batch);
+    a.vec4 = ((reinterpret_cast<uintptr_t>(a.src) & 15) == 0 && (reinterpret_cast<uintptr_t>(a.dst) & 7) == 0 &&
+              ((a.ld | a.src_z | a.src_z1 | a.Kp | a.plane_stride) & 3) == 0 && ((a.dst_k0 | a.dst_k_z1) & 3) == 0)
+                 ? 1 : 0;
+    dim3 grid((unsigned)((kspan + 1023) / 1024), (unsigned)(a.rows < 16384 ? a.rows : 16384), (unsigned)(batch * a.nz1));
     split_rows_kernel<<<grid, 256, 0, st>>>(a);
     return check_launch();
 }
 
 inline int split_transpose(const SplitArgs& a, int batch, cudaStream_t st) {
-    if (a.rows <= 0 || a.cols <= 0 || batch <= 0) return RQ_OK;
+    if (a.rows <= 0 || a.cols <= 0 || batch <= 0 || a.nz1 <= 0) return RQ_OK;
     const int kspan = a.pad_k_to > a.rows ? a.pad_k_to : a.rows;
-    dim3 grid((unsigned)((a.cols + 31) / 32), (unsigned)((kspan + 31) / 32), (unsigned)batch);
+    dim3 grid((unsigned)((a.cols + 31) / 32), (unsigned)((kspan + 63) / 64), (unsigned)(batch * a.nz1));
     split_transpose_kernel<<<grid, 256, 0, st>>>(a);
     return check_launch();
 }
