@@ -427,6 +427,9 @@ __global__ void merge_status_kernel(const int* __restrict__ status, int* __restr
 
 // use the tensor-core trailing update from this many block columns on (below that the launch is all prologue)
 constexpr int kTensorTrailingMinBlocks = 4;
+// block columns per outer block of the two-level trailing update (must equal kTensorTrailingMinBlocks: block
+// columns below it form the outer block that is updated on the CUDA cores)
+constexpr int kOuterBlocks = 4;
 // levels of the triangular inverse with blocks at least this wide run on the tensor cores
 constexpr int kTensorInverseMinBlock = 512;
 
@@ -435,7 +438,9 @@ constexpr int kTensorInverseMinBlock = 512;
 
 using namespace rq;
 
-static size_t chol_panel_plane_bytes(size_t Cp, int G) { return (size_t)G * 2 * Cp * chol::NB * 2; }
+static size_t chol_panel_plane_bytes(size_t Cp, int G) {
+    return (size_t)G * 2 * Cp * chol::NB * chol::kOuterBlocks * 2;
+}
 static size_t chol_full_plane_bytes(size_t Cp, int G) {       // hi + lo planes of one Cp x Cp matrix per group
     return Cp >= (size_t)chol::kTensorInverseMinBlock * 2 ? (size_t)G * 2 * Cp * Cp * 2 + 1024 : 0;
 }
@@ -497,22 +502,36 @@ extern "C" int rq_chol_hinv(const float* H, const int64_t* perm, const float* da
             }
             prof::Scope t3(RQ_PROF_CHOL_TRAILING, st);
             if (k >= kTensorTrailingMinBlocks) {
-                // split the panel R[0:k*128, block k] into bf16 planes and run A_ij -= R_ik . R_jk^T on the tensor cores
+                // Two-level update on the tensor cores.  Block columns are grouped four to an outer block; the
+                // panel R[0:k*128, block k] is split into bf16 planes at its place inside the outer block's
+                // 512-wide panel.  Inside an outer block only its own columns are brought up to date after
+                // each step (k-extent 128); everything to the left receives ONE update per outer block with
+                // k-extent 512, which divides the read-modify-write traffic of the trailing matrix by four.
+                const int c0 = k / kOuterBlocks * kOuterBlocks, p = k - c0;
+                const int W = NB * kOuterBlocks;
                 tcgemm::SplitArgs sa;
                 sa.src = A + (size_t)k * NB; sa.ld = Cp; sa.src_z = (long long)Cp * Cp;
                 sa.rows = k * NB; sa.cols = NB;
-                sa.dst = panel_planes; sa.Kp = NB; sa.plane_stride = (long long)Cp * NB;
-                sa.plane = 0; sa.plane_z = 2; sa.dst_row0 = 0; sa.dst_row_z = 0; sa.dst_k0 = 0; sa.pad_k_to = 0;
+                sa.dst = panel_planes; sa.Kp = W; sa.plane_stride = (long long)Cp * W;
+                sa.plane = 0; sa.plane_z = 2; sa.dst_row0 = 0; sa.dst_row_z = 0; sa.dst_k0 = p * NB; sa.pad_k_to = 0;
                 rc = tcgemm::split_rows(sa, G, st);
                 if (rc != RQ_OK) return rc;
-                tcgemm::PlaneTensor pt{panel_planes, NB, Cp, 2LL * G};
+                tcgemm::PlaneTensor pt{panel_planes, W, Cp, 2LL * G};
                 tcgemm::Params gp;
-                gp.a_row0 = gp.b_row0 = 0; gp.a_k0 = gp.b_k0 = 0; gp.a_plane = gp.b_plane = 0;
-                gp.a_plane_z = gp.b_plane_z = 2; gp.a_row_z = gp.b_row_z = 0;
-                gp.M = gp.N = k * NB; gp.k_len = NB; gp.tri = 1; gp.kmode = 0; gp.batch = G;
-                gp.C = A; gp.ldc = Cp; gp.c_z = (long long)Cp * Cp;
+                gp.a_plane = gp.b_plane = 0; gp.a_plane_z = gp.b_plane_z = 2; gp.a_row_z = gp.b_row_z = 0;
+                gp.tri = 1; gp.kmode = 0; gp.batch = G;
+                gp.ldc = Cp; gp.c_z = (long long)Cp * Cp;
                 gp.Aux = nullptr; gp.ldaux = 0; gp.aux_z = 0;
                 gp.alpha = -1.f; gp.beta = 1.f; gp.gamma = 0.f;
+                gp.a_row0 = 0;
+                if (p > 0) {            // columns [c0*128, k*128) of the outer block: A_ij -= R_ik . R_jk^T
+                    gp.b_row0 = c0 * NB; gp.a_k0 = gp.b_k0 = p * NB; gp.k_len = NB;
+                    gp.M = k * NB; gp.N = p * NB; gp.tri_col0 = c0 * NB; gp.C = A + (size_t)c0 * NB;
+                } else {                // everything left of the outer block, all of its block columns at once
+                    const int blocks = (nblk - c0 < kOuterBlocks) ? nblk - c0 : kOuterBlocks;
+                    gp.b_row0 = 0; gp.a_k0 = gp.b_k0 = 0; gp.k_len = blocks * NB;
+                    gp.M = gp.N = k * NB; gp.tri_col0 = 0; gp.C = A;
+                }
                 rc = tcgemm::launch(pt, pt, gp, tc_status, st);
                 if (rc != RQ_OK) return rc;
             } else {

@@ -41,7 +41,8 @@ struct Params {
     int a_plane_z, b_plane_z;      // plane increment per batch
     int a_row_z, b_row_z;          // row increment per batch
     int M, N, k_len;               // output extent and k extent (k_len is covered in 64-blocks; padding must be zero)
-    int tri;                       // 1: skip tiles that lie wholly below the diagonal (i0 >= j0 + BN)
+    int tri;                       // 1: skip tiles that lie wholly below the diagonal (i0 >= tri_col0 + j0 + BN)
+    int tri_col0 = 0;              // global column index of C's column 0 (row 0 is global row 0)
     int kmode;                     // 0: all k;  1: k >= i0 (A[m,k] = 0 for k < m);  2: k < j0 + BN (B[n,k] = 0 for k > n);
                                    // 3: k >= j0 (B[n,k] = 0 for k < n)
     int batch;                     // total batch count = nz1 * (number of outer batches)
@@ -73,7 +74,7 @@ __device__ __forceinline__ TileCtx decode(const Params& p, int t, int MT, int NT
         const int lim = p.n_limit - c.z1 * p.n_limit_z1;
         if (lim < c.n_eff) c.n_eff = lim;
     }
-    c.skip = (p.tri && c.i * BM >= (c.j + 1) * BN) || c.j * BN >= c.n_eff;
+    c.skip = (p.tri && c.i * BM >= p.tri_col0 + (c.j + 1) * BN) || c.j * BN >= c.n_eff;
     return c;
 }
 
@@ -234,7 +235,7 @@ split_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
 #pragma unroll
             for (int cb = 0; cb < 4; ++cb) {
                 const int col0 = colbase + cb * 32;
-                use[cb] = !(col0 >= n_eff || row0 >= p.M || (p.tri && col0 + 31 < row0));
+                use[cb] = !(col0 >= n_eff || row0 >= p.M || (p.tri && p.tri_col0 + col0 + 31 < row0));
             }
             float run[128];
 #pragma unroll
