@@ -208,6 +208,7 @@ class LayerWorkload:
         unit_owner = assign_owners(costs, world)
         self.owner = {name: [unit_owner[(name, g)] for g in range(self.G)] for name, _, _, _ in self.LINEARS}
         self.recorder = None
+        self.copy_stream = None
 
     # ---- algorithmic work figures
     def hessian_flops(self, local=False):
@@ -231,11 +232,31 @@ class LayerWorkload:
             o.quantizer.configure(4, perchannel=True, sym=True, mse=False)
             o.profile_recorder = self.recorder
             objs[name] = o
+        main = torch.cuda.current_stream()
+
+        def fetch(s):
+            """Batch s of the three activation streams.  From the host: copied on a side stream, one batch ahead of
+            the kernels that consume it, so that the PCIe transfer overlaps the Hessian GEMMs of the batch before."""
+            if s >= self.nseq_local:
+                return None
+            if not from_host:
+                return {key: inputs[key][s:s + self.BSZ] for key in ("hid", "attn", "mlp")}, None
+            if self.copy_stream is None:
+                self.copy_stream = torch.cuda.Stream()
+            with torch.cuda.stream(self.copy_stream):
+                got = {key: inputs[key][s:s + self.BSZ].cuda(non_blocking=True) for key in ("hid", "attn", "mlp")}
+                ev = torch.cuda.Event()
+                ev.record(self.copy_stream)
+            return got, ev
+
+        nxt = fetch(0)
         for s in range(0, self.nseq_local, self.BSZ):
-            batch = {}
-            for key in ("hid", "attn", "mlp"):
-                x = inputs[key][s:s + self.BSZ]
-                batch[key] = x.cuda(non_blocking=True) if from_host else x
+            batch, ready = nxt
+            nxt = fetch(s + self.BSZ)
+            if ready is not None:
+                main.wait_event(ready)
+                for t in batch.values():
+                    t.record_stream(main)
             rot = {"hid": hu.matmul_hadU_cuda(batch["hid"], None, 1), "attn": batch["attn"],
                    "mlp": hu.matmul_hadU_cuda(batch["mlp"], self.had12, 12)}
             for name, _, _, key in self.LINEARS:
