@@ -262,18 +262,22 @@ class LayerWorkload:
             for name, _, _, key in self.LINEARS:
                 objs[name].add_batch(rot[key], None)
         checksum = torch.zeros((), device=self.dev)
+        # three phases, so that no rank waits in a collective for another rank's fasterquant: all exchanges of
+        # the partial Hessians, then every rank's own (linear, group) units, then the gather of the rows
         for name, R, C, _ in self.LINEARS:
             o = objs[name]
             o.group_owners = self.owner[name] if self.world > 1 else None
             o.finalize_hessian()
+        for name, R, C, _ in self.LINEARS:
             if self.world == 1 or self.rank in self.owner[name]:
-                o.fasterquant(blocksize=128, percdamp=0.01, groupsize=128, actorder=True, static_groups=True)
+                objs[name].fasterquant(blocksize=128, percdamp=0.01, groupsize=128, actorder=True, static_groups=True)
+        for name, R, C, _ in self.LINEARS:
             if self.world > 1:
                 w, rps = self.layers[name].weight.data, R // self.G
                 for g, src in enumerate(self.owner[name]):
                     dist.broadcast(w[g * rps:(g + 1) * rps], src=src)
             checksum += self.layers[name].weight.data.float().abs().mean()
-            o.free()
+            objs[name].free()
         return checksum
 
     def step_device(self):
