@@ -209,6 +209,10 @@ class LayerWorkload:
         self.owner = {name: [unit_owner[(name, g)] for g in range(self.G)] for name, _, _, _ in self.LINEARS}
         self.recorder = None
         self.copy_stream = None
+        self.fq_streams = int(os.environ.get("REALQ_BENCH_FQ_STREAMS", str(len(self.LINEARS))))
+        self.fq_pool = None
+        self.unit_cost = {name: sum(c for (n, g), c in costs.items() if n == name and (world == 1 or unit_owner[(n, g)] == rank))
+                          for name, _, _, _ in self.LINEARS}
 
     # ---- algorithmic work figures
     def hessian_flops(self, local=False):
@@ -268,9 +272,42 @@ class LayerWorkload:
             o = objs[name]
             o.group_owners = self.owner[name] if self.world > 1 else None
             o.finalize_hessian()
-        for name, R, C, _ in self.LINEARS:
-            if self.world == 1 or self.rank in self.owner[name]:
-                objs[name].fasterquant(blocksize=128, percdamp=0.01, groupsize=128, actorder=True, static_groups=True)
+        mine = [name for name, _, _, _ in self.LINEARS if self.world == 1 or self.rank in self.owner[name]]
+
+        def quantize(name):
+            objs[name].fasterquant(blocksize=128, percdamp=0.01, groupsize=128, actorder=True, static_groups=True)
+
+        if self.fq_streams <= 1 or len(mine) <= 1:
+            for name in mine:
+                quantize(name)
+        else:
+            # The linears are independent, and much of fasterquant is a chain of short dependent launches (the
+            # diagonal blocks of the factorisation, the 128-column block loop): one host thread and one stream per
+            # linear lets those chains overlap each other and the other linears' GEMMs.
+            if self.fq_pool is None:
+                from concurrent.futures import ThreadPoolExecutor
+                self.fq_pool = ThreadPoolExecutor(max_workers=self.fq_streams)
+                self.fq_stream_list = [torch.cuda.Stream() for _ in range(self.fq_streams)]
+            ready = torch.cuda.Event()
+            ready.record(main)
+            dev_index = self.dev.index
+
+            def work(slot, names):
+                torch.cuda.set_device(dev_index)
+                st = self.fq_stream_list[slot]
+                st.wait_event(ready)
+                with torch.cuda.stream(st):
+                    for name in names:
+                        quantize(name)
+                done = torch.cuda.Event()
+                done.record(st)
+                return done
+
+            order = sorted(mine, key=lambda n: -self.unit_cost[n])          # longest first, round-robin over slots
+            slots = [order[i::self.fq_streams] for i in range(self.fq_streams)]
+            futures = [self.fq_pool.submit(work, i, names) for i, names in enumerate(slots) if names]
+            for f in futures:
+                main.wait_event(f.result())
         for name, R, C, _ in self.LINEARS:
             if self.world > 1:
                 w, rps = self.layers[name].weight.data, R // self.G

@@ -17,8 +17,9 @@ _status = {}
 
 
 def _workspace(device, nbytes: int, key: str = "main") -> torch.Tensor:
-    """Cached scratch buffer per (device, key); grown on demand, never shrunk."""
-    k = (device, key)
+    """Cached scratch buffer per (device, key, current stream); grown on demand, never shrunk.  Keyed by the
+    stream so that linears quantized concurrently on different streams never share scratch."""
+    k = (device, key, torch.cuda.current_stream(device).cuda_stream)
     buf = _scratch.get(k)
     if buf is None or buf.numel() < nbytes:
         _scratch[k] = None
