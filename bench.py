@@ -207,6 +207,18 @@ class LayerWorkload:
                  for name, R, C, _ in self.LINEARS for g in range(self.G)}
         unit_owner = assign_owners(costs, world)
         self.owner = {name: [unit_owner[(name, g)] for g in range(self.G)] for name, _, _, _ in self.LINEARS}
+        # every linear has the same G, so a fixed pattern balances as well as the cost model and turns the exchange
+        # of a linear into one reduce-scatter
+        from gptq_plus_mp_quant_b200.utils import dist_utils as du
+        k = world // self.G if world % self.G == 0 else 1
+        lin_class = assign_owners({name: sum(costs[(name, g)] for g in range(self.G)) for name, _, _, _ in self.LINEARS},
+                                  max(k, 1))                           # which of a group's k ranks owns it, per linear
+        for name, _, _, _ in self.LINEARS:
+            pat = du.group_owner_pattern(self.G, world, salt=lin_class[name])
+            if pat is not None:
+                self.owner[name] = pat
+                for g in range(self.G):
+                    unit_owner[(name, g)] = pat[g]
         self.recorder = None
         self.copy_stream = None
         self.fq_streams = int(os.environ.get("REALQ_BENCH_FQ_STREAMS", str(len(self.LINEARS))))

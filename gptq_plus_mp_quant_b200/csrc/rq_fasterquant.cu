@@ -144,6 +144,13 @@ struct BlockArgs {
     float* Eeff;             // [R, BS]: Err (- D*Z1 when PLUS), A operand of the lazy update
     __nv_bfloat16* Ehi;      // optional: the same operand split into bf16 planes [R][BS] for the tensor-core update
     __nv_bfloat16* Elo;
+    // optional second operand for a deferred update of the columns beyond the current group of blocks:
+    // Err - (D + far_after) * Z split into planes [R][far_ld] at column offset far_k0 (far_after = number of
+    // columns between this block's end and the end of its group)
+    __nv_bfloat16* Fhi;
+    __nv_bfloat16* Flo;
+    int far_ld, far_k0;
+    float far_after;
     const float* scale_row;  // mode 0: [R]
     const float* scale_tab;  // mode 1: [ngroups, R] static groups
     const int* colgrp;       // mode 1: [C] group of (permuted) column j
@@ -325,11 +332,22 @@ __global__ void __launch_bounds__(kBlockThreads) block_kernel(const BlockArgs p)
                 p.Ehi[(int64_t)r * BS + col] = h;
                 p.Elo[(int64_t)r * BS + col] = __float2bfloat16_rn(e - __bfloat162float(h));
             }
+            if (p.Fhi) {
+                float f = ev[k];
+                if (PLUS) f = f - ((float)(p.count - 1 - col) + p.far_after) * z[k];
+                const __nv_bfloat16 h = __float2bfloat16_rn(f);
+                p.Fhi[(int64_t)r * p.far_ld + p.far_k0 + col] = h;
+                p.Flo[(int64_t)r * p.far_ld + p.far_k0 + col] = __float2bfloat16_rn(f - __bfloat162float(h));
+            }
         } else {
             p.Eeff[(int64_t)r * BS + col] = 0.f;
             if (p.Ehi) {
                 p.Ehi[(int64_t)r * BS + col] = __float2bfloat16_rn(0.f);
                 p.Elo[(int64_t)r * BS + col] = __float2bfloat16_rn(0.f);
+            }
+            if (p.Fhi) {
+                p.Fhi[(int64_t)r * p.far_ld + p.far_k0 + col] = __float2bfloat16_rn(0.f);
+                p.Flo[(int64_t)r * p.far_ld + p.far_k0 + col] = __float2bfloat16_rn(0.f);
             }
         }
     }
@@ -435,7 +453,9 @@ static int fq_block_launch(float* Wp, float* GH, const float* Z, const float* Hi
                            float* Eeff, __nv_bfloat16* Ehi, __nv_bfloat16* Elo, const float* scale_row,
                            const float* scale_tab, const int* colgrp, float* scale_blk, int R, int C, int G, int i1,
                            int count, int mode, int dyn_gs, int sym, int maxq, int plus, const float* anchor,
-                           const float* beta, int inner_mode, int atomic, void* stream) {
+                           const float* beta, int inner_mode, int atomic, void* stream,
+                           __nv_bfloat16* Fhi = nullptr, __nv_bfloat16* Flo = nullptr, int far_ld = 0, int far_k0 = 0,
+                           int far_after = 0) {
     using namespace rq::fq;
     if (!Wp || !Hinv || !Q || !codes || !Eeff || R <= 0 || C <= 0 || G <= 0 || R % G != 0) return RQ_ERR_INVALID;
     if (i1 < 0 || count <= 0 || count > BS || i1 + count > C) return RQ_ERR_INVALID;
@@ -450,6 +470,7 @@ static int fq_block_launch(float* Wp, float* GH, const float* Z, const float* Hi
     p.anchor = anchor; p.beta = beta; p.inner_mode = inner_mode; p.atomic = atomic ? 1 : 0;
     p.Wp = Wp; p.GH = GH; p.Z = Z; p.Hinv = Hinv; p.Q = Q; p.codes = codes; p.Eeff = Eeff;
     p.Ehi = Ehi; p.Elo = Elo;
+    p.Fhi = Fhi; p.Flo = Flo; p.far_ld = far_ld; p.far_k0 = far_k0; p.far_after = (float)far_after;
     p.scale_row = scale_row; p.scale_tab = scale_tab; p.colgrp = colgrp; p.scale_blk = scale_blk;
     p.R = R; p.C = C; p.Cp = (C + 127) / 128 * 128; p.G = G; p.i1 = i1; p.count = count;
     p.mode = mode; p.dyn_gs = dyn_gs; p.sym = sym;
@@ -555,8 +576,9 @@ extern "C" int rq_fq_run(float* Wp, float* GH, const float* Z, const float* Hinv
 // tensor-core variants: the GEMM-shaped parts run on tcgen05 from bf16-split operand planes
 // ------------------------------------------------------------------------------------------
 namespace {
+constexpr int kFarBlocks = 4;        // blocks per group of the two-level lazy update
 struct TcLayout {
-    size_t put, pu, pa, pe, status, total;
+    size_t put, pu, pa, pe, pf, status, total;
     int Cp;
 };
 
@@ -569,6 +591,7 @@ TcLayout tc_layout(int R, int C, int G, int plus) {
     L.pu = off;  if (plus) off = up(off + (size_t)G * 2 * L.Cp * L.Cp * 2);
     L.pa = off;  if (plus) off = up(off + (size_t)2 * R * L.Cp * 2);
     L.pe = off;  off = up(off + (size_t)2 * R * rq::fq::BS * 2);
+    L.pf = off;  off = up(off + (size_t)2 * R * rq::fq::BS * kFarBlocks * 2);
     L.status = off; off += 1024;
     L.total = off;
     return L;
@@ -669,12 +692,27 @@ extern "C" int rq_fq_run_tc(float* Wp, float* GH, const float* Z, const float* H
     PlaneTensor tE{PE, fq::BS, R, 2};
     PlaneTensor tZ{ws + L.pa, Cp, R, 2};
     PlaneTensor tUt{ws + L.put, Cp, Cp, 2LL * G};
+    // Two-level lazy update (frozen mode): blocks are grouped four to a group of 512 columns.  After a block only
+    // the rest of its own group is brought up to date (k-extent 128); the columns beyond the group receive one
+    // update per group with k-extent 512, a quarter of the read-modify-write traffic.  For those columns the
+    // first-order term seen by block b is GH_start - sum_{b' < b} Z_b'.H_b', so the group's total is
+    //   W_far -= sum_b (Err_b - (D + after_b) o Z_b) . H_b,far + n_group * GH_far,   GH_far -= sum_b Z_b . H_b,far
+    // with after_b the number of group columns behind block b: the block kernel writes that operand directly.
+    // The surrogate modes read the trailing weights after every block and keep the one-level schedule.
+    const bool two_level = inner_mode == 0;
+    const int W = fq::BS * kFarBlocks;
+    __nv_bfloat16* PF = reinterpret_cast<__nv_bfloat16*>(ws + L.pf);
+    PlaneTensor tF{PF, W, R, 2};
     for (int i1 = 0; i1 < C; i1 += fq::BS) {
         const int count = (C - i1 < fq::BS) ? C - i1 : fq::BS;
         const int i2 = i1 + count;
+        const int o0 = i1 / W * W;                                   // current group [o0, o1)
+        const int o1 = two_level ? ((o0 + W < C) ? o0 + W : C) : C;
+        const bool far = two_level && o1 < C;
         int rc = fq_block_launch(Wp, GH, Z, Hinv, Q, codes, Eeff, PE, PE + (size_t)R * fq::BS, scale_row, scale_tab,
                                  colgrp, scale_blk, R, C, G, i1, count, mode, dyn_gs, sym, maxq, plus, anchor, beta,
-                                 inner_mode, (atomic && i2 < C) ? 1 : 0, stream);
+                                 inner_mode, (atomic && i2 < C) ? 1 : 0, stream, far ? PF : nullptr,
+                                 far ? PF + (size_t)R * W : nullptr, W, i1 - o0, o1 - i2);
         if (rc != RQ_OK) return rc;
         if (i2 >= C) break;
         prof::Scope timed(RQ_PROF_LAZY, st);
@@ -683,18 +721,31 @@ extern "C" int rq_fq_run_tc(float* Wp, float* GH, const float* Z, const float* H
             if (rc != RQ_OK) return rc;
         }
         Params p;
-        p.a_row0 = 0; p.a_k0 = 0; p.a_plane = 0; p.a_plane_z = 0; p.a_row_z = Rg;
-        p.b_row0 = i2; p.b_k0 = i1; p.b_plane = 0; p.b_plane_z = 2; p.b_row_z = 0;
-        p.M = Rg; p.N = C - i2; p.k_len = fq::BS; p.tri = 0; p.kmode = 0; p.batch = G;
-        p.C = Wp + i2; p.ldc = C; p.c_z = (long long)Rg * C;
-        p.Aux = plus ? GH + i2 : nullptr; p.ldaux = C; p.aux_z = (long long)Rg * C;
-        p.alpha = -1.f; p.beta = 1.f; p.gamma = plus ? -(float)count : 0.f;
-        rc = launch(tE, tUt, p, tc_status, st);                      // W[:, i2:] -= Eeff . Hinv[i1:i2, i2:] + count * GH
-        if (rc != RQ_OK) return rc;
-        if (plus) {
-            p.a_k0 = i1; p.C = GH + i2; p.Aux = nullptr; p.gamma = 0.f;
-            rc = launch(tZ, tUt, p, tc_status, st);                  // GH[:, i2:] -= Z[:, i1:i2] . Hinv[i1:i2, i2:]
+        p.a_row0 = 0; p.a_plane = 0; p.a_plane_z = 0; p.a_row_z = Rg;
+        p.b_plane = 0; p.b_plane_z = 2; p.b_row_z = 0;
+        p.M = Rg; p.tri = 0; p.kmode = 0; p.batch = G;
+        p.ldc = C; p.c_z = (long long)Rg * C; p.ldaux = C; p.aux_z = (long long)Rg * C;
+        p.alpha = -1.f; p.beta = 1.f;
+        if (i2 < o1) {                                               // rest of the group (or of the matrix)
+            p.a_k0 = 0; p.b_row0 = i2; p.b_k0 = i1; p.N = o1 - i2; p.k_len = fq::BS;
+            p.C = Wp + i2; p.Aux = plus ? GH + i2 : nullptr; p.gamma = plus ? -(float)count : 0.f;
+            rc = launch(tE, tUt, p, tc_status, st);                  // W[:, i2:o1] -= Eeff . Hinv[i1:i2, i2:o1] + count * GH
             if (rc != RQ_OK) return rc;
+            if (plus) {
+                p.a_k0 = i1; p.C = GH + i2; p.Aux = nullptr; p.gamma = 0.f;
+                rc = launch(tZ, tUt, p, tc_status, st);              // GH[:, i2:o1] -= Z[:, i1:i2] . Hinv[i1:i2, i2:o1]
+                if (rc != RQ_OK) return rc;
+            }
+        } else if (far) {                                            // the group is complete: everything beyond it
+            p.a_k0 = 0; p.b_row0 = o1; p.b_k0 = o0; p.N = C - o1; p.k_len = o1 - o0;
+            p.C = Wp + o1; p.Aux = plus ? GH + o1 : nullptr; p.gamma = plus ? -(float)(o1 - o0) : 0.f;
+            rc = launch(tF, tUt, p, tc_status, st);
+            if (rc != RQ_OK) return rc;
+            if (plus) {
+                p.a_k0 = o0; p.C = GH + o1; p.Aux = nullptr; p.gamma = 0.f;
+                rc = launch(tZ, tUt, p, tc_status, st);
+                if (rc != RQ_OK) return rc;
+            }
         }
     }
     return RQ_OK;

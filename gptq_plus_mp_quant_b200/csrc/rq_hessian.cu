@@ -550,20 +550,12 @@ static int launch_umma(void* planes, int64_t Kc, int C, int G, int nplanes, int 
     const int MT = (C + BM - 1) / BM, NT = (C + BN - 1) / BN;
     const int total = ((NT - 1) * NT + MT) * G;
     const int kblocks = (int)(Kc / BK);
-    // token split: pick the number of parts that minimises rounds x (k-blocks per part + a per-visit overhead);
-    // needs the reduction epilogue (beta == 1, whole 32-column chunks), since two visits of a tile may overlap
-    int ksplit = 1;
-    if (beta == 1.f && (C & 31) == 0) {
-        constexpr int WIN = kWindowTokens / BK;
-        long long best = -1;
-        for (int sp = 1; sp <= 8; ++sp) {
-            const int per = ((kblocks + sp - 1) / sp + WIN - 1) / WIN * WIN;
-            if (sp > 1 && per < 8 * WIN) break;
-            const long long rounds = ((long long)total * sp + num_sms() - 1) / num_sms();
-            const long long cost = rounds * (per + 3);
-            if (best < 0 || cost < best) { best = cost; ksplit = sp; }
-        }
-    }
+    // The kernel can visit every tile ksplit times, each visit adding the sum over a share of the k-blocks with
+    // the reduction epilogue (units are (tile, part), part-major); that evens out the last round when the tile
+    // count is a poor multiple of the grid (+11 % at C = 1024, nothing at C = 4096).  It is left at 1: the order
+    // in which two parts reach an element of H is not fixed, and H + a + b is not H + b + a in fp32, so the
+    // split would make the accumulated Hessian differ from run to run in the last bit.
+    const int ksplit = 1;
     const long long units = (long long)total * ksplit;
     const int grid = units < num_sms() ? (int)units : num_sms();
     prof::Scope timed(RQ_PROF_HESSIAN_UMMA, st);
@@ -587,9 +579,13 @@ extern "C" size_t rq_hessian_workspace_bytes(int64_t chunk_tokens, int C, int G,
     return bytes + 1024;
 }
 
-extern "C" int rq_hessian_accum(const void* x, int x_dtype, int64_t ldx, const float* sal, float* H, float* act_sq,
-                                int64_t N, int C, int G, float alpha, float beta, void* workspace,
-                                size_t workspace_bytes, int* status, int variant, void* stream) {
+// Shared body of rq_hessian_accum and rq_hessian_accum_pipelined.  With gemm_stream == pack stream the
+// launches are simply ordered; otherwise the workspace is cut into chunk slots, the packing of chunk c runs on
+// `st` while the tensor-core kernel of an earlier chunk runs on `gst`, and events order the two per slot.
+static int hessian_accum_impl(const void* x, int x_dtype, int64_t ldx, const float* sal, float* H, float* act_sq,
+                              int64_t N, int C, int G, float alpha, float beta, void* workspace,
+                              size_t workspace_bytes, int* status, int variant, int64_t chunk_tokens, cudaStream_t st,
+                              cudaStream_t gst) {
     using namespace rq::hess;
     if (!x || !H || !workspace || C <= 0 || G <= 0 || G > 8 || N < 0 || ldx < C) return RQ_ERR_INVALID;
     if (!sal && G != 1) return RQ_ERR_INVALID;
@@ -597,26 +593,42 @@ extern "C" int rq_hessian_accum(const void* x, int x_dtype, int64_t ldx, const f
     if (variant < 0 || variant > 2) return RQ_ERR_UNSUPPORTED;
     if (reinterpret_cast<uintptr_t>(workspace) % 1024 != 0) return RQ_ERR_INVALID;
     if (N == 0) return RQ_OK;
-    cudaStream_t st = as_stream(stream);
+    const bool piped = gst != st;
 
-    // largest chunk (multiple of 64 tokens) the workspace can hold
+    // largest chunk (multiple of 64 tokens) the workspace can hold; pipelined: the requested chunk, as many slots as fit
     const int has_sal = sal != nullptr;
     int64_t chunk = (N + 63) / 64 * 64;
+    if (piped && chunk_tokens > 0 && chunk_tokens < chunk) chunk = (chunk_tokens + 63) / 64 * 64;
     while (chunk > 64 && rq_hessian_workspace_bytes(chunk, C, G, has_sal) > workspace_bytes) chunk -= 64;
-    if (rq_hessian_workspace_bytes(chunk, C, G, has_sal) > workspace_bytes) return RQ_ERR_WORKSPACE;
+    const size_t slot_bytes = rq_hessian_workspace_bytes(chunk, C, G, has_sal);
+    if (slot_bytes > workspace_bytes) return RQ_ERR_WORKSPACE;
+    int nslots = 1;
+    if (piped) {
+        nslots = (int)(workspace_bytes / slot_bytes);
+        if (nslots > 4) nslots = 4;
+    }
+    cudaEvent_t slot_free[4] = {nullptr, nullptr, nullptr, nullptr};
 
     const int nplanes = has_sal ? 2 + 2 * G : 2;
     const int b_plane0 = has_sal ? 2 : 0;
     const int nprod = (x_dtype == RQ_BF16) ? 2 : 3;
-    __nv_bfloat16* planes = reinterpret_cast<__nv_bfloat16*>(workspace);
     const size_t esz = x_dtype == RQ_F32 ? 4 : 2;
-
-    for (int64_t n0 = 0; n0 < N; n0 += chunk) {
+    int rc = RQ_OK;
+    int64_t ci = 0;
+    for (int64_t n0 = 0; n0 < N && rc == RQ_OK; n0 += chunk, ++ci) {
+        const int slot = (int)(ci % nslots);
+        uint8_t* slot_base = reinterpret_cast<uint8_t*>(workspace) + (size_t)slot * slot_bytes;
+        __nv_bfloat16* planes = reinterpret_cast<__nv_bfloat16*>(slot_base);
+        if (piped && slot_free[slot]) {                       // the kernel that last read this slot must be done
+            if (cudaStreamWaitEvent(st, slot_free[slot], 0) != cudaSuccess) { rc = RQ_ERR_CUDA; break; }
+            cudaEventDestroy(slot_free[slot]);
+            slot_free[slot] = nullptr;
+        }
         const int nvalid = (int)((N - n0) < chunk ? (N - n0) : chunk);
         const int64_t Kc = ((int64_t)nvalid + 63) / 64 * 64;
         size_t plane_bytes = (size_t)nplanes * (size_t)C * (size_t)Kc * 2;
         plane_bytes = (plane_bytes + 1023) / 1024 * 1024;
-        float* partial = act_sq ? reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) + plane_bytes) : nullptr;
+        float* partial = act_sq ? reinterpret_cast<float*>(slot_base + plane_bytes) : nullptr;
         const uint8_t* xp = reinterpret_cast<const uint8_t*>(x) + (size_t)n0 * (size_t)ldx * esz;
         const float* sp = has_sal ? sal + n0 * G : nullptr;
         dim3 pgrid((unsigned)(Kc / kPackTile), (unsigned)((C + kPackTile - 1) / kPackTile));
@@ -633,26 +645,55 @@ extern "C" int rq_hessian_accum(const void* x, int x_dtype, int64_t ldx, const f
             pack_kernel<__half><<<pgrid, 256, 0, st>>>(reinterpret_cast<const __half*>(xp), ldx, sp, nvalid, C, G,
                                                         (int)Kc, planes, partial, write_xlo);
         }
-        int rc = check_launch();
-        if (rc != RQ_OK) return rc;
+        rc = check_launch();
+        if (rc != RQ_OK) break;
         if (act_sq) {
             act_reduce_kernel<<<(C + 255) / 256, 256, 0, st>>>(partial, (int)(Kc / kPackTile), C, act_sq);
             rc = check_launch();
-            if (rc != RQ_OK) return rc;
+            if (rc != RQ_OK) break;
+        }
+        if (piped) {
+            cudaEvent_t packed;
+            if (cudaEventCreateWithFlags(&packed, cudaEventDisableTiming) != cudaSuccess) { rc = RQ_ERR_CUDA; break; }
+            const bool ok = cudaEventRecord(packed, st) == cudaSuccess && cudaStreamWaitEvent(gst, packed, 0) == cudaSuccess;
+            cudaEventDestroy(packed);                          // released once the recorded work has completed
+            if (!ok) { rc = RQ_ERR_CUDA; break; }
         }
         const float b = (n0 == 0) ? beta : 1.f;
         if (variant == 2)
-            rc = nprod == 3 ? launch_umma<64, 3>(planes, Kc, C, G, nplanes, b_plane0, H, alpha, b, status, st)
-                            : launch_umma<64, 2, true>(planes, Kc, C, G, nplanes, b_plane0, H, alpha, b, status, st);
+            rc = nprod == 3 ? launch_umma<64, 3>(planes, Kc, C, G, nplanes, b_plane0, H, alpha, b, status, gst)
+                            : launch_umma<64, 2, true>(planes, Kc, C, G, nplanes, b_plane0, H, alpha, b, status, gst);
         else if (variant == 0)
-            rc = nprod == 3 ? launch_umma<64, 3>(planes, Kc, C, G, nplanes, b_plane0, H, alpha, b, status, st)
-                            : launch_umma<64, 2>(planes, Kc, C, G, nplanes, b_plane0, H, alpha, b, status, st);
+            rc = nprod == 3 ? launch_umma<64, 3>(planes, Kc, C, G, nplanes, b_plane0, H, alpha, b, status, gst)
+                            : launch_umma<64, 2>(planes, Kc, C, G, nplanes, b_plane0, H, alpha, b, status, gst);
         else
-            rc = nprod == 3 ? launch_umma<32, 3>(planes, Kc, C, G, nplanes, b_plane0, H, alpha, b, status, st)
-                            : launch_umma<32, 2>(planes, Kc, C, G, nplanes, b_plane0, H, alpha, b, status, st);
-        if (rc != RQ_OK) return rc;
+            rc = nprod == 3 ? launch_umma<32, 3>(planes, Kc, C, G, nplanes, b_plane0, H, alpha, b, status, gst)
+                            : launch_umma<32, 2>(planes, Kc, C, G, nplanes, b_plane0, H, alpha, b, status, gst);
+        if (rc != RQ_OK) break;
+        if (piped && n0 + chunk < N) {
+            if (cudaEventCreateWithFlags(&slot_free[slot], cudaEventDisableTiming) != cudaSuccess ||
+                cudaEventRecord(slot_free[slot], gst) != cudaSuccess) { rc = RQ_ERR_CUDA; break; }
+        }
     }
-    return RQ_OK;
+    for (int i = 0; i < 4; ++i)
+        if (slot_free[i]) cudaEventDestroy(slot_free[i]);
+    return rc;
+}
+
+extern "C" int rq_hessian_accum(const void* x, int x_dtype, int64_t ldx, const float* sal, float* H, float* act_sq,
+                                int64_t N, int C, int G, float alpha, float beta, void* workspace,
+                                size_t workspace_bytes, int* status, int variant, void* stream) {
+    return hessian_accum_impl(x, x_dtype, ldx, sal, H, act_sq, N, C, G, alpha, beta, workspace, workspace_bytes, status,
+                              variant, 0, as_stream(stream), as_stream(stream));
+}
+
+extern "C" int rq_hessian_accum_pipelined(const void* x, int x_dtype, int64_t ldx, const float* sal, float* H,
+                                          float* act_sq, int64_t N, int C, int G, float alpha, float beta,
+                                          void* workspace, size_t workspace_bytes, int* status, int variant,
+                                          int64_t chunk_tokens, void* stream, void* gemm_stream) {
+    if (!gemm_stream || gemm_stream == stream) return RQ_ERR_INVALID;
+    return hessian_accum_impl(x, x_dtype, ldx, sal, H, act_sq, N, C, G, alpha, beta, workspace, workspace_bytes, status,
+                              variant, chunk_tokens, as_stream(stream), as_stream(gemm_stream));
 }
 
 extern "C" int rq_hessian_finalize(float* H, float* act_sq, int C, int G, float div_tokens, float div_scale,

@@ -86,7 +86,8 @@ class GPTQPlus:
                 sal_batch = sal_batch.reshape(-1, sal_batch.shape[-1])
                 n_tokens = inp.shape[0]
             with rec.section("add_batch.hessian_block") if rec else _NULL_CONTEXT:
-                ops.hessian_accum(inp, sal_batch, self._H, self.act_square, alpha=1.0, beta=1.0)
+                ops.hessian_accum(inp, sal_batch, self._H, self.act_square, alpha=1.0, beta=1.0,
+                                  pipeline=ops.HESSIAN_PIPELINE)
                 self._H_upper_only = True
             self.token_count += n_tokens
 
@@ -96,10 +97,10 @@ class GPTQPlus:
         (gptq_plus_utils.py:859-908)."""
         if self._finalized:
             return
+        ops.hessian_join(self.dev)
         if self.group_owners is not None:
             assert len(self.group_owners) == self.num_groups
-            for g, owner in enumerate(self.group_owners):
-                dist_utils.reduce_sum_(self._H[g], owner)
+            dist_utils.reduce_groups_to_owners_(self._H, self.group_owners)
         elif self.hessian_owner is None:
             dist_utils.allreduce_sum_(self._H)
         else:
@@ -147,5 +148,6 @@ class GPTQPlus:
     def free(self):
         # Drops the Hessian; unlike the reference this does not return cached blocks to the driver
         # (torch.cuda.empty_cache / cleanup_memory): the next linear re-uses them without a cudaMalloc.
+        ops.hessian_join(self.dev)          # no contraction may still be writing the buffer that is released
         self.H = None
         self.Losses = None

@@ -49,7 +49,8 @@ class GPTQ:
             inp = inp.reshape((-1, inp.shape[-1]))
         beta = self.nsamples / (self.nsamples + tmp)
         self.nsamples += tmp
-        ops.hessian_accum(inp, None, self._H, None, alpha=2.0 / self.nsamples, beta=beta)
+        ops.hessian_accum(inp, None, self._H, None, alpha=2.0 / self.nsamples, beta=beta,
+                          pipeline=ops.HESSIAN_PIPELINE)
         self._H_upper_only = True
 
     def fasterquant(self, blocksize=128, percdamp=0.01, groupsize=-1, actorder=False, static_groups=False,
@@ -67,5 +68,6 @@ class GPTQ:
     def free(self):
         # Drops the Hessian; unlike the reference this does not return cached blocks to the driver
         # (torch.cuda.empty_cache / cleanup_memory): the next linear re-uses them without a cudaMalloc.
+        ops.hessian_join(self.dev)          # no contraction may still be writing the buffer that is released
         self.H = None
         self.Losses = None

@@ -12,8 +12,40 @@ from . import _lib
 # (2 + 2G) * C * chunk * 2 bytes)
 HESSIAN_CHUNK_TOKENS = int(os.environ.get("REALQ_HESSIAN_CHUNK", "8192"))
 
+# Optional: packing on the caller's stream, tensor-core contraction on one extra stream per device, two rings of
+# chunk slots, so that the packing of one linear overlaps the contraction of another.  H is then complete in
+# the order of that extra stream: every reader of H calls hessian_join() first.  Off by default: on a part that
+# runs against its power cap the overlap was measured to slow the contraction by as much as it hides of the
+# packing (0.686 s against 0.683 s per layer); it pays where the clock is not power-limited.
+HESSIAN_PIPELINE = os.environ.get("REALQ_HESSIAN_PIPELINE", "0") != "0"
+_PIPE_SLOTS = 2             # chunk slots per workspace
+_PIPE_RING = 2              # workspaces alternated between calls
+
 _scratch = {}
 _status = {}
+_pipe = {}
+
+
+class _PipeState:
+    def __init__(self, device):
+        self.stream = torch.cuda.Stream(device=device)
+        self.turn = 0
+        self.free = [None] * _PIPE_RING           # event: the contraction that last read workspace i has finished
+        self.dirty = False
+
+
+def _pipe_state(device) -> "_PipeState":
+    st = _pipe.get(device)
+    if st is None:
+        st = _pipe[device] = _PipeState(device)
+    return st
+
+
+def hessian_join(device) -> None:
+    """Make the current stream wait for every Hessian contraction issued so far on ``device``."""
+    st = _pipe.get(device)
+    if st is not None and st.dirty:
+        torch.cuda.current_stream(device).wait_stream(st.stream)
 
 
 def _workspace(device, nbytes: int, key: str = "main") -> torch.Tensor:
@@ -50,10 +82,11 @@ def check_status(device) -> None:
 
 
 def hessian_accum(x: torch.Tensor, sal, H: torch.Tensor, act_sq, alpha: float = 1.0, beta: float = 1.0,
-                  variant: int = 0, chunk_tokens: int | None = None) -> None:
+                  variant: int = 0, chunk_tokens: int | None = None, pipeline: bool = False) -> None:
     """``H[g] = beta*H[g] + alpha * X^T diag(sal[:, g]) X`` (upper-triangular tiles only) and
     ``act_sq += sum x^2``.  x: [N, C] fp32/bf16/fp16 (row stride free), sal: [N, G] fp32 or None,
-    H: [G, C, C] fp32 contiguous (or [C, C] when sal is None)."""
+    H: [G, C, C] fp32 contiguous (or [C, C] when sal is None).  ``pipeline=True`` issues the contraction on the
+    device's extra stream (see HESSIAN_PIPELINE): H is then only complete after hessian_join()."""
     _lib.require_cuda(x, H, sal, act_sq)
     assert x.dim() == 2, "x must be [tokens, channels]"
     N, Cc = x.shape
@@ -68,6 +101,30 @@ def hessian_accum(x: torch.Tensor, sal, H: torch.Tensor, act_sq, alpha: float = 
         assert act_sq.dtype == torch.float32 and act_sq.is_contiguous() and act_sq.numel() == Cc
     chunk = int(chunk_tokens or HESSIAN_CHUNK_TOKENS)
     chunk = max(64, min(chunk, (N + 63) // 64 * 64))
+    if pipeline:
+        with torch.cuda.device(x.device):
+            ps = _pipe_state(x.device)
+            cur = torch.cuda.current_stream(x.device)
+            if not ps.dirty:
+                ps.stream.wait_stream(cur)        # H as the caller left it (zero-filled, or read back earlier)
+            slot_bytes = _lib.lib.rq_hessian_workspace_bytes(chunk, Cc, G, 0 if sal is None else 1)
+            ring = ps.turn % _PIPE_RING
+            ps.turn += 1
+            ws = _workspace(x.device, _PIPE_SLOTS * slot_bytes + 1024, key=f"hpipe{ring}")
+            if ps.free[ring] is not None:
+                cur.wait_event(ps.free[ring])
+            base = ws.data_ptr()
+            aligned = (base + 1023) // 1024 * 1024
+            rc = _lib.lib.rq_hessian_accum_pipelined(
+                _lib.ptr(x), _lib.dtype_code(x), x.stride(0), _lib.ptr(sal), _lib.ptr(H), _lib.ptr(act_sq), N, Cc, G,
+                float(alpha), float(beta), aligned, ws.numel() - (aligned - base), _lib.ptr(status_word(x.device)),
+                int(variant), chunk, cur.cuda_stream, ps.stream.cuda_stream)
+            ev = torch.cuda.Event()
+            ev.record(ps.stream)
+            ps.free[ring] = ev
+            ps.dirty = True
+        _lib.check("rq_hessian_accum_pipelined", rc)
+        return
     with torch.cuda.device(x.device):
         need = _lib.lib.rq_hessian_workspace_bytes(chunk, Cc, G, 0 if sal is None else 1)
         ws = _workspace(x.device, need)
@@ -86,6 +143,7 @@ def hessian_finalize(H: torch.Tensor, act_sq, div_tokens: float = 1.0, div_scale
     Returns the device uint64[2] (NaN count, Inf count) when ``sanitize`` else None."""
     _lib.require_cuda(H, act_sq)
     assert H.is_contiguous() and H.dtype == torch.float32
+    hessian_join(H.device)
     Cc = H.shape[-1]
     G = H.numel() // (Cc * Cc)
     counts = torch.zeros(2, dtype=torch.int64, device=H.device) if sanitize else None

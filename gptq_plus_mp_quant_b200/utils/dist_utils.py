@@ -53,6 +53,65 @@ def reduce_sum_(tensor: torch.Tensor, dst: int) -> torch.Tensor:
     return tensor
 
 
+def _reduce_scatter_inplace_(flat: torch.Tensor, world: int, rank: int) -> torch.Tensor:
+    """Sum over ranks of ``flat`` (numel divisible by world), chunk r of the sum delivered into chunk r of rank
+    r's own buffer; the other chunks are left unspecified.  Returns this rank's chunk (a view)."""
+    chunks = flat.view(world, -1)
+    if dist.get_backend() == "nccl":
+        dist.reduce_scatter_tensor(chunks[rank], flat, op=dist.ReduceOp.SUM)   # NCCL's in-place layout
+    else:                                                                      # gloo has no reduce-scatter
+        for s in range(world):
+            dist.reduce(chunks[s], dst=s, op=dist.ReduceOp.SUM)
+    return chunks[rank]
+
+
+def group_owner_pattern(num_groups: int, world: int, salt: int = 0):
+    """Owners for which reduce_groups_to_owners_ needs one reduce-scatter: ``world`` divides ``num_groups``
+    (rank r owns a run of groups) or ``num_groups`` divides ``world`` (group g lands on the ranks
+    [g*k, (g+1)*k), k = world / num_groups, and ``salt`` picks which of them owns it, so that successive linears
+    load different ranks).  None when neither divides."""
+    if world <= 1:
+        return [0] * num_groups
+    if num_groups % world == 0:
+        return [g // (num_groups // world) for g in range(num_groups)]
+    if world % num_groups == 0:
+        k = world // num_groups
+        return [g * k + salt % k for g in range(num_groups)]
+    return None
+
+
+def reduce_groups_to_owners_(H: torch.Tensor, owners) -> None:
+    """``H`` [G, ...] holds this rank's partial sums; afterwards rank ``owners[g]`` holds the sum of ``H[g]`` (the
+    other ranks' copies of that group are unspecified).  One bandwidth-optimal reduce-scatter when the owners follow
+    group_owner_pattern (plus, when several ranks share a group, a gather of its pieces on the owner); one reduce
+    per group otherwise."""
+    world, rank = get_world_size(), get_rank()
+    if world <= 1:
+        return
+    G = H.shape[0]
+    owners = [int(o) for o in owners]
+    assert len(owners) == G and H.is_contiguous()
+    flat = H.view(-1)
+    if G % world == 0 and owners == group_owner_pattern(G, world):
+        _reduce_scatter_inplace_(flat, world, rank)
+        return
+    k = world // G if world % G == 0 else 0
+    if k > 1 and flat.numel() % world == 0 and all(g * k <= owners[g] < (g + 1) * k for g in range(G)):
+        _reduce_scatter_inplace_(flat, world, rank)            # piece s = g*k + j of the sum now sits on rank s
+        chunks = flat.view(world, -1)
+        g = rank // k
+        ops = []
+        if rank == owners[g]:
+            ops = [dist.P2POp(dist.irecv, chunks[src], src) for src in range(g * k, (g + 1) * k) if src != rank]
+        else:
+            ops = [dist.P2POp(dist.isend, chunks[rank], owners[g])]
+        for req in dist.batch_isend_irecv(ops):
+            req.wait()
+        return
+    for g, owner in enumerate(owners):
+        dist.reduce(H[g], dst=owner, op=dist.ReduceOp.SUM)
+
+
 def allreduce_sum_scalar(scalar) -> float:
     """Sum of a Python scalar over ranks in fp64 (dist_utils.py:142-149)."""
     if get_world_size() <= 1:

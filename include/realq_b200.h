@@ -80,6 +80,18 @@ int rq_hessian_accum(const void* x, int x_dtype, int64_t ldx, const float* sal, 
                      int64_t N, int C, int G, float alpha, float beta, void* workspace, size_t workspace_bytes,
                      int* status, int variant, void* stream);
 
+/* Same accumulation, with the packing launches on `stream` and the tensor-core launches on `gemm_stream` (two
+ * different streams of the caller): the workspace is cut into up to four slots of `chunk_tokens` tokens, chunk c
+ * is packed while an earlier chunk is being contracted, events order the two per slot.  act_sq is complete in
+ * `stream` order; H is complete in `gemm_stream` order: make the stream that reads H wait for `gemm_stream`
+ * (cudaStreamWaitEvent) first, and do not reuse `workspace` on `stream` before the kernels of this call have left
+ * `gemm_stream`.  Feeding the linears of a layer through one gemm_stream lets the packing of one linear overlap
+ * the contraction of another. */
+int rq_hessian_accum_pipelined(const void* x, int x_dtype, int64_t ldx, const float* sal, float* H, float* act_sq,
+                               int64_t N, int C, int G, float alpha, float beta, void* workspace,
+                               size_t workspace_bytes, int* status, int variant, int64_t chunk_tokens, void* stream,
+                               void* gemm_stream);
+
 /* Allocation-free variant of rq_hessian_accum.  It has no counterpart in the reference; it exists
  * for hosts that must not allocate device memory where they feed calibration batches (a hook that
  * runs while the framework's memory pool is frozen, a process whose device-memory budget belongs to

@@ -68,8 +68,7 @@ def _worker(rank, world, port, results):
         owners = [1, 0]
         part2 = ohess.GroupedHessian(C, S[sl])
         part2.add_batch(X[sl])
-        for g, owner in enumerate(owners):
-            du.reduce_sum_(part2.H[g], owner)
+        du.reduce_groups_to_owners_(part2.H, owners)                 # general path: one reduce per group
         du.allreduce_sum_(part2.act_square)
         part2.index = int(du.allreduce_sum_scalar(part2.index))
         part2.token_count = int(du.allreduce_sum_scalar(part2.token_count))
@@ -93,6 +92,20 @@ def _worker(rank, world, port, results):
                                    static_groups=True)["Q"]
         assert float((Wq != full).float().mean()) < 0.02             # summation order differs in the last bit
         du.assert_bit_exact(Wq, "gathered weights")
+        # the two reduce-scatter patterns: world divides G (rank r owns a run of groups), and G divides world
+        # (pieces of a group land on k ranks and are gathered on the one that owns it)
+        assert du.group_owner_pattern(4, 2) == [0, 0, 1, 1] and du.group_owner_pattern(2, 2) == [0, 1]
+        assert du.group_owner_pattern(1, 2, salt=0) == [0] and du.group_owner_pattern(1, 2, salt=1) == [1]
+        assert du.group_owner_pattern(4, 3) is None
+        for owners_p, shape in (([0, 1], (2, 6, 6)), ([0, 0, 1, 1], (4, 5, 4)), ([1], (1, 4, 6)), ([0], (1, 4, 6))):
+            gen = torch.Generator().manual_seed(11)
+            parts = [torch.randn(shape, generator=gen) for _ in range(world)]
+            Hp = parts[rank].clone()
+            du.reduce_groups_to_owners_(Hp, owners_p)
+            total = parts[0] + parts[1]
+            for g, owner in enumerate(owners_p):
+                if owner == rank:
+                    assert torch.allclose(Hp[g], total[g], rtol=0, atol=1e-6), (owners_p, g)
         results[rank] = "ok"
     finally:
         dist.destroy_process_group()

@@ -291,3 +291,25 @@ def test_ste_gradient_passes_through():
     q.find_params(W.detach())
     q.quantize(W).sum().backward()
     assert torch.equal(W.grad, torch.ones_like(W))
+
+
+@pytest.mark.gpu
+def test_hessian_pipelined_matches_in_order():
+    """Packing and contraction on two streams (chunk slots ordered by events) give the bits of the in-order call."""
+    from gptq_plus_mp_quant_b200 import ops
+    torch.manual_seed(3)
+    N, C, G = 3 * 8192 + 640, 384, 2
+    x = (torch.randn(N, C, device=DEV) * torch.exp(torch.randn(C, device=DEV))).bfloat16()
+    s = torch.exp(torch.randn(N, G, device=DEV))
+    outs = []
+    for piped in (False, True):
+        H = torch.zeros(G, C, C, device=DEV)
+        act = torch.zeros(C, device=DEV)
+        for part in (x[:N // 2], x[N // 2:]):
+            sal = s[:N // 2] if part.data_ptr() == x.data_ptr() else s[N // 2:]
+            ops.hessian_accum(part, sal, H, act, pipeline=piped)
+        ops.hessian_join(H.device)
+        ops.hessian_finalize(H, None)
+        outs.append((H.clone(), act.clone()))
+    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+    ops.check_status(H.device)
