@@ -117,7 +117,7 @@ def hessian_accum(x: torch.Tensor, sal, H: torch.Tensor, act_sq, alpha: float = 
             aligned = (base + 1023) // 1024 * 1024
             rc = _lib.lib.rq_hessian_accum_pipelined(
                 _lib.ptr(x), _lib.dtype_code(x), x.stride(0), _lib.ptr(sal), _lib.ptr(H), _lib.ptr(act_sq), N, Cc, G,
-                float(alpha), float(beta), aligned, ws.numel() - (aligned - base), _lib.ptr(status_word(x.device)),
+                float(alpha), float(beta), aligned, _PIPE_SLOTS * slot_bytes, _lib.ptr(status_word(x.device)),
                 int(variant), chunk, cur.cuda_stream, ps.stream.cuda_stream)
             ev = torch.cuda.Event()
             ev.record(ps.stream)
@@ -127,12 +127,12 @@ def hessian_accum(x: torch.Tensor, sal, H: torch.Tensor, act_sq, alpha: float = 
         return
     with torch.cuda.device(x.device):
         need = _lib.lib.rq_hessian_workspace_bytes(chunk, Cc, G, 0 if sal is None else 1)
-        ws = _workspace(x.device, need)
-        base = ws.data_ptr()
+        ws = _workspace(x.device, need)              # the cached buffer may be larger: pass `need`, so that the
+        base = ws.data_ptr()                         # chunking (hence the bits of H) never depends on its history
         aligned = (base + 1023) // 1024 * 1024
         rc = _lib.lib.rq_hessian_accum(_lib.ptr(x), _lib.dtype_code(x), x.stride(0), _lib.ptr(sal), _lib.ptr(H),
                                        _lib.ptr(act_sq), N, Cc, G, float(alpha), float(beta), aligned,
-                                       ws.numel() - (aligned - base), _lib.ptr(status_word(x.device)), int(variant),
+                                       need, _lib.ptr(status_word(x.device)), int(variant),
                                        _lib.stream_of(x))
     _lib.check("rq_hessian_accum", rc)
 
