@@ -504,9 +504,10 @@ def run_ours(args):
         "data": "synthetic",
         "config": {"workload": wl.name, "tokens": wl.nseq_total * wl.T, "hessian_accum_bsz": wl.BSZ,
                    "l2": "per-step inputs (10.7 GB of activations, 4 GB of Hessians) exceed the 126 MB L2",
-                   "parallelism": (f"dp{world}: calibration sequences sharded, NCCL reduce of each group's H to the "
-                                   "owner of that (linear, group), fasterquant of the 28 (linear, group) units "
-                                   "spread over ranks, quantized rows broadcast from their owners"),
+                   "parallelism": (f"dp{world}: calibration sequences sharded, one NCCL reduce-scatter per linear "
+                                   "delivers each group's H to the owner of that (linear, group), fasterquant of "
+                                   "the 28 (linear, group) units spread over ranks, quantized rows broadcast from "
+                                   "their owners"),
                    "fasterquant_owner": wl.owner if world > 1 else None},
         "hessian_accum_tflops": round(wl.hessian_flops() * args.steps / (umma_ms * 1e-3 + prof["pack"][0] * 1e-3)
                                       / 1e12, 1) if umma_ms else None,
