@@ -377,6 +377,9 @@ class LayerWorkload:
 # ----------------------------------------------------------------------------------------------
 # CPU arm: the port of the reference's own code on the host cores
 # ----------------------------------------------------------------------------------------------
+CPU_SAMPLE_SEQS, CPU_SAMPLE_ROWS = 8, 512     # bounded sample of the CPU arm: about 10-20 s on 16 host cores
+
+
 def cpu_layer_seconds(hess_seqs: int, fq_rows: int):
     """Times the CPU port on a bounded sample and extrapolates to the whole layer:
     Hessian stage by its flop count, fasterquant by rows (the sample quantizes `fq_rows` rows of a
@@ -422,12 +425,13 @@ def run_reference(args):
     torch.set_num_threads(os.cpu_count() or 1)
     vals, busy = [], []
     for i in range(max(args.warmup, 0) + args.steps):
-        v, tf, b = cpu_layer_seconds(hess_seqs=2, fq_rows=64)
+        v, tf, b = cpu_layer_seconds(hess_seqs=CPU_SAMPLE_SEQS, fq_rows=CPU_SAMPLE_ROWS)
         if i >= args.warmup:
             vals.append(v)
             busy.append(b)
     v = sum(vals) / len(vals)
-    sample = ("per step: reference add_batch on 2 of 128 sequences at C=4096 G=4 plus fasterquant of 64 rows x 4096 "
+    sample = (f"per step: reference add_batch on {CPU_SAMPLE_SEQS} of 128 sequences at C=4096 G=4 plus fasterquant of "
+              f"{CPU_SAMPLE_ROWS} rows x 4096 "
               "(G=4, g128, act_order, alpha=0.25), extrapolated to the layer by flops (Hessian), C^3 (Cholesky) "
               "and rows*C^2 (block loop)")
     print(json.dumps({
@@ -531,10 +535,10 @@ def run_ours(args):
     }
     if rank == 0 and world == 1 and not args.no_cpu:
         torch.set_num_threads(os.cpu_count() or 1)
-        v, tf, busy = cpu_layer_seconds(hess_seqs=2, fq_rows=64)
+        v, tf, busy = cpu_layer_seconds(hess_seqs=CPU_SAMPLE_SEQS, fq_rows=CPU_SAMPLE_ROWS)
         out["cpu_baseline"] = {"value": round(v, 1), "unit": "s", "cores": torch.get_num_threads(), "kind": "port",
-                               "sample": f"add_batch on 2 of 128 sequences (C=4096, G=4: {tf:.2f} TFLOP/s) and "
-                                         f"fasterquant of 64 rows x 4096, {busy:.1f} s of CPU work, extrapolated to "
+                               "sample": f"add_batch on {CPU_SAMPLE_SEQS} of 128 sequences (C=4096, G=4: {tf:.2f} TFLOP/s) and "
+                                         f"fasterquant of {CPU_SAMPLE_ROWS} rows x 4096, {busy:.1f} s of CPU work, extrapolated to "
                                          "the layer by flops / C^3 / rows*C^2"}
     if rank == 0:
         print(json.dumps(out))

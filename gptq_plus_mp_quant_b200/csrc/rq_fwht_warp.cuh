@@ -282,12 +282,26 @@ __device__ __forceinline__ void mix_pair(const float* buf, int slice, const floa
     }
     for (int ko = 0; ko < K; ++ko) {
         float s0 = 0.f, s1 = 0.f;
+        if ((K & 3) == 0) {                          // rows of hadK as 16-byte words (same address in every lane)
+            const float4* hrow = reinterpret_cast<const float4*>(hk + ko * K);
 #pragma unroll
-        for (int k = 0; k < KK; ++k) {
-            if (k < K) {
-                const float h = hk[ko * K + k];
-                s0 = fmaf(h, v0[k], s0);
-                s1 = fmaf(h, v1[k], s1);
+            for (int k4 = 0; k4 < KK / 4; ++k4) {
+                if (4 * k4 < K) {
+                    const float4 h = hrow[k4];
+                    s0 = fmaf(h.x, v0[4 * k4 + 0], s0); s1 = fmaf(h.x, v1[4 * k4 + 0], s1);
+                    s0 = fmaf(h.y, v0[4 * k4 + 1], s0); s1 = fmaf(h.y, v1[4 * k4 + 1], s1);
+                    s0 = fmaf(h.z, v0[4 * k4 + 2], s0); s1 = fmaf(h.z, v1[4 * k4 + 2], s1);
+                    s0 = fmaf(h.w, v0[4 * k4 + 3], s0); s1 = fmaf(h.w, v1[4 * k4 + 3], s1);
+                }
+            }
+        } else {
+#pragma unroll
+            for (int k = 0; k < KK; ++k) {
+                if (k < K) {
+                    const float h = hk[ko * K + k];
+                    s0 = fmaf(h, v0[k], s0);
+                    s1 = fmaf(h, v1[k], s1);
+                }
             }
         }
         store2<T>(yrow + (int64_t)ko * P + p, s0 * scale, s1 * scale);

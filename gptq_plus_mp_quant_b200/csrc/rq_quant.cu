@@ -217,3 +217,57 @@ extern "C" int rq_quantize(const void* x, void* deq, float* codes, int dtype, in
         return RQ_ERR_INVALID;
     return check_launch();
 }
+
+
+// ------------------------------------------------------------------------------------------
+// Pre-clip of a weight matrix to the range its quantizer can represent
+// (gptq_utils/gptq_plus_utils.py:197-225): per row r, with s = max(scale[r], 1e-8),
+//   symmetric:  [s * -(maxq+1), s * maxq];   asymmetric:  [s * (-zero[r]), s * (maxq - zero[r])],
+// w = min(max(w, lo), hi) evaluated in fp32, stored in the matrix's own dtype.
+// ------------------------------------------------------------------------------------------
+namespace rq {
+namespace quant {
+template <typename T>
+__global__ void __launch_bounds__(kThreads) clip_bounds_kernel(T* __restrict__ w, int64_t R, int64_t C, int64_t ldw,
+                                                              const float* __restrict__ scale,
+                                                              const float* __restrict__ zero, float maxq, int sym) {
+    for (int64_t r = blockIdx.y; r < R; r += gridDim.y) {
+        const float s = fmaxf(scale[r], 1e-8f);
+        float lo, hi;
+        if (sym) {
+            lo = __fmul_rn(s, -(maxq + 1.f));
+            hi = __fmul_rn(s, maxq);
+        } else {
+            const float z = zero[r];
+            lo = __fmul_rn(s, -z);
+            hi = __fmul_rn(s, __fsub_rn(maxq, z));
+        }
+        for (int64_t c = (int64_t)blockIdx.x * kThreads + threadIdx.x; c < C; c += (int64_t)gridDim.x * kThreads) {
+            const float v = load_as_float<T>(w, r * ldw + c);
+            if (v == v) store_from_float<T>(w, r * ldw + c, fminf(fmaxf(v, lo), hi));   // NaN stays, as torch.maximum keeps it
+        }
+    }
+}
+}  // namespace quant
+}  // namespace rq
+
+extern "C" int rq_clip_to_quant_bounds(void* W, int dtype, int64_t R, int64_t C, int64_t ldw, const float* scale,
+                                       const float* zero, int maxq, int sym, void* stream) {
+    using namespace rq::quant;
+    if (!W || !scale || (!sym && !zero) || R < 0 || C < 0 || ldw < C || maxq <= 0) return RQ_ERR_INVALID;
+    if (R * C == 0) return RQ_OK;
+    dim3 grid((unsigned)((C + kThreads - 1) / kThreads > 64 ? 64 : (C + kThreads - 1) / kThreads),
+              (unsigned)(R < 32768 ? R : 32768));
+    cudaStream_t st = as_stream(stream);
+    if (dtype == RQ_F32)
+        clip_bounds_kernel<float><<<grid, kThreads, 0, st>>>(reinterpret_cast<float*>(W), R, C, ldw, scale, zero, (float)maxq, sym);
+    else if (dtype == RQ_BF16)
+        clip_bounds_kernel<__nv_bfloat16><<<grid, kThreads, 0, st>>>(reinterpret_cast<__nv_bfloat16*>(W), R, C, ldw, scale,
+                                                                      zero, (float)maxq, sym);
+    else if (dtype == RQ_F16)
+        clip_bounds_kernel<__half><<<grid, kThreads, 0, st>>>(reinterpret_cast<__half*>(W), R, C, ldw, scale, zero,
+                                                               (float)maxq, sym);
+    else
+        return RQ_ERR_INVALID;
+    return check_launch();
+}

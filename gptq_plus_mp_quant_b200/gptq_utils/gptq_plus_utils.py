@@ -17,6 +17,46 @@ from . import fasterquant_impl
 _NULL_CONTEXT = nullcontext()
 
 
+def compute_quant_clip_bounds(scale, zero, maxq, sym):
+    """Representable range of a quantizer per row (gptq_plus_utils.py:197-203)."""
+    scale = scale.clamp(min=1e-8)
+    maxq_value = int(maxq.item()) if isinstance(maxq, torch.Tensor) else int(maxq)
+    if sym:
+        return scale * (-(maxq_value + 1)), scale * maxq_value
+    return scale * (-zero), scale * (maxq_value - zero)
+
+
+def clip_tensor_to_quant_bounds(weight, clip_min, clip_max):
+    """gptq_plus_utils.py:206-209, for callers that bring their own bounds."""
+    clip_min = clip_min.to(weight.device, dtype=weight.dtype)
+    clip_max = clip_max.to(weight.device, dtype=weight.dtype)
+    return torch.minimum(torch.maximum(weight, clip_min), clip_max)
+
+
+def clip_module_weight_to_quant_bounds_(module, bits, sym, mse):
+    """Clamp a linear's weight, in place, to the range its (shrink-grid searched) quantizer represents
+    (gptq_plus_utils.py:212-225): native range search on the fp32 view, then one clamp kernel on the weight in its
+    own dtype."""
+    from .. import _lib
+    from ..utils import quant_utils
+    if bits >= 16 or not mse:
+        return
+    quantizer = quant_utils.WeightQuantizer()
+    quantizer.configure(bits, perchannel=True, sym=sym, mse=mse)
+    w = module.weight.data
+    _lib.require_cuda(w)
+    quantizer.find_params(w.float())
+    if not w.is_contiguous():
+        raise ValueError("clip_module_weight_to_quant_bounds_ needs a contiguous weight")
+    R, Cc = w.shape
+    scale = quantizer.scale.to(w.device, torch.float32).reshape(-1).contiguous()
+    zero = quantizer.zero.to(w.device, torch.float32).reshape(-1).contiguous()
+    with torch.cuda.device(w.device):
+        rc = _lib.lib.rq_clip_to_quant_bounds(_lib.ptr(w), _lib.dtype_code(w), R, Cc, w.stride(0), _lib.ptr(scale),
+                                              _lib.ptr(zero), int(quantizer.maxq), 1 if sym else 0, _lib.stream_of(w))
+    _lib.check("rq_clip_to_quant_bounds", rc)
+
+
 class GPTQPlus:
     def __init__(self, layer, saliency: torch.Tensor, gradient: torch.Tensor, num_groups: int, alpha: float,
                  reference_loss: float, hessian_saliency_scale: float = 1.0):

@@ -147,6 +147,14 @@ int rq_find_params(const float* W, int64_t R, int64_t C, int64_t ldw, int groups
 int rq_quantize(const void* x, void* deq, float* codes, int dtype, int64_t R, int64_t C, const float* scale,
                 const float* zero, int pertensor, int maxq, int honour_zero, void* stream);
 
+/* rq_clip_to_quant_bounds replaces clip_module_weight_to_quant_bounds_'s arithmetic
+ * (gptq_utils/gptq_plus_utils.py:197-225: compute_quant_clip_bounds + clip_tensor_to_quant_bounds) once
+ * rq_find_params has produced scale / zero: W [R, C] of dtype (row stride ldw) is clamped in place, per row, to
+ * [s * -(maxq+1), s * maxq] (sym) or [s * (-zero), s * (maxq - zero)] with s = max(scale, 1e-8); the comparison
+ * runs in fp32 on the widened value, the result is stored in W's dtype. */
+int rq_clip_to_quant_bounds(void* W, int dtype, int64_t R, int64_t C, int64_t ldw, const float* scale,
+                            const float* zero, int maxq, int sym, void* stream);
+
 /* ------------------------------------------------------------------------------------------
  * Damped inverse-Hessian factor.
  * Replaces _compute_hessian_inverse_with_fallback's numerical body (gptq_utils/gptq_plus_utils.py:525-531)

@@ -155,3 +155,25 @@ class OracleWeightQuantizer:
 
     def ready(self):
         return bool(torch.all(self.scale != 0))
+
+
+def compute_quant_clip_bounds(scale, zero, maxq, sym):
+    """gptq_utils/gptq_plus_utils.py:197-203."""
+    scale = scale.clamp(min=1e-8)
+    maxq_value = int(maxq.item()) if isinstance(maxq, torch.Tensor) else int(maxq)
+    if sym:
+        return scale * (-(maxq_value + 1)), scale * maxq_value
+    return scale * (-zero), scale * (maxq_value - zero)
+
+
+def clip_weight_to_quant_bounds(weight, bits, sym, mse):
+    """clip_module_weight_to_quant_bounds_ on a bare tensor (gptq_utils/gptq_plus_utils.py:206-225): the clipped
+    weight in the input's dtype (the input itself when nothing is to be done)."""
+    if bits >= 16 or not mse:
+        return weight
+    q = OracleWeightQuantizer()
+    q.configure(bits, perchannel=True, sym=sym, mse=mse)
+    w = weight.float()
+    q.find_params(w)
+    lo, hi = compute_quant_clip_bounds(q.scale, q.zero, q.maxq, q.sym)
+    return torch.minimum(torch.maximum(w, lo.to(w.dtype)), hi.to(w.dtype)).to(weight.dtype)

@@ -72,6 +72,13 @@ QUANTIZER_CASES = [
     ("w8_asym_pt", 16, 64, 8, False, False, False),
 ]
 
+CLIP_CASES = [
+    # name, rows, cols, bits, sym, weight dtype
+    ("clip_w4_sym_f32", 32, 128, 4, True, "float32"),
+    ("clip_w4_asym_bf16", 32, 128, 4, False, "bfloat16"),
+    ("clip_w3_sym_bf16", 24, 200, 3, True, "bfloat16"),
+]
+
 HADAMARD_CASES = [
     # name, rows, n, dtype
     ("n128_f32", 37, 128, "float32"),

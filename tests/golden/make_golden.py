@@ -69,6 +69,17 @@ def gen_quantizer(qu, out):
         out[f"{name}.ste"] = np32(ste)
 
 
+def gen_clip(qu, gpu, out):
+    """Pre-clip of a linear's weight to its quantizer's range (clip_module_weight_to_quant_bounds_)."""
+    for name, rows, cols, bits, sym, dtype in cases.CLIP_CASES:
+        W = cases.make_weight(rows, cols, seed=13).to(getattr(torch, dtype))
+        layer = _Lin(W.clone())
+        gpu.clip_module_weight_to_quant_bounds_(layer, bits, sym, True)
+        out[f"{name}.digest"] = np.array(cases.digest(W.float()))
+        out[f"{name}.clipped"] = np32(layer.weight.data.float())
+        out[f"{name}.changed"] = np.array(int((layer.weight.data.float() != W.float()).sum()))
+
+
 def gen_hadamard(hu, out):
     had_tab = torch.load(os.path.join(os.path.dirname(hu.__file__), "had_mat.pt"))
     for k in (12, 20, 28):
@@ -196,7 +207,8 @@ def main():
                             ("hadamard.npz", gen_hadamard, (hu,)),
                             ("plain_gptq.npz", gen_plain, (qu, gu)),
                             ("gptq_plus.npz", gen_plus, (qu, gpu)),
-                            ("faults.npz", gen_faults, (qu, gpu))):
+                            ("faults.npz", gen_faults, (qu, gpu)),
+                            ("clip.npz", gen_clip, (qu, gpu))):
         out = {}
         with torch.no_grad():
             fn(*mods, out)

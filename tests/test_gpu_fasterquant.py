@@ -334,3 +334,44 @@ def test_group_owners_quantize_only_owned_rows():
         assert torch.equal(qa[r], qb[r]) and torch.equal(ca[r], cb[r]) and torch.equal(sa[r], sb[r])
     r = slice(rps, 2 * rps)
     assert torch.equal(qb[r], W[r]) and not torch.equal(qa[r], W[r])
+
+
+@pytest.mark.parametrize("cols", [640, 896])
+def test_two_level_schedule_with_ragged_last_group(cols):
+    """Column counts that leave a partial group of blocks at the end (640 = 512 + 128, 896 = 512 + 384): the
+    two-level tensor-core schedule, the one-level CUDA-core schedule and the oracle run on the device's Hessian
+    must agree on the codes (up to isolated rounding ties)."""
+    from gptq_plus_mp_quant_b200.gptq_utils import fasterquant_impl as fi
+    from gptq_plus_mp_quant_b200.gptq_utils.gptq_plus_utils import GPTQPlus
+    from gptq_plus_mp_quant_b200.utils.quant_utils import WeightQuantizer
+    rows, G, nseq, seqlen = 64, 2, 4, 2048
+    W = cases.make_weight(rows, cols, seed=51)
+    X = cases.make_acts(nseq, seqlen, cols, seed=51)
+    S = cases.make_saliency(nseq, seqlen, G, seed=51)
+    Gr = cases.make_grad(rows, cols, seed=51)
+    got = {}
+    H_dev = act_dev = perm = None
+    for tensor_cores in (True, False):
+        layer = _layer(W)
+        obj = GPTQPlus(layer, S, Gr, G, 0.25, 0.7)
+        obj.quantizer = WeightQuantizer()
+        obj.quantizer.configure(4, perchannel=True, sym=True)
+        obj.add_batch(X.to(DEV), None)
+        obj.finalize_hessian()
+        H_dev, act_dev = obj.H.clone().cpu(), obj.act_square.clone().cpu()
+        old = fi.USE_TENSOR_CORES
+        fi.USE_TENSOR_CORES = tensor_cores
+        try:
+            obj.fasterquant(actorder=True, static_groups=True, groupsize=128, export_to_et=True)
+        finally:
+            fi.USE_TENSOR_CORES = old
+        perm = obj._last_fasterquant["perm"].cpu()
+        got[tensor_cores] = layer.int_weight.cpu()
+    q = oq.OracleWeightQuantizer()
+    q.configure(4, perchannel=True, sym=True)
+    ref = ogptq.plus_fasterquant(W, H_dev, act_dev, Gr, q, G, 0.25, 0.7, groupsize=128, actorder=True,
+                                 static_groups=True)["W_int"].float()
+    for name, codes in (("two-level tensor-core", got[True]), ("one-level CUDA-core", got[False])):
+        frac, touched, first = _code_report(codes, ref, perm)
+        print(f"C={cols} {name}: {frac * 100:.4f}% codes differ in {touched} rows")
+        assert frac < 5e-3 and all(d == 1.0 for d in first)

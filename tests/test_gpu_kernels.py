@@ -313,3 +313,37 @@ def test_hessian_pipelined_matches_in_order():
         outs.append((H.clone(), act.clone()))
     assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
     ops.check_status(H.device)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("case", cases.CLIP_CASES, ids=lambda c: c[0])
+def test_clip_module_weight_to_quant_bounds(golden, case):
+    """Pre-clip of a linear to its quantizer's range against the reference's output.  The range search may pick the
+    neighbouring lattice point in a near-tie (see the quantizer test), which moves that row's bounds: rows whose
+    scale matches the oracle's must match bit for bit, and all but a few rows must."""
+    from gptq_plus_mp_quant_b200.gptq_utils.gptq_plus_utils import clip_module_weight_to_quant_bounds_
+    from gptq_plus_mp_quant_b200.utils.quant_utils import WeightQuantizer
+    name, rows, cols, bits, sym, dtype = case
+    g = golden("clip.npz")
+    W = cases.make_weight(rows, cols, seed=13).to(getattr(torch, dtype))
+    layer = torch.nn.Linear(cols, rows, bias=False, device=DEV, dtype=W.dtype)
+    layer.weight.data.copy_(W)
+    clip_module_weight_to_quant_bounds_(layer, bits, sym, True)
+    got = layer.weight.data.float().cpu()
+    ref = torch.from_numpy(g[f"{name}.clipped"])
+    assert layer.weight.dtype == W.dtype
+    q_dev = WeightQuantizer()
+    q_dev.configure(bits, perchannel=True, sym=sym, mse=True)
+    q_dev.find_params(W.float().to(DEV))
+    q_ref = oq.OracleWeightQuantizer()
+    q_ref.configure(bits, perchannel=True, sym=sym, mse=True)
+    q_ref.find_params(W.float())
+    same = (q_dev.scale.cpu().flatten() == q_ref.scale.flatten()) & (q_dev.zero.cpu().flatten() == q_ref.zero.flatten())
+    assert float(same.float().mean()) >= 0.9
+    assert torch.equal(got[same], ref[same])
+    assert int((got != W.float()).sum()) > 0
+    # no-ops
+    before = layer.weight.data.clone()
+    clip_module_weight_to_quant_bounds_(layer, 16, sym, True)
+    clip_module_weight_to_quant_bounds_(layer, bits, sym, False)
+    assert torch.equal(before, layer.weight.data)

@@ -182,3 +182,17 @@ def test_finalize_before_accumulate_raises():
     acc = ohess.GroupedHessian(3, torch.ones(1, 4, 1))
     with pytest.raises(RuntimeError):
         acc.finalize()
+
+
+@pytest.mark.parametrize("case", cases.CLIP_CASES, ids=lambda c: c[0])
+def test_clip_to_quant_bounds(golden, case):
+    """clip_module_weight_to_quant_bounds_ (shrink-grid searched range, then the clamp), bit for bit."""
+    name, rows, cols, bits, sym, dtype = case
+    g = golden("clip.npz")
+    W = cases.make_weight(rows, cols, seed=13).to(getattr(torch, dtype))
+    assert cases.digest(W.float()) == str(g[f"{name}.digest"])
+    out = oq.clip_weight_to_quant_bounds(W, bits, sym, True)
+    assert out.dtype == W.dtype
+    assert torch.equal(out.float(), t(g[f"{name}.clipped"]))
+    assert int((out.float() != W.float()).sum()) == int(g[f"{name}.changed"]) > 0
+    assert oq.clip_weight_to_quant_bounds(W, 16, sym, True) is W and oq.clip_weight_to_quant_bounds(W, bits, sym, False) is W
