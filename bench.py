@@ -377,7 +377,7 @@ class LayerWorkload:
 # ----------------------------------------------------------------------------------------------
 # CPU arm: the port of the reference's own code on the host cores
 # ----------------------------------------------------------------------------------------------
-CPU_SAMPLE_SEQS, CPU_SAMPLE_ROWS = 8, 512     # bounded sample of the CPU arm: about 10-20 s on 16 host cores
+CPU_SAMPLE_SEQS, CPU_SAMPLE_ROWS = 16, 1024   # bounded sample of the CPU arm: 10-20 s on 16 host cores
 
 
 def cpu_layer_seconds(hess_seqs: int, fq_rows: int):
