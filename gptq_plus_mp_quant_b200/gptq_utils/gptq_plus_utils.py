@@ -5,6 +5,7 @@ first-order terms and the block loop run in the sm_100a kernels of this package;
 cross-rank sum stays a ``torch.distributed`` all-reduce."""
 from __future__ import annotations
 
+import functools
 import logging
 from contextlib import nullcontext
 
@@ -191,3 +192,76 @@ class GPTQPlus:
         ops.hessian_join(self.dev)          # no contraction may still be writing the buffer that is released
         self.H = None
         self.Losses = None
+
+
+# loss scale of the static saliency / Fisher precompute and its square (gptq_plus_utils.py:34-37)
+_E2E_PRECOMPUTE_LOSS_GRAD_SCALE = 1000.0
+_E2E_PRECOMPUTE_QUADRATIC_SCALE = _E2E_PRECOMPUTE_LOSS_GRAD_SCALE * _E2E_PRECOMPUTE_LOSS_GRAD_SCALE
+
+
+class SaliencyCache:
+    """Per-token saliencies of the named linears: mean squared output gradient per channel group, collected by a
+    gradient hook during the calibration backward pass (gptq_plus_utils.py:2363-2431).  The hook's arithmetic runs in
+    one kernel that reads the gradient once, sink positions sliced off without a copy."""
+
+    def __init__(self, names, num_groups, sink_size=0):
+        self.num_groups = num_groups
+        self.saliency_cache = {name: [] for name in names}
+        self.names = names
+        self.handles = []
+        self.hooks_enabled = False
+        self.sink_size = max(0, int(sink_size))
+
+    def cache_saliency(self, module, inp, out, name):
+        out.retain_grad()
+
+        def grad_hook(grad):
+            if not self.hooks_enabled:
+                return
+            g = grad
+            if self.sink_size > 0 and g.dim() >= 2 and g.shape[1] > self.sink_size:
+                g = g[:, self.sink_size:]
+            self.saliency_cache[name].append(ops.group_mean_square(g, self.num_groups))
+
+        out.register_hook(grad_hook)
+
+    def add_hook(self, full, enable=True):
+        for name in self.names:
+            self.handles.append(
+                full.get(name, full.get(name + ".module", None)).register_forward_hook(
+                    functools.partial(self.cache_saliency, name=name)))
+        self.hooks_enabled = enable
+
+    def enable_hooks(self):
+        self.hooks_enabled = True
+
+    def disable_hooks(self):
+        self.hooks_enabled = False
+
+    def clear_hook(self):
+        for h in self.handles:
+            h.remove()
+        self.handles = []
+        self.hooks_enabled = False
+
+    def clear_cache(self):
+        for name in self.names:
+            self.saliency_cache[name] = []
+
+
+def fisher_accumulate_(fisher: torch.Tensor, grad: torch.Tensor, sink_size: int = 0,
+                       scale: float = _E2E_PRECOMPUTE_QUADRATIC_SCALE) -> torch.Tensor:
+    """``fisher += grad_flat^T grad_flat / scale`` for a layer-output gradient ``[batch, seq, hidden]``, the body of the
+    Fisher hook (gptq_plus_utils.py:2908-2921) on the tensor-core Gram kernel.  Only the tiles on or above the
+    diagonal are maintained; fisher_finalize_ mirrors them once after the last batch."""
+    if sink_size > 0 and grad.dim() >= 2 and grad.shape[1] > sink_size:
+        grad = grad[:, sink_size:]
+    flat = grad.detach().reshape(-1, grad.shape[-1])
+    ops.hessian_accum(flat, None, fisher, None, alpha=1.0 / float(scale), beta=1.0)
+    return fisher
+
+
+def fisher_finalize_(fisher: torch.Tensor) -> torch.Tensor:
+    """Fill the lower triangle of a matrix accumulated by fisher_accumulate_."""
+    ops.hessian_finalize(fisher, None)
+    return fisher

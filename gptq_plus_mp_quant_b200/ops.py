@@ -152,3 +152,21 @@ def hessian_finalize(H: torch.Tensor, act_sq, div_tokens: float = 1.0, div_scale
                                           float(div_seq), 1 if sanitize else 0, _lib.ptr(counts), _lib.stream_of(H))
     _lib.check("rq_hessian_finalize", rc)
     return counts
+
+
+def group_mean_square(grad: torch.Tensor, num_groups: int) -> torch.Tensor:
+    """``grad.float().pow(2).view(b, t, G, -1).mean(-1)`` for a ``[batch, seq, hidden]`` gradient (fp32 / bf16 / fp16,
+    channels contiguous; the batch and sequence strides are free, so a ``grad[:, sink:]`` slice is taken as is)."""
+    _lib.require_cuda(grad)
+    assert grad.dim() == 3, "grad must be [batch, seq, hidden]"
+    if grad.stride(2) != 1:
+        grad = grad.contiguous()
+    b, t, hidden = grad.shape
+    if hidden % num_groups != 0:
+        raise ValueError(f"hidden size {hidden} is not divisible by num_groups {num_groups}")
+    out = torch.empty(b, t, num_groups, dtype=torch.float32, device=grad.device)
+    with torch.cuda.device(grad.device):
+        rc = _lib.lib.rq_group_mean_square(_lib.ptr(grad), _lib.dtype_code(grad), b, t, grad.stride(0), grad.stride(1),
+                                           hidden, int(num_groups), _lib.ptr(out), _lib.stream_of(grad))
+    _lib.check("rq_group_mean_square", rc)
+    return out

@@ -147,6 +147,14 @@ int rq_find_params(const float* W, int64_t R, int64_t C, int64_t ldw, int groups
 int rq_quantize(const void* x, void* deq, float* codes, int dtype, int64_t R, int64_t C, const float* scale,
                 const float* zero, int pertensor, int maxq, int honour_zero, void* stream);
 
+/* rq_group_mean_square replaces the arithmetic of SaliencyCache's gradient hook
+ * (gptq_utils/gptq_plus_utils.py:2388-2404): out[b, t, g] = mean over the hidden/G channels of group g of
+ * grad[b, t, c]^2, in fp32.  grad: [batch, seq, hidden] of dtype with element strides stride_b / stride_t (channels
+ * contiguous), so a slice along the sequence (dropped sink positions, :2395-2396) needs no copy; out: [batch, seq, G]
+ * fp32 contiguous.  The layer-output Fisher sum grad^T grad (:2908-2921) is rq_hessian_accum with sal = NULL. */
+int rq_group_mean_square(const void* grad, int dtype, int64_t batch, int64_t seq, int64_t stride_b, int64_t stride_t,
+                         int hidden, int G, float* out, void* stream);
+
 /* rq_clip_to_quant_bounds replaces clip_module_weight_to_quant_bounds_'s arithmetic
  * (gptq_utils/gptq_plus_utils.py:197-225: compute_quant_clip_bounds + clip_tensor_to_quant_bounds) once
  * rq_find_params has produced scale / zero: W [R, C] of dtype (row stride ldw) is clamped in place, per row, to

@@ -102,3 +102,24 @@ class GroupedHessian:
             self.H = torch.nan_to_num(self.H, nan=0.0, posinf=0.0, neginf=0.0)
         self.finalized = True
         return n_nan, n_inf
+
+
+def group_mean_square(grad, num_groups, sink_size=0):
+    """The gradient hook of SaliencyCache (gptq_utils/gptq_plus_utils.py:2388-2404): mean squared gradient per
+    channel group and token, sink positions dropped."""
+    g = grad
+    if sink_size > 0 and g.dim() >= 2 and g.shape[1] > sink_size:
+        g = g[:, sink_size:]
+    bsz, seq_len, hidden_dim = g.shape
+    group_size = hidden_dim // num_groups
+    return g.float().pow(2).view(bsz, seq_len, num_groups, group_size).mean(dim=-1)
+
+
+def fisher_block(grad, sink_size=0, scale=1000.0 * 1000.0):
+    """One batch's contribution to the layer-output Fisher sum (gptq_utils/gptq_plus_utils.py:2908-2921)."""
+    if sink_size > 0 and grad.dim() >= 2 and grad.shape[1] > sink_size:
+        grad = grad[:, sink_size:]
+    flat = grad.detach().float().reshape(-1, grad.shape[-1])
+    out = flat.t() @ flat
+    out.div_(scale)
+    return out

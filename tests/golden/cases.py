@@ -79,6 +79,20 @@ CLIP_CASES = [
     ("clip_w3_sym_bf16", 24, 200, 3, True, "bfloat16"),
 ]
 
+SALIENCY_CASES = [
+    # name, batch, seq, hidden, groups, sink_size, dtype
+    ("sal_f32_g4", 2, 24, 256, 4, 0, "float32"),
+    ("sal_bf16_g4_sink", 3, 40, 512, 4, 4, "bfloat16"),
+    ("sal_bf16_g2_odd", 1, 17, 200, 2, 1, "bfloat16"),
+]
+
+
+def make_out_grad(batch, seq, hidden, seed):
+    """Heavy-tailed stand-in for the gradient of a loss with respect to a layer output."""
+    g = torch.Generator().manual_seed(seed)
+    return torch.randn(batch, seq, hidden, generator=g) * torch.exp(2.0 * torch.randn(batch, seq, 1, generator=g)) * 1e-3
+
+
 HADAMARD_CASES = [
     # name, rows, n, dtype
     ("n128_f32", 37, 128, "float32"),

@@ -80,6 +80,24 @@ def gen_clip(qu, gpu, out):
         out[f"{name}.changed"] = np.array(int((layer.weight.data.float() != W.float()).sum()))
 
 
+def gen_saliency(gpu, out):
+    """SaliencyCache's gradient hook on a linear whose output gradient is known exactly: the loss is
+    sum(out * coef), so d loss / d out = coef (in the layer's dtype)."""
+    for name, batch, seq, hidden, G, sink, dtype in cases.SALIENCY_CASES:
+        dt = getattr(torch, dtype)
+        lin = torch.nn.Linear(hidden, hidden, bias=False).to(dt)
+        x = cases.make_acts(batch, seq, hidden, seed=17).to(dt)
+        coef = cases.make_out_grad(batch, seq, hidden, seed=17).to(dt)
+        cache = gpu.SaliencyCache(["lin"], G, sink_size=sink)
+        cache.add_hook({"lin": lin})
+        with torch.enable_grad():
+            (lin(x) * coef).sum().backward()
+        (sal,) = cache.saliency_cache["lin"]
+        cache.clear_hook()
+        out[f"{name}.digest"] = np.array(cases.digest(coef.float()))
+        out[f"{name}.saliency"] = np32(sal)
+
+
 def gen_hadamard(hu, out):
     had_tab = torch.load(os.path.join(os.path.dirname(hu.__file__), "had_mat.pt"))
     for k in (12, 20, 28):
@@ -208,7 +226,8 @@ def main():
                             ("plain_gptq.npz", gen_plain, (qu, gu)),
                             ("gptq_plus.npz", gen_plus, (qu, gpu)),
                             ("faults.npz", gen_faults, (qu, gpu)),
-                            ("clip.npz", gen_clip, (qu, gpu))):
+                            ("clip.npz", gen_clip, (qu, gpu)),
+                            ("saliency.npz", gen_saliency, (gpu,))):
         out = {}
         with torch.no_grad():
             fn(*mods, out)

@@ -347,3 +347,45 @@ def test_clip_module_weight_to_quant_bounds(golden, case):
     clip_module_weight_to_quant_bounds_(layer, 16, sym, True)
     clip_module_weight_to_quant_bounds_(layer, bits, sym, False)
     assert torch.equal(before, layer.weight.data)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("case", cases.SALIENCY_CASES, ids=lambda c: c[0])
+def test_saliency_cache_hook_vs_reference(golden, case):
+    """The drop-in SaliencyCache on a CUDA linear whose output gradient is known exactly (loss = sum(out * coef))
+    against the reference's cached saliency: fp32 sums of squares in a different order, 2e-6 relative."""
+    from gptq_plus_mp_quant_b200.gptq_utils.gptq_plus_utils import SaliencyCache
+    name, batch, seq, hidden, G, sink, dtype = case
+    g = golden("saliency.npz")
+    dt = getattr(torch, dtype)
+    lin = torch.nn.Linear(hidden, hidden, bias=False, device=DEV, dtype=dt)
+    x = cases.make_acts(batch, seq, hidden, seed=17).to(dt).to(DEV)
+    coef = cases.make_out_grad(batch, seq, hidden, seed=17).to(dt).to(DEV)
+    cache = SaliencyCache(["lin"], G, sink_size=sink)
+    cache.add_hook({"lin": lin})
+    (lin(x) * coef).sum().backward()
+    (sal,) = cache.saliency_cache["lin"]
+    cache.disable_hooks()
+    (lin(x) * coef).sum().backward()
+    assert len(cache.saliency_cache["lin"]) == 1                       # disabled hooks record nothing
+    cache.clear_hook()
+    cache.clear_cache()
+    assert cache.saliency_cache["lin"] == [] and cache.handles == []
+    ref = torch.from_numpy(g[f"{name}.saliency"])
+    assert sal.shape == ref.shape and sal.dtype == torch.float32
+    assert torch.allclose(sal.cpu(), ref, rtol=2e-6, atol=0)
+
+
+@pytest.mark.gpu
+def test_fisher_accumulation_vs_oracle():
+    """Layer-output Fisher sum grad^T grad / scale over two batches on the tensor-core Gram kernel."""
+    from gptq_plus_mp_quant_b200.gptq_utils.gptq_plus_utils import fisher_accumulate_, fisher_finalize_
+    hidden, sink = 384, 3
+    grads = [cases.make_out_grad(2, 515, hidden, seed=s).bfloat16() for s in (5, 6)]
+    ref = sum(ohess.fisher_block(gr, sink) for gr in grads)
+    F = torch.zeros(hidden, hidden, device=DEV)
+    for gr in grads:
+        fisher_accumulate_(F, gr.to(DEV), sink)
+    fisher_finalize_(F)
+    assert float((F.cpu() - ref).norm() / ref.norm()) < 5e-6
+    assert torch.equal(F, F.t())

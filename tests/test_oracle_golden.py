@@ -196,3 +196,15 @@ def test_clip_to_quant_bounds(golden, case):
     assert torch.equal(out.float(), t(g[f"{name}.clipped"]))
     assert int((out.float() != W.float()).sum()) == int(g[f"{name}.changed"]) > 0
     assert oq.clip_weight_to_quant_bounds(W, 16, sym, True) is W and oq.clip_weight_to_quant_bounds(W, bits, sym, False) is W
+
+
+@pytest.mark.parametrize("case", cases.SALIENCY_CASES, ids=lambda c: c[0])
+def test_saliency_hook(golden, case):
+    """SaliencyCache's gradient hook (mean squared output gradient per channel group, sink positions dropped)."""
+    name, batch, seq, hidden, G, sink, dtype = case
+    g = golden("saliency.npz")
+    coef = cases.make_out_grad(batch, seq, hidden, seed=17).to(getattr(torch, dtype))
+    assert cases.digest(coef.float()) == str(g[f"{name}.digest"])
+    sal = ohess.group_mean_square(coef, G, sink)
+    assert sal.shape == (batch, seq - sink, G)
+    assert torch.equal(sal, t(g[f"{name}.saliency"]))
