@@ -29,6 +29,7 @@ SIGNATURES = {
     "rq_hessian_workspace_bytes": (_sz, [_i64, _i, _i, _i]),
     "rq_hessian_accum": (_i, [_vp, _i, _i64, _vp, _vp, _vp, _i64, _i, _i, _f, _f, _vp, _sz, _vp, _i, _vp]),
     "rq_group_mean_square": (_i, [_vp, _i, _i64, _i64, _i64, _i64, _i, _i, _vp, _vp]),
+    "rq_act_quant": (_i, [_vp, _vp, _i, _i64, _i, _i, _f, _i, _i, _vp, _vp, _vp, _vp, _i, _i, _vp]),
     "rq_clip_to_quant_bounds": (_i, [_vp, _i, _i64, _i64, _i64, _vp, _vp, _i, _i, _vp]),
     "rq_hessian_accum_pipelined": (_i, [_vp, _i, _i64, _vp, _vp, _vp, _i64, _i, _i, _f, _f, _vp, _sz, _vp, _i, _i64,
                                         _vp, _vp]),

@@ -1,0 +1,170 @@
+// Dynamic per-token (or per-token-group) fake quantization of activations: ActQuantizer.find_params followed by
+// STEQuantize / AsymSTEQuantize.forward (utils/quant_utils.py:60-84, 133-206) in one pass over the tensor.
+// The reference's group-wise path evaluates every step in the tensor's own dtype (bf16 / fp16 inputs: each torch op
+// computes in fp32 and rounds its result to the dtype); its per-token path mixes in an fp32 zero vector when it
+// forms the range (:180-182), which promotes everything after it to fp32 with one cast at the end.  Both are
+// followed here (dtype_math selects which), so the result is the reference's bit for bit.  T(.) below is that
+// rounding (the identity with fp32 math):
+//   range     per-token rows include 0 in the range, group-wise ranges do not (amax / amin of the group)
+//             xmin = T(min * clip), xmax = T(max * clip)
+//   symmetric xmax = max(|xmin|, xmax); scale = T(xmax / maxq) (1 where xmax == 0); q = clamp(rint(T(x / scale)),
+//             -(maxq+1), maxq); out = T(scale * q)
+//   otherwise (xmin, xmax) = (-1, +1) where both are 0; scale = T(T(xmax - xmin) / maxq); zero = rint(T(-xmin / scale));
+//             q = clamp(T(rint(T(x / scale)) + zero), 0, maxq); out = T(scale * T(q - zero))
+// HBM-bound: the unit is read from DRAM once (the second read hits L1 / L2) and written once.
+#include "rq_common.cuh"
+
+namespace rq {
+namespace actq {
+
+template <typename T>
+__device__ __forceinline__ float rnd(float v);
+template <>
+__device__ __forceinline__ float rnd<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float rnd<__nv_bfloat16>(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+template <>
+__device__ __forceinline__ float rnd<__half>(float v) { return __half2float(__float2half_rn(v)); }
+
+// 16-byte vectors: 4 floats or 8 half-precision values
+template <typename T>
+struct Vec {
+    static constexpr int N = 16 / sizeof(T);
+    uint4 raw;
+    __device__ __forceinline__ float get(int i) const { return load_as_float<T>(reinterpret_cast<const T*>(&raw), i); }
+    __device__ __forceinline__ void set(int i, float v) { store_from_float<T>(reinterpret_cast<T*>(&raw), i, v); }
+};
+
+// TPU threads cooperate on one unit (a token row or one group of a token); blockDim.x = 256.
+template <typename T, int TPU>
+__global__ void __launch_bounds__(256) act_quant_kernel(const T* __restrict__ x, T* __restrict__ out, int64_t units,
+                                                        int len, int with_zero, float clip, float maxq, int sym,
+                                                        float* __restrict__ scale_out, float* __restrict__ zero_out,
+                                                        const float* __restrict__ scale_in,
+                                                        const float* __restrict__ zero_in, int codes, int dtype_math,
+                                                        int vec_ok) {
+    constexpr int UPB = 256 / TPU;                       // units per block
+    constexpr int VN = Vec<T>::N;
+    auto R = [dtype_math](float v) { return dtype_math ? rnd<T>(v) : v; };
+    __shared__ float red_lo[8], red_hi[8];
+    const int sub = threadIdx.x / TPU, t = threadIdx.x % TPU;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int64_t u0 = (int64_t)blockIdx.x * UPB; u0 < units; u0 += (int64_t)gridDim.x * UPB) {
+        const int64_t u = u0 + sub;
+        const bool live = u < units;
+        const T* xr = x + (live ? u : 0) * (int64_t)len;
+        float scale, zero = 0.f;
+        if (scale_in != nullptr) {
+            scale = live ? scale_in[u] : 1.f;
+            zero = (live && zero_in != nullptr) ? zero_in[u] : 0.f;
+        } else {
+            float lo = with_zero ? 0.f : INFINITY, hi = with_zero ? 0.f : -INFINITY;
+            if (live && vec_ok) {
+                for (int c = t * VN; c < len; c += TPU * VN) {
+                    Vec<T> v;
+                    v.raw = *reinterpret_cast<const uint4*>(xr + c);
+#pragma unroll
+                    for (int i = 0; i < VN; ++i) {
+                        lo = fminf(lo, v.get(i));
+                        hi = fmaxf(hi, v.get(i));
+                    }
+                }
+            } else if (live) {
+                for (int c = t; c < len; c += TPU) {
+                    const float v = load_as_float<T>(xr, c);
+                    lo = fminf(lo, v);
+                    hi = fmaxf(hi, v);
+                }
+            }
+#pragma unroll
+            for (int o = (TPU < 32 ? TPU : 32) / 2; o > 0; o >>= 1) {
+                lo = fminf(lo, __shfl_xor_sync(0xffffffffu, lo, o));
+                hi = fmaxf(hi, __shfl_xor_sync(0xffffffffu, hi, o));
+            }
+            if (TPU > 32) {                              // one unit per block: combine the 8 warps
+                __syncthreads();
+                if (lane == 0) { red_lo[warp] = lo; red_hi[warp] = hi; }
+                __syncthreads();
+                lo = red_lo[0]; hi = red_hi[0];
+#pragma unroll
+                for (int w = 1; w < 8; ++w) { lo = fminf(lo, red_lo[w]); hi = fmaxf(hi, red_hi[w]); }
+            }
+            float xmin = R(lo * clip), xmax = R(hi * clip);
+            if (sym) {
+                xmax = fmaxf(fabsf(xmin), xmax);
+                scale = (xmax == 0.f) ? 1.f : R(__fdiv_rn(xmax, maxq));
+            } else {
+                if (xmin == 0.f && xmax == 0.f) { xmin = -1.f; xmax = 1.f; }
+                scale = R(__fdiv_rn(R(xmax - xmin), maxq));
+                zero = rintf(R(__fdiv_rn(-xmin, scale)));
+            }
+            if (live && t == 0) {
+                if (scale_out) scale_out[u] = scale;
+                if (zero_out) zero_out[u] = zero;
+            }
+        }
+        if (live && out != nullptr) {
+            T* orow = out + u * (int64_t)len;
+            auto one = [&](float v) -> float {
+                float q = rintf(R(__fdiv_rn(v, scale)));
+                float r;
+                if (sym) {
+                    q = fminf(fmaxf(q, -(maxq + 1.f)), maxq);
+                    r = codes ? q : R(scale * q);
+                } else {
+                    q = fminf(fmaxf(R(q + zero), 0.f), maxq);
+                    r = codes ? q : R(scale * R(q - zero));
+                }
+                return (v != v) ? v : r;                 // NaN propagates as in the reference
+            };
+            if (vec_ok) {
+                for (int c = t * VN; c < len; c += TPU * VN) {
+                    Vec<T> v, w;
+                    v.raw = *reinterpret_cast<const uint4*>(xr + c);
+#pragma unroll
+                    for (int i = 0; i < VN; ++i) w.set(i, one(v.get(i)));
+                    *reinterpret_cast<uint4*>(orow + c) = w.raw;
+                }
+            } else {
+                for (int c = t; c < len; c += TPU) store_from_float<T>(orow, c, one(load_as_float<T>(xr, c)));
+            }
+        }
+    }
+}
+
+}  // namespace actq
+}  // namespace rq
+
+extern "C" int rq_act_quant(const void* x, void* out, int dtype, int64_t units, int unit_len, int with_zero,
+                            float clip_ratio, int maxq, int sym, float* scale_out, float* zero_out,
+                            const float* scale_in, const float* zero_in, int codes, int dtype_math, void* stream) {
+    using namespace rq::actq;
+    if (!x || units < 0 || unit_len <= 0 || maxq <= 0 || !(clip_ratio > 0.f) || clip_ratio > 1.f) return RQ_ERR_INVALID;
+    if (!out && !scale_out) return RQ_ERR_INVALID;
+    if (!sym && scale_in && !zero_in) return RQ_ERR_INVALID;
+    if (units == 0) return RQ_OK;
+    cudaStream_t st = rq::as_stream(stream);
+    const int vn = dtype == RQ_F32 ? 4 : 8;
+    const int vec_ok = (unit_len % vn == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0 &&
+                        (!out || reinterpret_cast<uintptr_t>(out) % 16 == 0)) ? 1 : 0;
+    const bool wide = unit_len > 1024;                    // a block per unit, else a warp per unit
+    int64_t blocks = wide ? units : (units + 7) / 8;
+    if (blocks > 148 * 64) blocks = 148 * 64;
+#define RQ_ACTQ_LAUNCH(T)                                                                                          \
+    do {                                                                                                           \
+        if (wide)                                                                                                  \
+            act_quant_kernel<T, 256><<<(unsigned)blocks, 256, 0, st>>>(                                            \
+                reinterpret_cast<const T*>(x), reinterpret_cast<T*>(out), units, unit_len, with_zero, clip_ratio,  \
+                (float)maxq, sym, scale_out, zero_out, scale_in, zero_in, codes, dtype_math, vec_ok);              \
+        else                                                                                                       \
+            act_quant_kernel<T, 32><<<(unsigned)blocks, 256, 0, st>>>(                                             \
+                reinterpret_cast<const T*>(x), reinterpret_cast<T*>(out), units, unit_len, with_zero, clip_ratio,  \
+                (float)maxq, sym, scale_out, zero_out, scale_in, zero_in, codes, dtype_math, vec_ok);              \
+    } while (0)
+    if (dtype == RQ_F32) RQ_ACTQ_LAUNCH(float);
+    else if (dtype == RQ_BF16) RQ_ACTQ_LAUNCH(__nv_bfloat16);
+    else if (dtype == RQ_F16) RQ_ACTQ_LAUNCH(__half);
+    else return RQ_ERR_INVALID;
+#undef RQ_ACTQ_LAUNCH
+    return rq::check_launch();
+}

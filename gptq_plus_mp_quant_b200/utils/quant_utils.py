@@ -106,6 +106,146 @@ class AsymSTEQuantize(torch.autograd.Function):
         return grad_output, None, None, None
 
 
+class ActQuantizer(torch.nn.Module):
+    """Dynamic per-token (``groupsize <= 0``) or per-token-group activation quantizer (utils/quant_utils.py:87-206),
+    both symmetric and asymmetric.  Ranges and the quantize-dequantize run in one kernel that rounds every
+    intermediate to the tensor's dtype exactly as the reference's chain of torch ops does.  The ranges are kept as one
+    scale / zero per token (or token group); ``scale`` / ``zero`` expand them to the input's shape on request."""
+
+    def __init__(self) -> None:
+        super().__init__()
+        self.register_buffer("maxq", torch.tensor(0))
+        self._scale = self._zero = None
+        self._shape = None
+        self.bits = 16
+
+    def free(self) -> None:
+        self._scale = self._zero = None
+        self._shape = None
+
+    def configure(self, bits: int, groupsize: int = -1, sym: bool = False, clip_ratio: float = 1.0) -> None:
+        _, self.maxq = get_minq_maxq(bits, sym)
+        self.bits = bits
+        self.groupsize = groupsize
+        self.sym = sym
+        self.clip_ratio = clip_ratio
+        assert self.clip_ratio <= 1 and self.clip_ratio > 0, "Clip ratio should be in (0, 1]"
+
+    def _units(self, x):
+        n = x.shape[-1]
+        if self.groupsize > 0:
+            if n % self.groupsize != 0:
+                raise ValueError(f"last dimension {n} is not divisible by groupsize {self.groupsize}")
+            return x.numel() // self.groupsize, self.groupsize, 0
+        return x.numel() // n, n, 1
+
+    def _run(self, x, out, scale_out, zero_out, scale_in, zero_in, codes=False):
+        _lib.require_cuda(x)
+        units, length, with_zero = self._units(x)
+        with torch.cuda.device(x.device):
+            rc = _lib.lib.rq_act_quant(_lib.ptr(x), _lib.ptr(out), _lib.dtype_code(x), units, length, with_zero,
+                                       float(self.clip_ratio), int(self.maxq), 1 if self.sym else 0,
+                                       _lib.ptr(scale_out), _lib.ptr(zero_out), _lib.ptr(scale_in), _lib.ptr(zero_in),
+                                       1 if codes else 0, 0 if with_zero else 1, _lib.stream_of(x))
+        _lib.check("rq_act_quant", rc)
+
+    def find_params(self, x) -> None:
+        if self.bits == 16:
+            return
+        x = x.contiguous()
+        units, _, _ = self._units(x)
+        self._scale = torch.empty(units, dtype=torch.float32, device=x.device)
+        self._zero = torch.zeros(units, dtype=torch.float32, device=x.device)
+        self._shape, self._dtype = tuple(x.shape), x.dtype
+        self._run(x, None, self._scale, self._zero, None, None)
+
+    def _expand(self, v):
+        if v is None:
+            return None
+        per = 1
+        for d in self._shape:
+            per *= d
+        per //= v.numel()
+        # group-wise ranges live in the input's dtype; the per-token path of the reference promotes them to fp32
+        dt = self._dtype if self.groupsize > 0 else torch.float32
+        return v.to(dt).repeat_interleave(per).reshape(self._shape)
+
+    @property
+    def scale(self):
+        return self._expand(self._scale)
+
+    @property
+    def zero(self):
+        return self._expand(self._zero)
+
+    def forward(self, x):
+        if self.bits == 16:
+            return x
+        xc = x.contiguous()
+        out = torch.empty_like(xc)
+        self._run(xc, out, None, None, self._scale, self._zero)
+        return out
+
+    def fake_quant(self, x):
+        """find_params + forward + free in one pass (what ActQuantWrapper.forward does around every linear)."""
+        if self.bits == 16:
+            return x
+        xc = x.contiguous()
+        out = torch.empty_like(xc)
+        self._run(xc, out, None, None, None, None)
+        return out
+
+    def quantize(self, x):
+        """Integer codes with the stored ranges (utils/quant_utils.py:112-117): (q, scale) or (q, scale, zero)."""
+        xc = x.contiguous()
+        q = torch.empty_like(xc)
+        self._run(xc, q, None, None, self._scale, self._zero, codes=True)
+        return (q, self.scale) if self.sym else (q, self.scale, self.zero)
+
+
+class ActQuantWrapper(torch.nn.Module):
+    """Linear wrapped with an optional online Hadamard rotation and dynamic input / output fake quantization
+    (utils/quant_utils.py:209-297): rotation and quantization are one kernel each."""
+
+    def __init__(self, module) -> None:
+        super().__init__()
+        self.module = module
+        self.weight = module.weight
+        self.bias = module.bias
+        self.quantizer = ActQuantizer()
+        self.out_quantizer = ActQuantizer()
+        self.register_buffer("had_K", torch.tensor(0))
+        self._buffers["had_K"] = None
+        self.K = 1
+        self.online_full_had = False
+        self.online_partial_had = False
+        self.had_dim = 0
+        self.fp32_had = False
+
+    def extra_repr(self) -> str:
+        def kind(q):
+            return "" if q.bits >= 16 else (" (Symmetric Per-Token)" if q.sym else " (Asymmetric Per-Token)")
+        return (f"Input Quantizer Bits: {self.quantizer.bits}{kind(self.quantizer)}"
+                f"\nOutput Quantizer Bits: {self.out_quantizer.bits}{kind(self.out_quantizer)}")
+
+    def forward(self, x, R1=None, R2=None, transpose=False):
+        from . import hadamard_utils
+        x_dtype = x.dtype
+        if self.online_full_had:
+            if self.fp32_had:
+                x = hadamard_utils.matmul_hadU_cuda(x.float(), self.had_K, self.K).to(x_dtype)
+            else:
+                x = hadamard_utils.matmul_hadU_cuda(x, self.had_K, self.K)
+        elif self.online_partial_had:
+            raise NotImplementedError("the per-head partial Hadamard of the attention output is not built")
+        if self.quantizer.bits < 16:
+            x = self.quantizer.fake_quant(x).to(x_dtype)
+        x = (self.module(x, R1, R2, transpose) if R1 is not None else self.module(x)).to(x_dtype)
+        if self.out_quantizer.bits < 16:
+            x = self.out_quantizer.fake_quant(x).to(x_dtype)
+        return x
+
+
 def find_params_groups(W: torch.Tensor, groupsize: int, maxq: int, sym: bool, mse: bool = False,
                        norm: float = 2.4, grid: int = 50, maxshrink: float = 0.5):
     """Per-row ranges of every ``groupsize``-wide column group in one launch:

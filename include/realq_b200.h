@@ -155,6 +155,20 @@ int rq_quantize(const void* x, void* deq, float* codes, int dtype, int64_t R, in
 int rq_group_mean_square(const void* grad, int dtype, int64_t batch, int64_t seq, int64_t stride_b, int64_t stride_t,
                          int hidden, int G, float* out, void* stream);
 
+/* rq_act_quant replaces ActQuantizer.find_params followed by STEQuantize / AsymSTEQuantize.forward
+ * (utils/quant_utils.py:60-84, 133-206; call site ActQuantWrapper.forward :283-295): dynamic fake quantization of
+ * activations per unit, a unit being one token row (with_zero = 1: the range includes 0, :180-183) or one group of a
+ * token (with_zero = 0: amax / amin of the group, :139-140).  x, out: [units, unit_len] of dtype.  dtype_math != 0:
+ * every intermediate is rounded to dtype, as the reference's group-wise chain of torch ops does; dtype_math == 0: fp32
+ * throughout with one final cast, as its per-token path does (the fp32 zero vector of :180 promotes it); with the
+ * matching setting results agree bit for bit.  scale_out / zero_out
+ * (optional, fp32 [units]) receive the ranges; scale_in / zero_in (optional) replace the range search (forward with
+ * stored ranges); out may be NULL when only the ranges are wanted; codes != 0 writes the integer codes
+ * (ActQuantizer.quantize, :112-117) instead of the dequantized values. */
+int rq_act_quant(const void* x, void* out, int dtype, int64_t units, int unit_len, int with_zero, float clip_ratio,
+                 int maxq, int sym, float* scale_out, float* zero_out, const float* scale_in, const float* zero_in,
+                 int codes, int dtype_math, void* stream);
+
 /* rq_clip_to_quant_bounds replaces clip_module_weight_to_quant_bounds_'s arithmetic
  * (gptq_utils/gptq_plus_utils.py:197-225: compute_quant_clip_bounds + clip_tensor_to_quant_bounds) once
  * rq_find_params has produced scale / zero: W [R, C] of dtype (row stride ldw) is clamped in place, per row, to

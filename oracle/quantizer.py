@@ -177,3 +177,59 @@ def clip_weight_to_quant_bounds(weight, bits, sym, mse):
     q.find_params(w)
     lo, hi = compute_quant_clip_bounds(q.scale, q.zero, q.maxq, q.sym)
     return torch.minimum(torch.maximum(w, lo.to(w.dtype)), hi.to(w.dtype)).to(weight.dtype)
+
+
+def act_find_params(x, bits, groupsize=-1, sym=False, clip_ratio=1.0):
+    """ActQuantizer.find_params (utils/quant_utils.py:133-206): (scale, zero, maxq), scale / zero of x's shape."""
+    maxq = torch.tensor(2 ** (bits - 1) - 1) if sym else torch.tensor(2 ** bits - 1)
+    init_shape = x.shape
+    if groupsize > 0:
+        reshaped_x = x.reshape(-1, x.shape[-2], x.shape[-1] // groupsize, groupsize)
+        xmax = torch.amax(reshaped_x, dim=3, keepdim=True) * clip_ratio
+        xmin = torch.amin(reshaped_x, dim=3, keepdim=True) * clip_ratio
+        if sym:
+            xmax = torch.maximum(torch.abs(xmin), xmax)
+            tmp = xmax == 0
+            scale = xmax / maxq
+            scale[tmp] = 1
+            zero = torch.zeros_like(scale)
+        else:
+            tmp = (xmin == 0) & (xmax == 0)
+            xmin[tmp] = -1
+            xmax[tmp] = +1
+            scale = (xmax - xmin) / maxq
+            zero = torch.round(-xmin / scale)
+        return (scale.repeat(1, 1, 1, groupsize).reshape(init_shape),
+                zero.repeat(1, 1, 1, groupsize).reshape(init_shape), maxq)
+    reshaped_x = x.reshape((-1, x.shape[-1]))
+    tmp = torch.zeros(reshaped_x.shape[0])
+    xmin = torch.minimum(reshaped_x.min(1)[0], tmp) * clip_ratio
+    xmax = torch.maximum(reshaped_x.max(1)[0], tmp) * clip_ratio
+    if sym:
+        xmax = torch.maximum(torch.abs(xmin), xmax)
+        tmp = xmax == 0
+        scale = (xmax / maxq).unsqueeze(1).repeat(1, reshaped_x.shape[-1])
+        scale[tmp] = 1
+        scale = scale.reshape(init_shape)
+        zero = torch.zeros_like(scale)
+    else:
+        tmp = (xmin == 0) & (xmax == 0)
+        xmin[tmp] = -1
+        xmax[tmp] = +1
+        scale = (xmax - xmin) / maxq
+        zero = torch.round(-xmin / scale)
+        scale = scale.unsqueeze(1).repeat(1, reshaped_x.shape[-1]).reshape(init_shape)
+        zero = zero.unsqueeze(1).repeat(1, reshaped_x.shape[-1]).reshape(init_shape)
+    return scale, zero, maxq
+
+
+def act_fake_quant(x, bits, groupsize=-1, sym=False, clip_ratio=1.0):
+    """ActQuantizer.find_params + forward (utils/quant_utils.py:103-110): the fake-quantized activations."""
+    if bits == 16:
+        return x
+    scale, zero, maxq = act_find_params(x, bits, groupsize, sym, clip_ratio)
+    if sym:
+        q = torch.clamp(torch.round(x / scale), -(maxq + 1), maxq)
+        return (scale * q).to(x.dtype)
+    q = torch.clamp(torch.round(x / scale) + zero, 0, maxq)
+    return (scale * (q - zero)).to(x.dtype)

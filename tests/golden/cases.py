@@ -93,6 +93,26 @@ def make_out_grad(batch, seq, hidden, seed):
     return torch.randn(batch, seq, hidden, generator=g) * torch.exp(2.0 * torch.randn(batch, seq, 1, generator=g)) * 1e-3
 
 
+ACT_QUANT_CASES = [
+    # name, shape, bits, groupsize, sym, clip_ratio, dtype
+    ("act_a4_asym_tok_bf16", (2, 9, 256), 4, -1, False, 1.0, "bfloat16"),
+    ("act_a4_sym_tok_clip_bf16", (2, 9, 256), 4, -1, True, 0.9, "bfloat16"),
+    ("act_a8_asym_g64_f16", (1, 7, 192), 8, 64, False, 0.95, "float16"),
+    ("act_a4_sym_g128_bf16", (3, 5, 384), 4, 128, True, 1.0, "bfloat16"),
+    ("act_a4_asym_tok_f32_long", (1, 3, 1536), 4, -1, False, 0.9, "float32"),
+    ("act_a8_sym_tok_f32", (1, 4, 200), 8, -1, True, 1.0, "float32"),
+]
+
+
+def make_act_tensor(shape, seed):
+    """Activations with outlier channels, one all-zero row and one all-positive row."""
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(*shape, generator=g) * torch.exp(1.5 * torch.randn(shape[-1], generator=g))
+    x[0, 0] = 0.0
+    x[0, 1] = x[0, 1].abs() + 0.5
+    return x
+
+
 HADAMARD_CASES = [
     # name, rows, n, dtype
     ("n128_f32", 37, 128, "float32"),

@@ -98,6 +98,22 @@ def gen_saliency(gpu, out):
         out[f"{name}.saliency"] = np32(sal)
 
 
+def gen_act_quant(qu, out):
+    """ActQuantizer: find_params then forward (what ActQuantWrapper.forward does), and the integer codes."""
+    for name, shape, bits, gs, sym, clip, dtype in cases.ACT_QUANT_CASES:
+        x = cases.make_act_tensor(shape, seed=23).to(getattr(torch, dtype))
+        q = qu.ActQuantizer()
+        q.configure(bits, groupsize=gs, sym=sym, clip_ratio=clip)
+        q.find_params(x)
+        y = q(x)
+        codes = q.quantize(x)[0]
+        out[f"{name}.digest"] = np.array(cases.digest(x.float()))
+        out[f"{name}.deq"] = np32(y.float())
+        out[f"{name}.codes"] = np32(codes.float())
+        out[f"{name}.scale"] = np32(q.scale.float())
+        out[f"{name}.zero"] = np32(q.zero.float())
+
+
 def gen_hadamard(hu, out):
     had_tab = torch.load(os.path.join(os.path.dirname(hu.__file__), "had_mat.pt"))
     for k in (12, 20, 28):
@@ -227,7 +243,8 @@ def main():
                             ("gptq_plus.npz", gen_plus, (qu, gpu)),
                             ("faults.npz", gen_faults, (qu, gpu)),
                             ("clip.npz", gen_clip, (qu, gpu)),
-                            ("saliency.npz", gen_saliency, (gpu,))):
+                            ("saliency.npz", gen_saliency, (gpu,)),
+                            ("act_quant.npz", gen_act_quant, (qu,))):
         out = {}
         with torch.no_grad():
             fn(*mods, out)

@@ -389,3 +389,48 @@ def test_fisher_accumulation_vs_oracle():
     fisher_finalize_(F)
     assert float((F.cpu() - ref).norm() / ref.norm()) < 5e-6
     assert torch.equal(F, F.t())
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("case", cases.ACT_QUANT_CASES, ids=lambda c: c[0])
+def test_act_quantizer_vs_reference(golden, case):
+    """The fused activation fake-quant kernel against the reference's ActQuantizer, bit for bit: ranges, dequantized
+    values (stored-range forward and the one-pass path) and integer codes."""
+    from gptq_plus_mp_quant_b200.utils.quant_utils import ActQuantizer
+    name, shape, bits, gs, sym, clip, dtype = case
+    g = golden("act_quant.npz")
+    x = cases.make_act_tensor(shape, seed=23).to(getattr(torch, dtype)).to(DEV)
+    q = ActQuantizer()
+    q.configure(bits, groupsize=gs, sym=sym, clip_ratio=clip)
+    q.find_params(x)
+    assert torch.equal(q.scale.float().cpu(), torch.from_numpy(g[f"{name}.scale"]))
+    assert torch.equal(q.zero.float().cpu(), torch.from_numpy(g[f"{name}.zero"]))
+    y = q(x)
+    assert y.dtype == x.dtype and y.shape == x.shape
+    assert torch.equal(y.float().cpu(), torch.from_numpy(g[f"{name}.deq"]))
+    assert torch.equal(q.quantize(x)[0].float().cpu(), torch.from_numpy(g[f"{name}.codes"]))
+    q.free()
+    assert torch.equal(q.fake_quant(x).float().cpu(), torch.from_numpy(g[f"{name}.deq"]))
+    q16 = ActQuantizer()
+    q16.configure(16)
+    assert q16(x) is x
+
+
+@pytest.mark.gpu
+def test_act_quant_wrapper_rotates_and_quantizes():
+    """ActQuantWrapper: online Hadamard + 4-bit input fake-quant around a linear equals the same steps done by the
+    oracle on the CPU (rotation within one bf16 rounding, hence compared after the quantizer on the kernel's own
+    rotated input)."""
+    from gptq_plus_mp_quant_b200.utils import hadamard_utils as hu
+    from gptq_plus_mp_quant_b200.utils.quant_utils import ActQuantWrapper
+    torch.manual_seed(0)
+    lin = torch.nn.Linear(512, 64, bias=False, device=DEV, dtype=torch.bfloat16)
+    wrap = ActQuantWrapper(lin)
+    wrap.online_full_had = True
+    wrap.had_K, wrap.K = hu.get_hadK(512)
+    wrap.quantizer.configure(4, groupsize=-1, sym=False, clip_ratio=0.9)
+    x = cases.make_act_tensor((2, 6, 512), seed=29).bfloat16().to(DEV)
+    y = wrap(x)
+    xr = hu.matmul_hadU_cuda(x, wrap.had_K, wrap.K)
+    xq = oq.act_fake_quant(xr.cpu(), 4, -1, False, 0.9).to(DEV)
+    assert torch.equal(y, lin(xq))

@@ -208,3 +208,16 @@ def test_saliency_hook(golden, case):
     sal = ohess.group_mean_square(coef, G, sink)
     assert sal.shape == (batch, seq - sink, G)
     assert torch.equal(sal, t(g[f"{name}.saliency"]))
+
+
+@pytest.mark.parametrize("case", cases.ACT_QUANT_CASES, ids=lambda c: c[0])
+def test_act_quantizer(golden, case):
+    """ActQuantizer: dynamic per-token / per-token-group ranges and the fake quantization, in the tensor's dtype."""
+    name, shape, bits, gs, sym, clip, dtype = case
+    g = golden("act_quant.npz")
+    x = cases.make_act_tensor(shape, seed=23).to(getattr(torch, dtype))
+    assert cases.digest(x.float()) == str(g[f"{name}.digest"])
+    scale, zero, maxq = oq.act_find_params(x, bits, gs, sym, clip)
+    assert torch.equal(scale.float(), t(g[f"{name}.scale"])) and torch.equal(zero.float(), t(g[f"{name}.zero"]))
+    y = oq.act_fake_quant(x, bits, gs, sym, clip)
+    assert y.dtype == x.dtype and torch.equal(y.float(), t(g[f"{name}.deq"]))
