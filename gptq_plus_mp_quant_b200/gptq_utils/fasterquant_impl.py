@@ -382,6 +382,34 @@ def _quantize_owned_groups(obj, W32, H3, perm, grads, alpha_eff, plus, percdamp,
 
 
 # ----------------------------------------------------------------------------------------------
+# GuidedQuant (gptq_utils/gptq_guided_utils.py:86-259): grouped Hessians, no first-order terms
+# ----------------------------------------------------------------------------------------------
+@torch.no_grad()
+def guided_fasterquant(obj, H3, blocksize, percdamp, groupsize, actorder, static_groups, export_to_et):
+    layer, dev = obj.layer, obj.dev
+    W32 = layer.weight.data.float().contiguous()
+    G = obj.num_groups
+    if not obj.quantizer.ready():
+        obj.quantizer.find_params(W32)
+    _check_common(obj.quantizer, blocksize)
+    if groupsize != -1 and not static_groups and actorder:
+        raise NotImplementedError("GuidedQuant with dynamic weight groups under act_order (the reference ranges them "
+                                  "from un-permuted, un-updated columns) is not built")
+    empty = (H3.reshape(G, -1) == 0).all(dim=1).tolist()           # no calibration data: round to nearest (:119-121)
+    if any(empty):
+        H3 = H3.clone()
+        for g, e in enumerate(empty):
+            if e:
+                H3[g] = torch.eye(obj.columns, device=dev)
+    perm = torch.argsort(obj.act_square, descending=True) if actorder else None
+    mode_pack = _scale_setup(obj.quantizer, W32, groupsize, static_groups, blocksize, perm, None)
+    Hinv, damp, _ = hinv_with_fallback(H3, perm, percdamp, identity_fallback=False)
+    _quantize_linear(layer, W32, H3, perm, None, obj.quantizer, G, 0.0, 0.0, False, Hinv, mode_pack, export_to_et,
+                     permute_export=True)
+    obj._last_fasterquant = {"perm": perm, "damp_percent": damp}
+
+
+# ----------------------------------------------------------------------------------------------
 # plain GPTQ (gptq_utils/gptq_utils.py:45-174)
 # ----------------------------------------------------------------------------------------------
 @torch.no_grad()

@@ -363,3 +363,19 @@ def plus_fasterquant(weight, H, act_square, gradients, quantizer, num_groups, al
         Scale_final[st["r0"]:st["r1"]] = Sc
     return {"Q": Q_final, "W_int": Wint_final, "Scale": Scale_final,
             "perm": states[0]["perm"], "states": states}
+
+
+def guided_fasterquant(weight, H_ccg, act_square, quantizer, num_groups, blocksize=128, percdamp=0.01,
+                       groupsize=-1, actorder=False, static_groups=False):
+    """GPTQGuided.fasterquant (gptq_guided_utils.py:86-259): the GPTQ+ loop without first-order terms on the raw
+    Hessian sums ``H_ccg`` [C, C, G]; damping failures raise instead of falling back to the identity."""
+    H = H_ccg.permute(2, 0, 1).contiguous()
+    for g in range(num_groups):
+        if bool((H[g] == 0).all()):
+            H[g] = torch.eye(H.shape[-1])
+    out = plus_fasterquant(weight, H, act_square, torch.zeros_like(weight, dtype=torch.float32), quantizer,
+                           num_groups, 0.0, 0.0, blocksize=blocksize, percdamp=percdamp, groupsize=groupsize,
+                           actorder=actorder, static_groups=static_groups, enable_gradient_update=False)
+    if any(st["identity"] for st in out["states"]):
+        raise ValueError("Quantization: `damp_percent` must between 0 and 1.")
+    return out

@@ -93,6 +93,14 @@ def make_out_grad(batch, seq, hidden, seed):
     return torch.randn(batch, seq, hidden, generator=g) * torch.exp(2.0 * torch.randn(batch, seq, 1, generator=g)) * 1e-3
 
 
+GUIDED_CASES = [
+    # name, rows, cols, nseq, seqlen, G, bits, groupsize, actorder, static
+    ("guided_pc_act", 32, 256, 4, 96, 4, 4, -1, True, False),
+    ("guided_g128_static_act", 32, 256, 4, 96, 2, 4, 128, True, True),
+    ("guided_pc_noact", 16, 384, 3, 64, 2, 3, -1, False, False),
+    ("guided_g128_dynamic_noact", 16, 256, 3, 64, 2, 4, 128, False, False),
+]
+
 ACT_QUANT_CASES = [
     # name, shape, bits, groupsize, sym, clip_ratio, dtype
     ("act_a4_asym_tok_bf16", (2, 9, 256), 4, -1, False, 1.0, "bfloat16"),

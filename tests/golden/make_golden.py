@@ -38,10 +38,10 @@ def import_reference(ref_root: str):
             sys.modules[name] = mod
     sys.path.insert(0, ref_root)
     from utils import quant_utils, hadamard_utils, memory_utils
-    from gptq_utils import gptq_utils, gptq_plus_utils
+    from gptq_utils import gptq_utils, gptq_plus_utils, gptq_guided_utils
     torch.cuda.synchronize = lambda *a, **k: None
     memory_utils.cleanup_memory = lambda *a, **k: None
-    return quant_utils, hadamard_utils, gptq_utils, gptq_plus_utils
+    return quant_utils, hadamard_utils, gptq_utils, gptq_plus_utils, gptq_guided_utils
 
 
 # cases whose full Hessian / inverse factor is stored (the rest keep only the small outputs)
@@ -96,6 +96,26 @@ def gen_saliency(gpu, out):
         cache.clear_hook()
         out[f"{name}.digest"] = np.array(cases.digest(coef.float()))
         out[f"{name}.saliency"] = np32(sal)
+
+
+def gen_guided(qu, gg, out):
+    for (name, rows, cols, nseq, seqlen, G, bits, gs, act, static) in cases.GUIDED_CASES:
+        W = cases.make_weight(rows, cols, seed=61)
+        X = cases.make_acts(nseq, seqlen, cols, seed=61)
+        S = cases.make_saliency(nseq, seqlen, G, seed=61)
+        layer = _Lin(W)
+        g = gg.GPTQGuided(layer, S, G)
+        g.quantizer = qu.WeightQuantizer()
+        g.quantizer.configure(bits, perchannel=True, sym=True, mse=False)
+        g.add_batch(X[:1], None)
+        g.add_batch(X[1:], None)
+        out[f"{name}.digest"] = np.array(cases.digest(W, X, S))
+        out[f"{name}.act_square"] = np32(g.act_square)
+        out[f"{name}.H_trace"] = np32(torch.einsum("iig->g", g.H))
+        g.fasterquant(blocksize=128, percdamp=0.01, groupsize=gs, actorder=act, static_groups=static, export_to_et=True)
+        out[f"{name}.Q"] = np32(layer.weight.data)
+        out[f"{name}.W_int"] = np32(layer.int_weight).astype(np.int8)
+        out[f"{name}.Scale"] = np32(layer.scale)
 
 
 def gen_act_quant(qu, out):
@@ -236,7 +256,7 @@ def main():
     ap.add_argument("--ref", default="/root/reference")
     args = ap.parse_args()
     torch.set_num_threads(1)                        # fixed reduction order on any host
-    qu, hu, gu, gpu = import_reference(args.ref)
+    qu, hu, gu, gpu, gg = import_reference(args.ref)
     for fname, fn, mods in (("quantizer.npz", gen_quantizer, (qu,)),
                             ("hadamard.npz", gen_hadamard, (hu,)),
                             ("plain_gptq.npz", gen_plain, (qu, gu)),
@@ -244,7 +264,8 @@ def main():
                             ("faults.npz", gen_faults, (qu, gpu)),
                             ("clip.npz", gen_clip, (qu, gpu)),
                             ("saliency.npz", gen_saliency, (gpu,)),
-                            ("act_quant.npz", gen_act_quant, (qu,))):
+                            ("act_quant.npz", gen_act_quant, (qu,)),
+                            ("guided.npz", gen_guided, (qu, gg))):
         out = {}
         with torch.no_grad():
             fn(*mods, out)

@@ -375,3 +375,40 @@ def test_two_level_schedule_with_ragged_last_group(cols):
         frac, touched, first = _code_report(codes, ref, perm)
         print(f"C={cols} {name}: {frac * 100:.4f}% codes differ in {touched} rows")
         assert frac < 5e-3 and all(d == 1.0 for d in first)
+
+
+@pytest.mark.parametrize("case", cases.GUIDED_CASES, ids=lambda c: c[0])
+def test_gptq_guided_vs_reference(golden, case):
+    """GPTQGuided on the device against the reference's outputs, and its block loop against the oracle run on the
+    Hessian the device accumulated."""
+    from gptq_plus_mp_quant_b200.gptq_utils.gptq_guided_utils import GPTQGuided
+    from gptq_plus_mp_quant_b200.utils.quant_utils import WeightQuantizer
+    (name, rows, cols, nseq, seqlen, G, bits, gs, act, static) = case
+    g = golden("guided.npz")
+    W = cases.make_weight(rows, cols, seed=61)
+    X = cases.make_acts(nseq, seqlen, cols, seed=61)
+    S = cases.make_saliency(nseq, seqlen, G, seed=61)
+    layer = _layer(W)
+    obj = GPTQGuided(layer, S, G)
+    obj.quantizer = WeightQuantizer()
+    obj.quantizer.configure(bits, perchannel=True, sym=True, mse=False)
+    obj.add_batch(X[:1].to(DEV), None)
+    obj.add_batch(X[1:].to(DEV), None)
+    assert obj.H.shape == (cols, cols, G)
+    assert torch.allclose(obj.act_square.cpu(), torch.from_numpy(g[f"{name}.act_square"]), rtol=1e-5)
+    assert torch.allclose(torch.einsum("iig->g", obj.H).cpu(), torch.from_numpy(g[f"{name}.H_trace"]), rtol=1e-5)
+    H_dev, act_dev = obj.H.clone().cpu(), obj.act_square.clone().cpu()
+    obj.fasterquant(blocksize=128, percdamp=0.01, groupsize=gs, actorder=act, static_groups=static, export_to_et=True)
+    order = obj._last_fasterquant["perm"].cpu() if act else None
+    codes_ref = torch.from_numpy(g[f"{name}.W_int"]).float()
+    frac, touched, first = _code_report(layer.int_weight.cpu(), codes_ref, order)
+    print(f"{name}: {frac * 100:.4f}% codes differ in {touched} rows")
+    assert frac < 0.01 and all(d == 1.0 for d in first)
+    q = oq.OracleWeightQuantizer()
+    q.configure(bits, perchannel=True, sym=True)
+    o = ogptq.guided_fasterquant(W, H_dev, act_dev, q, G, groupsize=gs, actorder=act, static_groups=static)
+    frac2, _, first2 = _code_report(layer.int_weight.cpu(), o["W_int"].float(), order)
+    print(f"{name}: against the oracle on the device's Hessian {frac2 * 100:.4f}% differ")
+    assert frac2 < 0.01 and all(d == 1.0 for d in first2)
+    obj.free()
+    assert obj.H is None

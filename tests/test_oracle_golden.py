@@ -221,3 +221,28 @@ def test_act_quantizer(golden, case):
     assert torch.equal(scale.float(), t(g[f"{name}.scale"])) and torch.equal(zero.float(), t(g[f"{name}.zero"]))
     y = oq.act_fake_quant(x, bits, gs, sym, clip)
     assert y.dtype == x.dtype and torch.equal(y.float(), t(g[f"{name}.deq"]))
+
+
+@pytest.mark.parametrize("case", cases.GUIDED_CASES, ids=lambda c: c[0])
+def test_gptq_guided(golden, case):
+    """GPTQGuided (GuidedQuant): raw-sum grouped Hessians, the block loop without first-order terms."""
+    (name, rows, cols, nseq, seqlen, G, bits, gs, act, static) = case
+    g = golden("guided.npz")
+    W = cases.make_weight(rows, cols, seed=61)
+    X = cases.make_acts(nseq, seqlen, cols, seed=61)
+    S = cases.make_saliency(nseq, seqlen, G, seed=61)
+    assert cases.digest(W, X, S) == str(g[f"{name}.digest"])
+    H = torch.zeros(cols, cols, G)
+    act_sq = torch.zeros(cols)
+    for sl in (slice(0, 1), slice(1, nseq)):
+        inp = X[sl].reshape(-1, cols).float()
+        sal = S[sl].reshape(-1, G).float()
+        H.add_(torch.einsum("ni,njg->ijg", inp, torch.einsum("nj,ng->njg", inp, sal)))
+        act_sq.add_((inp ** 2).sum(0), alpha=1 / inp.shape[0])
+    assert torch.equal(act_sq, t(g[f"{name}.act_square"]))
+    q = oq.OracleWeightQuantizer()
+    q.configure(bits, perchannel=True, sym=True, mse=False)
+    out = ogptq.guided_fasterquant(W, H, act_sq, q, G, groupsize=gs, actorder=act, static_groups=static)
+    assert torch.equal(out["W_int"], t(g[f"{name}.W_int"]).float())
+    assert torch.equal(out["Scale"], t(g[f"{name}.Scale"]))
+    assert torch.equal(out["Q"], t(g[f"{name}.Q"]))
