@@ -750,3 +750,358 @@ extern "C" int rq_fq_run_tc(float* Wp, float* GH, const float* Z, const float* H
     }
     return RQ_OK;
 }
+
+// ==========================================================================================
+// GPTAQ (asymmetric calibration): gptq_utils/gptaq_utils.py.  Besides H it accumulates
+//   dXXT = mean-normalised sum over tokens of (x_fp - x) x^T          (:36-39, not symmetric)
+// and fasterquant adds, per quantized column i, the term  + w_i (x) P[i, i:]  with
+//   P = alpha * triu(dXXT . Hinv^T, 1) . Hinv                         (:105)
+// to the error feedback (:140), and  + Q1 . P[i1:i2, i2:]  to the lazy update (:146).
+// ==========================================================================================
+namespace rq {
+namespace aq {
+
+using fq::BS;
+using fq::kBlockThreads;
+using fq::kRowsPerCta;
+
+// planes of d' = fl(x_fp * s) - fl(x * s) and x' = fl(x * s), transposed: dst[c][t].  grid (ceil(C/32), ceil(Np/64)).
+// x: [N, C] (row stride ldx); x_fp: [N, C] (row stride ldf) or, with FT, channel-major [C, N] as the reference's
+// input cache stores it (gptaq_utils.py:185-189).
+template <typename TX, typename TF, bool FT>
+__global__ void __launch_bounds__(256) diff_pack_kernel(const TX* __restrict__ x, int64_t ldx, const TF* __restrict__ xf,
+                                                        int64_t ldf, int64_t N, int C, float s,
+                                                        __nv_bfloat16* __restrict__ PD, __nv_bfloat16* __restrict__ PX,
+                                                        int64_t Kp) {
+    __shared__ float td[64][33], tx[64][33];
+    const int lx = threadIdx.x & 31, ly = threadIdx.x >> 5;
+    const int c0 = blockIdx.x * 32;
+    const int64_t t0 = (int64_t)blockIdx.y * 64;
+    if (FT) {                                              // stage x_fp with the lanes running along the tokens
+#pragma unroll
+        for (int cc = ly; cc < 32; cc += 8)
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int64_t t = t0 + 32 * h + lx;
+                const int c = c0 + cc;
+                td[32 * h + lx][cc] = (t < N && c < C) ? load_as_float<TF>(xf, (int64_t)c * ldf + t) : 0.f;
+            }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int rr = ly; rr < 64; rr += 8) {
+        const int64_t t = t0 + rr;
+        const int c = c0 + lx;
+        float xv = 0.f, dv = 0.f;
+        if (t < N && c < C) {
+            xv = __fmul_rn(load_as_float<TX>(x, t * ldx + c), s);
+            const float fv = FT ? td[rr][lx] : load_as_float<TF>(xf, t * ldf + c);
+            dv = __fsub_rn(__fmul_rn(fv, s), xv);
+        }
+        tx[rr][lx] = xv;
+        td[rr][lx] = dv;
+    }
+    __syncthreads();
+    const int64_t plane = (int64_t)C * Kp;
+#pragma unroll
+    for (int cc = ly; cc < 32; cc += 8) {
+        const int c = c0 + cc;
+        const int64_t t = t0 + 2 * lx;
+        if (c >= C || t >= Kp) continue;
+        const int64_t d = (int64_t)c * Kp + t;
+        __nv_bfloat16 h0, l0, h1, l1;
+        tcgemm::split2(td[2 * lx][cc], h0, l0);
+        tcgemm::split2(td[2 * lx + 1][cc], h1, l1);
+        *reinterpret_cast<__nv_bfloat162*>(PD + d) = __halves2bfloat162(h0, h1);
+        *reinterpret_cast<__nv_bfloat162*>(PD + plane + d) = __halves2bfloat162(l0, l1);
+        tcgemm::split2(tx[2 * lx][cc], h0, l0);
+        tcgemm::split2(tx[2 * lx + 1][cc], h1, l1);
+        *reinterpret_cast<__nv_bfloat162*>(PX + d) = __halves2bfloat162(h0, h1);
+        *reinterpret_cast<__nv_bfloat162*>(PX + plane + d) = __halves2bfloat162(l0, l1);
+    }
+}
+
+// D[i][j] = dXXT[perm[i]][perm[j]], zero where column perm[j] is dead (H[pj][pj] == 0)  (:72, :84)
+__global__ void __launch_bounds__(256) gather_dxxt_kernel(const float* __restrict__ dXXT, const float* __restrict__ H,
+                                                          const int64_t* __restrict__ perm, int C, float* __restrict__ D) {
+    const int i = blockIdx.y;
+    const int64_t pi = perm ? perm[i] : i;
+    for (int j = blockIdx.x * 256 + threadIdx.x; j < C; j += gridDim.x * 256) {
+        const int64_t pj = perm ? perm[j] : j;
+        const bool dead = H[pj * C + pj] == 0.f;
+        D[(int64_t)i * C + j] = dead ? 0.f : dXXT[pi * C + pj];
+    }
+}
+
+// T[i][k] = k > i ? alpha * T[i][k] : 0
+__global__ void __launch_bounds__(256) triu_scale_kernel(float* __restrict__ T, int C, float alpha) {
+    const int i = blockIdx.y;
+    for (int k = blockIdx.x * 256 + threadIdx.x; k < C; k += gridDim.x * 256)
+        T[(int64_t)i * C + k] = (k > i) ? __fmul_rn(alpha, T[(int64_t)i * C + k]) : 0.f;
+}
+
+struct AqArgs {
+    float* Wp;               // [R, C] working weights, permuted order
+    const float* Hinv;       // [Cp, Cp]
+    const float* P;          // [C, C]
+    float* Q;                // [R, C]
+    __nv_bfloat16 *Ehi, *Elo, *Qhi, *Qlo;   // [R][BS] operand planes of the lazy update
+    const float* scale_row; const float* zero_row;      // mode 0: [R]
+    const float* scale_tab; const float* zero_tab;      // mode 1: [ngroups, R]
+    const int* colgrp;
+    int R, C, Cp, i1, count, mode, asym;
+    float maxq;
+};
+
+// One warp per weight row; Hinv and P blocks of the current 128 columns in shared memory.
+__global__ void __launch_bounds__(kBlockThreads) aq_block_kernel(const AqArgs p) {
+    extern __shared__ float smem[];
+    float* Hs = smem;                                      // [BS][BS]
+    float* Ps = smem + BS * BS;                            // [BS][BS]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const float* Hb = p.Hinv + (int64_t)p.i1 * p.Cp + p.i1;
+    const float* Pb = p.P + (int64_t)p.i1 * p.C + p.i1;
+    for (int e = threadIdx.x; e < BS * BS; e += kBlockThreads) {
+        const int i = e >> 7, j = e & 127;
+        const bool in = i < p.count && j < p.count;
+        Hs[e] = in ? Hb[(int64_t)i * p.Cp + j] : 0.f;
+        Ps[e] = in ? Pb[(int64_t)i * p.C + j] : 0.f;
+    }
+    __syncthreads();
+    const int r = blockIdx.x * kRowsPerCta + warp;
+    if (r >= p.R) return;
+    const int64_t base = (int64_t)r * p.C + p.i1;
+    float w[4], sc[4], zr[4], qv[4], ev[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int col = lane + 32 * k;
+        const bool in = col < p.count;
+        w[k] = in ? p.Wp[base + col] : 0.f;
+        qv[k] = 0.f; ev[k] = 0.f; sc[k] = 1.f; zr[k] = 0.f;
+        if (p.mode == 0) {
+            sc[k] = p.scale_row[r];
+            if (p.asym) zr[k] = p.zero_row[r];
+        } else if (in) {
+            const int64_t gi = (int64_t)p.colgrp[p.i1 + col] * p.R + r;
+            sc[k] = p.scale_tab[gi];
+            if (p.asym) zr[k] = p.zero_tab[gi];
+        }
+    }
+#pragma unroll
+    for (int slot = 0; slot < 4; ++slot) {
+        const int ibase = slot * 32;
+        if (ibase >= p.count) break;
+        const int iend = (p.count - ibase < 32) ? p.count - ibase : 32;
+        for (int o = 0; o < iend; ++o) {
+            const int i = ibase + o;
+            const float wi = __shfl_sync(0xffffffffu, w[slot], o);
+            const float si = __shfl_sync(0xffffffffu, sc[slot], o);
+            const float zi = __shfl_sync(0xffffffffu, zr[slot], o);
+            float q;                                       // WeightQuantizer.quantize: the zero point is honoured
+            if (p.asym) {
+                float c = __fadd_rn(rintf(__fdiv_rn(wi, si)), zi);
+                c = c < 0.f ? 0.f : (c > p.maxq ? p.maxq : c);
+                q = __fmul_rn(si, __fsub_rn(c, zi));
+            } else {
+                q = __fmul_rn(si, quant_code(wi, si, -(p.maxq + 1.f), p.maxq));
+            }
+            const float err = __fdiv_rn(__fsub_rn(wi, q), Hs[i * BS + i]);
+            if (lane == o) { qv[slot] = q; ev[slot] = err; }
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int col = lane + 32 * k;
+                if (col >= i && col < p.count) {
+                    const float upd = __fsub_rn(__fmul_rn(err, Hs[i * BS + col]), __fmul_rn(wi, Ps[i * BS + col]));
+                    w[k] = __fsub_rn(w[k], upd);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int col = lane + 32 * k;
+        const bool in = col < p.count;
+        if (in) p.Q[base + col] = qv[k];
+        // the lazy update multiplies the block's working weights after the loop (W1, :146); column i of it is
+        // w_i - err_i * d_i, the quantized value up to one rounding
+        const float e = in ? ev[k] : 0.f, qq = in ? w[k] : 0.f;
+        __nv_bfloat16 h, l;
+        tcgemm::split2(e, h, l);
+        p.Ehi[(int64_t)r * BS + col] = h; p.Elo[(int64_t)r * BS + col] = l;
+        tcgemm::split2(qq, h, l);
+        p.Qhi[(int64_t)r * BS + col] = h; p.Qlo[(int64_t)r * BS + col] = l;
+    }
+}
+
+struct Layout {
+    size_t put, ppt, pe, pq, tmp1, tmp2, status, total;
+    int Cp;
+};
+static Layout layout(int R, int C) {
+    Layout L;
+    L.Cp = (C + 127) / 128 * 128;
+    auto up = [](size_t v) { return (v + 1023) / 1024 * 1024; };
+    size_t off = 0;
+    L.put = off; off = up(off + (size_t)2 * L.Cp * L.Cp * 2);          // planes of U^T
+    L.ppt = off; off = up(off + (size_t)2 * L.Cp * L.Cp * 2);          // planes of P^T
+    L.pe = off; off = up(off + (size_t)2 * R * BS * 2);
+    L.pq = off; off = up(off + (size_t)2 * R * BS * 2);
+    L.tmp1 = off; off = up(off + (size_t)C * C * 4);                   // gathered dXXT, then T
+    L.tmp2 = off; off = up(off + (size_t)C * C * 4);
+    L.status = off; off += 1024;
+    L.total = off;
+    return L;
+}
+
+}  // namespace aq
+}  // namespace rq
+
+extern "C" size_t rq_gptaq_accum_workspace_bytes(int64_t tokens, int C) {
+    if (tokens <= 0 || C <= 0) return 0;
+    const int64_t Kp = (tokens + 63) / 64 * 64;
+    return (size_t)2 * 2 * C * Kp * 2 + 2048;
+}
+
+// dXXT = beta * dXXT + (fl(x_fp * s) - fl(x * s))^T . fl(x * s) over the N tokens  (gptaq_utils.py:33-39)
+extern "C" int rq_gptaq_accum(const void* x, int x_dtype, int64_t ldx, const void* x_fp, int fp_dtype, int64_t ldf,
+                              int fp_channel_major, int64_t N, int C, float s, float beta, float* dXXT, void* workspace,
+                              size_t workspace_bytes, int* status, void* stream) {
+    using namespace rq::tcgemm;
+    if (!x || !x_fp || !dXXT || !workspace || N <= 0 || C <= 0) return RQ_ERR_INVALID;
+    if (reinterpret_cast<uintptr_t>(workspace) % 1024 != 0) return RQ_ERR_INVALID;
+    if (workspace_bytes < rq_gptaq_accum_workspace_bytes(N, C)) return RQ_ERR_WORKSPACE;
+    if ((x_dtype != RQ_F32 && x_dtype != RQ_BF16 && x_dtype != RQ_F16) ||
+        (fp_dtype != RQ_F32 && fp_dtype != RQ_BF16 && fp_dtype != RQ_F16)) return RQ_ERR_INVALID;
+    cudaStream_t st = as_stream(stream);
+    const int64_t Kp = (N + 63) / 64 * 64;
+    __nv_bfloat16* PD = reinterpret_cast<__nv_bfloat16*>(workspace);
+    __nv_bfloat16* PX = PD + (size_t)2 * C * Kp;
+    dim3 grid((unsigned)((C + 31) / 32), (unsigned)(Kp / 64));
+#define RQ_AQ_PACK(TX, TF)                                                                                          \
+    do {                                                                                                            \
+        if (fp_channel_major)                                                                                       \
+            rq::aq::diff_pack_kernel<TX, TF, true><<<grid, 256, 0, st>>>(                                           \
+                reinterpret_cast<const TX*>(x), ldx, reinterpret_cast<const TF*>(x_fp), ldf, N, C, s, PD, PX, Kp);  \
+        else                                                                                                        \
+            rq::aq::diff_pack_kernel<TX, TF, false><<<grid, 256, 0, st>>>(                                          \
+                reinterpret_cast<const TX*>(x), ldx, reinterpret_cast<const TF*>(x_fp), ldf, N, C, s, PD, PX, Kp);  \
+    } while (0)
+#define RQ_AQ_PACK_F(TX)                                                                 \
+    do {                                                                                 \
+        if (fp_dtype == RQ_F32) RQ_AQ_PACK(TX, float);                                   \
+        else if (fp_dtype == RQ_BF16) RQ_AQ_PACK(TX, __nv_bfloat16);                     \
+        else RQ_AQ_PACK(TX, __half);                                                     \
+    } while (0)
+    if (x_dtype == RQ_F32) RQ_AQ_PACK_F(float);
+    else if (x_dtype == RQ_BF16) RQ_AQ_PACK_F(__nv_bfloat16);
+    else RQ_AQ_PACK_F(__half);
+#undef RQ_AQ_PACK_F
+#undef RQ_AQ_PACK
+    int rc = check_launch();
+    if (rc != RQ_OK) return rc;
+    PlaneTensor tD{PD, Kp, C, 2}, tX{PX, Kp, C, 2};
+    Params p;
+    p.a_row0 = p.b_row0 = 0; p.a_k0 = p.b_k0 = 0; p.a_plane = p.b_plane = 0; p.a_plane_z = p.b_plane_z = 0;
+    p.a_row_z = p.b_row_z = 0;
+    p.M = C; p.N = C; p.k_len = (int)Kp; p.tri = 0; p.kmode = 0; p.batch = 1;
+    p.C = dXXT; p.ldc = C; p.c_z = 0; p.Aux = nullptr; p.ldaux = 0; p.aux_z = 0;
+    p.alpha = 1.f; p.beta = beta; p.gamma = 0.f;
+    return launch(tD, tX, p, status, st);
+}
+
+extern "C" size_t rq_gptaq_workspace_bytes(int R, int C) {
+    if (R <= 0 || C <= 0) return 0;
+    return rq::aq::layout(R, C).total + 1024;
+}
+
+// P = alpha * triu(D . Hinv^T, 1) . Hinv with D the permuted dXXT, dead columns zeroed (gptaq_utils.py:72, 84, 105).
+// H: the un-damped Hessian [C, C] (only its diagonal is read, for the dead-column test).  P: [C, C] output.
+extern "C" int rq_gptaq_terms(const float* dXXT, const float* H, const int64_t* perm, const float* Hinv, int C,
+                              float alpha, float* P, void* workspace, size_t workspace_bytes, void* stream) {
+    using namespace rq;
+    if (!dXXT || !H || !Hinv || !P || !workspace || C <= 0) return RQ_ERR_INVALID;
+    const aq::Layout L = aq::layout(1, C);
+    if (workspace_bytes < L.total) return RQ_ERR_WORKSPACE;
+    cudaStream_t st = as_stream(stream);
+    uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
+    float* D = reinterpret_cast<float*>(ws + L.tmp1);
+    float* T = reinterpret_cast<float*>(ws + L.tmp2);
+    dim3 eg((unsigned)((C + 1023) / 1024), (unsigned)C);
+    aq::gather_dxxt_kernel<<<eg, 256, 0, st>>>(dXXT, H, perm, C, D);
+    dim3 grid((unsigned)((C + gemm::TM - 1) / gemm::TM), (unsigned)((C + gemm::TN - 1) / gemm::TN), 1);
+    fq::terms_gemm_kernel<<<grid, gemm::kThreads, gemm::kSmemBytes, st>>>(D, Hinv, T, C, C, L.Cp, 1);   // D . U^T
+    aq::triu_scale_kernel<<<eg, 256, 0, st>>>(T, C, alpha);
+    fq::terms_gemm_kernel<<<grid, gemm::kThreads, gemm::kSmemBytes, st>>>(T, Hinv, P, C, C, L.Cp, 2);   // . U
+    return check_launch();
+}
+
+// The block loop of GPTAQ.fasterquant (gptaq_utils.py:107-146) for every block of the linear.  mode 0: per-row
+// scale_row / zero_row [R]; mode 1: static groups scale_tab / zero_tab [ngroups, R] indexed by colgrp [C].
+// asym != 0 honours the zero point (WeightQuantizer.quantize).  Wp is consumed; Q receives the quantized weights.
+extern "C" int rq_gptaq_run(float* Wp, const float* Hinv, const float* P, float* Q, const float* scale_row,
+                            const float* zero_row, const float* scale_tab, const float* zero_tab, const int* colgrp,
+                            int R, int C, int mode, int asym, int maxq, void* workspace, size_t workspace_bytes,
+                            int* status, void* stream) {
+    using namespace rq;
+    using namespace rq::tcgemm;
+    if (!Wp || !Hinv || !P || !Q || !workspace || R <= 0 || C <= 0 || maxq <= 0) return RQ_ERR_INVALID;
+    if (mode == 0 ? (!scale_row || (asym && !zero_row)) : (!scale_tab || !colgrp || (asym && !zero_tab)))
+        return RQ_ERR_INVALID;
+    if (mode < 0 || mode > 1) return RQ_ERR_INVALID;
+    const aq::Layout L = aq::layout(R, C);
+    if (workspace_bytes < L.total) return RQ_ERR_WORKSPACE;
+    cudaStream_t st = as_stream(stream);
+    uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
+    __nv_bfloat16* PUt = reinterpret_cast<__nv_bfloat16*>(ws + L.put);
+    __nv_bfloat16* PPt = reinterpret_cast<__nv_bfloat16*>(ws + L.ppt);
+    __nv_bfloat16* PE = reinterpret_cast<__nv_bfloat16*>(ws + L.pe);
+    __nv_bfloat16* PQ = reinterpret_cast<__nv_bfloat16*>(ws + L.pq);
+    int* tc_status = status ? status : reinterpret_cast<int*>(ws + L.status);
+    const int Cp = L.Cp;
+    {   // operand planes of U^T and P^T (rows = output columns, k = rows of the block)
+        SplitArgs a;
+        a.src = Hinv; a.ld = Cp; a.src_z = 0; a.rows = Cp; a.cols = Cp;
+        a.dst = PUt; a.Kp = Cp; a.plane_stride = (long long)Cp * Cp; a.plane = 0; a.plane_z = 0;
+        a.dst_row0 = 0; a.dst_row_z = 0; a.dst_k0 = 0; a.pad_k_to = 0;
+        int rc = split_transpose(a, 1, st);
+        if (rc != RQ_OK) return rc;
+        a.src = P; a.ld = C; a.rows = C; a.cols = C; a.dst = PPt; a.pad_k_to = Cp;
+        if (cudaMemsetAsync(PPt, 0, (size_t)2 * Cp * Cp * 2, st) != cudaSuccess) return RQ_ERR_CUDA;
+        rc = split_transpose(a, 1, st);
+        if (rc != RQ_OK) return rc;
+    }
+    const size_t smem = (size_t)2 * fq::BS * fq::BS * sizeof(float);
+    if (cudaFuncSetAttribute(aq::aq_block_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+        return RQ_ERR_CUDA;
+    PlaneTensor tE{PE, fq::BS, R, 2}, tQ{PQ, fq::BS, R, 2}, tUt{PUt, Cp, Cp, 2}, tPt{PPt, Cp, Cp, 2};
+    for (int i1 = 0; i1 < C; i1 += fq::BS) {
+        const int count = (C - i1 < fq::BS) ? C - i1 : fq::BS;
+        const int i2 = i1 + count;
+        aq::AqArgs p;
+        p.Wp = Wp; p.Hinv = Hinv; p.P = P; p.Q = Q;
+        p.Ehi = PE; p.Elo = PE + (size_t)R * fq::BS; p.Qhi = PQ; p.Qlo = PQ + (size_t)R * fq::BS;
+        p.scale_row = scale_row; p.zero_row = zero_row; p.scale_tab = scale_tab; p.zero_tab = zero_tab;
+        p.colgrp = colgrp; p.R = R; p.C = C; p.Cp = Cp; p.i1 = i1; p.count = count; p.mode = mode; p.asym = asym;
+        p.maxq = (float)maxq;
+        {
+            prof::Scope timed(RQ_PROF_BLOCK, st);
+            aq::aq_block_kernel<<<(R + fq::kRowsPerCta - 1) / fq::kRowsPerCta, fq::kBlockThreads, smem, st>>>(p);
+        }
+        int rc = check_launch();
+        if (rc != RQ_OK) return rc;
+        if (i2 >= C) break;
+        prof::Scope timed(RQ_PROF_LAZY, st);
+        Params g;
+        g.a_row0 = 0; g.a_k0 = 0; g.a_plane = 0; g.a_plane_z = 0; g.a_row_z = 0;
+        g.b_row0 = i2; g.b_k0 = i1; g.b_plane = 0; g.b_plane_z = 0; g.b_row_z = 0;
+        g.M = R; g.N = C - i2; g.k_len = fq::BS; g.tri = 0; g.kmode = 0; g.batch = 1;
+        g.C = Wp + i2; g.ldc = C; g.c_z = 0; g.Aux = nullptr; g.ldaux = 0; g.aux_z = 0;
+        g.alpha = -1.f; g.beta = 1.f; g.gamma = 0.f;
+        rc = launch(tE, tUt, g, tc_status, st);                     // W[:, i2:] -= Err1 . Hinv[i1:i2, i2:]
+        if (rc != RQ_OK) return rc;
+        g.alpha = 1.f;
+        rc = launch(tQ, tPt, g, tc_status, st);                     // W[:, i2:] += Q1 . P[i1:i2, i2:]
+        if (rc != RQ_OK) return rc;
+    }
+    return RQ_OK;
+}

@@ -442,6 +442,69 @@ def plain_fasterquant(obj, H, blocksize, percdamp, groupsize, actorder, static_g
 
 
 # ----------------------------------------------------------------------------------------------
+# GPTAQ (gptq_utils/gptaq_utils.py:43-167)
+# ----------------------------------------------------------------------------------------------
+@torch.no_grad()
+def gptaq_fasterquant(obj, H, blocksize, percdamp, groupsize, actorder, static_groups, alpha):
+    layer, dev = obj.layer, obj.dev
+    W32 = layer.weight.data.float().contiguous()
+    R, Cc = W32.shape
+    quantizer = obj.quantizer
+    if not quantizer.ready():
+        quantizer.find_params(W32)
+    _check_common(quantizer, blocksize)
+    if groupsize != -1 and not static_groups:
+        raise NotImplementedError("GPTAQ with dynamic weight groups is not built (per-row and static groups are)")
+    if bool((H == 0).all()):                                    # no calibration data: round to nearest
+        H = torch.eye(Cc, device=dev)
+    H3 = H.reshape(1, Cc, Cc).contiguous()
+    diag = torch.diagonal(H3[0])
+    dead = diag == 0
+    perm = None
+    if actorder:
+        key = torch.where(dead, torch.ones_like(diag), diag)
+        perm = torch.argsort(key, descending=True)
+    maxq = int(quantizer.maxq)
+    asym = 0 if quantizer.sym else 1
+    scale_row = zero_row = scale_tab = zero_tab = colgrp = None
+    if groupsize == -1:
+        mode = 0
+        scale_row = quantizer.scale.to(dev, torch.float32).reshape(-1).contiguous()
+        zero_row = quantizer.zero.to(dev, torch.float32).reshape(-1).contiguous()
+    else:
+        mode = 1
+        Wz = W32.clone()
+        Wz[:, dead] = 0                                          # the groups are ranged after dead-zeroing (:70-78)
+        scale_tab, zero_tab = quant_utils.find_params_groups(Wz, groupsize, maxq, quantizer.sym, quantizer.mse,
+                                                             quantizer.norm, quantizer.grid, quantizer.maxshrink)
+        cols = perm if perm is not None else torch.arange(Cc, device=dev)
+        colgrp = (cols // groupsize).to(torch.int32).contiguous()
+    Hinv, _, _ = hinv_with_fallback(H3, perm, percdamp, identity_fallback=False)
+    st = _lib.stream_of(W32)
+    Wp = torch.empty(R, Cc, dtype=torch.float32, device=dev)
+    Q = torch.empty(R, Cc, dtype=torch.float32, device=dev)
+    P = torch.empty(Cc, Cc, dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        _lib.check("rq_fq_prepare", _lib.lib.rq_fq_prepare(_lib.ptr(W32), 0, _lib.ptr(H3), _lib.ptr(perm), R, Cc, 1,
+                                                           _lib.ptr(Wp), 0, st))
+        need = _lib.lib.rq_gptaq_workspace_bytes(R, Cc)
+        ws = ops._workspace(dev, need + 1024, key="gptaq")
+        base = (ws.data_ptr() + 1023) // 1024 * 1024
+        _lib.check("rq_gptaq_terms", _lib.lib.rq_gptaq_terms(_lib.ptr(obj.dXXT), _lib.ptr(H3), _lib.ptr(perm),
+                                                             _lib.ptr(Hinv), Cc, float(alpha), _lib.ptr(P), base, need,
+                                                             st))
+        _lib.check("rq_gptaq_run", _lib.lib.rq_gptaq_run(_lib.ptr(Wp), _lib.ptr(Hinv), _lib.ptr(P), _lib.ptr(Q),
+                                                         _lib.ptr(scale_row), _lib.ptr(zero_row), _lib.ptr(scale_tab),
+                                                         _lib.ptr(zero_tab), _lib.ptr(colgrp), R, Cc, mode, asym, maxq,
+                                                         base, need, _lib.ptr(ops.status_word(dev)), st))
+        out = torch.empty(layer.weight.shape, dtype=layer.weight.dtype, device=dev)
+        _lib.check("rq_fq_finish", _lib.lib.rq_fq_finish(_lib.ptr(Q), 0, _lib.ptr(perm), R, Cc, _lib.ptr(out),
+                                                         _lib.dtype_code(out), 0, 0, 0, 0, 0, 0, st))
+    layer.weight.data = out
+    obj._last_fasterquant = {"perm": perm, "P": P if KEEP_INTERMEDIATES else None}
+
+
+# ----------------------------------------------------------------------------------------------
 # GPTQ+ (gptq_utils/gptq_plus_utils.py:910-1896)
 # ----------------------------------------------------------------------------------------------
 @torch.no_grad()

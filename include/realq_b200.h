@@ -274,6 +274,30 @@ int rq_fq_finish(const float* Q, const int8_t* codes, const int64_t* perm, int R
                  float* out_codes, float* out_scale, const float* scale_row, const float* scale_tab,
                  const int* colgrp, int permute_export, void* stream);
 
+/* ------------------------------------------------------------------------------------------
+ * GPTAQ (gptq_utils/gptaq_utils.py), the asymmetric-calibration sibling of GPTQ, on the same kernels.
+ * rq_gptaq_accum replaces the dXXT update of GPTAQ.add_batch (:33-39):
+ *     dXXT = beta * dXXT + (fl(x_fp * s) - fl(x * s))^T . fl(x * s)        (s = sqrt(2 / nsamples), beta = n_old / n_new)
+ * x: [N, C] of its dtype (row stride ldx); x_fp: [N, C] (row stride ldf) or, with fp_channel_major != 0, [C, N] with
+ * row stride ldf as the reference's input cache stores it (:185-189); dXXT [C, C] fp32, not symmetric; the product
+ * runs as a split-bf16 tcgen05 GEMM over the tokens.  rq_gptaq_terms replaces :72, :84 and :105:
+ *     P = alpha * triu(D . Hinv^T, 1) . Hinv,  D = dXXT[perm][:, perm] with the dead columns (H[j][j] == 0) zeroed.
+ * rq_gptaq_run replaces the block loop (:107-146): per column  q = quantize(w) (zero point honoured when asym),
+ * err = (w - q) / Hinv[i,i],  W1[:, i:] -= err (x) Hinv[i, i:] - w (x) P[i, i:];  per block
+ * W[:, i2:] -= Err1 . Hinv[i1:i2, i2:] - W1 . P[i1:i2, i2:].  mode 0: scale_row / zero_row [R]; mode 1: static groups
+ * scale_tab / zero_tab [ngroups, R] indexed by colgrp [C].  Wp (permuted working weights) is consumed, Q receives the
+ * quantized weights in permuted order (rq_fq_finish un-permutes).  Workspaces: 1024-byte aligned device memory. */
+size_t rq_gptaq_accum_workspace_bytes(int64_t tokens, int C);
+int rq_gptaq_accum(const void* x, int x_dtype, int64_t ldx, const void* x_fp, int fp_dtype, int64_t ldf,
+                   int fp_channel_major, int64_t N, int C, float s, float beta, float* dXXT, void* workspace,
+                   size_t workspace_bytes, int* status, void* stream);
+size_t rq_gptaq_workspace_bytes(int R, int C);
+int rq_gptaq_terms(const float* dXXT, const float* H, const int64_t* perm, const float* Hinv, int C, float alpha,
+                   float* P, void* workspace, size_t workspace_bytes, void* stream);
+int rq_gptaq_run(float* Wp, const float* Hinv, const float* P, float* Q, const float* scale_row, const float* zero_row,
+                 const float* scale_tab, const float* zero_tab, const int* colgrp, int R, int C, int mode, int asym,
+                 int maxq, void* workspace, size_t workspace_bytes, int* status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

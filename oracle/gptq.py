@@ -14,6 +14,7 @@ Test infrastructure (see ``oracle/__init__.py``).  Restates
 from __future__ import annotations
 
 import copy
+import math
 
 import torch
 
@@ -379,3 +380,91 @@ def guided_fasterquant(weight, H_ccg, act_square, quantizer, num_groups, blocksi
     if any(st["identity"] for st in out["states"]):
         raise ValueError("Quantization: `damp_percent` must between 0 and 1.")
     return out
+
+
+# --------------------------------------------------------------------------------------
+# GPTAQ
+# --------------------------------------------------------------------------------------
+class AsymCalibState:
+    """H and dXXT of GPTAQ.add_batch (gptaq_utils.py:14-41): running means over sequences of (2/n) X^T X and
+    (2/n) (X_fp - X)^T X."""
+
+    def __init__(self, columns):
+        self.H = torch.zeros(columns, columns)
+        self.dXXT = torch.zeros(columns, columns)
+        self.nsamples = 0
+
+    def add_batch(self, inp, fp_inp):
+        if inp.dim() == 2:
+            inp = inp.unsqueeze(0)
+        tmp = inp.shape[0]
+        inp = inp.reshape(-1, inp.shape[-1]).t()
+        self.H *= self.nsamples / (self.nsamples + tmp)
+        self.dXXT *= self.nsamples / (self.nsamples + tmp)
+        self.nsamples += tmp
+        inp = math.sqrt(2 / self.nsamples) * inp.float()
+        self.H += inp.matmul(inp.t())
+        dX = fp_inp.float() * math.sqrt(2 / self.nsamples) - inp       # fp_inp: [C, tokens]
+        self.dXXT += dX.matmul(inp.t())
+
+
+def gptaq_fasterquant(weight, H, dXXT, quantizer, blocksize=128, percdamp=0.01, groupsize=-1, actorder=False,
+                      static_groups=False, alpha=0.25):
+    """GPTAQ.fasterquant (gptaq_utils.py:43-167) for per-row and static-group scales: dict(Q, perm, P)."""
+    W = weight.clone().float()
+    columns = W.shape[1]
+    if not quantizer.ready():
+        quantizer.find_params(W)
+    H = H.clone()
+    dXXT = dXXT.clone()
+    if (H == 0).all():
+        H = torch.eye(columns)
+    dead = torch.diag(H) == 0
+    H[dead, dead] = 1
+    W[:, dead] = 0
+    dXXT[:, dead] = 0
+    groups = None
+    if static_groups:
+        groups = []
+        for i in range(0, columns, groupsize):
+            q = copy.deepcopy(quantizer)
+            q.find_params(W[:, i:(i + groupsize)])
+            groups.append(q)
+    perm = invperm = None
+    if actorder:
+        perm = torch.argsort(torch.diag(H), descending=True)
+        W = W[:, perm]
+        H = H[perm][:, perm]
+        dXXT = dXXT[perm][:, perm]
+        invperm = torch.argsort(perm)
+    Q = torch.zeros_like(W)
+    Hinv = plain_hinv(H, percdamp)
+    P = alpha * ((dXXT @ Hinv.T).triu_(diagonal=1)) @ Hinv
+    for i1 in range(0, columns, blocksize):
+        i2 = min(i1 + blocksize, columns)
+        count = i2 - i1
+        W1 = W[:, i1:i2].clone()
+        Q1 = torch.zeros_like(W1)
+        Err1 = torch.zeros_like(W1)
+        Hinv1 = Hinv[i1:i2, i1:i2]
+        P1 = P[i1:i2, i1:i2]
+        for i in range(count):
+            w = W1[:, i]
+            d = Hinv1[i, i]
+            qz = quantizer
+            if groupsize != -1:
+                assert static_groups, "dynamic groups are not restated"
+                idx = i1 + i
+                if actorder:
+                    idx = perm[idx]
+                qz = groups[idx // groupsize]
+            q = qz.quantize(w.unsqueeze(1)).flatten()
+            Q1[:, i] = q
+            err1 = (w - q) / d
+            W1[:, i:] -= err1.unsqueeze(1).matmul(Hinv1[i, i:].unsqueeze(0)) - w.unsqueeze(1).matmul(P1[i, i:].unsqueeze(0))
+            Err1[:, i] = err1
+        Q[:, i1:i2] = Q1
+        W[:, i2:] -= Err1.matmul(Hinv[i1:i2, i2:]) - W1.matmul(P[i1:i2, i2:])
+    if actorder:
+        Q = Q[:, invperm]
+    return {"Q": Q, "perm": perm, "P": P}

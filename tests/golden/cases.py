@@ -93,6 +93,20 @@ def make_out_grad(batch, seq, hidden, seed):
     return torch.randn(batch, seq, hidden, generator=g) * torch.exp(2.0 * torch.randn(batch, seq, 1, generator=g)) * 1e-3
 
 
+GPTAQ_CASES = [
+    # name, rows, cols, nseq, seqlen, bits, sym, groupsize, actorder, static, alpha
+    ("gptaq_pc_sym_act", 32, 256, 4, 96, 4, True, -1, True, False, 0.25),
+    ("gptaq_pc_asym_noact", 24, 256, 3, 80, 4, False, -1, False, False, 0.25),
+    ("gptaq_g128_static_act", 32, 384, 4, 96, 4, True, 128, True, True, 0.5),
+]
+
+
+def make_fp_acts(X, seed):
+    """Full-precision inputs of GPTAQ: the quantized-path activations plus a few per cent of deviation."""
+    g = torch.Generator().manual_seed(seed)
+    return X + 0.05 * X.abs().mean() * torch.randn(X.shape, generator=g)
+
+
 GUIDED_CASES = [
     # name, rows, cols, nseq, seqlen, G, bits, groupsize, actorder, static
     ("guided_pc_act", 32, 256, 4, 96, 4, 4, -1, True, False),

@@ -38,10 +38,10 @@ def import_reference(ref_root: str):
             sys.modules[name] = mod
     sys.path.insert(0, ref_root)
     from utils import quant_utils, hadamard_utils, memory_utils
-    from gptq_utils import gptq_utils, gptq_plus_utils, gptq_guided_utils
+    from gptq_utils import gptq_utils, gptq_plus_utils, gptq_guided_utils, gptaq_utils
     torch.cuda.synchronize = lambda *a, **k: None
     memory_utils.cleanup_memory = lambda *a, **k: None
-    return quant_utils, hadamard_utils, gptq_utils, gptq_plus_utils, gptq_guided_utils
+    return quant_utils, hadamard_utils, gptq_utils, gptq_plus_utils, gptq_guided_utils, gptaq_utils
 
 
 # cases whose full Hessian / inverse factor is stored (the rest keep only the small outputs)
@@ -116,6 +116,25 @@ def gen_guided(qu, gg, out):
         out[f"{name}.Q"] = np32(layer.weight.data)
         out[f"{name}.W_int"] = np32(layer.int_weight).astype(np.int8)
         out[f"{name}.Scale"] = np32(layer.scale)
+
+
+def gen_gptaq(qu, ga, out):
+    for (name, rows, cols, nseq, seqlen, bits, sym, gs, act, static, alpha) in cases.GPTAQ_CASES:
+        W = cases.make_weight(rows, cols, seed=71)
+        X = cases.make_acts(nseq, seqlen, cols, seed=71)
+        Xfp = cases.make_fp_acts(X, seed=72)
+        layer = _Lin(W)
+        g = ga.GPTAQ(layer)
+        g.quantizer = qu.WeightQuantizer()
+        g.quantizer.configure(bits, perchannel=True, sym=sym, mse=False)
+        for s_ in range(nseq):
+            g.fp_inp.append(Xfp[s_].t().contiguous())              # [C, tokens], as FPInputsCache stores it
+            g.add_batch(X[s_:s_ + 1], None)
+        out[f"{name}.digest"] = np.array(cases.digest(W, X, Xfp))
+        out[f"{name}.dXXT"] = np32(g.dXXT)
+        out[f"{name}.H_diag"] = np32(torch.diag(g.H))
+        g.fasterquant(blocksize=128, percdamp=0.01, groupsize=gs, actorder=act, static_groups=static, alpha=alpha)
+        out[f"{name}.Q"] = np32(layer.weight.data)
 
 
 def gen_act_quant(qu, out):
@@ -256,7 +275,7 @@ def main():
     ap.add_argument("--ref", default="/root/reference")
     args = ap.parse_args()
     torch.set_num_threads(1)                        # fixed reduction order on any host
-    qu, hu, gu, gpu, gg = import_reference(args.ref)
+    qu, hu, gu, gpu, gg, ga = import_reference(args.ref)
     for fname, fn, mods in (("quantizer.npz", gen_quantizer, (qu,)),
                             ("hadamard.npz", gen_hadamard, (hu,)),
                             ("plain_gptq.npz", gen_plain, (qu, gu)),
@@ -265,7 +284,8 @@ def main():
                             ("clip.npz", gen_clip, (qu, gpu)),
                             ("saliency.npz", gen_saliency, (gpu,)),
                             ("act_quant.npz", gen_act_quant, (qu,)),
-                            ("guided.npz", gen_guided, (qu, gg))):
+                            ("guided.npz", gen_guided, (qu, gg)),
+                            ("gptaq.npz", gen_gptaq, (qu, ga))):
         out = {}
         with torch.no_grad():
             fn(*mods, out)

@@ -412,3 +412,40 @@ def test_gptq_guided_vs_reference(golden, case):
     assert frac2 < 0.01 and all(d == 1.0 for d in first2)
     obj.free()
     assert obj.H is None
+
+
+@pytest.mark.parametrize("case", cases.GPTAQ_CASES, ids=lambda c: c[0])
+def test_gptaq_vs_reference(golden, case):
+    """GPTAQ on the device: dXXT against the reference's, quantized weights against the reference's and against
+    the oracle run on the statistics the device accumulated."""
+    from gptq_plus_mp_quant_b200.gptq_utils.gptaq_utils import GPTAQ
+    from gptq_plus_mp_quant_b200.utils.quant_utils import WeightQuantizer
+    (name, rows, cols, nseq, seqlen, bits, sym, gs, act, static, alpha) = case
+    g = golden("gptaq.npz")
+    W = cases.make_weight(rows, cols, seed=71)
+    X = cases.make_acts(nseq, seqlen, cols, seed=71)
+    Xfp = cases.make_fp_acts(X, seed=72)
+    layer = _layer(W)
+    obj = GPTAQ(layer)
+    obj.quantizer = WeightQuantizer()
+    obj.quantizer.configure(bits, perchannel=True, sym=sym, mse=False)
+    for s_ in range(nseq):
+        obj.fp_inp.append(Xfp[s_].t().contiguous())                # [C, tokens] on the CPU, as the reference queues it
+        obj.add_batch(X[s_:s_ + 1].to(DEV), None)
+    assert obj.fp_inp == []
+    assert rel_fro(obj.dXXT, torch.from_numpy(g[f"{name}.dXXT"])) < 3e-5
+    assert torch.allclose(torch.diag(obj.H).cpu(), torch.from_numpy(g[f"{name}.H_diag"]), rtol=1e-5)
+    H_dev, d_dev = obj.H.clone().cpu(), obj.dXXT.clone().cpu()
+    obj.fasterquant(blocksize=128, percdamp=0.01, groupsize=gs, actorder=act, static_groups=static, alpha=alpha)
+    got = layer.weight.data.cpu()
+    ref = torch.from_numpy(g[f"{name}.Q"])
+    frac = float((got != ref).float().mean())
+    q = oq.OracleWeightQuantizer()
+    q.configure(bits, perchannel=True, sym=sym, mse=False)
+    o = ogptq.gptaq_fasterquant(W, H_dev, d_dev, q, groupsize=gs, actorder=act, static_groups=static, alpha=alpha)
+    frac2 = float((got != o["Q"]).float().mean())
+    print(f"{name}: {frac * 100:.4f}% of the quantized weights differ from the reference, {frac2 * 100:.4f}% from the "
+          "oracle on the device's statistics")
+    assert frac < 0.02 and frac2 < 0.01
+    # differing entries are one quantization step away in the row where the first tie flipped, never garbage
+    assert float((got - ref).abs().max()) < 16 * float(ref.abs().max()) / (2 ** bits)

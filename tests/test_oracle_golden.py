@@ -246,3 +246,23 @@ def test_gptq_guided(golden, case):
     assert torch.equal(out["W_int"], t(g[f"{name}.W_int"]).float())
     assert torch.equal(out["Scale"], t(g[f"{name}.Scale"]))
     assert torch.equal(out["Q"], t(g[f"{name}.Q"]))
+
+
+@pytest.mark.parametrize("case", cases.GPTAQ_CASES, ids=lambda c: c[0])
+def test_gptaq(golden, case):
+    """GPTAQ: H / dXXT accumulation from queued full-precision inputs and the block loop with the P term."""
+    (name, rows, cols, nseq, seqlen, bits, sym, gs, act, static, alpha) = case
+    g = golden("gptaq.npz")
+    W = cases.make_weight(rows, cols, seed=71)
+    X = cases.make_acts(nseq, seqlen, cols, seed=71)
+    Xfp = cases.make_fp_acts(X, seed=72)
+    assert cases.digest(W, X, Xfp) == str(g[f"{name}.digest"])
+    st = ogptq.AsymCalibState(cols)
+    for s_ in range(nseq):
+        st.add_batch(X[s_:s_ + 1], Xfp[s_].t().contiguous())
+    assert torch.equal(st.dXXT, t(g[f"{name}.dXXT"]))
+    assert torch.equal(torch.diag(st.H), t(g[f"{name}.H_diag"]))
+    q = oq.OracleWeightQuantizer()
+    q.configure(bits, perchannel=True, sym=sym, mse=False)
+    out = ogptq.gptaq_fasterquant(W, st.H, st.dXXT, q, groupsize=gs, actorder=act, static_groups=static, alpha=alpha)
+    assert torch.equal(out["Q"], t(g[f"{name}.Q"]))
