@@ -285,3 +285,100 @@ extern "C" int rq_fwht(const void* x, void* y, int dtype, int64_t rows, int n, i
 #undef RQ_FWHT_LAUNCH
     return check_launch();
 }
+
+// ------------------------------------------------------------------------------------------
+// Hadamard transform ACROSS the heads of an attention output (the online partial rotation in front of o_proj,
+// utils/quant_utils.py:258-281): x viewed [tokens, H, D]; for every token and every position d inside a head
+//     y[t][h'][d] = scale * sum_h Had_H[h'][h] * x[t][h][d].
+// One thread owns a (token, d) pair and holds the H values in registers: the loads and stores of a warp are
+// contiguous along d, the transform needs no shared memory.  H = K * 2^m, K * 2^m <= 64; hadK as in rq_fwht.
+// ------------------------------------------------------------------------------------------
+namespace rq {
+namespace fwht {
+
+template <typename T, int HMAX>
+__global__ void __launch_bounds__(256) heads_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t tokens, int H,
+                                                    int D, int K, const float* __restrict__ hadK, float scale) {
+    __shared__ float hk[kMaxK * kMaxK];
+    if (K > 1)
+        for (int e = threadIdx.x; e < K * K; e += blockDim.x) hk[e] = hadK[e];
+    __syncthreads();
+    const int P = H / K;                                   // power-of-two part, contiguous inside each of the K chunks
+    const int64_t total = tokens * D;
+    for (int64_t u = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; u < total; u += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t t = u / D;
+        const int d = (int)(u - t * D);
+        const T* px = x + t * (int64_t)H * D + d;
+        float v[HMAX];
+#pragma unroll
+        for (int h = 0; h < HMAX; ++h) v[h] = (h < H) ? load_as_float<T>(px, (int64_t)h * D) : 0.f;
+#pragma unroll
+        for (int len = 1; len < HMAX; len <<= 1) {
+            if (len < P) {
+#pragma unroll
+                for (int h = 0; h < HMAX; ++h) {
+                    if ((h & len) == 0 && h + len < HMAX) {
+                        const float a = v[h], b = v[h + len];
+                        v[h] = a + b;
+                        v[h + len] = a - b;
+                    }
+                }
+            }
+        }
+        T* py = y + t * (int64_t)H * D + d;
+        if (K == 1) {
+#pragma unroll
+            for (int h = 0; h < HMAX; ++h)
+                if (h < H) store_from_float<T>(py, (int64_t)h * D, v[h] * scale);
+        } else {
+            // chunk k' = sum_k hadK[k'][k] * chunk k, position by position
+            for (int ko = 0; ko < K; ++ko) {
+                for (int pp = 0; pp < P; ++pp) {
+                    float s = 0.f;
+                    for (int k = 0; k < K; ++k) {
+                        float val = 0.f;
+#pragma unroll
+                        for (int h = 0; h < HMAX; ++h)
+                            if (h == k * P + pp) val = v[h];
+                        s = fmaf(hk[ko * K + k], val, s);
+                    }
+                    store_from_float<T>(py, (int64_t)(ko * P + pp) * D, s * scale);
+                }
+            }
+        }
+    }
+}
+
+}  // namespace fwht
+}  // namespace rq
+
+extern "C" int rq_fwht_heads(const void* x, void* y, int dtype, int64_t tokens, int H, int D, int K, const float* hadK,
+                             float scale, void* stream) {
+    using namespace rq::fwht;
+    if (!x || !y || tokens < 0 || H <= 0 || D <= 0 || K <= 0 || H % K != 0 || H > 64) return RQ_ERR_INVALID;
+    if (K > 1 && !hadK) return RQ_ERR_INVALID;
+    if (K > kMaxK) return RQ_ERR_UNSUPPORTED;
+    const int P = H / K;
+    if ((P & (P - 1)) != 0) return RQ_ERR_INVALID;
+    if (K > 1 && x == y) return RQ_ERR_INVALID;            // the K x K mix is not done in place
+    if (tokens == 0) return RQ_OK;
+    cudaStream_t st = as_stream(stream);
+    prof::Scope timed(RQ_PROF_FWHT, st);
+    int64_t blocks = (tokens * D + 255) / 256;
+    if (blocks > 148 * 32) blocks = 148 * 32;
+#define RQ_HEADS(T)                                                                                              \
+    do {                                                                                                         \
+        if (H <= 32)                                                                                             \
+            heads_kernel<T, 32><<<(unsigned)blocks, 256, 0, st>>>(reinterpret_cast<const T*>(x),                 \
+                                                                  reinterpret_cast<T*>(y), tokens, H, D, K, hadK, scale); \
+        else                                                                                                     \
+            heads_kernel<T, 64><<<(unsigned)blocks, 256, 0, st>>>(reinterpret_cast<const T*>(x),                 \
+                                                                  reinterpret_cast<T*>(y), tokens, H, D, K, hadK, scale); \
+    } while (0)
+    if (dtype == RQ_F32) RQ_HEADS(float);
+    else if (dtype == RQ_BF16) RQ_HEADS(__nv_bfloat16);
+    else if (dtype == RQ_F16) RQ_HEADS(__half);
+    else return RQ_ERR_INVALID;
+#undef RQ_HEADS
+    return check_launch();
+}

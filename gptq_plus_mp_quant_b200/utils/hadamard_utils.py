@@ -141,6 +141,24 @@ def fwht(x: torch.Tensor, hadK=None, K: int = 1, scale: float = 1.0, out: torch.
     return out.view(x.shape)
 
 
+def fwht_heads(x: torch.Tensor, heads: int, head_dim: int, hadK=None, K: int = 1, scale: float = 1.0) -> torch.Tensor:
+    """Hadamard transform across the ``heads`` of ``x[..., heads * head_dim]`` for every position inside a head (the
+    online partial rotation of utils/quant_utils.py:258-281), times ``scale``.  ``K == 1``: Sylvester order;
+    otherwise ``hadK`` [K, K] mixes the ``heads / K``-long power-of-two chunks (``K == heads``: a dense matrix)."""
+    _lib.require_cuda(x)
+    assert x.shape[-1] == heads * head_dim
+    xc = x.contiguous()
+    out = torch.empty_like(xc)
+    hk = None
+    if K > 1:
+        hk = _hadK_on(x.device, hadK)
+    with torch.cuda.device(x.device):
+        rc = _lib.lib.rq_fwht_heads(_lib.ptr(xc), _lib.ptr(out), _lib.dtype_code(xc), xc.numel() // (heads * head_dim),
+                                    int(heads), int(head_dim), int(K), _lib.ptr(hk), float(scale), _lib.stream_of(xc))
+    _lib.check("rq_fwht_heads", rc)
+    return out
+
+
 class HadamardTransform(torch.autograd.Function):
     """The unnormalised Hadamard transform over the last (power-of-two) dim; its own adjoint
     (hadamard_utils.py:89-98)."""

@@ -237,7 +237,16 @@ class ActQuantWrapper(torch.nn.Module):
             else:
                 x = hadamard_utils.matmul_hadU_cuda(x, self.had_K, self.K)
         elif self.online_partial_had:
-            raise NotImplementedError("the per-head partial Hadamard of the attention output is not built")
+            import math
+            heads = x.shape[-1] // self.had_dim
+            if self.fp32_had:
+                x = x.float()
+            if self.K == 1:
+                x = hadamard_utils.fwht_heads(x, heads, self.had_dim, None, 1, 1.0 / math.sqrt(heads))
+            else:                                           # dense had_K [heads, heads] applied across the heads
+                x = hadamard_utils.fwht_heads(x, heads, self.had_dim, self.had_K, heads, 1.0 / math.sqrt(heads))
+            if self.fp32_had:
+                x = x.to(x_dtype)
         if self.quantizer.bits < 16:
             x = self.quantizer.fake_quant(x).to(x_dtype)
         x = (self.module(x, R1, R2, transpose) if R1 is not None else self.module(x)).to(x_dtype)

@@ -127,6 +127,14 @@ int rq_hessian_finalize(float* H, float* act_sq, int C, int G, float div_tokens,
 int rq_fwht(const void* x, void* y, int dtype, int64_t rows, int n, int K, const float* hadK, float scale,
             void* stream);
 
+/* rq_fwht_heads replaces the online partial rotation in front of o_proj (utils/quant_utils.py:258-281): x viewed
+ * [tokens, H, D] (H heads of width D); y[t][h'][d] = scale * sum_h Had[h'][h] * x[t][h][d], i.e. the transform runs
+ * ACROSS the heads for every position inside a head.  K == 1: H a power of two, Sylvester order (the reference's
+ * HadamardTransform on the transposed view); K > 1: H = K * 2^m with the K x K matrix hadK mixing the 2^m-chunks
+ * (K = H, m = 0 is the reference's dense had_K @ x).  H <= 64; in place allowed when K == 1. */
+int rq_fwht_heads(const void* x, void* y, int dtype, int64_t tokens, int H, int D, int K, const float* hadK,
+                  float scale, void* stream);
+
 /* ------------------------------------------------------------------------------------------
  * Weight quantizer.
  * rq_find_params replaces WeightQuantizer.find_params (utils/quant_utils.py:390-457), and, with

@@ -434,3 +434,37 @@ def test_act_quant_wrapper_rotates_and_quantizes():
     xr = hu.matmul_hadU_cuda(x, wrap.had_K, wrap.K)
     xq = oq.act_fake_quant(xr.cpu(), 4, -1, False, 0.9).to(DEV)
     assert torch.equal(y, lin(xq))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("heads,head_dim,dtype", [(32, 128, torch.bfloat16), (8, 64, torch.float16), (64, 32, torch.float32)])
+def test_fwht_across_heads(heads, head_dim, dtype):
+    """The online partial rotation: Hadamard across the heads for every position inside a head, against the
+    reference's formula evaluated in fp64 (one rounding of the I/O dtype)."""
+    from gptq_plus_mp_quant_b200.utils import hadamard_utils as hu
+    x = cases.make_act_tensor((2, 5, heads * head_dim), seed=31).to(dtype)
+    y = hu.fwht_heads(x.to(DEV), heads, head_dim, None, 1, 1.0 / heads ** 0.5)
+    v = x.double().reshape(-1, heads, head_dim).transpose(1, 2)               # [.., D, H]: transform the last dim
+    ref = (ohad.fwht_pow2(v.reshape(-1, heads)).reshape(v.shape) / heads ** 0.5).transpose(1, 2).reshape(x.shape)
+    assert y.dtype == dtype and y.shape == x.shape
+    tol = {torch.float32: 2e-6, torch.float16: 1.5e-3, torch.bfloat16: 1.2e-2}[dtype]
+    assert float((y.cpu().double() - ref).abs().max() / ref.abs().max()) < tol
+    # dense K x K matrix across the heads (the K != 1 branch): the Sylvester matrix itself must give the same
+    if heads <= 32:
+        Hm = ohad.fwht_pow2(torch.eye(heads, dtype=torch.float64)).float()
+        y2 = hu.fwht_heads(x.to(DEV), heads, head_dim, Hm, heads, 1.0 / heads ** 0.5)
+        assert float((y2.cpu().double() - ref).abs().max() / ref.abs().max()) < tol
+
+
+@pytest.mark.gpu
+def test_act_quant_wrapper_partial_rotation():
+    from gptq_plus_mp_quant_b200.utils.quant_utils import ActQuantWrapper
+    torch.manual_seed(1)
+    lin = torch.nn.Linear(512, 32, bias=False, device=DEV, dtype=torch.bfloat16)
+    wrap = ActQuantWrapper(lin)
+    wrap.online_partial_had, wrap.had_dim, wrap.K = True, 64, 1
+    x = cases.make_act_tensor((1, 7, 512), seed=37).bfloat16().to(DEV)
+    y = wrap(x)
+    v = x.float().reshape(-1, 8, 64).transpose(1, 2)
+    xr = (ohad.fwht_pow2(v.cpu().double().reshape(-1, 8)).reshape(v.shape) / 8 ** 0.5).transpose(1, 2).reshape(x.shape)
+    assert torch.allclose(y.float().cpu(), lin(xr.to(DEV).bfloat16()).float().cpu(), rtol=0.05, atol=0.05)
