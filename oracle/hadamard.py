@@ -98,3 +98,22 @@ def rotate_strided(x: torch.Tensor, hadK: torch.Tensor | None, K: int) -> torch.
     if K > 1:
         src = hadK.view(1, K, K).to(src) @ src
     return src.view(x.shape) / torch.tensor(n).sqrt()
+
+
+def qk_rotate_quant(q, k, k_bits=16, k_groupsize=-1, k_sym=False, k_clip_ratio=1.0):
+    """QKRotationWrapper.forward after the wrapped function (utils/rotation_utils.py:231-260): head-dim Hadamard of
+    q and k in fp32, then token-wise or head-wise fake quantization of k."""
+    import math
+    from .quantizer import act_fake_quant
+    dtype = q.dtype
+    q = (fwht_pow2(q.float()).reshape(q.shape) / math.sqrt(q.shape[-1])).to(dtype)
+    k = (fwht_pow2(k.float()).reshape(k.shape) / math.sqrt(k.shape[-1])).to(dtype)
+    if k_bits >= 16:
+        return q, k
+    bsz, num_heads, seq_len, head_dim = k.shape
+    if k_groupsize == -1:
+        tok = k.transpose(1, 2).reshape(-1, num_heads * head_dim)
+        k = act_fake_quant(tok, k_bits, -1, k_sym, k_clip_ratio).reshape(bsz, seq_len, num_heads, head_dim).transpose(1, 2).to(q)
+    else:
+        k = act_fake_quant(k.reshape(-1, head_dim), k_bits, -1, k_sym, k_clip_ratio).reshape(bsz, num_heads, seq_len, head_dim).to(q)
+    return q, k

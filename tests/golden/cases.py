@@ -93,6 +93,13 @@ def make_out_grad(batch, seq, hidden, seed):
     return torch.randn(batch, seq, hidden, generator=g) * torch.exp(2.0 * torch.randn(batch, seq, 1, generator=g)) * 1e-3
 
 
+QK_CASES = [
+    # name, (batch, heads, kv_heads, seq, head_dim), k_bits, k_groupsize (-1 or head_dim), k_sym, clip, dtype
+    ("qk_k4_token_asym_bf16", (2, 4, 2, 9, 64), 4, -1, False, 0.95, "bfloat16"),
+    ("qk_k4_head_sym_f16", (1, 4, 4, 7, 128), 4, 128, True, 1.0, "float16"),
+    ("qk_k16_bf16", (1, 2, 2, 5, 64), 16, -1, False, 1.0, "bfloat16"),
+]
+
 GPTAQ_CASES = [
     # name, rows, cols, nseq, seqlen, bits, sym, groupsize, actorder, static, alpha
     ("gptaq_pc_sym_act", 32, 256, 4, 96, 4, True, -1, True, False, 0.25),

@@ -37,10 +37,11 @@ def import_reference(ref_root: str):
                 setattr(mod, a, lambda *args, **kw: None)
             sys.modules[name] = mod
     sys.path.insert(0, ref_root)
-    from utils import quant_utils, hadamard_utils, memory_utils
+    from utils import quant_utils, hadamard_utils, memory_utils, rotation_utils
     from gptq_utils import gptq_utils, gptq_plus_utils, gptq_guided_utils, gptaq_utils
     torch.cuda.synchronize = lambda *a, **k: None
     memory_utils.cleanup_memory = lambda *a, **k: None
+    import_reference.rotation_utils = rotation_utils
     return quant_utils, hadamard_utils, gptq_utils, gptq_plus_utils, gptq_guided_utils, gptaq_utils
 
 
@@ -135,6 +136,19 @@ def gen_gptaq(qu, ga, out):
         out[f"{name}.H_diag"] = np32(torch.diag(g.H))
         g.fasterquant(blocksize=128, percdamp=0.01, groupsize=gs, actorder=act, static_groups=static, alpha=alpha)
         out[f"{name}.Q"] = np32(layer.weight.data)
+
+
+def gen_qk(ru, out):
+    """QKRotationWrapper behind an identity (q, k) function."""
+    for name, (b, h, kvh, t_, d), bits, gs, sym, clip, dtype in cases.QK_CASES:
+        dt = getattr(torch, dtype)
+        q = cases.make_act_tensor((b * h, t_, d), seed=41).reshape(b, h, t_, d).to(dt)
+        k = cases.make_act_tensor((b * kvh, t_, d), seed=42).reshape(b, kvh, t_, d).to(dt)
+        wrap = ru.QKRotationWrapper(lambda a, c: (a, c), d, k_bits=bits, k_groupsize=gs, k_sym=sym, k_clip_ratio=clip)
+        qo, ko = wrap(q, k)
+        out[f"{name}.digest"] = np.array(cases.digest(q.float(), k.float()))
+        out[f"{name}.q"] = np32(qo.float())
+        out[f"{name}.k"] = np32(ko.float())
 
 
 def gen_act_quant(qu, out):
@@ -285,7 +299,8 @@ def main():
                             ("saliency.npz", gen_saliency, (gpu,)),
                             ("act_quant.npz", gen_act_quant, (qu,)),
                             ("guided.npz", gen_guided, (qu, gg)),
-                            ("gptaq.npz", gen_gptaq, (qu, ga))):
+                            ("gptaq.npz", gen_gptaq, (qu, ga)),
+                            ("qk.npz", gen_qk, (import_reference.rotation_utils,))):
         out = {}
         with torch.no_grad():
             fn(*mods, out)

@@ -468,3 +468,25 @@ def test_act_quant_wrapper_partial_rotation():
     v = x.float().reshape(-1, 8, 64).transpose(1, 2)
     xr = (ohad.fwht_pow2(v.cpu().double().reshape(-1, 8)).reshape(v.shape) / 8 ** 0.5).transpose(1, 2).reshape(x.shape)
     assert torch.allclose(y.float().cpu(), lin(xr.to(DEV).bfloat16()).float().cpu(), rtol=0.05, atol=0.05)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("case", cases.QK_CASES, ids=lambda c: c[0])
+def test_qk_rotation_wrapper_vs_reference(golden, case):
+    """The K-cache wrapper on the device against the reference's outputs.  The rotation agrees up to a rare last-bit
+    flip of the I/O dtype, which can move a key across a quantization boundary: at most 0.5 % of the entries differ."""
+    from gptq_plus_mp_quant_b200.utils.rotation_utils import QKRotationWrapper
+    name, (b, h, kvh, t_, d), bits, gs, sym, clip, dtype = case
+    g = golden("qk.npz")
+    dt = getattr(torch, dtype)
+    q = cases.make_act_tensor((b * h, t_, d), seed=41).reshape(b, h, t_, d).to(dt).to(DEV)
+    k = cases.make_act_tensor((b * kvh, t_, d), seed=42).reshape(b, kvh, t_, d).to(dt).to(DEV)
+    wrap = QKRotationWrapper(lambda a, c: (a, c), d, k_bits=bits, k_groupsize=gs, k_sym=sym, k_clip_ratio=clip)
+    qo, ko = wrap(q, k)
+    qr, kr = torch.from_numpy(g[f"{name}.q"]), torch.from_numpy(g[f"{name}.k"])
+    assert qo.dtype == dt and ko.dtype == dt and qo.shape == q.shape and ko.shape == k.shape
+    assert float((qo.float().cpu() != qr).float().mean()) < 0.005
+    assert torch.allclose(qo.float().cpu(), qr, rtol=2 ** -7, atol=1e-6)
+    assert float((ko.float().cpu() != kr).float().mean()) < 0.005
+    with pytest.raises(ValueError):
+        wrap.configure_k_quant(head_dim=d * 2)

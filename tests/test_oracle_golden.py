@@ -266,3 +266,16 @@ def test_gptaq(golden, case):
     q.configure(bits, perchannel=True, sym=sym, mse=False)
     out = ogptq.gptaq_fasterquant(W, st.H, st.dXXT, q, groupsize=gs, actorder=act, static_groups=static, alpha=alpha)
     assert torch.equal(out["Q"], t(g[f"{name}.Q"]))
+
+
+@pytest.mark.parametrize("case", cases.QK_CASES, ids=lambda c: c[0])
+def test_qk_rotation_wrapper(golden, case):
+    """QKRotationWrapper: head-dim Hadamard of q and k, K-cache fake quantization per token or per head."""
+    name, (b, h, kvh, t_, d), bits, gs, sym, clip, dtype = case
+    g = golden("qk.npz")
+    dt = getattr(torch, dtype)
+    q = cases.make_act_tensor((b * h, t_, d), seed=41).reshape(b, h, t_, d).to(dt)
+    k = cases.make_act_tensor((b * kvh, t_, d), seed=42).reshape(b, kvh, t_, d).to(dt)
+    assert cases.digest(q.float(), k.float()) == str(g[f"{name}.digest"])
+    qo, ko = ohad.qk_rotate_quant(q, k, bits, gs, sym, clip)
+    assert torch.equal(qo.float(), t(g[f"{name}.q"])) and torch.equal(ko.float(), t(g[f"{name}.k"]))
