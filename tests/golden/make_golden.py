@@ -2,10 +2,10 @@
 
 Run where the reference checkout is mounted (it cannot travel to the GPU box):
 
-    python tests/golden/make_golden.py [--ref /path/to/gptq_plus_mp_quant]
+    python tests/golden/make_golden.py --ref /path/to/gptq_plus_mp_quant      (or REALQ_REFERENCE_ROOT=...)
 
-The script imports the reference's own classes (``GPTQ``, ``GPTQPlus``,
-``WeightQuantizer``, ``hadamard_utils``) on CPU, feeds them the seeded inputs of
+The script imports the reference's own classes (``GPTQ``, ``GPTQPlus``, ``GPTQGuided``, ``GPTAQ``,
+``WeightQuantizer``, ``ActQuantizer``, ``SaliencyCache``, ``QKRotationWrapper``, ``hadamard_utils``) on CPU, feeds them the seeded inputs of
 ``cases.py`` and stores their outputs in ``*.npz`` files next to this script.  The
 only accommodations, none of which edits the reference: ``transformers`` is imported
 first, the absent ``accelerate`` package is stubbed, and the CUDA-only calls
@@ -286,7 +286,8 @@ def gen_faults(qu, gpu, out):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--ref", default=os.environ.get("REALQ_REFERENCE_ROOT"), required="REALQ_REFERENCE_ROOT" not in os.environ,
+                    help="checkout of the unmodified reference repository")
     args = ap.parse_args()
     torch.set_num_threads(1)                        # fixed reduction order on any host
     qu, hu, gu, gpu, gg, ga = import_reference(args.ref)
