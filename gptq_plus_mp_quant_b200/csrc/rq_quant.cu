@@ -271,3 +271,50 @@ extern "C" int rq_clip_to_quant_bounds(void* W, int dtype, int64_t R, int64_t C,
         return RQ_ERR_INVALID;
     return check_launch();
 }
+
+// ------------------------------------------------------------------------------------------
+// Packed export of integer codes: the fp32 code matrix that fasterquant registers as `int_weight`
+// (gptq_utils/gptq_plus_utils.py:1866-1871 keeps it as fp32 [R, C]) as a little-endian bit stream per row,
+// `bits` bits per code in two's complement: 8 consecutive codes fill `bits` bytes.  One thread per 8 codes.
+// ------------------------------------------------------------------------------------------
+namespace rq {
+namespace quant {
+__global__ void __launch_bounds__(kThreads) pack_codes_kernel(const float* __restrict__ codes, int64_t R, int64_t C,
+                                                             int64_t ldc, int bits, uint8_t* __restrict__ out,
+                                                             int64_t row_bytes) {
+    const int64_t groups = (C + 7) / 8;
+    const uint64_t mask = (1ull << bits) - 1ull;
+    for (int64_t u = (int64_t)blockIdx.x * kThreads + threadIdx.x; u < R * groups; u += (int64_t)gridDim.x * kThreads) {
+        const int64_t r = u / groups, gidx = u - r * groups;
+        uint64_t word = 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int64_t c = gidx * 8 + i;
+            const long long v = c < C ? (long long)codes[r * ldc + c] : 0;
+            word |= ((uint64_t)v & mask) << (i * bits);
+        }
+        uint8_t* dst = out + r * row_bytes + gidx * bits;
+        for (int b = 0; b < bits; ++b)
+            if (gidx * bits + b < row_bytes) dst[b] = (uint8_t)(word >> (8 * b));
+    }
+}
+}  // namespace quant
+}  // namespace rq
+
+extern "C" int64_t rq_packed_row_bytes(int64_t C, int bits) {
+    if (C <= 0 || bits < 2 || bits > 8) return 0;
+    return (C + 7) / 8 * bits;
+}
+
+extern "C" int rq_pack_codes(const float* codes, int64_t R, int64_t C, int64_t ldc, int bits, uint8_t* out,
+                             void* stream) {
+    using namespace rq::quant;
+    if (!codes || !out || R < 0 || C <= 0 || ldc < C || bits < 2 || bits > 8) return RQ_ERR_INVALID;
+    if (R == 0) return RQ_OK;
+    const int64_t groups = (C + 7) / 8;
+    int64_t blocks = (R * groups + kThreads - 1) / kThreads;
+    if (blocks > 148 * 32) blocks = 148 * 32;
+    pack_codes_kernel<<<(unsigned)blocks, kThreads, 0, rq::as_stream(stream)>>>(codes, R, C, ldc, bits, out,
+                                                                               rq_packed_row_bytes(C, bits));
+    return rq::check_launch();
+}

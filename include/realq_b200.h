@@ -177,6 +177,13 @@ int rq_act_quant(const void* x, void* out, int dtype, int64_t units, int unit_le
                  int maxq, int sym, float* scale_out, float* zero_out, const float* scale_in, const float* zero_in,
                  int codes, int dtype_math, void* stream);
 
+/* Packed export (an addition: the reference registers its integer codes as an fp32 [R, C] buffer `int_weight`,
+ * gptq_utils/gptq_plus_utils.py:1866-1871, and has no packed format).  rq_pack_codes turns that matrix (row stride
+ * ldc) into a little-endian bit stream per row, `bits` in 2..8 bits per code in two's complement, 8 consecutive codes
+ * filling `bits` bytes; out: uint8 [R, rq_packed_row_bytes(C, bits)]. */
+int64_t rq_packed_row_bytes(int64_t C, int bits);
+int rq_pack_codes(const float* codes, int64_t R, int64_t C, int64_t ldc, int bits, uint8_t* out, void* stream);
+
 /* rq_clip_to_quant_bounds replaces clip_module_weight_to_quant_bounds_'s arithmetic
  * (gptq_utils/gptq_plus_utils.py:197-225: compute_quant_clip_bounds + clip_tensor_to_quant_bounds) once
  * rq_find_params has produced scale / zero: W [R, C] of dtype (row stride ldw) is clamped in place, per row, to

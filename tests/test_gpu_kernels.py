@@ -490,3 +490,40 @@ def test_qk_rotation_wrapper_vs_reference(golden, case):
     assert float((ko.float().cpu() != kr).float().mean()) < 0.005
     with pytest.raises(ValueError):
         wrap.configure_k_quant(head_dim=d * 2)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("bits,cols", [(4, 256), (3, 200), (2, 72), (8, 64)])
+def test_packed_export_round_trip(bits, cols):
+    """Bit-stream packing of the integer codes and its torch inverse; the packed form of a quantized linear
+    dequantizes to the layer's weight."""
+    from gptq_plus_mp_quant_b200.utils import export_utils as ex
+    g = torch.Generator().manual_seed(bits)
+    lo, hi = -(2 ** (bits - 1)), 2 ** (bits - 1) - 1
+    codes = torch.randint(lo, hi + 1, (37, cols), generator=g).float().to(DEV)
+    packed = ex.pack_codes(codes, bits)
+    assert packed.shape == (37, (cols + 7) // 8 * bits) and packed.dtype == torch.uint8
+    assert torch.equal(ex.unpack_codes(packed, bits, cols).float(), codes)
+
+
+@pytest.mark.gpu
+def test_pack_quantized_linear():
+    from gptq_plus_mp_quant_b200.gptq_utils.gptq_plus_utils import GPTQPlus
+    from gptq_plus_mp_quant_b200.utils import export_utils as ex
+    from gptq_plus_mp_quant_b200.utils.quant_utils import WeightQuantizer
+    rows, cols, G = 32, 256, 2
+    W = cases.make_weight(rows, cols, seed=81)
+    X = cases.make_acts(2, 128, cols, seed=81)
+    S = cases.make_saliency(2, 128, G, seed=81)
+    layer = torch.nn.Linear(cols, rows, bias=False, device=DEV)
+    layer.weight.data.copy_(W)
+    obj = GPTQPlus(layer, S, cases.make_grad(rows, cols, seed=81), G, 0.25, 0.7)
+    obj.quantizer = WeightQuantizer()
+    obj.quantizer.configure(4, perchannel=True, sym=True)
+    obj.add_batch(X.to(DEV), None)
+    obj.finalize_hessian()
+    obj.fasterquant(groupsize=128, actorder=True, static_groups=True, export_to_et=True)
+    blob = ex.pack_quantized_linear(layer, 4, 128)
+    assert blob["qweight"].numel() == rows * cols // 2 and blob["scales"].shape == (rows, 2)
+    deq = ex.unpack_codes(blob["qweight"], 4, cols).float() * blob["scales"].repeat_interleave(128, dim=1)
+    assert torch.equal(deq, layer.weight.data)
