@@ -37,7 +37,7 @@ SIGNATURES = {
     "rq_fwht_heads": (_i, [_vp, _vp, _i, _i64, _i, _i, _i, _vp, _f, _vp]),
     "rq_packed_row_bytes": (_i64, [_i64, _i]),
     "rq_pack_codes": (_i, [_vp, _i64, _i64, _i64, _i, _vp, _vp]),
-    "rq_act_quant": (_i, [_vp, _vp, _i, _i64, _i, _i, _f, _i, _i, _vp, _vp, _vp, _vp, _i, _i, _vp]),
+    "rq_act_quant": (_i, [_vp, _vp, _i, _i64, _i, _i, _f, _i, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "rq_clip_to_quant_bounds": (_i, [_vp, _i, _i64, _i64, _i64, _vp, _vp, _i, _i, _vp]),
     "rq_hessian_accum_pipelined": (_i, [_vp, _i, _i64, _vp, _vp, _vp, _i64, _i, _i, _f, _f, _vp, _sz, _vp, _i, _i64,
                                         _vp, _vp]),

@@ -9,6 +9,8 @@
 //             xmin = T(min * clip), xmax = T(max * clip)
 //   symmetric xmax = max(|xmin|, xmax); scale = T(xmax / maxq) (1 where xmax == 0); q = clamp(rint(T(x / scale)),
 //             -(maxq+1), maxq); out = T(scale * q)
+//             (weight_rule, WeightQuantizer's group-wise ranges :333-352: scale = T(T(max(xmax, 1e-5)) / maxq), and
+//             T(max(T(xmax - xmin), 1e-5)) in the asymmetric span)
 //   otherwise (xmin, xmax) = (-1, +1) where both are 0; scale = T(T(xmax - xmin) / maxq); zero = rint(T(-xmin / scale));
 //             q = clamp(T(rint(T(x / scale)) + zero), 0, maxq); out = T(scale * T(q - zero))
 // HBM-bound: the unit is read from DRAM once (the second read hits L1 / L2) and written once.
@@ -42,7 +44,7 @@ __global__ void __launch_bounds__(256) act_quant_kernel(const T* __restrict__ x,
                                                         float* __restrict__ scale_out, float* __restrict__ zero_out,
                                                         const float* __restrict__ scale_in,
                                                         const float* __restrict__ zero_in, int codes, int dtype_math,
-                                                        int vec_ok) {
+                                                        int vec_ok, int weight_rule) {
     constexpr int UPB = 256 / TPU;                       // units per block
     constexpr int VN = Vec<T>::N;
     auto R = [dtype_math](float v) { return dtype_math ? rnd<T>(v) : v; };
@@ -92,10 +94,12 @@ __global__ void __launch_bounds__(256) act_quant_kernel(const T* __restrict__ x,
             float xmin = R(lo * clip), xmax = R(hi * clip);
             if (sym) {
                 xmax = fmaxf(fabsf(xmin), xmax);
-                scale = (xmax == 0.f) ? 1.f : R(__fdiv_rn(xmax, maxq));
+                if (weight_rule) scale = R(__fdiv_rn(R(fmaxf(xmax, 1e-5f)), maxq));      // .clamp(min=1e-5) / maxq
+                else scale = (xmax == 0.f) ? 1.f : R(__fdiv_rn(xmax, maxq));
             } else {
                 if (xmin == 0.f && xmax == 0.f) { xmin = -1.f; xmax = 1.f; }
-                scale = R(__fdiv_rn(R(xmax - xmin), maxq));
+                const float span = R(xmax - xmin);
+                scale = R(__fdiv_rn(weight_rule ? R(fmaxf(span, 1e-5f)) : span, maxq));
                 zero = rintf(R(__fdiv_rn(-xmin, scale)));
             }
             if (live && t == 0) {
@@ -137,7 +141,8 @@ __global__ void __launch_bounds__(256) act_quant_kernel(const T* __restrict__ x,
 
 extern "C" int rq_act_quant(const void* x, void* out, int dtype, int64_t units, int unit_len, int with_zero,
                             float clip_ratio, int maxq, int sym, float* scale_out, float* zero_out,
-                            const float* scale_in, const float* zero_in, int codes, int dtype_math, void* stream) {
+                            const float* scale_in, const float* zero_in, int codes, int dtype_math, int weight_rule,
+                            void* stream) {
     using namespace rq::actq;
     if (!x || units < 0 || unit_len <= 0 || maxq <= 0 || !(clip_ratio > 0.f) || clip_ratio > 1.f) return RQ_ERR_INVALID;
     if (!out && !scale_out) return RQ_ERR_INVALID;
@@ -155,11 +160,11 @@ extern "C" int rq_act_quant(const void* x, void* out, int dtype, int64_t units, 
         if (wide)                                                                                                  \
             act_quant_kernel<T, 256><<<(unsigned)blocks, 256, 0, st>>>(                                            \
                 reinterpret_cast<const T*>(x), reinterpret_cast<T*>(out), units, unit_len, with_zero, clip_ratio,  \
-                (float)maxq, sym, scale_out, zero_out, scale_in, zero_in, codes, dtype_math, vec_ok);              \
+                (float)maxq, sym, scale_out, zero_out, scale_in, zero_in, codes, dtype_math, vec_ok, weight_rule); \
         else                                                                                                       \
             act_quant_kernel<T, 32><<<(unsigned)blocks, 256, 0, st>>>(                                             \
                 reinterpret_cast<const T*>(x), reinterpret_cast<T*>(out), units, unit_len, with_zero, clip_ratio,  \
-                (float)maxq, sym, scale_out, zero_out, scale_in, zero_in, codes, dtype_math, vec_ok);              \
+                (float)maxq, sym, scale_out, zero_out, scale_in, zero_in, codes, dtype_math, vec_ok, weight_rule); \
     } while (0)
     if (dtype == RQ_F32) RQ_ACTQ_LAUNCH(float);
     else if (dtype == RQ_BF16) RQ_ACTQ_LAUNCH(__nv_bfloat16);

@@ -146,7 +146,7 @@ class ActQuantizer(torch.nn.Module):
             rc = _lib.lib.rq_act_quant(_lib.ptr(x), _lib.ptr(out), _lib.dtype_code(x), units, length, with_zero,
                                        float(self.clip_ratio), int(self.maxq), 1 if self.sym else 0,
                                        _lib.ptr(scale_out), _lib.ptr(zero_out), _lib.ptr(scale_in), _lib.ptr(zero_in),
-                                       1 if codes else 0, 0 if with_zero else 1, _lib.stream_of(x))
+                                       1 if codes else 0, 0 if with_zero else 1, 0, _lib.stream_of(x))
         _lib.check("rq_act_quant", rc)
 
     def find_params(self, x) -> None:
@@ -303,7 +303,9 @@ class WeightQuantizer(torch.nn.Module):
         if self.bits == 16:
             return
         if self.weight_groupsize > 0:
-            raise NotImplementedError("grouped per-token weight ranges (weight_groupsize > 0) are outside the GPTQ path")
+            self._find_params_weight_groupwise(x)
+            return
+        self._g_scale = self._g_zero = None
         _lib.require_cuda(x)
         dev = x.device
         self.maxq = self.maxq.to(dev)
@@ -330,8 +332,38 @@ class WeightQuantizer(torch.nn.Module):
         self.scale = scale.reshape(out_shape)
         self.zero = zero.reshape(out_shape)
 
+    # ---- ranges per row and group of ``weight_groupsize`` columns (quant_utils.py:333-388), in the weight's dtype
+    def _grouped_call(self, x, out, scale_out, zero_out, scale_in, zero_in, sym, codes=False):
+        gs = self.weight_groupsize
+        with torch.cuda.device(x.device):
+            rc = _lib.lib.rq_act_quant(_lib.ptr(x), _lib.ptr(out), _lib.dtype_code(x), x.numel() // gs, gs, 0, 1.0,
+                                       int(self.maxq), 1 if sym else 0, _lib.ptr(scale_out), _lib.ptr(zero_out),
+                                       _lib.ptr(scale_in), _lib.ptr(zero_in), 1 if codes else 0, 1, 1, _lib.stream_of(x))
+        _lib.check("rq_act_quant", rc)
+
+    def _find_params_weight_groupwise(self, x) -> None:
+        if self.mse:
+            raise NotImplementedError("the shrink-grid search over grouped weight ranges is not built")
+        _lib.require_cuda(x)
+        if x.shape[-1] % self.weight_groupsize != 0:
+            raise ValueError(f"columns {x.shape[-1]} not divisible by weight_groupsize {self.weight_groupsize}")
+        self.maxq = self.maxq.to(x.device)
+        xc = x.contiguous()
+        units = xc.numel() // self.weight_groupsize
+        self._g_scale = torch.empty(units, dtype=torch.float32, device=x.device)
+        self._g_zero = torch.zeros(units, dtype=torch.float32, device=x.device)
+        self._grouped_call(xc, None, self._g_scale, self._g_zero, None, None, self.sym)
+        expand = lambda v: v.to(x.dtype).repeat_interleave(self.weight_groupsize).reshape(x.shape)   # noqa: E731
+        self.scale = expand(self._g_scale)
+        self.zero = expand(self._g_zero)
+
     def quantize(self, x):
         x_dtype = x.dtype
+        if getattr(self, "_g_scale", None) is not None and self.bits < 16:
+            xc = x.contiguous()
+            out = torch.empty_like(xc)
+            self._grouped_call(xc, out, None, None, self._g_scale, self._g_zero, self.sym)
+            return out
         if self.ready() and self.bits < 16:
             if self.sym:
                 return STEQuantize.apply(x, self.scale, self.maxq).to(x_dtype)
@@ -341,6 +373,16 @@ class WeightQuantizer(torch.nn.Module):
     def fake_quantize(self, x, st_idx=None, end_idx=None):
         """(dequantized, integer codes, scale): always the symmetric clamp, the zero-point is
         ignored, exactly like the reference (quant_utils.py:471-480)."""
+        if getattr(self, "_g_scale", None) is not None and self.bits < 16:
+            scale, gsc = self.scale.to(x.device), self._g_scale
+            if st_idx is not None and end_idx is not None:
+                per_row = scale.shape[-1] // self.weight_groupsize
+                scale, gsc = scale[st_idx:end_idx], gsc[st_idx * per_row:end_idx * per_row].contiguous()
+            xc = x.contiguous()
+            deq, codes = torch.empty_like(xc), torch.empty_like(xc)
+            self._grouped_call(xc, deq, None, None, gsc, None, True)
+            self._grouped_call(xc, codes, None, None, gsc, None, True, codes=True)
+            return deq, codes, scale
         if self.ready() and self.bits < 16:
             scale = self.scale.to(x.device)
             if st_idx is not None and end_idx is not None:

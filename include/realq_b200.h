@@ -172,10 +172,12 @@ int rq_group_mean_square(const void* grad, int dtype, int64_t batch, int64_t seq
  * matching setting results agree bit for bit.  scale_out / zero_out
  * (optional, fp32 [units]) receive the ranges; scale_in / zero_in (optional) replace the range search (forward with
  * stored ranges); out may be NULL when only the ranges are wanted; codes != 0 writes the integer codes
- * (ActQuantizer.quantize, :112-117) instead of the dequantized values. */
+ * (ActQuantizer.quantize, :112-117) instead of the dequantized values.  weight_rule != 0 selects the range rule of
+ * WeightQuantizer.find_params_weight_groupwise (:333-352: the magnitude / span is clamped at 1e-5 instead of a zero
+ * range mapping to scale 1), which makes the same kernel serve grouped weight quantization (units = row groups). */
 int rq_act_quant(const void* x, void* out, int dtype, int64_t units, int unit_len, int with_zero, float clip_ratio,
                  int maxq, int sym, float* scale_out, float* zero_out, const float* scale_in, const float* zero_in,
-                 int codes, int dtype_math, void* stream);
+                 int codes, int dtype_math, int weight_rule, void* stream);
 
 /* Packed export (an addition: the reference registers its integer codes as an fp32 [R, C] buffer `int_weight`,
  * gptq_utils/gptq_plus_utils.py:1866-1871, and has no packed format).  rq_pack_codes turns that matrix (row stride

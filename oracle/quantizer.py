@@ -233,3 +233,35 @@ def act_fake_quant(x, bits, groupsize=-1, sym=False, clip_ratio=1.0):
         return (scale * q).to(x.dtype)
     q = torch.clamp(torch.round(x / scale) + zero, 0, maxq)
     return (scale * (q - zero)).to(x.dtype)
+
+
+def weight_groupwise_params(x, bits, groupsize, sym):
+    """WeightQuantizer.find_params_weight_groupwise without the shrink-grid search (utils/quant_utils.py:333-352):
+    (scale, zero, maxq) with scale / zero of x's shape, in x's dtype."""
+    maxq = torch.tensor(2 ** (bits - 1) - 1) if sym else torch.tensor(2 ** bits - 1)
+    init_shape = x.shape
+    xr = x.reshape(x.shape[-2], x.shape[-1] // groupsize, groupsize)
+    xmax = torch.amax(xr, dim=-1, keepdim=True)
+    xmin = torch.amin(xr, dim=-1, keepdim=True)
+    if sym:
+        scale = torch.maximum(torch.abs(xmin), xmax).clamp(min=1e-5) / maxq
+        zero = torch.zeros_like(scale)
+    else:
+        tmp = (xmin == 0) & (xmax == 0)
+        xmin[tmp] = -1
+        xmax[tmp] = +1
+        scale = (xmax - xmin).clamp(min=1e-5) / maxq
+        zero = torch.round(-xmin / scale)
+    scale = scale.repeat(1, 1, groupsize).reshape(init_shape)
+    zero = zero.repeat(1, 1, groupsize).reshape(init_shape)
+    return scale, zero, maxq
+
+
+def weight_groupwise_rtn(x, bits, groupsize, sym):
+    """Round-to-nearest of a weight with grouped ranges as rtn_fwrd applies it (gptq_utils/gptq_utils.py:339-350):
+    fake_quantize (symmetric clamp, zero ignored) -> (dequantized, codes, scale), plus quantize() (zero honoured)."""
+    scale, zero, maxq = weight_groupwise_params(x, bits, groupsize, sym)
+    q = torch.clamp(torch.round(x / scale), -(maxq + 1), maxq)
+    fake = (scale * q).to(x.dtype)
+    ste = ste_quantize(x, scale, zero, int(maxq), sym).to(x.dtype)
+    return fake, q, scale, zero, ste

@@ -72,6 +72,14 @@ QUANTIZER_CASES = [
     ("w8_asym_pt", 16, 64, 8, False, False, False),
 ]
 
+WGROUP_CASES = [
+    # name, rows, cols, bits, weight_groupsize, sym, dtype
+    ("wg_w4_g128_sym_bf16", 24, 256, 4, 128, True, "bfloat16"),
+    ("wg_w4_g64_asym_bf16", 24, 256, 4, 64, False, "bfloat16"),
+    ("wg_w3_g128_sym_f32", 16, 384, 3, 128, True, "float32"),
+    ("wg_w8_g32_asym_f16", 8, 96, 8, 32, False, "float16"),
+]
+
 CLIP_CASES = [
     # name, rows, cols, bits, sym, weight dtype
     ("clip_w4_sym_f32", 32, 128, 4, True, "float32"),

@@ -70,6 +70,23 @@ def gen_quantizer(qu, out):
         out[f"{name}.ste"] = np32(ste)
 
 
+def gen_wgroup(qu, out):
+    """WeightQuantizer with weight_groupsize > 0 (the round-to-nearest path of rtn_fwrd), in the weight's dtype."""
+    for name, rows, cols, bits, gs, sym, dtype in cases.WGROUP_CASES:
+        W = cases.make_weight(rows, cols, seed=19).to(getattr(torch, dtype))
+        W[0, :gs] = 0                                                # one all-zero group
+        q = qu.WeightQuantizer()
+        q.configure(bits, perchannel=True, sym=sym, mse=False, weight_groupsize=gs)
+        q.find_params(W)
+        deq, codes, scale = q.fake_quantize(W)
+        out[f"{name}.digest"] = np.array(cases.digest(W.float()))
+        out[f"{name}.scale"] = np32(q.scale.float())
+        out[f"{name}.zero"] = np32(q.zero.float())
+        out[f"{name}.fake"] = np32(deq.float())
+        out[f"{name}.codes"] = np32(codes.float())
+        out[f"{name}.ste"] = np32(q.quantize(W).float())
+
+
 def gen_clip(qu, gpu, out):
     """Pre-clip of a linear's weight to its quantizer's range (clip_module_weight_to_quant_bounds_)."""
     for name, rows, cols, bits, sym, dtype in cases.CLIP_CASES:
@@ -297,6 +314,7 @@ def main():
                             ("gptq_plus.npz", gen_plus, (qu, gpu)),
                             ("faults.npz", gen_faults, (qu, gpu)),
                             ("clip.npz", gen_clip, (qu, gpu)),
+                            ("wgroup.npz", gen_wgroup, (qu,)),
                             ("saliency.npz", gen_saliency, (gpu,)),
                             ("act_quant.npz", gen_act_quant, (qu,)),
                             ("guided.npz", gen_guided, (qu, gg)),

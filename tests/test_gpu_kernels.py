@@ -527,3 +527,32 @@ def test_pack_quantized_linear():
     assert blob["qweight"].numel() == rows * cols // 2 and blob["scales"].shape == (rows, 2)
     deq = ex.unpack_codes(blob["qweight"], 4, cols).float() * blob["scales"].repeat_interleave(128, dim=1)
     assert torch.equal(deq, layer.weight.data)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("case", cases.WGROUP_CASES, ids=lambda c: c[0])
+def test_weight_quantizer_grouped_vs_reference(golden, case):
+    """Grouped weight ranges (weight_groupsize > 0) on the device, bit for bit against the reference: ranges,
+    fake_quantize (values, codes, row-sliced call) and quantize()."""
+    from gptq_plus_mp_quant_b200.utils.quant_utils import WeightQuantizer
+    name, rows, cols, bits, gs, sym, dtype = case
+    g = golden("wgroup.npz")
+    W = cases.make_weight(rows, cols, seed=19).to(getattr(torch, dtype))
+    W[0, :gs] = 0
+    Wd = W.to(DEV)
+    q = WeightQuantizer()
+    q.configure(bits, perchannel=True, sym=sym, mse=False, weight_groupsize=gs)
+    q.find_params(Wd)
+    assert bool(q.ready()) and q.scale.shape == W.shape and q.scale.dtype == W.dtype
+    assert torch.equal(q.scale.float().cpu(), torch.from_numpy(g[f"{name}.scale"]))
+    assert torch.equal(q.zero.float().cpu(), torch.from_numpy(g[f"{name}.zero"]))
+    deq, codes, scale = q.fake_quantize(Wd)
+    assert torch.equal(deq.float().cpu(), torch.from_numpy(g[f"{name}.fake"]))
+    assert torch.equal(codes.float().cpu(), torch.from_numpy(g[f"{name}.codes"]))
+    assert torch.equal(q.quantize(Wd).float().cpu(), torch.from_numpy(g[f"{name}.ste"]))
+    d2, c2, s2 = q.fake_quantize(Wd[4:8], st_idx=4, end_idx=8)
+    assert torch.equal(d2, deq[4:8]) and torch.equal(c2, codes[4:8]) and torch.equal(s2, scale[4:8])
+    qm = WeightQuantizer()
+    qm.configure(bits, perchannel=True, sym=sym, mse=True, weight_groupsize=gs)
+    with pytest.raises(NotImplementedError):
+        qm.find_params(Wd)

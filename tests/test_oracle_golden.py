@@ -279,3 +279,17 @@ def test_qk_rotation_wrapper(golden, case):
     assert cases.digest(q.float(), k.float()) == str(g[f"{name}.digest"])
     qo, ko = ohad.qk_rotate_quant(q, k, bits, gs, sym, clip)
     assert torch.equal(qo.float(), t(g[f"{name}.q"])) and torch.equal(ko.float(), t(g[f"{name}.k"]))
+
+
+@pytest.mark.parametrize("case", cases.WGROUP_CASES, ids=lambda c: c[0])
+def test_weight_quantizer_grouped(golden, case):
+    """WeightQuantizer with weight_groupsize > 0 (round-to-nearest path), evaluated in the weight's own dtype."""
+    name, rows, cols, bits, gs, sym, dtype = case
+    g = golden("wgroup.npz")
+    W = cases.make_weight(rows, cols, seed=19).to(getattr(torch, dtype))
+    W[0, :gs] = 0
+    assert cases.digest(W.float()) == str(g[f"{name}.digest"])
+    fake, codes, scale, zero, ste = oq.weight_groupwise_rtn(W, bits, gs, sym)
+    assert torch.equal(scale.float(), t(g[f"{name}.scale"])) and torch.equal(zero.float(), t(g[f"{name}.zero"]))
+    assert torch.equal(fake.float(), t(g[f"{name}.fake"])) and torch.equal(codes.float(), t(g[f"{name}.codes"]))
+    assert torch.equal(ste.float(), t(g[f"{name}.ste"]))
