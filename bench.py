@@ -235,6 +235,10 @@ class LayerWorkload:
                     unit_owner[(name, g)] = pat[g]
         self.recorder = None
         self.copy_stream = None
+        self.comm_stream = None
+        # "1": start each linear's exchange of partial Hessians right after its last add_batch, on a side stream
+        # (GPTQPlus.begin_exchange).  Same results; measured on 2 GPUs it did not shorten the step, so it is off.
+        self.overlap_exchange = os.environ.get("REALQ_BENCH_OVERLAP_EXCHANGE", "0") != "0"
         self.fq_streams = int(os.environ.get("REALQ_BENCH_FQ_STREAMS", str(len(self.LINEARS))))
         self.fq_pool = None
         self.unit_cost = {name: sum(c for (n, g), c in costs.items() if n == name and (world == 1 or unit_owner[(n, g)] == rank))
@@ -289,8 +293,16 @@ class LayerWorkload:
                     t.record_stream(main)
             rot = {"hid": hu.matmul_hadU_cuda(batch["hid"], None, 1), "attn": batch["attn"],
                    "mlp": hu.matmul_hadU_cuda(batch["mlp"], self.had12, 12)}
-            for name, _, _, key in self.LINEARS:
+            last = self.world > 1 and self.overlap_exchange and s + self.BSZ >= self.nseq_local
+            if last and self.comm_stream is None:
+                self.comm_stream = torch.cuda.Stream()
+            # in the last batch the widest linear goes first: its exchange is the longest, and it then runs under
+            # the GEMMs of the others (every rank uses the same order, as the collectives require)
+            for name, _, _, key in (self.LINEARS[::-1] if last else self.LINEARS):
                 objs[name].add_batch(rot[key], None)
+                if last:
+                    objs[name].group_owners = self.owner[name]
+                    objs[name].begin_exchange(self.comm_stream)
         checksum = torch.zeros((), device=self.dev)
         # three phases, so that no rank waits in a collective for another rank's fasterquant: all exchanges of
         # the partial Hessians, then every rank's own (linear, group) units, then the gather of the rows
@@ -495,7 +507,7 @@ def run_ours(args):
         wl.step_device()
     sections = {k: round(v, 2) for k, v in sorted(wl.recorder.summary().items(), key=lambda kv: -kv[1])}
     wl.recorder = None
-    wl.step_e2e()
+    checksum = wl.step_e2e()
     e2e_ms = timed(wl.step_e2e, args.steps)
 
     sec_per_layer = total_ms / args.steps / 1e3
@@ -535,6 +547,7 @@ def run_ours(args):
         "gpu_launches_source": ("kernels named rq::* in a CUPTI activity trace of one untimed step of the same workload"
                                 if counted else "counted from the host loops (no activity trace available)"),
         "clocks": clocks,
+        "checksum": checksum,                          # sum over linears of mean |quantized weight| (rank 0's copy)
     }
     if rank == 0 and world == 1 and not args.no_cpu:
         torch.set_num_threads(os.cpu_count() or 1)

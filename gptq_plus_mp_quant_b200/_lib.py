@@ -45,6 +45,7 @@ SIGNATURES = {
     "rq_hessian_accum_noalloc": (_i, [_vp, _i, _i64, _vp, _vp, _vp, _i64, _i, _i, _f, _f, _vp, _vp]),
     "rq_hessian_finalize": (_i, [_vp, _vp, _i, _i, _f, _f, _f, _i, _vp, _vp]),
     "rq_fwht": (_i, [_vp, _vp, _i, _i64, _i, _i, _vp, _f, _vp]),
+    "rq_fwht_act_quant": (_i, [_vp, _vp, _i, _i64, _i, _i, _vp, _f, _f, _i, _i, _vp, _vp, _vp]),
     "rq_find_params": (_i, [_vp, _i64, _i64, _i64, _i, _i, _i, _i, _i, _f, _i, _f, _vp, _vp, _vp]),
     "rq_quantize": (_i, [_vp, _vp, _vp, _i, _i64, _i64, _vp, _vp, _i, _i, _i, _vp]),
     "rq_chol_workspace_bytes": (_sz, [_i, _i]),

@@ -12,7 +12,9 @@ namespace rq {
 namespace fwht {
 
 constexpr int kThreads = 256;
-constexpr int kMaxK = 64;       // register-resident mix; larger K takes the generic path
+constexpr int kMaxK = 64;       // register-resident mix, matrix in shared memory
+constexpr int kMaxWideK = 256;  // beyond kMaxK: the mix reads the matrix from global memory (L1-resident) and
+                                // writes its sums straight to the output
 
 // one padding word per 16 keeps the strided radix-16 accesses of every pass on distinct banks
 __device__ __forceinline__ int pad(int i) { return i + (i >> 4); }
@@ -80,7 +82,7 @@ __global__ void __launch_bounds__(kThreads) fwht_kernel(const T* __restrict__ x,
     extern __shared__ float buf[];                       // pad(rows_per_item * n) floats, then K*K mix matrix
     const int item_elems = rows_per_item * n;
     float* hk = buf + pad(item_elems) + 1;
-    if (K > 1)
+    if (K > 1 && K <= kMaxK)
         for (int e = threadIdx.x; e < K * K; e += kThreads) hk[e] = hadK[e];
     const int64_t items = (rows + rows_per_item - 1) / rows_per_item;
     const int P = n / K;
@@ -118,6 +120,20 @@ __global__ void __launch_bounds__(kThreads) fwht_kernel(const T* __restrict__ x,
             lo += r;
             __syncthreads();
         }
+        if (K > kMaxK) {
+            // ---- wide mix: one output element per thread and turn, chunk positions fastest, so that a warp reads
+            // one matrix entry (a broadcast) and consecutive shared-memory words per term
+            for (int e = threadIdx.x; e < (int)valid; e += kThreads) {
+                const int r = e / n, c = e - r * n;
+                const int ko = c / P, p = c - ko * P;
+                const float* hrow = hadK + (size_t)ko * K;
+                const int base = r * n + p;
+                float acc = 0.f;
+                for (int k = 0; k < K; ++k) acc = fmaf(__ldg(hrow + k), buf[pad(base + k * P)], acc);
+                store_from_float<T>(dst, e, acc * scale);
+            }
+            continue;
+        }
         // ---- K x K mix across the K chunks of each row (in place: a thread owns one position of one row)
         if (K > 1) {
             const int positions = rows_per_item * P;
@@ -151,12 +167,13 @@ __global__ void __launch_bounds__(kThreads) fwht_kernel(const T* __restrict__ x,
 
 using namespace rq;
 
-extern "C" int rq_fwht(const void* x, void* y, int dtype, int64_t rows, int n, int K, const float* hadK, float scale,
-                       void* stream) {
+// rqp != nullptr: the fused rotation + per-token quantization, which only the register-resident paths offer
+static int fwht_impl(const void* x, void* y, int dtype, int64_t rows, int n, int K, const float* hadK, float scale,
+                     const rq::fwht::RowQuant* rqp, void* stream) {
     using namespace rq::fwht;
     if (!x || !y || rows < 0 || n <= 0 || K <= 0 || n % K != 0) return RQ_ERR_INVALID;
     if (K > 1 && !hadK) return RQ_ERR_INVALID;
-    if (K > kMaxK) return RQ_ERR_UNSUPPORTED;
+    if (K > kMaxWideK) return RQ_ERR_UNSUPPORTED;
     const int P = n / K;
     if ((P & (P - 1)) != 0) return RQ_ERR_INVALID;
     if (rows == 0) return RQ_OK;
@@ -180,10 +197,18 @@ extern "C" int rq_fwht(const void* x, void* y, int dtype, int64_t rows, int n, i
         int64_t grid = nchunks < (int64_t)sms0 * per_sm ? nchunks : (int64_t)sms0 * per_sm;
         cudaError_t e = cudaSuccess;
 #define RQ_SPLIT_LAUNCH(T, WW)                                                                                    \
-    e = cudaFuncSetAttribute(fwht_split_kernel<T, WW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);    \
-    if (e != cudaSuccess) return RQ_ERR_CUDA;                                                                      \
-    fwht_split_kernel<T, WW><<<(unsigned)grid, 32 * WW, smem, st>>>(reinterpret_cast<const T*>(x),                 \
-                                                                    reinterpret_cast<T*>(y), nchunks, scale)
+    if (rqp) {                                                                                                     \
+        e = cudaFuncSetAttribute(fwht_split_kernel<T, WW, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,      \
+                                 (int)smem);                                                                       \
+        if (e != cudaSuccess) return RQ_ERR_CUDA;                                                                  \
+        fwht_split_kernel<T, WW, true><<<(unsigned)grid, 32 * WW, smem, st>>>(                                     \
+            reinterpret_cast<const T*>(x), reinterpret_cast<T*>(y), nchunks, scale, *rqp);                         \
+    } else {                                                                                                       \
+        e = cudaFuncSetAttribute(fwht_split_kernel<T, WW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        if (e != cudaSuccess) return RQ_ERR_CUDA;                                                                  \
+        fwht_split_kernel<T, WW><<<(unsigned)grid, 32 * WW, smem, st>>>(reinterpret_cast<const T*>(x),             \
+                                                                        reinterpret_cast<T*>(y), nchunks, scale);  \
+    }
 #define RQ_SPLIT_DISPATCH(T)                                \
     if (W == 2) { RQ_SPLIT_LAUNCH(T, 2); }                  \
     else if (W == 4) { RQ_SPLIT_LAUNCH(T, 4); }             \
@@ -202,6 +227,7 @@ extern "C" int rq_fwht(const void* x, void* y, int dtype, int64_t rows, int n, i
         const int logs = m < 10 ? 10 : m;
         const int S = 1 << logs;
         cudaError_t e = cudaSuccess;
+        if (K == 1 && rqp) return RQ_ERR_UNSUPPORTED;
         if (K == 1) {
             const int64_t total = rows * (int64_t)n;
             const int64_t nsc = (total + S - 1) / S;
@@ -233,10 +259,18 @@ extern "C" int rq_fwht(const void* x, void* y, int dtype, int64_t rows, int n, i
             if (per_sm < 1) per_sm = 1;
             int64_t grid = rows < (int64_t)sms0 * per_sm ? rows : (int64_t)sms0 * per_sm;
 #define RQ_MIX_LAUNCH(T, L)                                                                                       \
-    e = cudaFuncSetAttribute(fwht_mix_kernel<T, L>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);       \
-    if (e != cudaSuccess) return RQ_ERR_CUDA;                                                                      \
-    fwht_mix_kernel<T, L><<<(unsigned)grid, 32 * kMixWarps, smem, st>>>(reinterpret_cast<const T*>(x),          \
-                                                                           reinterpret_cast<T*>(y), rows, K, hadK, scale)
+    if (rqp) {                                                                                                     \
+        e = cudaFuncSetAttribute(fwht_mix_kernel<T, L, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,         \
+                                 (int)smem);                                                                       \
+        if (e != cudaSuccess) return RQ_ERR_CUDA;                                                                  \
+        fwht_mix_kernel<T, L, true><<<(unsigned)grid, 32 * kMixWarps, smem, st>>>(                                 \
+            reinterpret_cast<const T*>(x), reinterpret_cast<T*>(y), rows, K, hadK, scale, *rqp);                   \
+    } else {                                                                                                       \
+        e = cudaFuncSetAttribute(fwht_mix_kernel<T, L>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);   \
+        if (e != cudaSuccess) return RQ_ERR_CUDA;                                                                  \
+        fwht_mix_kernel<T, L><<<(unsigned)grid, 32 * kMixWarps, smem, st>>>(                                       \
+            reinterpret_cast<const T*>(x), reinterpret_cast<T*>(y), rows, K, hadK, scale);                         \
+    }
 #define RQ_MIX_DISPATCH(T)                                  \
     if (logs == 10) { RQ_MIX_LAUNCH(T, 10); }               \
     else if (logs == 11) { RQ_MIX_LAUNCH(T, 11); }          \
@@ -250,7 +284,8 @@ extern "C" int rq_fwht(const void* x, void* y, int dtype, int64_t rows, int n, i
             return check_launch();
         }
     }
-    // ---- general path: shared-memory radix passes (any K up to 64, chunks longer than 4096, unaligned buffers)
+    if (rqp) return RQ_ERR_UNSUPPORTED;
+    // ---- general path: shared-memory radix passes (any K, chunks longer than 4096, unaligned buffers)
     // short rows are batched so that an item has about 4096 elements; whole chunks only
     int rows_per_item = 1;
     if (n < 4096) {
@@ -259,7 +294,7 @@ extern "C" int rq_fwht(const void* x, void* y, int dtype, int64_t rows, int n, i
         if (rows_per_item < 1) rows_per_item = 1;
     }
     const int64_t item_elems = (int64_t)rows_per_item * n;
-    const size_t smem = ((size_t)(item_elems + (item_elems >> 4)) + 2 + (size_t)K * K) * sizeof(float);
+    const size_t smem = ((size_t)(item_elems + (item_elems >> 4)) + 2 + (K <= kMaxK ? (size_t)K * K : 0)) * sizeof(float);
     if (smem > 220 * 1024) return RQ_ERR_UNSUPPORTED;
     const int64_t items = (rows + rows_per_item - 1) / rows_per_item;
     int dev = 0, sms = 148;
@@ -284,6 +319,24 @@ extern "C" int rq_fwht(const void* x, void* y, int dtype, int64_t rows, int n, i
     else return RQ_ERR_INVALID;
 #undef RQ_FWHT_LAUNCH
     return check_launch();
+}
+
+extern "C" int rq_fwht(const void* x, void* y, int dtype, int64_t rows, int n, int K, const float* hadK, float scale,
+                       void* stream) {
+    return fwht_impl(x, y, dtype, rows, n, K, hadK, scale, nullptr, stream);
+}
+
+extern "C" int rq_fwht_act_quant(const void* x, void* y, int dtype, int64_t rows, int n, int K, const float* hadK,
+                                 float scale, float clip_ratio, int maxq, int sym, float* scale_out, float* zero_out,
+                                 void* stream) {
+    if (maxq <= 0 || !(clip_ratio > 0.f) || clip_ratio > 1.f) return RQ_ERR_INVALID;
+    rq::fwht::RowQuant q;
+    q.clip = clip_ratio;
+    q.maxq = (float)maxq;
+    q.sym = sym ? 1 : 0;
+    q.scale_out = scale_out;
+    q.zero_out = zero_out;
+    return fwht_impl(x, y, dtype, rows, n, K, hadK, scale, &q, stream);
 }
 
 // ------------------------------------------------------------------------------------------

@@ -202,16 +202,92 @@ __global__ void __launch_bounds__(32 * kWarpsPerCta) fwht_warp_kernel(const T* _
     }
 }
 
+// ---- optional fused epilogue: dynamic per-token fake quantization of the rotated row (the activation quantizer
+// that follows the online rotation in front of a linear).  The rotated values are first rounded to the I/O type,
+// exactly what a separate rotation kernel would have stored, and kept in shared memory; the range (which includes
+// 0), scale and zero point then follow the per-token rule in fp32, and the row is written once.
+struct RowQuant {
+    float clip, maxq;
+    int sym;
+    float* scale_out;     // [rows] or nullptr
+    float* zero_out;      // [rows] or nullptr
+};
+
+template <typename T>
+__device__ __forceinline__ float round_io(float v);
+template <>
+__device__ __forceinline__ float round_io<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float round_io<__nv_bfloat16>(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+template <>
+__device__ __forceinline__ float round_io<__half>(float v) { return __half2float(__float2half_rn(v)); }
+
+// CTA-wide min / max (every thread calls; red: 64 floats of shared memory), then the row's scale and zero point.
+__device__ __forceinline__ void row_quant_params(float lo, float hi, float* red, const RowQuant& q, float& scale,
+                                                 float& zero) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        lo = fminf(lo, __shfl_xor_sync(0xffffffffu, lo, o));
+        hi = fmaxf(hi, __shfl_xor_sync(0xffffffffu, hi, o));
+    }
+    if (lane == 0) { red[warp] = lo; red[32 + warp] = hi; }
+    __syncthreads();
+    lo = red[0]; hi = red[32];
+    for (int w = 1; w < nwarps; ++w) { lo = fminf(lo, red[w]); hi = fmaxf(hi, red[32 + w]); }
+    float xmin = lo * q.clip, xmax = hi * q.clip;
+    zero = 0.f;
+    if (q.sym) {
+        xmax = fmaxf(fabsf(xmin), xmax);
+        scale = (xmax == 0.f) ? 1.f : __fdiv_rn(xmax, q.maxq);
+    } else {
+        if (xmin == 0.f && xmax == 0.f) { xmin = -1.f; xmax = 1.f; }
+        scale = __fdiv_rn(xmax - xmin, q.maxq);
+        zero = rintf(__fdiv_rn(-xmin, scale));
+    }
+}
+
+__device__ __forceinline__ float row_quant_one(float v, float scale, float zero, const RowQuant& q) {
+    float c = rintf(__fdiv_rn(v, scale)), r;
+    if (q.sym) {
+        c = fminf(fmaxf(c, -(q.maxq + 1.f)), q.maxq);
+        r = scale * c;
+    } else {
+        c = fminf(fmaxf(c + zero, 0.f), q.maxq);
+        r = scale * (c - zero);
+    }
+    return (v != v) ? v : r;
+}
+
+// Quantize the row held in shared memory as `chunks` slices of S floats (wphys layout) and write it out.
+template <typename T>
+__device__ __forceinline__ void row_quant_store(const float* wsm, int slice, int S, int chunks, T* yrow, float scale,
+                                                float zero, const RowQuant& q) {
+    const int n = chunks * S;
+    for (int idx = 8 * threadIdx.x; idx < n; idx += 8 * blockDim.x) {
+        const int c = idx / S, p = idx - c * S;
+        const float* src = wsm + (size_t)c * slice + wphys(p);
+        const float4 t0 = *reinterpret_cast<const float4*>(src);
+        const float4 t1 = *reinterpret_cast<const float4*>(src + 4);
+        const float o[8] = {row_quant_one(t0.x, scale, zero, q), row_quant_one(t0.y, scale, zero, q),
+                            row_quant_one(t0.z, scale, zero, q), row_quant_one(t0.w, scale, zero, q),
+                            row_quant_one(t1.x, scale, zero, q), row_quant_one(t1.y, scale, zero, q),
+                            row_quant_one(t1.z, scale, zero, q), row_quant_one(t1.w, scale, zero, q)};
+        store8<T>(yrow + idx, o);
+    }
+}
+
 // K == 1, chunk length P = W * 1024 with W = 2, 4 or 8: a CTA of W warps owns one chunk.  Every warp transforms
 // its 1024-element quarter over index bits 0-9 (32 registers per lane, so many warps stay resident and hide
 // the load latency); after a CTA barrier a last radix-W pass over bits 10+ combines the W slices position by
 // position and writes the result with 16-byte stores.
-template <typename T, int W>
+template <typename T, int W, bool QUANT = false>
 __global__ void __launch_bounds__(32 * W) fwht_split_kernel(const T* __restrict__ x, T* __restrict__ y,
-                                                            int64_t nchunks, float scale) {
+                                                            int64_t nchunks, float scale, RowQuant rq = RowQuant()) {
     constexpr int S = 1024;
     constexpr int slice = warp_slice_floats(S);
     extern __shared__ float wsm[];
+    __shared__ float red[64];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t total = nchunks * (int64_t)(W * S);
     for (int64_t ch = blockIdx.x; ch < nchunks; ch += gridDim.x) {
@@ -221,6 +297,7 @@ __global__ void __launch_bounds__(32 * W) fwht_split_kernel(const T* __restrict_
         __syncthreads();
         // thread t handles positions 8t .. 8t+7 of every slice (W * 32 threads cover 1024 positions when W = 4;
         // other W loop)
+        float lo = 0.f, hi = 0.f;
         for (int p = 8 * threadIdx.x; p < S; p += 8 * 32 * W) {
             float v[W][8];
 #pragma unroll
@@ -248,8 +325,29 @@ __global__ void __launch_bounds__(32 * W) fwht_split_kernel(const T* __restrict_
                 float o[8];
 #pragma unroll
                 for (int e = 0; e < 8; ++e) o[e] = v[w][e] * scale;
-                store8<T>(y + base + (int64_t)w * S + p, o);
+                if (QUANT) {                                    // back into place, rounded as a store would round
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) {
+                        o[e] = round_io<T>(o[e]);
+                        lo = fminf(lo, o[e]);
+                        hi = fmaxf(hi, o[e]);
+                    }
+                    float* q = wsm + w * slice + wphys(p);
+                    *reinterpret_cast<float4*>(q) = make_float4(o[0], o[1], o[2], o[3]);
+                    *reinterpret_cast<float4*>(q + 4) = make_float4(o[4], o[5], o[6], o[7]);
+                } else {
+                    store8<T>(y + base + (int64_t)w * S + p, o);
+                }
             }
+        }
+        if (QUANT) {
+            float qs, qz;
+            row_quant_params(lo, hi, red, rq, qs, qz);          // its barrier also publishes the rounded row
+            if (threadIdx.x == 0) {
+                if (rq.scale_out) rq.scale_out[ch] = qs;
+                if (rq.zero_out) rq.zero_out[ch] = qz;
+            }
+            row_quant_store<T>(wsm, slice, S, W, y + base, qs, qz, rq);
         }
     }
 }
@@ -268,9 +366,9 @@ __device__ __forceinline__ void store2<__half>(__half* p, float a, float b) {
 }
 
 // two neighbouring positions of every chunk -> K outputs each; hadK entries are +-1, so the products are exact
-template <typename T, int KK>
-__device__ __forceinline__ void mix_pair(const float* buf, int slice, const float* hk, int p, int P, T* yrow,
-                                         float scale, int K) {
+template <typename T, int KK, bool QUANT = false>
+__device__ __forceinline__ void mix_pair(float* buf, int slice, const float* hk, int p, int P, T* yrow,
+                                         float scale, int K, float* lo = nullptr, float* hi = nullptr) {
     float v0[KK], v1[KK];
 #pragma unroll
     for (int k = 0; k < KK; ++k) {
@@ -304,19 +402,28 @@ __device__ __forceinline__ void mix_pair(const float* buf, int slice, const floa
                 }
             }
         }
-        store2<T>(yrow + (int64_t)ko * P + p, s0 * scale, s1 * scale);
+        if (QUANT) {                                 // every input of this position pair is already in registers
+            const float r0 = round_io<T>(s0 * scale), r1 = round_io<T>(s1 * scale);
+            *lo = fminf(*lo, fminf(r0, r1));
+            *hi = fmaxf(*hi, fmaxf(r0, r1));
+            *reinterpret_cast<float2*>(buf + ko * slice + wphys(p)) = make_float2(r0, r1);
+        } else {
+            store2<T>(yrow + (int64_t)ko * P + p, s0 * scale, s1 * scale);
+        }
     }
 }
 
 // K > 1 with chunk length P = S: one CTA per row; warps transform the K chunks into shared memory, then
 // all threads mix the chunks position by position.
-template <typename T, int LOGS>
+template <typename T, int LOGS, bool QUANT = false>
 __global__ void __launch_bounds__(32 * kMixWarps) fwht_mix_kernel(const T* __restrict__ x, T* __restrict__ y,
                                                                      int64_t rows, int K,
-                                                                     const float* __restrict__ hadK, float scale) {
+                                                                     const float* __restrict__ hadK, float scale,
+                                                                     RowQuant rq = RowQuant()) {
     constexpr int S = 1 << LOGS;
     constexpr int slice = warp_slice_floats(S);
     extern __shared__ float wsm[];
+    __shared__ float red[64];
     float* hk = wsm + (size_t)K * slice;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     for (int e = threadIdx.x; e < K * K; e += blockDim.x) hk[e] = hadK[e];
@@ -327,10 +434,20 @@ __global__ void __launch_bounds__(32 * kMixWarps) fwht_mix_kernel(const T* __res
             warp_transform<T, LOGS>(x, row * n + (int64_t)c * S, (rows * n), LOGS, wsm + (size_t)c * slice, lane);
         __syncthreads();
         T* yrow = y + row * n;
+        float lo = 0.f, hi = 0.f;
         for (int p = 2 * threadIdx.x; p < S; p += 2 * blockDim.x) {
-            if (K <= 12) mix_pair<T, 12>(wsm, slice, hk, p, S, yrow, scale, K);
-            else if (K <= 20) mix_pair<T, 20>(wsm, slice, hk, p, S, yrow, scale, K);
-            else mix_pair<T, 28>(wsm, slice, hk, p, S, yrow, scale, K);
+            if (K <= 12) mix_pair<T, 12, QUANT>(wsm, slice, hk, p, S, yrow, scale, K, &lo, &hi);
+            else if (K <= 20) mix_pair<T, 20, QUANT>(wsm, slice, hk, p, S, yrow, scale, K, &lo, &hi);
+            else mix_pair<T, 28, QUANT>(wsm, slice, hk, p, S, yrow, scale, K, &lo, &hi);
+        }
+        if (QUANT) {
+            float qs, qz;
+            row_quant_params(lo, hi, red, rq, qs, qz);          // its barrier also publishes the rounded row
+            if (threadIdx.x == 0) {
+                if (rq.scale_out) rq.scale_out[row] = qs;
+                if (rq.zero_out) rq.zero_out[row] = qz;
+            }
+            row_quant_store<T>(wsm, slice, S, K, yrow, qs, qz, rq);
         }
     }
 }

@@ -90,6 +90,7 @@ class GPTQPlus:
         # group_owners[g] only and fasterquant quantizes just the rows of the groups this rank owns; the
         # other rows of layer.weight keep their values until the caller gathers them from their owners.
         self.group_owners = None
+        self._exchange = None           # (stream, totals) while begin_exchange's collectives are in flight
         assert self.rows % self.num_groups == 0, (
             f"Number of rows ({self.rows}) must be divisible by num_groups ({self.num_groups})")
 
@@ -110,6 +111,8 @@ class GPTQPlus:
         """``H[g] += X^T diag(s_g) X``; ``act_square += sum x^2`` (gptq_plus_utils.py:798-857)."""
         if self._finalized:
             raise RuntimeError("add_batch called after finalize_hessian. Re-init GPTQPlus to reuse.")
+        if self._exchange is not None:
+            raise RuntimeError("add_batch called after begin_exchange: the partial sums are already being reduced.")
         rec = self.profile_recorder
         with rec.section("add_batch.total") if rec else _NULL_CONTEXT:
             if inp.dim() == 2:
@@ -132,13 +135,8 @@ class GPTQPlus:
                 self._H_upper_only = True
             self.token_count += n_tokens
 
-    @torch.no_grad()
-    def finalize_hessian(self):
-        """All-reduce the sums over ranks, normalise, symmetrise, zero non-finite entries
-        (gptq_plus_utils.py:859-908)."""
-        if self._finalized:
-            return
-        ops.hessian_join(self.dev)
+    def _reduce_sums_(self):
+        """The cross-rank sums of the accumulators, to the owners that hessian_owner / group_owners name."""
         if self.group_owners is not None:
             assert len(self.group_owners) == self.num_groups
             dist_utils.reduce_groups_to_owners_(self._H, self.group_owners)
@@ -147,8 +145,48 @@ class GPTQPlus:
         else:
             dist_utils.reduce_sum_(self._H, self.hessian_owner)
         dist_utils.allreduce_sum_(self.act_square)
-        total_samples = dist_utils.allreduce_sum_scalar(self.index)
-        total_tokens = dist_utils.allreduce_sum_scalar(self.token_count)
+
+    @torch.no_grad()
+    def begin_exchange(self, stream=None):
+        """Starts finalize_hessian's cross-rank sums without waiting for them.  Call it after this linear's last
+        add_batch, on every rank and in the same order over linears; the collectives are enqueued on ``stream``
+        (which first waits for the work already queued on the current stream), so that they overlap whatever the
+        current stream runs next, e.g. the Hessian GEMMs of the other linears.  The host does not block.
+        finalize_hessian then waits for them instead of issuing its own.  No-op for a single process."""
+        if self._finalized or self._exchange is not None or dist_utils.get_world_size() <= 1:
+            return
+        ops.hessian_join(self.dev)
+        on_gpu = self._H.is_cuda
+        side = None
+        if on_gpu:
+            cur = torch.cuda.current_stream(self.dev)
+            side = stream if stream is not None else cur
+            if side is not cur:
+                side.wait_stream(cur)
+        with (torch.cuda.stream(side) if on_gpu else _NULL_CONTEXT):
+            self._reduce_sums_()
+            totals = torch.tensor([float(self.index), float(self.token_count)], dtype=torch.float64,
+                                  device=self._H.device)
+            dist_utils.allreduce_sum_(totals)
+        self._exchange = (side, totals)
+
+    @torch.no_grad()
+    def finalize_hessian(self):
+        """All-reduce the sums over ranks, normalise, symmetrise, zero non-finite entries
+        (gptq_plus_utils.py:859-908)."""
+        if self._finalized:
+            return
+        if self._exchange is not None:
+            side, totals = self._exchange
+            self._exchange = None
+            if side is not None:
+                torch.cuda.current_stream(self.dev).wait_stream(side)
+            total_samples, total_tokens = (float(v) for v in totals.tolist())
+        else:
+            ops.hessian_join(self.dev)
+            self._reduce_sums_()
+            total_samples = dist_utils.allreduce_sum_scalar(self.index)
+            total_tokens = dist_utils.allreduce_sum_scalar(self.token_count)
         if total_samples <= 0 or total_tokens <= 0:
             raise RuntimeError("finalize_hessian called before any add_batch ran.")
         seq_len = total_tokens / total_samples

@@ -141,6 +141,27 @@ def fwht(x: torch.Tensor, hadK=None, K: int = 1, scale: float = 1.0, out: torch.
     return out.view(x.shape)
 
 
+def fwht_act_quant(x: torch.Tensor, hadK, K: int, scale: float, clip_ratio: float, maxq: int, sym: bool):
+    """Rotation and per-token fake quantization in one kernel (``rq_fwht_act_quant``); None when the shape is not one
+    the fused kernel covers, so that the caller runs the two kernels in turn."""
+    _lib.require_cuda(x)
+    n = x.shape[-1]
+    xc = x.contiguous()
+    rows = xc.numel() // n if n else 0
+    if rows == 0:
+        return torch.empty_like(xc).view(x.shape)
+    out = torch.empty_like(xc)
+    hk = _hadK_on(x.device, hadK) if K > 1 else None
+    with torch.cuda.device(x.device):
+        rc = _lib.lib.rq_fwht_act_quant(_lib.ptr(xc), _lib.ptr(out), _lib.dtype_code(xc), rows, n, K, _lib.ptr(hk),
+                                        float(scale), float(clip_ratio), int(maxq), 1 if sym else 0, None, None,
+                                        _lib.stream_of(xc))
+    if rc == _lib.RQ_ERR_UNSUPPORTED:
+        return None
+    _lib.check("rq_fwht_act_quant", rc)
+    return out.view(x.shape)
+
+
 def fwht_heads(x: torch.Tensor, heads: int, head_dim: int, hadK=None, K: int = 1, scale: float = 1.0) -> torch.Tensor:
     """Hadamard transform across the ``heads`` of ``x[..., heads * head_dim]`` for every position inside a head (the
     online partial rotation of utils/quant_utils.py:258-281), times ``scale``.  ``K == 1``: Sylvester order;

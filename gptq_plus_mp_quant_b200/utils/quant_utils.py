@@ -231,6 +231,18 @@ class ActQuantWrapper(torch.nn.Module):
     def forward(self, x, R1=None, R2=None, transpose=False):
         from . import hadamard_utils
         x_dtype = x.dtype
+        q = self.quantizer
+        if (self.online_full_had and q.bits < 16 and q.groupsize <= 0
+                and (not self.fp32_had or x_dtype == torch.float32)):
+            # rotation and per-token quantization in one pass over the activations where the kernel covers the shape
+            import math
+            y = hadamard_utils.fwht_act_quant(x, self.had_K, self.K, 1.0 / math.sqrt(x.shape[-1]), q.clip_ratio,
+                                              int(q.maxq), q.sym)
+            if y is not None:
+                x = (self.module(y, R1, R2, transpose) if R1 is not None else self.module(y)).to(x_dtype)
+                if self.out_quantizer.bits < 16:
+                    x = self.out_quantizer.fake_quant(x).to(x_dtype)
+                return x
         if self.online_full_had:
             if self.fp32_had:
                 x = hadamard_utils.matmul_hadU_cuda(x.float(), self.had_K, self.K).to(x_dtype)

@@ -123,9 +123,21 @@ int rq_hessian_finalize(float* H, float* act_sq, int C, int G, float div_tokens,
  * Replaces hadamard_utils.matmul_hadU_cuda / HadamardTransform (utils/hadamard_utils.py:89-98,121-130)
  * and the third-party fast_hadamard_transform call (utils/hadamard_utils.py:31-34).
  * x, y: [rows, n] contiguous, same dtype (in place allowed); hadK: device fp32 [K, K] (+-1), NULL when K == 1.
- * The FWHT runs over each contiguous n/K chunk, then chunk k' = sum_k hadK[k'][k] * chunk k. */
+ * The FWHT runs over each contiguous n/K chunk, then chunk k' = sum_k hadK[k'][k] * chunk k.
+ * K <= 256 (every order of the reference's table); RQ_ERR_UNSUPPORTED when a row does not fit shared memory
+ * (about 50 000 elements). */
 int rq_fwht(const void* x, void* y, int dtype, int64_t rows, int n, int K, const float* hadK, float scale,
             void* stream);
+
+/* The online rotation in front of a linear fused with the dynamic per-token fake quantization that follows it
+ * (ActQuantWrapper.forward, utils/quant_utils.py:258-289: matmul_hadU_cuda, then ActQuantizer.find_params and the
+ * quantizer call): y = fake_quant(rq_fwht(x)), bit for bit what rq_fwht followed by rq_act_quant (per-token,
+ * with_zero = 1, dtype_math = 0) writes, with one read and one write of the activations instead of two each.
+ * scale_out / zero_out: optional [rows] fp32.  Only the shapes of the register-resident rotation paths (16-byte
+ * aligned buffers and n = 2048, 4096, 8192, or K <= 28 with 1024 <= n/K <= 4096); RQ_ERR_UNSUPPORTED otherwise -
+ * call the two entry points in turn then. */
+int rq_fwht_act_quant(const void* x, void* y, int dtype, int64_t rows, int n, int K, const float* hadK, float scale,
+                      float clip_ratio, int maxq, int sym, float* scale_out, float* zero_out, void* stream);
 
 /* rq_fwht_heads replaces the online partial rotation in front of o_proj (utils/quant_utils.py:258-281): x viewed
  * [tokens, H, D] (H heads of width D); y[t][h'][d] = scale * sum_h Had[h'][h] * x[t][h][d], i.e. the transform runs

@@ -4,6 +4,8 @@ quantizer.  Tolerances: H <= 5e-6 relative Frobenius for sums over a few hundred
 <= 2e-6 from a few thousand tokens on (the split-bf16 rounding terms average out with the
 token count; bar: 1e-5), scale/zero <= 1e-6 relative
 (bar: 1e-5), integer codes identical, rotation within one rounding of the I/O dtype."""
+import math
+
 import numpy as np
 import pytest
 import torch
@@ -208,6 +210,25 @@ def test_rotation_full_sizes_are_orthogonal(n):
     hadKt, _ = hu.get_hadK(n, transpose=True)
     back = hu.matmul_hadU_cuda(y, hadKt, K)
     assert float((back - x).abs().max()) < 2e-5 * float(x.abs().max()) * 4
+
+
+@pytest.mark.parametrize("K,P,dtype", [(172, 64, "float32"), (172, 64, "bfloat16"), (68, 32, "float16"), (252, 16, "float32")])
+def test_rotation_with_wide_mix_matrix(K, P, dtype):
+    """Orders above 64 (11008 = 172 * 64 and the like): the mix reads its matrix from global memory.  Any +-1
+    matrix exercises the arithmetic; compared with the exact operator built from the same matrix."""
+    from gptq_plus_mp_quant_b200.utils import hadamard_utils as hu
+    g = torch.Generator().manual_seed(K)
+    hadK = (torch.randint(0, 2, (K, K), generator=g) * 2 - 1).float()
+    n, rows = K * P, 37
+    dt = getattr(torch, dtype)
+    x = cases.make_acts(1, rows, n, seed=9).reshape(rows, n).to(dt)
+    y = hu.matmul_hadU_cuda(x.to(DEV), hadK, K)
+    exact = ohad.rotate_exact(x, hadK, K)
+    tol = {"float32": 2e-6, "bfloat16": 2.0 ** -8, "float16": 2.0 ** -11}[dtype]
+    assert float((y.double().cpu() - exact).abs().max()) <= tol * float(exact.abs().max()) * 1.01
+    xin = x.to(DEV).clone()
+    hu.fwht(xin, hadK, K, scale=1.0 / math.sqrt(n), out=xin)                      # in place
+    assert torch.equal(xin, y)
 
 
 def test_hadamard_autograd_is_self_adjoint():
@@ -430,6 +451,46 @@ def test_act_quant_wrapper_rotates_and_quantizes():
     wrap.had_K, wrap.K = hu.get_hadK(512)
     wrap.quantizer.configure(4, groupsize=-1, sym=False, clip_ratio=0.9)
     x = cases.make_act_tensor((2, 6, 512), seed=29).bfloat16().to(DEV)
+    y = wrap(x)
+    xr = hu.matmul_hadU_cuda(x, wrap.had_K, wrap.K)
+    xq = oq.act_fake_quant(xr.cpu(), 4, -1, False, 0.9).to(DEV)
+    assert torch.equal(y, lin(xq))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("n", [2048, 4096, 8192, 12288, 20480, 28672])
+@pytest.mark.parametrize("dtype,sym,clip", [(torch.bfloat16, False, 0.9), (torch.float16, True, 1.0),
+                                            (torch.float32, False, 1.0), (torch.bfloat16, True, 0.85)])
+def test_fused_rotation_and_act_quant_is_the_two_kernels(n, dtype, sym, clip):
+    """rq_fwht_act_quant writes exactly what rq_fwht followed by the per-token rq_act_quant writes (the rotated
+    values are rounded to the I/O dtype before the range is taken), including an all-zero and a constant token."""
+    from gptq_plus_mp_quant_b200.utils import hadamard_utils as hu
+    from gptq_plus_mp_quant_b200.utils.quant_utils import ActQuantizer
+    x = cases.make_act_tensor((3, 11, n), seed=n % 97).to(dtype)
+    x[0, 0] = 0
+    x[1, 3] = 0.5
+    x = x.to(DEV)
+    hadK, K = hu.get_hadK(n)
+    q = ActQuantizer()
+    q.configure(4, groupsize=-1, sym=sym, clip_ratio=clip)
+    two = q.fake_quant(hu.matmul_hadU_cuda(x, hadK, K))
+    one = hu.fwht_act_quant(x, hadK, K, 1.0 / math.sqrt(n), clip, int(q.maxq), sym)
+    assert one is not None and one.dtype == dtype
+    assert torch.equal(one, two)
+
+
+@pytest.mark.gpu
+def test_act_quant_wrapper_uses_the_fused_kernel_where_it_applies():
+    from gptq_plus_mp_quant_b200.utils import hadamard_utils as hu
+    from gptq_plus_mp_quant_b200.utils.quant_utils import ActQuantWrapper
+    assert hu.fwht_act_quant(torch.zeros(4, 1024, device=DEV), None, 1, 1.0, 1.0, 15, True) is None   # not covered
+    torch.manual_seed(0)
+    lin = torch.nn.Linear(12288, 32, bias=False, device=DEV, dtype=torch.bfloat16)
+    wrap = ActQuantWrapper(lin)
+    wrap.online_full_had = True
+    wrap.had_K, wrap.K = hu.get_hadK(12288)
+    wrap.quantizer.configure(4, groupsize=-1, sym=False, clip_ratio=0.9)
+    x = cases.make_act_tensor((2, 6, 12288), seed=33).bfloat16().to(DEV)
     y = wrap(x)
     xr = hu.matmul_hadU_cuda(x, wrap.had_K, wrap.K)
     xq = oq.act_fake_quant(xr.cpu(), 4, -1, False, 0.9).to(DEV)
