@@ -29,6 +29,8 @@ SIGNATURES = {
     "rq_hessian_workspace_bytes": (_sz, [_i64, _i, _i, _i]),
     "rq_hessian_accum": (_i, [_vp, _i, _i64, _vp, _vp, _vp, _i64, _i, _i, _f, _f, _vp, _sz, _vp, _i, _vp]),
     "rq_group_mean_square": (_i, [_vp, _i, _i64, _i64, _i64, _i64, _i, _i, _vp, _vp]),
+    "rq_quantile_workspace_bytes": (_sz, []),
+    "rq_clamp_to_quantile": (_i, [_vp, _i64, _f, _vp, _vp, _sz, _vp]),
     "rq_gptaq_accum_workspace_bytes": (_sz, [_i64, _i]),
     "rq_gptaq_accum": (_i, [_vp, _i, _i64, _vp, _i, _i64, _i, _i64, _i, _f, _f, _vp, _vp, _sz, _vp, _vp]),
     "rq_gptaq_workspace_bytes": (_sz, [_i, _i]),

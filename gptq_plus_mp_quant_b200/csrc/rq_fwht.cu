@@ -121,16 +121,43 @@ __global__ void __launch_bounds__(kThreads) fwht_kernel(const T* __restrict__ x,
             __syncthreads();
         }
         if (K > kMaxK) {
-            // ---- wide mix: one output element per thread and turn, chunk positions fastest, so that a warp reads
-            // one matrix entry (a broadcast) and consecutive shared-memory words per term
-            for (int e = threadIdx.x; e < (int)valid; e += kThreads) {
-                const int r = e / n, c = e - r * n;
-                const int ko = c / P, p = c - ko * P;
-                const float* hrow = hadK + (size_t)ko * K;
+            // ---- wide mix, straight from shared memory to the output: a thread owns 4 output chunks x 2
+            // neighbouring positions, so that a term costs 2 shared-memory words and 4 matrix entries (the same
+            // address in every lane of a warp: a broadcast from L1) for 8 multiply-adds
+            const int kt = (K + 3) >> 2, half = P >> 1;                // P is a power of two >= 2 on this path
+            const int live_rows = (int)(valid / n);
+            const int tiles = live_rows * kt * half;
+            if (P == 1) {                                              // n == K: a plain matrix-vector product per row
+                for (int e = threadIdx.x; e < (int)valid; e += kThreads) {
+                    const int r = e / n, ko = e - r * n;
+                    float acc = 0.f;
+                    for (int k = 0; k < K; ++k) acc = fmaf(__ldg(hadK + (size_t)ko * K + k), buf[pad(r * n + k)], acc);
+                    store_from_float<T>(dst, e, acc * scale);
+                }
+            }
+            for (int t = threadIdx.x; t < tiles; t += kThreads) {
+                const int pp = t % half, rest = t / half;
+                const int k4 = rest % kt, r = rest / kt;
+                const int ko = 4 * k4, p = 2 * pp;
+                const float* h0 = hadK + (size_t)ko * K;
+                const float* h1 = h0 + (ko + 1 < K ? K : 0);
+                const float* h2 = h0 + (ko + 2 < K ? 2 * K : 0);
+                const float* h3 = h0 + (ko + 3 < K ? 3 * K : 0);
                 const int base = r * n + p;
-                float acc = 0.f;
-                for (int k = 0; k < K; ++k) acc = fmaf(__ldg(hrow + k), buf[pad(base + k * P)], acc);
-                store_from_float<T>(dst, e, acc * scale);
+                float a00 = 0.f, a01 = 0.f, a10 = 0.f, a11 = 0.f, a20 = 0.f, a21 = 0.f, a30 = 0.f, a31 = 0.f;
+                for (int k = 0; k < K; ++k) {
+                    const float v0 = buf[pad(base + k * P)], v1 = buf[pad(base + k * P + 1)];
+                    const float c0 = __ldg(h0 + k), c1 = __ldg(h1 + k), c2 = __ldg(h2 + k), c3 = __ldg(h3 + k);
+                    a00 = fmaf(c0, v0, a00); a01 = fmaf(c0, v1, a01);
+                    a10 = fmaf(c1, v0, a10); a11 = fmaf(c1, v1, a11);
+                    a20 = fmaf(c2, v0, a20); a21 = fmaf(c2, v1, a21);
+                    a30 = fmaf(c3, v0, a30); a31 = fmaf(c3, v1, a31);
+                }
+                T* o = dst + (size_t)r * n + (size_t)ko * P + p;
+                store_from_float<T>(o, 0, a00 * scale); store_from_float<T>(o, 1, a01 * scale);
+                if (ko + 1 < K) { store_from_float<T>(o, P, a10 * scale); store_from_float<T>(o, P + 1, a11 * scale); }
+                if (ko + 2 < K) { store_from_float<T>(o, 2 * P, a20 * scale); store_from_float<T>(o, 2 * P + 1, a21 * scale); }
+                if (ko + 3 < K) { store_from_float<T>(o, 3 * P, a30 * scale); store_from_float<T>(o, 3 * P + 1, a31 * scale); }
             }
             continue;
         }

@@ -104,3 +104,138 @@ extern "C" int rq_group_mean_square(const void* grad, int dtype, int64_t batch, 
 #undef RQ_SAL_LAUNCH
     return rq::check_launch();
 }
+
+// ------------------------------------------------------------------------------------------
+// Percentile clip of the saliencies (gptq_utils/gptq_plus_utils.py:2834-2839):
+//     cap = torch.quantile(s.flatten(), q);  s = clamp(s, max=cap)
+// torch.quantile sorts; only two order statistics are needed.  With rank = fl32(q) * fl32(n - 1), the values at
+// floor(rank) and ceil(rank) are found exactly by a most-significant-digit-first radix selection over the
+// order-preserving integer image of the floats: four passes of a 256-bin histogram per statistic (a pass only
+// counts the elements whose higher digits match the digits chosen so far), then
+//     cap = lerp(lo, hi, rank - floor(rank))        (torch's two-sided lerp)
+// and one clamp pass.  NaN anywhere makes the quantile, and with it every clamped value, NaN as in torch.
+// HBM-bound, five reads and one write of the tensor (which is small: tokens x G floats).
+// ------------------------------------------------------------------------------------------
+namespace rq {
+namespace sal {
+
+struct SelectState {
+    unsigned int prefix[2];      // digits chosen so far (higher bytes), order-preserving image
+    unsigned int remaining[2];   // rank of the wanted element among those that match the prefix
+    unsigned int nan_count;
+    unsigned int pad[3];
+    unsigned int hist[2][256];
+};
+
+__device__ __forceinline__ unsigned int ordered_bits(float v) {
+    const unsigned int b = __float_as_uint(v);
+    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+__device__ __forceinline__ float from_ordered_bits(unsigned int u) {
+    return __uint_as_float((u & 0x80000000u) ? (u & 0x7fffffffu) : ~u);
+}
+
+__global__ void select_init_kernel(SelectState* st, unsigned int k0, unsigned int k1) {
+    for (int i = threadIdx.x; i < 512; i += blockDim.x) (&st->hist[0][0])[i] = 0u;
+    if (threadIdx.x == 0) {
+        st->prefix[0] = st->prefix[1] = 0u;
+        st->remaining[0] = k0;
+        st->remaining[1] = k1;
+        st->nan_count = 0u;
+    }
+}
+
+__global__ void __launch_bounds__(256) select_hist_kernel(const float* __restrict__ x, int64_t n, SelectState* st,
+                                                          int shift) {
+    __shared__ unsigned int h[2][256];
+    h[0][threadIdx.x] = 0u;
+    h[1][threadIdx.x] = 0u;
+    __syncthreads();
+    const unsigned int mask = shift == 24 ? 0u : (0xffffffffu << (shift + 8));
+    const unsigned int p0 = st->prefix[0] & mask, p1 = st->prefix[1] & mask;
+    unsigned int nans = 0;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        const float v = x[i];
+        if (shift == 24 && v != v) ++nans;
+        const unsigned int u = ordered_bits(v);
+        const unsigned int d = (u >> shift) & 255u;
+        if ((u & mask) == p0) atomicAdd(&h[0][d], 1u);
+        if ((u & mask) == p1) atomicAdd(&h[1][d], 1u);
+    }
+    __syncthreads();
+    if (h[0][threadIdx.x]) atomicAdd(&st->hist[0][threadIdx.x], h[0][threadIdx.x]);
+    if (h[1][threadIdx.x]) atomicAdd(&st->hist[1][threadIdx.x], h[1][threadIdx.x]);
+    if (nans) atomicAdd(&st->nan_count, nans);
+}
+
+// one warp per statistic: pick the digit whose bin holds the wanted rank, descend into it
+__global__ void select_scan_kernel(SelectState* st, int shift) {
+    const int sel = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (sel < 2) {
+        unsigned int c[8], sum = 0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { c[j] = st->hist[sel][lane * 8 + j]; sum += c[j]; }
+        unsigned int incl = sum;                                   // inclusive scan over lanes
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const unsigned int t = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += t;
+        }
+        unsigned int below = incl - sum;
+        const unsigned int want = st->remaining[sel];
+        int digit = -1;
+        unsigned int rem = 0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            if (digit < 0 && want >= below && want < below + c[j]) { digit = lane * 8 + j; rem = want - below; }
+            below += c[j];
+        }
+        __syncwarp();
+        if (digit >= 0) {
+            st->prefix[sel] |= (unsigned int)digit << shift;
+            st->remaining[sel] = rem;
+        }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < 512; i += blockDim.x) (&st->hist[0][0])[i] = 0u;
+}
+
+__global__ void __launch_bounds__(256) clamp_to_quantile_kernel(float* __restrict__ x, int64_t n,
+                                                                const SelectState* __restrict__ st, float weight,
+                                                                float* __restrict__ cap_out) {
+    const float lo = from_ordered_bits(st->prefix[0]), hi = from_ordered_bits(st->prefix[1]);
+    float cap = (fabsf(weight) < 0.5f) ? lo + weight * (hi - lo) : hi - (hi - lo) * (1.f - weight);
+    if (st->nan_count) cap = __uint_as_float(0x7fc00000u);
+    if (blockIdx.x == 0 && threadIdx.x == 0 && cap_out) *cap_out = cap;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        const float v = x[i];
+        x[i] = (cap != cap) ? cap : ((v != v) ? v : fminf(v, cap));
+    }
+}
+
+}  // namespace sal
+}  // namespace rq
+
+extern "C" size_t rq_quantile_workspace_bytes(void) { return sizeof(rq::sal::SelectState); }
+
+extern "C" int rq_clamp_to_quantile(float* x, int64_t n, float q, float* cap_out, void* workspace,
+                                    size_t workspace_bytes, void* stream) {
+    using namespace rq::sal;
+    if (!x || n < 0 || !(q >= 0.f) || q > 1.f || n >= (int64_t)1 << 31) return RQ_ERR_INVALID;
+    if (!workspace || workspace_bytes < sizeof(SelectState) || reinterpret_cast<uintptr_t>(workspace) % 16 != 0)
+        return RQ_ERR_WORKSPACE;
+    if (n == 0) return RQ_OK;
+    cudaStream_t st = rq::as_stream(stream);
+    SelectState* state = static_cast<SelectState*>(workspace);
+    const float rank = q * (float)(n - 1);                         // fp32, as torch forms it
+    const float below = floorf(rank), above = ceilf(rank);
+    int64_t grid = (n + 255) / 256;
+    if (grid > 148 * 8) grid = 148 * 8;
+    select_init_kernel<<<1, 256, 0, st>>>(state, (unsigned int)below, (unsigned int)above);
+    for (int shift = 24; shift >= 0; shift -= 8) {
+        select_hist_kernel<<<(unsigned)grid, 256, 0, st>>>(x, n, state, shift);
+        select_scan_kernel<<<1, 64, 0, st>>>(state, shift);
+    }
+    clamp_to_quantile_kernel<<<(unsigned)grid, 256, 0, st>>>(x, n, state, rank - below, cap_out);
+    return rq::check_launch();
+}

@@ -242,8 +242,11 @@ class SaliencyCache:
     gradient hook during the calibration backward pass (gptq_plus_utils.py:2363-2431).  The hook's arithmetic runs in
     one kernel that reads the gradient once, sink positions sliced off without a copy."""
 
-    def __init__(self, names, num_groups, sink_size=0):
+    def __init__(self, names, num_groups, sink_size=0, clip_percentile=None):
         self.num_groups = num_groups
+        # cap every hook call's saliencies at this quantile of theirs (the saliency_clip_percentile of the
+        # calibration backward pass, gptq_plus_utils.py:2834-2839); None or outside (0, 1): no clip
+        self.clip_percentile = clip_percentile
         self.saliency_cache = {name: [] for name in names}
         self.names = names
         self.handles = []
@@ -259,7 +262,10 @@ class SaliencyCache:
             g = grad
             if self.sink_size > 0 and g.dim() >= 2 and g.shape[1] > self.sink_size:
                 g = g[:, self.sink_size:]
-            self.saliency_cache[name].append(ops.group_mean_square(g, self.num_groups))
+            sal = ops.group_mean_square(g, self.num_groups)
+            if self.clip_percentile is not None and 0 < self.clip_percentile < 1:
+                ops.clamp_to_quantile_(sal, self.clip_percentile)
+            self.saliency_cache[name].append(sal)
 
         out.register_hook(grad_hook)
 

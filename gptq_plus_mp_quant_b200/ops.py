@@ -154,6 +154,21 @@ def hessian_finalize(H: torch.Tensor, act_sq, div_tokens: float = 1.0, div_scale
     return counts
 
 
+def clamp_to_quantile_(x: torch.Tensor, q: float) -> torch.Tensor:
+    """In place ``x = clamp(x, max=torch.quantile(x.flatten(), q))`` for a contiguous fp32 tensor of any size (no
+    sort, no 16M-element limit); returns the cap as a 0-dim tensor."""
+    _lib.require_cuda(x)
+    assert x.dtype == torch.float32 and x.is_contiguous()
+    cap = torch.empty((), dtype=torch.float32, device=x.device)
+    need = int(_lib.lib.rq_quantile_workspace_bytes())
+    ws = _workspace(x.device, need, key="quantile")
+    with torch.cuda.device(x.device):
+        rc = _lib.lib.rq_clamp_to_quantile(_lib.ptr(x), x.numel(), float(q), _lib.ptr(cap), _lib.ptr(ws), need,
+                                           _lib.stream_of(x))
+    _lib.check("rq_clamp_to_quantile", rc)
+    return cap
+
+
 def group_mean_square(grad: torch.Tensor, num_groups: int) -> torch.Tensor:
     """``grad.float().pow(2).view(b, t, G, -1).mean(-1)`` for a ``[batch, seq, hidden]`` gradient (fp32 / bf16 / fp16,
     channels contiguous; the batch and sequence strides are free, so a ``grad[:, sink:]`` slice is taken as is)."""

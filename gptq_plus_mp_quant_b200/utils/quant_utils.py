@@ -232,9 +232,11 @@ class ActQuantWrapper(torch.nn.Module):
         from . import hadamard_utils
         x_dtype = x.dtype
         q = self.quantizer
-        if (self.online_full_had and q.bits < 16 and q.groupsize <= 0
+        if (self.online_full_had and q.bits < 16 and q.groupsize <= 0 and self.K == 1 and x.shape[-1] <= 4096
                 and (not self.fp32_had or x_dtype == torch.float32)):
-            # rotation and per-token quantization in one pass over the activations where the kernel covers the shape
+            # rotation and per-token quantization in one pass over the activations; both kernels are bound by the
+            # quantizer's IEEE divisions rather than by memory, and only up to 4096-long rows did the fused kernel
+            # measure faster than the two in turn
             import math
             y = hadamard_utils.fwht_act_quant(x, self.had_K, self.K, 1.0 / math.sqrt(x.shape[-1]), q.clip_ratio,
                                               int(q.maxq), q.sym)

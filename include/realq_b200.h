@@ -175,6 +175,15 @@ int rq_quantize(const void* x, void* deq, float* codes, int dtype, int64_t R, in
 int rq_group_mean_square(const void* grad, int dtype, int64_t batch, int64_t seq, int64_t stride_b, int64_t stride_t,
                          int hidden, int G, float* out, void* stream);
 
+/* Percentile clip of the saliencies (gptq_utils/gptq_plus_utils.py:2834-2839): cap = torch.quantile(x.flatten(), q)
+ * (linear interpolation between the two neighbouring order statistics, rank = fl32(q) * fl32(n - 1)), then
+ * x = clamp(x, max = cap) in place; cap_out (optional, device fp32) receives the cap.  The order statistics are exact
+ * (radix selection, no sort); a NaN anywhere makes the cap and every output NaN, as in torch.  n < 2^31.
+ * workspace: rq_quantile_workspace_bytes() bytes of device memory, 16-byte aligned. */
+size_t rq_quantile_workspace_bytes(void);
+int rq_clamp_to_quantile(float* x, int64_t n, float q, float* cap_out, void* workspace, size_t workspace_bytes,
+                         void* stream);
+
 /* rq_act_quant replaces ActQuantizer.find_params followed by STEQuantize / AsymSTEQuantize.forward
  * (utils/quant_utils.py:60-84, 133-206; call site ActQuantWrapper.forward :283-295): dynamic fake quantization of
  * activations per unit, a unit being one token row (with_zero = 1: the range includes 0, :180-183) or one group of a

@@ -115,6 +115,24 @@ def group_mean_square(grad, num_groups, sink_size=0):
     return g.float().pow(2).view(bsz, seq_len, num_groups, group_size).mean(dim=-1)
 
 
+def clip_at_percentile(sal, q):
+    """Saliency outlier clip of the calibration hook (gptq_utils/gptq_plus_utils.py:2834-2839):
+    ``clamp(sal, max=torch.quantile(sal.flatten(), q))``, with torch.quantile restated: sort, rank = fl32(q) * fl32(n-1),
+    two-sided lerp between the neighbouring order statistics.  Returns (clipped, cap)."""
+    import numpy as np
+    flat = np.sort(sal.detach().float().flatten().numpy())
+    n = flat.size
+    rank = np.float32(q) * np.float32(n - 1)
+    below, above = int(np.floor(rank)), int(np.ceil(rank))
+    w = np.float32(rank - np.float32(below))
+    lo, hi = flat[below], flat[above]
+    cap = lo + w * (hi - lo) if abs(w) < 0.5 else hi - (hi - lo) * (np.float32(1) - w)
+    if np.isnan(flat).any():
+        cap = np.float32(np.nan)
+    cap_t = torch.tensor(cap, dtype=torch.float32)
+    return torch.clamp(sal.float(), max=cap_t), cap_t
+
+
 def fisher_block(grad, sink_size=0, scale=1000.0 * 1000.0):
     """One batch's contribution to the layer-output Fisher sum (gptq_utils/gptq_plus_utils.py:2908-2921)."""
     if sink_size > 0 and grad.dim() >= 2 and grad.shape[1] > sink_size:

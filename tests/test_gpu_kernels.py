@@ -212,7 +212,8 @@ def test_rotation_full_sizes_are_orthogonal(n):
     assert float((back - x).abs().max()) < 2e-5 * float(x.abs().max()) * 4
 
 
-@pytest.mark.parametrize("K,P,dtype", [(172, 64, "float32"), (172, 64, "bfloat16"), (68, 32, "float16"), (252, 16, "float32")])
+@pytest.mark.parametrize("K,P,dtype", [(172, 64, "float32"), (172, 64, "bfloat16"), (68, 32, "float16"), (252, 16, "float32"),
+                                           (70, 2, "float32"), (172, 1, "float32")])
 def test_rotation_with_wide_mix_matrix(K, P, dtype):
     """Orders above 64 (11008 = 172 * 64 and the like): the mix reads its matrix from global memory.  Any +-1
     matrix exercises the arithmetic; compared with the exact operator built from the same matrix."""
@@ -398,6 +399,45 @@ def test_saliency_cache_hook_vs_reference(golden, case):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("n,q", [(8 * 2048 * 4, 0.99), (100, 0.5), (4097, 0.999), (2, 0.3), (1, 0.99),
+                                 (3_000_001, 0.99), (20_000_000, 0.9)])
+def test_saliency_percentile_clip_vs_oracle(n, q):
+    """Radix selection of the two order statistics + lerp + clamp against the oracle's sort-based restatement of
+    torch.quantile: the cap within one rounding (the lerp may or may not contract to a fused multiply-add), every
+    element below the cap untouched, the rest equal to the cap.  Sizes beyond torch.quantile's 16M limit work."""
+    from gptq_plus_mp_quant_b200 import ops
+    s = torch.exp(3.0 * torch.randn(n, generator=torch.Generator().manual_seed(n % 1000)))
+    s[: n // 7] = s[0]
+    s[n // 3] = -0.0
+    _, cap_ref = ohess.clip_at_percentile(s, q)
+    x = s.to(DEV)
+    cap = ops.clamp_to_quantile_(x, q)
+    assert abs(float(cap) - float(cap_ref)) <= 1.2e-7 * abs(float(cap_ref))
+    assert torch.equal(x.cpu(), torch.clamp(s, max=cap.cpu()))
+    bad = s.clone()
+    bad[n // 2] = float("nan")
+    xb = bad.to(DEV)
+    assert torch.isnan(ops.clamp_to_quantile_(xb, q)) and bool(torch.isnan(xb).all())
+
+
+@pytest.mark.gpu
+def test_saliency_cache_clips_at_percentile():
+    from gptq_plus_mp_quant_b200.gptq_utils.gptq_plus_utils import SaliencyCache
+    lin = torch.nn.Linear(256, 256, bias=False, device=DEV)
+    x = cases.make_acts(2, 300, 256, seed=3).to(DEV)
+    coef = cases.make_out_grad(2, 300, 256, seed=3).to(DEV)
+    got = []
+    for pct in (None, 0.9):
+        cache = SaliencyCache(["lin"], 4, clip_percentile=pct)
+        cache.add_hook({"lin": lin})
+        (lin(x) * coef).sum().backward()
+        got.append(cache.saliency_cache["lin"][0].cpu())
+        cache.clear_hook()
+    ref, _ = ohess.clip_at_percentile(got[0], 0.9)
+    assert torch.allclose(got[1], ref, rtol=2e-7, atol=0) and int((got[1] != got[0]).sum()) > 0
+
+
+@pytest.mark.gpu
 def test_fisher_accumulation_vs_oracle():
     """Layer-output Fisher sum grad^T grad / scale over two batches on the tensor-core Gram kernel."""
     from gptq_plus_mp_quant_b200.gptq_utils.gptq_plus_utils import fisher_accumulate_, fisher_finalize_
@@ -485,12 +525,12 @@ def test_act_quant_wrapper_uses_the_fused_kernel_where_it_applies():
     from gptq_plus_mp_quant_b200.utils.quant_utils import ActQuantWrapper
     assert hu.fwht_act_quant(torch.zeros(4, 1024, device=DEV), None, 1, 1.0, 1.0, 15, True) is None   # not covered
     torch.manual_seed(0)
-    lin = torch.nn.Linear(12288, 32, bias=False, device=DEV, dtype=torch.bfloat16)
+    lin = torch.nn.Linear(4096, 32, bias=False, device=DEV, dtype=torch.bfloat16)
     wrap = ActQuantWrapper(lin)
     wrap.online_full_had = True
-    wrap.had_K, wrap.K = hu.get_hadK(12288)
+    wrap.had_K, wrap.K = hu.get_hadK(4096)
     wrap.quantizer.configure(4, groupsize=-1, sym=False, clip_ratio=0.9)
-    x = cases.make_act_tensor((2, 6, 12288), seed=33).bfloat16().to(DEV)
+    x = cases.make_act_tensor((2, 6, 4096), seed=33).bfloat16().to(DEV)
     y = wrap(x)
     xr = hu.matmul_hadU_cuda(x, wrap.had_K, wrap.K)
     xq = oq.act_fake_quant(xr.cpu(), 4, -1, False, 0.9).to(DEV)

@@ -210,6 +210,22 @@ def test_saliency_hook(golden, case):
     assert torch.equal(sal, t(g[f"{name}.saliency"]))
 
 
+@pytest.mark.parametrize("n,q", [(8192, 0.99), (100, 0.5), (4097, 0.999), (2, 0.3), (1, 0.99), (65536, 0.01)])
+def test_saliency_percentile_clip_is_torch_quantile(n, q):
+    """The oracle's restatement of the hook's outlier clip against the library call the reference makes
+    (torch.quantile + clamp, gptq_plus_utils.py:2834-2839), on log-normal saliencies with ties."""
+    s = cases.make_saliency(1, n, 1, seed=n).flatten()
+    s[: n // 7] = s[0]                                              # ties
+    ref_cap = torch.quantile(s, q)
+    out, cap = ohess.clip_at_percentile(s, q)
+    assert torch.equal(cap, ref_cap)
+    assert torch.equal(out, torch.clamp(s, max=ref_cap))
+    bad = s.clone()
+    bad[n // 2] = float("nan")
+    _, cap = ohess.clip_at_percentile(bad, q)
+    assert torch.isnan(cap) and torch.isnan(torch.quantile(bad, q))
+
+
 @pytest.mark.parametrize("case", cases.ACT_QUANT_CASES, ids=lambda c: c[0])
 def test_act_quantizer(golden, case):
     """ActQuantizer: dynamic per-token / per-token-group ranges and the fake quantization, in the tensor's dtype."""
