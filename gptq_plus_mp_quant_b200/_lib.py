@@ -54,8 +54,8 @@ SIGNATURES = {
     "rq_chol_hinv": (_i, [_vp, _vp, C.POINTER(C.c_float), _vp, _i, _i, _vp, _vp, _sz, _vp]),
     "rq_fq_prepare": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _vp, _vp, _vp]),
     "rq_gptqplus_terms": (_i, [_vp, _vp, _i, _i, _i, _f, _f, _vp, _vp, _vp, _vp, _vp]),
-    "rq_fq_block": (_i, [_vp] * 11 + [_i] * 10 + [_vp, _vp, _i, _i, _vp]),
-    "rq_fq_lazy_update": (_i, [_vp] * 5 + [_i] * 6 + [_vp, _vp, _i, _vp]),
+    "rq_fq_block": (_i, [_vp] * 11 + [_i] * 10 + [_vp, _vp, _i, _i, _f, _vp]),
+    "rq_fq_lazy_update": (_i, [_vp] * 5 + [_i] * 6 + [_vp, _vp, _i, _f, _vp]),
     "rq_fq_run": (_i, [_vp] * 11 + [_i] * 8 + [_vp, _vp, _i, _i, _vp]),
     "rq_fq_tc_workspace_bytes": (_sz, [_i, _i, _i, _i]),
     "rq_fq_tc_prepare": (_i, [_vp, _i, _i, _i, _i, _vp, _sz, _vp]),

@@ -160,6 +160,7 @@ struct BlockArgs {
     const float* beta;       // [R] (surrogate modes)
     int inner_mode;          // 0 frozen, 1 surrogate_block, 2 surrogate_online: GHinv_eff = GHinv + beta*(W - anchor)
     int atomic;              // quantize the whole block from its start values, then solve for the errors
+    float so_scale;          // factor on the in-block weight update (block_gd's second_order_scale); 1 elsewhere
     int mode;                // 0 per-row scale, 1 static groups, 2 dynamic groups
     int dyn_gs;              // mode 2: group width (divides BS)
     int sym;                 // mode 2: range rule
@@ -311,6 +312,7 @@ __global__ void __launch_bounds__(kBlockThreads) block_kernel(const BlockArgs p)
                         upd = __fadd_rn(upd, eff[k]);
                         gh[k] = __fsub_rn(gh[k], __fmul_rn(zi, h));
                     }
+                    if (p.so_scale != 1.f) upd = __fmul_rn(p.so_scale, upd);
                     w[k] = __fsub_rn(w[k], upd);
                 }
             }
@@ -374,7 +376,8 @@ __global__ void __launch_bounds__(gemm::kThreads, 2) lazy_kernel(float* __restri
                                                               const float* __restrict__ Z,
                                                               const float* __restrict__ Eeff,
                                                               const float* __restrict__ Hinv, int R, int C, int Cp,
-                                                              int G, int i1, int count, int step, int plus) {
+                                                              int G, int i1, int count, int step, int plus,
+                                                              float so_scale) {
     extern __shared__ float smem[];
     const int g = blockIdx.z;
     const int Rg = R / G;
@@ -389,7 +392,8 @@ __global__ void __launch_bounds__(gemm::kThreads, 2) lazy_kernel(float* __restri
     if (step == 1) {
         a.A = Eeff + rofs * BS; a.lda = BS;
         a.C = Wp + rofs * C + i2; a.ldc = C;
-        if (plus) { a.Aux = GH + rofs * C + i2; a.ldaux = C; a.gamma = -(float)count; }
+        a.alpha = -so_scale;                                    // block_gd scales the whole weight update
+        if (plus) { a.Aux = GH + rofs * C + i2; a.ldaux = C; a.gamma = -so_scale * (float)count; }
     } else {
         a.A = Z + rofs * C + i1; a.lda = C;
         a.C = GH + rofs * C + i2; a.ldc = C;
@@ -455,7 +459,7 @@ static int fq_block_launch(float* Wp, float* GH, const float* Z, const float* Hi
                            int count, int mode, int dyn_gs, int sym, int maxq, int plus, const float* anchor,
                            const float* beta, int inner_mode, int atomic, void* stream,
                            __nv_bfloat16* Fhi = nullptr, __nv_bfloat16* Flo = nullptr, int far_ld = 0, int far_k0 = 0,
-                           int far_after = 0) {
+                           int far_after = 0, float so_scale = 1.f) {
     using namespace rq::fq;
     if (!Wp || !Hinv || !Q || !codes || !Eeff || R <= 0 || C <= 0 || G <= 0 || R % G != 0) return RQ_ERR_INVALID;
     if (i1 < 0 || count <= 0 || count > BS || i1 + count > C) return RQ_ERR_INVALID;
@@ -468,6 +472,7 @@ static int fq_block_launch(float* Wp, float* GH, const float* Z, const float* Hi
     cudaStream_t st = as_stream(stream);
     BlockArgs p;
     p.anchor = anchor; p.beta = beta; p.inner_mode = inner_mode; p.atomic = atomic ? 1 : 0;
+    p.so_scale = so_scale;
     p.Wp = Wp; p.GH = GH; p.Z = Z; p.Hinv = Hinv; p.Q = Q; p.codes = codes; p.Eeff = Eeff;
     p.Ehi = Ehi; p.Elo = Elo;
     p.Fhi = Fhi; p.Flo = Flo; p.far_ld = far_ld; p.far_k0 = far_k0; p.far_after = (float)far_after;
@@ -495,9 +500,10 @@ extern "C" int rq_fq_block(float* Wp, float* GH, const float* Z, const float* Hi
                            float* Eeff, const float* scale_row, const float* scale_tab, const int* colgrp,
                            float* scale_blk, int R, int C, int G, int i1, int count, int mode, int dyn_gs, int sym,
                            int maxq, int plus, const float* anchor, const float* beta, int inner_mode, int atomic,
-                           void* stream) {
+                           float second_order_scale, void* stream) {
     return fq_block_launch(Wp, GH, Z, Hinv, Q, codes, Eeff, nullptr, nullptr, scale_row, scale_tab, colgrp, scale_blk, R,
-                           C, G, i1, count, mode, dyn_gs, sym, maxq, plus, anchor, beta, inner_mode, atomic, stream);
+                           C, G, i1, count, mode, dyn_gs, sym, maxq, plus, anchor, beta, inner_mode, atomic, stream,
+                           nullptr, nullptr, 0, 0, 0, second_order_scale);
 }
 
 static int surrogate_outer(float* Wp, const float* anchor, const float* beta, int R, int C, int i2, int count,
@@ -509,7 +515,7 @@ static int surrogate_outer(float* Wp, const float* anchor, const float* beta, in
 
 extern "C" int rq_fq_lazy_update(float* Wp, float* GH, const float* Z, const float* Eeff, const float* Hinv, int R,
                                  int C, int G, int i1, int count, int plus, const float* anchor, const float* beta,
-                                 int outer_surrogate, void* stream) {
+                                 int outer_surrogate, float second_order_scale, void* stream) {
     if (!Wp || !Eeff || !Hinv || R <= 0 || C <= 0 || G <= 0 || R % G != 0 || count <= 0 || count > fq::BS)
         return RQ_ERR_INVALID;
     if (plus && (!GH || !Z)) return RQ_ERR_INVALID;
@@ -525,9 +531,11 @@ extern "C" int rq_fq_lazy_update(float* Wp, float* GH, const float* Z, const flo
         const int rc0 = surrogate_outer(Wp, anchor, beta, R, C, i2, count, st);
         if (rc0 != RQ_OK) return rc0;
     }
-    fq::lazy_kernel<<<grid, gemm::kThreads, gemm::kSmemBytes, st>>>(Wp, GH, Z, Eeff, Hinv, R, C, Cp, G, i1, count, 1, plus);
+    fq::lazy_kernel<<<grid, gemm::kThreads, gemm::kSmemBytes, st>>>(Wp, GH, Z, Eeff, Hinv, R, C, Cp, G, i1, count, 1, plus,
+                                                                    second_order_scale);
     if (plus)
-        fq::lazy_kernel<<<grid, gemm::kThreads, gemm::kSmemBytes, st>>>(Wp, GH, Z, Eeff, Hinv, R, C, Cp, G, i1, count, 2, plus);
+        fq::lazy_kernel<<<grid, gemm::kThreads, gemm::kSmemBytes, st>>>(Wp, GH, Z, Eeff, Hinv, R, C, Cp, G, i1, count, 2, plus,
+                                                                        1.f);
     return check_launch();
 }
 
@@ -564,9 +572,10 @@ extern "C" int rq_fq_run(float* Wp, float* GH, const float* Z, const float* Hinv
         const int last = i1 + count >= C;
         int rc = rq_fq_block(Wp, GH, Z, Hinv, Q, codes, Eeff, scale_row, scale_tab, colgrp, scale_blk, R, C, G, i1,
                              count, mode, dyn_gs, sym, maxq, plus, anchor, beta, inner_mode, (atomic && !last) ? 1 : 0,
-                             stream);
+                             1.f, stream);
         if (rc != RQ_OK) return rc;
-        rc = rq_fq_lazy_update(Wp, GH, Z, Eeff, Hinv, R, C, G, i1, count, plus, anchor, beta, inner_mode != 0, stream);
+        rc = rq_fq_lazy_update(Wp, GH, Z, Eeff, Hinv, R, C, G, i1, count, plus, anchor, beta, inner_mode != 0, 1.f,
+                               stream);
         if (rc != RQ_OK) return rc;
     }
     return RQ_OK;

@@ -6,6 +6,7 @@ from __future__ import annotations
 
 import ctypes
 import logging
+import math
 import os
 from contextlib import nullcontext
 
@@ -153,7 +154,7 @@ _INNER_MODES = {"frozen": 0, "surrogate_block": 1, "surrogate_online": 2}
 
 
 def _quantize_linear(layer, W32, H3, perm, grads, quantizer, G, alpha_eff, ref_loss, plus, Hinv, mode_pack,
-                     export_to_et, permute_export, rec=None, inner_mode=0, atomic=False, refresh=None):
+                     export_to_et, permute_export, rec=None, inner_mode=0, atomic=False, refresh=None, gd_pack=None):
     dev = W32.device
     R, Cc = W32.shape
     mode, scale_row, scale_tab, colgrp, scale_blk, dyn_gs = mode_pack
@@ -202,7 +203,11 @@ def _quantize_linear(layer, W32, H3, perm, grads, quantizer, G, alpha_eff, ref_l
         codes = torch.empty(R, Cc, dtype=torch.int8, device=dev)
         Eeff = torch.empty(R, BS, dtype=torch.float32, device=dev)
         with _sec(rec, "fasterquant.block.total"):
-            if refresh is not None:
+            if gd_pack is not None:
+                gd, gd_refresh, gd_groupsize, gd_static = gd_pack
+                _block_gd_loop(gd, gd_refresh, quantizer, W32, Wp, GH, Z, Hinv, Q, codes, Eeff, mode_pack, perm, G,
+                               plus, 1 if quantizer.sym else 0, maxq, atomic, gd_groupsize, gd_static, H3, st, rec)
+            elif refresh is not None:
                 beta, Z, GH = _block_backward_loop(
                     refresh, W32, Wp, GH, Z, beta, Hinv, Q, codes, Eeff, mode_pack, perm, G, alpha_eff, ref_loss,
                     plus, 1 if quantizer.sym else 0, maxq, atomic, st, rec)
@@ -249,6 +254,7 @@ _OBSERVER_NONE_KEYS = (
     "sine_regularizer_update_abs_mean", "sine_regularizer_update_mean_row_l2")
 _OBSERVER_META_KEYS = ("mean_refresh_loss", "train_mean_refresh_loss", "val_mean_refresh_loss",
                        "refresh_subset_mean_refresh_loss")
+_GD_META_KEYS = ("slide_alpha", "mean_refresh_loss_current", "mean_refresh_loss_next")
 
 
 def _block_backward_loop(refresh, W32, Wp, GH, Z, beta, Hinv, Q, codes, Eeff, mode_pack, perm, G, alpha_eff,
@@ -273,7 +279,7 @@ def _block_backward_loop(refresh, W32, Wp, GH, Z, beta, Hinv, Q, codes, Eeff, mo
                                             _lib.ptr(codes), _lib.ptr(Eeff), _lib.ptr(scale_row), _lib.ptr(scale_tab),
                                             _lib.ptr(colgrp), _lib.ptr(scale_blk), R, Cc, G, i1, count, mode, dyn_gs,
                                             sym, maxq, 1 if plus else 0, _lib.ptr(anchor), _lib.ptr(beta),
-                                            2 if plus else 0, 1 if (atomic and i2 < Cc) else 0, st))
+                                            2 if plus else 0, 1 if (atomic and i2 < Cc) else 0, 1.0, st))
         if enabled:
             if refresh_fn is None:
                 raise ValueError("`gradient_refresh_fn` must be provided for g_update_mode='block_backward'.")
@@ -310,8 +316,246 @@ def _block_backward_loop(refresh, W32, Wp, GH, Z, beta, Hinv, Q, codes, Eeff, mo
         with _sec(rec, "fasterquant.block.outer_update_delta_w"):
             _lib.check("rq_fq_lazy_update",
                        _lib.lib.rq_fq_lazy_update(_lib.ptr(Wp), _lib.ptr(GH), _lib.ptr(Z), _lib.ptr(Eeff),
-                                                  _lib.ptr(Hinv), R, Cc, G, i1, count, 1 if plus else 0, 0, 0, 0, st))
+                                                  _lib.ptr(Hinv), R, Cc, G, i1, count, 1 if plus else 0, 0, 0, 0, 1.0,
+                                                  st))
     return beta, Z, GH
+
+
+# ----------------------------------------------------------------------------------------------
+# block_gd: optimizer steps on the trailing weights between blocks (gptq_plus_utils.py:586-795, 1572-1848)
+# ----------------------------------------------------------------------------------------------
+GD_DEFAULTS = dict(grad_lr=1e-3, grad_optimizer="sgd", curvature_damping=0.1, grad_reg_strategy="none",
+                   grad_reg_lambda=0.0, grad_gate_floor=0.1, grad_gate_sharpness=1.0, grad_gate_sine_amp=0.0,
+                   second_order_scale=1.0, grad_clip=1.0, slide_refresh_start=0, slide_refresh_block_total=None)
+_GD_STRATEGIES = ("none", "l2", "hessian", "quant_error_gate", "quant_error_gate_optimized")
+
+
+def _validate_gd(gd):
+    """gptq_plus_utils.py:586-589, 666-686."""
+    if gd["grad_optimizer"] not in ("sgd", "adam", "h_adam"):
+        raise ValueError(f"Unsupported `grad_optimizer={gd['grad_optimizer']}`. Expected one of: sgd, adam, h_adam.")
+    if gd["grad_reg_strategy"] not in _GD_STRATEGIES:
+        raise ValueError(f"Unsupported `grad_reg_strategy={gd['grad_reg_strategy']}`. Expected one of: "
+                         f"{', '.join(sorted(_GD_STRATEGIES))}.")
+    if gd["grad_reg_lambda"] < 0:
+        raise ValueError(f"`grad_reg_lambda` must be non-negative. Got {gd['grad_reg_lambda']}.")
+    if not (0.0 <= gd["grad_gate_floor"] <= 1.0):
+        raise ValueError(f"`grad_gate_floor` must be in [0, 1]. Got {gd['grad_gate_floor']}.")
+    if gd["grad_gate_sharpness"] < 0:
+        raise ValueError(f"`grad_gate_sharpness` must be non-negative. Got {gd['grad_gate_sharpness']}.")
+    if gd["grad_gate_sine_amp"] < 0:
+        raise ValueError(f"`grad_gate_sine_amp` must be non-negative. Got {gd['grad_gate_sine_amp']}.")
+
+
+class _TrailingOptimizer:
+    """SGD / Adam / curvature-preconditioned Adam on the not yet quantized columns of all row groups at once
+    (gptq_plus_utils.py:586-663; the groups' states advance in lockstep, so one [G, R/G, C] state serves them).
+    ``curvature``: [G, 1, C] for h_adam."""
+
+    def __init__(self, kind, G, Rg, Cc, device, curvature=None):
+        self.kind, self.step = kind, 0
+        self.m = torch.zeros(G, Rg, Cc, dtype=torch.float32, device=device) if kind != "sgd" else None
+        self.v = torch.zeros(G, Rg, Cc, dtype=torch.float32, device=device) if kind == "adam" else None
+        self.curvature = curvature
+
+    def clear(self, c0, c1):
+        if self.m is not None:
+            self.m[:, :, c0:c1].zero_()
+        if self.v is not None:
+            self.v[:, :, c0:c1].zero_()
+
+    def update(self, grad3, col_start, lr, clip, b1=0.9, b2=0.999, eps=1e-8):
+        g = grad3[:, :, col_start:]
+        if g.numel() == 0:
+            return g
+        if clip is not None and clip > 0:
+            g = g.clamp(min=-clip, max=clip)
+        if self.kind == "sgd":
+            return lr * g
+        self.step += 1
+        m = self.m[:, :, col_start:]
+        m.mul_(b1).add_(g, alpha=1 - b1)
+        bc1 = 1 - b1 ** self.step
+        if self.kind == "h_adam":
+            return (lr / bc1) * (m / (self.curvature[:, :, col_start:].sqrt() + eps))
+        v = self.v[:, :, col_start:]
+        v.mul_(b2).addcmul_(g, g, value=1 - b2)
+        denom = v.sqrt() / math.sqrt(1 - b2 ** self.step)
+        denom.add_(eps)
+        return (lr / bc1) * (m / denom)
+
+
+def _gd_setup(gd, quantizer, W32, Wp, H3, perm, G, groupsize, static_groups):
+    """Per-linear state of the regularisers and of h_adam, in the permuted column order of ``Wp`` [R, C]."""
+    dev = Wp.device
+    R, Cc = Wp.shape
+    Rg = R // G
+    st = {}
+    strategy = gd["grad_reg_strategy"]
+    need_h = strategy == "hessian" or gd["grad_optimizer"] == "h_adam"
+    if need_h:
+        diag = torch.diagonal(H3, dim1=1, dim2=2).clone()                 # [G, C]
+        dead = diag == 0
+    if gd["grad_optimizer"] == "h_adam":                                   # input-only KFAC diagonal (:4601-4640)
+        a = torch.where(dead, torch.ones_like(diag), diag)
+        if perm is not None:
+            a = a[:, perm]
+        a = a.clamp_min(0.0)
+        a = a / a.mean(dim=1, keepdim=True).clamp_min(1e-12)
+        if gd["curvature_damping"] and gd["curvature_damping"] > 0:
+            a = a + float(gd["curvature_damping"])
+        st["curvature"] = a.view(G, 1, Cc)
+    if strategy in ("l2", "hessian"):
+        st["full_precision"] = Wp.clone()
+    if strategy == "hessian":                                              # dead-fixed, permuted H (:1062-1064)
+        Hr = H3.clone()
+        idx = torch.arange(Cc, device=dev)
+        Hr[:, idx, idx] = torch.where(dead, torch.ones_like(diag), diag)
+        if perm is not None:
+            Hr = Hr[:, perm][:, :, perm]
+        st["hessian_reg"] = Hr.contiguous()
+    if strategy in ("quant_error_gate", "quant_error_gate_optimized"):     # :688-722
+        if groupsize == -1:
+            st["gate_scale"] = quantizer.scale.to(dev, torch.float32).reshape(R, 1).expand(R, Cc)
+            st["gate_zero"] = quantizer.zero.to(dev, torch.float32).reshape(R, 1).expand(R, Cc)
+        else:
+            if not static_groups:
+                raise ValueError("`groups` must be provided when groupsize != -1.")
+            tab_s, tab_z = quant_utils.find_params_groups(W32, groupsize, int(quantizer.maxq), quantizer.sym,
+                                                          quantizer.mse, quantizer.norm, quantizer.grid,
+                                                          quantizer.maxshrink)
+            cols = perm if perm is not None else torch.arange(Cc, device=dev)
+            ids = (cols // groupsize).long()
+            st["gate_scale"] = tab_s[ids].t().contiguous()                 # [R, C]
+            st["gate_zero"] = tab_z[ids].t().contiguous()
+    st["opt"] = _TrailingOptimizer(gd["grad_optimizer"], G, Rg, Cc, dev, st.get("curvature"))
+    return st
+
+
+def _gd_regularize(gd, st, current, raw, col_start, G, maxq, sym):
+    """(update, gate part, sine part) of the first-order step (gptq_plus_utils.py:730-795); ``current`` [R, C] holds
+    the quantized columns left of ``col_start`` and the working weights from there on; ``raw`` [R, C - col_start]."""
+    strategy, lr, lam = gd["grad_reg_strategy"], gd["grad_lr"], gd["grad_reg_lambda"]
+    zero = None
+    if raw.numel() == 0 or strategy == "none":
+        return raw, zero, zero
+    trailing = current[:, col_start:]
+    if strategy == "l2":
+        reg = lr * lam * (trailing - st["full_precision"][:, col_start:])
+        return raw + reg, reg, zero
+    if strategy == "hessian":
+        R, Cc = current.shape
+        diff = (current - st["full_precision"]).view(G, R // G, Cc)
+        reg = lr * lam * torch.bmm(diff, st["hessian_reg"][:, :, col_start:]).view(R, Cc - col_start)
+        return raw + reg, reg, zero
+    sc = st["gate_scale"][:, col_start:].clamp(min=1e-8)
+    zr = st["gate_zero"][:, col_start:]
+    if sym:
+        nearest = sc * torch.clamp(torch.round(trailing / sc), -(maxq + 1), maxq)
+    else:
+        nearest = sc * (torch.clamp(torch.round(trailing / sc) + zr, 0, maxq) - zr)
+    distance = (trailing - nearest).abs() / sc
+    floor = gd["grad_gate_floor"]
+    gate = floor + (1.0 - floor) * (1.0 - torch.exp(-gd["grad_gate_sharpness"] * distance))
+    gated = raw * gate
+    if strategy == "quant_error_gate":
+        return gated, gated - raw, zero
+    phase = 2 * math.pi * (trailing / sc) if sym else 2 * math.pi * ((trailing / sc) + zr)
+    sine = lr * (gd["grad_gate_sine_amp"] * (2 * math.pi / sc) * torch.sin(phase))
+    return gated + sine, gated - raw, sine
+
+
+def _abs_stats(t):
+    """(mean |t|, mean row l2) of a [R, n] tensor, or (None, None) when empty."""
+    if t is None or t.numel() == 0:
+        return None, None
+    return t.abs().mean().item(), torch.linalg.norm(t, dim=1).mean().item()
+
+
+def _block_gd_loop(gd, refresh, quantizer, W32, Wp, GH, Z, Hinv, Q, codes, Eeff, mode_pack, perm, G, plus, sym, maxq,
+                   atomic, groupsize, static_groups, H3, st, rec):
+    """``g_update_mode="block_gd"`` (gptq_plus_utils.py:1190, 1344-1349, 1546-1848): frozen first-order terms inside
+    the kernels, the weight updates scaled by ``second_order_scale``; after every block but the last the caller's
+    ``gradient_refresh_fn`` sees the current weights and an optimizer step (with the chosen regulariser) moves the
+    columns that are still to be quantized.  Kernels: rq_fq_block / rq_fq_lazy_update per block; the optimizer
+    arithmetic is elementwise torch on the device, as in the reference."""
+    refresh_fn, observer, enabled, full_metrics = refresh
+    dev = Wp.device
+    R, Cc = Wp.shape
+    Rg = R // G
+    mode, scale_row, scale_tab, colgrp, scale_blk, dyn_gs = mode_pack
+    inv = torch.argsort(perm) if perm is not None else None
+    state = _gd_setup(gd, quantizer, W32, Wp, H3, perm, G, groupsize, static_groups)
+    opt = state["opt"]
+    so = float(gd["second_order_scale"])
+    n_refresh_total = max((Cc + BS - 1) // BS - 1, 0)
+    Cp = Hinv.shape[-1]
+    for i1 in range(0, Cc, BS):
+        count = min(BS, Cc - i1)
+        i2 = i1 + count
+        with _sec(rec, "fasterquant.block.inner_loop"):
+            _lib.check("rq_fq_block",
+                       _lib.lib.rq_fq_block(_lib.ptr(Wp), _lib.ptr(GH), _lib.ptr(Z), _lib.ptr(Hinv), _lib.ptr(Q),
+                                            _lib.ptr(codes), _lib.ptr(Eeff), _lib.ptr(scale_row), _lib.ptr(scale_tab),
+                                            _lib.ptr(colgrp), _lib.ptr(scale_blk), R, Cc, G, i1, count, mode, dyn_gs,
+                                            sym, maxq, 1 if plus else 0, 0, 0, 0,
+                                            1 if (atomic and i2 < Cc) else 0, so, st))
+        second = None
+        if full_metrics and i2 < Cc:                    # applied second-order part of the lazy update, for the report
+            err = Eeff[:, :count]
+            if plus:
+                err = err + torch.arange(count - 1, -1, -1, device=dev, dtype=torch.float32) * Z[:, i1:i2]
+            second = so * torch.bmm(err.reshape(G, Rg, count), Hinv.view(G, Cp, Cp)[:, i1:i2, i2:Cc]).view(R, Cc - i2)
+        with _sec(rec, "fasterquant.block.outer_update_delta_w"):
+            _lib.check("rq_fq_lazy_update",
+                       _lib.lib.rq_fq_lazy_update(_lib.ptr(Wp), _lib.ptr(GH), _lib.ptr(Z), _lib.ptr(Eeff),
+                                                  _lib.ptr(Hinv), R, Cc, G, i1, count, 1 if plus else 0, 0, 0, 0, so,
+                                                  st))
+        opt.clear(i1, i2)
+        if not (enabled and i2 < Cc):
+            continue
+        if refresh_fn is None:
+            raise ValueError("`gradient_refresh_fn` must be provided for g_update_mode='block_gd'.")
+        with _sec(rec, "fasterquant.block.true_gradient_refresh"):
+            current = Wp.clone()
+            current[:, :i2] = Q[:, :i2]
+            total = gd["slide_refresh_block_total"] if gd["slide_refresh_block_total"] is not None else n_refresh_total
+            idx = gd["slide_refresh_start"] + i1 // BS
+            slide_alpha = 1.0 - idx / max(total - 1, 1) if total > 1 else 1.0
+            refreshed, meta = refresh_fn(current[:, inv] if inv is not None else current, slide_alpha=slide_alpha)
+            refreshed = refreshed.to(dev).float()
+            Gp = (refreshed[:, perm] if perm is not None else refreshed).contiguous()
+            raw = opt.update(Gp.view(G, Rg, Cc), i2, gd["grad_lr"], gd["grad_clip"]).reshape(R, Cc - i2)
+            update, gate_part, sine_part = _gd_regularize(gd, state, current, raw, i2, G, maxq, bool(sym))
+            if observer is not None:
+                report = {"block_idx": i1 // BS, "col_start": i1, "col_end": i2, "remaining_columns": Cc - i2,
+                          "remaining_grad_abs_mean": None, "remaining_grad_clipped_abs_mean": None,
+                          "remaining_grad_mean_row_l2": None}
+                report.update({k: None for k in _OBSERVER_NONE_KEYS})
+                if full_metrics:
+                    trailing = Gp[:, i2:]
+                    clip = gd["grad_clip"]
+                    report["remaining_grad_abs_mean"], report["remaining_grad_mean_row_l2"] = _abs_stats(trailing)
+                    report["remaining_grad_clipped_abs_mean"] = (
+                        trailing.clamp(min=-clip, max=clip).abs().mean().item() if clip is not None and clip > 0
+                        else report["remaining_grad_abs_mean"])
+                    for key, t in (("second_order_update", second), ("first_order_update", update)):
+                        report[key + "_abs_mean"], report[key + "_mean_row_l2"] = _abs_stats(t)
+                        if t is not None and t.numel() > 0:
+                            a = t.abs()
+                            report[key + "_abs_max"] = a.max().item()
+                            report[key + "_abs_q99"] = ops.clamp_to_quantile_(a.flatten().clone(), 0.99).item()
+                    report["first_order_raw_abs_mean"], report["first_order_raw_mean_row_l2"] = _abs_stats(raw)
+                    zeros = torch.zeros_like(update)
+                    report["regularizer_update_abs_mean"], report["regularizer_update_mean_row_l2"] = _abs_stats(
+                        gate_part if gate_part is not None else zeros)
+                    (report["sine_regularizer_update_abs_mean"],
+                     report["sine_regularizer_update_mean_row_l2"]) = _abs_stats(sine_part if sine_part is not None else zeros)
+                report.update({k: None if meta is None else meta.get(k) for k in _OBSERVER_META_KEYS + _GD_META_KEYS})
+                observer(report)
+        with _sec(rec, "fasterquant.block.outer_update_grad_descent"):
+            if update.numel() > 0:
+                Wp[:, i2:] -= update
 
 
 def _check_common(quantizer, blocksize):
@@ -511,20 +755,17 @@ def gptaq_fasterquant(obj, H, blocksize, percdamp, groupsize, actorder, static_g
 def plus_fasterquant(obj, blocksize, percdamp, groupsize, actorder, static_groups, enable_gradient_update,
                      g_update_mode, export_to_et, profile_recorder, gradient_refresh_fn, grad_reg_strategy,
                      second_order_scale, block_atomic_quant, block_observer, diagnostic_recorder, grad_clip=1.0,
-                     refresh_full_metrics=False):
-    if g_update_mode == "block_gd":
-        raise NotImplementedError(
-            "g_update_mode='block_gd' (an optimizer step on the trailing weights between blocks, "
-            "gptq_plus_utils.py:1572-1848) is not built; 'frozen', 'surrogate_block', 'surrogate_online' and "
-            "'block_backward' are")
-    if g_update_mode not in _INNER_MODES and g_update_mode != "block_backward":
+                     refresh_full_metrics=False, gd=None):
+    if g_update_mode not in _INNER_MODES and g_update_mode not in ("block_backward", "block_gd"):
         raise ValueError(f"Unknown g_update_mode '{g_update_mode}'")
+    gd_mode = g_update_mode == "block_gd"
+    if gd_mode:
+        gd = dict(GD_DEFAULTS, **(gd or {}))
+        _validate_gd(gd)
     if (g_update_mode != "frozen" or block_atomic_quant) and blocksize != BS:
         raise NotImplementedError(
             f"surrogate modes and block_atomic_quant depend on the block boundaries: blocksize must be {BS}, "
             f"got {blocksize}")
-    if grad_reg_strategy != "none":
-        raise NotImplementedError("gradient regularisers belong to the block_gd refresh path, which stays in PyTorch")
     if diagnostic_recorder is not None:
         raise NotImplementedError("the tensor-dump recorder needs the per-column intermediates of the PyTorch path")
     layer, dev = obj.layer, obj.dev
@@ -550,9 +791,13 @@ def plus_fasterquant(obj, blocksize, percdamp, groupsize, actorder, static_group
     alpha_eff = obj.alpha / (obj.rows * obj.columns) if plus else 0.0
     refresh = ((gradient_refresh_fn, block_observer, bool(enable_gradient_update), grad_clip,
                 bool(refresh_full_metrics)) if g_update_mode == "block_backward" else None)
+    gd_pack = None
+    if gd_mode:
+        gd_pack = (gd, (gradient_refresh_fn, block_observer, bool(enable_gradient_update),
+                        bool(refresh_full_metrics)), groupsize, static_groups)
     if getattr(obj, "group_owners", None) is not None:
-        if refresh is not None:
-            raise NotImplementedError("block_backward needs every row group on one rank (the callback sees the "
+        if refresh is not None or gd_pack is not None:
+            raise NotImplementedError(f"{g_update_mode} needs every row group on one rank (the callback sees the "
                                       "whole weight); use hessian_owner instead of group_owners")
         _quantize_owned_groups(obj, W32, H3, perm, grads, alpha_eff, plus, percdamp, groupsize, static_groups,
                                blocksize, export_to_et, rec, _INNER_MODES.get(g_update_mode, 0),
@@ -565,6 +810,6 @@ def plus_fasterquant(obj, blocksize, percdamp, groupsize, actorder, static_group
     state = _quantize_linear(layer, W32, H3, perm, grads, obj.quantizer, G, alpha_eff, obj.reference_loss, plus, Hinv,
                              mode_pack, export_to_et, permute_export=True, rec=rec,
                              inner_mode=_INNER_MODES.get(g_update_mode, 0), atomic=bool(block_atomic_quant),
-                             refresh=refresh)
+                             refresh=refresh, gd_pack=gd_pack)
     obj._last_fasterquant = {"Hinv": Hinv if KEEP_INTERMEDIATES else None, "perm": perm, "damp_percent": damp,
                              "identity_fallback": identity, **state}

@@ -219,7 +219,13 @@ class GPTQPlus:
                 gradient_refresh_fn=gradient_refresh_fn, grad_reg_strategy=grad_reg_strategy,
                 second_order_scale=second_order_scale, block_atomic_quant=block_atomic_quant,
                 block_observer=block_observer, diagnostic_recorder=diagnostic_recorder, grad_clip=grad_clip,
-                refresh_full_metrics=refresh_full_metrics)
+                refresh_full_metrics=refresh_full_metrics,
+                gd=dict(grad_lr=grad_lr, grad_optimizer=grad_optimizer, curvature_damping=curvature_damping,
+                        grad_reg_strategy=grad_reg_strategy, grad_reg_lambda=grad_reg_lambda,
+                        grad_gate_floor=grad_gate_floor, grad_gate_sharpness=grad_gate_sharpness,
+                        grad_gate_sine_amp=grad_gate_sine_amp, second_order_scale=second_order_scale,
+                        grad_clip=grad_clip, slide_refresh_start=slide_refresh_start,
+                        slide_refresh_block_total=slide_refresh_block_total))
         if torch.any(torch.isnan(self.layer.weight.data)):
             logging.warning("NaN in weights")
             raise ValueError("NaN in weights")

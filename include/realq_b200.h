@@ -275,14 +275,16 @@ int rq_gptqplus_terms(const float* Gp, const float* Hinv, int R, int C, int G, f
  * beta * (W - anchor) to the first-order term (gptq_utils/gptq_plus_utils.py:580-584, 1190-1200, 1360-1367, 1500-1509;
  * anchor = Wp as it was before the first block, beta [R] from rq_gptqplus_terms); atomic != 0 quantizes the whole
  * block from its start values and obtains Err from the triangular solve Err . Hinv[i1:i2, i1:i2] = W - Q - GHinv
- * (:1238-1288; rq_fq_run never applies it to the last block, :1174). */
+ * (:1238-1288; rq_fq_run never applies it to the last block, :1174).
+ * second_order_scale (rq_fq_block, rq_fq_lazy_update): factor on the weight update of W, 1 everywhere except in
+ * g_update_mode="block_gd" (:1344-1349, 1546-1550), whose optimizer steps between the blocks stay on the host. */
 int rq_fq_block(float* Wp, float* GH, const float* Z, const float* Hinv, float* Q, int8_t* codes, float* Eeff,
                 const float* scale_row, const float* scale_tab, const int* colgrp, float* scale_blk, int R, int C,
                 int G, int i1, int count, int mode, int dyn_gs, int sym, int maxq, int plus, const float* anchor,
-                const float* beta, int inner_mode, int atomic, void* stream);
+                const float* beta, int inner_mode, int atomic, float second_order_scale, void* stream);
 int rq_fq_lazy_update(float* Wp, float* GH, const float* Z, const float* Eeff, const float* Hinv, int R, int C, int G,
                       int i1, int count, int plus, const float* anchor, const float* beta, int outer_surrogate,
-                      void* stream);
+                      float second_order_scale, void* stream);
 int rq_fq_run(float* Wp, float* GH, const float* Z, const float* Hinv, float* Q, int8_t* codes, float* Eeff,
               const float* scale_row, const float* scale_tab, const int* colgrp, float* scale_blk, int R, int C, int G,
               int mode, int dyn_gs, int sym, int maxq, int plus, const float* anchor, const float* beta,

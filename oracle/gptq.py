@@ -183,6 +183,131 @@ def plain_fasterquant(weight: torch.Tensor, H: torch.Tensor, quantizer, blocksiz
 # --------------------------------------------------------------------------------------
 # GPTQ+
 # --------------------------------------------------------------------------------------
+GD_DEFAULTS = dict(grad_lr=1e-3, grad_optimizer="sgd", curvature_damping=0.1, grad_reg_strategy="none",
+                   grad_reg_lambda=0.0, grad_gate_floor=0.1, grad_gate_sharpness=1.0, grad_gate_sine_amp=0.0,
+                   second_order_scale=1.0, grad_clip=1.0, slide_refresh_start=0, slide_refresh_block_total=None)
+
+
+def validate_regularizer(gd):
+    """gptq_plus_utils.py:666-686."""
+    if gd["grad_reg_strategy"] not in ("none", "l2", "hessian", "quant_error_gate", "quant_error_gate_optimized"):
+        raise ValueError(f"Unsupported `grad_reg_strategy={gd['grad_reg_strategy']}`.")
+    if gd["grad_reg_lambda"] < 0 or gd["grad_gate_sharpness"] < 0 or gd["grad_gate_sine_amp"] < 0:
+        raise ValueError("regulariser weights must be non-negative")
+    if not 0.0 <= gd["grad_gate_floor"] <= 1.0:
+        raise ValueError("`grad_gate_floor` must be in [0, 1]")
+
+
+def input_curvature_diag(h_diag, damping):
+    """Input-only KFAC diagonal of H-Adam (gptq_plus_utils.py:4601-4640 with output_fisher=None): the Hessian
+    diagonal clamped at 0, normalised to unit mean, plus the damping; [1, C]."""
+    a = h_diag.float().clamp_min(0.0)
+    a = a / a.mean().clamp_min(1e-12)
+    cur = a.view(1, -1)
+    if damping and damping > 0:
+        cur = cur + float(damping)
+    return cur
+
+
+def make_optimizer_state(w_sub, kind, curvature=None):
+    """gptq_plus_utils.py:586-605."""
+    if kind not in ("sgd", "adam", "h_adam"):
+        raise ValueError(f"Unsupported `grad_optimizer={kind}`. Expected one of: sgd, adam, h_adam.")
+    state = {"type": kind, "step": 0}
+    if kind in ("adam", "h_adam"):
+        state["m"] = torch.zeros_like(w_sub)
+    if kind == "adam":
+        state["v"] = torch.zeros_like(w_sub)
+    if kind == "h_adam":
+        if curvature is None:
+            raise ValueError("h_adam requires the curvature diagonal")
+        state["curvature"] = curvature
+    return state
+
+
+def clear_optimizer_state(state, c0, c1):
+    """gptq_plus_utils.py:607-615."""
+    if state is None or c1 <= c0:
+        return
+    if "m" in state:
+        state["m"][:, c0:c1].zero_()
+    if "v" in state:
+        state["v"][:, c0:c1].zero_()
+
+
+def optimizer_update(state, grad_sub, col_start, lr, grad_clip=1.0, b1=0.9, b2=0.999, eps=1e-8):
+    """Step of the trailing columns (gptq_plus_utils.py:617-663): SGD, Adam, or Adam's first moment preconditioned
+    by the fixed curvature diagonal."""
+    g = grad_sub[:, col_start:]
+    if g.numel() == 0:
+        return g
+    if grad_clip is not None and grad_clip > 0:
+        g = g.clamp(min=-grad_clip, max=grad_clip)
+    if state["type"] == "sgd":
+        return lr * g
+    state["step"] += 1
+    m = state["m"][:, col_start:]
+    m.mul_(b1).add_(g, alpha=1 - b1)
+    bc1 = 1 - b1 ** state["step"]
+    if state["type"] == "h_adam":
+        denom = state["curvature"][:, col_start:].sqrt() + eps
+        return (lr / bc1) * (m / denom)
+    v = state["v"][:, col_start:]
+    v.mul_(b2).addcmul_(g, g, value=1 - b2)
+    bc2 = 1 - b2 ** state["step"]
+    denom = v.sqrt() / math.sqrt(bc2)
+    denom.add_(eps)
+    return (lr / bc1) * (m / denom)
+
+
+def gate_quant_maps(quantizer, w_sub, groupsize, r0, r1, groups=None, perm=None):
+    """Per-element scale / zero of the grid each weight will be rounded to (gptq_plus_utils.py:688-722)."""
+    gs, gz = torch.zeros_like(w_sub), torch.zeros_like(w_sub)
+    if groupsize == -1:
+        gs.copy_(quantizer.scale[r0:r1].expand_as(w_sub))
+        gz.copy_(quantizer.zero[r0:r1].expand_as(w_sub))
+        return gs, gz
+    if groups is None:
+        raise ValueError("`groups` must be provided when groupsize != -1.")
+    ids = (torch.arange(w_sub.shape[1]) if perm is None else perm) // groupsize
+    for gid, q in enumerate(groups):
+        mask = ids == gid
+        n = int(mask.sum())
+        if n:
+            gs[:, mask] = q.scale[r0:r1].expand(-1, n)
+            gz[:, mask] = q.zero[r0:r1].expand(-1, n)
+    return gs, gz
+
+
+def regularized_update(st, current, raw, col_start, gd, maxq, sym):
+    """First-order step after the regulariser (gptq_plus_utils.py:730-795)."""
+    if raw.numel() == 0:
+        return raw
+    strategy, lr, lam = gd["grad_reg_strategy"], gd["grad_lr"], gd["grad_reg_lambda"]
+    trailing = current[:, col_start:]
+    if strategy == "none":
+        return raw
+    if strategy == "l2":
+        return raw + lr * lam * (trailing - st["full_precision"][:, col_start:])
+    if strategy == "hessian":
+        return raw + lr * lam * (current - st["full_precision"]).matmul(st["hessian_reg"][:, col_start:])
+    sc = st["gate_scale"][:, col_start:].clamp(min=1e-8)
+    zr = st["gate_zero"][:, col_start:]
+    if sym:
+        nearest = sc * torch.clamp(torch.round(trailing / sc), -(maxq + 1), maxq)
+    else:
+        nearest = sc * (torch.clamp(torch.round(trailing / sc) + zr, 0, maxq) - zr)
+    distance = (trailing - nearest).abs() / sc
+    floor = gd["grad_gate_floor"]
+    gate = floor + (1.0 - floor) * (1.0 - torch.exp(-gd["grad_gate_sharpness"] * distance))
+    gated = raw * gate
+    if strategy == "quant_error_gate":
+        return gated
+    phase = 2 * math.pi * (trailing / sc) if sym else 2 * math.pi * ((trailing / sc) + zr)
+    sine = gd["grad_gate_sine_amp"] * (2 * math.pi / sc) * torch.sin(phase)
+    return gated + lr * sine
+
+
 def _effective_ghinv(base, cur_w, ref_w, bview, mode):
     """gptq_plus_utils.py:580-584."""
     if mode == "frozen":
@@ -193,13 +318,20 @@ def _effective_ghinv(base, cur_w, ref_w, bview, mode):
 def plus_fasterquant(weight, H, act_square, gradients, quantizer, num_groups, alpha, reference_loss,
                      blocksize=128, percdamp=0.01, groupsize=-1, actorder=False, static_groups=False,
                      enable_gradient_update=True, g_update_mode="frozen", block_atomic_quant=False,
-                     gradient_refresh_fn=None):
-    """GPTQ+ quantization of one linear (gptq_plus_utils.py:910-1896) for the callback-free
-    modes.  ``H`` is the finalised ``[G, C, C]`` Hessian.  Returns dict(Q, W_int, Scale,
+                     gradient_refresh_fn=None, gd=None):
+    """GPTQ+ quantization of one linear (gptq_plus_utils.py:910-1896).  ``gd`` (g_update_mode="block_gd"): dict
+    with grad_lr, grad_optimizer, curvature_damping, grad_reg_strategy, grad_reg_lambda, grad_gate_floor,
+    grad_gate_sharpness, grad_gate_sine_amp, second_order_scale, grad_clip, slide_refresh_start,
+    slide_refresh_block_total (the keyword arguments of the reference's fasterquant, :910-938).  ``H`` is the finalised ``[G, C, C]`` Hessian.  Returns dict(Q, W_int, Scale,
     perm, states) with all three matrices in the layer's natural column order (:1850-1866).
     """
-    assert g_update_mode in ("frozen", "surrogate_block", "surrogate_online", "block_backward")
+    assert g_update_mode in ("frozen", "surrogate_block", "surrogate_online", "block_backward", "block_gd")
     backward = g_update_mode == "block_backward"
+    gd_mode = g_update_mode == "block_gd"
+    if gd_mode:
+        gd = dict(GD_DEFAULTS, **(gd or {}))
+        validate_regularizer(gd)
+    so_scale = gd["second_order_scale"] if gd_mode else 1.0
     W = weight.clone().float()
     rows, columns = W.shape
     Q_final = torch.zeros_like(W)
@@ -239,17 +371,32 @@ def plus_fasterquant(weight, H, act_square, gradients, quantizer, num_groups, al
             H_sub = H_sub[perm][:, perm]
             G_sub = G_sub[:, perm]
             invperm = torch.argsort(perm)
+        extra = {}
+        if gd_mode:                                                        # :1052-1160
+            strategy = gd["grad_reg_strategy"]
+            if strategy in ("quant_error_gate", "quant_error_gate_optimized"):
+                extra["gate_scale"], extra["gate_zero"] = gate_quant_maps(quantizer, W_sub, groupsize, r0, r1,
+                                                                          shared_groups, perm)
+            if strategy in ("l2", "hessian"):
+                extra["full_precision"] = W_sub.clone()
+            if strategy == "hessian":
+                extra["hessian_reg"] = H_sub.clone()
+            curvature = None
+            if gd["grad_optimizer"] == "h_adam":
+                curvature = input_curvature_diag(torch.diagonal(H_sub).clone(), gd["curvature_damping"])
+            extra["opt"] = make_optimizer_state(W_sub, gd["grad_optimizer"], curvature)
         hinv_init, hinv, damp, ident = hinv_with_fallback(H_sub, percdamp)
         beta, bview, Z, GHinv = gradient_terms(G_sub, hinv_init, hinv, alpha, max(reference_loss, 0),
                                                rows, columns, enable_gradient_update)
-        states.append(dict(r0=r0, r1=r1, W_sub=W_sub, Hinv=hinv, Hinv_init=hinv_init, beta=beta, bview=bview,
+        states.append(dict(extra, r0=r0, r1=r1, W_sub=W_sub, Hinv=hinv, Hinv_init=hinv_init, beta=beta, bview=bview,
                            Z=Z, GHinv=GHinv, anchor=W_sub.clone(), Q=torch.zeros_like(W_sub),
                            Wint=torch.zeros_like(W_sub), Scale=torch.zeros_like(W_sub), perm=perm,
                            invperm=invperm, damp=damp, identity=ident,
                            fast_scale=quantizer.scale[r0:r1] if fast else None))
 
-    inner_mode = "surrogate_online" if backward else g_update_mode                        # :1190
-    outer_mode = "frozen" if g_update_mode in ("frozen", "block_backward") else "surrogate_block"   # :1500
+    inner_mode = "surrogate_online" if backward else "frozen" if gd_mode else g_update_mode        # :1190
+    outer_mode = "frozen" if g_update_mode in ("frozen", "block_backward", "block_gd") else "surrogate_block"   # :1500
+    n_refresh_total = max((columns + blocksize - 1) // blocksize - 1, 0)
     for i1 in range(0, columns, blocksize):
         i2 = min(i1 + blocksize, columns)
         count = i2 - i1
@@ -316,7 +463,11 @@ def plus_fasterquant(weight, H, act_square, gradients, quantizer, num_groups, al
                     Q1[:, i] = q
                     Wi1[:, i] = codes.flatten()
                     err = (w - q - GH1_eff[:, i]) / d
-                    W1[:, i:] -= err.unsqueeze(1).matmul(Hinv1[i, i:].unsqueeze(0)) + GH1_eff[:, i:]
+                    inner = err.unsqueeze(1).matmul(Hinv1[i, i:].unsqueeze(0))
+                    if gd_mode:                                                    # :1344-1349
+                        W1[:, i:] -= so_scale * (inner + GH1_eff[:, i:])
+                    else:
+                        W1[:, i:] -= inner + GH1_eff[:, i:]
                     Err1[:, i] = err
                     GH1[:, i:].sub_(Z1[:, i].unsqueeze(1).matmul(Hinv1[i, i:].unsqueeze(0)))
                     if inner_mode != "frozen":
@@ -352,8 +503,40 @@ def plus_fasterquant(weight, H, act_square, gradients, quantizer, num_groups, al
                                     st["bview"], outer_mode)
             g_update = count * rest - torch.einsum("ij,j,jk->ik", Z1, D, st["Hinv"][i1:i2, i2:])
             second = Err1.matmul(st["Hinv"][i1:i2, i2:])
-            st["W_sub"][:, i2:] -= second + g_update
+            if gd_mode:                                                           # :1546-1550
+                st["W_sub"][:, i2:] -= so_scale * (second + g_update)
+            else:
+                st["W_sub"][:, i2:] -= second + g_update
             st["GHinv"][:, i2:] -= st["Z"][:, i1:i2].matmul(st["Hinv"][i1:i2, i2:])
+            if gd_mode:
+                clear_optimizer_state(st["opt"], i1, i2)
+
+        if gd_mode and enable_gradient_update and i2 < columns:                   # :1572-1848
+            if gradient_refresh_fn is None:
+                raise ValueError("`gradient_refresh_fn` must be provided for g_update_mode='block_gd'.")
+            snapshot = weight.clone().float()
+            for st in states:
+                cur = st["W_sub"].clone()
+                cur[:, :i2] = st["Q"][:, :i2]
+                snapshot[st["r0"]:st["r1"]] = cur[:, st["invperm"]] if actorder else cur
+            total = gd["slide_refresh_block_total"] if gd["slide_refresh_block_total"] is not None else n_refresh_total
+            idx = gd["slide_refresh_start"] + i1 // blocksize
+            slide_alpha = 1.0 - idx / max(total - 1, 1) if total > 1 else 1.0
+            refreshed, _meta = gradient_refresh_fn(snapshot, slide_alpha=slide_alpha)
+            refreshed = refreshed.float()
+            for st in states:
+                g_sub = refreshed[st["r0"]:st["r1"]]
+                if actorder:
+                    g_sub = g_sub[:, st["perm"]]
+                cur = st["W_sub"].clone()
+                cur[:, :i2] = st["Q"][:, :i2]
+                raw = optimizer_update(st["opt"], g_sub, i2, gd["grad_lr"], gd["grad_clip"])
+                upd = regularized_update(st, cur, raw, i2, gd, maxq, quantizer.sym)
+                st["pending"] = upd
+            for st in states:
+                upd = st.pop("pending")
+                if upd.numel() > 0:
+                    st["W_sub"][:, i2:] -= upd
 
     for st in states:
         Qs, Wi, Sc = st["Q"], st["Wint"], st["Scale"]

@@ -188,6 +188,23 @@ PLUS_CASES = [
 ]
 
 
+GD_CASES = [
+    # name, rows, cols, nseq, seqlen, G, groupsize, actorder, static, alpha, ref_loss, atomic, block_gd keyword arguments
+    ("gd_sgd", 32, 384, 4, 96, 2, -1, True, True, 0.25, 0.7, False,
+     dict(grad_lr=5.0, grad_optimizer="sgd", grad_clip=1.0)),
+    ("gd_adam_gate_sine", 32, 384, 4, 96, 2, 128, True, True, 0.25, 0.7, False,
+     dict(grad_lr=1e-3, grad_optimizer="adam", grad_reg_strategy="quant_error_gate_optimized", grad_gate_floor=0.2,
+          grad_gate_sharpness=3.0, grad_gate_sine_amp=1e-9, second_order_scale=0.8, grad_clip=5e-5)),
+    ("gd_hadam_l2", 32, 384, 4, 96, 4, -1, False, False, 0.0, 0.7, False,
+     dict(grad_lr=1e-3, grad_optimizer="h_adam", curvature_damping=0.1, grad_reg_strategy="l2", grad_reg_lambda=0.3,
+          slide_refresh_start=1, slide_refresh_block_total=6)),
+    ("gd_adam_hessian_atomic", 32, 384, 4, 96, 2, -1, True, True, 0.25, 0.7, True,
+     dict(grad_lr=5e-4, grad_optimizer="adam", grad_reg_strategy="hessian", grad_reg_lambda=0.05)),
+    ("gd_adam_gate", 32, 400, 4, 96, 2, -1, True, True, 0.25, 0.7, False,
+     dict(grad_lr=1e-3, grad_optimizer="adam", grad_reg_strategy="quant_error_gate", second_order_scale=1.2)),
+]
+
+
 def make_refresh_fn(W0, G0, calls=None):
     """Deterministic stand-in for the model backward that ``block_backward`` calls between blocks: the
     gradient of a diagonal quadratic around the original weights, elementwise in fp32 on the CPU so that
@@ -196,9 +213,11 @@ def make_refresh_fn(W0, G0, calls=None):
     G0 = G0.detach().float().cpu().clone()
     curv = torch.linspace(0.5, 2.0, W0.shape[1]).unsqueeze(0) * 1e-3
 
-    def refresh(weight_snapshot):
+    def refresh(weight_snapshot, slide_alpha=None):
         snap = weight_snapshot.detach().float().cpu()
         grad = G0 + (snap - W0) * curv
+        if slide_alpha is not None:                       # block_gd passes its loss-window weight
+            grad = grad * (0.5 + 0.5 * float(slide_alpha))
         if calls is not None:
             calls.append(snap.clone())
         return grad.to(weight_snapshot.device), {"mean_refresh_loss": float(((snap - W0) ** 2).mean())}

@@ -281,6 +281,33 @@ def gen_plus(qu, gpu, out):
         out[f"{name}.Scale"] = np32(layer.scale)
 
 
+def gen_block_gd(qu, gpu, out):
+    """g_update_mode="block_gd": optimizer steps on the trailing weights between blocks, driven by the deterministic
+    refresh function of cases.make_refresh_fn."""
+    for (name, rows, cols, nseq, seqlen, G, gs, act, static, alpha, ref_loss, atomic, gd) in cases.GD_CASES:
+        W = cases.make_weight(rows, cols, seed=37)
+        X = cases.make_acts(nseq, seqlen, cols, seed=37)
+        S = cases.make_saliency(nseq, seqlen, G, seed=37)
+        Gr = cases.make_grad(rows, cols, seed=37)
+        layer = _Lin(W)
+        g = gpu.GPTQPlus(layer, S, Gr, G, alpha, ref_loss)
+        g.quantizer = qu.WeightQuantizer()
+        g.quantizer.configure(4, perchannel=True, sym=True, mse=False)
+        g.add_batch(X, None)
+        g.finalize_hessian()
+        out[f"{name}.digest"] = np.array(cases.digest(W, X, S, Gr))
+        reports = []
+        g.fasterquant(blocksize=128, percdamp=0.01, groupsize=gs, actorder=act, static_groups=static,
+                      enable_gradient_update=True, g_update_mode="block_gd", export_to_et=True,
+                      block_atomic_quant=atomic, gradient_refresh_fn=cases.make_refresh_fn(W, Gr),
+                      block_observer=reports.append, **gd)
+        out[f"{name}.Q"] = np32(layer.weight.data)
+        out[f"{name}.W_int"] = np32(layer.int_weight).astype(np.int8)
+        out[f"{name}.Scale"] = np32(layer.scale)
+        out[f"{name}.n_reports"] = np.array(len(reports))
+        out[f"{name}.refresh_loss"] = np.array([r["mean_refresh_loss"] for r in reports], dtype=np.float64)
+
+
 def gen_faults(qu, gpu, out):
     """Numeric guards: a non-SPD Hessian that needs damping retries, and non-finite entries."""
     torch.manual_seed(7)
@@ -312,6 +339,7 @@ def main():
                             ("hadamard.npz", gen_hadamard, (hu,)),
                             ("plain_gptq.npz", gen_plain, (qu, gu)),
                             ("gptq_plus.npz", gen_plus, (qu, gpu)),
+                            ("block_gd.npz", gen_block_gd, (qu, gpu)),
                             ("faults.npz", gen_faults, (qu, gpu)),
                             ("clip.npz", gen_clip, (qu, gpu)),
                             ("wgroup.npz", gen_wgroup, (qu,)),

@@ -216,6 +216,70 @@ def test_gptqplus_fasterquant_vs_reference(golden, case):
     assert frac2 < 0.01 and all(d == 1.0 for d in first2)      # the inverse factors differ at the 1e-5 level
 
 
+@pytest.mark.parametrize("case", cases.GD_CASES, ids=lambda c: c[0])
+def test_gptqplus_block_gd_vs_reference(golden, case):
+    """g_update_mode="block_gd": kernels per block, optimizer steps between them.  Against the reference's run
+    (rounding ties may flip where the device's Hessian differs in the last bits) and, exactly that isolated, against
+    the oracle fed the device's own Hessian."""
+    from gptq_plus_mp_quant_b200.gptq_utils.gptq_plus_utils import GPTQPlus
+    from gptq_plus_mp_quant_b200.utils.quant_utils import WeightQuantizer
+    from oracle import gptq as og, quantizer as oq
+    (name, rows, cols, nseq, seqlen, G, gs, act, static, alpha, ref_loss, atomic, gd) = case
+    g = golden("block_gd.npz")
+    W = cases.make_weight(rows, cols, seed=37)
+    X = cases.make_acts(nseq, seqlen, cols, seed=37)
+    S = cases.make_saliency(nseq, seqlen, G, seed=37)
+    Gr = cases.make_grad(rows, cols, seed=37)
+    layer = _layer(W)
+    obj = GPTQPlus(layer, S, Gr, G, alpha, ref_loss)
+    obj.quantizer = WeightQuantizer()
+    obj.quantizer.configure(4, perchannel=True, sym=True, mse=False)
+    obj.add_batch(X.to(DEV), None)
+    obj.finalize_hessian()
+    H_dev, act_sq_dev = obj.H.clone().cpu(), obj.act_square.clone().cpu()
+    seen = []
+    obj.fasterquant(blocksize=128, percdamp=0.01, groupsize=gs, actorder=act, static_groups=static,
+                    enable_gradient_update=True, g_update_mode="block_gd", export_to_et=True,
+                    block_atomic_quant=atomic, gradient_refresh_fn=cases.make_refresh_fn(W, Gr),
+                    block_observer=seen.append, refresh_full_metrics=True, **gd)
+    assert len(seen) == int(g[f"{name}.n_reports"])
+    assert np.allclose([r["mean_refresh_loss"] for r in seen], g[f"{name}.refresh_loss"], rtol=2e-2)
+    assert all(r["first_order_update_abs_mean"] is not None and r["second_order_update_abs_q99"] is not None
+               for r in seen)
+    order = obj._last_fasterquant["perm"].cpu() if act else None
+    codes_ref = torch.from_numpy(g[f"{name}.W_int"]).float()
+    frac, rows_touched, first_off = _code_report(layer.int_weight.cpu(), codes_ref, order)
+    print(f"{name}: {frac * 100:.4f}% codes differ from the reference in {rows_touched} rows")
+    assert frac < 0.02 and all(d == 1.0 for d in first_off)
+    assert torch.allclose(layer.scale.cpu(), torch.from_numpy(g[f"{name}.Scale"]), rtol=1e-6, atol=0)
+    q = oq.OracleWeightQuantizer()
+    q.configure(4, perchannel=True, sym=True)
+    o = og.plus_fasterquant(W, H_dev, act_sq_dev, Gr, q, G, alpha, ref_loss, groupsize=gs, actorder=act,
+                            static_groups=static, g_update_mode="block_gd", block_atomic_quant=atomic,
+                            gradient_refresh_fn=cases.make_refresh_fn(W, Gr), gd=gd)
+    frac2, _, first2 = _code_report(layer.int_weight.cpu(), o["W_int"].float(), order)
+    print(f"{name}: against the oracle on the device's Hessian {frac2 * 100:.4f}% differ")
+    assert frac2 < 0.01 and all(d == 1.0 for d in first2)
+
+
+def test_block_gd_argument_checks():
+    from gptq_plus_mp_quant_b200.gptq_utils.gptq_plus_utils import GPTQPlus
+    from gptq_plus_mp_quant_b200.utils.quant_utils import WeightQuantizer
+    W = cases.make_weight(16, 256, seed=1)
+    layer = _layer(W)
+    obj = GPTQPlus(layer, torch.ones(1, 32, 1), torch.zeros(16, 256), 1, 0.0, 0.0)
+    obj.quantizer = WeightQuantizer()
+    obj.quantizer.configure(4, perchannel=True, sym=True, mse=False)
+    obj.add_batch(cases.make_acts(1, 32, 256, seed=1).to(DEV), None)
+    obj.finalize_hessian()
+    for bad in (dict(grad_optimizer="lion"), dict(grad_reg_strategy="l1"), dict(grad_gate_floor=1.5),
+                dict(grad_reg_lambda=-1.0)):
+        with pytest.raises(ValueError):
+            obj.fasterquant(g_update_mode="block_gd", gradient_refresh_fn=cases.make_refresh_fn(W, W * 0), **bad)
+    with pytest.raises(ValueError):                         # the refresh function is mandatory
+        obj.fasterquant(g_update_mode="block_gd")
+
+
 @pytest.mark.parametrize("case", cases.PLAIN_CASES, ids=lambda c: c[0])
 def test_plain_gptq_fasterquant_vs_reference(golden, case):
     from gptq_plus_mp_quant_b200.gptq_utils.gptq_utils import GPTQ

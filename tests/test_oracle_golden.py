@@ -132,6 +132,35 @@ def test_gptq_plus(golden, case):
     assert torch.equal(out["Q"], t(g[f"{name}.Q"]))
 
 
+@pytest.mark.parametrize("case", cases.GD_CASES, ids=lambda c: c[0])
+def test_gptq_plus_block_gd(golden, case):
+    """g_update_mode="block_gd" (optimizer steps on the trailing weights between blocks, every regulariser and
+    optimizer of the reference) against the reference's own run with the same deterministic refresh function."""
+    (name, rows, cols, nseq, seqlen, G, gs, act, static, alpha, ref_loss, atomic, gd) = case
+    g = golden("block_gd.npz")
+    W = cases.make_weight(rows, cols, seed=37)
+    X = cases.make_acts(nseq, seqlen, cols, seed=37)
+    S = cases.make_saliency(nseq, seqlen, G, seed=37)
+    Gr = cases.make_grad(rows, cols, seed=37)
+    assert cases.digest(W, X, S, Gr) == str(g[f"{name}.digest"])
+    acc = ohess.GroupedHessian(cols, S)
+    acc.add_batch(X)
+    acc.finalize()
+    q = oq.OracleWeightQuantizer()
+    q.configure(4, perchannel=True, sym=True, mse=False)
+    out = ogptq.plus_fasterquant(W, acc.H, acc.act_square, Gr, q, G, alpha, ref_loss, blocksize=128, percdamp=0.01,
+                                 groupsize=gs, actorder=act, static_groups=static, g_update_mode="block_gd",
+                                 block_atomic_quant=atomic, gradient_refresh_fn=cases.make_refresh_fn(W, Gr), gd=gd)
+    assert torch.equal(out["W_int"], t(g[f"{name}.W_int"]).float())
+    assert torch.equal(out["Scale"], t(g[f"{name}.Scale"]))
+    assert torch.equal(out["Q"], t(g[f"{name}.Q"]))
+    # the optimizer steps matter: without them other codes come out
+    plain = ogptq.plus_fasterquant(W, acc.H, acc.act_square, Gr, q, G, alpha, ref_loss, blocksize=128, percdamp=0.01,
+                                   groupsize=gs, actorder=act, static_groups=static, g_update_mode="frozen",
+                                   block_atomic_quant=atomic)
+    assert int((plain["W_int"] != out["W_int"]).sum()) > 0
+
+
 def test_sharded_accumulation_matches_single(golden):
     """Token-sharded accumulation followed by a sum of the partial state (what the all-reduce
     in finalize_hessian does) equals the single-process result to fp32 summation noise."""
