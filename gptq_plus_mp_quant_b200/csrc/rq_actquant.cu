@@ -136,6 +136,77 @@ __global__ void __launch_bounds__(256) act_quant_kernel(const T* __restrict__ x,
     }
 }
 
+
+// Shrink-lattice search over grouped weight ranges (WeightQuantizer.find_params_weight_groupwise with mse,
+// utils/quant_utils.py:355-385): for every group the 25 x 25 candidates (1 - i/grid) * xmin, (1 - j/grid) * xmax,
+// error sum |q - x|^norm over the group, the first strictly smaller sum wins.  Every step is rounded to the weight's
+// dtype as the reference's chain of torch ops rounds it (T(.)); the sum is accumulated wide and rounded once, as
+// torch.sum does for half-precision inputs.  One warp per group; the group is re-read from L1 per candidate.
+template <typename T>
+__global__ void __launch_bounds__(256) group_mse_kernel(const T* __restrict__ x, int64_t units, int len, float maxq,
+                                                        int sym, float norm, int grid, int steps,
+                                                        float* __restrict__ scale_out, float* __restrict__ zero_out) {
+    const int lane = threadIdx.x & 31;
+    const int64_t u = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (u >= units) return;                                   // whole warps leave together
+    const T* xr = x + u * (int64_t)len;
+    float lo = INFINITY, hi = -INFINITY;
+    for (int c = lane; c < len; c += 32) {
+        const float v = load_as_float<T>(xr, c);
+        lo = fminf(lo, v);
+        hi = fmaxf(hi, v);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        lo = fminf(lo, __shfl_xor_sync(0xffffffffu, lo, o));
+        hi = fmaxf(hi, __shfl_xor_sync(0xffffffffu, hi, o));
+    }
+    float scale, zero = 0.f;
+    if (sym) {
+        scale = rnd<T>(__fdiv_rn(rnd<T>(fmaxf(fmaxf(fabsf(lo), hi), 1e-5f)), maxq));
+    } else {
+        if (lo == 0.f && hi == 0.f) { lo = -1.f; hi = 1.f; }
+        scale = rnd<T>(__fdiv_rn(rnd<T>(fmaxf(rnd<T>(hi - lo), 1e-5f)), maxq));
+        zero = rnd<T>(rintf(rnd<T>(__fdiv_rn(-lo, scale))));
+    }
+    float best = INFINITY;
+    const float expo = rnd<T>(norm);                          // torch casts a scalar exponent to the tensor's dtype
+    for (int i = 0; i < steps; ++i) {
+        const float lo1 = rnd<T>((float)(1.0 - (double)i / (double)grid) * lo);
+        for (int j = 0; j < steps; ++j) {
+            const float hi1 = rnd<T>((float)(1.0 - (double)j / (double)grid) * hi);
+            float s1, z1 = 0.f;
+            if (sym) {
+                s1 = rnd<T>(__fdiv_rn(rnd<T>(fmaxf(fmaxf(fabsf(lo1), hi1), 1e-5f)), maxq));
+            } else {
+                s1 = rnd<T>(__fdiv_rn(rnd<T>(hi1 - lo1), maxq));
+                z1 = rnd<T>(rintf(rnd<T>(__fdiv_rn(-lo1, s1))));
+            }
+            double acc = 0.0;
+            for (int c = lane; c < len; c += 32) {
+                const float v = load_as_float<T>(xr, c);
+                float q = rnd<T>(rintf(rnd<T>(__fdiv_rn(v, s1))));
+                if (sym) {
+                    q = fminf(fmaxf(q, -(maxq + 1.f)), maxq);
+                    q = rnd<T>(s1 * q);
+                } else {
+                    q = fminf(fmaxf(rnd<T>(q + z1), 0.f), maxq);
+                    q = rnd<T>(s1 * rnd<T>(q - z1));
+                }
+                acc += (double)rnd<T>(powf(fabsf(rnd<T>(q - v)), expo));
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+            const float err = rnd<T>((float)acc);
+            if (err < best) { best = err; scale = s1; zero = z1; }       // NaN sums never win
+        }
+    }
+    if (lane == 0) {
+        scale_out[u] = scale;
+        zero_out[u] = zero;
+    }
+}
+
 }  // namespace actq
 }  // namespace rq
 
@@ -171,5 +242,28 @@ extern "C" int rq_act_quant(const void* x, void* out, int dtype, int64_t units, 
     else if (dtype == RQ_F16) RQ_ACTQ_LAUNCH(__half);
     else return RQ_ERR_INVALID;
 #undef RQ_ACTQ_LAUNCH
+    return rq::check_launch();
+}
+
+extern "C" int rq_group_mse_search(const void* x, int dtype, int64_t units, int unit_len, int maxq, int sym, float norm,
+                                   int grid, float maxshrink, float* scale_out, float* zero_out, void* stream) {
+    using namespace rq::actq;
+    if (!x || !scale_out || !zero_out || units < 0 || unit_len <= 0 || maxq <= 0 || grid <= 0) return RQ_ERR_INVALID;
+    if (units == 0) return RQ_OK;
+    cudaStream_t st = rq::as_stream(stream);
+    const int steps = (int)(maxshrink * (float)grid);
+    const unsigned blocks = (unsigned)((units + 7) / 8);
+    if (dtype == RQ_F32)
+        group_mse_kernel<float><<<blocks, 256, 0, st>>>(reinterpret_cast<const float*>(x), units, unit_len, (float)maxq,
+                                                        sym, norm, grid, steps, scale_out, zero_out);
+    else if (dtype == RQ_BF16)
+        group_mse_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(x), units,
+                                                                unit_len, (float)maxq, sym, norm, grid, steps,
+                                                                scale_out, zero_out);
+    else if (dtype == RQ_F16)
+        group_mse_kernel<__half><<<blocks, 256, 0, st>>>(reinterpret_cast<const __half*>(x), units, unit_len,
+                                                         (float)maxq, sym, norm, grid, steps, scale_out, zero_out);
+    else
+        return RQ_ERR_INVALID;
     return rq::check_launch();
 }

@@ -859,6 +859,7 @@ struct AqArgs {
     const float* scale_tab; const float* zero_tab;      // mode 1: [ngroups, R]
     const int* colgrp;
     int R, C, Cp, i1, count, mode, asym;
+    int dyn_gs;              // mode 2: width of the groups ranged from the block-start values (divides BS)
     float maxq;
 };
 
@@ -890,10 +891,41 @@ __global__ void __launch_bounds__(kBlockThreads) aq_block_kernel(const AqArgs p)
         if (p.mode == 0) {
             sc[k] = p.scale_row[r];
             if (p.asym) zr[k] = p.zero_row[r];
-        } else if (in) {
+        } else if (p.mode == 1 && in) {
             const int64_t gi = (int64_t)p.colgrp[p.i1 + col] * p.R + r;
             sc[k] = p.scale_tab[gi];
             if (p.asym) zr[k] = p.zero_tab[gi];
+        }
+    }
+    if (p.mode == 2) {
+        // dynamic groups (gptaq_utils.py:126-131): find_params on the working columns of the group as they are when
+        // the block starts (the range contains 0; an all-zero group takes (-1, +1) in the asymmetric rule)
+        const int ngrp = (p.count + p.dyn_gs - 1) / p.dyn_gs;
+        for (int gi = 0; gi < ngrp; ++gi) {
+            float lo = 0.f, hi = 0.f;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int col = lane + 32 * k;
+                if (col < p.count && col / p.dyn_gs == gi) { lo = fminf(lo, w[k]); hi = fmaxf(hi, w[k]); }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                lo = fminf(lo, __shfl_xor_sync(0xffffffffu, lo, o));
+                hi = fmaxf(hi, __shfl_xor_sync(0xffffffffu, hi, o));
+            }
+            float s, z = 0.f;
+            if (!p.asym) {
+                s = __fdiv_rn(fmaxf(fmaxf(fabsf(lo), hi), 1e-5f), p.maxq);
+            } else {
+                if (lo == 0.f && hi == 0.f) { lo = -1.f; hi = 1.f; }
+                s = __fdiv_rn(fmaxf(__fsub_rn(hi, lo), 1e-5f), p.maxq);
+                z = rintf(__fdiv_rn(-lo, s));
+            }
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int col = lane + 32 * k;
+                if (col / p.dyn_gs == gi) { sc[k] = s; zr[k] = z; }
+            }
         }
     }
 #pragma unroll
@@ -1049,14 +1081,15 @@ extern "C" int rq_gptaq_terms(const float* dXXT, const float* H, const int64_t* 
 // asym != 0 honours the zero point (WeightQuantizer.quantize).  Wp is consumed; Q receives the quantized weights.
 extern "C" int rq_gptaq_run(float* Wp, const float* Hinv, const float* P, float* Q, const float* scale_row,
                             const float* zero_row, const float* scale_tab, const float* zero_tab, const int* colgrp,
-                            int R, int C, int mode, int asym, int maxq, void* workspace, size_t workspace_bytes,
-                            int* status, void* stream) {
+                            int R, int C, int mode, int dyn_gs, int asym, int maxq, void* workspace,
+                            size_t workspace_bytes, int* status, void* stream) {
     using namespace rq;
     using namespace rq::tcgemm;
     if (!Wp || !Hinv || !P || !Q || !workspace || R <= 0 || C <= 0 || maxq <= 0) return RQ_ERR_INVALID;
-    if (mode == 0 ? (!scale_row || (asym && !zero_row)) : (!scale_tab || !colgrp || (asym && !zero_tab)))
-        return RQ_ERR_INVALID;
-    if (mode < 0 || mode > 1) return RQ_ERR_INVALID;
+    if (mode < 0 || mode > 2) return RQ_ERR_INVALID;
+    if (mode == 0 && (!scale_row || (asym && !zero_row))) return RQ_ERR_INVALID;
+    if (mode == 1 && (!scale_tab || !colgrp || (asym && !zero_tab))) return RQ_ERR_INVALID;
+    if (mode == 2 && (dyn_gs <= 0 || fq::BS % dyn_gs != 0)) return RQ_ERR_INVALID;
     const aq::Layout L = aq::layout(R, C);
     if (workspace_bytes < L.total) return RQ_ERR_WORKSPACE;
     cudaStream_t st = as_stream(stream);
@@ -1091,6 +1124,7 @@ extern "C" int rq_gptaq_run(float* Wp, const float* Hinv, const float* P, float*
         p.Ehi = PE; p.Elo = PE + (size_t)R * fq::BS; p.Qhi = PQ; p.Qlo = PQ + (size_t)R * fq::BS;
         p.scale_row = scale_row; p.zero_row = zero_row; p.scale_tab = scale_tab; p.zero_tab = zero_tab;
         p.colgrp = colgrp; p.R = R; p.C = C; p.Cp = Cp; p.i1 = i1; p.count = count; p.mode = mode; p.asym = asym;
+        p.dyn_gs = dyn_gs > 0 ? dyn_gs : fq::BS;
         p.maxq = (float)maxq;
         {
             prof::Scope timed(RQ_PROF_BLOCK, st);

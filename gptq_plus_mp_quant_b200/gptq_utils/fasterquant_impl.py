@@ -636,9 +636,6 @@ def guided_fasterquant(obj, H3, blocksize, percdamp, groupsize, actorder, static
     if not obj.quantizer.ready():
         obj.quantizer.find_params(W32)
     _check_common(obj.quantizer, blocksize)
-    if groupsize != -1 and not static_groups and actorder:
-        raise NotImplementedError("GuidedQuant with dynamic weight groups under act_order (the reference ranges them "
-                                  "from un-permuted, un-updated columns) is not built")
     empty = (H3.reshape(G, -1) == 0).all(dim=1).tolist()           # no calibration data: round to nearest (:119-121)
     if any(empty):
         H3 = H3.clone()
@@ -646,7 +643,21 @@ def guided_fasterquant(obj, H3, blocksize, percdamp, groupsize, actorder, static
             if e:
                 H3[g] = torch.eye(obj.columns, device=dev)
     perm = torch.argsort(obj.act_square, descending=True) if actorder else None
-    mode_pack = _scale_setup(obj.quantizer, W32, groupsize, static_groups, blocksize, perm, None)
+    if groupsize != -1 and not static_groups and actorder:
+        # gptq_guided_utils.py:186-191 under act_order: the working matrix is a permuted copy, so the reference's
+        # find_params(W[:, pos:pos+groupsize]) ranges the original columns (dead ones zeroed, never updated) at the
+        # POSITION being quantized: a static table looked up by position, not by the permuted column's own index
+        Wz = W32.clone()
+        rps = W32.shape[0] // G
+        dead = torch.diagonal(H3, dim1=1, dim2=2) == 0                                # [G, C]
+        Wz.view(G, rps, -1).masked_fill_(dead.unsqueeze(1), 0.0)
+        tab, _ = quant_utils.find_params_groups(Wz, groupsize, int(obj.quantizer.maxq), obj.quantizer.sym,
+                                                obj.quantizer.mse, obj.quantizer.norm, obj.quantizer.grid,
+                                                obj.quantizer.maxshrink)
+        colgrp = (torch.arange(W32.shape[1], device=dev) // groupsize).to(torch.int32).contiguous()
+        mode_pack = (1, None, tab, colgrp, None, 0)
+    else:
+        mode_pack = _scale_setup(obj.quantizer, W32, groupsize, static_groups, blocksize, perm, None)
     Hinv, damp, _ = hinv_with_fallback(H3, perm, percdamp, identity_fallback=False)
     _quantize_linear(layer, W32, H3, perm, None, obj.quantizer, G, 0.0, 0.0, False, Hinv, mode_pack, export_to_et,
                      permute_export=True)
@@ -697,8 +708,11 @@ def gptaq_fasterquant(obj, H, blocksize, percdamp, groupsize, actorder, static_g
     if not quantizer.ready():
         quantizer.find_params(W32)
     _check_common(quantizer, blocksize)
-    if groupsize != -1 and not static_groups:
-        raise NotImplementedError("GPTAQ with dynamic weight groups is not built (per-row and static groups are)")
+    dynamic = groupsize != -1 and not static_groups
+    if dynamic and (BS % groupsize != 0 or blocksize != BS or quantizer.mse):
+        raise NotImplementedError(f"GPTAQ with dynamic weight groups is built for blocksize == {BS}, a groupsize that "
+                                  f"divides it and no shrink-grid search; got groupsize={groupsize}, "
+                                  f"blocksize={blocksize}, mse={quantizer.mse}")
     if bool((H == 0).all()):                                    # no calibration data: round to nearest
         H = torch.eye(Cc, device=dev)
     H3 = H.reshape(1, Cc, Cc).contiguous()
@@ -715,6 +729,8 @@ def gptaq_fasterquant(obj, H, blocksize, percdamp, groupsize, actorder, static_g
         mode = 0
         scale_row = quantizer.scale.to(dev, torch.float32).reshape(-1).contiguous()
         zero_row = quantizer.zero.to(dev, torch.float32).reshape(-1).contiguous()
+    elif dynamic:
+        mode = 2                                                 # ranged inside the kernel, block by block
     else:
         mode = 1
         Wz = W32.clone()
@@ -739,7 +755,8 @@ def gptaq_fasterquant(obj, H, blocksize, percdamp, groupsize, actorder, static_g
                                                              st))
         _lib.check("rq_gptaq_run", _lib.lib.rq_gptaq_run(_lib.ptr(Wp), _lib.ptr(Hinv), _lib.ptr(P), _lib.ptr(Q),
                                                          _lib.ptr(scale_row), _lib.ptr(zero_row), _lib.ptr(scale_tab),
-                                                         _lib.ptr(zero_tab), _lib.ptr(colgrp), R, Cc, mode, asym, maxq,
+                                                         _lib.ptr(zero_tab), _lib.ptr(colgrp), R, Cc, mode,
+                                                         groupsize if dynamic else 0, asym, maxq,
                                                          base, need, _lib.ptr(ops.status_word(dev)), st))
         out = torch.empty(layer.weight.shape, dtype=layer.weight.dtype, device=dev)
         _lib.check("rq_fq_finish", _lib.lib.rq_fq_finish(_lib.ptr(Q), 0, _lib.ptr(perm), R, Cc, _lib.ptr(out),

@@ -356,8 +356,6 @@ class WeightQuantizer(torch.nn.Module):
         _lib.check("rq_act_quant", rc)
 
     def _find_params_weight_groupwise(self, x) -> None:
-        if self.mse:
-            raise NotImplementedError("the shrink-grid search over grouped weight ranges is not built")
         _lib.require_cuda(x)
         if x.shape[-1] % self.weight_groupsize != 0:
             raise ValueError(f"columns {x.shape[-1]} not divisible by weight_groupsize {self.weight_groupsize}")
@@ -366,7 +364,15 @@ class WeightQuantizer(torch.nn.Module):
         units = xc.numel() // self.weight_groupsize
         self._g_scale = torch.empty(units, dtype=torch.float32, device=x.device)
         self._g_zero = torch.zeros(units, dtype=torch.float32, device=x.device)
-        self._grouped_call(xc, None, self._g_scale, self._g_zero, None, None, self.sym)
+        if self.mse:
+            with torch.cuda.device(x.device):
+                rc = _lib.lib.rq_group_mse_search(_lib.ptr(xc), _lib.dtype_code(xc), units, self.weight_groupsize,
+                                                  int(self.maxq), 1 if self.sym else 0, float(self.norm),
+                                                  int(self.grid), float(self.maxshrink), _lib.ptr(self._g_scale),
+                                                  _lib.ptr(self._g_zero), _lib.stream_of(xc))
+            _lib.check("rq_group_mse_search", rc)
+        else:
+            self._grouped_call(xc, None, self._g_scale, self._g_zero, None, None, self.sym)
         expand = lambda v: v.to(x.dtype).repeat_interleave(self.weight_groupsize).reshape(x.shape)   # noqa: E731
         self.scale = expand(self._g_scale)
         self.zero = expand(self._g_zero)

@@ -200,6 +200,15 @@ int rq_act_quant(const void* x, void* out, int dtype, int64_t units, int unit_le
                  int maxq, int sym, float* scale_out, float* zero_out, const float* scale_in, const float* zero_in,
                  int codes, int dtype_math, int weight_rule, void* stream);
 
+/* Shrink-lattice search over grouped weight ranges: WeightQuantizer.find_params_weight_groupwise with mse
+ * (utils/quant_utils.py:333-388).  x: [units, unit_len] of dtype (a weight [R, C] viewed as R * C / groupsize groups);
+ * scale_out / zero_out: [units] fp32.  Starts from the group's amin / amax range (an all-zero group: (-1, +1) in the
+ * asymmetric rule) and keeps, among the int(maxshrink * grid)^2 candidates (1 - i/grid) * xmin, (1 - j/grid) * xmax,
+ * the first with a strictly smaller sum |q - x|^norm, every step rounded to dtype as the reference's torch ops
+ * round it. */
+int rq_group_mse_search(const void* x, int dtype, int64_t units, int unit_len, int maxq, int sym, float norm,
+                        int grid, float maxshrink, float* scale_out, float* zero_out, void* stream);
+
 /* Packed export (an addition: the reference registers its integer codes as an fp32 [R, C] buffer `int_weight`,
  * gptq_utils/gptq_plus_utils.py:1866-1871, and has no packed format).  rq_pack_codes turns that matrix (row stride
  * ldc) into a little-endian bit stream per row, `bits` in 2..8 bits per code in two's complement, 8 consecutive codes
@@ -325,7 +334,8 @@ int rq_fq_finish(const float* Q, const int8_t* codes, const int64_t* perm, int R
  * rq_gptaq_run replaces the block loop (:107-146): per column  q = quantize(w) (zero point honoured when asym),
  * err = (w - q) / Hinv[i,i],  W1[:, i:] -= err (x) Hinv[i, i:] - w (x) P[i, i:];  per block
  * W[:, i2:] -= Err1 . Hinv[i1:i2, i2:] - W1 . P[i1:i2, i2:].  mode 0: scale_row / zero_row [R]; mode 1: static groups
- * scale_tab / zero_tab [ngroups, R] indexed by colgrp [C].  Wp (permuted working weights) is consumed, Q receives the
+ * scale_tab / zero_tab [ngroups, R] indexed by colgrp [C]; mode 2: dynamic groups of width dyn_gs (divides 128), ranged
+ * from the working columns as they are when their block starts (:126-131).  Wp (permuted working weights) is consumed, Q receives the
  * quantized weights in permuted order (rq_fq_finish un-permutes).  Workspaces: 1024-byte aligned device memory. */
 size_t rq_gptaq_accum_workspace_bytes(int64_t tokens, int C);
 int rq_gptaq_accum(const void* x, int x_dtype, int64_t ldx, const void* x_fp, int fp_dtype, int64_t ldf,
@@ -335,7 +345,7 @@ size_t rq_gptaq_workspace_bytes(int R, int C);
 int rq_gptaq_terms(const float* dXXT, const float* H, const int64_t* perm, const float* Hinv, int C, float alpha,
                    float* P, void* workspace, size_t workspace_bytes, void* stream);
 int rq_gptaq_run(float* Wp, const float* Hinv, const float* P, float* Q, const float* scale_row, const float* zero_row,
-                 const float* scale_tab, const float* zero_tab, const int* colgrp, int R, int C, int mode, int asym,
+                 const float* scale_tab, const float* zero_tab, const int* colgrp, int R, int C, int mode, int dyn_gs, int asym,
                  int maxq, void* workspace, size_t workspace_bytes, int* status, void* stream);
 
 #ifdef __cplusplus

@@ -318,7 +318,7 @@ def _effective_ghinv(base, cur_w, ref_w, bview, mode):
 def plus_fasterquant(weight, H, act_square, gradients, quantizer, num_groups, alpha, reference_loss,
                      blocksize=128, percdamp=0.01, groupsize=-1, actorder=False, static_groups=False,
                      enable_gradient_update=True, g_update_mode="frozen", block_atomic_quant=False,
-                     gradient_refresh_fn=None, gd=None):
+                     gradient_refresh_fn=None, gd=None, group_index_by_position=False):
     """GPTQ+ quantization of one linear (gptq_plus_utils.py:910-1896).  ``gd`` (g_update_mode="block_gd"): dict
     with grad_lr, grad_optimizer, curvature_damping, grad_reg_strategy, grad_reg_lambda, grad_gate_floor,
     grad_gate_sharpness, grad_gate_sine_amp, second_order_scale, grad_clip, slide_refresh_start,
@@ -428,7 +428,7 @@ def plus_fasterquant(weight, H, act_square, gradients, quantizer, num_groups, al
                     return dyn_q, None, None
                 if groupsize != -1:
                     idx = i1 + i
-                    if actorder:
+                    if actorder and not group_index_by_position:
                         idx = st["perm"][idx]
                     return shared_groups[idx // groupsize], st["r0"], st["r1"]
                 return quantizer, st["r0"], st["r1"]
@@ -557,9 +557,21 @@ def guided_fasterquant(weight, H_ccg, act_square, quantizer, num_groups, blocksi
     for g in range(num_groups):
         if bool((H[g] == 0).all()):
             H[g] = torch.eye(H.shape[-1])
+    by_position = False
+    if groupsize != -1 and not static_groups and actorder:
+        # :186-191 under act_order: W_sub is a permuted COPY, so find_params(W[:, pos:pos+groupsize]) ranges the
+        # original (dead-zeroed, un-permuted, never updated) columns at the POSITION being quantized: static ranges
+        # looked up by position instead of by the permuted column's own index
+        weight = weight.clone().float()
+        rps = weight.shape[0] // num_groups
+        for g in range(num_groups):
+            dead = torch.diag(H[g]) == 0
+            weight[g * rps:(g + 1) * rps][:, dead] = 0
+        static_groups, by_position = True, True
     out = plus_fasterquant(weight, H, act_square, torch.zeros_like(weight, dtype=torch.float32), quantizer,
                            num_groups, 0.0, 0.0, blocksize=blocksize, percdamp=percdamp, groupsize=groupsize,
-                           actorder=actorder, static_groups=static_groups, enable_gradient_update=False)
+                           actorder=actorder, static_groups=static_groups, enable_gradient_update=False,
+                           group_index_by_position=by_position)
     if any(st["identity"] for st in out["states"]):
         raise ValueError("Quantization: `damp_percent` must between 0 and 1.")
     return out
@@ -593,7 +605,7 @@ class AsymCalibState:
 
 def gptaq_fasterquant(weight, H, dXXT, quantizer, blocksize=128, percdamp=0.01, groupsize=-1, actorder=False,
                       static_groups=False, alpha=0.25):
-    """GPTAQ.fasterquant (gptaq_utils.py:43-167) for per-row and static-group scales: dict(Q, perm, P)."""
+    """GPTAQ.fasterquant (gptaq_utils.py:43-167): dict(Q, perm, P)."""
     W = weight.clone().float()
     columns = W.shape[1]
     if not quantizer.ready():
@@ -636,11 +648,14 @@ def gptaq_fasterquant(weight, H, dXXT, quantizer, blocksize=128, percdamp=0.01, 
             d = Hinv1[i, i]
             qz = quantizer
             if groupsize != -1:
-                assert static_groups, "dynamic groups are not restated"
-                idx = i1 + i
-                if actorder:
-                    idx = perm[idx]
-                qz = groups[idx // groupsize]
+                if not static_groups:                                   # :126-131, on the working matrix
+                    if (i1 + i) % groupsize == 0:
+                        quantizer.find_params(W[:, (i1 + i):(i1 + i + groupsize)])
+                else:
+                    idx = i1 + i
+                    if actorder:
+                        idx = perm[idx]
+                    qz = groups[idx // groupsize]
             q = qz.quantize(w.unsqueeze(1)).flatten()
             Q1[:, i] = q
             err1 = (w - q) / d

@@ -235,9 +235,9 @@ def act_fake_quant(x, bits, groupsize=-1, sym=False, clip_ratio=1.0):
     return (scale * (q - zero)).to(x.dtype)
 
 
-def weight_groupwise_params(x, bits, groupsize, sym):
-    """WeightQuantizer.find_params_weight_groupwise without the shrink-grid search (utils/quant_utils.py:333-352):
-    (scale, zero, maxq) with scale / zero of x's shape, in x's dtype."""
+def weight_groupwise_params(x, bits, groupsize, sym, mse=False, norm=2.4, grid=50, maxshrink=0.5):
+    """WeightQuantizer.find_params_weight_groupwise (utils/quant_utils.py:333-388), with the optional shrink-grid
+    search: (scale, zero, maxq) with scale / zero of x's shape, in x's dtype."""
     maxq = torch.tensor(2 ** (bits - 1) - 1) if sym else torch.tensor(2 ** bits - 1)
     init_shape = x.shape
     xr = x.reshape(x.shape[-2], x.shape[-1] // groupsize, groupsize)
@@ -252,9 +252,34 @@ def weight_groupwise_params(x, bits, groupsize, sym):
         xmax[tmp] = +1
         scale = (xmax - xmin).clamp(min=1e-5) / maxq
         zero = torch.round(-xmin / scale)
-    scale = scale.repeat(1, 1, groupsize).reshape(init_shape)
-    zero = zero.repeat(1, 1, groupsize).reshape(init_shape)
-    return scale, zero, maxq
+    scale = scale.repeat(1, 1, groupsize)
+    zero = zero.repeat(1, 1, groupsize)
+    if mse:                                                             # :355-385
+        best = torch.full([xr.shape[0], xr.shape[1]], float("inf")).type_as(xr)
+        steps = int(maxshrink * grid)
+        for i in range(steps):
+            for j in range(steps):
+                lo1 = (1 - i / grid) * xmin
+                hi1 = (1 - j / grid) * xmax
+                if sym:
+                    s1 = (torch.maximum(torch.abs(lo1), hi1).clamp(min=1e-5) / maxq).repeat(1, 1, groupsize)
+                    z1 = torch.zeros_like(s1)
+                    q = s1 * torch.clamp(torch.round(xr / s1), -(maxq + 1), maxq)
+                else:
+                    s1 = (hi1 - lo1) / maxq
+                    z1 = torch.round(-lo1 / s1).repeat(1, 1, groupsize)
+                    s1 = s1.repeat(1, 1, groupsize)
+                    q = s1 * (torch.clamp(torch.round(xr / s1) + z1, 0, maxq) - z1)
+                q -= xr
+                q.abs_()
+                q.pow_(norm)
+                err = torch.sum(q, -1)
+                better = err < best
+                if torch.any(better):
+                    best[better] = err[better]
+                    scale[better] = s1[better]
+                    zero[better] = z1[better]
+    return scale.reshape(init_shape), zero.reshape(init_shape), maxq
 
 
 def weight_groupwise_rtn(x, bits, groupsize, sym):

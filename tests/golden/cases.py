@@ -80,6 +80,14 @@ WGROUP_CASES = [
     ("wg_w8_g32_asym_f16", 8, 96, 8, 32, False, "float16"),
 ]
 
+WGROUP_MSE_CASES = [
+    # name, rows, cols, bits, weight_groupsize, sym, dtype  (find_params with mse=True)
+    ("wgm_w4_g128_sym_bf16", 12, 256, 4, 128, True, "bfloat16"),
+    ("wgm_w4_g64_asym_bf16", 12, 128, 4, 64, False, "bfloat16"),
+    ("wgm_w3_g128_sym_f32", 8, 256, 3, 128, True, "float32"),
+    ("wgm_w4_g32_asym_f16", 8, 96, 4, 32, False, "float16"),
+]
+
 CLIP_CASES = [
     # name, rows, cols, bits, sym, weight dtype
     ("clip_w4_sym_f32", 32, 128, 4, True, "float32"),
@@ -113,6 +121,7 @@ GPTAQ_CASES = [
     ("gptaq_pc_sym_act", 32, 256, 4, 96, 4, True, -1, True, False, 0.25),
     ("gptaq_pc_asym_noact", 24, 256, 3, 80, 4, False, -1, False, False, 0.25),
     ("gptaq_g128_static_act", 32, 384, 4, 96, 4, True, 128, True, True, 0.5),
+    ("gptaq_g64_dynamic_asym_act", 16, 256, 3, 80, 4, False, 64, True, False, 0.25),
 ]
 
 
@@ -128,6 +137,7 @@ GUIDED_CASES = [
     ("guided_g128_static_act", 32, 256, 4, 96, 2, 4, 128, True, True),
     ("guided_pc_noact", 16, 384, 3, 64, 2, 3, -1, False, False),
     ("guided_g128_dynamic_noact", 16, 256, 3, 64, 2, 4, 128, False, False),
+    ("guided_g64_dynamic_act", 16, 256, 3, 64, 2, 4, 64, True, False),
 ]
 
 ACT_QUANT_CASES = [

@@ -87,6 +87,21 @@ def gen_wgroup(qu, out):
         out[f"{name}.ste"] = np32(q.quantize(W).float())
 
 
+def gen_wgroup_mse(qu, out):
+    """WeightQuantizer with weight_groupsize > 0 and the shrink-grid search (mse=True), in the weight's dtype."""
+    for name, rows, cols, bits, gs, sym, dtype in cases.WGROUP_MSE_CASES:
+        W = cases.make_weight(rows, cols, seed=23).to(getattr(torch, dtype))
+        W[0, :gs] = 0                                                # one all-zero group
+        W[1, :gs] = 0.5                                              # one constant group
+        q = qu.WeightQuantizer()
+        q.configure(bits, perchannel=True, sym=sym, mse=True, weight_groupsize=gs)
+        q.find_params(W)
+        out[f"{name}.digest"] = np.array(cases.digest(W.float()))
+        out[f"{name}.scale"] = np32(q.scale.float())
+        out[f"{name}.zero"] = np32(q.zero.float())
+        out[f"{name}.ste"] = np32(q.quantize(W).float())
+
+
 def gen_clip(qu, gpu, out):
     """Pre-clip of a linear's weight to its quantizer's range (clip_module_weight_to_quant_bounds_)."""
     for name, rows, cols, bits, sym, dtype in cases.CLIP_CASES:
@@ -343,6 +358,7 @@ def main():
                             ("faults.npz", gen_faults, (qu, gpu)),
                             ("clip.npz", gen_clip, (qu, gpu)),
                             ("wgroup.npz", gen_wgroup, (qu,)),
+                            ("wgroup_mse.npz", gen_wgroup_mse, (qu,)),
                             ("saliency.npz", gen_saliency, (gpu,)),
                             ("act_quant.npz", gen_act_quant, (qu,)),
                             ("guided.npz", gen_guided, (qu, gg)),

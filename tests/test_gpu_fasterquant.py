@@ -364,7 +364,11 @@ def test_unsupported_modes_are_loud():
     obj.add_batch(torch.randn(1, 16, 128, device=DEV), None)
     obj.finalize_hessian()
     with pytest.raises(NotImplementedError):
-        obj.fasterquant(g_update_mode="block_gd")
+        obj.fasterquant(diagnostic_recorder=object())
+    with pytest.raises(NotImplementedError):
+        obj.fasterquant(g_update_mode="surrogate_block", blocksize=256)
+    with pytest.raises(ValueError):
+        obj.fasterquant(g_update_mode="no_such_mode")
     with pytest.raises(ValueError):
         obj.fasterquant(groupsize=64, static_groups=False)
 

@@ -326,6 +326,24 @@ def test_qk_rotation_wrapper(golden, case):
     assert torch.equal(qo.float(), t(g[f"{name}.q"])) and torch.equal(ko.float(), t(g[f"{name}.k"]))
 
 
+@pytest.mark.parametrize("case", cases.WGROUP_MSE_CASES, ids=lambda c: c[0])
+def test_weight_quantizer_grouped_mse(golden, case):
+    """Grouped weight ranges with the shrink-grid search, in the weight's own dtype (an all-zero and a constant
+    group included)."""
+    name, rows, cols, bits, gs, sym, dtype = case
+    g = golden("wgroup_mse.npz")
+    W = cases.make_weight(rows, cols, seed=23).to(getattr(torch, dtype))
+    W[0, :gs] = 0
+    W[1, :gs] = 0.5
+    assert cases.digest(W.float()) == str(g[f"{name}.digest"])
+    scale, zero, maxq = oq.weight_groupwise_params(W, bits, gs, sym, mse=True)
+    assert torch.equal(scale.float(), t(g[f"{name}.scale"])) and torch.equal(zero.float(), t(g[f"{name}.zero"]))
+    ste = oq.ste_quantize(W, scale, zero, int(maxq), sym).to(W.dtype)
+    assert torch.equal(ste.float(), t(g[f"{name}.ste"]))
+    plain, _, _ = oq.weight_groupwise_params(W, bits, gs, sym)
+    assert not torch.equal(plain, scale)                                # the search moved some ranges
+
+
 @pytest.mark.parametrize("case", cases.WGROUP_CASES, ids=lambda c: c[0])
 def test_weight_quantizer_grouped(golden, case):
     """WeightQuantizer with weight_groupsize > 0 (round-to-nearest path), evaluated in the weight's own dtype."""
