@@ -507,11 +507,14 @@ def test_gptaq_vs_reference(golden, case):
     obj.fasterquant(blocksize=128, percdamp=0.01, groupsize=gs, actorder=act, static_groups=static, alpha=alpha)
     got = layer.weight.data.cpu()
     ref = torch.from_numpy(g[f"{name}.Q"])
-    frac = float((got != ref).float().mean())
+    # dynamic groups are ranged from the working weights, whose last bits follow the accumulation order: the scales,
+    # and with them every dequantized value of the group, move in the last bits; a flipped code moves a whole step
+    tol = 1e-4 * float(ref.abs().max()) if (gs != -1 and not static) else 0.0
+    frac = float(((got - ref).abs() > tol).float().mean())
     q = oq.OracleWeightQuantizer()
     q.configure(bits, perchannel=True, sym=sym, mse=False)
     o = ogptq.gptaq_fasterquant(W, H_dev, d_dev, q, groupsize=gs, actorder=act, static_groups=static, alpha=alpha)
-    frac2 = float((got != o["Q"]).float().mean())
+    frac2 = float(((got - o["Q"]).abs() > tol).float().mean())
     print(f"{name}: {frac * 100:.4f}% of the quantized weights differ from the reference, {frac2 * 100:.4f}% from the "
           "oracle on the device's statistics")
     assert frac < 0.02 and frac2 < 0.01
