@@ -292,6 +292,12 @@ static int fwht_impl(const void* x, void* y, int dtype, int64_t rows, int n, int
         if (e != cudaSuccess) return RQ_ERR_CUDA;                                                                  \
         fwht_mix_kernel<T, L, true><<<(unsigned)grid, 32 * kMixWarps, smem, st>>>(                                 \
             reinterpret_cast<const T*>(x), reinterpret_cast<T*>(y), rows, K, hadK, scale, *rqp);                   \
+    } else if (K <= 12) {                                                                                          \
+        e = cudaFuncSetAttribute(fwht_mix_kernel<T, L, false, 12, RQ_MIX12_WARPS>,                                 \
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                          \
+        if (e != cudaSuccess) return RQ_ERR_CUDA;                                                                  \
+        fwht_mix_kernel<T, L, false, 12, RQ_MIX12_WARPS><<<(unsigned)grid, 32 * RQ_MIX12_WARPS, smem, st>>>(       \
+            reinterpret_cast<const T*>(x), reinterpret_cast<T*>(y), rows, K, hadK, scale);                         \
     } else {                                                                                                       \
         e = cudaFuncSetAttribute(fwht_mix_kernel<T, L>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);   \
         if (e != cudaSuccess) return RQ_ERR_CUDA;                                                                  \

@@ -415,8 +415,15 @@ __device__ __forceinline__ void mix_pair(float* buf, int slice, const float* hk,
 
 // K > 1 with chunk length P = S: one CTA per row; warps transform the K chunks into shared memory, then
 // all threads mix the chunks position by position.
-template <typename T, int LOGS, bool QUANT = false>
-__global__ void __launch_bounds__(32 * kMixWarps) fwht_mix_kernel(const T* __restrict__ x, T* __restrict__ y,
+// KMAX bounds K at compile time: the kernel for K <= 12 holds 24 instead of 56 chunk values per thread during the mix,
+// so that four CTAs instead of two share an SM's registers; it runs with 6 warps, which take the 12 chunks of a
+// 12288-long row in two full rounds (measured on 65536 x 12288 bf16: 8 warps and two CTAs per SM 1.98 TB/s, 8 warps
+// and four CTAs 2.36, 4 warps 2.43, 6 warps 2.68).
+#ifndef RQ_MIX12_WARPS
+#define RQ_MIX12_WARPS 6
+#endif
+template <typename T, int LOGS, bool QUANT = false, int KMAX = 28, int WARPS = kMixWarps>
+__global__ void __launch_bounds__(32 * WARPS, (KMAX <= 12 && LOGS == 10) ? 4 : 1) fwht_mix_kernel(const T* __restrict__ x, T* __restrict__ y,
                                                                      int64_t rows, int K,
                                                                      const float* __restrict__ hadK, float scale,
                                                                      RowQuant rq = RowQuant()) {
@@ -430,15 +437,18 @@ __global__ void __launch_bounds__(32 * kMixWarps) fwht_mix_kernel(const T* __res
     const int64_t n = (int64_t)K * S;
     for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
         __syncthreads();                                        // previous row's mix has finished reading
-        for (int c = warp; c < K; c += kMixWarps)
+        for (int c = warp; c < K; c += WARPS)
             warp_transform<T, LOGS>(x, row * n + (int64_t)c * S, (rows * n), LOGS, wsm + (size_t)c * slice, lane);
         __syncthreads();
         T* yrow = y + row * n;
         float lo = 0.f, hi = 0.f;
         for (int p = 2 * threadIdx.x; p < S; p += 2 * blockDim.x) {
-            if (K <= 12) mix_pair<T, 12, QUANT>(wsm, slice, hk, p, S, yrow, scale, K, &lo, &hi);
-            else if (K <= 20) mix_pair<T, 20, QUANT>(wsm, slice, hk, p, S, yrow, scale, K, &lo, &hi);
-            else mix_pair<T, 28, QUANT>(wsm, slice, hk, p, S, yrow, scale, K, &lo, &hi);
+            if (KMAX <= 12 || K <= 12) {
+                mix_pair<T, 12, QUANT>(wsm, slice, hk, p, S, yrow, scale, K, &lo, &hi);
+            } else if (KMAX > 12) {
+                if (K <= 20) mix_pair<T, 20, QUANT>(wsm, slice, hk, p, S, yrow, scale, K, &lo, &hi);
+                else mix_pair<T, 28, QUANT>(wsm, slice, hk, p, S, yrow, scale, K, &lo, &hi);
+            }
         }
         if (QUANT) {
             float qs, qz;
