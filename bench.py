@@ -277,29 +277,38 @@ class LayerWorkload:
                 return {key: inputs[key][s:s + self.BSZ] for key in ("hid", "attn", "mlp")}, None
             if self.copy_stream is None:
                 self.copy_stream = torch.cuda.Stream()
+            got, evs = {}, {}
             with torch.cuda.stream(self.copy_stream):
-                got = {key: inputs[key][s:s + self.BSZ].cuda(non_blocking=True) for key in ("hid", "attn", "mlp")}
-                ev = torch.cuda.Event()
-                ev.record(self.copy_stream)
-            return got, ev
+                for key in ("hid", "attn", "mlp"):            # in the order the linears consume them
+                    got[key] = inputs[key][s:s + self.BSZ].cuda(non_blocking=True)
+                    evs[key] = torch.cuda.Event()
+                    evs[key].record(self.copy_stream)
+            return got, evs
 
         nxt = fetch(0)
         for s in range(0, self.nseq_local, self.BSZ):
             batch, ready = nxt
             nxt = fetch(s + self.BSZ)
-            if ready is not None:
-                main.wait_event(ready)
-                for t in batch.values():
-                    t.record_stream(main)
-            rot = {"hid": hu.matmul_hadU_cuda(batch["hid"], None, 1), "attn": batch["attn"],
-                   "mlp": hu.matmul_hadU_cuda(batch["mlp"], self.had12, 12)}
+            rot = {}
+
+            def rotated(key):
+                """This batch's input of one activation stream, rotated where the layer rotates it; waits for that
+                stream's copy only, so that the first GEMMs start while the rest of the batch is still in flight."""
+                if key not in rot:
+                    if ready is not None:
+                        main.wait_event(ready[key])
+                        batch[key].record_stream(main)
+                    rot[key] = (hu.matmul_hadU_cuda(batch[key], None, 1) if key == "hid" else
+                                batch[key] if key == "attn" else hu.matmul_hadU_cuda(batch[key], self.had12, 12))
+                return rot[key]
+
             last = self.world > 1 and self.overlap_exchange and s + self.BSZ >= self.nseq_local
             if last and self.comm_stream is None:
                 self.comm_stream = torch.cuda.Stream()
             # in the last batch the widest linear goes first: its exchange is the longest, and it then runs under
             # the GEMMs of the others (every rank uses the same order, as the collectives require)
             for name, _, _, key in (self.LINEARS[::-1] if last else self.LINEARS):
-                objs[name].add_batch(rot[key], None)
+                objs[name].add_batch(rotated(key), None)
                 if last:
                     objs[name].group_owners = self.owner[name]
                     objs[name].begin_exchange(self.comm_stream)
