@@ -299,9 +299,11 @@ static int fwht_impl(const void* x, void* y, int dtype, int64_t rows, int n, int
         fwht_mix_kernel<T, L, false, 12, RQ_MIX12_WARPS><<<(unsigned)grid, 32 * RQ_MIX12_WARPS, smem, st>>>(       \
             reinterpret_cast<const T*>(x), reinterpret_cast<T*>(y), rows, K, hadK, scale);                         \
     } else {                                                                                                       \
-        e = cudaFuncSetAttribute(fwht_mix_kernel<T, L>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);   \
+        e = cudaFuncSetAttribute(fwht_mix_kernel<T, L, false, 28, (L == 10 ? RQ_MIX28_WARPS : kMixWarps)>,                               \
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                          \
         if (e != cudaSuccess) return RQ_ERR_CUDA;                                                                  \
-        fwht_mix_kernel<T, L><<<(unsigned)grid, 32 * kMixWarps, smem, st>>>(                                       \
+        fwht_mix_kernel<T, L, false, 28, (L == 10 ? RQ_MIX28_WARPS : kMixWarps)>                                   \
+            <<<(unsigned)grid, 32 * (L == 10 ? RQ_MIX28_WARPS : kMixWarps), smem, st>>>(                           \
             reinterpret_cast<const T*>(x), reinterpret_cast<T*>(y), rows, K, hadK, scale);                         \
     }
 #define RQ_MIX_DISPATCH(T)                                  \

@@ -422,6 +422,12 @@ __device__ __forceinline__ void mix_pair(float* buf, int slice, const float* hk,
 #ifndef RQ_MIX12_WARPS
 #define RQ_MIX12_WARPS 6
 #endif
+// Larger K (one CTA per SM by shared memory at K = 28): 16 warps, so that the 512 position pairs of a 1024-long
+// chunk take one round of the mix and more loads are in flight during the transform (bf16, 32768 rows: n = 28672
+// 1.04 -> 1.52 TB/s, n = 20480 1.32 -> 1.61 TB/s against 8 warps).
+#ifndef RQ_MIX28_WARPS
+#define RQ_MIX28_WARPS 16
+#endif
 template <typename T, int LOGS, bool QUANT = false, int KMAX = 28, int WARPS = kMixWarps>
 __global__ void __launch_bounds__(32 * WARPS, (KMAX <= 12 && LOGS == 10) ? 4 : 1) fwht_mix_kernel(const T* __restrict__ x, T* __restrict__ y,
                                                                      int64_t rows, int K,
