@@ -304,6 +304,7 @@ __global__ void __launch_bounds__(kBlockThreads) block_kernel(const BlockArgs p)
             if (lane == o) { qv[slot] = q; cv[slot] = qi; ev[slot] = err; }
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
+                if (32 * k + 31 < i) continue;             // every column of this slot is already quantized (warp-uniform)
                 const int col = lane + 32 * k;
                 if (col >= i && col < p.count) {
                     const float h = Hs[i * BS + col];
@@ -950,6 +951,7 @@ __global__ void __launch_bounds__(kBlockThreads) aq_block_kernel(const AqArgs p)
             if (lane == o) { qv[slot] = q; ev[slot] = err; }
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
+                if (32 * k + 31 < i) continue;             // slot already quantized (warp-uniform)
                 const int col = lane + 32 * k;
                 if (col >= i && col < p.count) {
                     const float upd = __fsub_rn(__fmul_rn(err, Hs[i * BS + col]), __fmul_rn(wi, Ps[i * BS + col]));
