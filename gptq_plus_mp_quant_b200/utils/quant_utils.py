@@ -234,9 +234,9 @@ class ActQuantWrapper(torch.nn.Module):
         q = self.quantizer
         if (self.online_full_had and q.bits < 16 and q.groupsize <= 0 and self.K == 1 and x.shape[-1] <= 4096
                 and (not self.fp32_had or x_dtype == torch.float32)):
-            # rotation and per-token quantization in one pass over the activations; both kernels are bound by the
-            # quantizer's IEEE divisions rather than by memory, and only up to 4096-long rows did the fused kernel
-            # measure faster than the two in turn
+            # rotation and per-token quantization in one pass over the activations; the quantizer's correctly rounded
+            # divisions take much of the issue bandwidth in either form, and only up to 4096-long rows did the fused
+            # kernel measure faster than the two in turn
             import math
             y = hadamard_utils.fwht_act_quant(x, self.had_K, self.K, 1.0 / math.sqrt(x.shape[-1]), q.clip_ratio,
                                               int(q.maxq), q.sym)
