@@ -171,12 +171,23 @@ __global__ void __launch_bounds__(256) group_mse_kernel(const T* __restrict__ x,
     }
     float best = INFINITY;
     const float expo = rnd<T>(norm);                          // torch casts a scalar exponent to the tensor's dtype
+    // symmetric rule: the scale is a function of max(|lo1|, hi1) alone, so a candidate whose maximum was evaluated
+    // before repeats that error sum and cannot be strictly smaller than the best so far: skipped, same result
+    unsigned seen_hi = 0u;
     for (int i = 0; i < steps; ++i) {
         const float lo1 = rnd<T>((float)(1.0 - (double)i / (double)grid) * lo);
+        bool lo_done = false;
         for (int j = 0; j < steps; ++j) {
             const float hi1 = rnd<T>((float)(1.0 - (double)j / (double)grid) * hi);
             float s1, z1 = 0.f;
             if (sym) {
+                if (fabsf(lo1) >= hi1) {
+                    if (lo_done) continue;
+                    lo_done = true;
+                } else if (j < 32) {
+                    if ((seen_hi >> j) & 1u) continue;
+                    seen_hi |= 1u << j;
+                }
                 s1 = rnd<T>(__fdiv_rn(rnd<T>(fmaxf(fmaxf(fabsf(lo1), hi1), 1e-5f)), maxq));
             } else {
                 s1 = rnd<T>(__fdiv_rn(rnd<T>(hi1 - lo1), maxq));

@@ -123,6 +123,119 @@ __global__ void __launch_bounds__(kThreads) find_params_kernel(const float* __re
     }
 }
 
+
+// Shrink-grid search with the unit (a row, or one column group of a row) held in registers: TPU threads per unit
+// (a warp for spans up to 1024 columns, the whole block beyond), EPT values per thread.  The 625 candidates then cost
+// arithmetic only - no reloads, and for a warp-sized unit no block barrier per candidate.  Same arithmetic, candidate
+// order and strictly-smaller rule as find_params_kernel.
+// |d|^norm.  The default norm 2.4 is evaluated as d^2 * 2^(0.4 * log2 d): the squaring is exact to one rounding and the
+// transcendental part carries a sixth of the exponent, which keeps the result within a few ulp (the accuracy class of
+// powf itself) at about a third of its instructions.  Equal inputs still give equal outputs, so candidates that
+// quantize identically still tie exactly, as the first-strictly-smaller rule needs.
+template <bool FAST24>
+__device__ __forceinline__ float abs_pow(float d, float norm) {
+    if (FAST24) return (d * d) * exp2f(0.4f * log2f(d));
+    return powf(d, norm);
+}
+
+template <int TPU, int EPT, bool FAST24>
+__global__ void __launch_bounds__(kThreads) mse_search_kernel(const float* __restrict__ W, int64_t R, int64_t C,
+                                                              int64_t ldw, int groupsize, int64_t groups, int maxq,
+                                                              int sym, float norm, int grid, float maxshrink,
+                                                              float* __restrict__ scale, float* __restrict__ zero) {
+    __shared__ float red[16];
+    __shared__ double dred[8];
+    constexpr int UPB = kThreads / TPU;
+    const int sub = threadIdx.x / TPU, t = threadIdx.x % TPU;
+    const int64_t u = (int64_t)blockIdx.x * UPB + sub;
+    const bool live = u < R * groups;                       // a dead unit idles through the same shuffles
+    const int64_t r = live ? u / groups : 0;
+    const int g = live ? (int)(u - r * groups) : 0;
+    const int64_t c0 = groupsize > 0 ? (int64_t)g * groupsize : 0;
+    const int64_t c1 = groupsize > 0 ? (c0 + groupsize < C ? c0 + groupsize : C) : C;
+    const int len = (int)(c1 - c0);
+    const float* row = W + r * ldw + c0;
+    float v[EPT];
+    float lo = 0.f, hi = 0.f;                               // the range always contains 0
+#pragma unroll
+    for (int j = 0; j < EPT; ++j) {
+        const int c = t + j * TPU;
+        v[j] = (live && c < len) ? row[c] : 0.f;            // padding zeros quantize to 0: no error contribution
+        lo = fminf(lo, v[j]);
+        hi = fmaxf(hi, v[j]);
+    }
+    if (TPU == kThreads) {
+        block_minmax(lo, hi, red);
+    } else {
+        lo = warp_min(lo);
+        hi = warp_max(hi);
+    }
+    float s, z;
+    range_to_params(lo, hi, maxq, sym, s, z);
+    if (!sym && lo == 0.f && hi == 0.f) { lo = -1.f; hi = 1.f; }
+    float best = __int_as_float(0x7f800000);
+    const int steps = (int)(maxshrink * (float)grid);
+    const float fmaxq = (float)maxq;
+    // Symmetric rule: the candidate's scale is max(|lo1|, hi1) / maxq, so the 25 x 25 lattice holds at most 25 + 25
+    // different scales.  A candidate whose scale was evaluated before has the same error sum and can never be strictly
+    // smaller than the best so far: skipping it leaves the result unchanged.  seen_hi marks the j whose hi1 was the
+    // maximum once; within one i, |lo1| is the maximum for every j after the first such j.
+    unsigned seen_hi = 0u;
+    for (int i = 0; i < steps; ++i) {
+        const float lo1 = (float)(1.0 - (double)i / (double)grid) * lo;
+        bool lo_done = false;
+        for (int j = 0; j < steps; ++j) {
+            const float hi1 = (float)(1.0 - (double)j / (double)grid) * hi;
+            float s1, z1;
+            if (sym) {
+                if (fabsf(lo1) >= hi1) {
+                    if (lo_done) continue;
+                    lo_done = true;
+                } else if (j < 32) {
+                    if ((seen_hi >> j) & 1u) continue;
+                    seen_hi |= 1u << j;
+                }
+                s1 = __fdiv_rn(fmaxf(fmaxf(fabsf(lo1), hi1), 1e-5f), fmaxq);
+                z1 = 0.f;
+            } else {
+                s1 = __fdiv_rn(hi1 - lo1, fmaxq);
+                z1 = rintf(__fdiv_rn(-lo1, s1));
+            }
+            double acc = 0.0;
+#pragma unroll
+            for (int e = 0; e < EPT; ++e) {
+                if (t + e * TPU < len) {
+                    const float x = v[e];
+                    float q;
+                    if (sym) {
+                        q = rintf(__fdiv_rn(x, s1));
+                        q = q < -(fmaxq + 1.f) ? -(fmaxq + 1.f) : (q > fmaxq ? fmaxq : q);
+                        q = s1 * q;
+                    } else {
+                        q = rintf(__fdiv_rn(x, s1)) + z1;
+                        q = q < 0.f ? 0.f : (q > fmaxq ? fmaxq : q);
+                        q = s1 * (q - z1);
+                    }
+                    acc += (double)abs_pow<FAST24>(fabsf(q - x), norm);
+                }
+            }
+            float err;
+            if (TPU == kThreads) {
+                err = (float)block_sum(acc, dred);
+            } else {
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+                err = (float)acc;
+            }
+            if (err < best) { best = err; s = s1; z = z1; }
+        }
+    }
+    if (live && t == 0) {
+        scale[(int64_t)g * R + r] = s;
+        zero[(int64_t)g * R + r] = z;
+    }
+}
+
 // whole-tensor range (perchannel == 0): single block, result replicated to all R entries
 __global__ void __launch_bounds__(kThreads) find_params_tensor_kernel(const float* __restrict__ W, int64_t R, int64_t C,
                                                                       int64_t ldw, int maxq, int sym,
@@ -187,6 +300,28 @@ extern "C" int rq_find_params(const float* W, int64_t R, int64_t C, int64_t ldw,
     }
     const int64_t groups = groupsize > 0 ? (C + groupsize - 1) / groupsize : 1;
     if (R > 2147483647LL || groups > 65535) return RQ_ERR_INVALID;
+    if (mse) {
+        const int64_t span = groupsize > 0 ? (groupsize < C ? groupsize : C) : C;
+        const int64_t units = R * groups;
+#define RQ_MSE_LAUNCH(TPU, EPT)                                                                                     \
+    if (norm == 2.4f)                                                                                               \
+        mse_search_kernel<TPU, EPT, true><<<(unsigned)((units + kThreads / TPU - 1) / (kThreads / TPU)), kThreads,  \
+                                            0, st>>>(W, R, C, ldw, groupsize, groups, maxq, sym, norm, grid,        \
+                                                     maxshrink, scale, zero);                                       \
+    else                                                                                                            \
+        mse_search_kernel<TPU, EPT, false><<<(unsigned)((units + kThreads / TPU - 1) / (kThreads / TPU)), kThreads, \
+                                             0, st>>>(W, R, C, ldw, groupsize, groups, maxq, sym, norm, grid,       \
+                                                      maxshrink, scale, zero)
+        if (units <= 2147483647LL) {
+            if (span <= 128) { RQ_MSE_LAUNCH(32, 4); return check_launch(); }
+            if (span <= 256) { RQ_MSE_LAUNCH(32, 8); return check_launch(); }
+            if (span <= 1024) { RQ_MSE_LAUNCH(32, 32); return check_launch(); }
+            if (span <= 4096) { RQ_MSE_LAUNCH(256, 16); return check_launch(); }
+            if (span <= 8192) { RQ_MSE_LAUNCH(256, 32); return check_launch(); }
+            if (span <= 16384) { RQ_MSE_LAUNCH(256, 64); return check_launch(); }
+        }
+#undef RQ_MSE_LAUNCH
+    }
     dim3 gridDim3((unsigned)R, (unsigned)groups);
     find_params_kernel<<<gridDim3, kThreads, 0, st>>>(W, R, C, ldw, groupsize, maxq, sym, mse, norm, grid, maxshrink,
                                                       scale, zero);
