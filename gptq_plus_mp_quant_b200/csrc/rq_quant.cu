@@ -300,7 +300,8 @@ extern "C" int rq_find_params(const float* W, int64_t R, int64_t C, int64_t ldw,
     }
     const int64_t groups = groupsize > 0 ? (C + groupsize - 1) / groupsize : 1;
     if (R > 2147483647LL || groups > 65535) return RQ_ERR_INVALID;
-    if (mse) {
+    {   // the register-resident kernel also serves the plain range search (no lattice steps): a warp per short unit
+        if (!mse) maxshrink = 0.f;
         const int64_t span = groupsize > 0 ? (groupsize < C ? groupsize : C) : C;
         const int64_t units = R * groups;
 #define RQ_MSE_LAUNCH(TPU, EPT)                                                                                     \
