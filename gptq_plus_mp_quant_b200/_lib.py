@@ -34,7 +34,7 @@ SIGNATURES = {
     "rq_gptaq_accum_workspace_bytes": (_sz, [_i64, _i]),
     "rq_gptaq_accum": (_i, [_vp, _i, _i64, _vp, _i, _i64, _i, _i64, _i, _f, _f, _vp, _vp, _sz, _vp, _vp]),
     "rq_gptaq_workspace_bytes": (_sz, [_i, _i]),
-    "rq_gptaq_terms": (_i, [_vp, _vp, _vp, _vp, _i, _f, _vp, _vp, _sz, _vp]),
+    "rq_gptaq_terms": (_i, [_vp, _vp, _vp, _vp, _i, _f, _vp, _vp, _sz, _vp, _vp]),
     "rq_gptaq_run": (_i, [_vp] * 9 + [_i] * 6 + [_vp, _sz, _vp, _vp]),
     "rq_fwht_heads": (_i, [_vp, _vp, _i, _i64, _i, _i, _i, _vp, _f, _vp]),
     "rq_packed_row_bytes": (_i64, [_i64, _i]),

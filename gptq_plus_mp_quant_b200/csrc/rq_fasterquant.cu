@@ -1060,21 +1060,57 @@ extern "C" size_t rq_gptaq_workspace_bytes(int R, int C) {
 // P = alpha * triu(D . Hinv^T, 1) . Hinv with D the permuted dXXT, dead columns zeroed (gptaq_utils.py:72, 84, 105).
 // H: the un-damped Hessian [C, C] (only its diagonal is read, for the dead-column test).  P: [C, C] output.
 extern "C" int rq_gptaq_terms(const float* dXXT, const float* H, const int64_t* perm, const float* Hinv, int C,
-                              float alpha, float* P, void* workspace, size_t workspace_bytes, void* stream) {
+                              float alpha, float* P, void* workspace, size_t workspace_bytes, int* status,
+                              void* stream) {
     using namespace rq;
+    using namespace rq::tcgemm;
     if (!dXXT || !H || !Hinv || !P || !workspace || C <= 0) return RQ_ERR_INVALID;
+    if (reinterpret_cast<uintptr_t>(workspace) % 1024 != 0) return RQ_ERR_INVALID;
     const aq::Layout L = aq::layout(1, C);
     if (workspace_bytes < L.total) return RQ_ERR_WORKSPACE;
     cudaStream_t st = as_stream(stream);
     uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
+    const int Cp = L.Cp;
     float* D = reinterpret_cast<float*>(ws + L.tmp1);
     float* T = reinterpret_cast<float*>(ws + L.tmp2);
+    // both products on the tensor cores from bf16-split planes, as the GPTQ+ first-order terms: the operand planes of
+    // D (then T) take the region that later holds the planes of U^T, those of U (then U^T) the region of P^T's -
+    // rq_gptaq_run rebuilds both for itself
+    __nv_bfloat16* PA = reinterpret_cast<__nv_bfloat16*>(ws + L.put);
+    __nv_bfloat16* PU = reinterpret_cast<__nv_bfloat16*>(ws + L.ppt);
+    int* tc_status = status ? status : reinterpret_cast<int*>(ws + L.status);
+    if (!status && cudaMemsetAsync(ws + L.status, 0, sizeof(int), st) != cudaSuccess) return RQ_ERR_CUDA;
     dim3 eg((unsigned)((C + 1023) / 1024), (unsigned)C);
     aq::gather_dxxt_kernel<<<eg, 256, 0, st>>>(dXXT, H, perm, C, D);
-    dim3 grid((unsigned)((C + gemm::TM - 1) / gemm::TM), (unsigned)((C + gemm::TN - 1) / gemm::TN), 1);
-    fq::terms_gemm_kernel<<<grid, gemm::kThreads, gemm::kSmemBytes, st>>>(D, Hinv, T, C, C, L.Cp, 1);   // D . U^T
+    SplitArgs a;
+    a.src = Hinv; a.ld = Cp; a.src_z = 0; a.rows = Cp; a.cols = Cp;
+    a.Kp = Cp; a.plane_stride = (long long)Cp * Cp; a.plane = 0; a.plane_z = 0;
+    a.dst_row0 = 0; a.dst_row_z = 0; a.dst_k0 = 0; a.pad_k_to = 0;
+    a.dst = PU;
+    int rc = split_rows(a, 1, st);                                   // planes of U
+    if (rc != RQ_OK) return rc;
+    PlaneTensor tA{PA, Cp, C, 2};
+    PlaneTensor tU{PU, Cp, Cp, 2};
+    Params p;
+    p.a_row0 = 0; p.b_row0 = 0; p.a_k0 = 0; p.b_k0 = 0; p.a_plane = 0; p.b_plane = 0;
+    p.a_plane_z = 0; p.b_plane_z = 2; p.a_row_z = C; p.b_row_z = 0;
+    p.M = C; p.N = C; p.k_len = Cp; p.tri = 0; p.batch = 1;
+    p.ldc = C; p.c_z = (long long)C * C; p.Aux = nullptr; p.ldaux = 0; p.aux_z = 0;
+    p.alpha = 1.f; p.beta = 0.f; p.gamma = 0.f;
+    rc = split_full_rows(D, C, C, Cp, PA, st);                       // T = D . U^T
+    if (rc != RQ_OK) return rc;
+    p.kmode = 3; p.C = T;
+    rc = launch(tA, tU, p, tc_status, st);
+    if (rc != RQ_OK) return rc;
     aq::triu_scale_kernel<<<eg, 256, 0, st>>>(T, C, alpha);
-    fq::terms_gemm_kernel<<<grid, gemm::kThreads, gemm::kSmemBytes, st>>>(T, Hinv, P, C, C, L.Cp, 2);   // . U
+    a.dst = PU;
+    rc = split_transpose(a, 1, st);                                  // planes of U^T over those of U
+    if (rc != RQ_OK) return rc;
+    rc = split_full_rows(T, C, C, Cp, PA, st);                       // P = alpha * triu(T, 1) . U
+    if (rc != RQ_OK) return rc;
+    p.kmode = 2; p.C = P;
+    rc = launch(tA, tU, p, tc_status, st);
+    if (rc != RQ_OK) return rc;
     return check_launch();
 }
 

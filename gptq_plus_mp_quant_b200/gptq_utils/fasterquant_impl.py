@@ -752,7 +752,7 @@ def gptaq_fasterquant(obj, H, blocksize, percdamp, groupsize, actorder, static_g
         base = (ws.data_ptr() + 1023) // 1024 * 1024
         _lib.check("rq_gptaq_terms", _lib.lib.rq_gptaq_terms(_lib.ptr(obj.dXXT), _lib.ptr(H3), _lib.ptr(perm),
                                                              _lib.ptr(Hinv), Cc, float(alpha), _lib.ptr(P), base, need,
-                                                             st))
+                                                             _lib.ptr(ops.status_word(dev)), st))
         _lib.check("rq_gptaq_run", _lib.lib.rq_gptaq_run(_lib.ptr(Wp), _lib.ptr(Hinv), _lib.ptr(P), _lib.ptr(Q),
                                                          _lib.ptr(scale_row), _lib.ptr(zero_row), _lib.ptr(scale_tab),
                                                          _lib.ptr(zero_tab), _lib.ptr(colgrp), R, Cc, mode,

@@ -343,7 +343,7 @@ int rq_gptaq_accum(const void* x, int x_dtype, int64_t ldx, const void* x_fp, in
                    size_t workspace_bytes, int* status, void* stream);
 size_t rq_gptaq_workspace_bytes(int R, int C);
 int rq_gptaq_terms(const float* dXXT, const float* H, const int64_t* perm, const float* Hinv, int C, float alpha,
-                   float* P, void* workspace, size_t workspace_bytes, void* stream);
+                   float* P, void* workspace, size_t workspace_bytes, int* status, void* stream);
 int rq_gptaq_run(float* Wp, const float* Hinv, const float* P, float* Q, const float* scale_row, const float* zero_row,
                  const float* scale_tab, const float* zero_tab, const int* colgrp, int R, int C, int mode, int dyn_gs, int asym,
                  int maxq, void* workspace, size_t workspace_bytes, int* status, void* stream);
