@@ -1,17 +1,31 @@
 // Saliency-weighted Hessian accumulation  H[g] = beta*H[g] + alpha * X^T diag(s_g) X  on the
 // 5th-generation tensor cores (tcgen05 + tensor memory), fed by TMA.
 //
-// Two kernels per chunk of tokens:
-//   1. pack:  reads X (fp32 / bf16 / fp16) and the saliency once, and writes token-contiguous
-//             ("K-major") bf16 planes  X_hi, X_lo, Y_hi[g], Y_lo[g]  with  Y_g = s_g * X,
-//             v_hi = bf16(v), v_lo = bf16(v - v_hi); also the per-channel sum of squares.
-//   2. umma:  persistent, warp-specialised GEMM over the upper-triangular 128x256 tiles of
-//             every H[g]:  D = X_hi.Y_lo^T + X_lo.Y_hi^T + X_hi.Y_hi^T  accumulated in fp32 in
-//             tensor memory over windows of 128 tokens; the epilogue warps sum the windows in
-//             registers with round-to-nearest adds (the tensor core's own accumulation truncates
-//             toward zero and would drift by ~4e-8 per MMA; measured: 5e-5 over 8192 tokens, and the
-//             same with the operand sign flipped) and read-modify-write the tile into H at the end.
-// The three-product split keeps the result within ~1e-6 relative Frobenius of an fp32 GEMM.
+// The contraction runs on fp16 operand planes.  fp16 carries 11 significant bits per plane (bf16: 8), so a value
+// split into hi + lo keeps 22 bits, within two bits of fp32, where two bf16 planes keep 16; what fp16 lacks is
+// exponent range, and that is supplied by exact power-of-two scalings chosen per chunk of tokens:
+//   * per saliency group g:  s' = s * 2^-c_g  brings the chunk's largest saliency of the group into [1, 2);
+//   * per token t:           X' = x * 2^a_t,  Y'_g = (s'_g * x) * 2^(E - a_t):  every product x'_i * y'_j equals
+//     s' x_i x_j * 2^E whatever a_t is, so a_t is free to balance the two operands of the token, and the global E
+//     puts the chunk's largest token just under the top of fp16's range.  With P_t = max_g s'_tg * (max_c |x_tc|)^2:
+//     E = 28 - floor(log2 max_t P_t),  a_t = floor((floor(log2 max_g s'_tg) + E) / 2), which gives
+//     max |x'_t| < 2^14.5 and max |y'_t| < 2^15.5 for every token.
+//   The epilogue multiplies the sums by 2^(c_g - E).  Tokens that weigh little in H (small P_t) sit lower in the
+//   format and lose relative precision in proportion to how little they contribute.
+//
+// Per chunk:
+//   1. group_scale (one block) and token_stats (a warp per token, one extra read of X): c_g, then per token
+//      max_c |x| and max_g s', and the chunk's largest P_t.
+//   2. pack:  reads X (fp32 / bf16 / fp16) and the saliency once, and writes token-contiguous ("K-major") fp16
+//             planes  X' (one plane for bf16 / fp16 input, whose 8 / 11 significant bits fit; hi and lo for fp32
+//             input)  and  Y'_g hi, lo  per group; also the per-channel sum of squares.
+//   3. umma:  persistent, warp-specialised GEMM over the upper-triangular 128x256 tiles of every H[g]:
+//             D = X'.Y'_lo^T + X'.Y'_hi^T  (bf16 / fp16 input)  or  X'_lo.Y'_hi^T + X'_hi.Y'_lo^T + X'_hi.Y'_hi^T
+//             (fp32 input; the lo.lo term, 2^-22, is dropped), every product exact in fp32, accumulated in
+//             tensor memory over windows of 128 tokens; the epilogue warps sum the windows in registers with
+//             round-to-nearest adds (the tensor core's own accumulation truncates toward zero and would drift
+//             by ~4e-8 per MMA; measured: 5e-5 over 8192 tokens, and the same with the operand sign flipped)
+//             and add the tile into H at the end.
 #include <cuda.h>
 
 #include "rq_common.cuh"
@@ -24,49 +38,175 @@ using namespace rq::sm100;
 
 constexpr int BM = 128;          // tile rows   (channels i)   = UMMA M
 constexpr int BN = 256;          // tile cols   (channels j)   = UMMA N
-constexpr int UK = 16;           // bf16 UMMA K
+constexpr int UK = 16;           // 16-bit UMMA K
 constexpr int kEpilogueWarps = 8;
 constexpr int kThreads = 64 + 32 * kEpilogueWarps;   // warp 0: TMA producer, warp 1: MMA issuer, warps 2-9: epilogue
 constexpr int kTmemCols = 512;   // two 128x256 fp32 accumulators
-constexpr int kWindowTokens = 128;   // tokens accumulated on the tensor core before a round-to-nearest add
+constexpr int kWindowTokens = 128;   // tokens accumulated on the tensor core before a round-to-nearest add (default)
 constexpr int kPackTile = 64;    // pack kernel tile edge (tokens and channels)
+constexpr int kTopExp = 28;      // 2^E * (largest P_t of the chunk) lands in [2^28, 2^29)
 
-template <int BK, int NPROD, bool WIDE_Y = false>
+// NX = number of fp16 planes of X' (1 for bf16 / fp16 input, 2 for fp32 input); Y' always has two.
+template <int BK, int NX, bool WIDE_Y = false>
 struct Cfg {
     static constexpr int kLayout = BK == 64 ? 2 : 4;              // UMMA swizzle mode: 128 B / 64 B
     static constexpr int kSBO = 8 * BK * 2;                        // bytes between 8-row groups
     static constexpr int kATile = BM * BK * 2;
     static constexpr int kBTile = BN * BK * 2;
-    // NPROD == 3 (fp32 / fp16 X):  A side (128 rows) = X_hi, X_lo;  B side (256 rows) = Y_hi, Y_lo.
-    // NPROD == 2 (bf16 X, X_lo = 0): the two-plane operand Y goes on the narrow A side and the single
-    // plane X_hi on the wide B side, 64 KB per stage instead of 80 KB: less L2->SM traffic per MMA
-    // and room for a third stage.
-    // WIDE_Y keeps Y on the wide side also for NPROD == 2 (80 KB per stage), for comparison.
-    static constexpr bool kSwap = NPROD == 2 && !WIDE_Y;
-    static constexpr int kAPlanes = (NPROD == 3 || kSwap) ? 2 : 1;
-    static constexpr int kBPlanes = (NPROD == 3 || !kSwap) ? 2 : 1;
+    // NX == 2:  A side (128 rows) = X' hi, lo;  B side (256 rows) = Y' hi, lo.
+    // NX == 1:  the two-plane operand Y' goes on the narrow A side and the single plane X' on the wide B side,
+    // 64 KB per stage instead of 80 KB: less L2->SM traffic per MMA and room for a third stage.
+    // WIDE_Y keeps Y' on the wide side also for NX == 1 (80 KB per stage), for comparison.
+    static constexpr bool kSwap = NX == 1 && !WIDE_Y;
+    static constexpr int kAPlanes = kSwap ? 2 : NX;
+    static constexpr int kBPlanes = kSwap ? 1 : 2;
     static constexpr int kStageBytes = kAPlanes * kATile + kBPlanes * kBTile;
     static constexpr int kStages = (200 * 1024) / kStageBytes;
     static constexpr int kBarBytes = 256;
     static constexpr int kSmemBytes = kStages * kStageBytes + kBarBytes + 1024;   // +1024: alignment slack
+    static_assert(kStages >= 2, "the ring needs two stages");
+    // products of a k-step as (X' plane, Y' plane), smallest terms first
+    static constexpr int kProducts = NX == 1 ? 2 : 3;
 };
+__device__ constexpr int kProdX[2][3] = {{0, 0, 0}, {1, 0, 0}};
+__device__ constexpr int kProdY[2][3] = {{1, 0, 0}, {0, 1, 0}};
+
+// ------------------------------------------------------------------------------------------
+// scales.  `aux` (16 floats per chunk slot): [0..7] 2^-c_g, [8..15] 2^c_g; `pmax`: bit pattern of max_t P_t.
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ bool finite_pos(float v) { return v > 0.f && v <= 3.0e38f; }
+
+// c_g = floor(log2(max_t |s[t, g]|)) over the chunk (0 when the group has no positive finite saliency, or when
+// there is no saliency at all).  One block; also clears pmax.
+__global__ void __launch_bounds__(1024) group_scale_kernel(const float* __restrict__ sal, int nvalid, int G,
+                                                           float* __restrict__ aux, unsigned int* __restrict__ pmax) {
+    __shared__ float red[32][8];
+    float m[8];
+#pragma unroll
+    for (int g = 0; g < 8; ++g) m[g] = 0.f;
+    if (sal != nullptr) {
+        for (int t = threadIdx.x; t < nvalid; t += 1024) {
+#pragma unroll
+            for (int g = 0; g < 8; ++g) {
+                if (g < G) {
+                    const float v = fabsf(sal[(int64_t)t * G + g]);
+                    if (v > m[g] && v <= 3.0e38f) m[g] = v;             // skips NaN and Inf
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int g = 0; g < 8; ++g) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m[g] = fmaxf(m[g], __shfl_xor_sync(0xffffffffu, m[g], o));
+        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5][g] = m[g];
+    }
+    __syncthreads();
+    if (threadIdx.x < 8) {
+        float v = 0.f;
+        for (int w = 0; w < 32; ++w) v = fmaxf(v, red[w][threadIdx.x]);
+        int c = (sal != nullptr && v > 0.f) ? ilogbf(v) : 0;
+        c = c < -100 ? -100 : (c > 100 ? 100 : c);
+        aux[threadIdx.x] = exp2f((float)-c);
+        aux[8 + threadIdx.x] = exp2f((float)c);
+    }
+    if (threadIdx.x == 0) *pmax = 0u;
+}
+
+// tok[t] = (max_g s'_tg, max_c |x_tc|), both 0 for padding tokens and for tokens that carry a non-finite value;
+// pmax = bit pattern of the largest P_t = tok.x * tok.y^2 (positive floats order like their bit patterns).
+// One warp per token.
+template <typename T>
+__global__ void __launch_bounds__(256) token_stats_kernel(const T* __restrict__ x, int64_t ldx,
+                                                          const float* __restrict__ sal, const float* __restrict__ aux,
+                                                          int nvalid, int Kc, int C, int G, float2* __restrict__ tok,
+                                                          unsigned int* __restrict__ pmax) {
+    const int t = blockIdx.x * 8 + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (t >= Kc) return;
+    float m = 0.f;
+    bool finite = true;
+    if (t < nvalid) {
+        const T* row = x + (int64_t)t * ldx;
+        const bool vec = (ldx * (int64_t)sizeof(T)) % 16 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0;
+        constexpr int PER = 16 / (int)sizeof(T);
+        const int nvec = vec ? C / PER : 0;
+        const uint4* r4 = reinterpret_cast<const uint4*>(row);
+        for (int i = lane; i < nvec; i += 32) {
+            const uint4 w = r4[i];
+            const T* h = reinterpret_cast<const T*>(&w);
+#pragma unroll
+            for (int e = 0; e < PER; ++e) {
+                const float a = fabsf(load_as_float<T>(h, e));
+                finite = finite && a <= 3.0e38f;
+                m = fmaxf(m, a);
+            }
+        }
+        for (int c = nvec * PER + lane; c < C; c += 32) {
+            const float a = fabsf(load_as_float<T>(row, c));
+            finite = finite && a <= 3.0e38f;
+            m = fmaxf(m, a);
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    finite = __all_sync(0xffffffffu, finite);
+    if (lane == 0) {
+        float smax = t < nvalid ? 1.f : 0.f;
+        if (sal != nullptr && t < nvalid) {
+            smax = 0.f;
+            for (int g = 0; g < G; ++g) {
+                const float v = fabsf(sal[(int64_t)t * G + g]) * aux[g];
+                if (!(v <= 3.0e38f)) finite = false;
+                smax = fmaxf(smax, v);
+            }
+        }
+        const float p = smax * m * m;
+        if (finite && finite_pos(p)) {
+            tok[t] = make_float2(smax, m);
+            atomicMax(pmax, __float_as_uint(p));
+        } else {
+            tok[t] = make_float2(0.f, 0.f);
+        }
+    }
+}
+
+// E of the chunk and the factor 2^-E the epilogue needs (clamped so that both stay ordinary floats).
+__device__ __forceinline__ int chunk_exponent(unsigned int pmax_bits) {
+    const float pm = __uint_as_float(pmax_bits);
+    int e = finite_pos(pm) ? kTopExp - ilogbf(pm) : 0;
+    return e < -60 ? -60 : (e > 60 ? 60 : e);
+}
+
+// (2^a_t, 2^(E - a_t)) of a token; (1, 2^E) for a token without a usable magnitude.
+__device__ __forceinline__ float2 token_scales(float2 tk, int E) {
+    int a = 0;
+    if (finite_pos(tk.x)) {
+        const int u = ilogbf(tk.x) + E;
+        a = (u >= 0) ? (u >> 1) : -((1 - u) >> 1);            // floor(u / 2)
+    }
+    a = a < -100 ? -100 : (a > 100 ? 100 : a);
+    return make_float2(exp2f((float)a), exp2f((float)(E - a)));
+}
 
 // ------------------------------------------------------------------------------------------
 // pack
 // ------------------------------------------------------------------------------------------
-__device__ __forceinline__ void split_bf16(float v, __nv_bfloat16& hi, __nv_bfloat16& lo) {
-    hi = __float2bfloat16_rn(v);
-    lo = __float2bfloat16_rn(v - __bfloat162float(hi));
+__device__ __forceinline__ uint32_t pair_f16(float a, float b) {
+    return (uint32_t)__half_as_ushort(__float2half_rn(a)) | ((uint32_t)__half_as_ushort(__float2half_rn(b)) << 16);
 }
+__device__ __forceinline__ float round_f16(float v) { return __half2float(__float2half_rn(v)); }
 
 // grid (Kc/64, ceil(C/64)), 256 threads: token tiles vary fastest, so that concurrently running blocks
-// extend the same plane rows (contiguous DRAM pages on the write side).  planes: [P][C][Kc] bf16, P = 2 (no saliency) or 2+2G.
+// extend the same plane rows (contiguous DRAM pages on the write side).
+// planes: [NX + 2G][C][Kc] fp16: X' (hi[, lo]) then per group Y' (hi, lo).
 // partial: [Kc/64][C] per-tile sums of x^2 (may be NULL).
-template <typename T>
+template <typename T, int NX>
 __global__ void __launch_bounds__(256) pack_kernel(const T* __restrict__ x, int64_t ldx,
-                                                   const float* __restrict__ sal, int nvalid, int C, int G, int Kc,
-                                                   __nv_bfloat16* __restrict__ planes, float* __restrict__ partial,
-                                                   int write_xlo) {
+                                                   const float* __restrict__ sal, const float* __restrict__ aux,
+                                                   const float2* __restrict__ tok, const unsigned int* __restrict__ pmax,
+                                                   int nvalid, int C, int G, int Kc, uint16_t* __restrict__ planes,
+                                                   float* __restrict__ partial) {
     // channel-major tile: the write side (64 consecutive channels of one token per 64 threads) strides by the
     // row length, the read side takes two adjacent tokens of one channel as one 8-byte word
     __shared__ __align__(8) float xs[kPackTile][kPackTile + 2];
@@ -85,11 +225,11 @@ __global__ void __launch_bounds__(256) pack_kernel(const T* __restrict__ x, int6
             if (t0 + t < nvalid && c0 + cc < C) v = load_as_float<T>(x, (int64_t)(t0 + t) * ldx + c0 + cc);
             xs[cc][t] = v;
         }
-        if (sal != nullptr) {
-            for (int e = tid; e < kPackTile * G; e += 256) {
-                const int t = e / G, g = e - t * G;
-                ss[t][g] = (t0 + t < nvalid) ? sal[(int64_t)(t0 + t) * G + g] : 0.f;
-            }
+        for (int e = tid; e < kPackTile * 8; e += 256) {
+            const int t = e >> 3, g = e & 7;
+            float v = 0.f;
+            if (g < G && t0 + t < nvalid) v = (sal != nullptr) ? sal[(int64_t)(t0 + t) * G + g] : 1.f;
+            ss[t][g] = v;
         }
     }
     __syncthreads();
@@ -97,11 +237,16 @@ __global__ void __launch_bounds__(256) pack_kernel(const T* __restrict__ x, int6
     const int warp = tid >> 5, lane = tid & 31;
     const int64_t plane_stride = (int64_t)C * Kc;
     const int ta = 2 * lane, tb = 2 * lane + 1;
-    float sa[8], sb[8];                                        // this lane's two tokens' saliencies, read once
+    const int E = chunk_exponent(*pmax);
+    const float2 sha = token_scales(tok[t0 + ta], E), shb = token_scales(tok[t0 + tb], E);
+    float sa[8], sb[8], da[8], db[8];                          // this lane's two tokens' saliencies and y scales
 #pragma unroll
     for (int g = 0; g < 8; ++g) {
-        sa[g] = (sal != nullptr && g < G) ? ss[ta][g] : 0.f;
-        sb[g] = (sal != nullptr && g < G) ? ss[tb][g] : 0.f;
+        sa[g] = g < G ? ss[ta][g] : 0.f;
+        sb[g] = g < G ? ss[tb][g] : 0.f;
+        const float gn = g < G ? aux[g] : 0.f;
+        da[g] = sha.y * gn;                                    // powers of two: exact
+        db[g] = shb.y * gn;
     }
     for (int cc = warp; cc < kPackTile; cc += 8) {
         const int c = c0 + cc;
@@ -109,22 +254,21 @@ __global__ void __launch_bounds__(256) pack_kernel(const T* __restrict__ x, int6
         const float2 xab = *reinterpret_cast<const float2*>(&xs[cc][ta]);
         const float xa = xab.x, xb = xab.y;
         const int64_t off = (int64_t)c * Kc + t0 + ta;          // even -> 4-byte aligned pair
-        __nv_bfloat16 ha, la, hb, lb;
-        split_bf16(xa, ha, la);
-        split_bf16(xb, hb, lb);
-        *reinterpret_cast<__nv_bfloat162*>(planes + off) = __halves2bfloat162(ha, hb);
-        if (write_xlo) *reinterpret_cast<__nv_bfloat162*>(planes + plane_stride + off) = __halves2bfloat162(la, lb);
-        if (sal != nullptr) {
+        {
+            const float ra = xa * sha.x, rb = xb * shb.x;
+            *reinterpret_cast<uint32_t*>(planes + off) = pair_f16(ra, rb);
+            if (NX == 2)
+                *reinterpret_cast<uint32_t*>(planes + plane_stride + off) = pair_f16(ra - round_f16(ra), rb - round_f16(rb));
+        }
 #pragma unroll
-            for (int g = 0; g < 8; ++g) {
-                if (g >= G) break;
-                const float ya = __fmul_rn(xa, sa[g]);
-                const float yb = __fmul_rn(xb, sb[g]);
-                split_bf16(ya, ha, la);
-                split_bf16(yb, hb, lb);
-                *reinterpret_cast<__nv_bfloat162*>(planes + (2 + 2 * g) * plane_stride + off) = __halves2bfloat162(ha, hb);
-                *reinterpret_cast<__nv_bfloat162*>(planes + (3 + 2 * g) * plane_stride + off) = __halves2bfloat162(la, lb);
-            }
+        for (int g = 0; g < 8; ++g) {
+            if (g >= G) break;
+            // the reference's fp32 product x * s, then the exact scaling
+            const float ya = __fmul_rn(xa, sa[g]) * da[g];
+            const float yb = __fmul_rn(xb, sb[g]) * db[g];
+            *reinterpret_cast<uint32_t*>(planes + (NX + 2 * g) * plane_stride + off) = pair_f16(ya, yb);
+            *reinterpret_cast<uint32_t*>(planes + (NX + 2 * g + 1) * plane_stride + off) =
+                pair_f16(ya - round_f16(ya), yb - round_f16(yb));
         }
         if (partial != nullptr) {
             float sq = xa * xa + xb * xb;
@@ -192,13 +336,17 @@ struct Bars {
 };
 static_assert(sizeof(Bars) <= 256, "barrier block");
 
-template <int BK, int NPROD, bool WIDE_Y>
+// x_plane0 / y_plane0: index of the first X' plane and of group 0's first Y' plane in the plane tensor.
+// aux / pmax: the chunk's group scales and largest P_t (see the scales section); the sums leave as
+// alpha * 2^(c_g - E) * D.
+template <int BK, int NX, bool WIDE_Y>
 __global__ void __launch_bounds__(kThreads, 1)
 umma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
-            float* __restrict__ H, int C, int G, int MT, int NT, int kblocks, int a_plane, int b_plane0,
-            float alpha, float beta, int ksplit, int* __restrict__ status) {
-    using K = Cfg<BK, NPROD, WIDE_Y>;
-    constexpr int WIN = kWindowTokens / BK;                              // k-blocks per accumulation window
+            float* __restrict__ H, int C, int G, int MT, int NT, int kblocks, int x_plane0, int y_plane0,
+            float alpha, float beta, const float* __restrict__ aux, const unsigned int* __restrict__ pmax,
+            int win_blocks, int* __restrict__ status) {
+    using K = Cfg<BK, NX, WIDE_Y>;
+    const int WIN = win_blocks;                                          // k-blocks per accumulation window
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t tiles = (raw + 1023u) & ~1023u;                       // shared-space address of stage 0
@@ -209,12 +357,6 @@ umma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CU
     const int lane = threadIdx.x & 31;
     const int tiles_per_group = (NT - 1) * NT + MT;
     const int total_tiles = tiles_per_group * G;
-    // A work unit is (tile, part of the chunk's tokens): with ksplit > 1 every tile is visited ksplit times, each
-    // visit adding the sum over its share of the k-blocks into H (only with the reduction epilogue, beta == 1),
-    // which evens out the last round when the tile count is a poor multiple of the grid.  Units are ordered
-    // part-major so that concurrently running CTAs stream the same token range.
-    const int total_units = total_tiles * ksplit;
-    const int kb_per_part = ((kblocks + ksplit - 1) / ksplit + WIN - 1) / WIN * WIN;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < K::kStages; ++s) {
@@ -244,34 +386,25 @@ umma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CU
         if (lane == 0) {
             uint32_t it = 0;
             bool ok = true;
-            for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
-                const int part = u / total_tiles, t = u - part * total_tiles;
-                const int kb0 = part * kb_per_part;
-                const int kb1 = (kb0 + kb_per_part < kblocks) ? kb0 + kb_per_part : kblocks;
+            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
                 int g, i, j;
                 decode_work<K::kSwap>(t, G, NT, g, i, j);
-                for (int kb = kb0; kb < kb1; ++kb, ++it) {
+                // A side: 128 rows of block i; B side: 256 rows of block j
+                const int a_first = K::kSwap ? y_plane0 + 2 * g : x_plane0;
+                const int b_first = K::kSwap ? x_plane0 : y_plane0 + 2 * g;
+                for (int kb = 0; kb < kblocks; ++kb, ++it) {
                     const uint32_t s = it % K::kStages;
                     const uint32_t ph = (it / K::kStages) & 1u;
                     if (!mbar_wait(smem_u32(&bars->empty[s]), ph ^ 1u, abort_flag)) { ok = false; break; }
                     const uint32_t fb = smem_u32(&bars->full[s]);
-                    uint32_t dst = tiles + s * K::kStageBytes;
+                    const uint32_t dst = tiles + s * K::kStageBytes;
                     mbar_expect_tx(fb, K::kStageBytes);
-                    if (NPROD == 3) {
-                        tma_load_3d(dst, &mapA, fb, kb * BK, i * BM, a_plane);
-                        tma_load_3d(dst + K::kATile, &mapA, fb, kb * BK, i * BM, a_plane + 1);
-                        dst += 2 * K::kATile;
-                        tma_load_3d(dst, &mapB, fb, kb * BK, j * BN, b_plane0 + 2 * g);
-                        tma_load_3d(dst + K::kBTile, &mapB, fb, kb * BK, j * BN, b_plane0 + 2 * g + 1);
-                    } else if (K::kSwap) {
-                        tma_load_3d(dst, &mapA, fb, kb * BK, i * BM, b_plane0 + 2 * g);
-                        tma_load_3d(dst + K::kATile, &mapA, fb, kb * BK, i * BM, b_plane0 + 2 * g + 1);
-                        tma_load_3d(dst + 2 * K::kATile, &mapB, fb, kb * BK, j * BN, a_plane);
-                    } else {
-                        tma_load_3d(dst, &mapA, fb, kb * BK, i * BM, a_plane);
-                        tma_load_3d(dst + K::kATile, &mapB, fb, kb * BK, j * BN, b_plane0 + 2 * g);
-                        tma_load_3d(dst + K::kATile + K::kBTile, &mapB, fb, kb * BK, j * BN, b_plane0 + 2 * g + 1);
-                    }
+#pragma unroll
+                    for (int pl = 0; pl < K::kAPlanes; ++pl)
+                        tma_load_3d(dst + pl * K::kATile, &mapA, fb, kb * BK, i * BM, a_first + pl);
+#pragma unroll
+                    for (int pl = 0; pl < K::kBPlanes; ++pl)
+                        tma_load_3d(dst + K::kAPlanes * K::kATile + pl * K::kBTile, &mapB, fb, kb * BK, j * BN, b_first + pl);
                 }
             }
             if (!ok) {
@@ -288,50 +421,38 @@ umma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CU
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0) {
-            constexpr uint32_t idesc = umma_idesc_bf16_f32(BM, BN);
+            constexpr uint32_t idesc = umma_idesc_f16_f32(BM, BN);      // fp16 x fp16 -> fp32
             uint32_t it = 0, win_iter = 0;
             bool ok = true;
-            for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
-                const int part = u / total_tiles;
-                const int kb0 = part * kb_per_part;
-                const int kb1 = (kb0 + kb_per_part < kblocks) ? kb0 + kb_per_part : kblocks;
-                const int nwin = (kb1 - kb0 + WIN - 1) / WIN;
+            const int nwin = (kblocks + WIN - 1) / WIN;
+            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
                 for (int w = 0; w < nwin && ok; ++w, ++win_iter) {
                     const uint32_t acc = win_iter & 1u;
                     const uint32_t acc_ph = (win_iter >> 1) & 1u;
                     if (!mbar_wait(smem_u32(&bars->tempty[acc]), acc_ph ^ 1u, abort_flag)) { ok = false; break; }
                     tc_fence_after();
                     const uint32_t d_tmem = tmem_base + acc * BN;
-                    const int kb_begin = kb0 + w * WIN;
-                    const int kb_end = (kb_begin + WIN < kb1) ? kb_begin + WIN : kb1;
+                    const int kb_begin = w * WIN;
+                    const int kb_end = (kb_begin + WIN < kblocks) ? kb_begin + WIN : kblocks;
                     for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
                         const uint32_t s = it % K::kStages;
                         const uint32_t ph = (it / K::kStages) & 1u;
                         if (!mbar_wait(smem_u32(&bars->full[s]), ph, abort_flag)) { ok = false; break; }
                         tc_fence_after();
-                        const uint32_t a_hi = tiles + s * K::kStageBytes;
-                        const uint32_t a_lo = a_hi + K::kATile;
-                        const uint32_t b_hi = a_hi + K::kAPlanes * K::kATile;
-                        const uint32_t b_lo = b_hi + K::kBTile;
+                        const uint32_t a_base = tiles + s * K::kStageBytes;
+                        const uint32_t b_base = a_base + K::kAPlanes * K::kATile;
 #pragma unroll
                         for (int k = 0; k < BK / UK; ++k) {
                             const uint32_t koff = k * UK * 2;           // bytes along K inside the swizzle row
-                            const uint64_t dah = umma_smem_desc(a_hi + koff, K::kSBO, K::kLayout);
-                            const uint64_t dal = umma_smem_desc(a_lo + koff, K::kSBO, K::kLayout);
-                            const uint64_t dbh = umma_smem_desc(b_hi + koff, K::kSBO, K::kLayout);
-                            // the first MMA of a window overwrites the accumulator; small terms go first
-                            const uint32_t keep = (kb != kb_begin || k != 0) ? 1u : 0u;
-                            if (NPROD == 3) {
-                                const uint64_t dbl = umma_smem_desc(b_lo + koff, K::kSBO, K::kLayout);
-                                umma_bf16(d_tmem, dah, dbl, idesc, keep);
-                                umma_bf16(d_tmem, dal, dbh, idesc, 1u);
-                            } else if (K::kSwap) {
-                                umma_bf16(d_tmem, dal, dbh, idesc, keep);
-                            } else {
-                                const uint64_t dbl = umma_smem_desc(b_lo + koff, K::kSBO, K::kLayout);
-                                umma_bf16(d_tmem, dah, dbl, idesc, keep);
+#pragma unroll
+                            for (int pr = 0; pr < K::kProducts; ++pr) {
+                                const int px = kProdX[NX - 1][pr], py = kProdY[NX - 1][pr];
+                                const int pa = K::kSwap ? py : px, pb = K::kSwap ? px : py;
+                                const uint64_t da = umma_smem_desc(a_base + pa * K::kATile + koff, K::kSBO, K::kLayout);
+                                const uint64_t db = umma_smem_desc(b_base + pb * K::kBTile + koff, K::kSBO, K::kLayout);
+                                // the first MMA of a window overwrites the accumulator; small terms go first
+                                umma_bf16(d_tmem, da, db, idesc, (kb != kb_begin || k != 0 || pr != 0) ? 1u : 0u);
                             }
-                            umma_bf16(d_tmem, dah, dbh, idesc, 1u);
                         }
                         umma_commit(smem_u32(&bars->empty[s]));        // frees the stage when these MMAs retire
                     }
@@ -350,14 +471,11 @@ umma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CU
         uint32_t win_iter = 0;
         const bool vec_ok = (C & 3) == 0;
         bool alive = true;
-        for (int u = blockIdx.x; u < total_units && alive; u += gridDim.x) {
-            const int part = u / total_tiles, t = u - part * total_tiles;
-            const int kb0 = part * kb_per_part;
-            const int kb1 = (kb0 + kb_per_part < kblocks) ? kb0 + kb_per_part : kblocks;
-            const int nwin = (kb1 - kb0 + WIN - 1) / WIN;
-            if (nwin <= 0) continue;
+        const int nwin = (kblocks + WIN - 1) / WIN;
+        for (int t = blockIdx.x; t < total_tiles && alive; t += gridDim.x) {
             int g, i, j;
             decode_work<K::kSwap>(t, G, NT, g, i, j);
+            const float alpha_g = (alpha * aux[8 + g]) * exp2f((float)-chunk_exponent(*pmax));
             const int row0 = i * BM + q * 32;
             const int row = row0 + lane;
             const int colbase = j * BN + half * 128;
@@ -407,8 +525,8 @@ umma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CU
 #pragma unroll
                         for (int e = 0; e < 8; ++e)
                             asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(hrow + col0 + 4 * e),
-                                         "f"(alpha * run[cb * 32 + 4 * e + 0]), "f"(alpha * run[cb * 32 + 4 * e + 1]),
-                                         "f"(alpha * run[cb * 32 + 4 * e + 2]), "f"(alpha * run[cb * 32 + 4 * e + 3])
+                                         "f"(alpha_g * run[cb * 32 + 4 * e + 0]), "f"(alpha_g * run[cb * 32 + 4 * e + 1]),
+                                         "f"(alpha_g * run[cb * 32 + 4 * e + 2]), "f"(alpha_g * run[cb * 32 + 4 * e + 3])
                                          : "memory");
                     } else if (vec_ok && col0 + 32 <= C) {
                         float4* p4 = reinterpret_cast<float4*>(hrow + col0);
@@ -416,10 +534,10 @@ umma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CU
                         for (int e = 0; e < 8; ++e) {
                             float4 o = (beta != 0.f) ? p4[e] : make_float4(0.f, 0.f, 0.f, 0.f);
                             if (beta != 1.f) { o.x *= beta; o.y *= beta; o.z *= beta; o.w *= beta; }
-                            o.x += alpha * run[cb * 32 + 4 * e + 0];
-                            o.y += alpha * run[cb * 32 + 4 * e + 1];
-                            o.z += alpha * run[cb * 32 + 4 * e + 2];
-                            o.w += alpha * run[cb * 32 + 4 * e + 3];
+                            o.x += alpha_g * run[cb * 32 + 4 * e + 0];
+                            o.y += alpha_g * run[cb * 32 + 4 * e + 1];
+                            o.z += alpha_g * run[cb * 32 + 4 * e + 2];
+                            o.w += alpha_g * run[cb * 32 + 4 * e + 3];
                             p4[e] = o;
                         }
                     } else {
@@ -428,7 +546,7 @@ umma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CU
                             if (col0 + e < C) {
                                 float o = (beta != 0.f) ? hrow[col0 + e] : 0.f;
                                 if (beta != 1.f) o *= beta;
-                                hrow[col0 + e] = o + alpha * run[cb * 32 + e];
+                                hrow[col0 + e] = o + alpha_g * run[cb * 32 + e];
                             }
                         }
                     }
@@ -535,33 +653,40 @@ static int num_sms() {
     return n;
 }
 
-template <int BK, int NPROD, bool WIDE_Y = false>
-static int launch_umma(void* planes, int64_t Kc, int C, int G, int nplanes, int b_plane0, float* H, float alpha,
-                       float beta, int* status, cudaStream_t st) {
-    using K = Cfg<BK, NPROD, WIDE_Y>;
+template <int BK, int NX, bool WIDE_Y = false>
+static int launch_umma(void* planes, int64_t Kc, int C, int G, int nplanes, float* H, float alpha, float beta,
+                       const float* aux, const unsigned int* pmax, int window_tokens, int* status, cudaStream_t st) {
+    using K = Cfg<BK, NX, WIDE_Y>;
+    const int win_blocks = window_tokens / BK > 0 ? window_tokens / BK : 1;
     CUtensorMap mapA, mapB;
     int rc = encode_map(&mapA, planes, Kc, C, nplanes, BK, BM, BK);
     if (rc != RQ_OK) return rc;
     rc = encode_map(&mapB, planes, Kc, C, nplanes, BK, BN, BK);
     if (rc != RQ_OK) return rc;
-    if (cudaFuncSetAttribute(umma_kernel<BK, NPROD, WIDE_Y>, cudaFuncAttributeMaxDynamicSharedMemorySize, K::kSmemBytes) !=
+    if (cudaFuncSetAttribute(umma_kernel<BK, NX, WIDE_Y>, cudaFuncAttributeMaxDynamicSharedMemorySize, K::kSmemBytes) !=
         cudaSuccess)
         return RQ_ERR_CUDA;
     const int MT = (C + BM - 1) / BM, NT = (C + BN - 1) / BN;
     const int total = ((NT - 1) * NT + MT) * G;
     const int kblocks = (int)(Kc / BK);
-    // The kernel can visit every tile ksplit times, each visit adding the sum over a share of the k-blocks with
-    // the reduction epilogue (units are (tile, part), part-major); that evens out the last round when the tile
-    // count is a poor multiple of the grid (+11 % at C = 1024, nothing at C = 4096).  It is left at 1: the order
-    // in which two parts reach an element of H is not fixed, and H + a + b is not H + b + a in fp32, so the
-    // split would make the accumulated Hessian differ from run to run in the last bit.
-    const int ksplit = 1;
-    const long long units = (long long)total * ksplit;
-    const int grid = units < num_sms() ? (int)units : num_sms();
+    // One work unit per tile and launch: every element of H receives exactly one add per launch, so the
+    // accumulated Hessian is the same bit pattern from run to run (splitting a tile's tokens over several
+    // CTAs would even out the last round of small problems, but H + a + b is not H + b + a in fp32).
+    const int grid = total < num_sms() ? total : num_sms();
     prof::Scope timed(RQ_PROF_HESSIAN_UMMA, st);
-    umma_kernel<BK, NPROD, WIDE_Y><<<grid, kThreads, K::kSmemBytes, st>>>(mapA, mapB, H, C, G, MT, NT, kblocks, 0,
-                                                                  b_plane0, alpha, beta, ksplit, status);
+    umma_kernel<BK, NX, WIDE_Y><<<grid, kThreads, K::kSmemBytes, st>>>(mapA, mapB, H, C, G, MT, NT, kblocks, 0, NX, alpha,
+                                                                      beta, aux, pmax, win_blocks, status);
     return check_launch();
+}
+
+template <typename T, int NX>
+static void launch_pack(const void* xp, int64_t ldx, const float* sp, float* aux, float2* tok, unsigned int* pmax,
+                        int nvalid, int C, int G, int64_t Kc, uint16_t* planes, float* partial, cudaStream_t st) {
+    const T* x = reinterpret_cast<const T*>(xp);
+    group_scale_kernel<<<1, 1024, 0, st>>>(sp, nvalid, G, aux, pmax);
+    token_stats_kernel<T><<<(unsigned)((Kc + 7) / 8), 256, 0, st>>>(x, ldx, sp, aux, nvalid, (int)Kc, C, G, tok, pmax);
+    dim3 pgrid((unsigned)(Kc / kPackTile), (unsigned)((C + kPackTile - 1) / kPackTile));
+    pack_kernel<T, NX><<<pgrid, 256, 0, st>>>(x, ldx, sp, aux, tok, pmax, nvalid, C, G, (int)Kc, planes, partial);
 }
 
 }  // namespace hess
@@ -569,13 +694,21 @@ static int launch_umma(void* planes, int64_t Kc, int C, int G, int nplanes, int 
 
 using namespace rq;
 
+// Layout of one chunk slot: planes [nx + 2G][C][Kc] fp16 | per-tile sums of squares [Kc/64][C] fp32 |
+// token statistics [Kc] float2 | group scales [16] fp32, largest P_t.  Sized for two X' planes (fp32 input),
+// whatever the dtype.
+static size_t slot_plane_bytes(int64_t Kc, int C, int nplanes) {
+    const size_t bytes = (size_t)nplanes * (size_t)C * (size_t)Kc * 2;
+    return (bytes + 1023) / 1024 * 1024;
+}
+
 extern "C" size_t rq_hessian_workspace_bytes(int64_t chunk_tokens, int C, int G, int has_saliency) {
+    (void)has_saliency;
     if (chunk_tokens <= 0 || C <= 0 || G <= 0) return 0;
     const int64_t Kc = (chunk_tokens + 63) / 64 * 64;
-    const int64_t planes = has_saliency ? 2 + 2 * (int64_t)G : 2;
-    size_t bytes = (size_t)planes * (size_t)C * (size_t)Kc * 2;
-    bytes = (bytes + 1023) / 1024 * 1024;
-    bytes += (size_t)(Kc / 64) * (size_t)C * 4;            // per-tile sums of squares
+    size_t bytes = slot_plane_bytes(Kc, C, 2 + 2 * G);
+    bytes += ((size_t)(Kc / 64) * (size_t)C * 4 + 1023) / 1024 * 1024;   // per-tile sums of squares
+    bytes += (size_t)Kc * 8 + 1024;                                        // token statistics, group scales
     return bytes + 1024;
 }
 
@@ -590,7 +723,11 @@ static int hessian_accum_impl(const void* x, int x_dtype, int64_t ldx, const flo
     if (!x || !H || !workspace || C <= 0 || G <= 0 || G > 8 || N < 0 || ldx < C) return RQ_ERR_INVALID;
     if (!sal && G != 1) return RQ_ERR_INVALID;
     if (x_dtype != RQ_F32 && x_dtype != RQ_BF16 && x_dtype != RQ_F16) return RQ_ERR_INVALID;
-    if (variant < 0 || variant > 2) return RQ_ERR_UNSUPPORTED;
+    // bits 0-3: operand layout; bits 4-5: accumulation window of 128 >> n tokens (32 needs the 32-token stages)
+    const int wincode = (variant >> 4) & 3;
+    if (variant < 0 || (variant & 15) > 2 || (variant >> 6) != 0 || wincode == 3) return RQ_ERR_UNSUPPORTED;
+    const int window = kWindowTokens >> wincode;
+    variant = (wincode == 2 && (variant & 15) == 0) ? 1 : (variant & 15);
     if (reinterpret_cast<uintptr_t>(workspace) % 1024 != 0) return RQ_ERR_INVALID;
     if (N == 0) return RQ_OK;
     const bool piped = gst != st;
@@ -609,16 +746,15 @@ static int hessian_accum_impl(const void* x, int x_dtype, int64_t ldx, const flo
     }
     cudaEvent_t slot_free[4] = {nullptr, nullptr, nullptr, nullptr};
 
-    const int nplanes = has_sal ? 2 + 2 * G : 2;
-    const int b_plane0 = has_sal ? 2 : 0;
-    const int nprod = (x_dtype == RQ_BF16) ? 2 : 3;
+    const int nx = x_dtype == RQ_F32 ? 2 : 1;
+    const int nplanes = nx + 2 * G;
     const size_t esz = x_dtype == RQ_F32 ? 4 : 2;
     int rc = RQ_OK;
     int64_t ci = 0;
     for (int64_t n0 = 0; n0 < N && rc == RQ_OK; n0 += chunk, ++ci) {
         const int slot = (int)(ci % nslots);
         uint8_t* slot_base = reinterpret_cast<uint8_t*>(workspace) + (size_t)slot * slot_bytes;
-        __nv_bfloat16* planes = reinterpret_cast<__nv_bfloat16*>(slot_base);
+        uint16_t* planes = reinterpret_cast<uint16_t*>(slot_base);
         if (piped && slot_free[slot]) {                       // the kernel that last read this slot must be done
             if (cudaStreamWaitEvent(st, slot_free[slot], 0) != cudaSuccess) { rc = RQ_ERR_CUDA; break; }
             cudaEventDestroy(slot_free[slot]);
@@ -626,24 +762,22 @@ static int hessian_accum_impl(const void* x, int x_dtype, int64_t ldx, const flo
         }
         const int nvalid = (int)((N - n0) < chunk ? (N - n0) : chunk);
         const int64_t Kc = ((int64_t)nvalid + 63) / 64 * 64;
-        size_t plane_bytes = (size_t)nplanes * (size_t)C * (size_t)Kc * 2;
-        plane_bytes = (plane_bytes + 1023) / 1024 * 1024;
+        const size_t plane_bytes = slot_plane_bytes(Kc, C, nplanes);
+        const size_t partial_bytes = ((size_t)(Kc / 64) * (size_t)C * 4 + 1023) / 1024 * 1024;
         float* partial = act_sq ? reinterpret_cast<float*>(slot_base + plane_bytes) : nullptr;
+        float2* tok = reinterpret_cast<float2*>(slot_base + plane_bytes + partial_bytes);
+        float* aux = reinterpret_cast<float*>(slot_base + plane_bytes + partial_bytes + (size_t)Kc * 8);
+        unsigned int* pmax = reinterpret_cast<unsigned int*>(aux + 16);
         const uint8_t* xp = reinterpret_cast<const uint8_t*>(x) + (size_t)n0 * (size_t)ldx * esz;
         const float* sp = has_sal ? sal + n0 * G : nullptr;
-        dim3 pgrid((unsigned)(Kc / kPackTile), (unsigned)((C + kPackTile - 1) / kPackTile));
-        const int write_xlo = (nprod == 3 || !has_sal) ? 1 : 0;     // without saliency X_lo doubles as Y_lo
         {
         prof::Scope timed(RQ_PROF_HESSIAN_PACK, st);
         if (x_dtype == RQ_F32)
-            pack_kernel<float><<<pgrid, 256, 0, st>>>(reinterpret_cast<const float*>(xp), ldx, sp, nvalid, C, G, (int)Kc,
-                                                       planes, partial, write_xlo);
+            launch_pack<float, 2>(xp, ldx, sp, aux, tok, pmax, nvalid, C, G, Kc, planes, partial, st);
         else if (x_dtype == RQ_BF16)
-            pack_kernel<__nv_bfloat16><<<pgrid, 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(xp), ldx, sp, nvalid,
-                                                               C, G, (int)Kc, planes, partial, write_xlo);
+            launch_pack<__nv_bfloat16, 1>(xp, ldx, sp, aux, tok, pmax, nvalid, C, G, Kc, planes, partial, st);
         else
-            pack_kernel<__half><<<pgrid, 256, 0, st>>>(reinterpret_cast<const __half*>(xp), ldx, sp, nvalid, C, G,
-                                                        (int)Kc, planes, partial, write_xlo);
+            launch_pack<__half, 1>(xp, ldx, sp, aux, tok, pmax, nvalid, C, G, Kc, planes, partial, st);
         }
         rc = check_launch();
         if (rc != RQ_OK) break;
@@ -660,15 +794,15 @@ static int hessian_accum_impl(const void* x, int x_dtype, int64_t ldx, const flo
             if (!ok) { rc = RQ_ERR_CUDA; break; }
         }
         const float b = (n0 == 0) ? beta : 1.f;
-        if (variant == 2)
-            rc = nprod == 3 ? launch_umma<64, 3>(planes, Kc, C, G, nplanes, b_plane0, H, alpha, b, status, gst)
-                            : launch_umma<64, 2, true>(planes, Kc, C, G, nplanes, b_plane0, H, alpha, b, status, gst);
-        else if (variant == 0)
-            rc = nprod == 3 ? launch_umma<64, 3>(planes, Kc, C, G, nplanes, b_plane0, H, alpha, b, status, gst)
-                            : launch_umma<64, 2>(planes, Kc, C, G, nplanes, b_plane0, H, alpha, b, status, gst);
+        if (nx == 2)
+            rc = variant == 1 ? launch_umma<32, 2>(planes, Kc, C, G, nplanes, H, alpha, b, aux, pmax, window, status, gst)
+                              : launch_umma<64, 2>(planes, Kc, C, G, nplanes, H, alpha, b, aux, pmax, window, status, gst);
+        else if (variant == 2)
+            rc = launch_umma<64, 1, true>(planes, Kc, C, G, nplanes, H, alpha, b, aux, pmax, window, status, gst);
+        else if (variant == 1)
+            rc = launch_umma<32, 1>(planes, Kc, C, G, nplanes, H, alpha, b, aux, pmax, window, status, gst);
         else
-            rc = nprod == 3 ? launch_umma<32, 3>(planes, Kc, C, G, nplanes, b_plane0, H, alpha, b, status, gst)
-                            : launch_umma<32, 2>(planes, Kc, C, G, nplanes, b_plane0, H, alpha, b, status, gst);
+            rc = launch_umma<64, 1>(planes, Kc, C, G, nplanes, H, alpha, b, aux, pmax, window, status, gst);
         if (rc != RQ_OK) break;
         if (piped && n0 + chunk < N) {
             if (cudaEventCreateWithFlags(&slot_free[slot], cudaEventDisableTiming) != cudaSuccess ||

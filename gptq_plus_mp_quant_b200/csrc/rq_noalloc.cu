@@ -10,9 +10,10 @@
 
 #include "rq_common.cuh"
 
-// 64 MiB per GPU that loads the library, held until the process exits.
+// 64 MiB per GPU that loads the library, held until the process exits.  The alignment is the one
+// rq_hessian_accum demands of any workspace it is given (1024 bytes: the swizzled TMA tiles of the planes).
 #define RQ_NOALLOC_SCRATCH_BYTES (64u * 1024u * 1024u)
-static __device__ __align__(256) unsigned char g_noalloc_scratch[RQ_NOALLOC_SCRATCH_BYTES];
+static __device__ __align__(1024) unsigned char g_noalloc_scratch[RQ_NOALLOC_SCRATCH_BYTES];
 
 namespace {
 constexpr int kMaxDevices = 64;

@@ -113,7 +113,14 @@ __host__ __device__ constexpr uint32_t umma_idesc_bf16_f32(int M, int N) {
            (static_cast<uint32_t>(M >> 4) << 24);
 }
 
+// The same for fp16 A and B (format code 0).  Both operands of a kind::f16 MMA must have the SAME 16-bit format:
+// a descriptor that paired an fp16 tile with a bf16 tile was rejected by the hardware as an illegal instruction.
+__host__ __device__ constexpr uint32_t umma_idesc_f16_f32(int M, int N) {
+    return (1u << 4) | (static_cast<uint32_t>(N >> 3) << 17) | (static_cast<uint32_t>(M >> 4) << 24);
+}
+
 // D[tmem] (+)= A[smem] . B[smem]^T, issued by one thread.
+// (kind::f16 covers bf16 and fp16 operands; the instruction descriptor says which.)
 __device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
                                           uint32_t accumulate) {
     asm volatile(

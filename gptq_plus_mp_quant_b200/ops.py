@@ -11,6 +11,9 @@ from . import _lib
 # tokens packed and contracted per launch pair; the scratch grows with it (about
 # (2 + 2G) * C * chunk * 2 bytes)
 HESSIAN_CHUNK_TOKENS = int(os.environ.get("REALQ_HESSIAN_CHUNK", "8192"))
+# kernel variant of rq_hessian_accum when the caller passes none (see the header: operand layout and
+# accumulation window)
+HESSIAN_VARIANT = int(os.environ.get("REALQ_HESSIAN_VARIANT", "0"))
 
 # Optional: packing on the caller's stream, tensor-core contraction on one extra stream per device, two rings of
 # chunk slots, so that the packing of one linear overlaps the contraction of another.  H is then complete in
@@ -82,12 +85,14 @@ def check_status(device) -> None:
 
 
 def hessian_accum(x: torch.Tensor, sal, H: torch.Tensor, act_sq, alpha: float = 1.0, beta: float = 1.0,
-                  variant: int = 0, chunk_tokens: int | None = None, pipeline: bool = False) -> None:
+                  variant: int | None = None, chunk_tokens: int | None = None, pipeline: bool = False) -> None:
     """``H[g] = beta*H[g] + alpha * X^T diag(sal[:, g]) X`` (upper-triangular tiles only) and
     ``act_sq += sum x^2``.  x: [N, C] fp32/bf16/fp16 (row stride free), sal: [N, G] fp32 or None,
     H: [G, C, C] fp32 contiguous (or [C, C] when sal is None).  ``pipeline=True`` issues the contraction on the
     device's extra stream (see HESSIAN_PIPELINE): H is then only complete after hessian_join()."""
     _lib.require_cuda(x, H, sal, act_sq)
+    if variant is None:
+        variant = HESSIAN_VARIANT
     assert x.dim() == 2, "x must be [tokens, channels]"
     N, Cc = x.shape
     if x.stride(1) != 1:

@@ -66,14 +66,18 @@ int rq_profile_read(int tag, double* total_ms, long long* launches);
  *
  * x: [N, C] with row stride ldx elements, dtype x_dtype; sal: [N, G] fp32; H: [G, C, C] fp32.
  * Only tiles on or above the diagonal of every H[g] are written; rq_hessian_finalize (or its
- * mirror-only mode) fills the lower triangle.  The contraction runs on the tensor cores as a
- * split-bf16 product with fp32 accumulation: three products when x is fp32/fp16, two when x is
- * bf16 (its low part is exactly zero).
+ * mirror-only mode) fills the lower triangle.  The contraction runs on the tensor cores as a split
+ * product of fp16 planes with fp32 accumulation: x and s*x are scaled per token and per group by
+ * powers of two (exact) so that they fit fp16's range, s*x is carried as hi + lo (22 significant
+ * bits), x as one plane when it is bf16 / fp16 and as hi + lo when it is fp32: two products per
+ * k-step for 16-bit input, three for fp32 input.
  * workspace: rq_hessian_workspace_bytes(chunk_tokens, C, G, sal != NULL) bytes for the chunk
  * size the caller wants (a multiple of 64; tokens are processed chunk by chunk), 1024-byte aligned.
  * status: optional device int; set to RQ_ERR_TIMEOUT if a device-side wait ran out.
- * variant: 0 = 64-token pipeline stages (128-byte swizzle), 1 = 32-token stages (64-byte swizzle),
- *          2 = as 0 but with the two-plane operand on the 256-row side also for bf16 input.
+ * variant: bits 0-3: 0 = 64-token pipeline stages (128-byte swizzle), 1 = 32-token stages (64-byte
+ *          swizzle), 2 = as 0 but with the two-plane operand on the 256-row side also for 16-bit input;
+ *          bits 4-5: tokens summed inside the tensor core before a round-to-nearest add, 128 >> n
+ *          (the tensor core's own accumulation truncates; shorter windows cost epilogue work).
  */
 size_t rq_hessian_workspace_bytes(int64_t chunk_tokens, int C, int G, int has_saliency);
 int rq_hessian_accum(const void* x, int x_dtype, int64_t ldx, const float* sal, float* H, float* act_sq,

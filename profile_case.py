@@ -1,9 +1,9 @@
 """Run one kernel of the quantization path on a small seeded case, a few launches, for profilers.
 
-    python -m gptq_plus_mp_quant_b200.profile_case hessian --C 2048 --G 4 --tokens 8192 --dtype bf16
-    python -m gptq_plus_mp_quant_b200.profile_case fwht --rows 65536 --n 12288 --dtype bf16
-    python -m gptq_plus_mp_quant_b200.profile_case chol --C 2048 --G 4
-    python -m gptq_plus_mp_quant_b200.profile_case fasterquant --R 4096 --C 2048 --G 4
+    python profile_case.py hessian --C 2048 --G 4 --tokens 8192 --dtype bf16
+    python profile_case.py fwht --rows 65536 --n 12288 --dtype bf16
+    python profile_case.py chol --C 2048 --G 4
+    python profile_case.py fasterquant --R 4096 --C 2048 --G 4
 
 The inputs exceed the 126 MB L2 but stay within a few GB, so that a multi-pass profiler capture
 finishes by itself in a minute or two.  Prints the mean device time per call measured with CUDA
@@ -12,8 +12,12 @@ events.
 from __future__ import annotations
 
 import argparse
+import os
+import sys
 
 import torch
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 
 
 def _time(fn, reps):
@@ -41,9 +45,9 @@ def main():
     ap.add_argument("--reps", type=int, default=3)
     ap.add_argument("--variant", type=int, default=0)
     a = ap.parse_args()
-    from . import ops
-    from .gptq_utils import fasterquant_impl as fi
-    from .utils import hadamard_utils as hu
+    from gptq_plus_mp_quant_b200 import ops
+    from gptq_plus_mp_quant_b200.gptq_utils import fasterquant_impl as fi
+    from gptq_plus_mp_quant_b200.utils import hadamard_utils as hu
     dt = {"bf16": torch.bfloat16, "f32": torch.float32, "f16": torch.float16}[a.dtype]
     dev = torch.device("cuda:0")
     g = torch.Generator(device=dev)
@@ -65,7 +69,7 @@ def main():
     elif a.case == "chol":
         x = torch.randn(4 * a.C, a.C, generator=g, device=dev) * torch.exp(torch.randn(a.C, generator=g, device=dev))
         H = (x.t() @ x / x.shape[0]).unsqueeze(0).repeat(a.G, 1, 1).contiguous()
-        from . import _lib
+        from gptq_plus_mp_quant_b200 import _lib
         fi.hinv_with_fallback(H, None, 0.01, True)
         _lib.profile_enable(True)
         ms = _time(lambda: fi.hinv_with_fallback(H, None, 0.01, True), a.reps)
@@ -75,8 +79,8 @@ def main():
         print(f"chol C={a.C} G={a.G}: {ms:.3f} ms per call, {(2.0 / 3.0) * a.C ** 3 * a.G / ms / 1e9:.2f} TFLOP/s (2/3 C^3 per group); "
               + ", ".join(f"{k} {v:.2f} ms" for k, v in parts.items()))
     else:
-        from .gptq_utils.gptq_plus_utils import GPTQPlus
-        from .utils.quant_utils import WeightQuantizer
+        from gptq_plus_mp_quant_b200.gptq_utils.gptq_plus_utils import GPTQPlus
+        from gptq_plus_mp_quant_b200.utils.quant_utils import WeightQuantizer
         x = (torch.randn(a.tokens, a.C, generator=g, device=dev) * torch.exp(torch.randn(a.C, generator=g, device=dev))).to(dt)
         s = torch.exp(3 * torch.randn(1, a.tokens, a.G, generator=g, device=dev)).clamp(max=1000.0)
         W = torch.randn(a.R, a.C, generator=g, device=dev) * 0.02
