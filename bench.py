@@ -1,18 +1,25 @@
 #!/usr/bin/env python
 """Benchmark of the per-layer GPTQ+ quantization path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload layer|hessian_c1]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--schedule sequential|all_at_once]
+                    [--workload c2|c3|c4_down]
 
-Prints ONE JSON line.  The default workload is one Qwen3-8B-shape decoder layer (hidden 4096,
-intermediate 12288, 32 query / 8 KV heads of 128): a step rotates the calibration activations
-online (Hadamard on [N, 4096] and [N, 12288]), accumulates the saliency-weighted Hessians of the
-seven linears over 128 x 2048 tokens, finalises them and runs fasterquant (W4, groupsize 128,
-act_order, GPTQ+ first-order term) on all seven.  Inputs are seeded synthetic tensors with the
-shapes and value distributions of the reference's calibration run; no dataset or checkpoint is
-used.  With N > 1 (torchrun, one rank per GPU) the calibration sequences are sharded over the ranks
-as the reference shards them, each partial Hessian sum is reduced over NCCL to the rank that owns
-the linear, the seven linears' fasterquant stages are spread over the ranks, and the quantized
-weights are broadcast back; timing is on the device, max over ranks.
+Prints ONE JSON line.  The default workload (c2) is one Qwen3-8B-shape decoder layer (hidden 4096,
+intermediate 12288, 32 query / 8 KV heads of 128): a step quantizes the layer's four module groups
+[q, k, v] -> [o] -> [gate, up] -> [down] one after the other, as the reference's caller must (each group's
+calibration inputs depend on the groups quantized before it); for every group it rotates the group's
+calibration activations online (Hadamard on [N, 4096] and [N, 12288]), accumulates the saliency-weighted
+Hessians of the group's linears over 128 x 2048 tokens, finalises them and runs fasterquant (W4, groupsize
+128, act_order, GPTQ+ first-order term), the linears of a group concurrently.  `--schedule all_at_once`
+feeds all seven linears in one pass and runs all seven fasterquant calls concurrently, which no caller of
+the drop-in API can do for a real model; it is kept for comparison.  Inputs are seeded synthetic tensors
+with the shapes and value distributions of the reference's calibration run; no dataset or checkpoint is
+used.  With N > 1 (torchrun, one rank per GPU) the calibration sequences are sharded over the ranks as the
+reference shards them (sequence s is the same tensor for every N), the upper triangles of the partial
+Hessian sums go through one NCCL reduce-scatter per linear (plus an all-gather among the ranks that share
+a saliency group), every rank quantizes its R/N rows of every linear, and one all-gather per linear
+completes the weights; timing is on the device, max over ranks, and after the timed region the result is
+compared with a one-rank run of the same data (`parity_vs_n1`).
 """
 from __future__ import annotations
 
@@ -138,7 +145,7 @@ def dist_setup():
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the Hessian kernel at C = 4096, G = 4, 8192 tokens
-# (ncu, summarised in profiles/hessian_umma_C4096_G4_tok8192_bf16.md)
+# (one ncu capture of that launch)
 UMMA_TRAFFIC_BYTES = 1.203e9
 
 
@@ -156,17 +163,6 @@ def count_library_launches(step):
         return 0
 
 
-def assign_owners(costs, world):
-    """Longest-processing-time-first assignment of fasterquant work units to ranks."""
-    load = [0.0] * world
-    owner = {}
-    for name, c in sorted(costs.items(), key=lambda kv: -kv[1]):
-        r = min(range(world), key=lambda i: load[i])
-        owner[name] = r
-        load[r] += c
-    return owner
-
-
 # ----------------------------------------------------------------------------------------------
 # workload: one Qwen3-8B-shape decoder layer (configs[2])
 # ----------------------------------------------------------------------------------------------
@@ -180,222 +176,311 @@ class LayerWorkload:
         ("o_proj", 4096, 4096, "attn"), ("gate_proj", 12288, 4096, "hid"), ("up_proj", 12288, 4096, "hid"),
         ("down_proj", 4096, 12288, "mlp"),
     ]
+    # the reference's caller quantizes these groups strictly one after the other, because each group's calibration
+    # inputs are produced by a forward pass through the groups quantized before it (utils/model_utils.py:406-418,
+    # gptq_utils/gptq_plus_utils.py:7096-7229)
+    MODULE_GROUPS = [["q_proj", "k_proj", "v_proj"], ["o_proj"], ["gate_proj", "up_proj"], ["down_proj"]]
+    STREAM_SEED = {"hid": 11, "attn": 12, "mlp": 13}
 
-    def __init__(self, rank, world, nseq=None):
+    def __init__(self, rank, world, nseq=None, schedule="sequential", full_data=False):
         from gptq_plus_mp_quant_b200.utils import hadamard_utils as hu
         self.rank, self.world = rank, world
+        self.schedule = schedule
         total = nseq or self.NSEQ
         self.nseq_total = total
-        self.nseq_local = total // world
+        # every rank materialises its shard of ONE dataset: sequence s is the same tensor whatever the world size
+        # (full_data: all of it, for the one-rank run a data-parallel result is compared with)
+        self.seqs = list(range(total)) if (full_data or world == 1) else \
+            list(range(rank * (total // world), (rank + 1) * (total // world)))
+        self.nseq_local = len(self.seqs)
+        self.parallel = world > 1 and not full_data
         dev = torch.device("cuda", torch.cuda.current_device())
         self.dev = dev
-        g = torch.Generator(device=dev)
-        g.manual_seed(4321 + rank)
         n, T = self.nseq_local, self.T
 
-        def acts(width):
-            ch = torch.exp(torch.randn(width, generator=g, device=dev))
+        def acts(key, width):
+            g = torch.Generator(device=dev)
+            g.manual_seed(4321 + self.STREAM_SEED[key])
+            ch = torch.exp(torch.randn(width, generator=g, device=dev))          # shared channel scales
             out = torch.empty(n, T, width, dtype=torch.bfloat16, device=dev)
-            for s in range(0, n, 8):
-                out[s:s + 8] = (torch.randn(min(8, n - s), T, width, generator=g, device=dev) * ch).bfloat16()
+            for i, sq in enumerate(self.seqs):
+                g.manual_seed(1_000_003 * self.STREAM_SEED[key] + sq)            # by GLOBAL sequence index
+                out[i] = (torch.randn(T, width, generator=g, device=dev) * ch).bfloat16()
             return out
 
-        self.dev_in = {"hid": acts(self.HID), "attn": acts(self.HID), "mlp": acts(self.INTER)}
-        self.host_in = {k: v.cpu().pin_memory() for k, v in self.dev_in.items()}
+        self.dev_in = {"hid": acts("hid", self.HID), "attn": acts("attn", self.HID), "mlp": acts("mlp", self.INTER)}
+        self.host_in = None
         self.had12, _ = hu.get_hadK(self.INTER)
         gw = torch.Generator(device=dev)
-        gw.manual_seed(99)                                       # weights identical on every rank
+        gw.manual_seed(99)                                       # weights, gradients, saliencies: same on every rank
         self.layers, self.master, self.sal, self.grad = {}, {}, {}, {}
         for name, R, C, _ in self.LINEARS:
             w = (torch.randn(R, C, generator=gw, device=dev) * 0.02).bfloat16()
             lin = torch.nn.Linear(C, R, bias=False, device=dev, dtype=torch.bfloat16)
             lin.weight.requires_grad_(False)
             self.layers[name], self.master[name] = lin, w
-            s = torch.exp(3.0 * torch.randn(n, T, self.G, generator=g, device=dev))
+            s = torch.exp(3.0 * torch.randn(total, T, self.G, generator=gw, device=dev))
             cap = torch.quantile(s.flatten()[:1_000_000], 0.99)
-            self.sal[name] = torch.clamp(s, max=cap)
+            self.sal[name] = torch.clamp(s, max=cap)[self.seqs[0]:self.seqs[-1] + 1].contiguous()
             self.grad[name] = torch.randn(R, C, generator=gw, device=dev) * 1e-4
-        # a unit of fasterquant work = one saliency group of one linear (own Hessian, own rows): factorisation
-        # ~ C^3, first-order terms and lazy updates ~ rows * C^2, plus a per-unit launch overhead
-        costs = {(name, g): (2.0 / 3.0) * C ** 3 + 5.0 * (R // self.G) * C * C + 3e10
-                 for name, R, C, _ in self.LINEARS for g in range(self.G)}
-        unit_owner = assign_owners(costs, world)
-        self.owner = {name: [unit_owner[(name, g)] for g in range(self.G)] for name, _, _, _ in self.LINEARS}
-        # every linear has the same G, so a fixed pattern balances as well as the cost model and turns the exchange
-        # of a linear into one reduce-scatter
-        from gptq_plus_mp_quant_b200.utils import dist_utils as du
-        k = world // self.G if world % self.G == 0 else 1
-        lin_class = assign_owners({name: sum(costs[(name, g)] for g in range(self.G)) for name, _, _, _ in self.LINEARS},
-                                  max(k, 1))                           # which of a group's k ranks owns it, per linear
-        for name, _, _, _ in self.LINEARS:
-            pat = du.group_owner_pattern(self.G, world, salt=lin_class[name])
-            if pat is not None:
-                self.owner[name] = pat
-                for g in range(self.G):
-                    unit_owner[(name, g)] = pat[g]
         self.recorder = None
         self.copy_stream = None
         self.comm_stream = None
         # "1": start each linear's exchange of partial Hessians right after its last add_batch, on a side stream
-        # (GPTQPlus.begin_exchange).  Same results; measured on 2 GPUs it did not shorten the step, so it is off.
+        # (GPTQPlus.begin_exchange), so that it runs under the Hessian GEMMs of the group's other linears
         self.overlap_exchange = os.environ.get("REALQ_BENCH_OVERLAP_EXCHANGE", "0") != "0"
         self.fq_streams = int(os.environ.get("REALQ_BENCH_FQ_STREAMS", str(len(self.LINEARS))))
         self.fq_pool = None
-        self.unit_cost = {name: sum(c for (n, g), c in costs.items() if n == name and (world == 1 or unit_owner[(n, g)] == rank))
-                          for name, _, _, _ in self.LINEARS}
+        self.stage_events = None                                 # list of (stage name, start event, end event)
+        self.keep = None                                         # dict: per-linear H / codes of the last step
+        self.force_act_square = None                             # dict: per-linear act_square to order the columns by
+
+    def groups(self):
+        if self.schedule == "sequential":
+            return self.MODULE_GROUPS
+        return [[name for name, _, _, _ in self.LINEARS]]        # all seven at once
 
     # ---- algorithmic work figures
     def hessian_flops(self, local=False):
         n = (self.nseq_local if local else self.nseq_total) * self.T
         return sum(2.0 * n * C * C * self.G for _, _, C, _ in self.LINEARS)
 
+    def rotations_per_step(self):
+        """(stream, width) of every online rotation a step performs: each group's pass rotates its own inputs."""
+        out = []
+        for grp in self.groups():
+            keys = {key for name, _, _, key in self.LINEARS if name in grp}
+            out += [(k, self.HID if k == "hid" else self.INTER) for k in sorted(keys) if k != "attn"]
+        return out
+
     def fwht_bytes_local(self):
         n = self.nseq_local * self.T
-        return 2 * n * (self.HID + self.INTER) * 2
+        return sum(2 * n * width * 2 for _, width in self.rotations_per_step())
 
-    def _quantize(self, inputs, from_host):
+    def _mark(self, name, start):
+        if self.stage_events is not None:
+            e = torch.cuda.Event(enable_timing=True)
+            e.record()
+            self.stage_events.append((name, start, e))
+
+    def _quantize(self, from_host, export=False):
         from gptq_plus_mp_quant_b200.gptq_utils.gptq_plus_utils import GPTQPlus
         from gptq_plus_mp_quant_b200.utils import hadamard_utils as hu
         from gptq_plus_mp_quant_b200.utils.quant_utils import WeightQuantizer
-        import torch.distributed as dist
-        objs = {}
-        for name, R, C, _ in self.LINEARS:
-            self.layers[name].weight.data.copy_(self.master[name])
-            o = GPTQPlus(self.layers[name], self.sal[name], self.grad[name], self.G, 0.25, 0.7)
-            o.quantizer = WeightQuantizer()
-            o.quantizer.configure(4, perchannel=True, sym=True, mse=False)
-            o.profile_recorder = self.recorder
-            objs[name] = o
+        if from_host and self.host_in is None:
+            self.host_in = {k: v.cpu().pin_memory() for k, v in self.dev_in.items()}
+        inputs = self.host_in if from_host else self.dev_in
         main = torch.cuda.current_stream()
-
-        def fetch(s):
-            """Batch s of the three activation streams.  From the host: copied on a side stream, one batch ahead of
-            the kernels that consume it, so that the PCIe transfer overlaps the Hessian GEMMs of the batch before."""
-            if s >= self.nseq_local:
-                return None
-            if not from_host:
-                return {key: inputs[key][s:s + self.BSZ] for key in ("hid", "attn", "mlp")}, None
-            if self.copy_stream is None:
-                self.copy_stream = torch.cuda.Stream()
-            got, evs = {}, {}
-            with torch.cuda.stream(self.copy_stream):
-                for key in ("hid", "attn", "mlp"):            # in the order the linears consume them
-                    got[key] = inputs[key][s:s + self.BSZ].cuda(non_blocking=True)
-                    evs[key] = torch.cuda.Event()
-                    evs[key].record(self.copy_stream)
-            return got, evs
-
-        nxt = fetch(0)
-        for s in range(0, self.nseq_local, self.BSZ):
-            batch, ready = nxt
-            nxt = fetch(s + self.BSZ)
-            rot = {}
-
-            def rotated(key):
-                """This batch's input of one activation stream, rotated where the layer rotates it; waits for that
-                stream's copy only, so that the first GEMMs start while the rest of the batch is still in flight."""
-                if key not in rot:
-                    if ready is not None:
-                        main.wait_event(ready[key])
-                        batch[key].record_stream(main)
-                    rot[key] = (hu.matmul_hadU_cuda(batch[key], None, 1) if key == "hid" else
-                                batch[key] if key == "attn" else hu.matmul_hadU_cuda(batch[key], self.had12, 12))
-                return rot[key]
-
-            last = self.world > 1 and self.overlap_exchange and s + self.BSZ >= self.nseq_local
-            if last and self.comm_stream is None:
-                self.comm_stream = torch.cuda.Stream()
-            # in the last batch the widest linear goes first: its exchange is the longest, and it then runs under
-            # the GEMMs of the others (every rank uses the same order, as the collectives require)
-            for name, _, _, key in (self.LINEARS[::-1] if last else self.LINEARS):
-                objs[name].add_batch(rotated(key), None)
-                if last:
-                    objs[name].group_owners = self.owner[name]
-                    objs[name].begin_exchange(self.comm_stream)
+        spec = {name: (R, C, key) for name, R, C, key in self.LINEARS}
         checksum = torch.zeros((), device=self.dev)
-        # three phases, so that no rank waits in a collective for another rank's fasterquant: all exchanges of
-        # the partial Hessians, then every rank's own (linear, group) units, then the gather of the rows
-        for name, R, C, _ in self.LINEARS:
-            o = objs[name]
-            o.group_owners = self.owner[name] if self.world > 1 else None
-            o.finalize_hessian()
-        mine = [name for name, _, _, _ in self.LINEARS if self.world == 1 or self.rank in self.owner[name]]
+        for grp in self.groups():
+            keys = [k for k in ("hid", "attn", "mlp") if any(spec[nm][2] == k for nm in grp)]
+            objs = {}
+            for name in grp:
+                self.layers[name].weight.data.copy_(self.master[name])
+                o = GPTQPlus(self.layers[name], self.sal[name], self.grad[name], self.G, 0.25, 0.7)
+                o.quantizer = WeightQuantizer()
+                o.quantizer.configure(4, perchannel=True, sym=True, mse=False)
+                o.profile_recorder = self.recorder
+                o.row_parallel = self.parallel
+                objs[name] = o
+            t_pass = torch.cuda.Event(enable_timing=True) if self.stage_events is not None else None
+            if t_pass is not None:
+                t_pass.record()
 
-        def quantize(name):
-            objs[name].fasterquant(blocksize=128, percdamp=0.01, groupsize=128, actorder=True, static_groups=True)
+            def fetch(s):
+                """Batch s of this group's activation streams.  From the host: copied on a side stream, one batch
+                ahead of the kernels that consume it, so that the transfer overlaps the Hessian GEMMs before it."""
+                if s >= self.nseq_local:
+                    return None
+                if not from_host:
+                    return {key: inputs[key][s:s + self.BSZ] for key in keys}, None
+                if self.copy_stream is None:
+                    self.copy_stream = torch.cuda.Stream()
+                got, evs = {}, {}
+                with torch.cuda.stream(self.copy_stream):
+                    for key in keys:
+                        got[key] = inputs[key][s:s + self.BSZ].cuda(non_blocking=True)
+                        evs[key] = torch.cuda.Event()
+                        evs[key].record(self.copy_stream)
+                return got, evs
 
-        if self.fq_streams <= 1 or len(mine) <= 1:
-            for name in mine:
-                quantize(name)
-        else:
-            # The linears are independent, and much of fasterquant is a chain of short dependent launches (the
-            # diagonal blocks of the factorisation, the 128-column block loop): one host thread and one stream per
-            # linear lets those chains overlap each other and the other linears' GEMMs.
-            if self.fq_pool is None:
-                from concurrent.futures import ThreadPoolExecutor
-                self.fq_pool = ThreadPoolExecutor(max_workers=self.fq_streams)
-                self.fq_stream_list = [torch.cuda.Stream() for _ in range(self.fq_streams)]
-            ready = torch.cuda.Event()
-            ready.record(main)
-            dev_index = self.dev.index
+            nxt = fetch(0)
+            for s in range(0, self.nseq_local, self.BSZ):
+                batch, ready = nxt
+                nxt = fetch(s + self.BSZ)
+                rot = {}
 
-            def work(slot, names):
-                torch.cuda.set_device(dev_index)
-                st = self.fq_stream_list[slot]
-                st.wait_event(ready)
-                with torch.cuda.stream(st):
-                    for name in names:
-                        quantize(name)
-                done = torch.cuda.Event()
-                done.record(st)
-                return done
+                def rotated(key):
+                    if key not in rot:
+                        if ready is not None:
+                            main.wait_event(ready[key])
+                            batch[key].record_stream(main)
+                        rot[key] = (hu.matmul_hadU_cuda(batch[key], None, 1) if key == "hid" else
+                                    batch[key] if key == "attn" else hu.matmul_hadU_cuda(batch[key], self.had12, 12))
+                    return rot[key]
 
-            order = sorted(mine, key=lambda n: -self.unit_cost[n])          # longest first, round-robin over slots
-            slots = [order[i::self.fq_streams] for i in range(self.fq_streams)]
-            futures = [self.fq_pool.submit(work, i, names) for i, names in enumerate(slots) if names]
-            for f in futures:
-                main.wait_event(f.result())
-        for name, R, C, _ in self.LINEARS:
-            if self.world > 1:
-                w, rps = self.layers[name].weight.data, R // self.G
-                for g, src in enumerate(self.owner[name]):
-                    dist.broadcast(w[g * rps:(g + 1) * rps], src=src)
-            checksum += self.layers[name].weight.data.float().abs().mean()
-            objs[name].free()
+                last = self.parallel and self.overlap_exchange and s + self.BSZ >= self.nseq_local
+                if last and self.comm_stream is None:
+                    self.comm_stream = torch.cuda.Stream()
+                # in the last batch the widest linear goes first: its exchange is the longest, and it then runs under
+                # the GEMMs of the others (every rank uses the same order, as the collectives require)
+                for name in (sorted(grp, key=lambda nm: -spec[nm][1] * spec[nm][1]) if last else grp):
+                    objs[name].add_batch(rotated(spec[name][2]), None)
+                    if last:
+                        objs[name].begin_exchange(self.comm_stream)
+            if t_pass is not None:
+                self._mark("hessian_pass", t_pass)
+                t_x = torch.cuda.Event(enable_timing=True)
+                t_x.record()
+            for name in grp:
+                objs[name].finalize_hessian()
+                if self.keep is not None:
+                    self.keep[name] = {"act_square": objs[name].act_square.clone()}
+                if self.force_act_square is not None:
+                    objs[name].act_square.copy_(self.force_act_square[name])
+            if t_pass is not None:
+                self._mark("exchange_finalize", t_x)
+                t_f = torch.cuda.Event(enable_timing=True)
+                t_f.record()
+
+            def quantize(name):
+                objs[name].fasterquant(blocksize=128, percdamp=0.01, groupsize=128, actorder=True, static_groups=True,
+                                       export_to_et=export)
+
+            if self.fq_streams <= 1 or len(grp) <= 1:
+                for name in grp:
+                    quantize(name)
+            else:
+                # The linears of a group are independent, and much of fasterquant is a chain of short dependent
+                # launches (the diagonal blocks of the factorisation, the 128-column block loop): one host thread
+                # and one stream per linear lets those chains overlap each other and the other linears' GEMMs.
+                if self.fq_pool is None:
+                    from concurrent.futures import ThreadPoolExecutor
+                    self.fq_pool = ThreadPoolExecutor(max_workers=self.fq_streams)
+                    self.fq_stream_list = [torch.cuda.Stream() for _ in range(self.fq_streams)]
+                ready_ev = torch.cuda.Event()
+                ready_ev.record(main)
+                dev_index = self.dev.index
+
+                def work(slot, names):
+                    torch.cuda.set_device(dev_index)
+                    st = self.fq_stream_list[slot]
+                    st.wait_event(ready_ev)
+                    with torch.cuda.stream(st):
+                        for name in names:
+                            quantize(name)
+                    done = torch.cuda.Event()
+                    done.record(st)
+                    return done
+
+                order = sorted(grp, key=lambda nm: -(spec[nm][1] ** 3 + spec[nm][0] * spec[nm][1] ** 2))
+                slots = [order[i::self.fq_streams] for i in range(self.fq_streams)]
+                futures = [self.fq_pool.submit(work, i, names) for i, names in enumerate(slots) if names]
+                for f in futures:
+                    main.wait_event(f.result())
+            if t_pass is not None:
+                self._mark("fasterquant", t_f)
+                t_g = torch.cuda.Event(enable_timing=True)
+                t_g.record()
+            for name in grp:
+                objs[name].gather_rows_()
+                checksum += self.layers[name].weight.data.float().abs().mean()
+            if t_pass is not None:
+                self._mark("gather_rows", t_g)
+            for name in grp:
+                if self.keep is not None:
+                    o = objs[name]
+                    first, count = o._owned_groups if o._owned_groups is not None else (0, self.G)
+                    self.keep[name].update({"H": o._H[first:first + count].clone(), "groups": (first, count),
+                                            "codes": self.layers[name].int_weight.clone() if export else None,
+                                            "weight": self.layers[name].weight.data.clone()})
+                objs[name].free()
         return checksum
 
     def step_device(self):
-        return self._quantize(self.dev_in, False)
+        return self._quantize(False)
 
     def step_e2e(self):
         """Public API with HOST activations: each batch is copied from pinned host memory inside the timed
         region and a checksum of the quantized weights is read back."""
-        return float(self._quantize(self.host_in, True).item())
+        return float(self._quantize(True).item())
 
     def h2d_bytes(self):
-        return sum(v.numel() * 2 for v in self.host_in.values())
-
-    def _owned_runs(self, name):
-        """Runs of consecutive groups of this linear that this rank owns (one fasterquant pass each)."""
-        mine = [g for g, r in enumerate(self.owner[name]) if r == self.rank]
-        return sum(1 for i, g in enumerate(mine) if i == 0 or mine[i - 1] != g - 1)
+        """Bytes copied from the host per step: every group's pass fetches the streams it consumes."""
+        n = self.nseq_local * self.T
+        total = 0
+        for grp in self.groups():
+            keys = {key for name, _, _, key in self.LINEARS if name in grp}
+            total += sum(n * (self.INTER if k == "mlp" else self.HID) * 2 for k in keys)
+        return total
 
     def launches_per_step(self):
         """Kernel launches of this library in one step on this rank, counted from the host loops (used where no
-        activity trace is taken; agrees with the traced count of the 1-GPU step to about one per cent)."""
+        activity trace is taken; agrees with the traced count of the 1-GPU step to a few per cent)."""
         batches = self.nseq_local // self.BSZ
         chunks = max(1, (self.BSZ * self.T) // 8192)
-        n = batches * 2                                               # two rotations per batch
-        n += batches * len(self.LINEARS) * chunks * 3                 # pack + sum-of-squares reduce + tensor-core GEMM
+        n = batches * len(self.rotations_per_step())
+        n += batches * len(self.LINEARS) * chunks * 5           # scales (2) + pack + sum-of-squares reduce + GEMM
         for name, R, C, _ in self.LINEARS:
-            n += 1                                                    # finalize
-            runs = 1 if self.world == 1 else self._owned_runs(name)
+            n += 1 + (2 if self.parallel else 0)                      # finalize (+ pack / unpack of the exchange)
             blocks = C // 128
             levels = max(0, math.ceil(math.log2(max(C / 512, 1))))    # tensor-core levels of the triangular inverse
             chol = 4 * blocks + 5 * levels + 3                        # diag, panel, (split +) trailing, inverse, checks
             loop = 3 * blocks + 9                                     # prepare, splits, terms, block + 2 updates, epilogue
-            n += runs * (chol + loop + 3)                             # + range searches
+            n += chol + loop + 3                                      # + range searches
         return n
+
+
+def parity_vs_one_rank(wl, rank, world):
+    """Outside the timed region: the data-parallel result against a one-rank run of the same data.  Every rank runs
+    the one-rank computation itself on the full data set (no communication), then compares: the Hessian groups it
+    holds (relative Frobenius), act_square, the integer codes and the written weights of every linear.  Also
+    asserts that all ranks hold the same gathered weights, bit for bit (the reference's own check,
+    utils/dist_utils.py:179-199).
+
+    act_order sorts the input channels by act_square.  Sums over the same tokens taken in another order (per rank,
+    then over ranks) differ by fp32 rounding, ~1e-7 relative, and among thousands of channels a few neighbours in
+    the sorted order are closer than that; where two such channels swap, every row is quantized in a different
+    column order and its codes change for real, not by rounding.  That is a property of the ordering rule, not of
+    the sums, so the one-rank run is given the data-parallel run's act_square to order by, and the number of
+    positions at which its own order would have differed is reported beside the comparison."""
+    import torch.distributed as dist
+    from gptq_plus_mp_quant_b200.utils import dist_utils as du
+    wl.keep = {}
+    wl._quantize(False, export=True)
+    got = wl.keep
+    for name in got:
+        du.assert_bit_exact(got[name]["weight"], tag=f"{name}.weight")
+    torch.cuda.synchronize()
+    solo = LayerWorkload(rank, world, nseq=wl.nseq_total, schedule=wl.schedule, full_data=True)
+    solo.keep = {}
+    solo.force_act_square = {name: got[name]["act_square"] for name in got}
+    with du.local_only():
+        solo._quantize(False, export=True)
+    ref = solo.keep
+    out = {}
+    for name in got:
+        first, count = got[name]["groups"]
+        h_ref = ref[name]["H"][first:first + count].double()
+        h_err = float(((got[name]["H"].double() - h_ref).norm() / h_ref.norm()).item())
+        a_ref = ref[name]["act_square"]
+        a_err = float(((got[name]["act_square"] - a_ref).abs() / a_ref.abs().clamp_min(1e-30)).max().item())
+        moved = int((torch.argsort(got[name]["act_square"], descending=True)
+                     != torch.argsort(a_ref, descending=True)).sum().item())
+        diff = got[name]["codes"] != ref[name]["codes"]
+        w_ok = torch.allclose(got[name]["weight"].float(), ref[name]["weight"].float(), rtol=1e-4, atol=1e-3)
+        stats = torch.tensor([h_err, a_err, float(diff.float().mean().item()),
+                              float(diff.any(dim=1).float().mean().item()), 0.0 if w_ok else 1.0],
+                             device=wl.dev, dtype=torch.float64)
+        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+        out[name] = {"H_rel_fro": float(f"{stats[0].item():.3e}"), "act_square_rel_max": float(f"{stats[1].item():.3e}"),
+                     "act_order_positions_moved": moved, "codes_differ": float(f"{stats[2].item():.3e}"),
+                     "rows_touched": float(f"{stats[3].item():.3e}"),
+                     "weights_allclose_atol1e-3_rtol1e-4": bool(stats[4].item() == 0.0)}
+    wl.keep = None
+    del solo
+    return out
 
 
 # ----------------------------------------------------------------------------------------------
@@ -473,13 +558,19 @@ def run_ours(args):
     from gptq_plus_mp_quant_b200 import _lib
     rank, world, local = dist_setup()
     peaks = load_peaks()
-    wl = LayerWorkload(rank, world)
+    wl = LayerWorkload(rank, world, schedule=args.schedule)
     dev = wl.dev
 
     def barrier():
         if world > 1:
             torch.distributed.barrier()
         torch.cuda.synchronize()
+
+    def max_over_ranks(values):
+        t = torch.tensor(values, device=dev, dtype=torch.float64)
+        if world > 1:
+            torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        return t.tolist()
 
     def timed(fn, steps):
         barrier()
@@ -489,10 +580,7 @@ def run_ours(args):
             fn()
         e1.record()
         barrier()
-        ms = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
-        if world > 1:
-            torch.distributed.all_reduce(ms, op=torch.distributed.ReduceOp.MAX)
-        return float(ms.item())
+        return max_over_ranks([e0.elapsed_time(e1)])[0]
 
     warm = max(args.warmup, 3)
     for _ in range(warm):
@@ -508,16 +596,28 @@ def run_ours(args):
              ("terms", _lib.PROF_TERMS), ("block", _lib.PROF_BLOCK), ("lazy", _lib.PROF_LAZY))}
     _lib.profile_enable(False)
     clocks = sampler.stop()
-    wl.recorder = EventRecorder()                      # one extra, untimed step for the host-level stage breakdown
+    # one extra, untimed step for the wall-clock stages of the schedule (events on the main stream between the
+    # phases of every module group, summed over the groups, max over ranks) and the host-level sections
+    wl.recorder = EventRecorder()
+    wl.stage_events = []
+    barrier()
     if world == 1:
         counted = count_library_launches(wl.step_device)   # ... and for the launch count (activity trace of that step)
     else:
         counted = 0                                  # ranks must not diverge inside a step with collectives
         wl.step_device()
+    torch.cuda.synchronize()
+    stage_names = ["hessian_pass", "exchange_finalize", "fasterquant", "gather_rows"]
+    wall = {k: 0.0 for k in stage_names}
+    for name, a, b in wl.stage_events:
+        wall[name] += a.elapsed_time(b)
+    wall = dict(zip(stage_names, (round(v, 2) for v in max_over_ranks([wall[k] for k in stage_names]))))
+    wl.stage_events = None
     sections = {k: round(v, 2) for k, v in sorted(wl.recorder.summary().items(), key=lambda kv: -kv[1])}
     wl.recorder = None
     checksum = wl.step_e2e()
     e2e_ms = timed(wl.step_e2e, args.steps)
+    parity = parity_vs_one_rank(wl, rank, world) if (world > 1 and not args.no_parity) else None
 
     sec_per_layer = total_ms / args.steps / 1e3
     umma_ms, umma_n = prof["umma"]
@@ -525,29 +625,41 @@ def run_ours(args):
     achieved = wl.hessian_flops(local=True) * args.steps / (umma_ms * 1e-3) / 1e12 if umma_ms else 0.0
     peak = peaks["bf16_tflops_sustained"]
     fwht_ms, fwht_n = prof["fwht"]
+    if world > 1:
+        par = (f"dp{world}: calibration sequences sharded (sequence s is the same tensor for every world size); per "
+               "linear one NCCL reduce-scatter of the packed upper triangles of the partial Hessians"
+               + (" and an all-gather among the ranks that share a saliency group" if world > wl.G else "")
+               + f"; every rank runs fasterquant on its R/{world} rows of every linear; one all-gather per linear "
+               "completes the weights")
+    else:
+        par = "single GPU"
     out = {
         "metric": METRIC, "value": round(sec_per_layer, 4), "unit": "s", "n_gpus": world, "steps": args.steps,
         "warmup": warm, "ms_per_step": round(total_ms / args.steps, 2), "higher_is_better": False,
-        "scaling": "strong", "vs_baseline": None, "dtype": "bf16 split products, f32 accumulate; f32 elsewhere",
+        "scaling": "strong", "vs_baseline": None, "dtype": "f16 split products, f32 accumulate; f32 elsewhere",
         "data": "synthetic",
         "config": {"workload": wl.name, "tokens": wl.nseq_total * wl.T, "hessian_accum_bsz": wl.BSZ,
+                   "schedule": (wl.schedule + (": module groups [q,k,v] -> [o] -> [gate,up] -> [down] one after the "
+                                               "other, concurrency only inside a group"
+                                               if wl.schedule == "sequential" else
+                                               ": all seven linears fed in one pass and quantized concurrently")),
                    "l2": "per-step inputs (10.7 GB of activations, 4 GB of Hessians) exceed the 126 MB L2",
-                   "parallelism": (f"dp{world}: calibration sequences sharded, one NCCL reduce-scatter per linear "
-                                   "delivers each group's H to the owner of that (linear, group), fasterquant of "
-                                   "the 28 (linear, group) units spread over ranks, quantized rows broadcast from "
-                                   "their owners"),
-                   "fasterquant_owner": wl.owner if world > 1 else None},
+                   "parallelism": par},
         "hessian_accum_tflops": round(wl.hessian_flops() * args.steps / (umma_ms * 1e-3 + prof["pack"][0] * 1e-3)
                                       / 1e12, 1) if umma_ms else None,
         "roofline": {"bound": "tensor", "achieved": round(achieved, 1), "peak": peak, "unit": "TFLOP/s",
                      "frac": round(achieved / peak, 4), "traffic": UMMA_TRAFFIC_BYTES,
                      "traffic_note": "dram__bytes_read+write of one C=4096 G=4 8192-token launch (6 of the 7 launches "
-                                     "per chunk), ncu; algorithmic 0.89e9; the C=12288 launch was not captured",
+                                     "per chunk), ncu; algorithmic 0.89e9",
                      "peak_source": peaks["source"] + " sustained",
-                     "kernel": "rq::hess::umma_kernel<64,2> (+<64,3> for fp32 inputs)", "launches": umma_n,
-                     "note": "algorithmic 2*N*C^2*G; the kernel issues 2 bf16 products on the ~53% of tiles that "
+                     "kernel": "rq::hess::umma_kernel<64,1> (<64,2> for fp32 inputs)", "launches": umma_n,
+                     "note": "algorithmic 2*N*C^2*G; the kernel issues 2 fp16 products on the ~53% of tiles that "
                              "touch the upper triangle"},
-        "stage_ms_per_step": {k: round(v[0] / args.steps, 2) for k, v in prof.items()},
+        # device time of the tagged kernels, summed over their launches (the linears of a group run on concurrent
+        # streams, so the fasterquant-side figures add up to more than the wall time of that phase)
+        "kernel_ms_per_step": {k: round(v[0] / args.steps, 2) for k, v in prof.items()},
+        # wall time of the phases of the schedule, from events on the main stream, summed over the module groups
+        "stage_ms_per_step": wall,
         "section_ms": sections,
         "fwht_gbs": round(wl.fwht_bytes_local() * args.steps / (fwht_ms * 1e-3) / 1e9, 1) if fwht_ms else None,
         "e2e": {"value": round(e2e_ms / args.steps / 1e3, 4), "unit": "s", "h2d_bytes_per_step": wl.h2d_bytes(),
@@ -557,6 +669,7 @@ def run_ours(args):
                                 if counted else "counted from the host loops (no activity trace available)"),
         "clocks": clocks,
         "checksum": checksum,                          # sum over linears of mean |quantized weight| (rank 0's copy)
+        "parity_vs_n1": parity,
     }
     if rank == 0 and world == 1 and not args.no_cpu:
         torch.set_num_threads(os.cpu_count() or 1)
@@ -578,6 +691,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", dest="no_cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-parity", dest="no_parity", action="store_true",
+                    help="N > 1: skip the comparison with a one-rank run of the same data")
+    ap.add_argument("--schedule", default="sequential", choices=["sequential", "all_at_once"])
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -46,6 +46,9 @@ SIGNATURES = {
                                         _vp, _vp]),
     "rq_hessian_noalloc_scratch_bytes": (_sz, []),
     "rq_hessian_accum_noalloc": (_i, [_vp, _i, _i64, _vp, _vp, _vp, _i64, _i, _i, _f, _f, _vp, _vp]),
+    "rq_hessian_packed_elems": (_i64, [_i]),
+    "rq_hessian_pack_upper": (_i, [_vp, _i, _i, _vp, _i64, _vp]),
+    "rq_hessian_unpack_upper": (_i, [_vp, _i64, _i, _i, _vp, _vp]),
     "rq_hessian_finalize": (_i, [_vp, _vp, _i, _i, _f, _f, _f, _i, _vp, _vp]),
     "rq_fwht": (_i, [_vp, _vp, _i, _i64, _i, _i, _vp, _f, _vp]),
     "rq_fwht_act_quant": (_i, [_vp, _vp, _i, _i64, _i, _i, _vp, _f, _f, _i, _i, _vp, _vp, _vp]),

@@ -628,6 +628,35 @@ __global__ void __launch_bounds__(256) finalize_kernel(float* __restrict__ H, fl
 }
 
 // ------------------------------------------------------------------------------------------
+// packed upper storage for the cross-rank exchange.  Only entries on or above the diagonal of H[g] carry
+// information before finalize; row r keeps its columns from the start of its 128-row block, c0 = (r / 128) * 128,
+// to C - 1, rows back to back:  offset(r) = 128 * b * C - 128 * 128 * b * (b - 1) / 2 + (r - 128 * b) * (C - 128 * b),
+// b = r / 128.  Row starts stay 16-byte aligned when C is a multiple of 4.
+// ------------------------------------------------------------------------------------------
+__host__ __device__ inline long long packed_row_offset(int r, int C) {
+    const long long b = r / 128;
+    return 128ll * b * C - 8192ll * b * (b - 1) + (r - 128 * b) * (C - 128 * b);
+}
+
+// grid (C, G), 256 threads: one row of one group per block.  to_packed != 0: H -> packed, else packed -> H.
+__global__ void __launch_bounds__(256) upper_copy_kernel(float* __restrict__ H, float* __restrict__ packed, int C,
+                                                         long long group_stride, int to_packed) {
+    const int r = blockIdx.x, g = blockIdx.y;
+    const int c0 = (r / 128) * 128;
+    const int n = C - c0;
+    float* hrow = H + ((long long)g * C + r) * C + c0;
+    float* prow = packed + (long long)g * group_stride + packed_row_offset(r, C);
+    float* dst = to_packed ? prow : hrow;
+    const float* src = to_packed ? hrow : prow;
+    if ((C & 3) == 0) {
+        for (int i = threadIdx.x; i < n / 4; i += 256)
+            reinterpret_cast<float4*>(dst)[i] = reinterpret_cast<const float4*>(src)[i];
+    } else {
+        for (int i = threadIdx.x; i < n; i += 256) dst[i] = src[i];
+    }
+}
+
+// ------------------------------------------------------------------------------------------
 // host side
 // ------------------------------------------------------------------------------------------
 static int encode_map(CUtensorMap* map, void* base, int64_t Kc, int C, int planes, int box_k, int box_rows, int bk) {
@@ -838,5 +867,29 @@ extern "C" int rq_hessian_finalize(float* H, float* act_sq, int C, int G, float 
     dim3 grid((unsigned)(T * (T + 1) / 2), (unsigned)G);
     rq::hess::finalize_kernel<<<grid, 256, 0, as_stream(stream)>>>(H, act_sq, C, div_tokens, div_scale, div_seq,
                                                                   sanitize, counts);
+    return check_launch();
+}
+
+extern "C" int64_t rq_hessian_packed_elems(int C) {
+    return C <= 0 ? 0 : (int64_t)rq::hess::packed_row_offset(C, C);
+}
+
+extern "C" int rq_hessian_pack_upper(const float* H, int C, int G, float* packed, int64_t group_stride, void* stream) {
+    if (!H || !packed || C <= 0 || G <= 0 || group_stride < rq_hessian_packed_elems(C)) return RQ_ERR_INVALID;
+    if ((C & 3) == 0 && ((group_stride & 3) != 0 || (reinterpret_cast<uintptr_t>(packed) & 15) != 0 ||
+                         (reinterpret_cast<uintptr_t>(H) & 15) != 0))
+        return RQ_ERR_INVALID;
+    rq::hess::upper_copy_kernel<<<dim3((unsigned)C, (unsigned)G), 256, 0, as_stream(stream)>>>(
+        const_cast<float*>(H), packed, C, (long long)group_stride, 1);
+    return check_launch();
+}
+
+extern "C" int rq_hessian_unpack_upper(const float* packed, int64_t group_stride, int C, int G, float* H, void* stream) {
+    if (!H || !packed || C <= 0 || G <= 0 || group_stride < rq_hessian_packed_elems(C)) return RQ_ERR_INVALID;
+    if ((C & 3) == 0 && ((group_stride & 3) != 0 || (reinterpret_cast<uintptr_t>(packed) & 15) != 0 ||
+                         (reinterpret_cast<uintptr_t>(H) & 15) != 0))
+        return RQ_ERR_INVALID;
+    rq::hess::upper_copy_kernel<<<dim3((unsigned)C, (unsigned)G), 256, 0, as_stream(stream)>>>(
+        H, const_cast<float*>(packed), C, (long long)group_stride, 0);
     return check_launch();
 }

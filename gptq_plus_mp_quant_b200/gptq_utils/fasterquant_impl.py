@@ -625,6 +625,48 @@ def _quantize_owned_groups(obj, W32, H3, perm, grads, alpha_eff, plus, percdamp,
     obj._last_fasterquant = last
 
 
+def _quantize_row_shard(obj, W32, H3, perm, grads, alpha_eff, plus, percdamp, groupsize, static_groups, blocksize,
+                        export_to_et, rec, inner_mode, atomic):
+    """Row-parallel mode: this rank's rows ``[r*R/W, (r+1)*R/W)`` only.  They lie in the saliency groups whose summed
+    Hessians finalize_hessian left on this rank: whole groups when the world size divides the group count, one
+    of ``pieces`` equal row slices of a single group otherwise (the ranks that share a group factorise the same
+    Hessian, bit for bit, and split its rows, which are independent given the inverse factor).  The other rows
+    of layer.weight keep their values until gather_rows_()."""
+    from ..utils import dist_utils
+    layer = obj.layer
+    G = obj.num_groups
+    first, count, piece, pieces = dist_utils.row_parallel_layout(G)
+    rps = obj.rows // G
+    if rps % pieces != 0:
+        raise ValueError(f"row-parallel quantization: {rps} rows per group do not split over {pieces} ranks")
+    if pieces == 1:
+        rows = slice(first * rps, (first + count) * rps)
+    else:
+        sub = rps // pieces
+        rows = slice(first * rps + piece * sub, first * rps + (piece + 1) * sub)
+    with _sec(rec, "fasterquant.quantizer_build_groups"):
+        mode_pack = _scale_setup(obj.quantizer, W32, groupsize, static_groups, blocksize, perm, None, rows=rows)
+    with _sec(rec, "fasterquant.subgroup.compute_hinv"):
+        Hinv, damp, identity = hinv_with_fallback(H3[first:first + count], perm, percdamp, identity_fallback=True,
+                                                  log_context=f" groups {first}..{first + count - 1}")
+    part = _RowSlice(layer.weight.data[rows])
+    _quantize_linear(part, W32[rows], H3[first:first + count], perm, grads[rows] if plus else None, obj.quantizer,
+                     count, alpha_eff, obj.reference_loss, plus, Hinv, mode_pack, export_to_et, permute_export=True,
+                     rec=rec, inner_mode=inner_mode, atomic=atomic)
+    out = layer.weight.data
+    if not out.is_contiguous():
+        out = out.contiguous()
+    out[rows] = part.weight.data
+    layer.weight.data = out
+    if export_to_et:
+        codes, scales = torch.zeros_like(W32), torch.zeros_like(W32)
+        codes[rows] = part.buffers["int_weight"]
+        scales[rows] = part.buffers["scale"]
+        layer.register_buffer("int_weight", codes.reshape(layer.weight.shape))
+        layer.register_buffer("scale", scales)
+    obj._last_fasterquant = {"Hinv": None, "perm": perm, "damp_percent": damp, "identity_fallback": identity}
+
+
 # ----------------------------------------------------------------------------------------------
 # GuidedQuant (gptq_utils/gptq_guided_utils.py:86-259): grouped Hessians, no first-order terms
 # ----------------------------------------------------------------------------------------------
@@ -812,6 +854,13 @@ def plus_fasterquant(obj, blocksize, percdamp, groupsize, actorder, static_group
     if gd_mode:
         gd_pack = (gd, (gradient_refresh_fn, block_observer, bool(enable_gradient_update),
                         bool(refresh_full_metrics)), groupsize, static_groups)
+    if getattr(obj, "row_parallel", False) and obj._owned_groups is not None:
+        if refresh is not None or gd_pack is not None:
+            raise NotImplementedError(f"{g_update_mode} needs every row on one rank (the callback sees the whole "
+                                      "weight); use hessian_owner instead of row_parallel")
+        _quantize_row_shard(obj, W32, H3, perm, grads, alpha_eff, plus, percdamp, groupsize, static_groups,
+                            blocksize, export_to_et, rec, _INNER_MODES.get(g_update_mode, 0), bool(block_atomic_quant))
+        return
     if getattr(obj, "group_owners", None) is not None:
         if refresh is not None or gd_pack is not None:
             raise NotImplementedError(f"{g_update_mode} needs every row group on one rank (the callback sees the "

@@ -90,6 +90,13 @@ class GPTQPlus:
         # group_owners[g] only and fasterquant quantizes just the rows of the groups this rank owns; the
         # other rows of layer.weight keep their values until the caller gathers them from their owners.
         self.group_owners = None
+        # Row-parallel mode (new, default off): with W ranks, rank r quantizes rows [r*R/W, (r+1)*R/W) of this
+        # linear.  finalize_hessian then delivers to every rank the summed Hessian of the saliency group(s) that
+        # cover its rows (only the upper triangles cross the wire: one reduce-scatter, plus an all-gather among the
+        # ranks that share a group), fasterquant quantizes the rank's rows only, and gather_rows_() completes
+        # layer.weight on every rank.  W must divide num_groups or be a multiple of it.
+        self.row_parallel = False
+        self._owned_groups = None       # (first, count) of the Hessian groups this rank holds after finalize
         self._exchange = None           # (stream, totals) while begin_exchange's collectives are in flight
         assert self.rows % self.num_groups == 0, (
             f"Number of rows ({self.rows}) must be divisible by num_groups ({self.num_groups})")
@@ -136,7 +143,21 @@ class GPTQPlus:
             self.token_count += n_tokens
 
     def _reduce_sums_(self):
-        """The cross-rank sums of the accumulators, to the owners that hessian_owner / group_owners name."""
+        """The cross-rank sums of the accumulators, to the owners that hessian_owner / group_owners / row_parallel
+        name.  Returns the summed (sample count, token count) as a device tensor when it travelled with
+        act_square, else None."""
+        if self.row_parallel and dist_utils.get_world_size() > 1:
+            _, _, _, pieces = dist_utils.row_parallel_layout(self.num_groups)
+            packed = ops.pack_upper(self._H, pieces)
+            first, count = dist_utils.exchange_group_sums_(packed)
+            ops.unpack_upper(packed[first:first + count], self._H[first:first + count])
+            self._owned_groups = (first, count)
+            # the two counters ride along with act_square (both are integers below 2^24: exact in fp32)
+            small = torch.cat([self.act_square, torch.tensor([float(self.index), float(self.token_count)],
+                                                             device=self.act_square.device)])
+            dist_utils.allreduce_sum_(small)
+            self.act_square.copy_(small[:-2])
+            return small[-2:].double()
         if self.group_owners is not None:
             assert len(self.group_owners) == self.num_groups
             dist_utils.reduce_groups_to_owners_(self._H, self.group_owners)
@@ -145,6 +166,7 @@ class GPTQPlus:
         else:
             dist_utils.reduce_sum_(self._H, self.hessian_owner)
         dist_utils.allreduce_sum_(self.act_square)
+        return None
 
     @torch.no_grad()
     def begin_exchange(self, stream=None):
@@ -164,10 +186,11 @@ class GPTQPlus:
             if side is not cur:
                 side.wait_stream(cur)
         with (torch.cuda.stream(side) if on_gpu else _NULL_CONTEXT):
-            self._reduce_sums_()
-            totals = torch.tensor([float(self.index), float(self.token_count)], dtype=torch.float64,
-                                  device=self._H.device)
-            dist_utils.allreduce_sum_(totals)
+            totals = self._reduce_sums_()
+            if totals is None:
+                totals = torch.tensor([float(self.index), float(self.token_count)], dtype=torch.float64,
+                                      device=self._H.device)
+                dist_utils.allreduce_sum_(totals)
         self._exchange = (side, totals)
 
     @torch.no_grad()
@@ -184,13 +207,20 @@ class GPTQPlus:
             total_samples, total_tokens = (float(v) for v in totals.tolist())
         else:
             ops.hessian_join(self.dev)
-            self._reduce_sums_()
-            total_samples = dist_utils.allreduce_sum_scalar(self.index)
-            total_tokens = dist_utils.allreduce_sum_scalar(self.token_count)
+            totals = self._reduce_sums_()
+            if totals is not None:
+                total_samples, total_tokens = (float(v) for v in totals.tolist())
+            else:
+                total_samples = dist_utils.allreduce_sum_scalar(self.index)
+                total_tokens = dist_utils.allreduce_sum_scalar(self.token_count)
         if total_samples <= 0 or total_tokens <= 0:
             raise RuntimeError("finalize_hessian called before any add_batch ran.")
         seq_len = total_tokens / total_samples
-        counts = ops.hessian_finalize(self._H, self.act_square, div_tokens=total_samples * seq_len,
+        held = self._H
+        if self._owned_groups is not None:             # row-parallel: only the groups this rank will factorise
+            first, count = self._owned_groups
+            held = self._H[first:first + count]
+        counts = ops.hessian_finalize(held, self.act_square, div_tokens=total_samples * seq_len,
                                       div_scale=self.hessian_saliency_scale, div_seq=seq_len, sanitize=True)
         self._H_upper_only = False
         ops.check_status(self.dev)
@@ -229,6 +259,21 @@ class GPTQPlus:
         if torch.any(torch.isnan(self.layer.weight.data)):
             logging.warning("NaN in weights")
             raise ValueError("NaN in weights")
+
+    @torch.no_grad()
+    def gather_rows_(self):
+        """Row-parallel mode: after fasterquant every rank holds its own rows of the quantized weight; this
+        all-gathers them (and the export buffers, if present) so that layer.weight is complete on every rank."""
+        if not self.row_parallel or dist_utils.get_world_size() <= 1:
+            return
+        w = self.layer.weight.data
+        if not w.is_contiguous():
+            w = self.layer.weight.data = w.contiguous()
+        dist_utils.allgather_rows_(w)
+        for name in ("int_weight", "scale"):
+            buf = getattr(self.layer, name, None)
+            if isinstance(buf, torch.Tensor) and buf.shape[0] == self.rows:
+                dist_utils.allgather_rows_(buf)
 
     def free(self):
         # Drops the Hessian; unlike the reference this does not return cached blocks to the driver

@@ -159,6 +159,43 @@ def hessian_finalize(H: torch.Tensor, act_sq, div_tokens: float = 1.0, div_scale
     return counts
 
 
+def packed_upper_elems(columns: int) -> int:
+    """Floats per group of the packed upper storage (see pack_upper)."""
+    return int(_lib.lib.rq_hessian_packed_elems(int(columns)))
+
+
+def pack_upper(H: torch.Tensor, pieces: int = 1, key: str = "exchange") -> torch.Tensor:
+    """The entries on or above the diagonal of every ``H[g]`` (all that an un-finalised sum holds) as ``[G, L]``
+    with L = packed_upper_elems(C) rounded up to a multiple of ``4 * pieces``; the buffer comes from the
+    workspace cache of the current stream, the padding is zeroed."""
+    _lib.require_cuda(H)
+    assert H.is_contiguous() and H.dtype == torch.float32 and H.dim() == 3
+    G, Cc = H.shape[0], H.shape[-1]
+    n = packed_upper_elems(Cc)
+    unit = 4 * max(1, int(pieces))
+    L = (n + unit - 1) // unit * unit
+    ws = _workspace(H.device, G * L * 4 + 1024, key=key)
+    off = (-ws.data_ptr()) % 1024
+    packed = ws[off:off + G * L * 4].view(torch.float32).view(G, L)
+    if L > n:
+        packed[:, n:].zero_()
+    with torch.cuda.device(H.device):
+        rc = _lib.lib.rq_hessian_pack_upper(_lib.ptr(H), Cc, G, _lib.ptr(packed), L, _lib.stream_of(H))
+    _lib.check("rq_hessian_pack_upper", rc)
+    return packed
+
+
+def unpack_upper(packed: torch.Tensor, H: torch.Tensor) -> None:
+    """Inverse of pack_upper for the groups ``packed`` [g, L] / ``H`` [g, C, C] hold."""
+    _lib.require_cuda(packed, H)
+    assert H.is_contiguous() and H.dtype == torch.float32 and packed.dtype == torch.float32
+    assert packed.stride(-1) == 1 and packed.shape[0] == H.shape[0]
+    with torch.cuda.device(H.device):
+        rc = _lib.lib.rq_hessian_unpack_upper(_lib.ptr(packed), packed.stride(0), H.shape[-1], H.shape[0], _lib.ptr(H),
+                                              _lib.stream_of(H))
+    _lib.check("rq_hessian_unpack_upper", rc)
+
+
 def clamp_to_quantile_(x: torch.Tensor, q: float) -> torch.Tensor:
     """In place ``x = clamp(x, max=torch.quantile(x.flatten(), q))`` for a contiguous fp32 tensor of any size (no
     sort, no 16M-element limit); returns the cap as a 0-dim tensor."""

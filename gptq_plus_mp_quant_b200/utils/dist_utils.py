@@ -9,8 +9,25 @@ import torch
 import torch.distributed as dist
 
 
+_local_only = 0
+
+
 def is_dist_available_and_initialized() -> bool:
-    return dist.is_available() and dist.is_initialized()
+    return dist.is_available() and dist.is_initialized() and _local_only == 0
+
+
+class local_only:
+    """Context in which the helpers of this module behave as in a single process (world size 1, rank 0) although a
+    process group exists: for a rank that quantizes something on its own, e.g. a one-rank run of the same data to
+    compare a data-parallel result with."""
+
+    def __enter__(self):
+        global _local_only
+        _local_only += 1
+
+    def __exit__(self, *exc):
+        global _local_only
+        _local_only -= 1
 
 
 def get_world_size() -> int:
@@ -110,6 +127,80 @@ def reduce_groups_to_owners_(H: torch.Tensor, owners) -> None:
         return
     for g, owner in enumerate(owners):
         dist.reduce(H[g], dst=owner, op=dist.ReduceOp.SUM)
+
+
+def row_parallel_layout(num_groups: int, world: Optional[int] = None, rank: Optional[int] = None):
+    """Row-parallel fasterquant: rank r quantizes rows ``[r*R/W, (r+1)*R/W)`` of a linear whose rows fall into
+    ``num_groups`` saliency groups, each with a Hessian of its own.  Returns ``(first group, groups, piece, pieces)``:
+    the Hessian groups that cover this rank's rows, and which of the ``pieces`` equal row slices of that group the
+    rank takes (``pieces`` = ranks per group, 1 when a rank holds whole groups).  ``world`` must divide
+    ``num_groups`` or be a multiple of it."""
+    world = get_world_size() if world is None else world
+    rank = get_rank() if rank is None else rank
+    if world <= 1:
+        return 0, num_groups, 0, 1
+    if num_groups % world == 0:
+        n = num_groups // world
+        return rank * n, n, 0, 1
+    if world % num_groups == 0:
+        k = world // num_groups
+        return rank // k, 1, rank % k, k
+    raise ValueError(f"row-parallel quantization needs world_size ({world}) to divide num_groups ({num_groups}) "
+                     "or to be a multiple of it")
+
+
+_peer_groups = {}
+
+
+def _group_peers(num_groups: int, world: int):
+    """Process groups of the ranks that share one Hessian group (``world`` a multiple of ``num_groups``); created
+    once, by every rank, in the same order."""
+    key = (num_groups, world)
+    if key not in _peer_groups:
+        k = world // num_groups
+        _peer_groups[key] = [dist.new_group(list(range(g * k, (g + 1) * k))) for g in range(num_groups)]
+    return _peer_groups[key]
+
+
+def exchange_group_sums_(sums: torch.Tensor):
+    """``sums`` [G, L]: this rank's partial sums per saliency group (L a multiple of the ranks per group).
+    Afterwards rows ``first .. first + groups`` (see row_parallel_layout) hold the sums over all ranks; the other
+    rows are unspecified.  One reduce-scatter over all ranks, then, when several ranks share a group, one
+    all-gather among those ranks.  Returns ``(first, groups)``."""
+    world, rank = get_world_size(), get_rank()
+    G = sums.shape[0]
+    first, groups, _, k = row_parallel_layout(G, world, rank)
+    if world <= 1:
+        return first, groups
+    assert sums.is_contiguous() and sums.shape[1] % k == 0
+    flat = sums.view(-1)
+    mine = _reduce_scatter_inplace_(flat, world, rank)
+    if k > 1:
+        peers = _group_peers(G, world)[first]
+        if dist.get_backend() == "nccl":
+            dist.all_gather_into_tensor(sums[first], mine, group=peers)          # NCCL's in-place layout
+        else:
+            parts = [torch.empty_like(mine) for _ in range(k)]
+            dist.all_gather(parts, mine.clone(), group=peers)
+            sums[first].copy_(torch.cat(parts))
+    return first, groups
+
+
+def allgather_rows_(tensor: torch.Tensor) -> torch.Tensor:
+    """``tensor`` [R, ...] with R divisible by the world size: rank r's rows ``[r*R/W, (r+1)*R/W)`` are copied to
+    every rank, in place."""
+    world, rank = get_world_size(), get_rank()
+    if world <= 1:
+        return tensor
+    assert tensor.is_contiguous() and tensor.shape[0] % world == 0
+    n = tensor.shape[0] // world
+    if dist.get_backend() == "nccl":
+        dist.all_gather_into_tensor(tensor, tensor[rank * n:(rank + 1) * n])
+    else:
+        parts = [torch.empty_like(tensor[:n]) for _ in range(world)]
+        dist.all_gather(parts, tensor[rank * n:(rank + 1) * n].clone())
+        tensor.copy_(torch.cat(parts))
+    return tensor
 
 
 def allreduce_sum_scalar(scalar) -> float:

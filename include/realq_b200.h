@@ -113,6 +113,19 @@ size_t rq_hessian_noalloc_scratch_bytes(void);
 int rq_hessian_accum_noalloc(const void* x, int x_dtype, int64_t ldx, const float* sal, float* H, float* act_sq,
                              int64_t N, int C, int G, float alpha, float beta, int* status, void* stream);
 
+/* Packed upper storage of the un-finalised sums, for the cross-rank exchange that stands in for the all-reduce of
+ * GPTQPlus.finalize_hessian (gptq_utils/gptq_plus_utils.py:875-878: dist_utils.allreduce_sum_(self.H)).  Before
+ * finalize only the entries on or above the diagonal carry information (the finalize step mirrors them), so only
+ * those cross the wire: row r of a group keeps its columns from (r / 128) * 128 to C - 1, rows back to back,
+ * rq_hessian_packed_elems(C) = C (C + 128) / 2 floats per group when 128 divides C, a little over half of C * C.
+ * packed: [G][group_stride] fp32 with group_stride >= rq_hessian_packed_elems(C) (a multiple of 4 and 16-byte
+ * aligned buffers when C is a multiple of 4).  rq_hessian_unpack_upper writes the same entries back into H[g]
+ * (the strictly lower part of each 128-row block's first columns is left as it is; rq_hessian_finalize
+ * overwrites it). */
+int64_t rq_hessian_packed_elems(int C);
+int rq_hessian_pack_upper(const float* H, int C, int G, float* packed, int64_t group_stride, void* stream);
+int rq_hessian_unpack_upper(const float* packed, int64_t group_stride, int C, int G, float* H, void* stream);
+
 /* Replaces GPTQPlus.finalize_hessian after its all-reduce (gptq_utils/gptq_plus_utils.py:881-907):
  *   H /= div_tokens; H /= div_scale (skipped when 1); act_sq /= div_seq;
  *   H = (H + H^T)/2  — realised by mirroring the computed upper triangle —; non-finite -> 0.

@@ -120,12 +120,56 @@ def test_world2_sharded_hessian_and_helpers():
     assert dict(results) == {0: "ok", 1: "ok"}
 
 
-def test_owner_assignment_balances_cost():
+def _row_parallel_worker(rank, world, port, results):
     sys.path.insert(0, ROOT)
-    import bench
-    costs = {"a": 10.0, "b": 9.0, "c": 2.0, "d": 1.0, "e": 1.0}
-    own = bench.assign_owners(costs, 2)
-    load = [sum(c for n, c in costs.items() if own[n] == r) for r in range(2)]
-    assert set(own.values()) == {0, 1}
-    assert abs(load[0] - load[1]) <= 2.0
-    assert bench.assign_owners(costs, 1) == {k: 0 for k in costs}
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from gptq_plus_mp_quant_b200.utils import dist_utils as du
+        torch.set_num_threads(1)
+        for G in (1, 2, 4, 8):
+            first, count, piece, pieces = du.row_parallel_layout(G)
+            # the groups a rank holds cover exactly its row shard [r*R/W, (r+1)*R/W)
+            R = 64
+            rps = R // G
+            lo = first * rps + (piece * (rps // pieces) if pieces > 1 else 0)
+            hi = lo + (rps // pieces if pieces > 1 else count * rps)
+            assert (lo, hi) == (rank * R // world, (rank + 1) * R // world), (G, lo, hi)
+            L = 24
+            gen = torch.Generator().manual_seed(5 + G)
+            parts = [torch.randn(G, L, generator=gen) for _ in range(world)]
+            sums = parts[rank].clone()
+            f2, c2 = du.exchange_group_sums_(sums)
+            assert (f2, c2) == (first, count)
+            total = sum(parts)
+            assert torch.allclose(sums[first:first + count], total[first:first + count], rtol=0, atol=1e-5), G
+            # ranks that share a group hold the same bits of it
+            if pieces > 1:
+                same = [torch.empty_like(sums[first]) for _ in range(world)]
+                dist.all_gather(same, sums[first].clone())
+                k0 = (rank // pieces) * pieces
+                assert all(torch.equal(same[k0], same[k0 + j]) for j in range(pieces))
+        with pytest.raises(ValueError):
+            du.row_parallel_layout(3)
+        w = torch.zeros(8, 3)
+        n = 8 // world
+        w[rank * n:(rank + 1) * n] = float(rank + 1)
+        du.allgather_rows_(w)
+        assert torch.equal(w[:, 0], torch.arange(1, world + 1).repeat_interleave(n).float())
+        with du.local_only():
+            assert du.get_world_size() == 1 and du.get_rank() == 0
+            assert du.row_parallel_layout(4) == (0, 4, 0, 1)
+        assert du.get_world_size() == world
+        results[rank] = "ok"
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_row_parallel_exchange(world):
+    port = 31500 + (os.getpid() % 2000) + world
+    mgr = mp.Manager()
+    results = mgr.dict()
+    mp.spawn(_row_parallel_worker, args=(world, port, results), nprocs=world, join=True)
+    assert dict(results) == {r: "ok" for r in range(world)}

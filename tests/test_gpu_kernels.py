@@ -725,3 +725,27 @@ def test_weight_quantizer_grouped_mse_vs_reference(golden, case):
         e1 = (ste - W.float()).abs().pow(2.4).reshape(rows, -1, gs).sum(-1)
         e2 = (ref - W.float()).abs().pow(2.4).reshape(rows, -1, gs).sum(-1)
         assert torch.allclose(e1, e2, rtol=1e-5, atol=0)
+
+
+@pytest.mark.parametrize("C,G,pieces", [(256, 2, 1), (384, 4, 2), (200, 1, 4), (130, 3, 1)])
+def test_packed_upper_round_trip(C, G, pieces):
+    """pack_upper keeps exactly the entries from each row's 128-block start to the row's end; unpack_upper puts
+    them back; everything on or above the diagonal survives the trip bit for bit."""
+    from gptq_plus_mp_quant_b200 import ops
+    g = torch.Generator(device="cpu").manual_seed(C + G)
+    H = torch.randn(G, C, C, generator=g).to(DEV)
+    packed = ops.pack_upper(H, pieces)
+    n = ops.packed_upper_elems(C)
+    assert packed.shape[0] == G and packed.shape[1] >= n and packed.shape[1] % (4 * pieces) == 0
+    assert float(packed[:, n:].abs().sum()) == 0.0
+    # reference layout built with torch indexing
+    ref = torch.cat([H[:, r, (r // 128) * 128:] for r in range(C)], dim=1)
+    assert ref.shape[1] == n and torch.equal(packed[:, :n], ref)
+    out = torch.full_like(H, float("nan"))
+    ops.unpack_upper(packed.clone(), out)
+    iu = torch.triu(torch.ones(C, C, dtype=torch.bool, device=DEV))
+    assert torch.equal(out[:, iu], H[:, iu])
+    kept = torch.zeros(C, C, dtype=torch.bool, device=DEV)
+    for r in range(C):
+        kept[r, (r // 128) * 128:] = True
+    assert bool(torch.isnan(out[:, ~kept]).all())          # nothing else is written
