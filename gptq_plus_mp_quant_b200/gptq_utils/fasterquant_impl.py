@@ -25,6 +25,9 @@ def _sec(rec, name):
 
 BS = 128            # column block of the kernels
 _DAMP_STEP = 0.0015
+# the factorisation of all groups of a linear shares its launches when their scratch fits this many bytes;
+# beyond it (28672-wide inputs with four groups need 79 GB at once) the groups are factorised in smaller batches
+CHOL_WORKSPACE_CAP = int(float(os.environ.get("REALQ_CHOL_WORKSPACE_GB", "32")) * (1 << 30))
 # GEMM-shaped parts (first-order terms, lazy update) on the tensor cores (split-bf16, four products) or,
 # when False, as fp32 FMA tiles on the CUDA cores
 USE_TENSOR_CORES = os.environ.get("REALQ_FQ_TENSOR", "1") != "0"
@@ -77,7 +80,12 @@ def hinv_with_fallback(H3: torch.Tensor, perm, percdamp: float, identity_fallbac
         for g in todo:
             growth[g] *= 1.0 + p[g]
         if first and len(todo) == G:
-            _chol_once(H3, perm, [growth[g] - 1.0 for g in range(G)], Hinv, info)
+            batch = G
+            while batch > 1 and _lib.lib.rq_chol_workspace_bytes(Cc, batch) > CHOL_WORKSPACE_CAP:
+                batch = (batch + 1) // 2
+            for g0 in range(0, G, batch):
+                g1 = min(G, g0 + batch)
+                _chol_once(H3[g0:g1], perm, [growth[g] - 1.0 for g in range(g0, g1)], Hinv[g0:g1], info[g0:g1])
             flags = info.tolist()
         else:
             flags = [0] * G

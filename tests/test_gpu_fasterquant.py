@@ -89,6 +89,45 @@ def test_hinv_full_size_property():
     assert float((back - probe).norm() / probe.norm()) < 1e-3
 
 
+def test_hinv_c28672_property():
+    """The widest input of the benchmark configurations (Llama-70B down_proj, 28672 channels, one saliency group's
+    worth of work): the factor is finite, strictly upper, needs no retry, and U^T U (H + lambda I) v = v in fp64."""
+    from gptq_plus_mp_quant_b200.gptq_utils import fasterquant_impl as fi
+    C, n = 28672, 57344
+    g = torch.Generator(device=DEV).manual_seed(9)
+    ch = torch.exp(torch.randn(C, generator=g, device=DEV))
+    H = torch.zeros(C, C, device=DEV)
+    old = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        for _ in range(n // 4096):
+            x = torch.randn(4096, C, generator=g, device=DEV) * ch
+            H.addmm_(x.t(), x)
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = old
+    H /= n
+    H3 = H.reshape(1, C, C)
+    Hinv, damp, ident = fi.hinv_with_fallback(H3, None, 0.01, True)
+    assert damp[0] == 0.01 and not ident[0]
+    assert bool(torch.isfinite(Hinv).all())
+    lam = 0.01 * float(H.diagonal().double().mean())
+    probe = torch.randn(C, 4, dtype=torch.float64, device=DEV, generator=torch.Generator(device=DEV).manual_seed(1))
+    hv = torch.empty_like(probe)
+    for c0 in range(0, C, 4096):                            # H v in fp64 without an fp64 copy of H
+        hv[c0:c0 + 4096] = H[c0:c0 + 4096].double() @ probe
+    hv += lam * probe
+    uv = torch.empty_like(probe)
+    for c0 in range(0, C, 4096):
+        uv[c0:c0 + 4096] = Hinv[0, c0:c0 + 4096, :C].double() @ hv
+    back = torch.zeros_like(probe)
+    for c0 in range(0, C, 4096):
+        back += Hinv[0, c0:c0 + 4096, :C].double().t() @ uv[c0:c0 + 4096]
+    err = float((back - probe).norm() / probe.norm())
+    print(f"C=28672: |U^T U (H + lambda I) v - v| / |v| = {err:.3e}")
+    assert err < 1e-3
+    assert float(torch.tril(Hinv[0, :4096, :4096], -1).abs().max()) == 0.0
+
+
 def test_nonspd_retries_like_reference(golden):
     from gptq_plus_mp_quant_b200.gptq_utils import fasterquant_impl as fi
     g = golden("faults.npz")
