@@ -140,7 +140,7 @@ struct BlockArgs {
     const float* Z;          // [R, C] (PLUS)
     const float* Hinv;       // [G, Cp, Cp] upper factor
     float* Q;                // [R, C] dequantized result (permuted order)
-    int8_t* codes;           // [R, C] integer codes (permuted order)
+    int16_t* codes;           // [R, C] integer codes (permuted order)
     float* Eeff;             // [R, BS]: Err (- D*Z1 when PLUS), A operand of the lazy update
     __nv_bfloat16* Ehi;      // optional: the same operand split into bf16 planes [R][BS] for the tensor-core update
     __nv_bfloat16* Elo;
@@ -326,7 +326,7 @@ __global__ void __launch_bounds__(kBlockThreads) block_kernel(const BlockArgs p)
         const int col = lane + 32 * k;
         if (col < p.count) {
             p.Q[base + col] = qv[k];
-            p.codes[base + col] = (int8_t)cv[k];
+            p.codes[base + col] = (int16_t)cv[k];
             float e = ev[k];
             if (PLUS) e = e - (float)(p.count - 1 - col) * z[k];
             p.Eeff[(int64_t)r * BS + col] = e;
@@ -406,7 +406,7 @@ __global__ void __launch_bounds__(gemm::kThreads, 2) lazy_kernel(float* __restri
 // epilogue: un-permute and cast.  out[r][perm[j]] = Q[r][j]  (also codes / scale when exported)
 // ------------------------------------------------------------------------------------------
 template <typename T>
-__global__ void __launch_bounds__(256) unpermute_kernel(const float* __restrict__ Q, const int8_t* __restrict__ codes,
+__global__ void __launch_bounds__(256) unpermute_kernel(const float* __restrict__ Q, const int16_t* __restrict__ codes,
                                                         const int64_t* __restrict__ perm, int R, int C,
                                                         T* __restrict__ out, float* __restrict__ out_codes,
                                                         float* __restrict__ out_scale,
@@ -454,7 +454,7 @@ extern "C" int rq_gptqplus_terms(const float* Gp, const float* Hinv, int R, int 
     return check_launch();
 }
 
-static int fq_block_launch(float* Wp, float* GH, const float* Z, const float* Hinv, float* Q, int8_t* codes,
+static int fq_block_launch(float* Wp, float* GH, const float* Z, const float* Hinv, float* Q, int16_t* codes,
                            float* Eeff, __nv_bfloat16* Ehi, __nv_bfloat16* Elo, const float* scale_row,
                            const float* scale_tab, const int* colgrp, float* scale_blk, int R, int C, int G, int i1,
                            int count, int mode, int dyn_gs, int sym, int maxq, int plus, const float* anchor,
@@ -468,7 +468,7 @@ static int fq_block_launch(float* Wp, float* GH, const float* Z, const float* Hi
     if (mode == 0 && !scale_row) return RQ_ERR_INVALID;
     if (mode == 1 && (!scale_tab || !colgrp)) return RQ_ERR_INVALID;
     if (mode == 2 && (!scale_blk || dyn_gs <= 0 || BS % dyn_gs != 0 || i1 % dyn_gs != 0)) return RQ_ERR_INVALID;
-    if (mode < 0 || mode > 2 || maxq <= 0 || maxq > 127) return RQ_ERR_INVALID;
+    if (mode < 0 || mode > 2 || maxq <= 0 || maxq > 32767) return RQ_ERR_INVALID;
     if (inner_mode < 0 || inner_mode > 2 || (inner_mode != 0 && (!plus || !anchor || !beta))) return RQ_ERR_INVALID;
     cudaStream_t st = as_stream(stream);
     BlockArgs p;
@@ -497,7 +497,7 @@ static int fq_block_launch(float* Wp, float* GH, const float* Z, const float* Hi
     return check_launch();
 }
 
-extern "C" int rq_fq_block(float* Wp, float* GH, const float* Z, const float* Hinv, float* Q, int8_t* codes,
+extern "C" int rq_fq_block(float* Wp, float* GH, const float* Z, const float* Hinv, float* Q, int16_t* codes,
                            float* Eeff, const float* scale_row, const float* scale_tab, const int* colgrp,
                            float* scale_blk, int R, int C, int G, int i1, int count, int mode, int dyn_gs, int sym,
                            int maxq, int plus, const float* anchor, const float* beta, int inner_mode, int atomic,
@@ -540,7 +540,7 @@ extern "C" int rq_fq_lazy_update(float* Wp, float* GH, const float* Z, const flo
     return check_launch();
 }
 
-extern "C" int rq_fq_finish(const float* Q, const int8_t* codes, const int64_t* perm, int R, int C, void* out,
+extern "C" int rq_fq_finish(const float* Q, const int16_t* codes, const int64_t* perm, int R, int C, void* out,
                             int out_dtype, float* out_codes, float* out_scale, const float* scale_row,
                             const float* scale_tab, const int* colgrp, int permute_export, void* stream) {
     using namespace rq::fq;
@@ -564,7 +564,7 @@ extern "C" int rq_fq_finish(const float* Q, const int8_t* codes, const int64_t* 
 }
 
 // Every block of a linear in one call (the callback-free modes need no host work between blocks).
-extern "C" int rq_fq_run(float* Wp, float* GH, const float* Z, const float* Hinv, float* Q, int8_t* codes,
+extern "C" int rq_fq_run(float* Wp, float* GH, const float* Z, const float* Hinv, float* Q, int16_t* codes,
                          float* Eeff, const float* scale_row, const float* scale_tab, const int* colgrp,
                          float* scale_blk, int R, int C, int G, int mode, int dyn_gs, int sym, int maxq, int plus,
                          const float* anchor, const float* beta, int inner_mode, int atomic, void* stream) {
@@ -685,7 +685,7 @@ extern "C" int rq_gptqplus_terms_tc(const float* Gp, const float* Hinv, int R, i
     return split_full_rows(Z, R, C, Cp, PA, st);                     // planes of Z = beta * T for the lazy updates
 }
 
-extern "C" int rq_fq_run_tc(float* Wp, float* GH, const float* Z, const float* Hinv, float* Q, int8_t* codes,
+extern "C" int rq_fq_run_tc(float* Wp, float* GH, const float* Z, const float* Hinv, float* Q, int16_t* codes,
                             float* Eeff, const float* scale_row, const float* scale_tab, const int* colgrp,
                             float* scale_blk, int R, int C, int G, int mode, int dyn_gs, int sym, int maxq, int plus,
                             const float* anchor, const float* beta, int inner_mode, int atomic, void* workspace,

@@ -208,7 +208,7 @@ def _quantize_linear(layer, W32, H3, perm, grads, quantizer, G, alpha_eff, ref_l
         # surrogate modes measure the drift of the weights from their values before the first block
         anchor = Wp.clone() if inner_mode else None
         Q = torch.empty(R, Cc, dtype=torch.float32, device=dev)
-        codes = torch.empty(R, Cc, dtype=torch.int8, device=dev)
+        codes = torch.empty(R, Cc, dtype=torch.int16, device=dev)
         Eeff = torch.empty(R, BS, dtype=torch.float32, device=dev)
         with _sec(rec, "fasterquant.block.total"):
             if gd_pack is not None:
@@ -570,8 +570,8 @@ def _check_common(quantizer, blocksize):
     if blocksize % BS != 0:
         raise NotImplementedError(f"blocksize must be a multiple of {BS} (the kernels' column block); got {blocksize}")
     maxq = int(quantizer.maxq)
-    if not (0 < maxq <= 127):
-        raise NotImplementedError(f"integer codes are stored as int8: maxq must be in 1..127, got {maxq}")
+    if not (0 < maxq <= 32767):
+        raise NotImplementedError(f"integer codes are stored as int16: maxq must be in 1..32767, got {maxq}")
 
 
 class _RowSlice:

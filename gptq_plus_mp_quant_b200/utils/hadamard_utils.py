@@ -72,28 +72,28 @@ TABLE_ORDERS = (12, 20, 28, 36, 44, 52, 60, 68, 76, 84, 92, 100, 108, 116, 124, 
 _PALEY2_ORDERS = {28: 13, 36: 17, 76: 37, 148: 73, 204: 101, 220: 109}
 
 
-@lru_cache(maxsize=None)
-def _external_table():
-    path = os.environ.get("REALQ_HAD_MAT", "")
-    if path and os.path.exists(path):
-        return torch.load(path)
-    return {}
+def _unpack(K: int) -> torch.Tensor:
+    import base64
+
+    import numpy as np
+
+    from ._had_tables import PACKED
+    bits = np.unpackbits(np.frombuffer(base64.b64decode(PACKED[K]), dtype=np.uint8))[:K * K]
+    return torch.from_numpy(bits.astype(np.float32) * 2.0 - 1.0).reshape(K, K)
 
 
 @lru_cache(maxsize=None)
 def hadamard_of_order(K: int) -> torch.Tensor:
-    """The K x K (+-1) matrix the reference stores for order K.  Orders with a Paley
-    construction are generated (and are identical to the stored ones); the others are read
-    from the file named by ``REALQ_HAD_MAT`` (a copy of the reference's ``had_mat.pt``)."""
+    """The K x K (+-1) matrix the reference stores for order K (utils/had_mat.pt).  Orders with a Paley
+    construction are generated (and are identical to the stored ones); the other thirteen come from the bit-packed
+    table in ``_had_tables.py``."""
     if K in _PALEY2_ORDERS:
         return _paley2(_PALEY2_ORDERS[K])
     if K in TABLE_ORDERS and _is_prime(K - 1) and (K - 1) % 4 == 3 and K not in (212, 228, 252):
         return _paley1(K - 1)
-    ext = _external_table()
-    if K in ext:
-        return ext[K].float()
-    raise ValueError(
-        f"no built-in Hadamard matrix of order {K}; point REALQ_HAD_MAT at a had_mat.pt that holds it")
+    if K in TABLE_ORDERS:
+        return _unpack(K)
+    raise ValueError(f"no Hadamard matrix of order {K}: the table holds {TABLE_ORDERS}")
 
 
 def get_hadK(n, transpose=False):
@@ -115,12 +115,20 @@ _HADK_DEV = {}
 
 
 def _hadK_on(device, hadK: torch.Tensor) -> torch.Tensor:
-    key = (str(device), hadK.data_ptr(), tuple(hadK.shape), tuple(hadK.stride()))
-    t = _HADK_DEV.get(key)
-    if t is None:
-        t = hadK.detach().to(device=device, dtype=torch.float32).contiguous()
-        _HADK_DEV[key] = t
-    return t
+    """Device copy of a K x K mixing matrix.  Only the matrices that hadamard_of_order hands out (kept alive by its
+    cache, never modified) are remembered, keyed by their order and orientation; a caller's own matrix is copied on
+    every call, so a freed or edited tensor can never be confused with a cached one."""
+    K = hadK.shape[0]
+    if K in TABLE_ORDERS:
+        base = hadamard_of_order(K)
+        for tag, cand in (("n", base), ("t", base.T)):
+            if hadK.data_ptr() == cand.data_ptr() and hadK.stride() == cand.stride() and hadK.shape == cand.shape:
+                key = (str(device), K, tag)
+                t = _HADK_DEV.get(key)
+                if t is None:
+                    t = _HADK_DEV[key] = cand.to(device=device, dtype=torch.float32).contiguous()
+                return t
+    return hadK.detach().to(device=device, dtype=torch.float32).contiguous()
 
 
 def fwht(x: torch.Tensor, hadK=None, K: int = 1, scale: float = 1.0, out: torch.Tensor | None = None):

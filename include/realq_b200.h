@@ -285,7 +285,7 @@ int rq_gptqplus_terms(const float* Gp, const float* Hinv, int R, int C, int G, f
  * (gptq_utils/gptq_plus_utils.py:1296-1372; gptq_utils/gptq_utils.py:120-151):
  *   q_int = clamp(round(w/scale), -(maxq+1), maxq); q = scale*q_int; err = (w - q - GHinv[:, i]) / Hinv[i,i];
  *   W[:, i:i2] -= err (x) Hinv[i, i:i2] + GHinv[:, i:i2];  GHinv[:, i:i2] -= Z[:, i] (x) Hinv[i, i:i2].
- * Q receives q, codes q_int (int8), Eeff [R, 128] the A operand of the lazy update:
+ * Q receives q, codes q_int (int16: maxq up to 32767, e.g. 255 for asymmetric 8-bit), Eeff [R, 128] the A operand of the lazy update:
  * Err (minus (count-1-i) * Z[:, i] when plus).  Scale source: mode 0 scale_row [R]; mode 1 static
  * groups scale_tab [ngroups, R] indexed by colgrp [C]; mode 2 dynamic groups of width dyn_gs (divides
  * 128) ranged from the block-start values (sym selects the range rule), written to scale_blk
@@ -304,14 +304,14 @@ int rq_gptqplus_terms(const float* Gp, const float* Hinv, int R, int C, int G, f
  * (:1238-1288; rq_fq_run never applies it to the last block, :1174).
  * second_order_scale (rq_fq_block, rq_fq_lazy_update): factor on the weight update of W, 1 everywhere except in
  * g_update_mode="block_gd" (:1344-1349, 1546-1550), whose optimizer steps between the blocks stay on the host. */
-int rq_fq_block(float* Wp, float* GH, const float* Z, const float* Hinv, float* Q, int8_t* codes, float* Eeff,
+int rq_fq_block(float* Wp, float* GH, const float* Z, const float* Hinv, float* Q, int16_t* codes, float* Eeff,
                 const float* scale_row, const float* scale_tab, const int* colgrp, float* scale_blk, int R, int C,
                 int G, int i1, int count, int mode, int dyn_gs, int sym, int maxq, int plus, const float* anchor,
                 const float* beta, int inner_mode, int atomic, float second_order_scale, void* stream);
 int rq_fq_lazy_update(float* Wp, float* GH, const float* Z, const float* Eeff, const float* Hinv, int R, int C, int G,
                       int i1, int count, int plus, const float* anchor, const float* beta, int outer_surrogate,
                       float second_order_scale, void* stream);
-int rq_fq_run(float* Wp, float* GH, const float* Z, const float* Hinv, float* Q, int8_t* codes, float* Eeff,
+int rq_fq_run(float* Wp, float* GH, const float* Z, const float* Hinv, float* Q, int16_t* codes, float* Eeff,
               const float* scale_row, const float* scale_tab, const int* colgrp, float* scale_blk, int R, int C, int G,
               int mode, int dyn_gs, int sym, int maxq, int plus, const float* anchor, const float* beta,
               int inner_mode, int atomic, void* stream);
@@ -328,7 +328,7 @@ int rq_fq_tc_prepare(const float* Hinv, int R, int C, int G, int plus, void* wor
 int rq_gptqplus_terms_tc(const float* Gp, const float* Hinv, int R, int C, int G, float alpha_eff, float ref_loss,
                          float* Z, float* GHinv, float* beta, float* hdiag, void* workspace, size_t workspace_bytes,
                          int* status, void* stream);
-int rq_fq_run_tc(float* Wp, float* GH, const float* Z, const float* Hinv, float* Q, int8_t* codes, float* Eeff,
+int rq_fq_run_tc(float* Wp, float* GH, const float* Z, const float* Hinv, float* Q, int16_t* codes, float* Eeff,
                  const float* scale_row, const float* scale_tab, const int* colgrp, float* scale_blk, int R, int C,
                  int G, int mode, int dyn_gs, int sym, int maxq, int plus, const float* anchor, const float* beta,
                  int inner_mode, int atomic, void* workspace, size_t workspace_bytes, int* status, void* stream);
@@ -336,7 +336,7 @@ int rq_fq_run_tc(float* Wp, float* GH, const float* Z, const float* Hinv, float*
 /* rq_fq_finish replaces the epilogue (gptq_utils/gptq_plus_utils.py:1850-1875; gptq_utils/gptq_utils.py:157-166):
  * out[r][perm[j]] = Q[r][j] cast to out_dtype; when out_codes != NULL also the fp32 int_weight / scale
  * buffers, un-permuted (permute_export != 0, GPTQ+) or left in permuted order (plain GPTQ). */
-int rq_fq_finish(const float* Q, const int8_t* codes, const int64_t* perm, int R, int C, void* out, int out_dtype,
+int rq_fq_finish(const float* Q, const int16_t* codes, const int64_t* perm, int R, int C, void* out, int out_dtype,
                  float* out_codes, float* out_scale, const float* scale_row, const float* scale_tab,
                  const int* colgrp, int permute_export, void* stream);
 

@@ -559,3 +559,32 @@ def test_gptaq_vs_reference(golden, case):
     assert frac < 0.02 and frac2 < 0.01
     # differing entries are one quantization step away in the row where the first tie flipped, never garbage
     assert float((got - ref).abs().max()) < 16 * float(ref.abs().max()) / (2 ** bits)
+
+
+def test_w8_asymmetric_codes_beyond_int8():
+    """8-bit asymmetric ranges have maxq = 255 (utils/quant_utils.py:309-331) and fake_quantize clamps to
+    [-256, 255]: the kernels carry the integer codes in 16 bits.  Plain GPTQ, 64 x 256, against the oracle on the
+    device's own Hessian."""
+    from gptq_plus_mp_quant_b200.gptq_utils.gptq_utils import GPTQ
+    from gptq_plus_mp_quant_b200.utils.quant_utils import WeightQuantizer
+    rows, cols, nseq, seqlen = 64, 256, 4, 512
+    W = cases.make_weight(rows, cols, seed=61)
+    X = cases.make_acts(nseq, seqlen, cols, seed=61)
+    layer = _layer(W)
+    obj = GPTQ(layer)
+    obj.quantizer = WeightQuantizer()
+    obj.quantizer.configure(8, perchannel=True, sym=False, mse=False)
+    assert int(obj.quantizer.maxq) == 255
+    for s in range(nseq):
+        obj.add_batch(X[s:s + 1].to(DEV), None)
+    H_dev = obj.H.clone().cpu()
+    obj.fasterquant(blocksize=128, percdamp=0.01, groupsize=-1, actorder=True, export_to_et=True)
+    q = oq.OracleWeightQuantizer()
+    q.configure(8, perchannel=True, sym=False)
+    ref = ogptq.plain_fasterquant(W, H_dev, q, blocksize=128, percdamp=0.01, groupsize=-1, actorder=True)
+    codes = layer.int_weight.cpu()
+    assert float(codes.abs().max()) > 127.0                       # the case does leave the int8 range
+    frac, rows_touched, first_off = _code_report(codes, ref["W_int"])
+    print(f"W8 asymmetric: {frac * 100:.4f}% codes differ in {rows_touched} rows")
+    assert frac < 5e-3 and all(d == 1.0 for d in first_off)
+    assert torch.allclose(layer.scale.cpu(), ref["Scale"], rtol=1e-6, atol=0)

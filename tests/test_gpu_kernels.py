@@ -749,3 +749,57 @@ def test_packed_upper_round_trip(C, G, pieces):
     for r in range(C):
         kept[r, (r // 128) * 128:] = True
     assert bool(torch.isnan(out[:, ~kept]).all())          # nothing else is written
+
+
+@pytest.mark.parametrize("out_f,in_f,had_dim,output,dtype,use_r2", [
+    (96, 1536, -1, False, torch.bfloat16, False),       # full-width rotation of the input side, K = 12
+    (1536, 64, -1, True, torch.float16, False),          # full-width rotation of the output side
+    (48, 512, 128, False, torch.bfloat16, False),        # per-head rotation (fp64 matmul), input side
+    (512, 40, 64, True, torch.float32, False),           # per-head rotation, output side
+    (48, 512, 128, False, torch.bfloat16, True),         # caller's own orthogonal matrix R2 instead of the Hadamard
+])
+def test_apply_exact_had_to_linear(out_f, in_f, had_dim, output, dtype, use_r2):
+    """Fusing a rotation into a linear's weight (utils/hadamard_utils.py:133-168) against an fp64 evaluation of the
+    same operator: within one rounding of the weight's dtype, dtype and device preserved."""
+    from gptq_plus_mp_quant_b200.utils import hadamard_utils as hu
+    g = torch.Generator().manual_seed(out_f + in_f)
+    W = (torch.randn(out_f, in_f, generator=g) * 0.05).to(dtype)
+    lin = torch.nn.Linear(in_f, out_f, bias=False, device=DEV, dtype=dtype)
+    lin.weight.data.copy_(W)
+    R2 = None
+    if use_r2:
+        R2 = torch.linalg.qr(torch.randn(had_dim, had_dim, generator=g, dtype=torch.float64))[0].to(DEV)
+    hu.apply_exact_had_to_linear(lin, had_dim=had_dim, output=output, R2=R2)
+    assert lin.weight.dtype == dtype and lin.weight.device.type == "cuda" and lin.weight.shape == (out_f, in_f)
+    Wd = W.double()
+    if had_dim == -1:
+        n = out_f if output else in_f
+        hadK, K = hu.get_hadK(n)
+        exact = ohad.rotate_exact(Wd.t().contiguous(), hadK, K).t() if output else ohad.rotate_exact(Wd, hadK, K)
+    else:
+        Hm = R2.cpu() if use_r2 else ohad.rotate_exact(torch.eye(had_dim, dtype=torch.float64), None, 1)
+        src = Wd.t().contiguous() if output else Wd
+        rot = (src.reshape(-1, src.shape[-1] // had_dim, had_dim) @ Hm).reshape(src.shape)
+        exact = rot.t() if output else rot
+    got = lin.weight.data.double().cpu()
+    eps = {torch.bfloat16: 2 ** -8, torch.float16: 2 ** -11, torch.float32: 2 ** -22}[dtype]
+    assert float((got - exact).abs().max()) <= eps * float(exact.abs().max()) * 1.01 + 1e-12
+
+
+@pytest.mark.parametrize("size", [128, 1536])
+def test_random_hadamard_matrix(size):
+    """utils/hadamard_utils.py:76-80: diag(+-1) times the normalised Hadamard matrix, built in fp64: orthogonal to
+    fp64 accuracy, every entry +-1/sqrt(size), and the signs are the generator's."""
+    from gptq_plus_mp_quant_b200.utils import hadamard_utils as hu
+    gen = torch.Generator().manual_seed(3)
+    Q = hu.random_hadamard_matrix(size, DEV, generator=gen)
+    assert Q.dtype == torch.float64 and Q.shape == (size, size) and Q.device.type == "cuda"
+    eye = torch.eye(size, dtype=torch.float64, device=DEV)
+    assert float((Q @ Q.t() - eye).abs().max()) < 1e-12
+    assert float((Q.abs() - 1.0 / math.sqrt(size)).abs().max()) < 1e-14
+    signs = torch.randint(low=0, high=2, size=(size,), generator=torch.Generator().manual_seed(3)).double() * 2 - 1
+    hadK, K = hu.get_hadK(size)
+    exact = ohad.rotate_exact(torch.diag(signs), hadK, K)
+    assert float((Q.cpu() - exact).abs().max()) < 1e-14
+    H = hu.hadamard_matrix(size, DEV)
+    assert float((H.double() @ H.double().t() - eye).abs().max()) < 1e-5
