@@ -484,47 +484,120 @@ def parity_vs_one_rank(wl, rank, world):
 
 
 # ----------------------------------------------------------------------------------------------
-# CPU arm: the port of the reference's own code on the host cores
+# CPU arm: the reference's own classes (oracle/_ref, when that copy was built), else the oracle port, on the host cores
 # ----------------------------------------------------------------------------------------------
-CPU_SAMPLE_SEQS, CPU_SAMPLE_ROWS = 16, 1024   # bounded sample of the CPU arm: 10-20 s on 16 host cores
+CPU_SAMPLE_SEQS, CPU_SAMPLE_ROWS = 16, 1024   # bounded sample of the CPU arm: a few seconds on 16 host cores
 
 
-def cpu_layer_seconds(hess_seqs: int, fq_rows: int):
-    """Times the CPU port on a bounded sample and extrapolates to the whole layer:
+def _cpu_arm():
+    """('reference', modules) when oracle/_ref holds the reference's modules, else ('port', None)."""
+    try:
+        from oracle import ref_loader
+        mods = ref_loader.load()
+    except Exception:
+        mods = None
+    return ("reference", mods) if mods else ("port", None)
+
+
+def cpu_layer_seconds(hess_seqs: int, fq_rows: int, arm=None):
+    """Times the CPU path on a bounded sample and extrapolates to the whole layer:
     Hessian stage by its flop count, fasterquant by rows (the sample quantizes `fq_rows` rows of a
-    4096-input linear with G = 4; Cholesky cost is per linear, the block loop per row)."""
+    4096-input linear with G = 4; Cholesky cost is per linear, the block loop per row).
+    Returns (layer seconds extrapolated, Hessian TFLOP/s, seconds of CPU work, kind)."""
     import cases
-    from oracle import gptq as ogptq
-    from oracle import hessian as ohess
-    from oracle import quantizer as oq
+    kind, mods = arm or _cpu_arm()
     W = LayerWorkload
     C, G, T = W.HID, W.G, W.T
     X = cases.make_acts(hess_seqs, T, C, seed=77)
     S = cases.make_saliency(hess_seqs, T, G, seed=77)
-    acc = ohess.GroupedHessian(C, S)
-    t0 = time.perf_counter()
-    acc.add_batch(X)
-    t_h = time.perf_counter() - t0
-    acc.finalize()
-    hess_tflops = 2.0 * hess_seqs * T * C * C * G / t_h / 1e12
     Wt = cases.make_weight(fq_rows, C, seed=78)
     Gr = cases.make_grad(fq_rows, C, seed=78)
-    q = oq.OracleWeightQuantizer()
-    q.configure(4, perchannel=True, sym=True)
-    t0 = time.perf_counter()
-    hinv_t0 = time.perf_counter()
-    ogptq.hinv_with_fallback(acc.H[0], 0.01)
-    t_chol = (time.perf_counter() - hinv_t0) * G                       # per 4096-input linear
-    ogptq.plus_fasterquant(Wt, acc.H, acc.act_square, Gr, q, G, 0.25, 0.7, groupsize=128, actorder=True,
-                           static_groups=True)
-    t_fq = time.perf_counter() - t0 - t_chol / G
+    if kind == "reference":
+        gp, qu = mods["gptq_plus_utils"], mods["quant_utils"]
+        layer = torch.nn.Linear(C, fq_rows, bias=False)
+        layer.weight.data.copy_(Wt)
+        obj = gp.GPTQPlus(layer, S, Gr, G, 0.25, 0.7)
+        obj.quantizer = qu.WeightQuantizer()
+        obj.quantizer.configure(4, perchannel=True, sym=True, mse=False)
+        t0 = time.perf_counter()
+        for s in range(0, hess_seqs, W.BSZ):
+            obj.add_batch(X[s:s + W.BSZ], None)
+        t_h = time.perf_counter() - t0
+        obj.finalize_hessian()
+        t0 = time.perf_counter()
+        obj._compute_hessian_inverse_with_fallback(obj.H[0].clone(), 0.01)      # one group's damped inverse factor
+        t_chol = (time.perf_counter() - t0) * G                                 # per 4096-input linear
+        t0 = time.perf_counter()
+        obj.fasterquant(blocksize=128, percdamp=0.01, groupsize=128, actorder=True, static_groups=True)
+        t_fq = time.perf_counter() - t0
+    else:
+        from oracle import gptq as ogptq
+        from oracle import hessian as ohess
+        from oracle import quantizer as oq
+        acc = ohess.GroupedHessian(C, S)
+        t0 = time.perf_counter()
+        for s in range(0, hess_seqs, W.BSZ):
+            acc.add_batch(X[s:s + W.BSZ])
+        t_h = time.perf_counter() - t0
+        acc.finalize()
+        q = oq.OracleWeightQuantizer()
+        q.configure(4, perchannel=True, sym=True)
+        t0 = time.perf_counter()
+        ogptq.hinv_with_fallback(acc.H[0], 0.01)
+        t_chol = (time.perf_counter() - t0) * G                            # per 4096-input linear
+        t0 = time.perf_counter()
+        ogptq.plus_fasterquant(Wt, acc.H, acc.act_square, Gr, q, G, 0.25, 0.7, groupsize=128, actorder=True,
+                               static_groups=True)
+        t_fq = time.perf_counter() - t0
+    hess_tflops = 2.0 * hess_seqs * T * C * C * G / t_h / 1e12
     per_row = max(t_fq - t_chol, 0.0) / fq_rows                        # block loop + lazy update per row at C = 4096
     total_h = sum(2.0 * W.NSEQ * T * c * c * G for _, _, c, _ in W.LINEARS) / (hess_tflops * 1e12)
     total_fq = 0.0
     for _, R, Cc, _ in W.LINEARS:
         scale_c = (Cc / C)
         total_fq += t_chol * scale_c ** 3 + per_row * R * scale_c ** 2
-    return total_h + total_fq, hess_tflops, t_h + t_fq
+    return total_h + total_fq, hess_tflops, t_h + t_fq, kind
+
+
+def cpu_c0_full_seconds(arm=None):
+    """configs[0] in full on the host cores, nothing extrapolated: plain GPTQ, 4096 x 4096, 32 x 2048 fp32 tokens fed
+    one sequence per add_batch, 4-bit asymmetric per-channel, act_order, block 128."""
+    kind, mods = arm or _cpu_arm()
+    g = torch.Generator().manual_seed(0)
+    C = 4096
+    Wt = torch.randn(C, C, generator=g) * 0.02
+    Wt[:, torch.randperm(C, generator=g)[:20]] *= 10.0
+    ch = torch.exp(torch.randn(C, generator=g))
+    X = torch.stack([torch.randn(2048, C, generator=g) * ch for _ in range(32)])
+    t0 = time.perf_counter()
+    if kind == "reference":
+        layer = torch.nn.Linear(C, C, bias=False)
+        layer.weight.data.copy_(Wt)
+        obj = mods["gptq_utils"].GPTQ(layer)
+        obj.quantizer = mods["quant_utils"].WeightQuantizer()
+        obj.quantizer.configure(4, perchannel=True, sym=False, mse=False)
+        for s in range(32):
+            obj.add_batch(X[s:s + 1], None)
+        obj.fasterquant(blocksize=128, percdamp=0.01, groupsize=-1, actorder=True, static_groups=True)
+    else:
+        from oracle import gptq as ogptq
+        from oracle import hessian as ohess
+        from oracle import quantizer as oq
+        acc = ohess.PlainHessian(C)
+        for s in range(32):
+            acc.add_batch(X[s:s + 1])
+        q = oq.OracleWeightQuantizer()
+        q.configure(4, perchannel=True, sym=False)
+        ogptq.plain_fasterquant(Wt, acc.H, q, blocksize=128, percdamp=0.01, groupsize=-1, actorder=True,
+                                static_groups=True)
+    return time.perf_counter() - t0
+
+
+def _cpu_sample_text(kind):
+    who = "the reference's own GPTQPlus class (oracle/_ref)" if kind == "reference" else "the oracle port of the reference"
+    return (f"per step: {who} on all host cores: add_batch of {CPU_SAMPLE_SEQS} of 128 sequences at C=4096 G=4 (batches of "
+            f"8) plus fasterquant of a {CPU_SAMPLE_ROWS} x 4096 linear (G=4, g128 static groups, act_order, alpha=0.25); "
+            "extrapolated to the layer's seven linears by flops (Hessian), C^3 (factorisation) and rows*C^2 (block loop)")
 
 
 def run_reference(args):
@@ -532,25 +605,74 @@ def run_reference(args):
     if rank != 0:
         return
     torch.set_num_threads(os.cpu_count() or 1)
+    arm = _cpu_arm()
     vals, busy = [], []
     for i in range(max(args.warmup, 0) + args.steps):
-        v, tf, b = cpu_layer_seconds(hess_seqs=CPU_SAMPLE_SEQS, fq_rows=CPU_SAMPLE_ROWS)
+        v, tf, b, kind = cpu_layer_seconds(hess_seqs=CPU_SAMPLE_SEQS, fq_rows=CPU_SAMPLE_ROWS, arm=arm)
         if i >= args.warmup:
             vals.append(v)
             busy.append(b)
     v = sum(vals) / len(vals)
-    sample = (f"per step: reference add_batch on {CPU_SAMPLE_SEQS} of 128 sequences at C=4096 G=4 plus fasterquant of "
-              f"{CPU_SAMPLE_ROWS} rows x 4096 "
-              "(G=4, g128, act_order, alpha=0.25), extrapolated to the layer by flops (Hessian), C^3 (Cholesky) "
-              "and rows*C^2 (block loop)")
+    c0 = cpu_c0_full_seconds(arm)
+    sample = _cpu_sample_text(kind)
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": round(v, 2), "unit": "s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(1e3 * sum(busy) / len(busy), 1),
         "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": LayerWorkload.name, "sample": sample},
-        "cpu_baseline": {"value": round(v, 2), "unit": "s", "cores": torch.get_num_threads(), "kind": "port",
-                         "sample": sample},
+        "cpu_baseline": {"value": round(v, 2), "unit": "s", "cores": torch.get_num_threads(), "kind": kind,
+                         "sample": sample, "c0_full_seconds": round(c0, 2),
+                         "c0_note": "configs[0] (plain GPTQ, 4096 x 4096, 32 x 2048 fp32 tokens) run in full, "
+                                    "nothing extrapolated"},
         "e2e": {"value": round(v, 2), "unit": "s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+
+
+def reference_torch_path_on_gpu(dev):
+    """Informative only: the reference's arithmetic as stock torch calls on this GPU (the oracle port with CUDA
+    tensors: fp32 bmm with TF32 off, torch.linalg.cholesky / cholesky_inverse, the per-column Python loop) for ONE
+    4096 x 4096 linear with G = 4 and 16 sequences.  This is the library-call bar the kernels replace; it is not
+    part of any timed figure of this benchmark."""
+    import cases
+    from oracle import gptq as ogptq
+    from oracle import hessian as ohess
+    from oracle import quantizer as oq
+    C, G, T, nseq, R = 4096, 4, 2048, 16, 1024
+    old = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        X = cases.make_acts(nseq, T, C, seed=77).to(dev)
+        S = cases.make_saliency(nseq, T, G, seed=77).to(dev)
+        Wt = cases.make_weight(R, C, seed=78).to(dev)
+        Gr = cases.make_grad(R, C, seed=78).to(dev)
+        acc = ohess.GroupedHessian(C, S)
+        acc.H, acc.act_square = acc.H.to(dev), acc.act_square.to(dev)
+        for rep in range(2):                                             # second pass is the warm one
+            acc.H.zero_()
+            acc.act_square.zero_()
+            acc.index = acc.token_count = 0
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            for s in range(0, nseq, 8):
+                acc.add_batch(X[s:s + 8])
+            torch.cuda.synchronize()
+            t_h = time.perf_counter() - t0
+        acc.finalize()
+        q = oq.OracleWeightQuantizer()
+        q.configure(4, perchannel=True, sym=True)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        ogptq.plus_fasterquant(Wt, acc.H, acc.act_square, Gr, q, G, 0.25, 0.7, groupsize=128, actorder=True,
+                               static_groups=True)
+        torch.cuda.synchronize()
+        t_fq = time.perf_counter() - t0
+        return {"hessian_tflops": round(2.0 * nseq * T * C * C * G / t_h / 1e12, 1),
+                "hessian_ms_16seq_C4096_G4": round(t_h * 1e3, 1), "fasterquant_ms_1024x4096_G4": round(t_fq * 1e3, 1),
+                "what": "stock torch on this GPU with the reference's arithmetic (fp32 bmm, TF32 off; "
+                        "torch.linalg.cholesky / cholesky_inverse; per-column Python loop); informative"}
+    except Exception as e:                                               # never let the extra break the line
+        return {"error": repr(e)[:200]}
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = old
 
 
 # ----------------------------------------------------------------------------------------------
@@ -673,11 +795,15 @@ def run_ours(args):
     }
     if rank == 0 and world == 1 and not args.no_cpu:
         torch.set_num_threads(os.cpu_count() or 1)
-        v, tf, busy = cpu_layer_seconds(hess_seqs=CPU_SAMPLE_SEQS, fq_rows=CPU_SAMPLE_ROWS)
-        out["cpu_baseline"] = {"value": round(v, 1), "unit": "s", "cores": torch.get_num_threads(), "kind": "port",
-                               "sample": f"add_batch on {CPU_SAMPLE_SEQS} of 128 sequences (C=4096, G=4: {tf:.2f} TFLOP/s) and "
-                                         f"fasterquant of {CPU_SAMPLE_ROWS} rows x 4096, {busy:.1f} s of CPU work, extrapolated to "
-                                         "the layer by flops / C^3 / rows*C^2"}
+        arm = _cpu_arm()
+        v, tf, busy, kind = cpu_layer_seconds(hess_seqs=CPU_SAMPLE_SEQS, fq_rows=CPU_SAMPLE_ROWS, arm=arm)
+        out["cpu_baseline"] = {"value": round(v, 1), "unit": "s", "cores": torch.get_num_threads(), "kind": kind,
+                               "sample": _cpu_sample_text(kind) + f" ({busy:.1f} s of CPU work, Hessian stage at "
+                                         f"{tf:.2f} TFLOP/s)",
+                               "c0_full_seconds": round(cpu_c0_full_seconds(arm), 2),
+                               "c0_note": "configs[0] (plain GPTQ, 4096 x 4096, 32 x 2048 fp32 tokens) run in full on "
+                                          "the host cores, nothing extrapolated"}
+        out["reference_torch_path_on_this_gpu"] = reference_torch_path_on_gpu(dev)
     if rank == 0:
         print(json.dumps(out))
     if world > 1:

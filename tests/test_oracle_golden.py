@@ -356,3 +356,15 @@ def test_weight_quantizer_grouped(golden, case):
     assert torch.equal(scale.float(), t(g[f"{name}.scale"])) and torch.equal(zero.float(), t(g[f"{name}.zero"]))
     assert torch.equal(fake.float(), t(g[f"{name}.fake"])) and torch.equal(codes.float(), t(g[f"{name}.codes"]))
     assert torch.equal(ste.float(), t(g[f"{name}.ste"]))
+
+
+def test_reference_copy_loads_when_present():
+    """oracle/_ref (built by oracle/make_ref.py where the reference is mounted) holds the reference's own modules
+    for the CPU arm of the benchmark; when it is there it must import and expose the classes the arm drives."""
+    from oracle import ref_loader
+    mods = ref_loader.load()
+    if mods is None:
+        pytest.skip("oracle/_ref has not been built on this machine")
+    assert hasattr(mods["gptq_plus_utils"], "GPTQPlus") and hasattr(mods["gptq_utils"], "GPTQ")
+    assert hasattr(mods["quant_utils"], "WeightQuantizer")
+    assert hasattr(mods["gptq_plus_utils"].GPTQPlus, "_compute_hessian_inverse_with_fallback")
