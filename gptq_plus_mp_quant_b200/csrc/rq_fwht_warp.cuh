@@ -12,6 +12,7 @@
 #pragma once
 
 #include "rq_common.cuh"
+#include "rq_had_tables.cuh"
 
 namespace rq {
 namespace fwht {
@@ -413,6 +414,95 @@ __device__ __forceinline__ void mix_pair(float* buf, int slice, const float* hk,
     }
 }
 
+// The mix for the tabulated matrices of order 12, 20 and 28, with the signs known at compile time.  A generic
+// +-1 matrix costs K multiply-adds per output.  Here the K inputs are taken four at a time: the eight values
+// (a +- b) +- (c +- d) a quad can contribute (up to an overall sign) cost 12 additions, after which every output is
+// one signed term per quad: 12 * K/4 + K * (K/4 - 1) additions per position instead of K * K multiply-adds
+// (60 instead of 144 at K = 12, 252 instead of 784 at K = 28).  The sums are the same fp32 additions of the same
+// exact +-v terms, associated quad by quad.  Combinations no row uses are never computed (their indices are
+// constants after unrolling).
+template <int K>
+__device__ __forceinline__ void mix_fixed(const float (&v)[K], float (&y)[K]) {
+    constexpr int NQ = K / 4;
+#pragma unroll
+    for (int q = 0; q < NQ; ++q) {              // quad by quad, so that a quad's inputs and combinations die early
+        const float ab0 = v[4 * q] + v[4 * q + 1], ab1 = v[4 * q] - v[4 * q + 1];
+        const float cd0 = v[4 * q + 2] + v[4 * q + 3], cd1 = v[4 * q + 2] - v[4 * q + 3];
+        const float c[8] = {ab0 + cd0, ab1 + cd0, ab0 - cd0, ab1 - cd0, ab0 + cd1, ab1 + cd1, ab0 - cd1, ab1 - cd1};
+#pragma unroll
+        for (int r = 0; r < K; ++r) {
+            const uint32_t bits = (had_row<K>(r) >> (4 * q)) & 15u;
+            const bool s0 = bits & 1u, s1 = bits & 2u, s2 = bits & 4u, s3 = bits & 8u;
+            const int idx = (s1 != s0 ? 1 : 0) | (s2 != s0 ? 2 : 0) | (s3 != s2 ? 4 : 0);
+            const float t = c[idx];
+            y[r] = (q == 0) ? (s0 ? t : -t) : (s0 ? y[r] + t : y[r] - t);
+        }
+    }
+}
+
+// true in every thread when the K x K matrix in shared memory is the tabulated one of that order
+template <int K>
+__device__ __forceinline__ bool matches_table(const float* hk) {
+    uint32_t tab[K];
+#pragma unroll
+    for (int r = 0; r < K; ++r) tab[r] = had_row<K>(r);
+    bool ok = true;
+    for (int e = threadIdx.x; e < K * K; e += blockDim.x) {
+        const int r = e / K, col = e - r * K;
+        ok = ok && hk[e] == (((tab[r] >> col) & 1u) ? 1.f : -1.f);
+    }
+    return __syncthreads_and(ok) != 0;
+}
+
+// two neighbouring positions of every chunk through mix_fixed, stored as pairs (QUANT: rounded to the I/O type and
+// put back into shared memory, min / max tracked, as mix_pair does)
+template <typename T, int K, bool QUANT>
+__device__ __forceinline__ void mix_pair_fixed(float* buf, int slice, int p, int P, T* yrow, float scale, float* lo,
+                                               float* hi) {
+    float v0[K], v1[K], y0[K], y1[K];
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+        const float2 t = *reinterpret_cast<const float2*>(buf + k * slice + wphys(p));
+        v0[k] = t.x;
+        v1[k] = t.y;
+    }
+    mix_fixed<K>(v0, y0);
+    mix_fixed<K>(v1, y1);
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+        if (QUANT) {
+            const float r0 = round_io<T>(y0[k] * scale), r1 = round_io<T>(y1[k] * scale);
+            *lo = fminf(*lo, fminf(r0, r1));
+            *hi = fmaxf(*hi, fmaxf(r0, r1));
+            *reinterpret_cast<float2*>(buf + k * slice + wphys(p)) = make_float2(r0, r1);
+        } else {
+            store2<T>(yrow + (int64_t)k * P + p, y0[k] * scale, y1[k] * scale);
+        }
+    }
+}
+
+// one position of every chunk through mix_fixed (half the registers of the pair form; lanes take consecutive
+// positions, so a warp still writes 64 contiguous bytes per output chunk)
+template <typename T, int K, bool QUANT>
+__device__ __forceinline__ void mix_one_fixed(float* buf, int slice, int p, int P, T* yrow, float scale, float* lo,
+                                              float* hi) {
+    float v[K], y[K];
+#pragma unroll
+    for (int k = 0; k < K; ++k) v[k] = buf[k * slice + wphys(p)];
+    mix_fixed<K>(v, y);
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+        if (QUANT) {
+            const float r = round_io<T>(y[k] * scale);
+            *lo = fminf(*lo, r);
+            *hi = fmaxf(*hi, r);
+            buf[k * slice + wphys(p)] = r;
+        } else {
+            store_from_float<T>(yrow, (int64_t)k * P + p, y[k] * scale);
+        }
+    }
+}
+
 // K > 1 with chunk length P = S: one CTA per row; warps transform the K chunks into shared memory, then
 // all threads mix the chunks position by position.
 // KMAX bounds K at compile time: the kernel for K <= 12 holds 24 instead of 56 chunk values per thread during the mix,
@@ -440,6 +530,12 @@ __global__ void __launch_bounds__(32 * WARPS, (KMAX <= 12 && LOGS == 10) ? 4 : 1
     float* hk = wsm + (size_t)K * slice;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     for (int e = threadIdx.x; e < K * K; e += blockDim.x) hk[e] = hadK[e];
+    __syncthreads();
+    // 0: the caller's matrix, entry by entry; 12 / 20 / 28: the tabulated matrix of that order (uniform over the CTA)
+    int fixed = 0;
+    if (K == 12) fixed = matches_table<12>(hk) ? 12 : 0;
+    else if (KMAX > 12 && K == 20) fixed = matches_table<20>(hk) ? 20 : 0;
+    else if (KMAX > 12 && K == 28) fixed = matches_table<28>(hk) ? 28 : 0;
     const int64_t n = (int64_t)K * S;
     for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
         __syncthreads();                                        // previous row's mix has finished reading
@@ -448,8 +544,16 @@ __global__ void __launch_bounds__(32 * WARPS, (KMAX <= 12 && LOGS == 10) ? 4 : 1
         __syncthreads();
         T* yrow = y + row * n;
         float lo = 0.f, hi = 0.f;
+        if (KMAX > 12 && fixed == 28) {
+            for (int p = threadIdx.x; p < S; p += blockDim.x)
+                mix_one_fixed<T, 28, QUANT>(wsm, slice, p, S, yrow, scale, &lo, &hi);
+        } else
         for (int p = 2 * threadIdx.x; p < S; p += 2 * blockDim.x) {
-            if (KMAX <= 12 || K <= 12) {
+            if (fixed == 12) {
+                mix_pair_fixed<T, 12, QUANT>(wsm, slice, p, S, yrow, scale, &lo, &hi);
+            } else if (KMAX > 12 && fixed == 20) {
+                mix_pair_fixed<T, 20, QUANT>(wsm, slice, p, S, yrow, scale, &lo, &hi);
+            } else if (KMAX <= 12 || K <= 12) {
                 mix_pair<T, 12, QUANT>(wsm, slice, hk, p, S, yrow, scale, K, &lo, &hi);
             } else if (KMAX > 12) {
                 if (K <= 20) mix_pair<T, 20, QUANT>(wsm, slice, hk, p, S, yrow, scale, K, &lo, &hi);

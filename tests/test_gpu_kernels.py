@@ -788,18 +788,22 @@ def test_apply_exact_had_to_linear(out_f, in_f, had_dim, output, dtype, use_r2):
 
 @pytest.mark.parametrize("size", [128, 1536])
 def test_random_hadamard_matrix(size):
-    """utils/hadamard_utils.py:76-80: diag(+-1) times the normalised Hadamard matrix, built in fp64: orthogonal to
-    fp64 accuracy, every entry +-1/sqrt(size), and the signs are the generator's."""
+    """utils/hadamard_utils.py:76-80: diag(+-1) times the normalised Hadamard matrix, built in fp64.  As in the
+    reference the normalisation divides by ``torch.tensor(size).sqrt()``, an fp32 square root, so the entries are
+    +-1/sqrt(size) to fp32 accuracy (exactly when size is a power of four) and orthogonality holds to ~1e-7; the
+    signs are the generator's."""
     from gptq_plus_mp_quant_b200.utils import hadamard_utils as hu
     gen = torch.Generator().manual_seed(3)
     Q = hu.random_hadamard_matrix(size, DEV, generator=gen)
     assert Q.dtype == torch.float64 and Q.shape == (size, size) and Q.device.type == "cuda"
     eye = torch.eye(size, dtype=torch.float64, device=DEV)
-    assert float((Q @ Q.t() - eye).abs().max()) < 1e-12
-    assert float((Q.abs() - 1.0 / math.sqrt(size)).abs().max()) < 1e-14
+    assert float((Q @ Q.t() - eye).abs().max()) < 1e-6
+    assert float((Q.abs() - 1.0 / math.sqrt(size)).abs().max()) < 1e-8
+    assert float((Q.abs() - Q.abs()[0, 0]).abs().max()) < 1e-15          # one magnitude throughout
     signs = torch.randint(low=0, high=2, size=(size,), generator=torch.Generator().manual_seed(3)).double() * 2 - 1
     hadK, K = hu.get_hadK(size)
     exact = ohad.rotate_exact(torch.diag(signs), hadK, K)
-    assert float((Q.cpu() - exact).abs().max()) < 1e-14
+    assert float((Q.cpu() - exact).abs().max()) < 1e-8
+    assert torch.equal(torch.sign(Q.cpu()), torch.sign(exact))
     H = hu.hadamard_matrix(size, DEV)
     assert float((H.double() @ H.double().t() - eye).abs().max()) < 1e-5

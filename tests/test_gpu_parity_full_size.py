@@ -24,6 +24,7 @@ reference's own fp32 path no longer reproduces itself: accumulating the same tok
 second fp32 evaluation there, so that case measures this sensitivity in the test (CPU path against CPU path)
 and bounds the device's deviation by it, in proportion to the size of the two H perturbations.
 """
+import os
 import time
 
 import pytest
@@ -39,6 +40,16 @@ DEV = "cuda:0"
 H_BAR = 1e-5          # relative Frobenius, north-star figure
 SCALE_BAR = 1e-5      # relative
 CODE_BAR = 1e-3       # share of codes that may differ
+
+
+@pytest.fixture(autouse=True)
+def _all_host_cores():
+    """The CPU side of these cases is minutes of work on one thread and seconds on all of them; other test
+    modules of the session pin torch to one thread when they are imported."""
+    before = torch.get_num_threads()
+    torch.set_num_threads(os.cpu_count() or 1)
+    yield
+    torch.set_num_threads(before)
 
 
 def rel_fro(a, b):
@@ -94,7 +105,7 @@ def _align_act_order(obj, act_sq_cpu):
     ~1e-7 relative, and among thousands of channels some neighbours in the sorted order are closer than that, so the
     two sides may swap such near-equal channels.  Checks that the device's sums agree with the CPU's to fp32
     summation noise and that the device's order is a valid order of the CPU's values up to that noise, then
-    hands the device the CPU's sums so that both sides process the columns in the same order.
+    makes the device process the columns in the CPU's order.
     Returns (max relative difference, number of positions at which the two orders differ)."""
     dev_sq = obj.act_square.cpu()
     rel = float(((dev_sq - act_sq_cpu).abs() / act_sq_cpu.abs()).max())
@@ -103,7 +114,11 @@ def _align_act_order(obj, act_sq_cpu):
     moved = int((perm_dev != perm_cpu).sum())
     along = act_sq_cpu[perm_dev]
     assert bool((along[1:] <= along[:-1] * (1 + 4e-6)).all()), "device act_order is not an order of the CPU's sums"
-    obj.act_square.copy_(act_sq_cpu.to(obj.act_square.device))
+    # a strictly decreasing key along the CPU's order: the device's argsort then returns exactly that order, also
+    # where the CPU's sums hold exact ties (fasterquant reads act_square for the ordering only)
+    key = torch.empty_like(act_sq_cpu)
+    key[perm_cpu] = torch.arange(act_sq_cpu.numel(), 0, -1, dtype=act_sq_cpu.dtype)
+    obj.act_square.copy_(key.to(obj.act_square.device))
     return rel, moved
 
 
