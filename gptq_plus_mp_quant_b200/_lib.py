@@ -56,6 +56,7 @@ SIGNATURES = {
     "rq_quantize": (_i, [_vp, _vp, _vp, _i, _i64, _i64, _vp, _vp, _i, _i, _i, _vp]),
     "rq_chol_workspace_bytes": (_sz, [_i, _i]),
     "rq_chol_hinv": (_i, [_vp, _vp, C.POINTER(C.c_float), _vp, _i, _i, _vp, _vp, _sz, _vp]),
+    "rq_chol_hinv_flags": (_i, [_vp, _vp, C.POINTER(C.c_float), _vp, _i, _i, _vp, _vp, _sz, _i, _vp]),
     "rq_fq_prepare": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _vp, _vp, _vp]),
     "rq_gptqplus_terms": (_i, [_vp, _vp, _i, _i, _i, _f, _f, _vp, _vp, _vp, _vp, _vp]),
     "rq_fq_block": (_i, [_vp] * 11 + [_i] * 10 + [_vp, _vp, _i, _i, _f, _vp]),

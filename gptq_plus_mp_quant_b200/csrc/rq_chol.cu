@@ -43,17 +43,50 @@ __global__ void __launch_bounds__(256) diag_mean_kernel(const float* __restrict_
 }
 
 // ------------------------------------------------------------------------------------------
-// A[g][i][j] = H[g][perm[i]][perm[j]] (+ dead fix, + damping on the diagonal), padded to Cp with
+// Equilibration by powers of two.  dsc[g][i] = 2^-h_i with h_i chosen so that the damped diagonal entry
+// a_ii * dsc_i^2 lies in [0.5, 2).  The factorisation then runs on A' = D A D (D = diag(dsc)): scaling by powers
+// of two is exact and commutes with every fp32 operation of the factorisation, so R' = D R and
+// U' = R'^-1 = U D^-1 are the same numbers as without it, differently scaled; the result is scaled back at the
+// end, Hinv[i][j] = U'[i][j] * dsc[j].  What it buys: every entry of R' is below sqrt(2), which lets the operand
+// planes of the trailing updates be fp16 (22 bits in two planes) with ONE fixed scale, whatever the spread of the
+// channels' energies.  Padding rows and bad diagonals (non-positive, non-finite) keep dsc = 1.
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) equil_kernel(const float* __restrict__ H, const int64_t* __restrict__ perm,
+                                                    const float* __restrict__ mean, const float* __restrict__ factor,
+                                                    int C, int Cp, float* __restrict__ dsc) {
+    const int g = blockIdx.y;
+    const int i = blockIdx.x * 256 + threadIdx.x;
+    if (i >= Cp) return;
+    float d = 1.f;
+    if (i < C) {
+        const int64_t pi = perm ? perm[i] : i;
+        float a = H[(int64_t)g * C * C + pi * C + pi];
+        if (a == 0.f) a = 1.f;
+        a += factor[g] * mean[g];
+        if (a > 0.f && a <= 3.0e38f) {
+            const int e = ilogbf(a);
+            const int h = (e >= 0) ? (e + 1) / 2 : -((-e) / 2);
+            d = exp2f((float)-(h < -60 ? -60 : (h > 60 ? 60 : h)));
+        }
+    }
+    dsc[(int64_t)g * Cp + i] = d;
+}
+
+// ------------------------------------------------------------------------------------------
+// A[g][i][j] = dsc_i * H[g][perm[i]][perm[j]] * dsc_j (+ dead fix, + damping on the diagonal), padded to Cp with
 // an identity block.  Only the upper triangle is consumed afterwards.
 // ------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) gather_kernel(const float* __restrict__ H, const int64_t* __restrict__ perm,
                                                      const float* __restrict__ mean, const float* __restrict__ factor,
-                                                     int C, int Cp, float* __restrict__ A) {
+                                                     const float* __restrict__ dsc, int C, int Cp,
+                                                     float* __restrict__ A) {
     const int g = blockIdx.z;
     const int i = blockIdx.y;
     const float* Hg = H + (int64_t)g * C * C;
     float* Arow = A + ((int64_t)g * Cp + i) * Cp;
+    const float* dg = dsc + (int64_t)g * Cp;
     const float lambda = factor[g] * mean[g];
+    const float di = dg[i];
     const int64_t pi = (i < C) ? (perm ? perm[i] : i) : 0;
     for (int j = blockIdx.x * 256 + threadIdx.x; j < Cp; j += gridDim.x * 256) {
         float v;
@@ -64,6 +97,7 @@ __global__ void __launch_bounds__(256) gather_kernel(const float* __restrict__ H
                 if (v == 0.f) v = 1.f;               // dead input channel
                 v += lambda;
             }
+            v = (v * di) * dg[j];
         } else {
             v = (i == j) ? 1.f : 0.f;
         }
@@ -407,14 +441,24 @@ __global__ void __launch_bounds__(gemm::kThreads, 2) inv_level_kernel(const floa
     gemm::tile<false>(a, ti * NB, tj * NB, smem);
 }
 
-// non-finite scan of the result (upper triangle incl. diagonal); marks info[g] = -1 when info[g] == 0
-__global__ void __launch_bounds__(256) finite_check_kernel(const float* __restrict__ U, int Cp, int* __restrict__ info) {
+// Last pass over the result: undo the equilibration, Hinv[i][j] = U'[i][j] * dsc[j] (exact), and scan for
+// non-finite entries; marks info[g] = -1 when info[g] == 0.  grid (row blocks, G): a block walks whole rows.
+__global__ void __launch_bounds__(256) unscale_check_kernel(float* __restrict__ U, const float* __restrict__ dsc, int Cp,
+                                                            int* __restrict__ info) {
     const int g = blockIdx.y;
-    const float* Ug = U + (int64_t)g * Cp * Cp;
+    float* Ug = U + (int64_t)g * Cp * Cp;
+    const float* dg = dsc + (int64_t)g * Cp;
     int badv = 0;
-    for (int64_t e = (int64_t)blockIdx.x * 256 + threadIdx.x; e < (int64_t)Cp * Cp; e += (int64_t)gridDim.x * 256) {
-        const float v = Ug[e];
-        if (isnan(v) || isinf(v)) badv = 1;
+    for (int i = blockIdx.x; i < Cp; i += gridDim.x) {
+        float* row = Ug + (int64_t)i * Cp;
+        for (int j = (i & ~3) + 4 * threadIdx.x; j < Cp; j += 1024) {          // nothing but zeros left of the diagonal
+            float4 v = *reinterpret_cast<float4*>(row + j);
+            const float4 d = *reinterpret_cast<const float4*>(dg + j);
+            v.x *= d.x; v.y *= d.y; v.z *= d.z; v.w *= d.w;
+            if (!(fabsf(v.x) <= 3.4e38f) || !(fabsf(v.y) <= 3.4e38f) || !(fabsf(v.z) <= 3.4e38f) || !(fabsf(v.w) <= 3.4e38f))
+                badv = 1;
+            *reinterpret_cast<float4*>(row + j) = v;
+        }
     }
     if (__syncthreads_or(badv) && threadIdx.x == 0) atomicCAS(&info[g], 0, -1);
 }
@@ -432,6 +476,8 @@ constexpr int kTensorTrailingMinBlocks = 4;
 constexpr int kOuterBlocks = 4;
 // levels of the triangular inverse with blocks at least this wide run on the tensor cores
 constexpr int kTensorInverseMinBlock = 512;
+// fp16 planes of the panels: entries of the equilibrated factor are below sqrt(2); 2^13 puts them below 11586
+constexpr float kPanelScale = 8192.f;
 
 }  // namespace chol
 }  // namespace rq
@@ -450,12 +496,14 @@ extern "C" size_t rq_chol_workspace_bytes(int C, int G) {
     const size_t Cp = (size_t)(C + chol::NB - 1) / chol::NB * chol::NB;
     // A, T, per-group means / factors / status, bf16 planes of one block column
     return 2 * (size_t)G * Cp * Cp * sizeof(float) + 256 * sizeof(float) + chol_panel_plane_bytes(Cp, G) + 4096 +
-           4 * chol_full_plane_bytes(Cp, G);                  // R^T, U, U^T, T planes for the inverse
+           4 * chol_full_plane_bytes(Cp, G) +                 // R^T, U, U^T, T planes for the inverse
+           (size_t)G * Cp * sizeof(float) + 1024;             // equilibration factors
 }
 
-extern "C" int rq_chol_hinv(const float* H, const int64_t* perm, const float* damp_factor, float* Hinv, int C, int G,
-                            int* info, void* workspace, size_t workspace_bytes, void* stream) {
+static int chol_hinv_impl(const float* H, const int64_t* perm, const float* damp_factor, float* Hinv, int C, int G,
+                          int* info, void* workspace, size_t workspace_bytes, int flags, void* stream) {
     using namespace rq::chol;
+    const bool bf16_only = (flags & 1) != 0;
     if (!H || !damp_factor || !Hinv || !info || !workspace || C <= 0 || G <= 0 || G > 64) return RQ_ERR_INVALID;
     if (workspace_bytes < rq_chol_workspace_bytes(C, G)) return RQ_ERR_WORKSPACE;
     if (reinterpret_cast<uintptr_t>(workspace) % 256 != 0 || reinterpret_cast<uintptr_t>(Hinv) % 16 != 0)
@@ -471,6 +519,9 @@ extern "C" int rq_chol_hinv(const float* H, const int64_t* perm, const float* da
     int* tc_status = reinterpret_cast<int*>(mean + 128);
     __nv_bfloat16* panel_planes = reinterpret_cast<__nv_bfloat16*>(
         (reinterpret_cast<uintptr_t>(mean + 256) + 1023) / 1024 * 1024);
+    float* dsc = reinterpret_cast<float*>(
+        (reinterpret_cast<uintptr_t>(panel_planes) + chol_panel_plane_bytes(Cp, G) + 4 * chol_full_plane_bytes(Cp, G) + 2048 +
+         1023) / 1024 * 1024);
     prof::Scope timed(RQ_PROF_CHOL, st);
     if (cudaMemsetAsync(tc_status, 0, sizeof(int), st) != cudaSuccess) return RQ_ERR_CUDA;
 
@@ -479,9 +530,10 @@ extern "C" int rq_chol_hinv(const float* H, const int64_t* perm, const float* da
     if (cudaMemsetAsync(info, 0, (size_t)G * sizeof(int), st) != cudaSuccess) return RQ_ERR_CUDA;
     if (cudaMemsetAsync(Hinv, 0, mat * sizeof(float), st) != cudaSuccess) return RQ_ERR_CUDA;
     diag_mean_kernel<<<G, 256, 0, st>>>(H, C, mean);
+    equil_kernel<<<dim3((unsigned)((Cp + 255) / 256), (unsigned)G), 256, 0, st>>>(H, perm, mean, factor, C, Cp, dsc);
     {
         dim3 grid((unsigned)((Cp + 1023) / 1024), (unsigned)Cp, (unsigned)G);
-        gather_kernel<<<grid, 256, 0, st>>>(H, perm, mean, factor, C, Cp, A);
+        gather_kernel<<<grid, 256, 0, st>>>(H, perm, mean, factor, dsc, C, Cp, A);
     }
     int rc = check_launch();
     if (rc != RQ_OK) return rc;
@@ -514,6 +566,8 @@ extern "C" int rq_chol_hinv(const float* H, const int64_t* perm, const float* da
                 sa.rows = k * NB; sa.cols = NB;
                 sa.dst = panel_planes; sa.Kp = W; sa.plane_stride = (long long)Cp * W;
                 sa.plane = 0; sa.plane_z = 2; sa.dst_row0 = 0; sa.dst_row_z = 0; sa.dst_k0 = p * NB; sa.pad_k_to = 0;
+                sa.fp16 = bf16_only ? 0 : 1;                   // |R'| < sqrt(2) after the equilibration
+                sa.scale = bf16_only ? 1.f : kPanelScale;
                 rc = tcgemm::split_rows(sa, G, st);
                 if (rc != RQ_OK) return rc;
                 tcgemm::PlaneTensor pt{panel_planes, W, Cp, 2LL * G};
@@ -522,7 +576,8 @@ extern "C" int rq_chol_hinv(const float* H, const int64_t* perm, const float* da
                 gp.tri = 1; gp.kmode = 0; gp.batch = G;
                 gp.ldc = Cp; gp.c_z = (long long)Cp * Cp;
                 gp.Aux = nullptr; gp.ldaux = 0; gp.aux_z = 0;
-                gp.alpha = -1.f; gp.beta = 1.f; gp.gamma = 0.f;
+                gp.alpha = bf16_only ? -1.f : -1.f / (kPanelScale * kPanelScale); gp.beta = 1.f; gp.gamma = 0.f;
+                gp.fp16 = bf16_only ? 0 : 1;
                 gp.a_row0 = 0;
                 if (p > 0) {            // columns [c0*128, k*128) of the outer block: A_ij -= R_ik . R_jk^T
                     gp.b_row0 = c0 * NB; gp.a_k0 = gp.b_k0 = p * NB; gp.k_len = NB;
@@ -555,16 +610,32 @@ extern "C" int rq_chol_hinv(const float* H, const int64_t* perm, const float* da
     // planes (U and U^T) start as the band of diagonal blocks the CUDA-core levels produced and then receive,
     // level by level, just the off-diagonal blocks that level created; T is split block by block as well;
     // R^T once, above the diagonal.
-    auto plane_args = [&](const float* src, __nv_bfloat16* dst) {
+    // fp16 planes for the inverse as well.  The equilibrated damped matrix satisfies A' >= lambda D^2 with
+    // D^2 >= 1 / (2 max_i a_ii), so every entry of U' = R'^-1 is at most B = sqrt(2 max_i a_ii / lambda)
+    // <= sqrt(2 (1 + C / p)), p the smallest damping fraction of the groups: the scale of the U planes follows from
+    // that bound and cannot overflow.  The intermediate T = U'_aa.R'_ab has no comparably tight bound (its entries
+    // are at most B times a column norm of R'); its planes get a quarter of the head room of U's, 4.4 B, which
+    // real Hessians stay far below.  Should a matrix exceed it, the planes hold infinities, the result fails the
+    // finiteness scan (info = -1), and the caller repeats the factorisation with flag 1 (bf16 planes, four products)
+    // before treating it as a failed attempt.  Where B leaves less than one binary digit of head room the levels use
+    // bf16 planes from the start.
+    float pmin = damp_factor[0];
+    for (int g = 1; g < G; ++g) pmin = damp_factor[g] < pmin ? damp_factor[g] : pmin;
+    const double ubound = pmin > 0.f ? sqrt(2.0 * (1.0 + (double)C / (double)pmin)) : 1e30;
+    const float sU = (float)exp2(floor(log2(30000.0 / ubound)));
+    const int inv_fp16 = (sU >= 2.f && !bf16_only) ? 1 : 0;
+    const float sT = inv_fp16 ? sU * 0.5f : 1.f, sUu = inv_fp16 ? sU : 1.f, sR = inv_fp16 ? kPanelScale : 1.f;
+    auto plane_args = [&](const float* src, __nv_bfloat16* dst, float scale) {
         tcgemm::SplitArgs sa;
         sa.src = src; sa.ld = Cp; sa.src_z = (long long)Cp * Cp; sa.rows = Cp; sa.cols = Cp;
         sa.dst = dst; sa.Kp = Cp; sa.plane_stride = (long long)Cp * Cp; sa.plane = 0; sa.plane_z = 2;
         sa.dst_row0 = 0; sa.dst_row_z = 0; sa.dst_k0 = 0; sa.pad_k_to = 0;
+        sa.fp16 = inv_fp16; sa.scale = scale;
         return sa;
     };
     // blocks (a, b) of level s: rows [2ms, 2ms+s), columns [2ms+s, min(2ms+2s, Cp)), m = 0 .. pairs-1
-    auto split_pair_blocks = [&](const float* src, __nv_bfloat16* dst, int s, int pairs, bool transpose) {
-        tcgemm::SplitArgs sa = plane_args(src + s, dst);
+    auto split_pair_blocks = [&](const float* src, __nv_bfloat16* dst, int s, int pairs, bool transpose, float scale) {
+        tcgemm::SplitArgs sa = plane_args(src + s, dst, scale);
         sa.rows = s; sa.cols = s; sa.nz1 = pairs; sa.src_z1 = (long long)2 * s * Cp + 2 * s;
         sa.src_col0 = s; sa.src_col_z1 = 2 * s; sa.src_cols_total = Cp;
         sa.src_row0 = 0; sa.src_row_z1 = 2 * s; sa.src_rows_total = Cp;
@@ -584,12 +655,12 @@ extern "C" int rq_chol_hinv(const float* H, const int64_t* perm, const float* da
         }
         // tensor-core level: pair m merges a = [2ms, 2ms+s) and b = [2ms+s, min(2ms+2s, Cp))
         if (!planes_ready) {
-            tcgemm::SplitArgs sa = plane_args(A, PRt);             // planes of R^T: [n][k] = R[k][n], k <= n
+            tcgemm::SplitArgs sa = plane_args(A, PRt, sR);         // planes of R^T: [n][k] = R[k][n], k <= n
             sa.upper_only = 1;
             rc = tcgemm::split_transpose(sa, G, st);
             if (rc != RQ_OK) return rc;
             for (int tr = 0; tr < 2; ++tr) {                       // diagonal blocks of width s of U and U^T
-                tcgemm::SplitArgs sd = plane_args(Hinv, tr ? PUt : PU);
+                tcgemm::SplitArgs sd = plane_args(Hinv, tr ? PUt : PU, sUu);
                 sd.rows = s; sd.cols = s; sd.nz1 = (Cp + s - 1) / s; sd.src_z1 = (long long)s * Cp + s;
                 sd.src_col0 = 0; sd.src_col_z1 = s; sd.src_cols_total = Cp;
                 sd.src_row0 = 0; sd.src_row_z1 = s; sd.src_rows_total = Cp;
@@ -609,25 +680,36 @@ extern "C" int rq_chol_hinv(const float* H, const int64_t* perm, const float* da
         gp.n_limit = Cp - s; gp.n_limit_z1 = 2 * s;
         gp.a_row_z1 = 2 * s; gp.b_row_z1 = 2 * s; gp.a_k_z1 = 2 * s; gp.b_k_z1 = 2 * s;
         // step 1: T[a, b] = U[a, a] . R[a, b]
+        gp.fp16 = inv_fp16;
         gp.a_row0 = 0; gp.a_k0 = 0; gp.b_row0 = s; gp.b_k0 = 0; gp.kmode = 1;
-        gp.C = T + s; gp.alpha = 1.f;
+        gp.C = T + s; gp.alpha = 1.f / (sUu * sR);
         rc = tcgemm::launch(tU, tRt, gp, tc_status, st);
         if (rc != RQ_OK) return rc;
-        rc = split_pair_blocks(T, PT, s, pairs, false);
+        rc = split_pair_blocks(T, PT, s, pairs, false, sT);
         if (rc != RQ_OK) return rc;
         // step 2: U[a, b] = -T[a, b] . U[b, b]
         gp.a_row0 = 0; gp.a_k0 = s; gp.b_row0 = s; gp.b_k0 = s; gp.kmode = 2;
-        gp.C = Hinv + s; gp.alpha = -1.f;
+        gp.C = Hinv + s; gp.alpha = -1.f / (sT * sUu);
         rc = tcgemm::launch(tT, tUt, gp, tc_status, st);
         if (rc != RQ_OK) return rc;
         if (2 * s < Cp) {                                          // the next level reads the blocks just created
-            rc = split_pair_blocks(Hinv, PU, s, pairs, false);
+            rc = split_pair_blocks(Hinv, PU, s, pairs, false, sUu);
             if (rc != RQ_OK) return rc;
-            rc = split_pair_blocks(Hinv, PUt, s, pairs, true);
+            rc = split_pair_blocks(Hinv, PUt, s, pairs, true, sUu);
             if (rc != RQ_OK) return rc;
         }
     }
-    finite_check_kernel<<<dim3(64, (unsigned)G), 256, 0, st>>>(Hinv, Cp, info);
+    unscale_check_kernel<<<dim3(592, (unsigned)G), 256, 0, st>>>(Hinv, dsc, Cp, info);
     merge_status_kernel<<<1, 64, 0, st>>>(tc_status, info, G);
     return check_launch();
+}
+
+extern "C" int rq_chol_hinv(const float* H, const int64_t* perm, const float* damp_factor, float* Hinv, int C, int G,
+                            int* info, void* workspace, size_t workspace_bytes, void* stream) {
+    return chol_hinv_impl(H, perm, damp_factor, Hinv, C, G, info, workspace, workspace_bytes, 0, stream);
+}
+
+extern "C" int rq_chol_hinv_flags(const float* H, const int64_t* perm, const float* damp_factor, float* Hinv, int C,
+                                  int G, int* info, void* workspace, size_t workspace_bytes, int flags, void* stream) {
+    return chol_hinv_impl(H, perm, damp_factor, Hinv, C, G, info, workspace, workspace_bytes, flags, stream);
 }

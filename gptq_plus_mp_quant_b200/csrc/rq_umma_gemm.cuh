@@ -55,6 +55,9 @@ struct Params {
     int a_row_z1 = 0, b_row_z1 = 0, a_k_z1 = 0, b_k_z1 = 0;
     long long c_z1 = 0;
     int n_limit = 0, n_limit_z1 = 0;
+    // 1: the planes hold fp16 (11 significant bits each, the caller having scaled the operands into fp16's range by
+    // powers of two that alpha undoes); the lo.lo product, 2^-22 relative, is then left out (three products)
+    int fp16 = 0;
 };
 
 struct TileCtx {
@@ -179,7 +182,8 @@ split_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0) {
-            constexpr uint32_t idesc = umma_idesc_bf16_f32(BM, BN);
+            const uint32_t idesc = p.fp16 ? umma_idesc_f16_f32(BM, BN) : umma_idesc_bf16_f32(BM, BN);
+            const bool four = p.fp16 == 0;
             uint32_t it = 0, win_iter = 0;
             bool ok = true;
             for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
@@ -206,8 +210,9 @@ split_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
                             const uint64_t dal = umma_smem_desc(a_lo + koff, kSBO, kLayoutSW128);
                             const uint64_t dbh = umma_smem_desc(b_hi + koff, kSBO, kLayoutSW128);
                             const uint64_t dbl = umma_smem_desc(b_lo + koff, kSBO, kLayoutSW128);
-                            umma_bf16(d_tmem, dal, dbl, idesc, (kb != w0 || k != 0) ? 1u : 0u);
-                            umma_bf16(d_tmem, dah, dbl, idesc, 1u);
+                            const uint32_t keep = (kb != w0 || k != 0) ? 1u : 0u;    // a window's first MMA overwrites
+                            if (four) umma_bf16(d_tmem, dal, dbl, idesc, keep);
+                            umma_bf16(d_tmem, dah, dbl, idesc, four ? 1u : keep);
                             umma_bf16(d_tmem, dal, dbh, idesc, 1u);
                             umma_bf16(d_tmem, dah, dbh, idesc, 1u);
                         }
@@ -340,11 +345,29 @@ struct SplitArgs {
     int src_row0 = 0, src_row_z1 = 0, src_rows_total = 0;
     int upper_only = 0;                         // transpose: skip source tiles that lie strictly below the diagonal
     int vec4 = 0;                               // set by the launcher when every offset is a multiple of 4 elements
+    // fp16 planes: v * scale (a power of two chosen by the caller so that the products stay inside fp16's range)
+    // split into two fp16 values; otherwise two bf16 values of v itself
+    int fp16 = 0;
+    float scale = 1.f;
 };
 
 __device__ __forceinline__ void split2(float v, __nv_bfloat16& hi, __nv_bfloat16& lo) {
     hi = __float2bfloat16_rn(v);
     lo = __float2bfloat16_rn(v - __bfloat162float(hi));
+}
+
+// 16-bit patterns of hi and lo: bf16 (v = hi + lo to 16 bits) or fp16 of the scaled value (22 bits)
+__device__ __forceinline__ void split2(float v, const SplitArgs& a, __nv_bfloat16& hi, __nv_bfloat16& lo) {
+    if (a.fp16) {
+        const float w = v * a.scale;
+        const __half h = __float2half_rn(w);
+        const __half l = __float2half_rn(w - __half2float(h));
+        hi = __ushort_as_bfloat16(__half_as_ushort(h));
+        lo = __ushort_as_bfloat16(__half_as_ushort(l));
+    } else {
+        hi = __float2bfloat16_rn(v);
+        lo = __float2bfloat16_rn(v - __bfloat162float(hi));
+    }
 }
 
 __device__ __forceinline__ int split_clipped_rows(const SplitArgs& a, int z1) {
@@ -390,7 +413,7 @@ static __global__ void __launch_bounds__(256) split_rows_kernel(const SplitArgs 
                     if (c + 2 < cols) v.z = srow[c + 2];
                 }
                 __nv_bfloat16 h0, h1, h2, h3, l0, l1, l2, l3;
-                split2(v.x, h0, l0); split2(v.y, h1, l1); split2(v.z, h2, l2); split2(v.w, h3, l3);
+                split2(v.x, a, h0, l0); split2(v.y, a, h1, l1); split2(v.z, a, h2, l2); split2(v.w, a, h3, l3);
                 if (c + 3 < kspan) {
                     __nv_bfloat162 hp[2] = {__halves2bfloat162(h0, h1), __halves2bfloat162(h2, h3)};
                     __nv_bfloat162 lp[2] = {__halves2bfloat162(l0, l1), __halves2bfloat162(l2, l3)};
@@ -405,7 +428,7 @@ static __global__ void __launch_bounds__(256) split_rows_kernel(const SplitArgs 
             for (int c = blockIdx.x * 256 + threadIdx.x; c < kspan; c += gridDim.x * 256) {
                 const float v = c < cols ? srow[c] : 0.f;
                 __nv_bfloat16 h, l;
-                split2(v, h, l);
+                split2(v, a, h, l);
                 hi[drow + c] = h;
                 lo[drow + c] = l;
             }
@@ -442,8 +465,8 @@ static __global__ void __launch_bounds__(256) split_transpose_kernel(const Split
         const long long d =
             (long long)(a.dst_row0 + z * a.dst_row_z + z1 * a.dst_row_z1 + c) * a.Kp + a.dst_k0 + z1 * a.dst_k_z1 + r;
         __nv_bfloat16 h0, l0, h1, l1;
-        split2(tile[2 * tx][cc], h0, l0);
-        split2(tile[2 * tx + 1][cc], h1, l1);
+        split2(tile[2 * tx][cc], a, h0, l0);
+        split2(tile[2 * tx + 1][cc], a, h1, l1);
         if (pair_ok && r + 1 < kspan) {
             *reinterpret_cast<__nv_bfloat162*>(hi + d) = __halves2bfloat162(h0, h1);
             *reinterpret_cast<__nv_bfloat162*>(lo + d) = __halves2bfloat162(l0, l1);

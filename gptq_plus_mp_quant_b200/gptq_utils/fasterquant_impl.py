@@ -38,7 +38,13 @@ KEEP_INTERMEDIATES = False
 # ----------------------------------------------------------------------------------------------
 # damped inverse factor with the reference's retry semantics
 # ----------------------------------------------------------------------------------------------
-def _chol_once(H3: torch.Tensor, perm, factors, Hinv: torch.Tensor, info: torch.Tensor) -> None:
+# flag of rq_chol_hinv_flags: bf16 operand planes throughout (REALQ_CHOL_BF16=1 forces it for every call)
+CHOL_BF16_ONLY = 1
+_CHOL_FLAGS = CHOL_BF16_ONLY if os.environ.get("REALQ_CHOL_BF16", "0") != "0" else 0
+
+
+def _chol_once(H3: torch.Tensor, perm, factors, Hinv: torch.Tensor, info: torch.Tensor, flags: int | None = None) -> None:
+    flags = _CHOL_FLAGS if flags is None else flags
     G, Cc = H3.shape[0], H3.shape[-1]
     need = _lib.lib.rq_chol_workspace_bytes(Cc, G)
     ws = ops._workspace(H3.device, need + 256)
@@ -46,9 +52,9 @@ def _chol_once(H3: torch.Tensor, perm, factors, Hinv: torch.Tensor, info: torch.
     aligned = (base + 255) // 256 * 256
     arr = (ctypes.c_float * G)(*[float(f) for f in factors])
     with torch.cuda.device(H3.device):
-        rc = _lib.lib.rq_chol_hinv(_lib.ptr(H3), _lib.ptr(perm), arr, _lib.ptr(Hinv), Cc, G, _lib.ptr(info),
-                                   aligned, ws.numel() - (aligned - base), _lib.stream_of(H3))
-    _lib.check("rq_chol_hinv", rc)
+        rc = _lib.lib.rq_chol_hinv_flags(_lib.ptr(H3), _lib.ptr(perm), arr, _lib.ptr(Hinv), Cc, G, _lib.ptr(info),
+                                         aligned, ws.numel() - (aligned - base), int(flags), _lib.stream_of(H3))
+    _lib.check("rq_chol_hinv_flags", rc)
 
 
 def hinv_with_fallback(H3: torch.Tensor, perm, percdamp: float, identity_fallback: bool, log_context: str = ""):
@@ -87,12 +93,21 @@ def hinv_with_fallback(H3: torch.Tensor, perm, percdamp: float, identity_fallbac
                 g1 = min(G, g0 + batch)
                 _chol_once(H3[g0:g1], perm, [growth[g] - 1.0 for g in range(g0, g1)], Hinv[g0:g1], info[g0:g1])
             flags = info.tolist()
+            # a non-finite result of the fp16-plane route may be an overflowed intermediate of the inverse rather
+            # than a failed factorisation: those groups get one more try with bf16 planes at the same damping
+            for g in [g for g in range(G) if flags[g] == -1 and _CHOL_FLAGS == 0]:
+                sub = torch.zeros(1, dtype=torch.int32, device=H3.device)
+                _chol_once(H3[g:g + 1], perm, [growth[g] - 1.0], Hinv[g:g + 1], sub, flags=CHOL_BF16_ONLY)
+                flags[g] = int(sub.item())
         else:
             flags = [0] * G
             for g in todo:
                 sub = torch.zeros(1, dtype=torch.int32, device=H3.device)
                 _chol_once(H3[g:g + 1], perm, [growth[g] - 1.0], Hinv[g:g + 1], sub)
                 flags[g] = int(sub.item())
+                if flags[g] == -1 and _CHOL_FLAGS == 0:
+                    _chol_once(H3[g:g + 1], perm, [growth[g] - 1.0], Hinv[g:g + 1], sub, flags=CHOL_BF16_ONLY)
+                    flags[g] = int(sub.item())
         first = False
         pending = []
         if any(flags[g] == -2 for g in todo):

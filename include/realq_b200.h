@@ -260,6 +260,14 @@ int rq_clip_to_quant_bounds(void* W, int dtype, int64_t R, int64_t C, int64_t ld
 size_t rq_chol_workspace_bytes(int C, int G);
 int rq_chol_hinv(const float* H, const int64_t* perm, const float* damp_factor, float* Hinv, int C, int G,
                  int* info, void* workspace, size_t workspace_bytes, void* stream);
+/* rq_chol_hinv with options.  flags bit 0: keep every tensor-core operand plane in bf16 (four split products, 16
+ * significant bits per operand).  By default the matrix is equilibrated by powers of two (exact) and the planes are
+ * fp16 (22 bits, three products): the entries of the factor are then bounded by sqrt(2) and those of its inverse by
+ * sqrt(2 (1 + C / p)), which fixes the scales; only an intermediate of the inverse has no tight bound, and a matrix
+ * that overflows it shows up as info = -1 (non-finite result): repeat the call with flag 1 before counting the
+ * attempt as failed. */
+int rq_chol_hinv_flags(const float* H, const int64_t* perm, const float* damp_factor, float* Hinv, int C, int G,
+                       int* info, void* workspace, size_t workspace_bytes, int flags, void* stream);
 
 /* ------------------------------------------------------------------------------------------
  * fasterquant.  R = out_features, C = in_features, G row sub-groups of R/G rows (group g uses Hinv[g]);
