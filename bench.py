@@ -149,15 +149,26 @@ def dist_setup():
 UMMA_TRAFFIC_BYTES = 1.203e9
 
 
+KERNEL_TRACE = {}
+
+
 def count_library_launches(step):
     """Runs `step` once under torch's kernel activity trace and returns how many of the launched kernels are this
-    library's (namespace rq::); 0 when no trace can be taken."""
+    library's (namespace rq::); 0 when no trace can be taken.  Leaves the ten kernels with the most device time of
+    that step in KERNEL_TRACE (name -> launches, milliseconds, share of all kernel time)."""
     try:
         from torch.profiler import ProfilerActivity, profile
         with profile(activities=[ProfilerActivity.CUDA]) as prof:
             step()
             torch.cuda.synchronize()
-        return sum(int(e.count) for e in prof.key_averages() if "rq::" in e.key)
+        rows = [(e.key, int(e.count), float(getattr(e, "device_time_total", 0.0) or getattr(e, "cuda_time_total", 0.0)))
+                for e in prof.key_averages() if "cuda" in str(getattr(e, "device_type", "cuda")).lower()]
+        total = sum(r[2] for r in rows) or 1.0
+        KERNEL_TRACE.clear()
+        for name, n, us in sorted(rows, key=lambda r: -r[2])[:10]:
+            short = name.split("(")[0].replace("void ", "")[:70]
+            KERNEL_TRACE[short] = {"launches": n, "ms": round(us / 1e3, 2), "share": round(us / total, 3)}
+        return sum(n for name, n, _ in rows if "rq::" in name)
     except Exception:
         step()
         return 0
@@ -704,6 +715,16 @@ def run_ours(args):
         barrier()
         return max_over_ranks([e0.elapsed_time(e1)])[0]
 
+    if args.profile_steps > 0:
+        # for profilers: exactly this many steps of the workload, nothing else (no timing, no CPU arm)
+        for _ in range(args.profile_steps):
+            wl.step_device()
+        torch.cuda.synchronize()
+        if rank == 0:
+            print(json.dumps({"profile_steps": args.profile_steps, "workload": wl.name, "schedule": wl.schedule}))
+        if world > 1:
+            torch.distributed.destroy_process_group()
+        return
     warm = max(args.warmup, 3)
     for _ in range(warm):
         wl.step_device()
@@ -789,6 +810,7 @@ def run_ours(args):
         "gpu_launches": (counted if counted else wl.launches_per_step()) * args.steps,
         "gpu_launches_source": ("kernels named rq::* in a CUPTI activity trace of one untimed step of the same workload"
                                 if counted else "counted from the host loops (no activity trace available)"),
+        "top_kernels_one_step": dict(KERNEL_TRACE) or None,   # CUPTI activity trace of the untimed extra step
         "clocks": clocks,
         "checksum": checksum,                          # sum over linears of mean |quantized weight| (rank 0's copy)
         "parity_vs_n1": parity,
@@ -1075,6 +1097,8 @@ def main():
                     help="N > 1: skip the comparison with a one-rank run of the same data")
     ap.add_argument("--schedule", default="sequential", choices=["sequential", "all_at_once"])
     ap.add_argument("--workload", default="c2", choices=["c2", "c3", "c4_down"])
+    ap.add_argument("--profile-steps", dest="profile_steps", type=int, default=0,
+                    help="c2: run exactly this many steps and exit (for a profiler's launch list)")
     ap.add_argument("--layers", type=int, default=36, help="c3: number of decoder layers")
     ap.add_argument("--c4-seqs", dest="c4_seqs", type=int, default=256, help="c4_down: calibration sequences in total")
     args = ap.parse_args()
