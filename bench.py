@@ -168,6 +168,9 @@ def count_library_launches(step):
         for name, n, us in sorted(rows, key=lambda r: -r[2])[:10]:
             short = name.split("(")[0].replace("void ", "")[:70]
             KERNEL_TRACE[short] = {"launches": n, "ms": round(us / 1e3, 2), "share": round(us / total, 3)}
+        if os.environ.get("REALQ_BENCH_DEBUG_TRACE"):
+            for name, n, us in sorted(rows, key=lambda r: -r[1])[:14]:
+                sys.stderr.write(f"trace {n:7d} {us / 1e3:9.2f} ms {name[:110]}\n")
         return sum(n for name, n, _ in rows if "rq::" in name)
     except Exception:
         step()
@@ -369,7 +372,10 @@ class LayerWorkload:
                 if self.fq_pool is None:
                     from concurrent.futures import ThreadPoolExecutor
                     self.fq_pool = ThreadPoolExecutor(max_workers=self.fq_streams)
-                    self.fq_stream_list = [torch.cuda.Stream() for _ in range(self.fq_streams)]
+                    # the first slot gets the longest job (a serial chain of short launches): its stream has the
+                    # higher priority, so that its next launch is never queued behind the other linears' kernels
+                    self.fq_stream_list = [torch.cuda.Stream(priority=-1 if i == 0 else 0)
+                                           for i in range(self.fq_streams)]
                 ready_ev = torch.cuda.Event()
                 ready_ev.record(main)
                 dev_index = self.dev.index

@@ -51,7 +51,9 @@ class _FqPool:
     def __init__(self, device, width):
         self.device = device
         self.pool = ThreadPoolExecutor(max_workers=width)
-        self.streams = [torch.cuda.Stream(device=device) for _ in range(width)]
+        # slot 0 runs the longest job, a serial chain of short launches: higher priority keeps its next launch from
+        # queueing behind the other linears' kernels
+        self.streams = [torch.cuda.Stream(device=device, priority=-1 if i == 0 else 0) for i in range(width)]
 
     def run(self, jobs):
         """jobs: callables in priority order (longest first); returns when they are all enqueued, the current stream
