@@ -168,9 +168,6 @@ def count_library_launches(step):
         for name, n, us in sorted(rows, key=lambda r: -r[2])[:10]:
             short = name.split("(")[0].replace("void ", "")[:70]
             KERNEL_TRACE[short] = {"launches": n, "ms": round(us / 1e3, 2), "share": round(us / total, 3)}
-        if os.environ.get("REALQ_BENCH_DEBUG_TRACE"):
-            for name, n, us in sorted(rows, key=lambda r: -r[1])[:14]:
-                sys.stderr.write(f"trace {n:7d} {us / 1e3:9.2f} ms {name[:110]}\n")
         return sum(n for name, n, _ in rows if "rq::" in name)
     except Exception:
         step()
