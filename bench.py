@@ -284,7 +284,12 @@ class LayerWorkload:
         main = torch.cuda.current_stream()
         spec = {name: (R, C, key) for name, R, C, key in self.LINEARS}
         checksum = torch.zeros((), device=self.dev)
-        for grp in self.groups():
+        # from the host every activation stream crosses PCIe once per step: a stream that a later module group
+        # consumes again (the hidden states feed [q, k, v] and [gate, up]) stays on the device in between
+        groups = self.groups()
+        uses = {k: sum(any(spec[nm][2] == k for nm in g) for g in groups) for k in ("hid", "attn", "mlp")}
+        kept = {}
+        for grp in groups:
             keys = [k for k in ("hid", "attn", "mlp") if any(spec[nm][2] == k for nm in grp)]
             objs = {}
             for name in grp:
@@ -311,9 +316,14 @@ class LayerWorkload:
                 got, evs = {}, {}
                 with torch.cuda.stream(self.copy_stream):
                     for key in keys:
+                        if (key, s) in kept:
+                            got[key], evs[key] = kept[(key, s)]
+                            continue
                         got[key] = inputs[key][s:s + self.BSZ].cuda(non_blocking=True)
                         evs[key] = torch.cuda.Event()
                         evs[key].record(self.copy_stream)
+                        if uses[key] > 1:
+                            kept[(key, s)] = (got[key], evs[key])
                 return got, evs
 
             nxt = fetch(0)
@@ -421,13 +431,9 @@ class LayerWorkload:
         return float(self._quantize(True).item())
 
     def h2d_bytes(self):
-        """Bytes copied from the host per step: every group's pass fetches the streams it consumes."""
+        """Bytes copied from the host per step: every activation stream once."""
         n = self.nseq_local * self.T
-        total = 0
-        for grp in self.groups():
-            keys = {key for name, _, _, key in self.LINEARS if name in grp}
-            total += sum(n * (self.INTER if k == "mlp" else self.HID) * 2 for k in keys)
-        return total
+        return sum(n * (self.INTER if k == "mlp" else self.HID) * 2 for k in ("hid", "attn", "mlp"))
 
     def launches_per_step(self):
         """Kernel launches of this library in one step on this rank, counted from the host loops (used where no

@@ -43,7 +43,6 @@ constexpr int kEpilogueWarps = 8;
 constexpr int kThreads = 64 + 32 * kEpilogueWarps;   // warp 0: TMA producer, warp 1: MMA issuer, warps 2-9: epilogue
 constexpr int kTmemCols = 512;   // two 128x256 fp32 accumulators
 constexpr int kWindowTokens = 128;   // tokens accumulated on the tensor core before a round-to-nearest add (default)
-constexpr int kPackTile = 64;    // pack kernel tile edge (tokens and channels)
 constexpr int kTopExp = 28;      // 2^E * (largest P_t of the chunk) lands in [2^28, 2^29)
 
 // NX = number of fp16 planes of X' (1 for bf16 / fp16 input, 2 for fp32 input); Y' always has two.
@@ -192,86 +191,108 @@ __device__ __forceinline__ float2 token_scales(float2 tk, int E) {
 // ------------------------------------------------------------------------------------------
 // pack
 // ------------------------------------------------------------------------------------------
+// (a, b) -> packed fp16 pair (one conversion instruction), a in the low half
 __device__ __forceinline__ uint32_t pair_f16(float a, float b) {
-    return (uint32_t)__half_as_ushort(__float2half_rn(a)) | ((uint32_t)__half_as_ushort(__float2half_rn(b)) << 16);
+    const __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<const uint32_t*>(&h);
 }
-__device__ __forceinline__ float round_f16(float v) { return __half2float(__float2half_rn(v)); }
+// hi = fp16(a, b) packed, (la, lb) = what the rounding left over (exact in fp32)
+__device__ __forceinline__ uint32_t split_pair_f16(float a, float b, float& la, float& lb) {
+    const __half2 h = __floats2half2_rn(a, b);
+    const float2 f = __half22float2(h);
+    la = a - f.x;
+    lb = b - f.y;
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
 
-// grid (Kc/64, ceil(C/64)), 256 threads: token tiles vary fastest, so that concurrently running blocks
-// extend the same plane rows (contiguous DRAM pages on the write side).
+// grid (ceil(Kc/128), ceil(C/32)), 256 threads: a block packs 128 tokens x 32 channels; token tiles vary fastest,
+// so that concurrently running blocks extend the same plane rows.  A lane owns four consecutive tokens: it reads
+// them from the channel-major shared tile as one 16-byte word and writes four fp16 values per plane as one 8-byte
+// word, 256 contiguous bytes per (plane, channel) and warp.
 // planes: [NX + 2G][C][Kc] fp16: X' (hi[, lo]) then per group Y' (hi, lo).
-// partial: [Kc/64][C] per-tile sums of x^2 (may be NULL).
+// partial: [ceil(Kc/128)][C] per-tile sums of x^2 (may be NULL).
+constexpr int kPackTokens = 128, kPackChannels = 32;
+
 template <typename T, int NX>
 __global__ void __launch_bounds__(256) pack_kernel(const T* __restrict__ x, int64_t ldx,
                                                    const float* __restrict__ sal, const float* __restrict__ aux,
                                                    const float2* __restrict__ tok, const unsigned int* __restrict__ pmax,
                                                    int nvalid, int C, int G, int Kc, uint16_t* __restrict__ planes,
                                                    float* __restrict__ partial) {
-    // channel-major tile: the write side (64 consecutive channels of one token per 64 threads) strides by the
-    // row length, the read side takes two adjacent tokens of one channel as one 8-byte word
-    __shared__ __align__(8) float xs[kPackTile][kPackTile + 2];
-    __shared__ float ss[kPackTile][8];
-    const int t0 = blockIdx.x * kPackTile;
-    const int c0 = blockIdx.y * kPackTile;
+    __shared__ __align__(16) float xs[kPackChannels][kPackTokens + 4];
+    __shared__ __align__(16) float ss[8][kPackTokens];         // saliencies, group-major
+    __shared__ __align__(16) float sx[kPackTokens];            // 2^a_t
+    __shared__ __align__(16) float sy[kPackTokens];            // 2^(E - a_t)
+    const int t0 = blockIdx.x * kPackTokens;
+    const int c0 = blockIdx.y * kPackChannels;
     const int tid = threadIdx.x;
-
-    {   // load: 64 consecutive channels of one token per pass of 64 threads
-        const int cc = tid & 63;
-        const int tr = tid >> 6;
-#pragma unroll 4
+    {   // load: 32 consecutive channels of one token per warp, eight tokens per pass; all sixteen loads of a thread
+        // are issued before the first is consumed
+        const int cc = tid & 31, tr = tid >> 5;
+        float v[16];
+#pragma unroll
         for (int p = 0; p < 16; ++p) {
-            const int t = p * 4 + tr;
-            float v = 0.f;
-            if (t0 + t < nvalid && c0 + cc < C) v = load_as_float<T>(x, (int64_t)(t0 + t) * ldx + c0 + cc);
-            xs[cc][t] = v;
+            const int t = p * 8 + tr;
+            v[p] = (t0 + t < nvalid && c0 + cc < C) ? load_as_float<T>(x, (int64_t)(t0 + t) * ldx + c0 + cc) : 0.f;
         }
-        for (int e = tid; e < kPackTile * 8; e += 256) {
-            const int t = e >> 3, g = e & 7;
-            float v = 0.f;
-            if (g < G && t0 + t < nvalid) v = (sal != nullptr) ? sal[(int64_t)(t0 + t) * G + g] : 1.f;
-            ss[t][g] = v;
+#pragma unroll
+        for (int p = 0; p < 16; ++p) xs[cc][p * 8 + tr] = v[p];
+        for (int e = tid; e < 8 * kPackTokens; e += 256) {
+            const int g = e >> 7, t = e & (kPackTokens - 1);
+            float sv = 0.f;
+            if (g < G && t0 + t < nvalid) sv = (sal != nullptr) ? sal[(int64_t)(t0 + t) * G + g] : 1.f;
+            ss[g][t] = sv;
+        }
+        if (tid < kPackTokens) {
+            const int E = chunk_exponent(*pmax);
+            const float2 tk = (t0 + tid < Kc) ? tok[t0 + tid] : make_float2(0.f, 0.f);
+            const float2 sc = token_scales(tk, E);
+            sx[tid] = sc.x;
+            sy[tid] = sc.y;
         }
     }
     __syncthreads();
 
     const int warp = tid >> 5, lane = tid & 31;
     const int64_t plane_stride = (int64_t)C * Kc;
-    const int ta = 2 * lane, tb = 2 * lane + 1;
-    const int E = chunk_exponent(*pmax);
-    const float2 sha = token_scales(tok[t0 + ta], E), shb = token_scales(tok[t0 + tb], E);
-    float sa[8], sb[8], da[8], db[8];                          // this lane's two tokens' saliencies and y scales
+    const int ta = 4 * lane;
+    const bool in_range = t0 + ta < Kc;                        // Kc is a multiple of 64: a group of four never straddles
+    const float4 ax = *reinterpret_cast<const float4*>(&sx[ta]);
+    const float4 ay = *reinterpret_cast<const float4*>(&sy[ta]);
+    float gn[8];
 #pragma unroll
-    for (int g = 0; g < 8; ++g) {
-        sa[g] = g < G ? ss[ta][g] : 0.f;
-        sb[g] = g < G ? ss[tb][g] : 0.f;
-        const float gn = g < G ? aux[g] : 0.f;
-        da[g] = sha.y * gn;                                    // powers of two: exact
-        db[g] = shb.y * gn;
-    }
-    for (int cc = warp; cc < kPackTile; cc += 8) {
+    for (int g = 0; g < 8; ++g) gn[g] = g < G ? aux[g] : 0.f;
+    for (int cc = warp; cc < kPackChannels; cc += 8) {
         const int c = c0 + cc;
         if (c >= C) break;                                     // warp-uniform
-        const float2 xab = *reinterpret_cast<const float2*>(&xs[cc][ta]);
-        const float xa = xab.x, xb = xab.y;
-        const int64_t off = (int64_t)c * Kc + t0 + ta;          // even -> 4-byte aligned pair
-        {
-            const float ra = xa * sha.x, rb = xb * shb.x;
-            *reinterpret_cast<uint32_t*>(planes + off) = pair_f16(ra, rb);
-            if (NX == 2)
-                *reinterpret_cast<uint32_t*>(planes + plane_stride + off) = pair_f16(ra - round_f16(ra), rb - round_f16(rb));
-        }
+        const float4 xv = *reinterpret_cast<const float4*>(&xs[cc][ta]);
+        const int64_t off = (int64_t)c * Kc + t0 + ta;          // multiple of 4 elements: 8-byte aligned
+        if (in_range) {
+            float l0, l1, l2, l3;
+            uint2 hi;
+            hi.x = split_pair_f16(xv.x * ax.x, xv.y * ax.y, l0, l1);        // exact scalings: powers of two
+            hi.y = split_pair_f16(xv.z * ax.z, xv.w * ax.w, l2, l3);
+            *reinterpret_cast<uint2*>(planes + off) = hi;
+            if (NX == 2) *reinterpret_cast<uint2*>(planes + plane_stride + off) = make_uint2(pair_f16(l0, l1), pair_f16(l2, l3));
 #pragma unroll
-        for (int g = 0; g < 8; ++g) {
-            if (g >= G) break;
-            // the reference's fp32 product x * s, then the exact scaling
-            const float ya = __fmul_rn(xa, sa[g]) * da[g];
-            const float yb = __fmul_rn(xb, sb[g]) * db[g];
-            *reinterpret_cast<uint32_t*>(planes + (NX + 2 * g) * plane_stride + off) = pair_f16(ya, yb);
-            *reinterpret_cast<uint32_t*>(planes + (NX + 2 * g + 1) * plane_stride + off) =
-                pair_f16(ya - round_f16(ya), yb - round_f16(yb));
+            for (int g = 0; g < 8; ++g) {
+                if (g >= G) break;
+                const float4 sg = *reinterpret_cast<const float4*>(&ss[g][ta]);
+                // the reference's fp32 product x * s, then the exact scaling
+                const float y0 = __fmul_rn(xv.x, sg.x) * (ay.x * gn[g]);
+                const float y1 = __fmul_rn(xv.y, sg.y) * (ay.y * gn[g]);
+                const float y2 = __fmul_rn(xv.z, sg.z) * (ay.z * gn[g]);
+                const float y3 = __fmul_rn(xv.w, sg.w) * (ay.w * gn[g]);
+                uint2 yh;
+                yh.x = split_pair_f16(y0, y1, l0, l1);
+                yh.y = split_pair_f16(y2, y3, l2, l3);
+                *reinterpret_cast<uint2*>(planes + (NX + 2 * g) * plane_stride + off) = yh;
+                *reinterpret_cast<uint2*>(planes + (NX + 2 * g + 1) * plane_stride + off) =
+                    make_uint2(pair_f16(l0, l1), pair_f16(l2, l3));
+            }
         }
         if (partial != nullptr) {
-            float sq = xa * xa + xb * xb;
+            float sq = (xv.x * xv.x + xv.y * xv.y) + (xv.z * xv.z + xv.w * xv.w);
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
             if (lane == 0) partial[(int64_t)blockIdx.x * C + c] = sq;
@@ -714,7 +735,7 @@ static void launch_pack(const void* xp, int64_t ldx, const float* sp, float* aux
     const T* x = reinterpret_cast<const T*>(xp);
     group_scale_kernel<<<1, 1024, 0, st>>>(sp, nvalid, G, aux, pmax);
     token_stats_kernel<T><<<(unsigned)((Kc + 7) / 8), 256, 0, st>>>(x, ldx, sp, aux, nvalid, (int)Kc, C, G, tok, pmax);
-    dim3 pgrid((unsigned)(Kc / kPackTile), (unsigned)((C + kPackTile - 1) / kPackTile));
+    dim3 pgrid((unsigned)((Kc + kPackTokens - 1) / kPackTokens), (unsigned)((C + kPackChannels - 1) / kPackChannels));
     pack_kernel<T, NX><<<pgrid, 256, 0, st>>>(x, ldx, sp, aux, tok, pmax, nvalid, C, G, (int)Kc, planes, partial);
 }
 
@@ -811,7 +832,7 @@ static int hessian_accum_impl(const void* x, int x_dtype, int64_t ldx, const flo
         rc = check_launch();
         if (rc != RQ_OK) break;
         if (act_sq) {
-            act_reduce_kernel<<<(C + 255) / 256, 256, 0, st>>>(partial, (int)(Kc / kPackTile), C, act_sq);
+            act_reduce_kernel<<<(C + 255) / 256, 256, 0, st>>>(partial, (int)((Kc + kPackTokens - 1) / kPackTokens), C, act_sq);
             rc = check_launch();
             if (rc != RQ_OK) break;
         }
