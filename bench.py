@@ -664,27 +664,27 @@ def reference_torch_path_on_gpu(dev):
         S = cases.make_saliency(nseq, T, G, seed=77).to(dev)
         Wt = cases.make_weight(R, C, seed=78).to(dev)
         Gr = cases.make_grad(R, C, seed=78).to(dev)
-        acc = ohess.GroupedHessian(C, S)
-        acc.H, acc.act_square = acc.H.to(dev), acc.act_square.to(dev)
-        for rep in range(2):                                             # second pass is the warm one
-            acc.H.zero_()
-            acc.act_square.zero_()
-            acc.index = acc.token_count = 0
+        with torch.device(dev):                                          # the port's own tensors are created here too
+            acc = ohess.GroupedHessian(C, S)
+            for rep in range(2):                                         # second pass is the warm one
+                acc.H.zero_()
+                acc.act_square.zero_()
+                acc.index = acc.token_count = 0
+                torch.cuda.synchronize()
+                t0 = time.perf_counter()
+                for s in range(0, nseq, 8):
+                    acc.add_batch(X[s:s + 8])
+                torch.cuda.synchronize()
+                t_h = time.perf_counter() - t0
+            acc.finalize()
+            q = oq.OracleWeightQuantizer()
+            q.configure(4, perchannel=True, sym=True)
             torch.cuda.synchronize()
             t0 = time.perf_counter()
-            for s in range(0, nseq, 8):
-                acc.add_batch(X[s:s + 8])
+            ogptq.plus_fasterquant(Wt, acc.H, acc.act_square, Gr, q, G, 0.25, 0.7, groupsize=128, actorder=True,
+                                   static_groups=True)
             torch.cuda.synchronize()
-            t_h = time.perf_counter() - t0
-        acc.finalize()
-        q = oq.OracleWeightQuantizer()
-        q.configure(4, perchannel=True, sym=True)
-        torch.cuda.synchronize()
-        t0 = time.perf_counter()
-        ogptq.plus_fasterquant(Wt, acc.H, acc.act_square, Gr, q, G, 0.25, 0.7, groupsize=128, actorder=True,
-                               static_groups=True)
-        torch.cuda.synchronize()
-        t_fq = time.perf_counter() - t0
+            t_fq = time.perf_counter() - t0
         return {"hessian_tflops": round(2.0 * nseq * T * C * C * G / t_h / 1e12, 1),
                 "hessian_ms_16seq_C4096_G4": round(t_h * 1e3, 1), "fasterquant_ms_1024x4096_G4": round(t_fq * 1e3, 1),
                 "what": "stock torch on this GPU with the reference's arithmetic (fp32 bmm, TF32 off; "

@@ -1,8 +1,10 @@
 """Weight quantizer on B200: the ``WeightQuantizer`` / STE interface of the reference's
 ``utils/quant_utils.py`` (:21-84, :300-486) over the ``rq_find_params`` / ``rq_quantize``
-kernels.  Names, arguments, buffer shapes and error behaviour follow the reference; the
-per-token grouped variant (``weight_groupsize > 0``, :333-388), which the GPTQ path never
-reaches, is not provided and raises.
+kernels, and the activation-side ``ActQuantizer`` / ``ActQuantWrapper`` (:87-297) over
+``rq_act_quant`` and the rotation kernels.  Names, arguments, buffer shapes and error behaviour
+follow the reference, including the grouped variant of the weight quantizer
+(``weight_groupsize > 0``, :333-388: ranges per row and column group in the weight's dtype, with
+or without the shrink-grid search).
 """
 from __future__ import annotations
 
