@@ -157,17 +157,23 @@ def _scale_setup(quantizer, W32, groupsize, static_groups, blocksize, perm, dead
         cols = perm if perm is not None else torch.arange(Cc, device=dev)
         colgrp = (cols // groupsize).to(torch.int32).contiguous()
         return 1, None, tab, colgrp, None, 0
-    # dynamic groups: ranged from the working block right before it is quantized
-    if groupsize != blocksize or BS % groupsize != 0:
+    # dynamic groups: ranged from the working matrix as it is at the start of the block a group begins in
+    # (gptq_utils/gptq_utils.py:123-128; gptq_plus_utils.py:1205-1209).  The kernels' block is 128 columns wide, so
+    # that state is reproduced when the reference's block is 128 wide too, or when every group starts at one of
+    # the reference's own block boundaries.
+    if blocksize != BS and groupsize % blocksize != 0:
         raise NotImplementedError(
-            f"dynamic weight groups are built for groupsize == blocksize == {BS}; got groupsize={groupsize}, "
-            f"blocksize={blocksize} (use static groups for other widths)")
-    if quantizer.mse:
-        raise NotImplementedError("dynamic weight groups with the shrink-grid search are not built")
+            f"dynamic weight groups are ranged from the weights at the start of the reference's block: blocksize "
+            f"must be {BS} or divide groupsize; got groupsize={groupsize}, blocksize={blocksize} (use static groups)")
     ng = (Cc + groupsize - 1) // groupsize
-    scale_blk = torch.zeros(ng, R, dtype=torch.float32, device=dev)
     colgrp = (torch.arange(Cc, device=dev) // groupsize).to(torch.int32).contiguous()
-    return 2, None, None, colgrp, scale_blk, groupsize
+    if BS % groupsize == 0 and not quantizer.mse:
+        scale_blk = torch.zeros(ng, R, dtype=torch.float32, device=dev)        # ranged inside the block kernel
+        return 2, None, None, colgrp, scale_blk, groupsize
+    # wider than a block, not a divisor of it, or with the shrink-grid search: the host ranges every group between
+    # two block launches (mode 3 = a table indexed by position that fills up as the blocks go by)
+    tab = torch.zeros(ng, R, dtype=torch.float32, device=dev)
+    return 3, None, tab, colgrp, None, groupsize
 
 
 # ----------------------------------------------------------------------------------------------
@@ -177,7 +183,8 @@ _INNER_MODES = {"frozen": 0, "surrogate_block": 1, "surrogate_online": 2}
 
 
 def _quantize_linear(layer, W32, H3, perm, grads, quantizer, G, alpha_eff, ref_loss, plus, Hinv, mode_pack,
-                     export_to_et, permute_export, rec=None, inner_mode=0, atomic=False, refresh=None, gd_pack=None):
+                     export_to_et, permute_export, rec=None, inner_mode=0, atomic=False, refresh=None, gd_pack=None,
+                     diag=None, diag_info=None):
     dev = W32.device
     R, Cc = W32.shape
     mode, scale_row, scale_tab, colgrp, scale_blk, dyn_gs = mode_pack
@@ -218,6 +225,8 @@ def _quantize_linear(layer, W32, H3, perm, grads, quantizer, G, alpha_eff, ref_l
                                                           float(ref_loss), _lib.ptr(Z), _lib.ptr(GH), _lib.ptr(beta),
                                                           _lib.ptr(hdiag), st))
         GH_initial = GH.clone() if (plus and KEEP_INTERMEDIATES) else None
+        if diag is not None:
+            _dump_subgroups(diag, diag_info or {}, Wp, Gp, Hinv, perm, G, plus, Z, GH, beta)
         if not plus:
             inner_mode = 0                      # beta = 0: the surrogate term vanishes
         # surrogate modes measure the drift of the weights from their values before the first block
@@ -226,6 +235,9 @@ def _quantize_linear(layer, W32, H3, perm, grads, quantizer, G, alpha_eff, ref_l
         codes = torch.empty(R, Cc, dtype=torch.int16, device=dev)
         Eeff = torch.empty(R, BS, dtype=torch.float32, device=dev)
         with _sec(rec, "fasterquant.block.total"):
+            if mode == 3 and (gd_pack is not None or refresh is not None):
+                raise NotImplementedError("block_backward / block_gd with dynamic weight groups that the host ranges "
+                                          "(shrink-grid search) are not built")
             if gd_pack is not None:
                 gd, gd_refresh, gd_groupsize, gd_static = gd_pack
                 _block_gd_loop(gd, gd_refresh, quantizer, W32, Wp, GH, Z, Hinv, Q, codes, Eeff, mode_pack, perm, G,
@@ -234,6 +246,9 @@ def _quantize_linear(layer, W32, H3, perm, grads, quantizer, G, alpha_eff, ref_l
                 beta, Z, GH = _block_backward_loop(
                     refresh, W32, Wp, GH, Z, beta, Hinv, Q, codes, Eeff, mode_pack, perm, G, alpha_eff, ref_loss,
                     plus, 1 if quantizer.sym else 0, maxq, atomic, st, rec)
+            elif mode == 3 or diag is not None:
+                _host_block_loop(quantizer, Wp, GH, Z, Hinv, Q, codes, Eeff, mode_pack, G, plus,
+                                 1 if quantizer.sym else 0, maxq, anchor, beta, inner_mode, atomic, st, rec, diag)
             elif tc:
                 _lib.check("rq_fq_run_tc",
                            _lib.lib.rq_fq_run_tc(_lib.ptr(Wp), _lib.ptr(GH), _lib.ptr(Z), _lib.ptr(Hinv), _lib.ptr(Q),
@@ -255,7 +270,7 @@ def _quantize_linear(layer, W32, H3, perm, grads, quantizer, G, alpha_eff, ref_l
         if export_to_et:
             out_codes = torch.empty(R, Cc, dtype=torch.float32, device=dev)
             out_scale = torch.empty(R, Cc, dtype=torch.float32, device=dev)
-        tab = scale_tab if mode == 1 else scale_blk
+        tab = scale_blk if mode == 2 else scale_tab
         with _sec(rec, "fasterquant.write_layer_weight"):
             _lib.check("rq_fq_finish",
                        _lib.lib.rq_fq_finish(_lib.ptr(Q), _lib.ptr(codes), _lib.ptr(perm), R, Cc, _lib.ptr(out),
@@ -266,7 +281,135 @@ def _quantize_linear(layer, W32, H3, perm, grads, quantizer, G, alpha_eff, ref_l
         layer.register_buffer("int_weight", out_codes.reshape(layer.weight.shape))
         layer.register_buffer("scale", out_scale)
     layer.weight.data = out
+    if diag is not None:                                        # gptq_plus_utils.py:1878-1881, natural column order
+        inv = torch.argsort(perm) if perm is not None else slice(None)
+        diag.save_module_level("Q_final", Q[:, inv])
+        diag.save_module_level("W_int_final", codes.float()[:, inv])
+        diag.save_module_level("Scale_final", _scale_matrix(mode_pack, R, Cc)[:, inv])
     return {"beta": beta, "Z": Z, "GHinv_initial": GH_initial}
+
+
+def _scale_matrix(mode_pack, R, Cc):
+    """[R, Cc] scale of every working-matrix position, from whichever source the block kernel used."""
+    mode, scale_row, scale_tab, colgrp, scale_blk, _ = mode_pack
+    if mode == 0:
+        return scale_row[:, None].expand(R, Cc)
+    tab = scale_blk if mode == 2 else scale_tab
+    return tab[colgrp.long()].t()
+
+
+def _dump_subgroups(diag, info, Wp, Gp, Hinv, perm, G, plus, Z, GH, beta):
+    """Per-subgroup snapshot for the tensor-dump recorder (gptq_plus_utils.py:1108-1121): the permuted weight and
+    gradient, both forms of the Hessian inverse and the first-order state before the first block."""
+    R, Cc = Wp.shape
+    rps = R // G
+    grads = Gp
+    if grads is None and info.get("gradients") is not None:
+        grads = info["gradients"] if perm is None else info["gradients"][:, perm]
+    identity = info.get("identity") or [False] * G
+    for g in range(G):
+        rows = slice(g * rps, (g + 1) * rps)
+        U = Hinv[g, :Cc, :Cc]
+        diag.save_subgroup(g, "W_sub_initial", Wp[rows].clone())
+        if grads is not None:
+            diag.save_subgroup(g, "gradients_sub", grads[rows].clone())
+        diag.save_subgroup(g, "H_sub_damped_but_original", None)
+        diag.save_subgroup(g, "Hinv_init", U.t() @ U)
+        diag.save_subgroup(g, "Hinv_upper_cholesky", U.clone())
+        diag.save_subgroup(g, "hessian_identity_fallback", torch.tensor(bool(identity[g])))
+        diag.save_subgroup(g, "beta", beta[rows].clone() if plus else torch.zeros(1, device=Wp.device))
+        diag.save_subgroup(g, "Z_initial", Z[rows].clone() if plus else torch.zeros_like(Wp[rows]))
+        diag.save_subgroup(g, "GHinv_initial", GH[rows].clone() if plus else torch.zeros_like(Wp[rows]))
+        diag.save_subgroup(g, "row_slice", torch.tensor([g * rps, (g + 1) * rps]))
+        if perm is not None:
+            diag.save_subgroup(g, "perm", perm)
+            diag.save_subgroup(g, "invperm", torch.argsort(perm))
+
+
+def _host_block_loop(quantizer, Wp, GH, Z, Hinv, Q, codes, Eeff, mode_pack, G, plus, sym, maxq, anchor, beta,
+                     inner_mode, atomic, st, rec, diag):
+    """The block loop with the host between the launches: one ``rq_fq_block`` and one ``rq_fq_lazy_update`` per 128
+    columns.  Used for what needs the working matrix between two blocks:
+
+    * dynamic weight groups that the block kernel cannot range itself (wider than a block, not a divisor of it, or
+      with the shrink-grid search): every group that begins inside ``[i1, i2)`` is ranged from ``Wp[:, c:c+groupsize]``
+      as it stands before the block is launched, i.e. from the values the reference's global ``W`` holds at that
+      point (gptq_utils/gptq_utils.py:123-128; gptq_plus_utils.py:1205-1209);
+    * the tensor-dump recorder (gptq_plus_utils.py:1215-1229, 1377-1387, 1526-1565): the block's inputs and outputs
+      and the terms of its outer update, per saliency group."""
+    dev = Wp.device
+    R, Cc = Wp.shape
+    mode, scale_row, scale_tab, colgrp, scale_blk, dyn_gs = mode_pack
+    kmode = 1 if mode == 3 else mode
+    rps = R // G
+    for i1 in range(0, Cc, BS):
+        count = min(BS, Cc - i1)
+        i2 = i1 + count
+        blk = i1 // BS
+        if mode == 3:
+            g0 = (i1 + dyn_gs - 1) // dyn_gs                       # groups that begin in [i1, i2)
+            g1 = (i2 + dyn_gs - 1) // dyn_gs
+            if g1 > g0:
+                with _sec(rec, "fasterquant.block.dynamic_find_params"):
+                    span = Wp[:, g0 * dyn_gs:min(Cc, g1 * dyn_gs)]
+                    tab, _ = quant_utils.find_params_groups(span, dyn_gs, maxq, quantizer.sym, quantizer.mse,
+                                                            quantizer.norm, quantizer.grid, quantizer.maxshrink)
+                    scale_tab[g0:g1] = tab
+        if diag is not None:
+            w_trailing_start = Wp[:, i2:].clone()
+            for g in range(G):
+                rows = slice(g * rps, (g + 1) * rps)
+                diag.save_block(g, blk, "W1_start", Wp[rows, i1:i2].clone())
+                diag.save_block(g, blk, "W_trailing_start", w_trailing_start[rows])
+                diag.save_block(g, blk, "Hinv1", Hinv[g, i1:i2, i1:i2].clone())
+                if plus:
+                    diag.save_block(g, blk, "GHinv1_at_block_start", GH[rows, i1:i2].clone())
+                    diag.save_block(g, blk, "Z1", Z[rows, i1:i2].clone())
+                diag.save_block(g, blk, "block_column_range", torch.tensor([i1, i2]))
+        with _sec(rec, "fasterquant.block.inner_loop"):
+            _lib.check("rq_fq_block",
+                       _lib.lib.rq_fq_block(_lib.ptr(Wp), _lib.ptr(GH), _lib.ptr(Z), _lib.ptr(Hinv), _lib.ptr(Q),
+                                            _lib.ptr(codes), _lib.ptr(Eeff), _lib.ptr(scale_row), _lib.ptr(scale_tab),
+                                            _lib.ptr(colgrp), _lib.ptr(scale_blk), R, Cc, G, i1, count, kmode, dyn_gs,
+                                            sym, maxq, 1 if plus else 0, _lib.ptr(anchor),
+                                            _lib.ptr(beta) if inner_mode else 0, int(inner_mode),
+                                            1 if (atomic and i2 < Cc) else 0, 1.0, st))
+        if diag is not None:
+            Dk = torch.arange(count - 1, -1, -1, device=dev, dtype=torch.float32)
+            err = Eeff[:, :count] + (Dk * Z[:, i1:i2] if plus else 0.0)         # the kernel keeps Err - D*Z
+            scale1 = _scale_matrix(mode_pack, R, Cc)[:, i1:i2]
+            for g in range(G):
+                rows = slice(g * rps, (g + 1) * rps)
+                far = Hinv[g, i1:i2, i2:Cc]
+                second = err[rows] @ far
+                diag.save_block(g, blk, "Q1", Q[rows, i1:i2].clone())
+                diag.save_block(g, blk, "W_int1", codes[rows, i1:i2].float())
+                diag.save_block(g, blk, "Scale1", scale1[rows].contiguous())
+                diag.save_block(g, blk, "Err1", err[rows].contiguous())
+                total = second
+                if plus:
+                    gh_rest = GH[rows, i2:].clone()
+                    einsum_term = (Z[rows, i1:i2] * Dk) @ far
+                    g_update = count * gh_rest - einsum_term
+                    total = second + g_update
+                    diag.save_block(g, blk, "GHinv_rest_at_outer", gh_rest)
+                    diag.save_block(g, blk, "count_times_GHinv_rest", count * gh_rest)
+                    diag.save_block(g, blk, "einsum_Z1_D_Hinv_term", einsum_term)
+                    diag.save_block(g, blk, "G_Update", g_update)
+                diag.save_block(g, blk, "second_order_update", second)
+                diag.save_block(g, blk, "total_outer_update", total)
+                diag.save_block(g, blk, "W_trailing_before_outer_update", w_trailing_start[rows])
+                diag.save_block(g, blk, "applied_second_order_update", second)
+        with _sec(rec, "fasterquant.block.outer_update_delta_w"):
+            _lib.check("rq_fq_lazy_update",
+                       _lib.lib.rq_fq_lazy_update(_lib.ptr(Wp), _lib.ptr(GH), _lib.ptr(Z), _lib.ptr(Eeff),
+                                                  _lib.ptr(Hinv), R, Cc, G, i1, count, 1 if plus else 0,
+                                                  _lib.ptr(anchor), _lib.ptr(beta) if inner_mode else 0,
+                                                  1 if inner_mode else 0, 1.0, st))
+        if diag is not None:
+            for g in range(G):
+                rows = slice(g * rps, (g + 1) * rps)
+                diag.save_block(g, blk, "W_trailing_after_outer_update", Wp[rows, i2:].clone())
 
 
 _OBSERVER_NONE_KEYS = (
@@ -753,8 +896,6 @@ def plain_fasterquant(obj, H, blocksize, percdamp, groupsize, actorder, static_g
     if actorder:
         key = torch.where(dead, torch.ones_like(diag), diag)
         perm = torch.argsort(key, descending=True)
-    if groupsize != -1 and not static_groups and (groupsize != blocksize):
-        raise NotImplementedError("plain GPTQ with dynamic groups is built for groupsize == blocksize")
     mode_pack = _scale_setup(obj.quantizer, W32, groupsize, static_groups, blocksize, perm, Wz)
     Hinv, _, _ = hinv_with_fallback(H3, perm, percdamp, identity_fallback=False)
     _quantize_linear(layer, W32, H3, perm, None, obj.quantizer, 1, 0.0, 0.0, False, Hinv, mode_pack,
@@ -848,8 +989,10 @@ def plus_fasterquant(obj, blocksize, percdamp, groupsize, actorder, static_group
         raise NotImplementedError(
             f"surrogate modes and block_atomic_quant depend on the block boundaries: blocksize must be {BS}, "
             f"got {blocksize}")
-    if diagnostic_recorder is not None:
-        raise NotImplementedError("the tensor-dump recorder needs the per-column intermediates of the PyTorch path")
+    diag = diagnostic_recorder
+    if diag is not None and (g_update_mode != "frozen" or block_atomic_quant or blocksize != BS):
+        raise NotImplementedError(f"the tensor-dump recorder is built for g_update_mode='frozen', blocksize={BS} and "
+                                  "no block_atomic_quant (its per-block tags follow the frozen outer update)")
     layer, dev = obj.layer, obj.dev
     rec = profile_recorder
     with _sec(rec, "fasterquant.allocate_outputs"):
@@ -877,6 +1020,25 @@ def plus_fasterquant(obj, blocksize, percdamp, groupsize, actorder, static_group
     if gd_mode:
         gd_pack = (gd, (gradient_refresh_fn, block_observer, bool(enable_gradient_update),
                         bool(refresh_full_metrics)), groupsize, static_groups)
+    sharded = (getattr(obj, "row_parallel", False) and obj._owned_groups is not None) or \
+        getattr(obj, "group_owners", None) is not None
+    if diag is not None:
+        if sharded:
+            raise NotImplementedError("the tensor-dump recorder sees every subgroup: run it without row_parallel / "
+                                      "group_owners")
+        # gptq_plus_utils.py:957-972
+        diag.save_module_level("original_weight_rotated", W32)
+        for tag in ("scale", "zero"):
+            if hasattr(obj.quantizer, tag):
+                diag.save_module_level(f"quantizer_{tag}", getattr(obj.quantizer, tag))
+        mq = obj.quantizer.maxq
+        diag.save_module_level("quantizer_maxq", mq if isinstance(mq, torch.Tensor) else torch.tensor(float(mq)))
+        diag.save_module_level("H_after_accumulate", obj.H)
+        diag.save_module_level("act_square", obj.act_square)
+        diag.save_module_level("gradients", obj.gradients)
+        diag.save_module_level("reference_loss", torch.tensor(obj.reference_loss))
+        diag.save_module_level("saliencies", obj.saliencies)
+        diag.save_module_level("alpha", torch.tensor(obj.alpha))
     if getattr(obj, "row_parallel", False) and obj._owned_groups is not None:
         if refresh is not None or gd_pack is not None:
             raise NotImplementedError(f"{g_update_mode} needs every row on one rank (the callback sees the whole "
@@ -899,6 +1061,9 @@ def plus_fasterquant(obj, blocksize, percdamp, groupsize, actorder, static_group
     state = _quantize_linear(layer, W32, H3, perm, grads, obj.quantizer, G, alpha_eff, obj.reference_loss, plus, Hinv,
                              mode_pack, export_to_et, permute_export=True, rec=rec,
                              inner_mode=_INNER_MODES.get(g_update_mode, 0), atomic=bool(block_atomic_quant),
-                             refresh=refresh, gd_pack=gd_pack)
+                             refresh=refresh, gd_pack=gd_pack, diag=diag,
+                             diag_info=None if diag is None else {
+                                 "identity": identity,
+                                 "gradients": None if obj.gradients is None else obj.gradients.to(dev).float()})
     obj._last_fasterquant = {"Hinv": Hinv if KEEP_INTERMEDIATES else None, "perm": perm, "damp_percent": damp,
                              "identity_fallback": identity, **state}

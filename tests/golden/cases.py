@@ -181,6 +181,12 @@ PLAIN_CASES = [
     ("plain_g64_static_act", 32, 256, 4, 96, 4, True, 64, True, True, 128),
     ("plain_g128_dynamic", 32, 256, 3, 96, 4, True, 128, False, False, 128),
     ("plain_ragged_block", 24, 200, 3, 80, 3, True, -1, True, True, 128),
+    # dynamic groups that do not coincide with the 128-column block ("mse" in the name: shrink-grid search on)
+    ("plain_g256_dynamic_act", 32, 512, 3, 96, 4, True, 256, True, False, 128),
+    ("plain_g96_dynamic", 24, 384, 3, 96, 4, False, 96, False, False, 128),
+    ("plain_g64_dynamic_act", 24, 256, 3, 96, 4, True, 64, True, False, 128),
+    ("plain_g64_dynamic_mse", 24, 256, 3, 96, 4, True, 64, False, False, 128),
+    ("plain_g256_dynamic_bs256", 32, 512, 3, 96, 4, True, 256, False, False, 256),
 ]
 
 PLUS_CASES = [

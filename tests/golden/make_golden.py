@@ -235,7 +235,7 @@ def gen_plain(qu, gu, out):
         layer = _Lin(W)
         g = gu.GPTQ(layer)
         g.quantizer = qu.WeightQuantizer()
-        g.quantizer.configure(bits, perchannel=True, sym=sym, mse=False)
+        g.quantizer.configure(bits, perchannel=True, sym=sym, mse="mse" in name)
         for s in range(nseq):
             g.add_batch(X[s:s + 1], None)
         out[f"{name}.digest"] = np.array(cases.digest(W, X))
@@ -347,6 +347,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--ref", default=os.environ.get("REALQ_REFERENCE_ROOT"), required="REALQ_REFERENCE_ROOT" not in os.environ,
                     help="checkout of the unmodified reference repository")
+    ap.add_argument("--only", nargs="*", default=None, help="regenerate just these files, e.g. plain_gptq.npz")
     args = ap.parse_args()
     torch.set_num_threads(1)                        # fixed reduction order on any host
     qu, hu, gu, gpu, gg, ga = import_reference(args.ref)
@@ -364,6 +365,8 @@ def main():
                             ("guided.npz", gen_guided, (qu, gg)),
                             ("gptaq.npz", gen_gptaq, (qu, ga)),
                             ("qk.npz", gen_qk, (import_reference.rotation_utils,))):
+        if args.only is not None and fname not in args.only:
+            continue
         out = {}
         with torch.no_grad():
             fn(*mods, out)

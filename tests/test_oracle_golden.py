@@ -79,7 +79,7 @@ def test_plain_gptq(golden, case):
     if f"{name}.H" in g:
         assert torch.equal(acc.H, t(g[f"{name}.H"]))
     q = oq.OracleWeightQuantizer()
-    q.configure(bits, perchannel=True, sym=sym, mse=False)
+    q.configure(bits, perchannel=True, sym=sym, mse="mse" in name)
     out = ogptq.plain_fasterquant(W, acc.H, q, blocksize=bs, percdamp=0.01, groupsize=gs, actorder=act,
                                   static_groups=static)
     assert torch.equal(out["W_int"], t(g[f"{name}.W_int"]).float())
