@@ -233,6 +233,11 @@ static int fwht_impl(const void* x, void* y, int dtype, int64_t rows, int n, int
     } else {                                                                                                       \
         e = cudaFuncSetAttribute(fwht_split_kernel<T, WW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
         if (e != cudaSuccess) return RQ_ERR_CUDA;                                                                  \
+        /* a grid-stride loop: no more CTAs than are resident at once, or the surplus would run as a tail */      \
+        int occ = 0;                                                                                               \
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, fwht_split_kernel<T, WW>, 32 * WW, smem) ==        \
+                cudaSuccess && occ > 0 && grid > (int64_t)sms0 * occ)                                              \
+            grid = (int64_t)sms0 * occ;                                                                            \
         fwht_split_kernel<T, WW><<<(unsigned)grid, 32 * WW, smem, st>>>(reinterpret_cast<const T*>(x),             \
                                                                         reinterpret_cast<T*>(y), nchunks, scale);  \
     }

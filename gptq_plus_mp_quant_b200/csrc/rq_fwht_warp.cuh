@@ -77,64 +77,116 @@ __device__ __forceinline__ void store8<__half>(__half* p, const float (&v)[8]) {
     *reinterpret_cast<uint4*>(p) = r;
 }
 
+// sm_100 issues fp32 additions two at a time on aligned register pairs (add.f32x2 / fma.f32x2).  Where a kernel is
+// short of issue slots the butterflies run on pairs (PACK), wherever both partners of two neighbouring registers
+// are themselves neighbours.  Each half is the same IEEE round-to-nearest operation as the scalar form: u - w is
+// computed as fma(w, -1, u), one rounding of the exact difference, so PACK changes no bit of the result.  It is
+// chosen per kernel by measurement (bf16, GB/s of read + write, scalar -> paired): chunks of 4096 in four warps
+// 4336 -> 4521, the 12-chunk mix 3795 -> 3992; the register pairs cost occupancy elsewhere (one warp per 1024-long
+// chunk 3702 -> 2597, the 28-chunk mix 3085 -> 2858), and those stay scalar.
+__device__ __forceinline__ float2 add2(float2 u, float2 w) { return __fadd2_rn(u, w); }
+__device__ __forceinline__ float2 sub2(float2 u, float2 w) { return __ffma2_rn(w, make_float2(-1.f, -1.f), u); }
+__device__ __forceinline__ void bfly2(float& u0, float& u1, float& w0, float& w1) {
+    const float2 u = make_float2(u0, u1), w = make_float2(w0, w1);
+    const float2 s = add2(u, w), d = sub2(u, w);
+    u0 = s.x; u1 = s.y; w0 = d.x; w1 = d.y;
+}
+
 // butterfly over register-index bit RB of a[E]
-template <int E, int RB>
+template <int E, int RB, bool PACK>
 __device__ __forceinline__ void reg_butterfly(float (&a)[E]) {
+    if (!PACK) {
 #pragma unroll
-    for (int r = 0; r < E; ++r) {
-        if ((r & (1 << RB)) == 0) {
-            const float u = a[r], w = a[r | (1 << RB)];
-            a[r] = u + w;
-            a[r | (1 << RB)] = u - w;
+        for (int r = 0; r < E; ++r) {
+            if ((r & (1 << RB)) == 0) {
+                const float u = a[r], w = a[r | (1 << RB)];
+                a[r] = u + w;
+                a[r | (1 << RB)] = u - w;
+            }
         }
+    } else if (RB == 0) {
+#pragma unroll
+        for (int r = 0; r < E; r += 2) {
+            const float u = a[r], w = a[r + 1];
+            a[r] = u + w;
+            a[r + 1] = u - w;
+        }
+    } else {
+#pragma unroll
+        for (int r = 0; r < E; r += 2)
+            if ((r & (1 << RB)) == 0) bfly2(a[r], a[r + 1], a[r | (1 << RB)], a[(r | (1 << RB)) + 1]);
     }
 }
 
-template <int E, int RB, int LOG2E>
+template <int E, int RB, int LOG2E, bool PACK>
 struct PhaseA {   // register bit rb <-> index bit rb (rb < 3) or rb + 5 (rb >= 3)
     static __device__ __forceinline__ void run(float (&a)[E], int m) {
-        if ((RB < 3 ? RB : RB + 5) < m) reg_butterfly<E, RB>(a);
-        PhaseA<E, RB + 1, LOG2E>::run(a, m);
+        if ((RB < 3 ? RB : RB + 5) < m) reg_butterfly<E, RB, PACK>(a);
+        PhaseA<E, RB + 1, LOG2E, PACK>::run(a, m);
     }
 };
-template <int E, int LOG2E>
-struct PhaseA<E, LOG2E, LOG2E> {
+template <int E, int LOG2E, bool PACK>
+struct PhaseA<E, LOG2E, LOG2E, PACK> {
     static __device__ __forceinline__ void run(float (&)[E], int) {}
 };
 
-template <int E, int CB, int LOG2V>
+template <int E, int CB, int LOG2V, bool PACK>
 struct PhaseB {   // register bit LOG2V + cb <-> index bit 3 + cb, cb < 5
     static __device__ __forceinline__ void run(float (&a)[E], int m) {
-        if (3 + CB < m) reg_butterfly<E, LOG2V + CB>(a);
-        PhaseB<E, CB + 1, LOG2V>::run(a, m);
+        if (3 + CB < m) reg_butterfly<E, LOG2V + CB, PACK>(a);
+        PhaseB<E, CB + 1, LOG2V, PACK>::run(a, m);
     }
 };
-template <int E, int LOG2V>
-struct PhaseB<E, 5, LOG2V> {
+template <int E, int LOG2V, bool PACK>
+struct PhaseB<E, 5, LOG2V, PACK> {
     static __device__ __forceinline__ void run(float (&)[E], int) {}
 };
 
-// Transform the super-chunk that starts at element `base` of src (elements at or beyond `total` read as 0);
-// the result is left in `wbuf` (this warp's slice) at wphys(natural index).
-template <typename T, int LOGS>
-__device__ __forceinline__ void warp_transform(const T* __restrict__ src, int64_t base, int64_t total, int m,
-                                               float* wbuf, int lane) {
-    constexpr int S = 1 << LOGS, E = S / 32, LOG2E = LOGS - 5, J = E / 8, V = E / 32, LOG2V = LOG2E - 5;
-    float a[E];
+// The J pieces of 8 consecutive elements a lane loads of a super-chunk, still in the I/O type: loading them into
+// registers ahead of the transform that will use them keeps more global loads in flight per warp.
+template <typename T, int J>
+struct RawChunk {
+    uint4 v[J];
+    __device__ __forceinline__ void load(const T* __restrict__ src, int lane) {
 #pragma unroll
-    for (int j = 0; j < J; ++j) {
-        const int idx = j * 256 + lane * 8;
-        float v[8];
-        if (base + idx + 8 <= total) {
-            load8<T>(src + base + idx, v);
-        } else {
-#pragma unroll
-            for (int e = 0; e < 8; ++e) v[e] = (base + idx + e < total) ? load_as_float<T>(src, base + idx + e) : 0.f;
-        }
-#pragma unroll
-        for (int e = 0; e < 8; ++e) a[j * 8 + e] = v[e];
+        for (int j = 0; j < J; ++j) v[j] = *reinterpret_cast<const uint4*>(src + j * 256 + lane * 8);
     }
-    PhaseA<E, 0, LOG2E>::run(a, m);
+    template <int E>
+    __device__ __forceinline__ void unpack(float (&a)[E]) const {
+#pragma unroll
+        for (int j = 0; j < J; ++j) {
+            float t[8];
+            load8<T>(reinterpret_cast<const T*>(&v[j]), t);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) a[j * 8 + e] = t[e];
+        }
+    }
+};
+template <int J>
+struct RawChunk<float, J> {
+    float4 v[2 * J];
+    __device__ __forceinline__ void load(const float* __restrict__ src, int lane) {
+#pragma unroll
+        for (int j = 0; j < J; ++j) {
+            v[2 * j] = *reinterpret_cast<const float4*>(src + j * 256 + lane * 8);
+            v[2 * j + 1] = *reinterpret_cast<const float4*>(src + j * 256 + lane * 8 + 4);
+        }
+    }
+    template <int E>
+    __device__ __forceinline__ void unpack(float (&a)[E]) const {
+#pragma unroll
+        for (int j = 0; j < 2 * J; ++j) {
+            a[j * 4] = v[j].x; a[j * 4 + 1] = v[j].y; a[j * 4 + 2] = v[j].z; a[j * 4 + 3] = v[j].w;
+        }
+    }
+};
+
+// Transform the super-chunk held in a[] (lane l: elements j*256 + l*8 .. +7 in a[8j .. 8j+7]); the result is left
+// in `wbuf` (this warp's slice) at wphys(natural index).
+template <int LOGS, bool PACK = false>
+__device__ __forceinline__ void warp_transform_loaded(float (&a)[(1 << LOGS) / 32], int m, float* wbuf, int lane) {
+    constexpr int S = 1 << LOGS, E = S / 32, LOG2E = LOGS - 5, J = E / 8, V = E / 32, LOG2V = LOG2E - 5;
+    PhaseA<E, 0, LOG2E, PACK>::run(a, m);
 #pragma unroll
     for (int j = 0; j < J; ++j) {
         float* p = wbuf + wphys(j * 256 + lane * 8);
@@ -160,7 +212,7 @@ __device__ __forceinline__ void warp_transform(const T* __restrict__ src, int64_
             b[c] = *p;
         }
     }
-    PhaseB<E, 0, LOG2V>::run(b, m);
+    PhaseB<E, 0, LOG2V, PACK>::run(b, m);
 #pragma unroll
     for (int c = 0; c < 32; ++c) {
         float* p = wbuf + wphys(off + c * 8);
@@ -169,6 +221,28 @@ __device__ __forceinline__ void warp_transform(const T* __restrict__ src, int64_
         else *p = b[c];
     }
     __syncwarp();
+}
+
+// Transform the super-chunk that starts at element `base` of src (elements at or beyond `total` read as 0).
+template <typename T, int LOGS, bool PACK = false>
+__device__ __forceinline__ void warp_transform(const T* __restrict__ src, int64_t base, int64_t total, int m,
+                                               float* wbuf, int lane) {
+    constexpr int S = 1 << LOGS, E = S / 32, J = E / 8;
+    float a[E];
+#pragma unroll
+    for (int j = 0; j < J; ++j) {
+        const int idx = j * 256 + lane * 8;
+        float v[8];
+        if (base + idx + 8 <= total) {
+            load8<T>(src + base + idx, v);
+        } else {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[e] = (base + idx + e < total) ? load_as_float<T>(src, base + idx + e) : 0.f;
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) a[j * 8 + e] = v[e];
+    }
+    warp_transform_loaded<LOGS, PACK>(a, m, wbuf, lane);
 }
 
 // K == 1: every warp transforms super-chunks independently and writes them back with 16-byte stores.
@@ -287,14 +361,21 @@ __global__ void __launch_bounds__(32 * W) fwht_split_kernel(const T* __restrict_
                                                             int64_t nchunks, float scale, RowQuant rq = RowQuant()) {
     constexpr int S = 1024;
     constexpr int slice = warp_slice_floats(S);
+    constexpr bool PACK = W <= 4;                               // paired additions (see add2)
     extern __shared__ float wsm[];
     __shared__ float red[64];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int64_t total = nchunks * (int64_t)(W * S);
+    // every chunk is complete (total = nchunks * W * S), so a warp's quarter is loaded without bounds checks, one
+    // grid stride ahead of the transform that consumes it
+    RawChunk<T, 4> ahead;
+    if ((int64_t)blockIdx.x < nchunks) ahead.load(x + (int64_t)blockIdx.x * (W * S) + (int64_t)warp * S, lane);
     for (int64_t ch = blockIdx.x; ch < nchunks; ch += gridDim.x) {
         const int64_t base = ch * (int64_t)(W * S);
+        float a[32];
+        ahead.unpack(a);
+        if (ch + gridDim.x < nchunks) ahead.load(x + (ch + gridDim.x) * (int64_t)(W * S) + (int64_t)warp * S, lane);
         __syncthreads();                                        // previous chunk fully written out
-        warp_transform<T, 10>(x, base + (int64_t)warp * S, total, 10, wsm + warp * slice, lane);
+        warp_transform_loaded<10, PACK>(a, 10, wsm + warp * slice, lane);
         __syncthreads();
         // thread t handles positions 8t .. 8t+7 of every slice (W * 32 threads cover 1024 positions when W = 4;
         // other W loop)
@@ -314,18 +395,32 @@ __global__ void __launch_bounds__(32 * W) fwht_split_kernel(const T* __restrict_
 #pragma unroll
                 for (int w = 0; w < W; ++w)
                     if ((w & h) == 0) {
+                        if (PACK) {
 #pragma unroll
-                        for (int e = 0; e < 8; ++e) {
-                            const float a = v[w][e], b = v[w | h][e];
-                            v[w][e] = a + b;
-                            v[w | h][e] = a - b;
+                            for (int e = 0; e < 8; e += 2) bfly2(v[w][e], v[w][e + 1], v[w | h][e], v[w | h][e + 1]);
+                        } else {
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) {
+                                const float a = v[w][e], b = v[w | h][e];
+                                v[w][e] = a + b;
+                                v[w | h][e] = a - b;
+                            }
                         }
                     }
 #pragma unroll
             for (int w = 0; w < W; ++w) {
                 float o[8];
+                if (PACK) {
 #pragma unroll
-                for (int e = 0; e < 8; ++e) o[e] = v[w][e] * scale;
+                    for (int e = 0; e < 8; e += 2) {
+                        const float2 t = __fmul2_rn(make_float2(v[w][e], v[w][e + 1]), make_float2(scale, scale));
+                        o[e] = t.x;
+                        o[e + 1] = t.y;
+                    }
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) o[e] = v[w][e] * scale;
+                }
                 if (QUANT) {                                    // back into place, rounded as a store would round
 #pragma unroll
                     for (int e = 0; e < 8; ++e) {
@@ -440,6 +535,27 @@ __device__ __forceinline__ void mix_fixed(const float (&v)[K], float (&y)[K]) {
     }
 }
 
+// the same mix on two neighbouring positions at once (.x and .y), every addition as one paired instruction
+template <int K>
+__device__ __forceinline__ void mix_fixed2(const float2 (&v)[K], float2 (&y)[K]) {
+    constexpr int NQ = K / 4;
+#pragma unroll
+    for (int q = 0; q < NQ; ++q) {
+        const float2 ab0 = add2(v[4 * q], v[4 * q + 1]), ab1 = sub2(v[4 * q], v[4 * q + 1]);
+        const float2 cd0 = add2(v[4 * q + 2], v[4 * q + 3]), cd1 = sub2(v[4 * q + 2], v[4 * q + 3]);
+        const float2 c[8] = {add2(ab0, cd0), add2(ab1, cd0), sub2(ab0, cd0), sub2(ab1, cd0),
+                             add2(ab0, cd1), add2(ab1, cd1), sub2(ab0, cd1), sub2(ab1, cd1)};
+#pragma unroll
+        for (int r = 0; r < K; ++r) {
+            const uint32_t bits = (had_row<K>(r) >> (4 * q)) & 15u;
+            const bool s0 = bits & 1u, s1 = bits & 2u, s2 = bits & 4u, s3 = bits & 8u;
+            const int idx = (s1 != s0 ? 1 : 0) | (s2 != s0 ? 2 : 0) | (s3 != s2 ? 4 : 0);
+            const float2 t = c[idx];
+            y[r] = (q == 0) ? (s0 ? t : make_float2(-t.x, -t.y)) : (s0 ? add2(y[r], t) : sub2(y[r], t));
+        }
+    }
+}
+
 // true in every thread when the K x K matrix in shared memory is the tabulated one of that order
 template <int K>
 __device__ __forceinline__ bool matches_table(const float* hk) {
@@ -459,24 +575,20 @@ __device__ __forceinline__ bool matches_table(const float* hk) {
 template <typename T, int K, bool QUANT>
 __device__ __forceinline__ void mix_pair_fixed(float* buf, int slice, int p, int P, T* yrow, float scale, float* lo,
                                                float* hi) {
-    float v0[K], v1[K], y0[K], y1[K];
+    float2 v[K], y[K];
+#pragma unroll
+    for (int k = 0; k < K; ++k) v[k] = *reinterpret_cast<const float2*>(buf + k * slice + wphys(p));
+    mix_fixed2<K>(v, y);
 #pragma unroll
     for (int k = 0; k < K; ++k) {
-        const float2 t = *reinterpret_cast<const float2*>(buf + k * slice + wphys(p));
-        v0[k] = t.x;
-        v1[k] = t.y;
-    }
-    mix_fixed<K>(v0, y0);
-    mix_fixed<K>(v1, y1);
-#pragma unroll
-    for (int k = 0; k < K; ++k) {
+        const float2 o = __fmul2_rn(y[k], make_float2(scale, scale));
         if (QUANT) {
-            const float r0 = round_io<T>(y0[k] * scale), r1 = round_io<T>(y1[k] * scale);
+            const float r0 = round_io<T>(o.x), r1 = round_io<T>(o.y);
             *lo = fminf(*lo, fminf(r0, r1));
             *hi = fmaxf(*hi, fmaxf(r0, r1));
             *reinterpret_cast<float2*>(buf + k * slice + wphys(p)) = make_float2(r0, r1);
         } else {
-            store2<T>(yrow + (int64_t)k * P + p, y0[k] * scale, y1[k] * scale);
+            store2<T>(yrow + (int64_t)k * P + p, o.x, o.y);
         }
     }
 }
@@ -525,6 +637,7 @@ __global__ void __launch_bounds__(32 * WARPS, (KMAX <= 12 && LOGS == 10) ? 4 : 1
                                                                      RowQuant rq = RowQuant()) {
     constexpr int S = 1 << LOGS;
     constexpr int slice = warp_slice_floats(S);
+    constexpr bool PACK = KMAX <= 12 && LOGS == 10;             // paired additions (see add2)
     extern __shared__ float wsm[];
     __shared__ float red[64];
     float* hk = wsm + (size_t)K * slice;
@@ -539,8 +652,27 @@ __global__ void __launch_bounds__(32 * WARPS, (KMAX <= 12 && LOGS == 10) ? 4 : 1
     const int64_t n = (int64_t)K * S;
     for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
         __syncthreads();                                        // previous row's mix has finished reading
-        for (int c = warp; c < K; c += WARPS)
-            warp_transform<T, LOGS>(x, row * n + (int64_t)c * S, (rows * n), LOGS, wsm + (size_t)c * slice, lane);
+        if (LOGS == 10 && sizeof(T) == 2 && KMAX > 12) {
+            // rows are complete: a warp issues the loads of its next two chunks before it transforms the first
+            // (bf16, n = 28672: 2.53 -> 2.77 TB/s; the 12-chunk kernel, short of registers, lost with it: 3.99 -> 3.69)
+            for (int c = warp; c < K; c += 2 * WARPS) {
+                RawChunk<T, (1 << LOGS) / 256> r0, r1;
+                const bool two = c + WARPS < K;
+                r0.load(x + row * n + (int64_t)c * S, lane);
+                if (two) r1.load(x + row * n + (int64_t)(c + WARPS) * S, lane);
+                float a[(1 << LOGS) / 32];
+                r0.unpack(a);
+                warp_transform_loaded<LOGS, PACK>(a, LOGS, wsm + (size_t)c * slice, lane);
+                if (two) {
+                    r1.unpack(a);
+                    warp_transform_loaded<LOGS, PACK>(a, LOGS, wsm + (size_t)(c + WARPS) * slice, lane);
+                }
+            }
+        } else {
+            for (int c = warp; c < K; c += WARPS)
+                warp_transform<T, LOGS, PACK>(x, row * n + (int64_t)c * S, (rows * n), LOGS, wsm + (size_t)c * slice,
+                                              lane);
+        }
         __syncthreads();
         T* yrow = y + row * n;
         float lo = 0.f, hi = 0.f;
