@@ -647,6 +647,27 @@ def run_reference(args):
         "e2e": {"value": round(v, 2), "unit": "s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
 
 
+def fwht_alone_gbs(dev, lengths=(4096, 12288), rows=16384, reps=10):
+    """Achieved GB/s (bytes read + written) of the online rotation on its own, per row length of this workload, bf16,
+    one batch of 8 x 2048 tokens per call: outside the timed region, at whatever clock the idle GPU boosts to (inside
+    a step the same kernels run under the power cap of the Hessian contraction, see fwht_gbs)."""
+    from gptq_plus_mp_quant_b200.utils import hadamard_utils as hu
+    out = {}
+    for n in lengths:
+        x = torch.randn(rows, n, device=dev).to(torch.bfloat16)
+        hadK, K = hu.get_hadK(n)
+        for _ in range(3):
+            hu.matmul_hadU_cuda(x, hadK, K)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            hu.matmul_hadU_cuda(x, hadK, K)
+        e1.record()
+        torch.cuda.synchronize(dev)
+        out[str(n)] = round(2.0 * x.numel() * 2 * reps / (e0.elapsed_time(e1) * 1e-3) / 1e9, 1)
+    return out
+
+
 def reference_torch_path_on_gpu(dev):
     """Informative only: the reference's arithmetic as stock torch calls on this GPU (the oracle port with CUDA
     tensors: fp32 bmm with TF32 off, torch.linalg.cholesky / cholesky_inverse, the per-column Python loop) for ONE
@@ -835,6 +856,8 @@ def run_ours(args):
                                "c0_note": "configs[0] (plain GPTQ, 4096 x 4096, 32 x 2048 fp32 tokens) run in full on "
                                           "the host cores, nothing extrapolated"}
         out["reference_torch_path_on_this_gpu"] = reference_torch_path_on_gpu(dev)
+    if rank == 0 and world == 1:
+        out["fwht_alone_gbs_bf16"] = fwht_alone_gbs(dev)
     if rank == 0:
         print(json.dumps(out))
     if world > 1:

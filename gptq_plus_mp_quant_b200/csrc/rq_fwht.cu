@@ -285,31 +285,36 @@ static int fwht_impl(const void* x, void* y, int dtype, int64_t rows, int n, int
 #undef RQ_WARP_LAUNCH
             return check_launch();
         }
-        const size_t smem = ((size_t)K * warp_slice_floats(S) + (size_t)K * K) * sizeof(float);
+        const bool swz = mix_swizzled(logs, K <= 12 ? 12 : 28, rqp != nullptr);     // as the kernel chosen below
+        const size_t smem = ((size_t)K * warp_slice_floats(S, swz) + (mix_matrix_shared(K, swz) ? (size_t)K * K : 0)) *
+                            sizeof(float);
         if (smem <= 220 * 1024) {
-            int per_sm = (int)((220 * 1024) / (smem + 1024));
-            if (per_sm < 1) per_sm = 1;
-            int64_t grid = rows < (int64_t)sms0 * per_sm ? rows : (int64_t)sms0 * per_sm;
+            int64_t grid = rows;
+            // one row per CTA and a grid-stride loop: as many CTAs as are resident at once (two per SM up to K = 28 at
+            // S = 1024, which needs the whole shared-memory carve-out)
+#define RQ_MIX_GO(KERNEL, THREADS, ...)                                                                           \
+    {                                                                                                              \
+        auto kfn = KERNEL;                                                                                         \
+        e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                     \
+        if (e != cudaSuccess) return RQ_ERR_CUDA;                                                                  \
+        cudaFuncSetAttribute(kfn, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared); \
+        int occ = 0;                                                                                               \
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kfn, THREADS, smem) != cudaSuccess || occ < 1)     \
+            occ = 1;                                                                                               \
+        if (grid > (int64_t)sms0 * occ) grid = (int64_t)sms0 * occ;                                                \
+        kfn<<<(unsigned)grid, THREADS, smem, st>>>(__VA_ARGS__);                                                   \
+    }
 #define RQ_MIX_LAUNCH(T, L)                                                                                       \
     if (rqp) {                                                                                                     \
-        e = cudaFuncSetAttribute(fwht_mix_kernel<T, L, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,         \
-                                 (int)smem);                                                                       \
-        if (e != cudaSuccess) return RQ_ERR_CUDA;                                                                  \
-        fwht_mix_kernel<T, L, true><<<(unsigned)grid, 32 * kMixWarps, smem, st>>>(                                 \
-            reinterpret_cast<const T*>(x), reinterpret_cast<T*>(y), rows, K, hadK, scale, *rqp);                   \
+        RQ_MIX_GO((fwht_mix_kernel<T, L, true>), 32 * kMixWarps, reinterpret_cast<const T*>(x),                    \
+                  reinterpret_cast<T*>(y), rows, K, hadK, scale, *rqp)                                             \
     } else if (K <= 12) {                                                                                          \
-        e = cudaFuncSetAttribute(fwht_mix_kernel<T, L, false, 12, RQ_MIX12_WARPS>,                                 \
-                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                          \
-        if (e != cudaSuccess) return RQ_ERR_CUDA;                                                                  \
-        fwht_mix_kernel<T, L, false, 12, RQ_MIX12_WARPS><<<(unsigned)grid, 32 * RQ_MIX12_WARPS, smem, st>>>(       \
-            reinterpret_cast<const T*>(x), reinterpret_cast<T*>(y), rows, K, hadK, scale);                         \
+        RQ_MIX_GO((fwht_mix_kernel<T, L, false, 12, RQ_MIX12_WARPS>), 32 * RQ_MIX12_WARPS,                         \
+                  reinterpret_cast<const T*>(x), reinterpret_cast<T*>(y), rows, K, hadK, scale, RowQuant())        \
     } else {                                                                                                       \
-        e = cudaFuncSetAttribute(fwht_mix_kernel<T, L, false, 28, (L == 10 ? RQ_MIX28_WARPS : kMixWarps)>,                               \
-                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                          \
-        if (e != cudaSuccess) return RQ_ERR_CUDA;                                                                  \
-        fwht_mix_kernel<T, L, false, 28, (L == 10 ? RQ_MIX28_WARPS : kMixWarps)>                                   \
-            <<<(unsigned)grid, 32 * (L == 10 ? RQ_MIX28_WARPS : kMixWarps), smem, st>>>(                           \
-            reinterpret_cast<const T*>(x), reinterpret_cast<T*>(y), rows, K, hadK, scale);                         \
+        RQ_MIX_GO((fwht_mix_kernel<T, L, false, 28, (L == 10 ? RQ_MIX28_WARPS : kMixWarps)>),                      \
+                  32 * (L == 10 ? RQ_MIX28_WARPS : kMixWarps), reinterpret_cast<const T*>(x),                      \
+                  reinterpret_cast<T*>(y), rows, K, hadK, scale, RowQuant())                                       \
     }
 #define RQ_MIX_DISPATCH(T)                                  \
     if (logs == 10) { RQ_MIX_LAUNCH(T, 10); }               \
@@ -321,6 +326,7 @@ static int fwht_impl(const void* x, void* y, int dtype, int64_t rows, int n, int
             else return RQ_ERR_INVALID;
 #undef RQ_MIX_DISPATCH
 #undef RQ_MIX_LAUNCH
+#undef RQ_MIX_GO
             return check_launch();
         }
     }

@@ -4,8 +4,8 @@
 // short ones) and keeps it in registers, E = S/32 per lane:
 //   load   lane l reads 8 consecutive elements (16 B for bf16/fp16) at j*256 + l*8, j < E/8;
 //   phase A  butterflies over the index bits that are thread-local in this mapping (0-2 and 8+);
-//   transposition through the warp's private shared-memory slice (128-bit accesses, 8 padding words
-//            per 256 keep every access conflict free) so that index bits 3-7 become thread-local;
+//   transposition through the warp's private shared-memory slice (128-bit accesses, an XOR swizzle of the
+//            256-element blocks keeps every access conflict free) so that index bits 3-7 become thread-local;
 //   phase B  butterflies over bits 3-7; the result goes back to the same shared-memory slots.
 // About 16 instructions per element instead of the ~50 of a shared-memory radix pass design, which is
 // what an HBM-bound kernel can afford at 6.5 TB/s.  The K x K mix (n = K * 2^m) runs per row from shared memory.
@@ -18,10 +18,21 @@ namespace rq {
 namespace fwht {
 
 constexpr int kWarpsPerCta = 4;
+constexpr int kMixSharedMatrixMaxK = 24;
+// which mix kernels use the unpadded, swizzled slices, and whether the caller's K x K matrix is copied behind them
+__host__ __device__ constexpr bool mix_swizzled(int logs, int kmax, bool quant) { return logs == 10 && kmax > 12 && !quant; }
+__host__ __device__ constexpr bool mix_matrix_shared(int K, bool swz) { return !swz || K <= kMixSharedMatrixMaxK; }
 constexpr int kMixWarps = 8;          // warps of a CTA that transforms and mixes one row (n = K * 2^m, K > 1)
 
-__device__ __forceinline__ int wphys(int idx) { return idx + ((idx >> 8) << 3); }
-__host__ __device__ constexpr int warp_slice_floats(int S) { return S + (S >> 8) * 8; }
+// Position of natural index idx inside a slice.  Two layouts keep the four (or more) 256-element blocks a warp
+// touches in the second mapping on different banks: 8 padding words per 256 elements (addresses stay base + constant,
+// which costs the fewest registers), or, SWZ, bits 3-4 XORed with bits 8-9 (no padding: 28 slices of 1024 floats are
+// 112 KB, so that two rows fit an SM's shared memory).  Both keep aligned groups of 8 elements together.
+template <bool SWZ = false>
+__device__ __forceinline__ int wphys(int idx) {
+    return SWZ ? (idx ^ (((idx >> 8) & 3) << 3)) : (idx + ((idx >> 8) << 3));
+}
+__host__ __device__ constexpr int warp_slice_floats(int S, bool swz = false) { return swz ? S : S + (S >> 8) * 8; }
 
 template <typename T>
 __device__ __forceinline__ void load8(const T* p, float (&v)[8]);
@@ -51,6 +62,28 @@ __device__ __forceinline__ void load8<__half>(const __half* p, float (&v)[8]) {
         v[2 * i] = f.x;
         v[2 * i + 1] = f.y;
     }
+}
+
+// eight 16-bit values held in a 16-byte register quadruple -> fp32
+template <typename T>
+__device__ __forceinline__ void unpack8(const uint4& r, float (&v)[8]);
+template <>
+__device__ __forceinline__ void unpack8<__nv_bfloat16>(const uint4& r, float (&v)[8]) {
+    v[0] = __uint_as_float(r.x << 16); v[1] = __uint_as_float(r.x & 0xffff0000u);
+    v[2] = __uint_as_float(r.y << 16); v[3] = __uint_as_float(r.y & 0xffff0000u);
+    v[4] = __uint_as_float(r.z << 16); v[5] = __uint_as_float(r.z & 0xffff0000u);
+    v[6] = __uint_as_float(r.w << 16); v[7] = __uint_as_float(r.w & 0xffff0000u);
+}
+__device__ __forceinline__ float2 half2_bits_to_float2(uint32_t w) {
+    __half2 h;
+    *reinterpret_cast<uint32_t*>(&h) = w;
+    return __half22float2(h);
+}
+template <>
+__device__ __forceinline__ void unpack8<__half>(const uint4& r, float (&v)[8]) {
+    const float2 a = half2_bits_to_float2(r.x), b = half2_bits_to_float2(r.y);
+    const float2 c = half2_bits_to_float2(r.z), d = half2_bits_to_float2(r.w);
+    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y; v[4] = c.x; v[5] = c.y; v[6] = d.x; v[7] = d.y;
 }
 
 template <typename T>
@@ -156,7 +189,7 @@ struct RawChunk {
 #pragma unroll
         for (int j = 0; j < J; ++j) {
             float t[8];
-            load8<T>(reinterpret_cast<const T*>(&v[j]), t);
+            unpack8<T>(v[j], t);
 #pragma unroll
             for (int e = 0; e < 8; ++e) a[j * 8 + e] = t[e];
         }
@@ -182,14 +215,19 @@ struct RawChunk<float, J> {
 };
 
 // Transform the super-chunk held in a[] (lane l: elements j*256 + l*8 .. +7 in a[8j .. 8j+7]); the result is left
-// in `wbuf` (this warp's slice) at wphys(natural index).
-template <int LOGS, bool PACK = false>
+// in `wbuf` (this warp's slice) at wphys<>(natural index).
+template <int LOGS, bool PACK = false, bool SWZ = false>
 __device__ __forceinline__ void warp_transform_loaded(float (&a)[(1 << LOGS) / 32], int m, float* wbuf, int lane) {
     constexpr int S = 1 << LOGS, E = S / 32, LOG2E = LOGS - 5, J = E / 8, V = E / 32, LOG2V = LOG2E - 5;
     PhaseA<E, 0, LOG2E, PACK>::run(a, m);
+    // swizzled layout: the XOR only ever takes four values per thread, so four base addresses serve every access
+    // (wphys<true>(j * 256 + lane * 8) = j * 256 + ((lane ^ (j & 3)) << 3))
+    float* abase[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) abase[k] = wbuf + (SWZ ? ((lane ^ k) << 3) : lane * 8);
 #pragma unroll
     for (int j = 0; j < J; ++j) {
-        float* p = wbuf + wphys(j * 256 + lane * 8);
+        float* p = SWZ ? abase[j & 3] + j * 256 : wbuf + wphys<false>(j * 256 + lane * 8);
         *reinterpret_cast<float4*>(p) = make_float4(a[j * 8], a[j * 8 + 1], a[j * 8 + 2], a[j * 8 + 3]);
         *reinterpret_cast<float4*>(p + 4) = make_float4(a[j * 8 + 4], a[j * 8 + 5], a[j * 8 + 6], a[j * 8 + 7]);
     }
@@ -198,10 +236,14 @@ __device__ __forceinline__ void warp_transform_loaded(float (&a)[(1 << LOGS) / 3
     constexpr int LOWN = 8 / V;                               // lanes that share a 256-element block differ in the low part
     const int lowpart = lane % LOWN, highpart = lane / LOWN;
     const int off = highpart * 256 + lowpart * V;
+    // wphys<true>(off + c * 8) = off + (c >> 2) * 32 + (((c & 3) ^ (highpart & 3)) << 3)
+    float* bbase[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) bbase[k] = wbuf + off + ((k ^ (highpart & 3)) << 3);
     float b[E];
 #pragma unroll
     for (int c = 0; c < 32; ++c) {
-        const float* p = wbuf + wphys(off + c * 8);
+        const float* p = SWZ ? bbase[c & 3] + (c >> 2) * 32 : wbuf + wphys<false>(off + c * 8);
         if (V == 4) {
             const float4 t = *reinterpret_cast<const float4*>(p);
             b[c * 4] = t.x; b[c * 4 + 1] = t.y; b[c * 4 + 2] = t.z; b[c * 4 + 3] = t.w;
@@ -215,7 +257,7 @@ __device__ __forceinline__ void warp_transform_loaded(float (&a)[(1 << LOGS) / 3
     PhaseB<E, 0, LOG2V, PACK>::run(b, m);
 #pragma unroll
     for (int c = 0; c < 32; ++c) {
-        float* p = wbuf + wphys(off + c * 8);
+        float* p = SWZ ? bbase[c & 3] + (c >> 2) * 32 : wbuf + wphys<false>(off + c * 8);
         if (V == 4) *reinterpret_cast<float4*>(p) = make_float4(b[c * 4], b[c * 4 + 1], b[c * 4 + 2], b[c * 4 + 3]);
         else if (V == 2) *reinterpret_cast<float2*>(p) = make_float2(b[c * 2], b[c * 2 + 1]);
         else *p = b[c];
@@ -224,7 +266,7 @@ __device__ __forceinline__ void warp_transform_loaded(float (&a)[(1 << LOGS) / 3
 }
 
 // Transform the super-chunk that starts at element `base` of src (elements at or beyond `total` read as 0).
-template <typename T, int LOGS, bool PACK = false>
+template <typename T, int LOGS, bool PACK = false, bool SWZ = false>
 __device__ __forceinline__ void warp_transform(const T* __restrict__ src, int64_t base, int64_t total, int m,
                                                float* wbuf, int lane) {
     constexpr int S = 1 << LOGS, E = S / 32, J = E / 8;
@@ -242,7 +284,7 @@ __device__ __forceinline__ void warp_transform(const T* __restrict__ src, int64_
 #pragma unroll
         for (int e = 0; e < 8; ++e) a[j * 8 + e] = v[e];
     }
-    warp_transform_loaded<LOGS, PACK>(a, m, wbuf, lane);
+    warp_transform_loaded<LOGS, PACK, SWZ>(a, m, wbuf, lane);
 }
 
 // K == 1: every warp transforms super-chunks independently and writes them back with 16-byte stores.
@@ -260,7 +302,7 @@ __global__ void __launch_bounds__(32 * kWarpsPerCta) fwht_warp_kernel(const T* _
 #pragma unroll
         for (int j = 0; j < J; ++j) {
             const int idx = j * 256 + lane * 8;
-            const float* p = wbuf + wphys(idx);
+            const float* p = wbuf + wphys<>(idx);
             const float4 t0 = *reinterpret_cast<const float4*>(p);
             const float4 t1 = *reinterpret_cast<const float4*>(p + 4);
             const float v[8] = {t0.x * scale, t0.y * scale, t0.z * scale, t0.w * scale,
@@ -335,13 +377,13 @@ __device__ __forceinline__ float row_quant_one(float v, float scale, float zero,
 }
 
 // Quantize the row held in shared memory as `chunks` slices of S floats (wphys layout) and write it out.
-template <typename T>
+template <typename T, bool SWZ = false>
 __device__ __forceinline__ void row_quant_store(const float* wsm, int slice, int S, int chunks, T* yrow, float scale,
                                                 float zero, const RowQuant& q) {
     const int n = chunks * S;
     for (int idx = 8 * threadIdx.x; idx < n; idx += 8 * blockDim.x) {
         const int c = idx / S, p = idx - c * S;
-        const float* src = wsm + (size_t)c * slice + wphys(p);
+        const float* src = wsm + (size_t)c * slice + wphys<SWZ>(p);
         const float4 t0 = *reinterpret_cast<const float4*>(src);
         const float4 t1 = *reinterpret_cast<const float4*>(src + 4);
         const float o[8] = {row_quant_one(t0.x, scale, zero, q), row_quant_one(t0.y, scale, zero, q),
@@ -384,7 +426,7 @@ __global__ void __launch_bounds__(32 * W) fwht_split_kernel(const T* __restrict_
             float v[W][8];
 #pragma unroll
             for (int w = 0; w < W; ++w) {
-                const float* q = wsm + w * slice + wphys(p);
+                const float* q = wsm + w * slice + wphys<>(p);
                 const float4 t0 = *reinterpret_cast<const float4*>(q);
                 const float4 t1 = *reinterpret_cast<const float4*>(q + 4);
                 v[w][0] = t0.x; v[w][1] = t0.y; v[w][2] = t0.z; v[w][3] = t0.w;
@@ -428,7 +470,7 @@ __global__ void __launch_bounds__(32 * W) fwht_split_kernel(const T* __restrict_
                         lo = fminf(lo, o[e]);
                         hi = fmaxf(hi, o[e]);
                     }
-                    float* q = wsm + w * slice + wphys(p);
+                    float* q = wsm + w * slice + wphys<>(p);
                     *reinterpret_cast<float4*>(q) = make_float4(o[0], o[1], o[2], o[3]);
                     *reinterpret_cast<float4*>(q + 4) = make_float4(o[4], o[5], o[6], o[7]);
                 } else {
@@ -462,21 +504,22 @@ __device__ __forceinline__ void store2<__half>(__half* p, float a, float b) {
 }
 
 // two neighbouring positions of every chunk -> K outputs each; hadK entries are +-1, so the products are exact
-template <typename T, int KK, bool QUANT = false>
+template <typename T, int KK, bool QUANT = false, bool SWZ = false>
 __device__ __forceinline__ void mix_pair(float* buf, int slice, const float* hk, int p, int P, T* yrow,
-                                         float scale, int K, float* lo = nullptr, float* hi = nullptr) {
+                                         float scale, int K, float* lo = nullptr, float* hi = nullptr,
+                                         bool hk_vec = true) {
     float v0[KK], v1[KK];
 #pragma unroll
     for (int k = 0; k < KK; ++k) {
         if (k < K) {
-            const float2 t = *reinterpret_cast<const float2*>(buf + k * slice + wphys(p));
+            const float2 t = *reinterpret_cast<const float2*>(buf + k * slice + wphys<SWZ>(p));
             v0[k] = t.x;
             v1[k] = t.y;
         }
     }
     for (int ko = 0; ko < K; ++ko) {
         float s0 = 0.f, s1 = 0.f;
-        if ((K & 3) == 0) {                          // rows of hadK as 16-byte words (same address in every lane)
+        if ((K & 3) == 0 && hk_vec) {                // rows of hadK as 16-byte words (same address in every lane)
             const float4* hrow = reinterpret_cast<const float4*>(hk + ko * K);
 #pragma unroll
             for (int k4 = 0; k4 < KK / 4; ++k4) {
@@ -502,7 +545,7 @@ __device__ __forceinline__ void mix_pair(float* buf, int slice, const float* hk,
             const float r0 = round_io<T>(s0 * scale), r1 = round_io<T>(s1 * scale);
             *lo = fminf(*lo, fminf(r0, r1));
             *hi = fmaxf(*hi, fmaxf(r0, r1));
-            *reinterpret_cast<float2*>(buf + ko * slice + wphys(p)) = make_float2(r0, r1);
+            *reinterpret_cast<float2*>(buf + ko * slice + wphys<SWZ>(p)) = make_float2(r0, r1);
         } else {
             store2<T>(yrow + (int64_t)ko * P + p, s0 * scale, s1 * scale);
         }
@@ -535,14 +578,19 @@ __device__ __forceinline__ void mix_fixed(const float (&v)[K], float (&y)[K]) {
     }
 }
 
-// the same mix on two neighbouring positions at once (.x and .y), every addition as one paired instruction
+// the same mix on two neighbouring positions at once (.x and .y), every addition as one paired instruction; the
+// inputs are chunk k of this position pair at src + k * slice
 template <int K>
-__device__ __forceinline__ void mix_fixed2(const float2 (&v)[K], float2 (&y)[K]) {
+__device__ __forceinline__ void mix_fixed2(const float* __restrict__ src, int slice, float2 (&y)[K]) {
     constexpr int NQ = K / 4;
+    float2 v[K];
+#pragma unroll
+    for (int k = 0; k < K; ++k) v[k] = *reinterpret_cast<const float2*>(src + k * slice);
 #pragma unroll
     for (int q = 0; q < NQ; ++q) {
-        const float2 ab0 = add2(v[4 * q], v[4 * q + 1]), ab1 = sub2(v[4 * q], v[4 * q + 1]);
-        const float2 cd0 = add2(v[4 * q + 2], v[4 * q + 3]), cd1 = sub2(v[4 * q + 2], v[4 * q + 3]);
+        const int b = 4 * q;
+        const float2 ab0 = add2(v[b], v[b + 1]), ab1 = sub2(v[b], v[b + 1]);
+        const float2 cd0 = add2(v[b + 2], v[b + 3]), cd1 = sub2(v[b + 2], v[b + 3]);
         const float2 c[8] = {add2(ab0, cd0), add2(ab1, cd0), sub2(ab0, cd0), sub2(ab1, cd0),
                              add2(ab0, cd1), add2(ab1, cd1), sub2(ab0, cd1), sub2(ab1, cd1)};
 #pragma unroll
@@ -556,7 +604,7 @@ __device__ __forceinline__ void mix_fixed2(const float2 (&v)[K], float2 (&y)[K])
     }
 }
 
-// true in every thread when the K x K matrix in shared memory is the tabulated one of that order
+// true in every thread when the K x K matrix at hk is the tabulated one of that order
 template <int K>
 __device__ __forceinline__ bool matches_table(const float* hk) {
     uint32_t tab[K];
@@ -572,13 +620,12 @@ __device__ __forceinline__ bool matches_table(const float* hk) {
 
 // two neighbouring positions of every chunk through mix_fixed, stored as pairs (QUANT: rounded to the I/O type and
 // put back into shared memory, min / max tracked, as mix_pair does)
-template <typename T, int K, bool QUANT>
+template <typename T, int K, bool QUANT, bool SWZ = false>
 __device__ __forceinline__ void mix_pair_fixed(float* buf, int slice, int p, int P, T* yrow, float scale, float* lo,
                                                float* hi) {
-    float2 v[K], y[K];
-#pragma unroll
-    for (int k = 0; k < K; ++k) v[k] = *reinterpret_cast<const float2*>(buf + k * slice + wphys(p));
-    mix_fixed2<K>(v, y);
+    float2 y[K];
+    const float* src = buf + wphys<SWZ>(p);
+    mix_fixed2<K>(src, slice, y);
 #pragma unroll
     for (int k = 0; k < K; ++k) {
         const float2 o = __fmul2_rn(y[k], make_float2(scale, scale));
@@ -586,21 +633,21 @@ __device__ __forceinline__ void mix_pair_fixed(float* buf, int slice, int p, int
             const float r0 = round_io<T>(o.x), r1 = round_io<T>(o.y);
             *lo = fminf(*lo, fminf(r0, r1));
             *hi = fmaxf(*hi, fmaxf(r0, r1));
-            *reinterpret_cast<float2*>(buf + k * slice + wphys(p)) = make_float2(r0, r1);
+            *reinterpret_cast<float2*>(buf + k * slice + wphys<SWZ>(p)) = make_float2(r0, r1);
         } else {
             store2<T>(yrow + (int64_t)k * P + p, o.x, o.y);
         }
     }
 }
 
-// one position of every chunk through mix_fixed (half the registers of the pair form; lanes take consecutive
-// positions, so a warp still writes 64 contiguous bytes per output chunk)
-template <typename T, int K, bool QUANT>
+// one position of every chunk through mix_fixed (scalar additions; lanes take consecutive positions, so a warp
+// still writes 64 contiguous bytes per output chunk); used at K = 28, where the paired form does not fit the registers.
+template <typename T, int K, bool QUANT, bool SWZ = false>
 __device__ __forceinline__ void mix_one_fixed(float* buf, int slice, int p, int P, T* yrow, float scale, float* lo,
                                               float* hi) {
     float v[K], y[K];
 #pragma unroll
-    for (int k = 0; k < K; ++k) v[k] = buf[k * slice + wphys(p)];
+    for (int k = 0; k < K; ++k) v[k] = buf[k * slice + wphys<SWZ>(p)];
     mix_fixed<K>(v, y);
 #pragma unroll
     for (int k = 0; k < K; ++k) {
@@ -608,7 +655,7 @@ __device__ __forceinline__ void mix_one_fixed(float* buf, int slice, int p, int 
             const float r = round_io<T>(y[k] * scale);
             *lo = fminf(*lo, r);
             *hi = fmaxf(*hi, r);
-            buf[k * slice + wphys(p)] = r;
+            buf[k * slice + wphys<SWZ>(p)] = r;
         } else {
             store_from_float<T>(yrow, (int64_t)k * P + p, y[k] * scale);
         }
@@ -624,26 +671,41 @@ __device__ __forceinline__ void mix_one_fixed(float* buf, int slice, int p, int 
 #ifndef RQ_MIX12_WARPS
 #define RQ_MIX12_WARPS 6
 #endif
-// Larger K (one CTA per SM by shared memory at K = 28): 16 warps, so that the 512 position pairs of a 1024-long
-// chunk take one round of the mix and more loads are in flight during the transform (bf16, 32768 rows: n = 28672
-// 1.04 -> 1.52 TB/s, n = 20480 1.32 -> 1.61 TB/s against 8 warps).
+// Larger K: 8 warps and two CTAs per SM (28 unpadded slices of 4 KB are 112 KB, so two rows fit an SM's shared
+// memory; 128 registers per thread), so that one CTA's load-bound transform phase overlaps the other's issue-bound
+// mix.  Measured (bf16, 16384 rows, GB/s of read + write): n = 28672 one CTA of 16 warps 2779, two of 8 warps 3031,
+// with paired additions in the transform 3093; n = 20480 2695 -> 3010.  At K = 28 the mix itself stays scalar, one
+// position per thread: the paired form needs 56 two-wide sums (spills at 128 registers: 2655), and in two halves
+// of 14 outputs with the inputs read twice it reaches 2991.
 #ifndef RQ_MIX28_WARPS
-#define RQ_MIX28_WARPS 16
+#define RQ_MIX28_WARPS 8
+#endif
+#ifndef RQ_MIX28_PACK
+#define RQ_MIX28_PACK 1
 #endif
 template <typename T, int LOGS, bool QUANT = false, int KMAX = 28, int WARPS = kMixWarps>
-__global__ void __launch_bounds__(32 * WARPS, (KMAX <= 12 && LOGS == 10) ? 4 : 1) fwht_mix_kernel(const T* __restrict__ x, T* __restrict__ y,
+__global__ void __launch_bounds__(32 * WARPS, (LOGS != 10 || QUANT) ? 1 : (KMAX <= 12 ? 4 : (WARPS <= 8 ? 2 : 1))) fwht_mix_kernel(const T* __restrict__ x, T* __restrict__ y,
                                                                      int64_t rows, int K,
                                                                      const float* __restrict__ hadK, float scale,
                                                                      RowQuant rq = RowQuant()) {
     constexpr int S = 1 << LOGS;
-    constexpr int slice = warp_slice_floats(S);
-    constexpr bool PACK = KMAX <= 12 && LOGS == 10;             // paired additions (see add2)
+    constexpr bool SWZ = mix_swizzled(LOGS, KMAX, QUANT);
+    constexpr int slice = warp_slice_floats(S, SWZ);
+    constexpr bool PACK = LOGS == 10 && (KMAX <= 12 || RQ_MIX28_PACK);   // paired additions (see add2)
     extern __shared__ float wsm[];
     __shared__ float red[64];
-    float* hk = wsm + (size_t)K * slice;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int e = threadIdx.x; e < K * K; e += blockDim.x) hk[e] = hadK[e];
-    __syncthreads();
+    // the caller's matrix sits behind the slices in shared memory, except where that would cost the second CTA of an
+    // SM (K > kMixSharedMatrixMaxK at S = 1024): there the tabulated matrices need no copy and any other matrix is
+    // read in place, entry by entry
+    const bool hk_shared = mix_matrix_shared(K, SWZ);
+    const float* hk = hadK;
+    if (hk_shared) {
+        float* hs = wsm + (size_t)K * slice;
+        for (int e = threadIdx.x; e < K * K; e += blockDim.x) hs[e] = hadK[e];
+        hk = hs;
+        __syncthreads();
+    }
     // 0: the caller's matrix, entry by entry; 12 / 20 / 28: the tabulated matrix of that order (uniform over the CTA)
     int fixed = 0;
     if (K == 12) fixed = matches_table<12>(hk) ? 12 : 0;
@@ -662,15 +724,15 @@ __global__ void __launch_bounds__(32 * WARPS, (KMAX <= 12 && LOGS == 10) ? 4 : 1
                 if (two) r1.load(x + row * n + (int64_t)(c + WARPS) * S, lane);
                 float a[(1 << LOGS) / 32];
                 r0.unpack(a);
-                warp_transform_loaded<LOGS, PACK>(a, LOGS, wsm + (size_t)c * slice, lane);
+                warp_transform_loaded<LOGS, PACK, SWZ>(a, LOGS, wsm + (size_t)c * slice, lane);
                 if (two) {
                     r1.unpack(a);
-                    warp_transform_loaded<LOGS, PACK>(a, LOGS, wsm + (size_t)(c + WARPS) * slice, lane);
+                    warp_transform_loaded<LOGS, PACK, SWZ>(a, LOGS, wsm + (size_t)(c + WARPS) * slice, lane);
                 }
             }
         } else {
             for (int c = warp; c < K; c += WARPS)
-                warp_transform<T, LOGS, PACK>(x, row * n + (int64_t)c * S, (rows * n), LOGS, wsm + (size_t)c * slice,
+                warp_transform<T, LOGS, PACK, SWZ>(x, row * n + (int64_t)c * S, (rows * n), LOGS, wsm + (size_t)c * slice,
                                               lane);
         }
         __syncthreads();
@@ -678,18 +740,18 @@ __global__ void __launch_bounds__(32 * WARPS, (KMAX <= 12 && LOGS == 10) ? 4 : 1
         float lo = 0.f, hi = 0.f;
         if (KMAX > 12 && fixed == 28) {
             for (int p = threadIdx.x; p < S; p += blockDim.x)
-                mix_one_fixed<T, 28, QUANT>(wsm, slice, p, S, yrow, scale, &lo, &hi);
+                mix_one_fixed<T, 28, QUANT, SWZ>(wsm, slice, p, S, yrow, scale, &lo, &hi);
         } else
         for (int p = 2 * threadIdx.x; p < S; p += 2 * blockDim.x) {
             if (fixed == 12) {
-                mix_pair_fixed<T, 12, QUANT>(wsm, slice, p, S, yrow, scale, &lo, &hi);
+                mix_pair_fixed<T, 12, QUANT, SWZ>(wsm, slice, p, S, yrow, scale, &lo, &hi);
             } else if (KMAX > 12 && fixed == 20) {
-                mix_pair_fixed<T, 20, QUANT>(wsm, slice, p, S, yrow, scale, &lo, &hi);
+                mix_pair_fixed<T, 20, QUANT, SWZ>(wsm, slice, p, S, yrow, scale, &lo, &hi);
             } else if (KMAX <= 12 || K <= 12) {
-                mix_pair<T, 12, QUANT>(wsm, slice, hk, p, S, yrow, scale, K, &lo, &hi);
+                mix_pair<T, 12, QUANT, SWZ>(wsm, slice, hk, p, S, yrow, scale, K, &lo, &hi, hk_shared);
             } else if (KMAX > 12) {
-                if (K <= 20) mix_pair<T, 20, QUANT>(wsm, slice, hk, p, S, yrow, scale, K, &lo, &hi);
-                else mix_pair<T, 28, QUANT>(wsm, slice, hk, p, S, yrow, scale, K, &lo, &hi);
+                if (K <= 20) mix_pair<T, 20, QUANT, SWZ>(wsm, slice, hk, p, S, yrow, scale, K, &lo, &hi, hk_shared);
+                else mix_pair<T, 28, QUANT, SWZ>(wsm, slice, hk, p, S, yrow, scale, K, &lo, &hi, hk_shared);
             }
         }
         if (QUANT) {
@@ -699,7 +761,7 @@ __global__ void __launch_bounds__(32 * WARPS, (KMAX <= 12 && LOGS == 10) ? 4 : 1
                 if (rq.scale_out) rq.scale_out[row] = qs;
                 if (rq.zero_out) rq.zero_out[row] = qz;
             }
-            row_quant_store<T>(wsm, slice, S, K, yrow, qs, qz, rq);
+            row_quant_store<T, SWZ>(wsm, slice, S, K, yrow, qs, qz, rq);
         }
     }
 }
