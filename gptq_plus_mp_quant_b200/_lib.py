@@ -12,7 +12,8 @@ import os
 import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "csrc", "librealq_b200.so")
+# REALQ_B200_LIB names another build of the same library (same exports), e.g. one compiled with different tuning macros
+LIB_PATH = os.environ.get("REALQ_B200_LIB") or os.path.join(_HERE, "csrc", "librealq_b200.so")
 
 RQ_OK, RQ_ERR_INVALID, RQ_ERR_CUDA, RQ_ERR_TIMEOUT, RQ_ERR_WORKSPACE, RQ_ERR_UNSUPPORTED, RQ_ERR_TOO_LARGE = range(7)
 RQ_F32, RQ_BF16, RQ_F16 = 0, 1, 2
