@@ -137,11 +137,24 @@ def dist_setup():
     local = int(os.environ.get("LOCAL_RANK", "0"))
     if world > 1:
         import torch.distributed as dist
+        # plain peer-to-peer rings, no NVLink multicast objects: the exchanges here are two large reduce-scatter /
+        # all-gather calls per linear, which gain nothing from in-switch reduction, and ranks that leave at slightly
+        # different moments then never unmap memory that another rank's multicast object still refers to
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         torch.cuda.set_device(local)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     else:
         torch.cuda.set_device(0)
     return rank, world, local
+
+
+def dist_teardown(world):
+    """All ranks leave together: nothing in flight, then the communicator goes."""
+    if world > 1:
+        torch.cuda.synchronize()
+        torch.distributed.barrier()
+        torch.cuda.synchronize()
+        torch.distributed.destroy_process_group()
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the Hessian kernel at C = 4096, G = 4, 8192 tokens
@@ -752,8 +765,7 @@ def run_ours(args):
         torch.cuda.synchronize()
         if rank == 0:
             print(json.dumps({"profile_steps": args.profile_steps, "workload": wl.name, "schedule": wl.schedule}))
-        if world > 1:
-            torch.distributed.destroy_process_group()
+        dist_teardown(world)
         return
     warm = max(args.warmup, 3)
     for _ in range(warm):
@@ -860,8 +872,7 @@ def run_ours(args):
         out["fwht_alone_gbs_bf16"] = fwht_alone_gbs(dev)
     if rank == 0:
         print(json.dumps(out))
-    if world > 1:
-        torch.distributed.destroy_process_group()
+    dist_teardown(world)
 
 
 # ----------------------------------------------------------------------------------------------
@@ -998,8 +1009,7 @@ def run_c3(args):
     out = _common_line(args, world, total_ms / 1e3 / NL, NL, warm, total_ms, prof, peaks, flops_local, clocks, config, extra)
     if rank == 0:
         print(json.dumps(out))
-    if world > 1:
-        torch.distributed.destroy_process_group()
+    dist_teardown(world)
 
 
 # ----------------------------------------------------------------------------------------------
@@ -1114,8 +1124,7 @@ def run_c4_down(args):
     out["metric"] = "seconds per 28672-wide down_proj quantized (Llama-70B shape)"
     if rank == 0:
         print(json.dumps(out))
-    if world > 1:
-        torch.distributed.destroy_process_group()
+    dist_teardown(world)
 
 
 def main():
