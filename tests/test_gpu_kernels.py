@@ -212,6 +212,28 @@ def test_rotation_full_sizes_are_orthogonal(n):
     assert float((back - x).abs().max()) < 2e-5 * float(x.abs().max()) * 4
 
 
+@pytest.mark.parametrize("n,rows,dtype", [(12288, 1301, "bfloat16"), (12288, 700, "float32"), (20480, 650, "bfloat16"),
+                                          (28672, 650, "bfloat16"), (28672, 330, "float32"), (28672, 37, "float16"),
+                                          (24576, 300, "bfloat16"), (49152, 160, "float32"), (4096, 2500, "bfloat16"),
+                                          (8192, 700, "float16"), (2048, 3000, "float32")])
+def test_rotation_register_resident_kernels_vs_exact_operator(n, rows, dtype):
+    """The kernels the benchmark lengths run (K chunks of 1024 / 2048 / 4096 with the tabulated 12 / 20 / 28 mix, and
+    the 2048 / 4096 / 8192-long single chunks) against the exact operator in fp64, with enough rows that every CTA
+    takes several turns of its grid-stride loop and a row count that no tile size divides: fp32 internals plus one
+    rounding to the I/O dtype; also the transposed matrix (a non-tabulated one: the entry-by-entry mix)."""
+    from gptq_plus_mp_quant_b200.utils import hadamard_utils as hu
+    dt = getattr(torch, dtype)
+    x = cases.make_acts(1, rows, n, seed=13).reshape(rows, n).to(dt)
+    tol = {"float32": 2e-6, "bfloat16": 2.0 ** -8, "float16": 2.0 ** -11}[dtype]
+    for transpose in (False, True):
+        hadK, K = hu.get_hadK(n, transpose=transpose)
+        if transpose and K == 1:
+            continue
+        y = hu.matmul_hadU_cuda(x.to(DEV), hadK, K)
+        exact = ohad.rotate_exact(x, hadK, K)
+        assert float((y.double().cpu() - exact).abs().max()) <= tol * float(exact.abs().max()) * 1.01, (n, transpose)
+
+
 @pytest.mark.parametrize("K,P,dtype", [(172, 64, "float32"), (172, 64, "bfloat16"), (68, 32, "float16"), (252, 16, "float32"),
                                            (70, 2, "float32"), (172, 1, "float32")])
 def test_rotation_with_wide_mix_matrix(K, P, dtype):
