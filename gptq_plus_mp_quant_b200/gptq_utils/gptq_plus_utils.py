@@ -13,7 +13,7 @@ import torch
 
 from .. import ops
 from ..utils import dist_utils
-from . import fasterquant_impl
+from . import fasterquant_impl, ghinv_analysis
 
 _NULL_CONTEXT = nullcontext()
 
@@ -261,6 +261,33 @@ class GPTQPlus:
             raise ValueError("NaN in weights")
 
     @torch.no_grad()
+    # ---- diagnostics (gptq_plus_utils.py:489-492, 1898-2347): summaries of G.H^-1 and of the weight drift
+    def _selected_column_count(self, blocksize, max_blocks):
+        return ghinv_analysis.selected_column_count(self, blocksize, max_blocks)
+
+    def analyze_ghinv_dynamics(self, blocksize=128, percdamp=0.01, groupsize=-1, actorder=False, static_groups=False,
+                               enable_gradient_update=True, g_update_mode="frozen", max_subgroups=None,
+                               max_blocks=None, return_tensors=False):
+        return ghinv_analysis.analyze_ghinv_dynamics(
+            self, blocksize=blocksize, percdamp=percdamp, groupsize=groupsize, actorder=actorder,
+            static_groups=static_groups, enable_gradient_update=enable_gradient_update, g_update_mode=g_update_mode,
+            max_subgroups=max_subgroups, max_blocks=max_blocks, return_tensors=return_tensors)
+
+    def summarize_ghinv(self, percdamp=0.01, blocksize=128, actorder=False, enable_gradient_update=True,
+                        gradient_override=None, reference_loss_override=None, max_subgroups=None, max_blocks=None,
+                        return_tensors=False):
+        return ghinv_analysis.summarize_ghinv(
+            self, percdamp=percdamp, blocksize=blocksize, actorder=actorder,
+            enable_gradient_update=enable_gradient_update, gradient_override=gradient_override,
+            reference_loss_override=reference_loss_override, max_subgroups=max_subgroups, max_blocks=max_blocks,
+            return_tensors=return_tensors)
+
+    def summarize_weight_delta(self, blocksize=128, actorder=False, max_subgroups=None, max_blocks=None,
+                               ref_weight_override=None, weight_override=None, return_tensors=False):
+        return ghinv_analysis.summarize_weight_delta(
+            self, blocksize=blocksize, actorder=actorder, max_subgroups=max_subgroups, max_blocks=max_blocks,
+            ref_weight_override=ref_weight_override, weight_override=weight_override, return_tensors=return_tensors)
+
     def gather_rows_(self):
         """Row-parallel mode: after fasterquant every rank holds its own rows of the quantized weight; this
         all-gathers them (and the export buffers, if present) so that layer.weight is complete on every rank."""

@@ -1,6 +1,7 @@
-"""Data-parallel helpers of the quantization path: the subset of the reference's
-``utils/dist_utils.py`` (:105-199) that ``finalize_hessian`` and its callers use.  The
-collectives go through ``torch.distributed`` (NCCL over NVLink on GPUs, gloo in CPU tests)."""
+"""Data-parallel helpers of the quantization path: the reference's ``utils/dist_utils.py`` (:13-199) without
+``distribute_model`` (placing a model across devices is the caller's launcher's business), plus the exchanges
+of the row-parallel mode.  The collectives go through ``torch.distributed`` (NCCL over NVLink on GPUs, gloo in
+CPU tests)."""
 from __future__ import annotations
 
 from typing import Optional
@@ -30,12 +31,66 @@ class local_only:
         _local_only -= 1
 
 
+def init_process_group():
+    """Joins the job's process group and waits for the other ranks (dist_utils.py:13-23).  The caller has selected
+    its GPU with ``torch.cuda.set_device``; the group is bound to that device so that collectives never guess it.
+    NCCL with the reference's 8-hour timeout on GPUs, gloo where there is no GPU."""
+    import datetime
+    if torch.cuda.is_available():
+        dist.init_process_group(backend="nccl", timeout=datetime.timedelta(hours=8),
+                                device_id=torch.device("cuda", torch.cuda.current_device()))
+    else:
+        dist.init_process_group(backend="gloo", timeout=datetime.timedelta(hours=8))
+    dist.barrier()
+
+
 def get_world_size() -> int:
     return dist.get_world_size() if is_dist_available_and_initialized() else 1
 
 
 def get_rank() -> int:
     return dist.get_rank() if is_dist_available_and_initialized() else 0
+
+
+def is_main() -> bool:
+    return get_rank() == 0
+
+
+def print_on_main(*args, **kwargs):
+    if is_main():
+        print(*args, **kwargs)
+
+
+def barrier():
+    if is_dist_available_and_initialized():
+        dist.barrier()
+
+
+def broadcast_parameters(module, src=0, group=None):
+    """Every parameter of ``module`` takes rank ``src``'s values (dist_utils.py:47-49)."""
+    for param in module.parameters():
+        dist.broadcast(param.data, src=src, group=group)
+
+
+def broadcast_tensor_(tensor: torch.Tensor, src: int = 0) -> torch.Tensor:
+    """In-place broadcast; no-op for a single process (dist_utils.py:166-170)."""
+    if get_world_size() > 1:
+        dist.broadcast(tensor, src=src)
+    return tensor
+
+
+def gather_into_tensor(tensor, dim: int = 0):
+    """Rank 0 receives the ranks' tensors concatenated along ``dim`` in rank order; the other ranks get None
+    (dist_utils.py:52-62).  A single process gets a copy of its own tensor."""
+    world = get_world_size()
+    if world == 1:
+        return tensor.clone()
+    if not is_main():
+        dist.gather(tensor, None)
+        return None
+    pieces = [torch.empty_like(tensor) for _ in range(world)]
+    dist.gather(tensor, pieces)
+    return torch.cat(pieces, dim=dim)
 
 
 def shard_slice(total: int, rank: Optional[int] = None, world: Optional[int] = None) -> slice:
@@ -211,6 +266,18 @@ def allreduce_sum_scalar(scalar) -> float:
     t = torch.tensor([float(scalar)], device=device, dtype=torch.float64)
     dist.all_reduce(t, op=dist.ReduceOp.SUM)
     return t.item()
+
+
+def allreduce_mean_scalar(scalar, count: int = 1) -> float:
+    """Weighted mean over ranks, ``sum(scalar_r * count_r) / sum(count_r)``, in fp64; 0 when the counts sum to 0
+    (dist_utils.py:152-163)."""
+    if get_world_size() <= 1:
+        return float(scalar)
+    device = "cuda" if (torch.cuda.is_available() and dist.get_backend() == "nccl") else "cpu"
+    pair = torch.tensor([float(scalar) * count, float(count)], device=device, dtype=torch.float64)
+    dist.all_reduce(pair, op=dist.ReduceOp.SUM)
+    total, weight = pair.tolist()
+    return 0.0 if weight == 0 else total / weight
 
 
 def assert_bit_exact(tensor: torch.Tensor, tag: str = "", rtol: float = 0.0, atol: float = 0.0):

@@ -235,6 +235,15 @@ def _matmul_hadU_fp64(X, hadK, K):
     return v.reshape(X.shape) / torch.tensor(n).sqrt()
 
 
+def random_orthogonal_matrix(size, device, generator=None):
+    """hadamard_utils.py:56-73: the Q factor of a standard normal fp64 matrix (drawn on the host with
+    ``generator``), its columns signed so that the R factor would have a positive diagonal, which makes the result a
+    draw from the Haar measure rather than whatever the QR routine's sign convention gives."""
+    gauss = torch.randn(size, size, dtype=torch.float64, generator=generator).to(device)
+    q, r = torch.linalg.qr(gauss)
+    return q * torch.sign(torch.diagonal(r)).unsqueeze(0)
+
+
 def random_hadamard_matrix(size, device, generator=None):
     """hadamard_utils.py:76-80: rows of the normalised Hadamard matrix with random signs."""
     Q = torch.randint(low=0, high=2, size=(size,), generator=generator).to(torch.float64)

@@ -151,6 +151,12 @@ class ActQuantizer(torch.nn.Module):
                                        1 if codes else 0, 0 if with_zero else 1, 0, _lib.stream_of(x))
         _lib.check("rq_act_quant", rc)
 
+    def find_params_per_token_groupwise(self, x) -> None:
+        """Ranges per token and group of ``groupsize`` channels (utils/quant_utils.py:131-153)."""
+        if self.groupsize <= 0:
+            raise ValueError("find_params_per_token_groupwise needs groupsize > 0")
+        self.find_params(x)
+
     def find_params(self, x) -> None:
         if self.bits == 16:
             return
@@ -319,7 +325,7 @@ class WeightQuantizer(torch.nn.Module):
         if self.bits == 16:
             return
         if self.weight_groupsize > 0:
-            self._find_params_weight_groupwise(x)
+            self.find_params_weight_groupwise(x)
             return
         self._g_scale = self._g_zero = None
         _lib.require_cuda(x)
@@ -357,7 +363,7 @@ class WeightQuantizer(torch.nn.Module):
                                        _lib.ptr(scale_in), _lib.ptr(zero_in), 1 if codes else 0, 1, 1, _lib.stream_of(x))
         _lib.check("rq_act_quant", rc)
 
-    def _find_params_weight_groupwise(self, x) -> None:
+    def find_params_weight_groupwise(self, x) -> None:
         _lib.require_cuda(x)
         if x.shape[-1] % self.weight_groupsize != 0:
             raise ValueError(f"columns {x.shape[-1]} not divisible by weight_groupsize {self.weight_groupsize}")

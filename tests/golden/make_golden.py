@@ -343,6 +343,43 @@ def gen_faults(qu, gpu, out):
     out["nonspd.identity"] = np.array(ident)
 
 
+ANALYSIS_CASES = [
+    # name, groupsize, actorder, static_groups, g_update_mode
+    ("frozen_pc_act", -1, True, True, "frozen"),
+    ("online_g128_static_act", 128, True, True, "surrogate_online"),
+    ("block_g128_dynamic", 128, False, False, "surrogate_block"),
+]
+
+
+def gen_analysis(qu, gpu):
+    """The three diagnostic summaries of GPTQPlus (nested dicts of floats), written as JSON."""
+    rows, cols, nseq, seqlen, G = 64, 256, 4, 96, 4
+    W = cases.make_weight(rows, cols, seed=31)
+    X = cases.make_acts(nseq, seqlen, cols, seed=31)
+    X[..., 5] = 0.0                                                  # a dead input channel
+    S = cases.make_saliency(nseq, seqlen, G, seed=31)
+    Gr = cases.make_grad(rows, cols, seed=31)
+    other = cases.make_weight(rows, cols, seed=32)
+    out = {}
+    for name, gs, act, static, mode in ANALYSIS_CASES:
+        layer = _Lin(W)
+        g = gpu.GPTQPlus(layer, S, Gr, G, 0.25, 0.7)
+        g.quantizer = qu.WeightQuantizer()
+        g.quantizer.configure(4, perchannel=True, sym=True, mse=False)
+        g.add_batch(X, None)
+        g.finalize_hessian()
+        out[name] = {
+            "summarize_ghinv": g.summarize_ghinv(actorder=act, max_blocks=1),
+            "summarize_ghinv_off": g.summarize_ghinv(actorder=act, enable_gradient_update=False,
+                                                     reference_loss_override=0.3),
+            "summarize_weight_delta": g.summarize_weight_delta(actorder=act, ref_weight_override=other, max_subgroups=3),
+            "analyze_ghinv_dynamics": g.analyze_ghinv_dynamics(blocksize=128, percdamp=0.01, groupsize=gs,
+                                                               actorder=act, static_groups=static,
+                                                               g_update_mode=mode),
+        }
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--ref", default=os.environ.get("REALQ_REFERENCE_ROOT"), required="REALQ_REFERENCE_ROOT" not in os.environ,
@@ -351,6 +388,13 @@ def main():
     args = ap.parse_args()
     torch.set_num_threads(1)                        # fixed reduction order on any host
     qu, hu, gu, gpu, gg, ga = import_reference(args.ref)
+    if args.only is None or "analysis.json" in args.only:
+        import json
+        with torch.no_grad():
+            res = gen_analysis(qu, gpu)
+        with open(os.path.join(HERE, "analysis.json"), "w") as f:
+            json.dump(res, f, indent=1, sort_keys=True)
+        print(f"analysis.json: {len(res)} cases")
     for fname, fn, mods in (("quantizer.npz", gen_quantizer, (qu,)),
                             ("hadamard.npz", gen_hadamard, (hu,)),
                             ("plain_gptq.npz", gen_plain, (qu, gu)),

@@ -106,6 +106,30 @@ def _worker(rank, world, port, results):
             for g, owner in enumerate(owners_p):
                 if owner == rank:
                     assert torch.allclose(Hp[g], total[g], rtol=0, atol=1e-6), (owners_p, g)
+        # the small helpers of the reference's module (dist_utils.py:38-62, 152-176)
+        assert du.is_main() == (rank == 0)
+        du.barrier()
+        assert du.allreduce_mean_scalar(float(rank + 1)) == 1.5
+        assert du.allreduce_mean_scalar(2.0 if rank == 0 else 8.0, count=3 if rank == 0 else 1) == 3.5
+        assert du.allreduce_mean_scalar(5.0, count=0) == 0.0
+        b = torch.full((3,), float(rank))
+        assert torch.equal(du.broadcast_tensor_(b, src=1), torch.ones(3))
+        for dim, shape in ((0, (2, 3)), (1, (2, 3))):
+            mine = torch.arange(6.0).reshape(shape) + 10 * rank
+            got = du.gather_into_tensor(mine, dim=dim)
+            if rank == 0:
+                want = torch.cat([torch.arange(6.0).reshape(shape), torch.arange(6.0).reshape(shape) + 10], dim=dim)
+                assert torch.equal(got, want)
+            else:
+                assert got is None
+        lin = torch.nn.Linear(4, 3)
+        with torch.no_grad():
+            lin.weight.fill_(float(rank))
+            lin.bias.fill_(float(rank))
+        du.broadcast_parameters(lin, src=1)
+        assert float(lin.weight.min()) == 1.0 and float(lin.bias.max()) == 1.0
+        with du.local_only():
+            assert du.is_main() and torch.equal(du.gather_into_tensor(b), b) and du.allreduce_mean_scalar(7.0) == 7.0
         results[rank] = "ok"
     finally:
         dist.destroy_process_group()

@@ -429,6 +429,65 @@ def test_gptqplus_dynamic_groups_ranged_by_the_host(bs, mse):
     assert torch.allclose(layer.weight.data.cpu()[same], ref["Q"][same], rtol=1e-4, atol=0)
 
 
+def _compare_summaries(got, ref, path, rtol):
+    """Nested dicts / lists of the diagnostics: same keys, ints and bools equal, floats within rtol."""
+    if isinstance(ref, dict):
+        assert isinstance(got, dict) and set(got) == set(ref), (path, sorted(got), sorted(ref))
+        for k in ref:
+            _compare_summaries(got[k], ref[k], f"{path}.{k}", rtol)
+    elif isinstance(ref, list):
+        assert len(got) == len(ref), path
+        for i, (a, b) in enumerate(zip(got, ref)):
+            _compare_summaries(a, b, f"{path}[{i}]", rtol)
+    elif isinstance(ref, bool) or isinstance(ref, int) or ref is None or isinstance(ref, str):
+        assert got == ref, (path, got, ref)
+    else:
+        assert abs(got - ref) <= rtol * max(abs(ref), 1e-12) + 1e-9, (path, got, ref)
+
+
+@pytest.mark.parametrize("case", ["frozen_pc_act", "online_g128_static_act", "block_g128_dynamic"])
+def test_ghinv_diagnostics_vs_reference(case):
+    """GPTQPlus.summarize_ghinv / summarize_weight_delta / analyze_ghinv_dynamics against the summaries the
+    unmodified reference returns for the same seeded inputs (tests/golden/analysis.json): statistics of row norms,
+    so a relative tolerance of 1e-3 (the Hessian and its inverse factor come from this package's kernels)."""
+    import json
+    import os
+    from gptq_plus_mp_quant_b200.gptq_utils.gptq_plus_utils import GPTQPlus
+    from gptq_plus_mp_quant_b200.utils.quant_utils import WeightQuantizer
+    with open(os.path.join(os.path.dirname(__file__), "golden", "analysis.json")) as f:
+        ref = json.load(f)[case]
+    gs, act, static, mode = {"frozen_pc_act": (-1, True, True, "frozen"),
+                             "online_g128_static_act": (128, True, True, "surrogate_online"),
+                             "block_g128_dynamic": (128, False, False, "surrogate_block")}[case]
+    rows, cols, nseq, seqlen, G = 64, 256, 4, 96, 4
+    W = cases.make_weight(rows, cols, seed=31)
+    X = cases.make_acts(nseq, seqlen, cols, seed=31)
+    X[..., 5] = 0.0
+    S = cases.make_saliency(nseq, seqlen, G, seed=31)
+    Gr = cases.make_grad(rows, cols, seed=31)
+    other = cases.make_weight(rows, cols, seed=32).to(DEV)
+    layer = _layer(W)
+    obj = GPTQPlus(layer, S, Gr, G, 0.25, 0.7)
+    obj.quantizer = WeightQuantizer()
+    obj.quantizer.configure(4, perchannel=True, sym=True, mse=False)
+    obj.add_batch(X.to(DEV), None)
+    obj.finalize_hessian()
+    before = layer.weight.data.clone()
+    got = {
+        "summarize_ghinv": obj.summarize_ghinv(actorder=act, max_blocks=1),
+        "summarize_ghinv_off": obj.summarize_ghinv(actorder=act, enable_gradient_update=False,
+                                                   reference_loss_override=0.3),
+        "summarize_weight_delta": obj.summarize_weight_delta(actorder=act, ref_weight_override=other, max_subgroups=3),
+        "analyze_ghinv_dynamics": obj.analyze_ghinv_dynamics(blocksize=128, percdamp=0.01, groupsize=gs, actorder=act,
+                                                             static_groups=static, g_update_mode=mode),
+    }
+    assert torch.equal(layer.weight.data, before)                    # diagnostics write nothing back
+    _compare_summaries(got, ref, case, 1e-3)
+    cache = obj.analyze_ghinv_dynamics(groupsize=gs, actorder=act, static_groups=static, g_update_mode=mode,
+                                       max_subgroups=1, max_blocks=1, return_tensors=True)["_tensor_cache"]
+    assert len(cache) == 1 and cache[0]["final_raw_eff_ghinv"].shape == (rows // G, 128)
+
+
 def test_unsupported_modes_are_loud():
     from gptq_plus_mp_quant_b200.gptq_utils.gptq_plus_utils import GPTQPlus
     from gptq_plus_mp_quant_b200.utils.quant_utils import WeightQuantizer

@@ -560,6 +560,24 @@ def test_act_quantizer_vs_reference(golden, case):
 
 
 @pytest.mark.gpu
+def test_act_quantizer_groupwise_entry_point():
+    """ActQuantizer.find_params_per_token_groupwise (utils/quant_utils.py:131-153) is the grouped branch of
+    find_params under its own name; without a group size it has nothing to range."""
+    from gptq_plus_mp_quant_b200.utils.quant_utils import ActQuantizer
+    x = torch.randn(2, 5, 256, device=DEV, dtype=torch.bfloat16)
+    a, b = ActQuantizer(), ActQuantizer()
+    for q in (a, b):
+        q.configure(4, groupsize=64, sym=False, clip_ratio=0.9)
+    a.find_params(x)
+    b.find_params_per_token_groupwise(x)
+    assert torch.equal(a.scale, b.scale) and torch.equal(a.zero, b.zero) and a.scale.shape == x.shape
+    assert torch.equal(a(x), b(x))
+    c = ActQuantizer()
+    c.configure(4, groupsize=-1, sym=True)
+    with pytest.raises(ValueError):
+        c.find_params_per_token_groupwise(x)
+
+
 def test_act_quant_wrapper_rotates_and_quantizes():
     """ActQuantWrapper: online Hadamard + 4-bit input fake-quant around a linear equals the same steps done by the
     oracle on the CPU (rotation within one bf16 rounding, hence compared after the quantizer on the kernel's own

@@ -39,3 +39,14 @@ def test_get_hadK_picks_smallest_factor(n, K):
     hadK, k = hu.get_hadK(n)
     assert k == K
     assert (hadK is None) == (K == 1)
+
+
+def test_random_orthogonal_matrix():
+    """hadamard_utils.py:56-73: orthogonal in fp64, reproducible from the generator, sign convention of R's diagonal."""
+    g = torch.Generator().manual_seed(3)
+    q = hu.random_orthogonal_matrix(48, "cpu", generator=g)
+    assert q.dtype == torch.float64 and q.shape == (48, 48)
+    assert torch.allclose(q @ q.T, torch.eye(48, dtype=torch.float64), atol=1e-12)
+    gauss = torch.randn(48, 48, dtype=torch.float64, generator=torch.Generator().manual_seed(3))
+    assert bool((torch.diagonal(q.T @ gauss) > 0).all())            # R = Q^T A has a positive diagonal
+    assert torch.equal(q, hu.random_orthogonal_matrix(48, "cpu", generator=torch.Generator().manual_seed(3)))
