@@ -2,7 +2,9 @@
 ``oracle/_ref/`` (ignored by git, never imported by the product), so that the CPU arm of the benchmark can time the
 reference's classes themselves on a machine where the reference checkout is not mounted.
 
-    python oracle/make_ref.py [/path/to/gptq_plus_mp_quant]        (default: REALQ_REFERENCE_ROOT or /root/reference)
+    python oracle/make_ref.py [/path/to/gptq_plus_mp_quant]
+
+(default: ``REALQ_REFERENCE_ROOT``, else a checkout named ``reference`` beside this repository)
 
 Copied as they are: ``utils/*.py``, ``utils/had_mat.pt`` and ``gptq_utils/*.py`` (the classes import each other
 across these two packages).  Nothing is edited; ``oracle/ref_loader.py`` supplies the same accommodations as the
@@ -19,7 +21,8 @@ DEST = os.path.join(HERE, "_ref")
 
 
 def build(ref_root: str | None = None) -> str | None:
-    ref_root = ref_root or os.environ.get("REALQ_REFERENCE_ROOT", "/root/reference")
+    ref_root = ref_root or os.environ.get("REALQ_REFERENCE_ROOT") or os.path.join(
+        os.path.dirname(os.path.dirname(HERE)), "reference")
     if not os.path.isdir(os.path.join(ref_root, "gptq_utils")):
         return None
     for pkg in ("utils", "gptq_utils"):
