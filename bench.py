@@ -937,6 +937,7 @@ def run_c3(args):
 
     lq = LayerQuantizer(stats_fn, lambda layer, x: layer(x, cos, sin), num_groups=G, alpha=0.25, w_bits=4,
                         hessian_accum_bsz=8, hessian_once=(args.schedule == "all_at_once"),
+                        stage_fns=bm.decoder_layer_stages(cos, sin) if args.c3_forward == "staged" else None,
                         fasterquant_kwargs=dict(groupsize=-1, actorder=True, static_groups=True))
 
     def barrier():
@@ -992,7 +993,10 @@ def run_c3(args):
                           "128 x 2048 uniform-random token ids; stock-PyTorch layer forward feeds the hooks and replays "
                           "the quantized layer; a step is one decoder layer",
               "tokens": NSEQ * T, "hessian_accum_bsz": 8,
-              "schedule": ("sequential module groups, one forward pass over the shard per group plus the replay"
+              "schedule": (("sequential module groups; the layer's forward is cut at the groups and run once per "
+                            "layer (every stage applies the linears quantized before it), its tail is the replay"
+                            if args.c3_forward == "staged" else
+                            "sequential module groups, one forward pass over the shard per group plus the replay")
                            if args.schedule == "sequential" else
                            "one forward pass accumulates all seven Hessians (the reference's layer_hessian_once path), "
                            "then the groups are quantized, then the replay"),
@@ -1141,6 +1145,10 @@ def main():
     ap.add_argument("--profile-steps", dest="profile_steps", type=int, default=0,
                     help="c2: run exactly this many steps and exit (for a profiler's launch list)")
     ap.add_argument("--layers", type=int, default=36, help="c3: number of decoder layers")
+    ap.add_argument("--c3-forward", dest="c3_forward", default="staged", choices=["staged", "passes"],
+                    help="c3: 'staged' cuts the layer's forward at the module groups and keeps what earlier stages "
+                         "produced (one forward per layer in all); 'passes' runs the layer from the top for every "
+                         "group, as a caller without knowledge of the layer must, plus the replay")
     ap.add_argument("--c4-seqs", dest="c4_seqs", type=int, default=256, help="c4_down: calibration sequences in total")
     args = ap.parse_args()
     if args.impl == "reference":

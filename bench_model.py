@@ -87,6 +87,55 @@ class DecoderLayer(torch.nn.Module):
         return x + self.mlp(self.post_attention_layernorm(x))
 
 
+def decoder_layer_stages(cos, sin):
+    """DecoderLayer.forward cut at the inputs of the module groups [q, k, v] -> [o] -> [up, gate] -> [down], for
+    ``LayerQuantizer(stage_fns=...)``: every stage applies the linears of the group before it and everything up to
+    the next group's inputs, exactly the operations of forward() in the same order."""
+
+    def attention_core(attn, h):
+        b, t, _ = h.shape
+        q = attn.q_proj(h).view(b, t, attn.heads, attn.head_dim)
+        k = attn.k_proj(h).view(b, t, attn.kv_heads, attn.head_dim)
+        v = attn.v_proj(h).view(b, t, attn.kv_heads, attn.head_dim)
+        if attn.q_norm is not None:
+            q, k = attn.q_norm(q), attn.k_norm(k)
+        q, k, v = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)
+
+        def rope(u):
+            half = u.shape[-1] // 2
+            rot = torch.cat((-u[..., half:], u[..., :half]), dim=-1)
+            return u * cos + rot * sin
+
+        o = F.scaled_dot_product_attention(rope(q), rope(k), v, is_causal=True, enable_gqa=True)
+        return o.transpose(1, 2).reshape(b, t, attn.heads * attn.head_dim)
+
+    def to_qkv(layer, x):                          # carry: the layer input
+        h = layer.input_layernorm(x)
+        return {"self_attn.q_proj": h, "self_attn.k_proj": h, "self_attn.v_proj": h}, x
+
+    def to_o(layer, x):                            # carry: layer input and the attention output
+        a = attention_core(layer.self_attn, layer.input_layernorm(x))
+        return {"self_attn.o_proj": a}, (x, a)
+
+    def to_gate_up(layer, carry):                  # carry: the residual stream after attention
+        x, a = carry
+        y = x + layer.self_attn.o_proj(a)
+        h = layer.post_attention_layernorm(y)
+        return {"mlp.up_proj": h, "mlp.gate_proj": h}, y
+
+    def to_down(layer, y):                         # carry: residual stream and the rotated down_proj input
+        h = layer.post_attention_layernorm(y)
+        d = F.silu(layer.mlp.gate_proj(h)) * layer.mlp.up_proj(h)
+        d = hu.matmul_hadU_cuda(d, layer.mlp.hadK, layer.mlp.K)
+        return {"mlp.down_proj": d}, (y, d)
+
+    def tail(layer, carry):
+        y, d = carry
+        return y + layer.mlp.down_proj(d)
+
+    return [to_qkv, to_o, to_gate_up, to_down, tail]
+
+
 def rotary_tables(seq_len, head_dim, device, dtype, theta=1_000_000.0):
     inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2, device=device, dtype=torch.float32) / head_dim))
     ang = torch.arange(seq_len, device=device, dtype=torch.float32)[:, None] * inv[None, :]

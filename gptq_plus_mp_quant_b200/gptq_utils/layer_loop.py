@@ -18,7 +18,14 @@ Differences from the reference that a caller can see:
 * a group's calibration pass leaves the layer's forward as soon as the last linear of the group has seen its input
   (the rest of the layer would compute values that nobody reads; the reference runs the layer to the end);
 * ``hessian_once=True`` is the reference's ``layer_hessian_once`` path (:6951, :7041-7100): the Hessians of all
-  linears are accumulated in ONE forward pass of the still unquantized layer, then the groups are quantized.
+  linears are accumulated in ONE forward pass of the still unquantized layer, then the groups are quantized;
+* ``stage_fns`` (optional) lets a caller who knows the layer's structure avoid recomputing what earlier passes
+  already produced: the layer's forward cut at the inputs of every module group.  ``stage_fns[k](layer, carry)``
+  takes what stage k-1 left for one batch (the batch itself for k = 0), applies the linears of group k-1, which are
+  quantized by then, and everything up to the inputs of group k, and returns ``({linear name: input}, carry)``;
+  the last entry, one past the groups, returns the layer's output.  The inputs the linears see are the tensors a
+  pass from the top of the partly quantized layer would compute, bit for bit, so the result is the same; the work
+  is ONE forward of the layer instead of one per group plus the replay.
 """
 from __future__ import annotations
 
@@ -93,8 +100,9 @@ class LayerQuantizer:
 
     def __init__(self, stats_fn, forward_fn, num_groups=4, alpha=0.25, w_bits=4, w_sym=True, w_clip=False,
                  hessian_accum_bsz=8, row_parallel=None, hessian_once=False, groups=None, streams=3,
-                 fasterquant_kwargs=None):
+                 fasterquant_kwargs=None, stage_fns=None):
         self.stats_fn, self.forward_fn = stats_fn, forward_fn
+        self.stage_fns = stage_fns
         self.num_groups, self.alpha = num_groups, alpha
         self.w_bits, self.w_sym, self.w_clip = w_bits, w_sym, w_clip
         self.bsz = hessian_accum_bsz
@@ -167,11 +175,45 @@ class LayerQuantizer:
         e.record()
         return e
 
+    # ------------------------------------------------------------------ one layer, forward cut into stages
+    def _quantize_layer_staged(self, index, layer, inps, outs):
+        full = find_linears(layer)
+        present = [[n for n in grp if n in full] for grp in self.groups]
+        if len(self.stage_fns) != len(self.groups) + 1:
+            raise ValueError(f"stage_fns needs {len(self.groups) + 1} entries (one per module group and the tail), "
+                             f"got {len(self.stage_fns)}")
+        carries = [inps[j:j + self.bsz] for j in range(0, inps.shape[0], self.bsz)]
+        for k, names in enumerate(present):
+            t = self._now()
+            subset = {n: full[n] for n in names}
+            objs = self._build(index, subset) if subset else {}
+            for b in range(len(carries)):
+                fed, carries[b] = self.stage_fns[k](layer, carries[b])
+                for name, obj in objs.items():
+                    obj.add_batch(fed[name].data, None)
+            for obj in objs.values():
+                obj.finalize_hessian()
+            self._span("hessian_pass", t)
+            if subset:
+                t = self._now()
+                self._quantize(objs, subset)
+                self._span("fasterquant", t)
+        t = self._now()
+        if outs is None:
+            outs = torch.empty_like(inps)
+        for b, j in enumerate(range(0, inps.shape[0], self.bsz)):
+            outs[j:j + self.bsz] = self.stage_fns[-1](layer, carries[b])
+            carries[b] = None
+        self._span("replay", t)
+        return outs
+
     # ------------------------------------------------------------------ one layer
     @torch.no_grad()
     def quantize_layer(self, index, layer, inps, outs=None):
         """Quantizes ``layer`` in place from the rank's calibration inputs ``inps`` [n_local, T, hidden] and returns
         the quantized layer's outputs on them (written into ``outs`` when given)."""
+        if self.stage_fns is not None and not self.hessian_once:
+            return self._quantize_layer_staged(index, layer, inps, outs)
         full = find_linears(layer)
         if self.hessian_once:
             t = self._now()
