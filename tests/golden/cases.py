@@ -189,6 +189,13 @@ PLAIN_CASES = [
     ("plain_g256_dynamic_bs256", 32, 512, 3, 96, 4, True, 256, False, False, 256),
 ]
 
+# GPTQ+ with dynamic weight groups the block kernel cannot range itself: name, rows, cols, nseq, seqlen, G,
+# blocksize (= groupsize), shrink-grid search, actorder
+PLUS_DYNAMIC_CASES = [
+    ("plus_dyn_bs256", 32, 512, 4, 160, 2, 256, False, True),
+    ("plus_dyn_bs128_mse", 32, 384, 4, 128, 2, 128, True, False),
+]
+
 PLUS_CASES = [
     # name, rows, cols, nseq, seqlen, G, bits, groupsize, actorder, static, alpha, ref_loss, mode, atomic
     ("plus_frozen_pc", 64, 256, 4, 96, 4, 4, -1, True, True, 0.25, 0.7, "frozen", False),

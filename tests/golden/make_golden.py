@@ -296,6 +296,26 @@ def gen_plus(qu, gpu, out):
         out[f"{name}.Scale"] = np32(layer.scale)
 
 
+def gen_plus_dynamic(qu, gpu, out):
+    for (name, rows, cols, nseq, seqlen, G, bs, mse, act) in cases.PLUS_DYNAMIC_CASES:
+        W = cases.make_weight(rows, cols, seed=43)
+        X = cases.make_acts(nseq, seqlen, cols, seed=43)
+        S = cases.make_saliency(nseq, seqlen, G, seed=43)
+        Gr = cases.make_grad(rows, cols, seed=43)
+        layer = _Lin(W)
+        g = gpu.GPTQPlus(layer, S, Gr, G, 0.25, 0.7)
+        g.quantizer = qu.WeightQuantizer()
+        g.quantizer.configure(4, perchannel=True, sym=True, mse=mse)
+        g.add_batch(X, None)
+        g.finalize_hessian()
+        out[f"{name}.digest"] = np.array(cases.digest(W, X, S, Gr))
+        g.fasterquant(blocksize=bs, percdamp=0.01, groupsize=bs, actorder=act, static_groups=False,
+                      enable_gradient_update=True, g_update_mode="frozen", export_to_et=True)
+        out[f"{name}.Q"] = np32(layer.weight.data)
+        out[f"{name}.W_int"] = np32(layer.int_weight).astype(np.int8)
+        out[f"{name}.Scale"] = np32(layer.scale)
+
+
 def gen_block_gd(qu, gpu, out):
     """g_update_mode="block_gd": optimizer steps on the trailing weights between blocks, driven by the deterministic
     refresh function of cases.make_refresh_fn."""
@@ -399,6 +419,7 @@ def main():
                             ("hadamard.npz", gen_hadamard, (hu,)),
                             ("plain_gptq.npz", gen_plain, (qu, gu)),
                             ("gptq_plus.npz", gen_plus, (qu, gpu)),
+                            ("gptq_plus_dynamic.npz", gen_plus_dynamic, (qu, gpu)),
                             ("block_gd.npz", gen_block_gd, (qu, gpu)),
                             ("faults.npz", gen_faults, (qu, gpu)),
                             ("clip.npz", gen_clip, (qu, gpu)),

@@ -429,6 +429,34 @@ def test_gptqplus_dynamic_groups_ranged_by_the_host(bs, mse):
     assert torch.allclose(layer.weight.data.cpu()[same], ref["Q"][same], rtol=1e-4, atol=0)
 
 
+@pytest.mark.parametrize("case", cases.PLUS_DYNAMIC_CASES, ids=lambda c: c[0])
+def test_gptqplus_host_ranged_groups_vs_reference(golden, case):
+    """The same modes end to end (device Hessian included) against the unmodified reference's output."""
+    from gptq_plus_mp_quant_b200.gptq_utils.gptq_plus_utils import GPTQPlus
+    from gptq_plus_mp_quant_b200.utils.quant_utils import WeightQuantizer
+    (name, rows, cols, nseq, seqlen, G, bs, mse, act) = case
+    g = golden("gptq_plus_dynamic.npz")
+    W = cases.make_weight(rows, cols, seed=43)
+    X = cases.make_acts(nseq, seqlen, cols, seed=43)
+    S = cases.make_saliency(nseq, seqlen, G, seed=43)
+    Gr = cases.make_grad(rows, cols, seed=43)
+    layer = _layer(W)
+    obj = GPTQPlus(layer, S, Gr, G, 0.25, 0.7)
+    obj.quantizer = WeightQuantizer()
+    obj.quantizer.configure(4, perchannel=True, sym=True, mse=mse)
+    obj.add_batch(X.to(DEV), None)
+    obj.finalize_hessian()
+    obj.fasterquant(blocksize=bs, percdamp=0.01, groupsize=bs, actorder=act, static_groups=False, export_to_et=True)
+    codes_ref = torch.from_numpy(g[f"{name}.W_int"]).float()
+    frac, rows_touched, first_off = _code_report(layer.int_weight.cpu(), codes_ref)
+    print(f"{name}: {frac * 100:.4f}% codes differ in {rows_touched} rows; first deviations {first_off[:8]}")
+    assert frac < 0.02
+    same = (layer.int_weight.cpu() == codes_ref).all(dim=1)
+    assert same.float().mean() >= 0.75
+    assert torch.allclose(layer.scale.cpu()[same], torch.from_numpy(g[f"{name}.Scale"])[same], rtol=1e-4, atol=0)
+    assert torch.allclose(layer.weight.data.cpu()[same], torch.from_numpy(g[f"{name}.Q"])[same], rtol=1e-4, atol=0)
+
+
 def _compare_summaries(got, ref, path, rtol):
     """Nested dicts / lists of the diagnostics: same keys, ints and bools equal, floats within rtol."""
     if isinstance(ref, dict):

@@ -132,6 +132,28 @@ def test_gptq_plus(golden, case):
     assert torch.equal(out["Q"], t(g[f"{name}.Q"]))
 
 
+@pytest.mark.parametrize("case", cases.PLUS_DYNAMIC_CASES, ids=lambda c: c[0])
+def test_gptq_plus_dynamic_groups(golden, case):
+    """GPTQ+ with dynamic weight groups as wide as a 256-column block, and with the shrink-grid search."""
+    (name, rows, cols, nseq, seqlen, G, bs, mse, act) = case
+    g = golden("gptq_plus_dynamic.npz")
+    W = cases.make_weight(rows, cols, seed=43)
+    X = cases.make_acts(nseq, seqlen, cols, seed=43)
+    S = cases.make_saliency(nseq, seqlen, G, seed=43)
+    Gr = cases.make_grad(rows, cols, seed=43)
+    assert cases.digest(W, X, S, Gr) == str(g[f"{name}.digest"])
+    acc = ohess.GroupedHessian(cols, S)
+    acc.add_batch(X)
+    acc.finalize()
+    q = oq.OracleWeightQuantizer()
+    q.configure(4, perchannel=True, sym=True, mse=mse)
+    out = ogptq.plus_fasterquant(W, acc.H, acc.act_square, Gr, q, G, 0.25, 0.7, blocksize=bs, percdamp=0.01,
+                                 groupsize=bs, actorder=act, static_groups=False)
+    assert torch.equal(out["W_int"], t(g[f"{name}.W_int"]).float())
+    assert torch.equal(out["Scale"], t(g[f"{name}.Scale"]))
+    assert torch.equal(out["Q"], t(g[f"{name}.Q"]))
+
+
 @pytest.mark.parametrize("case", cases.GD_CASES, ids=lambda c: c[0])
 def test_gptq_plus_block_gd(golden, case):
     """g_update_mode="block_gd" (optimizer steps on the trailing weights between blocks, every regulariser and
