@@ -2,7 +2,8 @@
 """Benchmark of the per-layer GPTQ+ quantization path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--schedule sequential|all_at_once]
-                    [--workload c2|c3|c4_down]
+                    [--workload c2|c3|c4_down] [--layers L] [--c3-forward staged|passes] [--c4-seqs S]
+                    [--profile-steps P] [--no-parity] [--no-cpu]
 
 Prints ONE JSON line.  The default workload (c2) is one Qwen3-8B-shape decoder layer (hidden 4096,
 intermediate 12288, 32 query / 8 KV heads of 128): a step quantizes the layer's four module groups
